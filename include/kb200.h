@@ -1,0 +1,194 @@
+/*
+ * kb200.h -- C ABI of the B200-native kernel library behind Kiln's GPU backend.
+ *
+ * The library replaces what the reference's GPU backend does with generated
+ * Triton source: run the fused kernels of one optimised Kiln graph on the
+ * device, writing into the single planned arena.  The host side (Python,
+ * package kiln_b200) walks the Kiln graph and describes every launch with the
+ * plain-old-data structs below; nothing in this interface is a torch type.
+ *
+ * Threading: a plan is not re-entrant (one arena), exactly like the
+ * reference's GPUExecutable (kiln/gpu/runtime.py:135-136).  All functions
+ * return 0 on success and a negative kb200_status otherwise; the text of the
+ * last failure on the calling thread is returned by kb200_last_error().
+ * Nothing here aborts, throws, synchronises the device or (with the one
+ * documented exception of plan-owned scratch created in kb200_plan_create)
+ * allocates device memory; kb200_plan_launch is therefore capturable into a
+ * CUDA graph.
+ */
+#ifndef KB200_H
+#define KB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KB200_ABI_VERSION 3
+
+#define KB200_MAX_RANK 6      /* iteration dims after the host collapsed contiguous ones */
+#define KB200_MAX_OPERANDS 12 /* distinct tensors one fused kernel touches */
+#define KB200_MAX_TAPE 96     /* scalar ops of one fused kernel */
+
+typedef enum kb200_status {
+  KB200_OK = 0,
+  KB200_ERR_ARGUMENT = -1,    /* malformed descriptor, null pointer, rank/slot out of range */
+  KB200_ERR_UNSUPPORTED = -2, /* well-formed but no kernel covers it (maps to NotImplementedError) */
+  KB200_ERR_BOUNDS = -3,      /* an operand's span leaves the buffer it is bound to */
+  KB200_ERR_CUDA = -4,        /* a CUDA call failed; message carries cudaGetErrorString */
+  KB200_ERR_UNBOUND = -5,     /* launch before kb200_plan_bind */
+  KB200_ERR_DEVICE_WAIT = -6  /* a bounded device-side wait ran out (see kb200_plan_status) */
+} kb200_status;
+
+/* Where a tensor lives.  Mirrors the `bases` keys of the reference's Launch
+ * (kiln/gpu/codegen.py:106-116): ("arena",) ("const", name) ("input", i) ("output", i). */
+typedef enum kb200_base_kind {
+  KB200_BASE_ARENA = 0,
+  KB200_BASE_CONST = 1,
+  KB200_BASE_INPUT = 2,
+  KB200_BASE_OUTPUT = 3
+} kb200_base_kind;
+
+/* Kernel classes: the four kinds the reference writes (kiln/gpu/codegen.py:532-542). */
+typedef enum kb200_kclass {
+  KB200_K_ELEMENTWISE = 0, /* codegen.py:284-310; also copies */
+  KB200_K_ROW = 1,         /* codegen.py:312-430; LayerNorm, softmax, any row-reduction chain */
+  KB200_K_REDUCE = 2,      /* codegen.py:432-482; one reduce over arbitrary dims */
+  KB200_K_MATMUL = 3       /* codegen.py:484-530; batched matmul + fused epilogue */
+} kb200_kclass;
+
+/* Arithmetic mode of a matmul's operands (accumulation is always FP32).
+ * FP32 corresponds to input_precision="ieee", TF32 to "tf32"
+ * (codegen.py:515-516); BF16 is a backend-internal mode with no IR dtype. */
+typedef enum kb200_precision {
+  KB200_PREC_FP32 = 0,
+  KB200_PREC_TF32 = 1,
+  KB200_PREC_BF16 = 2
+} kb200_precision;
+
+/* Scalar op codes of the tape; the table follows _KernelWriter.apply
+ * (codegen.py:223-248) and the prelude formulas (codegen.py:53-88). */
+typedef enum kb200_opcode {
+  KB200_OP_LOAD = 0,   /* a = operand slot */
+  KB200_OP_IMM = 1,    /* imm = float32 literal (codegen.py:98-103) */
+  KB200_OP_ACC = 2,    /* the matmul accumulator element */
+  KB200_OP_ADD = 3, KB200_OP_SUB = 4, KB200_OP_MUL = 5, KB200_OP_DIV = 6,
+  KB200_OP_MAX = 7, KB200_OP_MIN = 8,
+  KB200_OP_NEG = 9, KB200_OP_RELU = 10, KB200_OP_EXP = 11, KB200_OP_TANH = 12,
+  KB200_OP_SIGMOID = 13, KB200_OP_ERF = 14, KB200_OP_GELU_TANH = 15, KB200_OP_GELU_ERF = 16,
+  KB200_OP_RSQRT = 17, KB200_OP_SQRT = 18, KB200_OP_COPY = 19,
+  KB200_OP_RSUM = 20,  /* keepdim sum over the row (last iteration dim); a = value */
+  KB200_OP_RMAX = 21,  /* keepdim max over the row */
+  KB200_OP_STORE = 22  /* a = value, b = operand slot */
+} kb200_opcode;
+
+/* One tape entry.  Entry i defines value i; `a`/`b` name earlier entries
+ * (or, for LOAD/STORE, an operand slot).  `level` is the number of row
+ * reductions on the longest path from the kernel's inputs to this value
+ * (the pass structure of the chunked row kernel, codegen.py:376-380). */
+typedef struct kb200_tape_op {
+  int32_t opcode;
+  int32_t a;
+  int32_t b;
+  int32_t level;
+  float imm;
+} kb200_tape_op;
+
+/* One tensor operand, already aligned to the kernel's iteration space:
+ * stride[d] is the element stride along iteration dim d, 0 where the tensor
+ * broadcasts (codegen.py:212-216 skips those dims the same way).
+ * elem_offset is in float32 elements from the start of the bound buffer;
+ * for the arena it already includes the planned byte offset / 4
+ * (codegen.py:545-549). */
+typedef struct kb200_operand {
+  int32_t base_kind;   /* kb200_base_kind */
+  int32_t base_index;  /* index into consts / inputs / outputs passed to kb200_plan_bind */
+  int64_t elem_offset;
+  int64_t stride[KB200_MAX_RANK];
+} kb200_operand;
+
+/* Iteration spaces, by class:
+ *   ELEMENTWISE  iter_shape = output shape (collapsed); one launch per output.
+ *   ROW          iter_shape = row dims..., inner; the reductions run over the last dim.
+ *   REDUCE       iter_shape = kept dims..., reduced dims...; n_kept says where they split.
+ *   MATMUL       iter_shape = batch, M, N; operands[a_slot].stride = {batch, M, K} strides,
+ *                operands[b_slot].stride = {batch, K, N} strides, every other operand
+ *                (epilogue inputs, outputs) is aligned to {batch, M, N}.
+ */
+typedef struct kb200_kernel_desc {
+  int32_t kclass;      /* kb200_kclass */
+  int32_t precision;   /* kb200_precision; only matmuls look at it */
+  int32_t iter_rank;
+  int32_t n_kept;      /* REDUCE only */
+  int64_t iter_shape[KB200_MAX_RANK];
+  int64_t k_extent;    /* MATMUL only: the contraction length K */
+  int32_t a_slot;      /* MATMUL only */
+  int32_t b_slot;      /* MATMUL only */
+  int32_t n_operands;
+  int32_t n_tape;
+  kb200_operand operands[KB200_MAX_OPERANDS];
+  kb200_tape_op tape[KB200_MAX_TAPE];
+  /* Tuner configuration, opaque to the reference seam (kiln/api.py:155-162):
+   * cfg[0] tile M, cfg[1] tile N, cfg[2] tile K, cfg[3] pipeline stages,
+   * cfg[4] split-K factor, cfg[5] implementation override (0 = library picks),
+   * cfg[6..7] reserved, all 0 = library default. */
+  int32_t cfg[8];
+  char name[32];       /* the Kiln kernel it comes from, e.g. "k3" (diagnostics only) */
+} kb200_kernel_desc;
+
+typedef struct kb200_plan kb200_plan;
+
+/* Library / ABI version; the host side refuses to run against a mismatch. */
+int kb200_version(void);
+
+/* Text of the last error on this thread ("" if none).  Never NULL. */
+const char* kb200_last_error(void);
+
+/* Builds a launch plan for `n` kernels on CUDA device `device`.
+ * Takes the place of kiln.gpu.codegen.generate + load_module
+ * (kiln/gpu/codegen.py:601-614, kiln/gpu/runtime.py:58-79): validates every
+ * descriptor on the host (ranks, slots, tape references), picks the kernel
+ * implementation for each class and returns KB200_ERR_UNSUPPORTED for anything
+ * the reference would raise NotImplementedError on.  The descriptors are copied. */
+int kb200_plan_create(const kb200_kernel_desc* descs, int n, int device, kb200_plan** out);
+
+/* Binds device buffers.  Takes the place of the `bases` resolution in
+ * GPUExecutable._run (kiln/gpu/runtime.py:164-176).  `*_bytes` are the sizes
+ * of the buffers; every operand's offset + span is checked against them here,
+ * on the host, before anything can run.  Buffers stay owned by the caller and
+ * must outlive the launches.  May be called again to re-bind. */
+int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
+                    void* const* consts, const uint64_t* const_bytes, int n_consts,
+                    void* const* inputs, const uint64_t* input_bytes, int n_inputs,
+                    void* const* outputs, const uint64_t* output_bytes, int n_outputs);
+
+/* Enqueues every kernel, in order, on `cuda_stream` (a cudaStream_t).
+ * Takes the place of the launch loop GPUExecutable._run
+ * (kiln/gpu/runtime.py:164-179).  No synchronisation, no allocation. */
+int kb200_plan_launch(kb200_plan* plan, void* cuda_stream);
+
+/* Enqueues kernel `i` alone (profiling, autotuning). */
+int kb200_kernel_launch(kb200_plan* plan, int i, void* cuda_stream);
+
+/* Number of device kernel launches kb200_plan_launch enqueues (a Kiln kernel
+ * may take more than one: packing an operand, then the matmul). */
+int kb200_plan_launch_count(const kb200_plan* plan);
+
+/* Name of the implementation chosen for kernel `i` ("ew_chain_vec4",
+ * "row_layernorm_warp", "mm_tcgen05_tf32", ...).  Never NULL for a valid i. */
+const char* kb200_kernel_impl(const kb200_plan* plan, int i);
+
+/* Reads back the plan's device status word after the caller synchronised:
+ * 0 = ok, otherwise KB200_ERR_DEVICE_WAIT with the kernel index in
+ * kb200_last_error().  Device-side waits are bounded; when one runs out the
+ * kernel records it here and returns normally. */
+int kb200_plan_status(kb200_plan* plan);
+
+/* Frees the plan and any scratch it owns. */
+void kb200_plan_destroy(kb200_plan* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KB200_H */

@@ -1,0 +1,113 @@
+"""Seeded synthetic workloads: the shapes, value distributions and seeds the benchmark is quoted on.
+
+No dataset is involved anywhere on this path; every tensor is drawn from a
+NumPy ``default_rng(seed)`` stream so that the machine that wrote the golden
+fixtures and the machine that runs the GPU tests produce identical bytes.
+
+Parameter names are the module paths the Kiln frontend gives constants
+(``fc.weight``; ``fc.weight.transpose`` after constant folding stores the
+weight as [K, N], kiln/passes/freeze.py:62-68).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+GPT2_SMALL = {"d": 768, "heads": 12}
+
+
+def _normal(rng, shape, std=1.0, mean=0.0):
+    return (rng.standard_normal(shape, dtype=np.float32) * np.float32(std) + np.float32(mean)).astype(np.float32)
+
+
+def causal_mask(t):
+    """[T, T] additive mask: 0 on and below the diagonal, -inf above."""
+    m = np.zeros((t, t), dtype=np.float32)
+    m[np.triu_indices(t, 1)] = -np.inf
+    return m
+
+
+def block_params(seed, t, d=768, heads=12, weight_std=0.02):
+    """GPT-2 style pre-LN block: weights N(0, 0.02), biases 0, LayerNorm gamma 1 / beta 0."""
+    del heads
+    rng = np.random.default_rng(seed)
+    p = {
+        "ln1.weight": np.ones(d, np.float32), "ln1.bias": np.zeros(d, np.float32),
+        "ln2.weight": np.ones(d, np.float32), "ln2.bias": np.zeros(d, np.float32),
+        "c_attn.weight": _normal(rng, (3 * d, d), weight_std), "c_attn.bias": np.zeros(3 * d, np.float32),
+        "c_proj.weight": _normal(rng, (d, d), weight_std), "c_proj.bias": np.zeros(d, np.float32),
+        "fc.weight": _normal(rng, (4 * d, d), weight_std), "fc.bias": np.zeros(4 * d, np.float32),
+        "proj.weight": _normal(rng, (d, 4 * d), weight_std), "proj.bias": np.zeros(d, np.float32),
+        "mask": causal_mask(t),
+    }
+    return p
+
+
+def block_input(seed, t, d=768, index=0):
+    """Input sequence number ``index`` of the seeded stream: [T, d] ~ N(0, 1)."""
+    rng = np.random.default_rng([seed, 1000 + index])
+    return _normal(rng, (t, d))
+
+
+def mlp_params(seed=1, d=768, hidden=3072):
+    """Linear(d, hidden) -> tanh-GELU -> Linear(hidden, d); W ~ N(0, 0.02), b ~ U(-0.01, 0.01)."""
+    rng = np.random.default_rng(seed)
+    u = lambda n: rng.uniform(-0.01, 0.01, n).astype(np.float32)
+    return {"0.weight": _normal(rng, (hidden, d), 0.02), "0.bias": u(hidden),
+            "2.weight": _normal(rng, (d, hidden), 0.02), "2.bias": u(d)}
+
+
+def mlp_input(seed=1, tokens=2048, d=768):
+    return _normal(np.random.default_rng([seed, 1000]), (tokens, d))
+
+
+LINEAR_SHAPES = [(2048, 3072, 768), (128, 2304, 768), (128, 768, 768), (128, 3072, 768), (128, 768, 3072),
+                 (1, 3072, 768)]      # M x N x K
+
+
+def linear_params(m, n, k, seed=2):
+    """A, W ~ N(0, 1/sqrt(K)); bias ~ N(0, 0.01)."""
+    rng = np.random.default_rng([seed, m, n, k])
+    std = 1.0 / np.sqrt(k)
+    return {"weight": _normal(rng, (n, k), std), "bias": _normal(rng, (n,), 0.01)}, _normal(rng, (m, k), std)
+
+
+def bias_gelu_data(seed=3, rows=2048, cols=3072):
+    rng = np.random.default_rng([seed, 0])
+    return {"bias": _normal(rng, (cols,), 0.1)}, _normal(rng, (rows, cols))
+
+
+def layernorm_data(seed=3, rows=2048, d=768):
+    rng = np.random.default_rng([seed, 1])
+    return {"weight": _normal(rng, (d,), 0.1, 1.0), "bias": _normal(rng, (d,), 0.1)}, _normal(rng, (rows, d))
+
+
+def softmax_data(seed=3, shape=(12, 512, 512)):
+    return {}, _normal(np.random.default_rng([seed, 2]), shape, 3.0)
+
+
+def plan_constants(const_shapes, params):
+    """Constant arrays for a plan from module-style parameters.
+
+    ``name.transpose`` is the folded [K, N] copy of ``name`` (constant folding
+    evaluates the transpose at compile time, kiln/passes/freeze.py:57-71).
+    """
+    out = {}
+    for name, shape in const_shapes.items():
+        if name in params:
+            arr = params[name]
+        elif name.endswith(".transpose") and name[:-len(".transpose")] in params:
+            arr = np.ascontiguousarray(params[name[:-len(".transpose")]].T)
+        else:
+            raise KeyError(f"no data for constant {name!r}")
+        arr = np.ascontiguousarray(arr, dtype=np.float32)
+        if tuple(arr.shape) != tuple(shape):
+            raise ValueError(f"constant {name!r}: expected {tuple(shape)}, got {arr.shape}")
+        out[name] = arr
+    return out
+
+
+def block_flops(t, d=768, heads=12):
+    """Algorithmic FLOPs of one block call as the reference computes it (full T x T attention)."""
+    del heads
+    return 2 * t * d * (3 * d) + 2 * t * d * d + 2 * 2 * t * d * (4 * d) + 2 * 2 * t * t * d
