@@ -1,0 +1,381 @@
+"""Benchmark of the B200 GPU backend on the reference's headline workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--precision bf16|tf32|fp32]
+
+Workload (one "step"): 64 independent sequences of 1024 tokens through the GPT-2-small
+transformer block (d_model 768, 12 heads, pre-LN, causal attention, tanh-GELU MLP), weights
+N(0, 0.02), inputs N(0, 1), seed 4 -- synthetic tensors of the benchmark's shapes.  Every rank
+(one process per GPU, independent replicas, no collective on the data path) processes its own
+64 sequences per step, so the job is weak-scaled: tokens/s = N * 64 * 1024 / step time.
+
+Two timed regions, both K steps bracketed by barrier + synchronize, CUDA events, max over ranks:
+  value  inputs already resident in HBM; each sequence is copied device-to-device into the
+         executable's static input, the captured CUDA graph is replayed, the result copied out.
+  e2e    the public call ``executable(x)`` with pinned host tensors: host-to-device copy of every
+         sequence and device-to-host read of every result inside the timed region.
+A step touches 64 x 3 MiB of inputs plus a 105 MiB arena, more than the 126 MB L2, so no explicit
+L2 flush is needed between iterations; the weights (14-28 MB) stay L2-resident, as in serving.
+
+--impl reference times the CPU implementation of the same block (eager PyTorch float32 on the
+host cores, the stand-in for the reference's MLIR CPU backend, see oracle/torch_block.py) on a
+bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT / "kiln-compiler_b200", ROOT, ROOT / "tests"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+SEQS, TOKENS, D, HEADS, SEED = 64, 1024, 768, 12, 4
+METRIC, UNIT = "gpt2_block_tokens_per_s", "tokens/s"
+
+
+def peaks():
+    try:
+        return json.loads((ROOT / "MEASURED_PEAKS.json").read_text()), "measured"
+    except (OSError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, r[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n):
+    """Process group only for the barrier and the max-over-ranks of the timings."""
+    import torch.distributed as dist
+
+    if n <= 1 or "RANK" not in os.environ:
+        return None, 0, 1, 0
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    backend = "nccl" if torch.cuda.is_available() else "gloo"
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    return dist, rank, world, local
+
+
+def barrier(dist):
+    if dist is not None:
+        dist.barrier()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def max_over_ranks(dist, ms):
+    if dist is None:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm
+# ---------------------------------------------------------------------------------------------
+
+def cpu_block_tokens_per_s(seconds_budget=12.0, threads=None):
+    """Eager-PyTorch float32 block on the host cores, on a bounded sample of the workload."""
+    from kiln_b200 import workloads as W
+    from oracle.torch_block import block_forward, to_torch
+
+    if threads:
+        torch.set_num_threads(threads)
+    p = to_torch(W.block_params(SEED, TOKENS))
+    xs = [torch.from_numpy(W.block_input(SEED, TOKENS, index=i)) for i in range(2)]
+    with torch.no_grad():
+        block_forward(p, xs[0], HEADS)
+        done, t0 = 0, time.perf_counter()
+        while True:
+            block_forward(p, xs[done % 2], HEADS)
+            done += 1
+            if time.perf_counter() - t0 > seconds_budget or done >= SEQS:
+                break
+        dt = time.perf_counter() - t0
+    return done * TOKENS / dt, done, torch.get_num_threads()
+
+
+def reference_arm(args, dist, rank):
+    if rank != 0:
+        return
+    values = []
+    for _ in range(args.warmup + args.steps):
+        v, done, cores = cpu_block_tokens_per_s(seconds_budget=max(2.0, 60.0 / (args.warmup + args.steps)))
+        values.append(v)
+    value = float(np.mean(values[args.warmup:]))
+    sample = f"{done} of {SEQS} sequences x {TOKENS} tokens per step, eager PyTorch float32 (oneDNN)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": SEQS * TOKENS / value * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config("fp32", 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(precision, n):
+    return {"workload": f"GPT-2-small block (d_model {D}, {HEADS} heads), {SEQS} sequences x {TOKENS} tokens per GPU "
+                        f"per step, independent replicas", "sequences_per_gpu": SEQS, "tokens": TOKENS,
+            "precision": precision, "parallelism": f"replicas x{n}", "l2": "inputs larger than L2 (no flush)",
+            "seed": SEED}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+def build_block(precision, tokens, seed, cuda_graphs=True):
+    from helpers import load_plan
+    from kiln_b200 import workloads as W
+    from kiln_b200.codegen import program_from_plan
+    from kiln_b200.runtime import GPUExecutable
+    from kiln_b200.spec import PlanSpec
+
+    plan = PlanSpec.from_json(load_plan(f"gpt2_block_t{tokens}"))
+    consts = W.plan_constants(plan.const_shapes, W.block_params(seed, tokens))
+    program = program_from_plan(plan, precision)
+    return GPUExecutable(program, plan.arena_bytes, consts, plan.input_shapes, plan.output_shapes,
+                         cuda_graphs=cuda_graphs), plan
+
+
+def time_region(dist, fn, steps):
+    barrier(dist)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    barrier(dist)
+    return max_over_ranks(dist, start.elapsed_time(end))
+
+
+def kernel_flops(kernel):
+    """Algorithmic FLOPs (matmul) and bytes (everything) of one plan kernel."""
+    flops, byts = 0, 0
+    for o in kernel.inputs:
+        byts += 4 * int(np.prod(o.shape))
+    for _, o in kernel.outputs:
+        byts += 4 * int(np.prod(o.shape))
+    for n in kernel.nodes:
+        if n.op == "matmul":
+            a = kernel.inputs[n.inputs[0][1]]
+            flops += 2 * int(np.prod(n.shape)) * a.shape[-1]
+    return flops, byts
+
+
+def roofline_of(exe, plan, precision, iters=20):
+    """Per-launch CUDA-event times of every kernel; roofline of the one with the largest share."""
+    pk, pk_kind = peaks()
+    times = exe.profile(exe.static_inputs[0], iters=iters)
+    total = sum(ms for _, ms in times)
+    i = max(range(len(times)), key=lambda j: times[j][1])
+    name, ms = times[i]
+    kernel = plan.kernels[exe.program.launches[i].kernel_index]
+    flops, byts = kernel_flops(kernel)
+    if flops:
+        achieved, unit, bound = flops / (ms * 1e-3) / 1e12, "TFLOP/s", "tensor"
+        peak = pk["bf16_tflops"] if precision == "bf16" else pk["bf16_tflops"] / 2
+        peak_note = f"{pk_kind} bf16 burst" + ("" if precision == "bf16" else " / 2 (tf32 and fp32 tensor rate)")
+    else:
+        achieved, unit, bound, peak, peak_note = byts / (ms * 1e-3) / 1e9, "GB/s", "hbm", pk["hbm_gbs"], f"{pk_kind} copy"
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "traffic": None, "kernel": f"{name} ({exe.impls[i]})", "ms_per_launch": ms, "share": ms / total,
+            "peak_source": peak_note,
+            "per_kernel_ms": {n: round(t, 5) for n, t in times}}
+
+
+def extras(precision):
+    """The reference's other headline numbers: block latency, Linear TFLOP/s, fused-op GB/s."""
+    from gpu_helpers import build_executable
+    from kiln_b200.runtime import kernel_seconds
+
+    out = {}
+    for case, byts in (("bias_gelu_2048x3072", 50343936), ("layernorm_2048x768", 12589056),
+                       ("softmax_12x512x512", 25165824)):
+        exe = build_executable(case, "fp32", cuda_graphs=False)
+        out[case] = {"warm_gbs": round(byts / kernel_seconds(exe.run_static) / 1e9, 1), "impl": exe.impls}
+        exe.close()
+    from kiln_b200 import workloads as W
+    mm_prec = precision if precision != "fp32" else "fp32"
+    for m, n, k in W.LINEAR_SHAPES:
+        exe = build_executable(f"linear_{m}x{n}x{k}", mm_prec, cuda_graphs=False)
+        out[f"linear_{m}x{n}x{k}"] = {"tflops": round(2 * m * n * k / kernel_seconds(exe.run_static) / 1e12, 2),
+                                      "precision": mm_prec, "impl": exe.impls}
+        exe.close()
+    for t, seed in ((128, 0), (2048, 4)):
+        exe, _ = build_block(precision, t, seed)
+        x = torch.randn(t, D).pin_memory()
+        for _ in range(5):
+            exe(x)
+        torch.cuda.synchronize()
+        lat = []
+        for _ in range(50):
+            t0 = time.perf_counter()
+            y = exe(x)[0]
+            y.cpu()
+            lat.append((time.perf_counter() - t0) * 1e3)
+        out[f"block_t{t}"] = {"e2e_p50_ms": round(float(np.median(lat)), 4),
+                              "kernel_ms": round(kernel_seconds(exe.run_static) * 1e3, 4)}
+        exe.close()
+    return out
+
+
+def dtype_of(precision, impls):
+    """The arithmetic the matmuls really ran in: the tensor-core kernels take tf32 / bf16 operands,
+    every other kernel (and every accumulation) is float32."""
+    if precision == "fp32" or not any(i == "mm_tcgen05" for i in impls):
+        return "f32"
+    return precision
+
+
+def gpu_arm(args, dist, rank, world, local):
+    from kiln_b200 import workloads as W
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    precision = args.precision
+    exe, plan = build_block(precision, TOKENS, SEED)
+    host = [torch.from_numpy(W.block_input(SEED, TOKENS, index=rank * SEQS + i)).pin_memory() for i in range(SEQS)]
+    dev_in = torch.stack([h.cuda(non_blocking=True) for h in host])
+    dev_out = torch.empty_like(dev_in)
+    host_out = [torch.empty(TOKENS, D).pin_memory() for _ in range(SEQS)]
+    torch.cuda.synchronize()
+
+    def step_resident():
+        for i in range(SEQS):
+            exe.static_inputs[0].copy_(dev_in[i], non_blocking=True)
+            exe.run_static()
+            dev_out[i].copy_(exe.static_outputs[0], non_blocking=True)
+
+    def step_e2e():
+        for i in range(SEQS):
+            (y,) = exe(host[i])
+            host_out[i].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_resident()
+    with ClockSampler(local) as clocks:
+        ms = time_region(dist, step_resident, args.steps)
+    exe.status()
+    for _ in range(max(1, args.warmup // 2)):
+        step_e2e()
+    ms_e2e = time_region(dist, step_e2e, args.steps)
+    tokens = world * SEQS * TOKENS * args.steps
+    value, e2e_value = tokens / (ms * 1e-3), tokens / (ms_e2e * 1e-3)
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": dtype_of(precision, exe.impls), "data": "synthetic",
+        "config": workload_config(precision, world),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": SEQS * TOKENS * D * 4,
+                "d2h_bytes_per_step": SEQS * TOKENS * D * 4, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": args.steps * SEQS * exe.device_launches,
+        "clocks": clocks.summary(),
+        "impls": dict(zip(exe.kernel_names, exe.impls)),
+    }
+    line["roofline"] = roofline_of(exe, plan, precision)
+    if world == 1:
+        v, done, cores = cpu_block_tokens_per_s(seconds_budget=12.0)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"{done} of {SEQS} sequences x {TOKENS} tokens, eager PyTorch float32 (oneDNN)"}
+        if not args.no_extras:
+            try:
+                line["extras"] = extras(precision)
+            except Exception as err:   # noqa: BLE001  (extras never invalidate the headline line)
+                line["extras"] = {"error": f"{type(err).__name__}: {err}"[:200]}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default=os.environ.get("KB200_BENCH_PRECISION", "bf16"),
+                    choices=["fp32", "tf32", "bf16"])
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", 0))
+        reference_arm(args, None, rank)
+        return
+    dist, rank, world, local = dist_setup(args.gpus)
+    try:
+        gpu_arm(args, dist, rank, world, local)
+    finally:
+        if dist is not None:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,290 @@
+// Elementwise kernels: fused chains of scalar ops over strided / broadcast operands, and copies.
+// Role of the reference's `elementwise` generator (kiln/gpu/codegen.py:284-310).
+//
+//   ew_generic      any tape, any strides: one element per thread, values in a per-thread file.
+//   ew_chain_vec4   the tape is a chain and every operand is contiguous (or constant) along the
+//                   innermost dim: 128-bit loads/stores, the running value stays in registers.
+//                   HBM-bound: reads each input once, writes the output once.
+//   ew_transpose    a chain whose first input is contiguous along a different dim than the output
+//                   (head-split K^T copy, unfrozen weight transposes): 32x32 tiles through shared
+//                   memory so both the read and the write are coalesced.
+#include "device_math.cuh"
+#include "kb200_internal.h"
+
+namespace kb200 {
+
+struct EwParams {
+  int rank;
+  int n_operands;
+  int64_t numel;
+  int64_t shape[KB200_MAX_RANK];
+  DevOperand ops[KB200_MAX_OPERANDS];
+  DevTape tape;
+};
+
+__global__ void __launch_bounds__(256) ew_generic_kernel(const __grid_constant__ EwParams p) {
+  float r[KB200_MAX_TAPE];
+  int64_t off[KB200_MAX_OPERANDS];
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < p.numel; idx += step) {
+    for (int o = 0; o < p.n_operands; ++o) off[o] = 0;
+    int64_t rest = idx;
+    for (int d = p.rank - 1; d >= 0; --d) {
+      int64_t i = rest % p.shape[d];
+      rest /= p.shape[d];
+      for (int o = 0; o < p.n_operands; ++o) off[o] += i * p.ops[o].stride[d];
+    }
+    for (int t = 0; t < p.tape.n; ++t) {
+      const kb200_tape_op op = p.tape.ops[t];
+      switch (op.opcode) {
+        case KB200_OP_LOAD: r[t] = p.ops[op.a].ptr[off[op.a]]; break;
+        case KB200_OP_IMM: r[t] = op.imm; break;
+        case KB200_OP_STORE: p.ops[op.b].ptr[off[op.b]] = r[op.a]; break;
+        default: r[t] = apply_op(op.opcode, r[op.a], r[op.b]); break;
+      }
+    }
+  }
+}
+
+// ---- vectorised chain ----
+constexpr int kVecRank = 4;
+
+struct EwChainParams {
+  int rank;                      // <= kVecRank; last dim counted in float4
+  int64_t nvec;
+  int64_t shape[kVecRank];       // last entry = inner / 4
+  DevOperand ops[KB200_MAX_OPERANDS];   // strides in elements; inner stride is 1 (vector) or 0 (scalar)
+  Chain chain;
+};
+
+__device__ __forceinline__ int64_t ew_offset(const EwChainParams& p, int slot, const int64_t* idx) {
+  int64_t off = 0;
+#pragma unroll
+  for (int d = 0; d < kVecRank; ++d)
+    if (d < p.rank) off += idx[d] * p.ops[slot].stride[d] * (d == p.rank - 1 ? 4 : 1);
+  return off;
+}
+
+__device__ __forceinline__ float4 ew_load4(const EwChainParams& p, int slot, const int64_t* idx) {
+  const float* ptr = p.ops[slot].ptr + ew_offset(p, slot, idx);
+  if (p.ops[slot].stride[p.rank - 1] == 0) {
+    float s = __ldg(ptr);
+    return make_float4(s, s, s, s);
+  }
+  return *reinterpret_cast<const float4*>(ptr);
+}
+
+template <int U>
+__global__ void __launch_bounds__(256) ew_chain_vec4_kernel(const __grid_constant__ EwChainParams p) {
+  const int64_t step = (int64_t)gridDim.x * blockDim.x * U;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x * U + threadIdx.x; base < p.nvec; base += step) {
+    float4 v[U];
+    int64_t idx[U][kVecRank];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      int64_t i = base + (int64_t)u * blockDim.x;
+      live[u] = i < p.nvec;
+      int64_t rest = live[u] ? i : 0;
+#pragma unroll
+      for (int d = kVecRank - 1; d >= 0; --d) {
+        if (d < p.rank) {
+          idx[u][d] = rest % p.shape[d];
+          rest /= p.shape[d];
+        } else {
+          idx[u][d] = 0;
+        }
+      }
+      if (live[u]) v[u] = ew_load4(p, p.chain.first_slot, idx[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      for (int s = 0; s < p.chain.n; ++s) {
+        const ChainStep st = p.chain.steps[s];
+        float4 side = make_float4(st.imm, st.imm, st.imm, st.imm);
+        if (st.slot >= 0) side = ew_load4(p, st.slot, idx[u]);
+        v[u].x = apply_chain(st.op, v[u].x, side.x);
+        v[u].y = apply_chain(st.op, v[u].y, side.y);
+        v[u].z = apply_chain(st.op, v[u].z, side.z);
+        v[u].w = apply_chain(st.op, v[u].w, side.w);
+      }
+      *reinterpret_cast<float4*>(p.ops[p.chain.out_slot].ptr + ew_offset(p, p.chain.out_slot, idx[u])) = v[u];
+    }
+  }
+}
+
+// ---- tiled transpose + chain ----
+struct EwTransposeParams {
+  int rank;                      // 2..kVecRank
+  int tdim;                      // the dim along which the first input is contiguous (!= rank - 1)
+  int64_t shape[kVecRank];
+  int64_t outer;                 // product of the dims other than tdim and the last
+  DevOperand ops[KB200_MAX_OPERANDS];
+  Chain chain;
+};
+
+__global__ void __launch_bounds__(256) ew_transpose_kernel(const __grid_constant__ EwTransposeParams p) {
+  __shared__ float tile[32][33];
+  const int last = p.rank - 1;
+  const int64_t n_t = p.shape[p.tdim], n_l = p.shape[last];
+  const int64_t tiles_l = (n_l + 31) / 32, tiles_t = (n_t + 31) / 32;
+  const int64_t total = tiles_l * tiles_t * p.outer;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  for (int64_t tile_id = blockIdx.x; tile_id < total; tile_id += gridDim.x) {
+    int64_t rest = tile_id;
+    const int64_t tl = rest % tiles_l; rest /= tiles_l;
+    const int64_t tt = rest % tiles_t; rest /= tiles_t;
+    int64_t idx[kVecRank] = {0, 0, 0, 0};
+#pragma unroll
+    for (int d = kVecRank - 1; d >= 0; --d) {
+      if (d < p.rank && d != p.tdim && d != last) {
+        idx[d] = rest % p.shape[d];
+        rest /= p.shape[d];
+      }
+    }
+    int64_t in_base = 0;
+#pragma unroll
+    for (int d = 0; d < kVecRank; ++d)
+      if (d < p.rank) in_base += idx[d] * p.ops[p.chain.first_slot].stride[d];
+    const int64_t s_t = p.ops[p.chain.first_slot].stride[p.tdim], s_l = p.ops[p.chain.first_slot].stride[last];
+    // read: threads run along tdim (contiguous in the input)
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      int64_t it = tt * 32 + tx, il = tl * 32 + ty + j;
+      if (it < n_t && il < n_l) tile[ty + j][tx] = p.ops[p.chain.first_slot].ptr[in_base + it * s_t + il * s_l];
+    }
+    __syncthreads();
+    // write: threads run along the last dim (contiguous in the output)
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      int64_t it = tt * 32 + ty + j, il = tl * 32 + tx;
+      if (it < n_t && il < n_l) {
+        idx[p.tdim] = it;
+        idx[last] = il;
+        float v = tile[tx][ty + j];
+        for (int s = 0; s < p.chain.n; ++s) {
+          const ChainStep st = p.chain.steps[s];
+          float side = st.imm;
+          if (st.slot >= 0) {
+            int64_t off = 0;
+#pragma unroll
+            for (int d = 0; d < kVecRank; ++d)
+              if (d < p.rank) off += idx[d] * p.ops[st.slot].stride[d];
+            side = p.ops[st.slot].ptr[off];
+          }
+          v = apply_chain(st.op, v, side);
+        }
+        int64_t off = 0;
+#pragma unroll
+        for (int d = 0; d < kVecRank; ++d)
+          if (d < p.rank) off += idx[d] * p.ops[p.chain.out_slot].stride[d];
+        p.ops[p.chain.out_slot].ptr[off] = v;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+
+static bool chain_slots(const Chain& c, int* slots, int* n) {
+  *n = 0;
+  if (c.first_slot < 0) return false;
+  slots[(*n)++] = c.first_slot;
+  for (int s = 0; s < c.n; ++s)
+    if (c.steps[s].slot >= 0) slots[(*n)++] = c.steps[s].slot;
+  slots[(*n)++] = c.out_slot;
+  return true;
+}
+
+int choose_elementwise(Plan& plan, PlanKernel& k) {
+  (void)plan;
+  const kb200_kernel_desc& d = k.desc;
+  k.impl = IMPL_EW_GENERIC;
+  k.launches = 1;
+  k.has_chain = extract_chain(d, &k.chain);
+  if (!k.has_chain || d.iter_rank > kVecRank) return KB200_OK;
+  int slots[kMaxChain + 2], n_slots;
+  if (!chain_slots(k.chain, slots, &n_slots)) return KB200_OK;
+  const int last = d.iter_rank - 1;
+  const int64_t inner = d.iter_shape[last];
+  // vec4: every operand contiguous or constant along the innermost dim, everything 16-byte aligned
+  bool vec = inner % 4 == 0;
+  for (int i = 0; i < n_slots && vec; ++i) {
+    const DevOperand& o = k.ops[slots[i]];
+    const bool is_out = slots[i] == k.chain.out_slot;
+    if (o.stride[last] == 1) {
+      vec = (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0;
+      for (int dd = 0; dd < last && vec; ++dd) vec = o.stride[dd] % 4 == 0;
+    } else if (o.stride[last] == 0 && !is_out) {
+      // scalar along the row: fine
+    } else {
+      vec = false;
+    }
+  }
+  if (vec) {
+    k.impl = IMPL_EW_CHAIN_VEC4;
+    return KB200_OK;
+  }
+  // transpose: output contiguous along the last dim, first input contiguous along another one
+  const DevOperand& in = k.ops[k.chain.first_slot];
+  const DevOperand& out = k.ops[k.chain.out_slot];
+  if (d.iter_rank >= 2 && out.stride[last] == 1 && in.stride[last] != 1) {
+    for (int t = 0; t < last; ++t) {
+      if (in.stride[t] == 1 && d.iter_shape[t] >= 8 && inner >= 8) {
+        k.impl = IMPL_EW_TRANSPOSE;
+        k.x_slot = t;   // reused field: the input's contiguous dim
+        return KB200_OK;
+      }
+    }
+  }
+  return KB200_OK;
+}
+
+int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
+  const kb200_kernel_desc& d = k.desc;
+  const int64_t numel = numel_of(d);
+  if (k.impl == IMPL_EW_CHAIN_VEC4) {
+    EwChainParams p{};
+    p.rank = d.iter_rank;
+    for (int i = 0; i < d.iter_rank; ++i) p.shape[i] = d.iter_shape[i];
+    p.shape[d.iter_rank - 1] /= 4;
+    p.nvec = numel / 4;
+    for (int o = 0; o < d.n_operands; ++o) p.ops[o] = k.ops[o];
+    p.chain = k.chain;
+    constexpr int U = 2;
+    int64_t blocks = (p.nvec + 256 * U - 1) / (256 * U);
+    int64_t cap = (int64_t)plan.sm_count * 16;
+    ew_chain_vec4_kernel<U><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(p);
+  } else if (k.impl == IMPL_EW_TRANSPOSE) {
+    EwTransposeParams p{};
+    p.rank = d.iter_rank;
+    p.tdim = k.x_slot;
+    p.outer = 1;
+    for (int i = 0; i < d.iter_rank; ++i) {
+      p.shape[i] = d.iter_shape[i];
+      if (i != p.tdim && i != d.iter_rank - 1) p.outer *= d.iter_shape[i];
+    }
+    for (int o = 0; o < d.n_operands; ++o) p.ops[o] = k.ops[o];
+    p.chain = k.chain;
+    int64_t tiles = ((p.shape[p.tdim] + 31) / 32) * ((p.shape[p.rank - 1] + 31) / 32) * p.outer;
+    int64_t cap = (int64_t)plan.sm_count * 16;
+    ew_transpose_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 256, 0, s>>>(p);
+  } else {
+    EwParams p{};
+    p.rank = d.iter_rank;
+    p.n_operands = d.n_operands;
+    p.numel = numel;
+    for (int i = 0; i < d.iter_rank; ++i) p.shape[i] = d.iter_shape[i];
+    for (int o = 0; o < d.n_operands; ++o) p.ops[o] = k.ops[o];
+    p.tape = k.tape;
+    int64_t blocks = (numel + 255) / 256;
+    int64_t cap = (int64_t)plan.sm_count * 8;
+    ew_generic_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(p);
+  }
+  KB200_CUDA(cudaGetLastError());
+  return KB200_OK;
+}
+
+}  // namespace kb200

@@ -1,0 +1,122 @@
+// Internal declarations shared by the translation units of libkb200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "kb200.h"
+
+namespace kb200 {
+
+// ---- error reporting (thread-local text behind kb200_last_error) ----
+int fail(int status, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define KB200_CUDA(call)                                   \
+  do {                                                     \
+    cudaError_t e_ = (call);                               \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #call);    \
+  } while (0)
+
+// ---- device-side views of a descriptor ----
+struct DevOperand {
+  float* ptr;  // base + elem_offset, resolved at bind
+  int64_t stride[KB200_MAX_RANK];
+};
+
+struct DevTape {
+  int n;
+  kb200_tape_op ops[KB200_MAX_TAPE];
+};
+
+// A fused elementwise chain in "running value" form: v = f_i(v, side_i).  Extracted from the
+// tape when every value feeds only the next op; lets the vectorised kernels keep v in registers.
+enum ChainOp : int {
+  CH_ADD = 0, CH_SUB, CH_RSUB, CH_MUL, CH_DIV, CH_RDIV, CH_MAX, CH_MIN,
+  CH_NEG, CH_RELU, CH_EXP, CH_TANH, CH_SIGMOID, CH_ERF, CH_GELU_TANH, CH_GELU_ERF, CH_RSQRT, CH_SQRT, CH_COPY
+};
+constexpr int kMaxChain = 8;
+struct ChainStep {
+  int op;     // ChainOp
+  int slot;   // operand slot of the side input, -1 = immediate, -2 = unary
+  float imm;
+};
+struct Chain {
+  int n;
+  int first_slot;  // operand slot of the initial value; -1 = the matmul accumulator
+  int out_slot;
+  ChainStep steps[kMaxChain];
+};
+
+// What the library decided for one descriptor.
+enum Impl : int {
+  IMPL_EW_GENERIC = 0,
+  IMPL_EW_CHAIN_VEC4,
+  IMPL_EW_TRANSPOSE,
+  IMPL_ROW_GENERIC,
+  IMPL_ROW_LAYERNORM,
+  IMPL_ROW_SOFTMAX,
+  IMPL_REDUCE_GENERIC,
+  IMPL_MM_SIMT,
+  IMPL_MM_GEMV,
+  IMPL_MM_TC,
+  IMPL_COUNT
+};
+const char* impl_name(int impl);
+
+struct PlanKernel {
+  kb200_kernel_desc desc;
+  int impl = 0;
+  int launches = 1;
+  DevOperand ops[KB200_MAX_OPERANDS];
+  DevTape tape;
+  Chain chain;          // valid when the impl uses it
+  bool has_chain = false;
+  // row specialisations
+  int x_slot = -1, g_slot = -1, b_slot = -1, out_slot = -1;
+  float ln_inv_n = 0.f, ln_eps = 0.f;
+  // matmul
+  int64_t batch = 1, M = 0, N = 0, K = 0;
+  void* tc = nullptr;   // tensor-core state (tensor maps, packed operands), owned by matmul_tc.cu
+};
+
+struct Plan {
+  int device = 0;
+  int sm_count = 148;
+  bool bound = false;
+  std::vector<PlanKernel> kernels;
+  int* d_status = nullptr;       // device status word for bounded waits
+  // bound buffers (for re-validation and the tensor-core path)
+  float* arena = nullptr;
+  uint64_t arena_bytes = 0;
+  std::vector<float*> consts, inputs, outputs;
+  std::vector<uint64_t> const_bytes, input_bytes, output_bytes;
+};
+
+// ---- tape analysis (host) ----
+bool extract_chain(const kb200_kernel_desc& d, Chain* out);
+bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k);
+bool match_softmax(const kb200_kernel_desc& d, PlanKernel* k);
+
+// ---- per-class entry points ----
+int choose_elementwise(Plan& plan, PlanKernel& k);
+int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s);
+int choose_row(Plan& plan, PlanKernel& k);
+int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s);
+int choose_reduce(Plan& plan, PlanKernel& k);
+int launch_reduce(const Plan& plan, const PlanKernel& k, cudaStream_t s);
+int choose_matmul(Plan& plan, PlanKernel& k);
+int bind_matmul(Plan& plan, PlanKernel& k);      // after pointers are resolved
+int launch_matmul(const Plan& plan, const PlanKernel& k, cudaStream_t s);
+void destroy_matmul(PlanKernel& k);
+
+inline int64_t numel_of(const kb200_kernel_desc& d) {
+  int64_t n = 1;
+  for (int i = 0; i < d.iter_rank; ++i) n *= d.iter_shape[i];
+  return n;
+}
+
+}  // namespace kb200

@@ -1,0 +1,518 @@
+// The C ABI of libkb200.so: descriptor validation, buffer binding with bounds checks, launch
+// dispatch.  Declared and documented in include/kb200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "kb200_internal.h"
+
+#define KB200_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace kb200 {
+
+static thread_local std::string g_error;
+
+int fail(int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_error = buf;
+  return status;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(KB200_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+const char* impl_name(int impl) {
+  static const char* names[IMPL_COUNT] = {
+      "ew_generic", "ew_chain_vec4", "ew_transpose", "row_generic", "row_layernorm", "row_softmax",
+      "reduce_generic", "mm_simt_fp32", "mm_gemv", "mm_tcgen05"};
+  return impl >= 0 && impl < IMPL_COUNT ? names[impl] : "?";
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tape analysis
+// ---------------------------------------------------------------------------------------------
+
+static bool is_binary(int op) { return op >= KB200_OP_ADD && op <= KB200_OP_MIN; }
+static bool is_unary(int op) { return op >= KB200_OP_NEG && op <= KB200_OP_COPY; }
+static bool is_reduce(int op) { return op == KB200_OP_RSUM || op == KB200_OP_RMAX; }
+
+static void use_counts(const kb200_kernel_desc& d, int* uses) {
+  for (int i = 0; i < d.n_tape; ++i) uses[i] = 0;
+  for (int i = 0; i < d.n_tape; ++i) {
+    const kb200_tape_op& t = d.tape[i];
+    if (is_binary(t.opcode)) { uses[t.a]++; uses[t.b]++; }
+    else if (is_unary(t.opcode) || is_reduce(t.opcode) || t.opcode == KB200_OP_STORE) uses[t.a]++;
+  }
+}
+
+static int chain_unary(int op) {
+  switch (op) {
+    case KB200_OP_NEG: return CH_NEG;
+    case KB200_OP_RELU: return CH_RELU;
+    case KB200_OP_EXP: return CH_EXP;
+    case KB200_OP_TANH: return CH_TANH;
+    case KB200_OP_SIGMOID: return CH_SIGMOID;
+    case KB200_OP_ERF: return CH_ERF;
+    case KB200_OP_GELU_TANH: return CH_GELU_TANH;
+    case KB200_OP_GELU_ERF: return CH_GELU_ERF;
+    case KB200_OP_RSQRT: return CH_RSQRT;
+    case KB200_OP_SQRT: return CH_SQRT;
+    default: return CH_COPY;
+  }
+}
+
+static int chain_binary(int op, bool reversed) {
+  switch (op) {
+    case KB200_OP_ADD: return CH_ADD;
+    case KB200_OP_SUB: return reversed ? CH_RSUB : CH_SUB;
+    case KB200_OP_MUL: return CH_MUL;
+    case KB200_OP_DIV: return reversed ? CH_RDIV : CH_DIV;
+    case KB200_OP_MAX: return CH_MAX;
+    default: return CH_MIN;
+  }
+}
+
+// A tape is a chain when it has one STORE and every computed value feeds exactly the next op.
+bool extract_chain(const kb200_kernel_desc& d, Chain* out) {
+  int uses[KB200_MAX_TAPE];
+  use_counts(d, uses);
+  int store = -1, n_ops = 0;
+  for (int i = 0; i < d.n_tape; ++i) {
+    int op = d.tape[i].opcode;
+    if (op == KB200_OP_STORE) {
+      if (store >= 0) return false;
+      store = i;
+    } else if (is_reduce(op)) {
+      return false;
+    } else if (is_binary(op) || is_unary(op)) {
+      ++n_ops;
+    }
+  }
+  if (store < 0 || n_ops > kMaxChain) return false;
+  ChainStep rev[kMaxChain];
+  int n = 0;
+  int cur = d.tape[store].a;
+  auto leaf_side = [&](int i) { int o = d.tape[i].opcode; return o == KB200_OP_LOAD || o == KB200_OP_IMM; };
+  auto leaf = [&](int i) { return leaf_side(i) || d.tape[i].opcode == KB200_OP_ACC; };
+  auto side_of = [&](int i, ChainStep* s) {
+    if (d.tape[i].opcode == KB200_OP_IMM) { s->slot = -1; s->imm = d.tape[i].imm; }
+    else { s->slot = d.tape[i].a; s->imm = 0.f; }
+  };
+  while (true) {
+    const kb200_tape_op& e = d.tape[cur];
+    if (e.opcode == KB200_OP_LOAD) { out->first_slot = e.a; break; }
+    if (e.opcode == KB200_OP_ACC) { out->first_slot = -1; break; }
+    if (e.opcode == KB200_OP_IMM) return false;
+    if (uses[cur] != 1) return false;
+    ChainStep s{};
+    int next;
+    if (is_unary(e.opcode)) {
+      s.op = chain_unary(e.opcode);
+      s.slot = -2;
+      next = e.a;
+    } else {
+      bool a_leaf = leaf(e.a), b_leaf = leaf(e.b);
+      int main_i, side_i;
+      bool reversed;
+      if (a_leaf && b_leaf) {
+        bool a_acc = d.tape[e.a].opcode == KB200_OP_ACC, b_acc = d.tape[e.b].opcode == KB200_OP_ACC;
+        if (a_acc && b_acc) return false;
+        if (b_acc || (!a_acc && d.tape[e.a].opcode == KB200_OP_IMM)) { main_i = e.b; side_i = e.a; reversed = true; }
+        else { main_i = e.a; side_i = e.b; reversed = false; }
+        if (d.tape[main_i].opcode == KB200_OP_IMM) return false;
+      } else if (b_leaf && leaf_side(e.b)) { main_i = e.a; side_i = e.b; reversed = false; }
+      else if (a_leaf && leaf_side(e.a)) { main_i = e.b; side_i = e.a; reversed = true; }
+      else return false;
+      if (main_i == side_i) return false;
+      s.op = chain_binary(e.opcode, reversed);
+      side_of(side_i, &s);
+      next = main_i;
+    }
+    if (n >= kMaxChain) return false;
+    rev[n++] = s;
+    cur = next;
+  }
+  if (n != n_ops) return false;   // some op is off the chain
+  out->n = n;
+  out->out_slot = d.tape[store].b;
+  for (int i = 0; i < n; ++i) out->steps[i] = rev[n - 1 - i];
+  return true;
+}
+
+namespace {
+struct Matcher {
+  const kb200_kernel_desc& d;
+  const kb200_tape_op& at(int i) const { return d.tape[i]; }
+  bool is(int i, int op) const { return d.tape[i].opcode == op; }
+  // For a commutative binary op at i: find the argument satisfying pred, return it and the other one.
+  template <class P>
+  bool split(int i, int op, P pred, int* hit, int* other) const {
+    if (!is(i, op)) return false;
+    if (pred(at(i).a)) { *hit = at(i).a; *other = at(i).b; return true; }
+    if (pred(at(i).b)) { *hit = at(i).b; *other = at(i).a; return true; }
+    return false;
+  }
+};
+}  // namespace
+
+// y = (x - mean) * rsqrt(var + eps) * gamma + beta with the two-pass mean / variance the frontend
+// emits (kiln/frontend/fx_import.py:217-230).
+bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k) {
+  Matcher m{d};
+  int stores = 0, st = -1, reduces = 0;
+  for (int i = 0; i < d.n_tape; ++i) {
+    if (m.is(i, KB200_OP_STORE)) { ++stores; st = i; }
+    if (is_reduce(d.tape[i].opcode)) ++reduces;
+  }
+  if (stores != 1 || reduces != 2 || d.n_tape != 17) return false;
+  auto is_load = [&](int i) { return m.is(i, KB200_OP_LOAD); };
+  auto is_imm = [&](int i) { return m.is(i, KB200_OP_IMM); };
+  int beta, y1, gamma, y0;
+  if (!m.split(m.at(st).a, KB200_OP_ADD, is_load, &beta, &y1)) return false;
+  if (!m.split(y1, KB200_OP_MUL, is_load, &gamma, &y0)) return false;
+  if (!m.is(y0, KB200_OP_MUL)) return false;
+  int xc = m.at(y0).a, rstd = m.at(y0).b;
+  if (!m.is(xc, KB200_OP_SUB)) { int t = xc; xc = rstd; rstd = t; }
+  if (!m.is(xc, KB200_OP_SUB) || !m.is(rstd, KB200_OP_RSQRT)) return false;
+  int x = m.at(xc).a, mean = m.at(xc).b;
+  if (!is_load(x)) return false;
+  int c1, s1;
+  if (!m.split(mean, KB200_OP_MUL, is_imm, &c1, &s1)) return false;
+  if (!m.is(s1, KB200_OP_RSUM) || m.at(s1).a != x) return false;
+  int eps, var;
+  if (!m.split(m.at(rstd).a, KB200_OP_ADD, is_imm, &eps, &var)) return false;
+  int c2, s2;
+  if (!m.split(var, KB200_OP_MUL, is_imm, &c2, &s2)) return false;
+  if (!m.is(s2, KB200_OP_RSUM)) return false;
+  int sq = m.at(s2).a;
+  if (!m.is(sq, KB200_OP_MUL) || m.at(sq).a != xc || m.at(sq).b != xc) return false;
+  if (m.at(c1).imm != m.at(c2).imm) return false;
+  k->x_slot = m.at(x).a;
+  k->g_slot = m.at(gamma).a;
+  k->b_slot = m.at(beta).a;
+  k->out_slot = m.at(st).b;
+  k->ln_inv_n = m.at(c1).imm;
+  k->ln_eps = m.at(eps).imm;
+  return true;
+}
+
+// out = exp(x - max(x)) / sum(exp(x - max(x))) (kiln/frontend/fx_import.py:212-216).
+bool match_softmax(const kb200_kernel_desc& d, PlanKernel* k) {
+  Matcher m{d};
+  if (d.n_tape != 7) return false;
+  int st = 6;
+  if (!m.is(st, KB200_OP_STORE)) return false;
+  int dv = m.at(st).a;
+  if (!m.is(dv, KB200_OP_DIV)) return false;
+  int e = m.at(dv).a, s = m.at(dv).b;
+  if (!m.is(e, KB200_OP_EXP) || !m.is(s, KB200_OP_RSUM) || m.at(s).a != e) return false;
+  int sub = m.at(e).a;
+  if (!m.is(sub, KB200_OP_SUB)) return false;
+  int x = m.at(sub).a, mx = m.at(sub).b;
+  if (!m.is(x, KB200_OP_LOAD) || !m.is(mx, KB200_OP_RMAX) || m.at(mx).a != x) return false;
+  k->x_slot = m.at(x).a;
+  k->out_slot = m.at(st).b;
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Validation
+// ---------------------------------------------------------------------------------------------
+
+static int validate(const kb200_kernel_desc& d, int index) {
+  const char* nm = d.name;
+  if (d.kclass < KB200_K_ELEMENTWISE || d.kclass > KB200_K_MATMUL)
+    return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): unknown class %d", index, nm, d.kclass);
+  if (d.iter_rank < 1 || d.iter_rank > KB200_MAX_RANK)
+    return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): iteration rank %d out of range", index, nm, d.iter_rank);
+  if (d.n_operands < 1 || d.n_operands > KB200_MAX_OPERANDS)
+    return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): %d operands out of range", index, nm, d.n_operands);
+  if (d.n_tape < 1 || d.n_tape > KB200_MAX_TAPE)
+    return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): tape length %d out of range", index, nm, d.n_tape);
+  if (d.precision < KB200_PREC_FP32 || d.precision > KB200_PREC_BF16)
+    return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): unknown precision %d", index, nm, d.precision);
+  for (int i = 0; i < d.iter_rank; ++i)
+    if (d.iter_shape[i] < 0 || d.iter_shape[i] > (int64_t(1) << 40))
+      return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): bad extent %lld", index, nm, (long long)d.iter_shape[i]);
+  for (int o = 0; o < d.n_operands; ++o) {
+    const kb200_operand& op = d.operands[o];
+    if (op.base_kind < KB200_BASE_ARENA || op.base_kind > KB200_BASE_OUTPUT || op.base_index < 0 || op.elem_offset < 0)
+      return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): operand %d has a bad base or offset", index, nm, o);
+    for (int i = 0; i < KB200_MAX_RANK; ++i)
+      if (op.stride[i] < 0)
+        return fail(KB200_ERR_UNSUPPORTED, "kernel %d (%s): operand %d has a negative stride", index, nm, o);
+  }
+  int stores = 0;
+  for (int i = 0; i < d.n_tape; ++i) {
+    const kb200_tape_op& t = d.tape[i];
+    bool ok = true;
+    switch (t.opcode) {
+      case KB200_OP_LOAD: ok = t.a >= 0 && t.a < d.n_operands; break;
+      case KB200_OP_IMM: break;
+      case KB200_OP_ACC: ok = d.kclass == KB200_K_MATMUL; break;
+      case KB200_OP_STORE:
+        ok = t.a >= 0 && t.a < i && t.b >= 0 && t.b < d.n_operands && d.tape[t.a].opcode != KB200_OP_STORE;
+        ++stores;
+        break;
+      case KB200_OP_RSUM:
+      case KB200_OP_RMAX:
+        ok = (d.kclass == KB200_K_ROW || d.kclass == KB200_K_REDUCE) && t.a >= 0 && t.a < i;
+        break;
+      default:
+        if (is_binary(t.opcode)) ok = t.a >= 0 && t.a < i && t.b >= 0 && t.b < i;
+        else if (is_unary(t.opcode)) ok = t.a >= 0 && t.a < i;
+        else return fail(KB200_ERR_UNSUPPORTED, "kernel %d (%s): no lowering for opcode %d", index, nm, t.opcode);
+    }
+    if (!ok) return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): tape entry %d is malformed", index, nm, i);
+    if ((is_binary(t.opcode) && (d.tape[t.a].opcode == KB200_OP_STORE || d.tape[t.b].opcode == KB200_OP_STORE)) ||
+        ((is_unary(t.opcode) || is_reduce(t.opcode)) && d.tape[t.a].opcode == KB200_OP_STORE))
+      return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): tape entry %d reads a STORE", index, nm, i);
+    if (t.level < 0 || t.level > 16)
+      return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): tape entry %d has level %d", index, nm, i, t.level);
+  }
+  if (stores == 0) return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): tape stores nothing", index, nm);
+  if (d.kclass == KB200_K_MATMUL) {
+    if (d.iter_rank != 3 || d.a_slot < 0 || d.a_slot >= d.n_operands || d.b_slot < 0 || d.b_slot >= d.n_operands ||
+        d.a_slot == d.b_slot || d.k_extent < 0)
+      return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): malformed matmul descriptor", index, nm);
+    if (d.iter_shape[0] > 65535)
+      return fail(KB200_ERR_UNSUPPORTED, "kernel %d (%s): matmul batch %lld exceeds CUDA grid limits", index, nm,
+                  (long long)d.iter_shape[0]);
+  }
+  if (d.kclass == KB200_K_REDUCE) {
+    if (d.n_kept < 0 || d.n_kept > d.iter_rank || d.n_tape != 3 || d.tape[0].opcode != KB200_OP_LOAD ||
+        !is_reduce(d.tape[1].opcode) || d.tape[2].opcode != KB200_OP_STORE)
+      return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): malformed reduction descriptor", index, nm);
+  }
+  return KB200_OK;
+}
+
+// Checks that every element an operand can reach lies inside the buffer it is bound to.
+static int check_span(const Plan& plan, const kb200_kernel_desc& d, int index, int slot, const int64_t* extents,
+                      int rank, uint64_t bytes) {
+  const kb200_operand& op = d.operands[slot];
+  int64_t last = op.elem_offset;
+  for (int i = 0; i < rank; ++i) {
+    if (extents[i] == 0) return KB200_OK;  // nothing is touched
+    last += (extents[i] - 1) * op.stride[i];
+  }
+  if (uint64_t(last + 1) * 4 > bytes)
+    return fail(KB200_ERR_BOUNDS, "kernel %d (%s): operand %d reaches element %lld but its buffer holds %llu bytes", index,
+                d.name, slot, (long long)last, (unsigned long long)bytes);
+  (void)plan;
+  return KB200_OK;
+}
+
+static int resolve(Plan& plan, PlanKernel& k, int index) {
+  const kb200_kernel_desc& d = k.desc;
+  for (int o = 0; o < d.n_operands; ++o) {
+    const kb200_operand& op = d.operands[o];
+    float* base = nullptr;
+    uint64_t bytes = 0;
+    auto pick = [&](const std::vector<float*>& ptrs, const std::vector<uint64_t>& sizes, const char* what) -> int {
+      if (op.base_index >= (int)ptrs.size())
+        return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): operand %d names %s %d but only %d were bound", index, d.name, o,
+                    what, op.base_index, (int)ptrs.size());
+      base = ptrs[op.base_index];
+      bytes = sizes[op.base_index];
+      return KB200_OK;
+    };
+    int rc = KB200_OK;
+    switch (op.base_kind) {
+      case KB200_BASE_ARENA: base = plan.arena; bytes = plan.arena_bytes; break;
+      case KB200_BASE_CONST: rc = pick(plan.consts, plan.const_bytes, "constant"); break;
+      case KB200_BASE_INPUT: rc = pick(plan.inputs, plan.input_bytes, "input"); break;
+      default: rc = pick(plan.outputs, plan.output_bytes, "output"); break;
+    }
+    if (rc) return rc;
+    if (base == nullptr) return fail(KB200_ERR_ARGUMENT, "kernel %d (%s): operand %d is bound to a null buffer", index, d.name, o);
+    int64_t ext[KB200_MAX_RANK];
+    int rank = d.iter_rank;
+    for (int i = 0; i < rank; ++i) ext[i] = d.iter_shape[i];
+    if (d.kclass == KB200_K_MATMUL) {
+      if (o == d.a_slot) { ext[2] = d.k_extent; }
+      else if (o == d.b_slot) { ext[1] = d.k_extent; ext[2] = d.iter_shape[2]; }
+    }
+    rc = check_span(plan, d, index, o, ext, rank, bytes);
+    if (rc) return rc;
+    k.ops[o].ptr = base + op.elem_offset;
+    for (int i = 0; i < KB200_MAX_RANK; ++i) k.ops[o].stride[i] = op.stride[i];
+  }
+  return KB200_OK;
+}
+
+static int launch_one(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
+  if (numel_of(k.desc) == 0) return KB200_OK;
+  switch (k.desc.kclass) {
+    case KB200_K_ELEMENTWISE: return launch_elementwise(plan, k, s);
+    case KB200_K_ROW: return launch_row(plan, k, s);
+    case KB200_K_REDUCE: return launch_reduce(plan, k, s);
+    default: return launch_matmul(plan, k, s);
+  }
+}
+
+}  // namespace kb200
+
+using namespace kb200;
+
+KB200_EXPORT int kb200_version(void) { return KB200_ABI_VERSION; }
+
+KB200_EXPORT const char* kb200_last_error(void) { return g_error.c_str(); }
+
+KB200_EXPORT int kb200_plan_create(const kb200_kernel_desc* descs, int n, int device, kb200_plan** out) {
+  if (out == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_create: out is null");
+  *out = nullptr;
+  if (n < 0 || (n > 0 && descs == nullptr)) return fail(KB200_ERR_ARGUMENT, "kb200_plan_create: bad descriptor array");
+  int count = 0;
+  KB200_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) return fail(KB200_ERR_ARGUMENT, "kb200_plan_create: no CUDA device %d", device);
+  cudaDeviceProp prop;
+  KB200_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(KB200_ERR_UNSUPPORTED, "kb200_plan_create: device %d is sm_%d%d; this library is built for sm_100a only",
+                device, prop.major, prop.minor);
+  for (int i = 0; i < n; ++i) {
+    int rc = validate(descs[i], i);
+    if (rc) return rc;
+  }
+  Plan* plan = new (std::nothrow) Plan();
+  if (!plan) return fail(KB200_ERR_ARGUMENT, "kb200_plan_create: out of host memory");
+  plan->device = device;
+  plan->sm_count = prop.multiProcessorCount;
+  plan->kernels.resize(n);
+  for (int i = 0; i < n; ++i) {
+    PlanKernel& k = plan->kernels[i];
+    k.desc = descs[i];
+    k.desc.name[sizeof(k.desc.name) - 1] = 0;
+    k.tape.n = descs[i].n_tape;
+    memcpy(k.tape.ops, descs[i].tape, sizeof(kb200_tape_op) * descs[i].n_tape);
+    if (k.desc.kclass == KB200_K_MATMUL) {
+      k.batch = k.desc.iter_shape[0];
+      k.M = k.desc.iter_shape[1];
+      k.N = k.desc.iter_shape[2];
+      k.K = k.desc.k_extent;
+    }
+  }
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaError_t e = cudaSetDevice(device);
+  if (e == cudaSuccess) e = cudaMalloc(&plan->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(plan->d_status, 0, sizeof(int));
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    delete plan;
+    return cuda_fail(e, "allocating the plan's status word");
+  }
+  *out = reinterpret_cast<kb200_plan*>(plan);
+  return KB200_OK;
+}
+
+KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_bytes, void* const* consts,
+                                 const uint64_t* const_bytes, int n_consts, void* const* inputs,
+                                 const uint64_t* input_bytes, int n_inputs, void* const* outputs,
+                                 const uint64_t* output_bytes, int n_outputs) {
+  if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_bind: plan is null");
+  Plan& plan = *reinterpret_cast<Plan*>(p);
+  if (n_consts < 0 || n_inputs < 0 || n_outputs < 0 || (n_consts && (!consts || !const_bytes)) ||
+      (n_inputs && (!inputs || !input_bytes)) || (n_outputs && (!outputs || !output_bytes)))
+    return fail(KB200_ERR_ARGUMENT, "kb200_plan_bind: bad buffer arrays");
+  plan.bound = false;
+  plan.arena = static_cast<float*>(arena);
+  plan.arena_bytes = arena_bytes;
+  auto fill = [](std::vector<float*>& ptrs, std::vector<uint64_t>& sizes, void* const* src, const uint64_t* bytes, int n) {
+    ptrs.resize(n);
+    sizes.resize(n);
+    for (int i = 0; i < n; ++i) { ptrs[i] = static_cast<float*>(src[i]); sizes[i] = bytes[i]; }
+  };
+  fill(plan.consts, plan.const_bytes, consts, const_bytes, n_consts);
+  fill(plan.inputs, plan.input_bytes, inputs, input_bytes, n_inputs);
+  fill(plan.outputs, plan.output_bytes, outputs, output_bytes, n_outputs);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  KB200_CUDA(cudaSetDevice(plan.device));
+  int rc = KB200_OK;
+  for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i) {
+    PlanKernel& k = plan.kernels[i];
+    rc = resolve(plan, k, (int)i);
+    if (rc) break;
+    switch (k.desc.kclass) {
+      case KB200_K_ELEMENTWISE: rc = choose_elementwise(plan, k); break;
+      case KB200_K_ROW: rc = choose_row(plan, k); break;
+      case KB200_K_REDUCE: rc = choose_reduce(plan, k); break;
+      default:
+        rc = choose_matmul(plan, k);
+        if (rc == KB200_OK) rc = bind_matmul(plan, k);
+        break;
+    }
+  }
+  cudaSetDevice(prev);
+  if (rc) return rc;
+  plan.bound = true;
+  return KB200_OK;
+}
+
+KB200_EXPORT int kb200_plan_launch(kb200_plan* p, void* stream) {
+  if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_launch: plan is null");
+  Plan& plan = *reinterpret_cast<Plan*>(p);
+  if (!plan.bound) return fail(KB200_ERR_UNBOUND, "kb200_plan_launch: call kb200_plan_bind first");
+  for (size_t i = 0; i < plan.kernels.size(); ++i) {
+    int rc = launch_one(plan, plan.kernels[i], static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return KB200_OK;
+}
+
+KB200_EXPORT int kb200_kernel_launch(kb200_plan* p, int i, void* stream) {
+  if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_kernel_launch: plan is null");
+  Plan& plan = *reinterpret_cast<Plan*>(p);
+  if (!plan.bound) return fail(KB200_ERR_UNBOUND, "kb200_kernel_launch: call kb200_plan_bind first");
+  if (i < 0 || i >= (int)plan.kernels.size()) return fail(KB200_ERR_ARGUMENT, "kb200_kernel_launch: no kernel %d", i);
+  return launch_one(plan, plan.kernels[i], static_cast<cudaStream_t>(stream));
+}
+
+KB200_EXPORT int kb200_plan_launch_count(const kb200_plan* p) {
+  if (p == nullptr) return 0;
+  const Plan& plan = *reinterpret_cast<const Plan*>(p);
+  int n = 0;
+  for (const PlanKernel& k : plan.kernels) n += numel_of(k.desc) == 0 ? 0 : k.launches;
+  return n;
+}
+
+KB200_EXPORT const char* kb200_kernel_impl(const kb200_plan* p, int i) {
+  if (p == nullptr) return "?";
+  const Plan& plan = *reinterpret_cast<const Plan*>(p);
+  if (i < 0 || i >= (int)plan.kernels.size()) return "?";
+  if (!plan.bound) return "unbound";
+  return impl_name(plan.kernels[i].impl);
+}
+
+KB200_EXPORT int kb200_plan_status(kb200_plan* p) {
+  if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_status: plan is null");
+  Plan& plan = *reinterpret_cast<Plan*>(p);
+  int word = 0;
+  KB200_CUDA(cudaMemcpy(&word, plan.d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (word != 0) {
+    cudaMemset(plan.d_status, 0, sizeof(int));
+    return fail(KB200_ERR_DEVICE_WAIT, "a bounded device-side wait ran out (code 0x%x: kernel %d, site %d)", word,
+                (word >> 8) & 0xffff, word & 0xff);
+  }
+  return KB200_OK;
+}
+
+KB200_EXPORT void kb200_plan_destroy(kb200_plan* p) {
+  if (p == nullptr) return;
+  Plan* plan = reinterpret_cast<Plan*>(p);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(plan->device);
+  for (PlanKernel& k : plan->kernels) destroy_matmul(k);
+  if (plan->d_status) cudaFree(plan->d_status);
+  cudaSetDevice(prev);
+  delete plan;
+}

@@ -203,7 +203,7 @@ def launches_of(plan: PlanSpec, configs=None):
         kind = launch_kind(k)
         if kind == "elementwise":
             for oi in range(len(k.outputs)):
-                out.append(Launch(f"{k.name}_ew{oi}", kind, k.name, _bases(k, [k.outputs[oi]]), ki, oi))
+                out.append(Launch(f"{k.name}_ew{oi}", kind, k.name, _bases(k, k.outputs), ki, oi))
         else:
             suffix = {"row": "row", "reduction": "reduce", "matmul": "matmul"}[kind]
             launch = Launch(f"{k.name}_{suffix}", kind, k.name, _bases(k, k.outputs), ki, None,

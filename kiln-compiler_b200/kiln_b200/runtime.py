@@ -1,0 +1,244 @@
+"""GPU runtime (stands in for kiln.gpu.runtime): owns device memory, binds it to the
+kernel library's launch plan, captures the launch sequence as one CUDA graph and replays it.
+
+Same contract as the reference's GPUExecutable (kiln/gpu/runtime.py:135-217):
+
+  * one arena holding every intermediate at the planner's offsets, allocated once;
+  * frozen constants uploaded once, only those some launch reads (runtime.py:146-154);
+  * a MemoryError with the sizes involved before anything is allocated (runtime.py:82-90);
+  * ``__call__(*tensors)`` checks shapes (ValueError), coerces inputs to contiguous float32
+    on the device, and returns fresh float32 tensors that do not alias internal buffers;
+  * not re-entrant: calls share the arena.
+
+The kernels are the hand-written sm_100a ones in libkb200.so, reached through the C ABI of
+include/kb200.h with raw device pointers; PyTorch only provides memory, streams and graphs.
+There is no CPU path: without a CUDA device or without the library, construction raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import hashlib
+import os
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from kiln_b200 import _cabi, lowering
+
+
+def interpreting() -> bool:
+    """The reference can run its kernels under Triton's CPU interpreter; this backend cannot."""
+    return False
+
+
+def device() -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("Kiln's B200 GPU backend needs a CUDA GPU (sm_100a); there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def cache_dir() -> Path:
+    base = os.environ.get("KILN_CACHE_DIR") or os.path.join(Path.home(), ".cache", "kiln")
+    return Path(base) / "b200"
+
+
+def write_source(source: str) -> Path:
+    """Store the plan dump where Report.lowering['source'] points (atomic, verified on reuse)."""
+    digest = hashlib.sha256(source.encode()).hexdigest()[:16]
+    path = cache_dir() / f"plan_{digest}.txt"
+    path.parent.mkdir(parents=True, exist_ok=True)
+    try:
+        intact = path.read_text() == source
+    except OSError:
+        intact = False
+    if not intact:
+        tmp = path.with_suffix(f".{os.getpid()}.tmp")
+        with open(tmp, "w") as f:
+            f.write(source)
+            f.flush()
+            os.fsync(f.fileno())
+        tmp.replace(path)
+    return path
+
+
+def check_memory(dev, needed_bytes, what):
+    if dev.type != "cuda":
+        return
+    free, total = torch.cuda.mem_get_info(dev)
+    if needed_bytes > free:
+        mib = lambda b: f"{b / 2**20:.1f} MiB"
+        raise MemoryError(f"Kiln needs {mib(needed_bytes)} of GPU memory for {what}, but only "
+                          f"{mib(free)} of {mib(total)} is free (other processes may be using the GPU). "
+                          f"Try a smaller batch or sequence length, or free GPU memory.")
+
+
+def kernel_seconds(fn, repeats=20, rounds=5):
+    """GPU time per call of ``fn`` without CPU launch overhead: ``repeats`` calls captured in one
+    CUDA graph, the replay timed with CUDA events, best of ``rounds`` (kiln/gpu/runtime.py:93-132)."""
+    device()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(repeats):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(rounds):
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(end) / 1e3 / repeats)
+    return best
+
+
+def _ptr_array(tensors):
+    n = len(tensors)
+    ptrs = (C.c_void_p * max(n, 1))(*[t.data_ptr() for t in tensors])
+    sizes = (C.c_uint64 * max(n, 1))(*[t.numel() * t.element_size() for t in tensors])
+    return ptrs, sizes, n
+
+
+class GPUExecutable:
+    """Runs one compiled graph on the GPU. Not reentrant: calls share one arena."""
+
+    def __init__(self, program, arena_bytes, constants, input_shapes, output_shapes, cuda_graphs=True):
+        self.device = device()
+        self.program = program
+        self.source_path = write_source(program.source)
+        self.input_shapes = [tuple(s) for s in input_shapes]
+        self.output_shapes = [tuple(s) for s in output_shapes]
+        self._lib = _cabi.load()
+        self._plan = C.c_void_p()
+
+        used = sorted({key[1] for launch in program.launches for key in launch.bases if key[0] == "const"})
+        const_bytes = sum(int(np.prod(constants[name].shape)) * 4 for name in used)
+        io_bytes = sum(4 * int(np.prod(s)) for s in self.input_shapes + self.output_shapes)
+        out_bytes = sum(4 * int(np.prod(s)) for s in self.output_shapes)
+        check_memory(self.device, arena_bytes + const_bytes + io_bytes + out_bytes,
+                     f"the arena ({arena_bytes / 2**20:.1f} MiB), weights ({const_bytes / 2**20:.1f} MiB) "
+                     f"and outputs")
+        self.arena = torch.empty(max(arena_bytes, 4), dtype=torch.uint8, device=self.device)
+        self.const_names = used
+        self.constants = {name: torch.from_numpy(np.ascontiguousarray(constants[name], np.float32)).to(self.device)
+                          for name in used}
+        self.arena_bytes = arena_bytes
+        self.weight_bytes = const_bytes
+        # Static input / output buffers: the plan is bound to fixed addresses once, which is what
+        # lets the whole launch sequence be one CUDA graph (kiln/gpu/runtime.py:191-204).
+        self.static_inputs = [torch.zeros(max(int(np.prod(s)), 1), device=self.device).view(-1)[:int(np.prod(s))].view(s)
+                              if int(np.prod(s)) else torch.zeros(s, device=self.device) for s in self.input_shapes]
+        self.static_outputs = [torch.empty(s, device=self.device) for s in self.output_shapes]
+
+        descs = lowering.lower(program.plan, program.launches, program.precision, self.const_names)
+        self._descs = descs
+        _cabi.check(self._lib.kb200_plan_create(descs, len(program.launches), self.device.index,
+                                                C.byref(self._plan)), self._lib)
+        self._bind()
+        self.kernel_names = [l.name for l in program.launches]
+        self.impls = [self._lib.kb200_kernel_impl(self._plan, i).decode() for i in range(len(program.launches))]
+        self.device_launches = self._lib.kb200_plan_launch_count(self._plan)
+        self.graph = None
+        self.use_cuda_graphs = bool(cuda_graphs)
+
+    # -- binding and launching ------------------------------------------------------------
+
+    def _bind(self):
+        consts = [self.constants[n] for n in self.const_names]
+        cp, cs, cn = _ptr_array(consts)
+        ip, is_, in_ = _ptr_array(self.static_inputs)
+        op, os_, on = _ptr_array(self.static_outputs)
+        with torch.cuda.device(self.device):
+            _cabi.check(self._lib.kb200_plan_bind(self._plan, self.arena.data_ptr(), self.arena.numel(),
+                                                  cp, cs, cn, ip, is_, in_, op, os_, on), self._lib)
+
+    def _launch(self):
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _cabi.check(self._lib.kb200_plan_launch(self._plan, C.c_void_p(stream)), self._lib)
+
+    def launch_kernel(self, i):
+        """Enqueue launch ``i`` alone on the current stream (profiling, autotuning)."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _cabi.check(self._lib.kb200_kernel_launch(self._plan, i, C.c_void_p(stream)), self._lib)
+
+    def status(self):
+        """Raises if a bounded device-side wait ran out since the last check."""
+        _cabi.check(self._lib.kb200_plan_status(self._plan), self._lib)
+
+    def _prepare(self, inputs):
+        if len(inputs) != len(self.input_shapes):
+            raise TypeError(f"expected {len(self.input_shapes)} inputs, got {len(inputs)}")
+        out = []
+        for t, shape in zip(inputs, self.input_shapes):
+            if tuple(t.shape) != shape:
+                raise ValueError(f"Kiln was compiled for input shape {shape}, got {tuple(t.shape)}")
+            out.append(t.detach())
+        return out
+
+    def _capture(self):
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):          # warm up: loads every kernel before capture
+            self._launch()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._launch()
+        self.graph = graph
+
+    def run_static(self):
+        """Run on whatever the static input buffers hold; results land in ``static_outputs``."""
+        if self.use_cuda_graphs:
+            if self.graph is None:
+                self._capture()
+            self.graph.replay()
+        else:
+            self._launch()
+
+    def __call__(self, *inputs):
+        inputs = self._prepare(inputs)
+        with torch.cuda.device(self.device):
+            for static, t in zip(self.static_inputs, inputs):
+                static.copy_(t, non_blocking=True)       # converts dtype / device / layout as needed
+            self.run_static()
+            return [o.clone() for o in self.static_outputs]
+
+    def profile(self, *inputs, iters=20):
+        """[(launch name, milliseconds)] per device launch, CUDA events around each."""
+        inputs = self._prepare(inputs)
+        with torch.cuda.device(self.device):
+            for static, t in zip(self.static_inputs, inputs):
+                static.copy_(t)
+            self._launch()
+            torch.cuda.synchronize(self.device)
+            totals = [0.0] * len(self.kernel_names)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(iters):
+                for i in range(len(self.kernel_names)):
+                    start.record()
+                    self.launch_kernel(i)
+                    end.record()
+                    end.synchronize()
+                    totals[i] += start.elapsed_time(end)
+        return [(name, total / iters) for name, total in zip(self.kernel_names, totals)]
+
+    def close(self):
+        if getattr(self, "_plan", None) is not None and self._plan:
+            self._lib.kb200_plan_destroy(self._plan)
+            self._plan = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:   # noqa: BLE001  (interpreter shutdown)
+            pass

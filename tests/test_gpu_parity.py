@@ -1,0 +1,122 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle and the golden
+vectors the reference produced.  Tolerances: the reference's own assert_close(rtol=1e-4,
+atol=1e-5) against eager PyTorch (tests/test_gpu.py:37 of the reference) and, against a float64
+evaluation, max|err| / max|expected| <= 1e-5 (FP32), 2e-3 (TF32), 2e-2 (BF16)."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import big_cases, small_cases, subsample
+from oracle.plan_oracle import run_plan, scale_relative_error
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = {"fp32": 1e-5, "tf32": 2e-3, "bf16": 2e-2}
+
+
+@pytest.fixture(autouse=True)
+def private_cache(tmp_path, monkeypatch):
+    monkeypatch.setenv("KILN_CACHE_DIR", str(tmp_path))
+    yield
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["graph", "eager-launch"])
+@pytest.mark.parametrize("case", small_cases())
+def test_small_cases_match_reference_vectors(case, graphs):
+    from gpu_helpers import run_case
+
+    exe, outs, (plan, inputs, consts, expected) = run_case(case, "fp32", cuda_graphs=graphs)
+    exact = run_plan(plan, inputs, consts, dtype=np.float64)
+    for got, eager, ref64 in zip(outs, expected["out"], exact):
+        np.testing.assert_allclose(got, eager, rtol=1e-4, atol=1e-5)
+        assert scale_relative_error(got, ref64) <= REL_TOL["fp32"], (case, exe.impls)
+
+
+@pytest.mark.parametrize("case", big_cases())
+def test_benchmark_configs_fp32(case):
+    from gpu_helpers import run_case
+
+    exe, outs, (plan, inputs, consts, expected) = run_case(case, "fp32")
+    exact = run_plan(plan, inputs, consts, dtype=np.float64)
+    for got, ref64, sub, step in zip(outs, exact, expected["sub"], expected["step"]):
+        assert scale_relative_error(got, ref64) <= REL_TOL["fp32"], (case, exe.impls)
+        # and directly against the stored float64 result of the reference's eager model
+        assert scale_relative_error(subsample(got, step), sub) <= REL_TOL["fp32"], (case, exe.impls)
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("case", [c for c in big_cases() if c.startswith(("gpt2_block", "mlp_", "linear_"))]
+                         + ["tf32_linear", "transformer_block", "bmm_transposed_operand", "odd_k", "wide_bmm",
+                            "erf_gelu_mlp", "decode_m1"])
+def test_reduced_precision_matmuls(case, precision):
+    from gpu_helpers import run_case
+
+    exe, outs, (plan, inputs, consts, expected) = run_case(case, precision)
+    exact = run_plan(plan, inputs, consts, dtype=np.float64)
+    for got, ref64 in zip(outs, exact):
+        assert scale_relative_error(got, ref64) <= REL_TOL[precision], (case, precision, exe.impls)
+
+
+def test_every_kernel_of_the_block_matches_the_oracle_step_by_step():
+    """Launch the block's 11 kernels one at a time and compare each kernel's output buffer."""
+    from gpu_helpers import build_executable
+    from helpers import case_data, load_plan
+
+    case = "gpt2_block_t128"
+    plan = load_plan(case)
+    inputs, consts, _ = case_data(case, plan)
+    exe = build_executable(case, "fp32", cuda_graphs=False, plan_json=plan, consts=consts)
+    exe.static_inputs[0].copy_(torch.from_numpy(inputs[0]))
+    _, per_kernel = run_plan(plan, inputs, consts, dtype=np.float64, trace=True)
+    arena = exe.arena.view(torch.float32)
+    for i, (kernel, want) in enumerate(zip(plan["kernels"], per_kernel)):
+        exe.launch_kernel(i)
+        torch.cuda.synchronize()
+        for (_, where), ref in zip(kernel["outputs"], want):
+            buf = arena if where["base"][0] == "arena" else exe.static_outputs[where["base"][1]].view(-1)
+            got = torch.as_strided(buf, where["shape"], where["strides"], where["offset"]).cpu().numpy()
+            assert scale_relative_error(got, ref) <= 1e-5, (kernel["name"], exe.impls[i])
+
+
+def test_replay_with_new_inputs():
+    """One captured graph, three different inputs (tests/test_gpu.py:161-169 of the reference)."""
+    from gpu_helpers import build_executable
+    from helpers import case_data, load_plan
+
+    plan = load_plan("block_d64")
+    _, consts, _ = case_data("block_d64", plan)
+    exe = build_executable("block_d64", plan_json=plan, consts=consts)
+    rng = np.random.default_rng(5)
+    for _ in range(3):
+        x = rng.standard_normal((16, 64)).astype(np.float32)
+        (got,) = exe(torch.from_numpy(x))
+        (want,) = run_plan(plan, [x], consts, dtype=np.float64)
+        assert scale_relative_error(got.cpu().numpy(), want) <= 1e-5
+    assert exe.graph is not None
+
+
+def test_wrong_shape_and_memory_errors(monkeypatch):
+    from gpu_helpers import build_executable
+    from kiln_b200.runtime import check_memory
+
+    exe = build_executable("layernorm")
+    with pytest.raises(ValueError, match="compiled for input shape"):
+        exe(torch.zeros(3, 3))
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (10 * 2**20, 32 * 2**30))
+    with pytest.raises(MemoryError, match="only 10.0 MiB"):
+        check_memory(torch.device("cuda"), 64 * 2**20, "the arena")
+    with pytest.raises(MemoryError):
+        build_executable("gpt2_block_t128")
+
+
+def test_hot_path_kernels_are_the_specialised_ones():
+    from gpu_helpers import build_executable
+
+    exe = build_executable("gpt2_block_t128")
+    by_name = dict(zip(exe.kernel_names, exe.impls))
+    assert by_name["k0_row"] == "row_layernorm" and by_name["k8_row"] == "row_layernorm"
+    assert by_name["k4_row"] == "row_softmax"
+    assert by_name["k2_ew0"] == "ew_transpose" and by_name["k6_ew0"] == "ew_chain_vec4"
+    assert build_executable("bias_gelu_2048x3072").impls == ["ew_chain_vec4"]
+    assert build_executable("linear_1x3072x768").impls == ["mm_gemv"]

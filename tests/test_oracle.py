@@ -37,3 +37,18 @@ def test_oracle_float64_matches_reference_float64(case):
     got = run_plan(plan, inputs, consts, dtype=np.float64)
     for g, sub, step in zip(got, expected["sub"], expected["step"]):
         assert scale_relative_error(subsample(g, step), sub) < 5e-7   # stored rounded to float32
+
+
+def test_torch_baseline_port_matches_the_plan_oracle():
+    """The eager-PyTorch CPU baseline computes the same block as the plan oracle."""
+    import torch
+
+    from kiln_b200 import workloads as W
+    from oracle.torch_block import block_forward, to_torch
+
+    plan = load_plan("gpt2_block_t128")
+    inputs, consts, _ = case_data("gpt2_block_t128", plan)
+    (want,) = run_plan(plan, inputs, consts, dtype=np.float64)
+    p = to_torch(W.block_params(0, 128), torch.float64)
+    got = block_forward(p, torch.from_numpy(inputs[0]).double()).numpy()
+    assert scale_relative_error(got, want) < 1e-7   # plan scalars (1/768, eps) are float32-rounded
