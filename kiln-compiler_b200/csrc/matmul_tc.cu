@@ -1,0 +1,507 @@
+// Tensor-core batched matmul with fused epilogue for sm_100a: TMA -> shared-memory ring ->
+// tcgen05.mma -> TMEM accumulator -> epilogue from TMEM.  Role of the reference's matmul generator
+// with input_precision="tf32" (kiln/gpu/codegen.py:484-530), plus a BF16-operand mode.
+//
+// One CTA computes one 128 x BN tile of C for one batch entry, 192 threads in three roles:
+//   warp 0      TMA producer: per K slab, one box of A (128 rows x 128 bytes, K-major) and BN/chunk
+//               boxes of B (slab rows x 128 bytes, N-major -- the layout the buffer-assignment pass
+//               guarantees for B, kiln/passes/buffers.py:208-217, so nothing is repacked), both
+//               written with the 128-byte swizzle the MMA descriptors expect.  Plain per-CTA loads.
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = BN, K = 32 bytes per
+//               instruction) on the slab and commits the stage back to the producer.
+//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time (each thread owns one row of the tile),
+//               the fused chain on registers (bias, GELU, residual, scale + mask ...), 128-bit stores.
+// A is read K-major and B N-major straight from the planned buffers (float32, consumed as TF32).
+// In BF16 mode both operands are first converted into packed bf16 scratch (constants once at
+// bind, activations per launch) and the same kernel runs with kind::f16.
+//
+// Every wait on an mbarrier is bounded.  When one runs out the thread records the site in the
+// plan's status word, raises a CTA-wide abort flag, and every role falls through to the common
+// exit, which waits (bounded) for copies in flight, frees the TMEM allocation and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "device_math.cuh"
+#include "kb200_internal.h"
+#include "matmul.h"
+
+namespace kb200 {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kSlabBytes = 128;           // bytes of K (A) or N (B) per swizzled row
+constexpr int kATileBytes = kTileM * kSlabBytes;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kWaitLimit = 1u << 20; // try_wait attempts before giving up (each blocks up to ~1 us..ms)
+
+struct TcParams {
+  MatmulParams mm;
+  int bn;               // tile width, multiple of 32 (tf32) / 64 (bf16), <= 256
+  int stages;
+  int num_kb;           // K slabs
+  int slab_k;           // elements of K per slab: 32 (tf32) or 64 (bf16)
+  int chunk_n;          // elements of N per B box: 32 (tf32) or 64 (bf16)
+  int b_step_bytes;     // bytes between consecutive MMA K steps inside a B chunk
+  int tmem_cols;        // power of two >= bn, >= 32
+  uint32_t idesc;
+  int kernel_index;
+  int* status;
+  int vec_ok;           // bit s: side operand of chain step s can be read with float4; bit 31: output
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false if the limit ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63) == 63 && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;   // 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                     bool bf16) {
+  if (bf16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// The fused chain on 32 consecutive columns of one row, values in registers.
+__device__ __forceinline__ void epilogue_row32(const TcParams& p, float* v, int64_t b, int64_t m, int64_t n0) {
+  const MatmulParams& mm = p.mm;
+  const int64_t n_left = mm.N - n0;       // > 0
+  for (int s = 0; s < mm.chain.n; ++s) {
+    const ChainStep st = mm.chain.steps[s];
+    if (st.slot >= 0) {
+      const DevOperand& o = mm.ops[st.slot];
+      const float* base = o.ptr + b * o.stride[0] + m * o.stride[1] + n0 * o.stride[2];
+      if (((p.vec_ok >> s) & 1) && n_left >= 32) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(base + j);
+          v[j] = apply_chain(st.op, v[j], t.x);
+          v[j + 1] = apply_chain(st.op, v[j + 1], t.y);
+          v[j + 2] = apply_chain(st.op, v[j + 2], t.z);
+          v[j + 3] = apply_chain(st.op, v[j + 3], t.w);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < n_left) v[j] = apply_chain(st.op, v[j], base[j * o.stride[2]]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_chain(st.op, v[j], st.imm);
+    }
+  }
+  const DevOperand& o = mm.ops[mm.chain.out_slot];
+  float* out = o.ptr + b * o.stride[0] + m * o.stride[1] + n0 * o.stride[2];
+  if (((p.vec_ok >> 31) & 1) && n_left >= 32) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < n_left) out[j * o.stride[2]] = v[j];
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(192, 1)
+mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+             const __grid_constant__ TcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 1];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  // 1024-byte aligned tile area (the 128-byte swizzle pattern repeats every 1024 bytes)
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const int b_tile_bytes = p.bn * kSlabBytes;
+  const int stage_bytes = kATileBytes + b_tile_bytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]), accum_bar = smem_u32(&bars[2 * kMaxStages]);
+
+  const int64_t tiles_n = (p.mm.N + p.bn - 1) / p.bn;
+  const int64_t m0 = (int64_t)(blockIdx.x / tiles_n) * kTileM;
+  const int64_t n0 = (int64_t)(blockIdx.x % tiles_n) * p.bn;
+  const int batch = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int n_chunks = p.bn / p.chunk_n;
+      const int chunk_bytes = p.slab_k * kSlabBytes;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t it = kb / p.stages;
+        if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_ptr)) {
+          if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 1); *abort_ptr = 1; }
+          break;
+        }
+        const uint32_t full = full0 + 8 * s;
+        mbar_expect_tx(full, (uint32_t)stage_bytes);
+        const uint32_t a_dst = tiles + s * stage_bytes;
+        tma_load_3d(a_dst, &tma_a, full, kb * p.slab_k, (int)m0, batch);
+        for (int c = 0; c < n_chunks; ++c)
+          tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, (int)n0 + c * p.chunk_n, kb * p.slab_k, batch);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t lbo = (uint32_t)(p.slab_k * kSlabBytes);   // between N chunks of B
+      bool ok = true;
+      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t it = kb / p.stages;
+        if (!mbar_wait(full0 + 8 * s, it & 1, abort_ptr)) {
+          if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = tiles + s * stage_bytes;
+        const uint32_t b_addr = a_addr + kATileBytes;
+#pragma unroll
+        for (int k = 0; k < kSlabBytes / 32; ++k) {
+          const uint64_t adesc = make_desc(a_addr + k * 32, 16, 1024);
+          const uint64_t bdesc = make_desc(b_addr + k * p.b_step_bytes, lbo, 1024);
+          umma(tmem_base, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u, BF16);
+        }
+        umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+      }
+      umma_commit(accum_bar);          // arrives when every MMA issued so far has completed
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quad = warp & 3;                      // TMEM lanes 32 * quad .. + 31 belong to this warp
+    const int64_t m = m0 + quad * 32 + lane;
+    bool ok = mbar_wait(accum_bar, 0, abort_ptr);
+    if (!ok && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !*abort_ptr;
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int c = 0; c < p.bn; c += 32) {
+        if (n0 + c >= p.mm.N) break;              // uniform across the warp
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, v);
+        if (m < p.mm.M) {
+          if (p.mm.has_chain) {
+            epilogue_row32(p, v, batch, m, n0 + c);
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c + j < p.mm.N) epilogue_store(p.mm, v[j], batch, m, n0 + c + j);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- common exit ----------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    // give copies that may still be in flight a bounded time to land before shared memory is released
+    for (int s = 0; s < p.stages; ++s)
+      for (uint32_t i = 0; i < 4096u; ++i)
+        if (mbar_try_wait(full0 + 8 * s, 0) || mbar_try_wait(full0 + 8 * s, 1)) break;
+  }
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+  }
+}
+
+// Strided float32 [batch, rows, cols] (cols contiguous) -> packed bf16 [batch, rows, cols].
+__global__ void __launch_bounds__(256) cvt_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                       int64_t batch, int64_t rows, int64_t cols, int64_t s_batch,
+                                                       int64_t s_row) {
+  const int64_t cols4 = cols >> 2;
+  const int64_t total = batch * rows * cols4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c = i % cols4, r = (i / cols4) % rows, b = i / (cols4 * rows);
+    const float4 v = *reinterpret_cast<const float4*>(src + b * s_batch + r * s_row + c * 4);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst + (b * rows + r) * cols + c * 4) = packed;
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+struct TcState {
+  CUtensorMap map_a, map_b;
+  TcParams params;
+  size_t smem_bytes = 0;
+  dim3 grid;
+  bool bf16 = false;
+  // bf16 operand copies
+  __nv_bfloat16* a16 = nullptr;
+  __nv_bfloat16* b16 = nullptr;
+  bool b_const = false;       // B is a frozen constant: converted once at bind
+};
+
+// A 3-D tiled map over [batch, rows, cols] with cols contiguous; box = (box_cols, box_rows, 1).
+bool encode_map(CUtensorMap* map, bool bf16, const void* base, int64_t cols, int64_t rows, int64_t batch,
+                int64_t row_stride_elems, int64_t batch_stride_elems, int box_cols, int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const int esz = bf16 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * esz, (cuuint64_t)(batch > 1 ? batch_stride_elems : row_stride_elems * rows) * esz};
+  if (strides[1] == 0) strides[1] = strides[0] * rows;
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base),
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// Can the tensor-core kernel take this matmul as it stands?
+bool tc_eligible(const PlanKernel& k) {
+  const kb200_kernel_desc& d = k.desc;
+  if (d.precision == KB200_PREC_FP32) return false;
+  const DevOperand& A = k.ops[d.a_slot];
+  const DevOperand& B = k.ops[d.b_slot];
+  if (k.M < 32 || k.N < 64 || k.K < 64) return false;
+  if (k.N % 4 || k.K % 4) return false;
+  if (d.precision == KB200_PREC_BF16 && (k.N % 8 || k.K % 8)) return false;
+  // A: K contiguous; B: N contiguous; 16-byte aligned bases and strides
+  if (A.stride[2] != 1 || B.stride[2] != 1) return false;
+  if (A.stride[1] % 4 || A.stride[0] % 4 || B.stride[1] % 4 || B.stride[0] % 4) return false;
+  if (A.stride[1] == 0 || B.stride[1] == 0) return false;
+  if (k.batch > 1 && (A.stride[0] == 0 || B.stride[0] == 0)) return false;
+  if (!aligned16(A.ptr) || !aligned16(B.ptr)) return false;
+  return true;
+}
+
+int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
+  const kb200_kernel_desc& d = k.desc;
+  TcState* st = static_cast<TcState*>(k.tc);
+  if (!st) {
+    st = new TcState();
+    k.tc = st;
+  }
+  st->bf16 = d.precision == KB200_PREC_BF16;
+  const int chunk_n = st->bf16 ? 64 : 32, slab_k = st->bf16 ? 64 : 32;
+  int bn = d.cfg[1] > 0 ? d.cfg[1] : 128;
+  if (bn > 256) bn = 256;
+  bn = (bn / chunk_n) * chunk_n;
+  if (bn < chunk_n) bn = chunk_n;
+  while (bn > chunk_n && bn / 2 >= k.N) bn /= 2;          // do not make the tile wider than the problem
+  if (bn % 16) return fail(KB200_ERR_ARGUMENT, "matmul %s: tile width %d is not a multiple of 16", d.name, bn);
+  int stages = d.cfg[3] > 0 ? d.cfg[3] : 4;
+  if (stages > kMaxStages) stages = kMaxStages;
+  const int stage_bytes = kATileBytes + bn * kSlabBytes;
+  while (stages > 2 && (size_t)stages * stage_bytes + 1024 > 220 * 1024) --stages;
+  TcParams& p = st->params;
+  fill_matmul_params(k, &p.mm);
+  p.bn = bn;
+  p.stages = stages;
+  p.slab_k = slab_k;
+  p.chunk_n = chunk_n;
+  p.num_kb = (int)((k.K + slab_k - 1) / slab_k);
+  p.b_step_bytes = (st->bf16 ? 16 : 8) * kSlabBytes;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < bn) p.tmem_cols *= 2;
+  // instruction descriptor: D = F32, A/B = TF32 or BF16, A K-major, B MN-major, N = bn, M = 128
+  const uint32_t fmt = st->bf16 ? 1u : 2u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+  p.kernel_index = kernel_index;
+  p.status = plan.d_status;
+  p.vec_ok = 0;
+  if (k.has_chain) {
+    auto vec = [&](int slot) {
+      const DevOperand& o = k.ops[slot];
+      return o.stride[2] == 1 && o.stride[1] % 4 == 0 && o.stride[0] % 4 == 0 && aligned16(o.ptr) && bn % 32 == 0;
+    };
+    for (int s = 0; s < k.chain.n; ++s)
+      if (k.chain.steps[s].slot >= 0 && vec(k.chain.steps[s].slot)) p.vec_ok |= 1 << s;
+    if (vec(k.chain.out_slot)) p.vec_ok |= 1u << 31;
+  }
+  st->smem_bytes = (size_t)stages * stage_bytes + 1024;
+  st->grid = dim3((unsigned)(((k.M + kTileM - 1) / kTileM) * ((k.N + bn - 1) / bn)), 1, (unsigned)k.batch);
+
+  const DevOperand& A = k.ops[d.a_slot];
+  const DevOperand& B = k.ops[d.b_slot];
+  const void* a_base = A.ptr;
+  const void* b_base = B.ptr;
+  int64_t a_row = A.stride[1], a_batch = A.stride[0], b_row = B.stride[1], b_batch = B.stride[0];
+  k.launches = 1;
+  if (st->bf16) {
+    if (st->a16) cudaFree(st->a16);
+    if (st->b16) cudaFree(st->b16);
+    st->a16 = st->b16 = nullptr;
+    KB200_CUDA(cudaMalloc(&st->a16, (size_t)k.batch * k.M * k.K * 2));
+    KB200_CUDA(cudaMalloc(&st->b16, (size_t)k.batch * k.K * k.N * 2));
+    st->b_const = d.operands[d.b_slot].base_kind == KB200_BASE_CONST;
+    if (st->b_const) {
+      const int64_t total = k.batch * k.K * (k.N / 4);
+      cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256>>>(
+          B.ptr, st->b16, k.batch, k.K, k.N, B.stride[0], B.stride[1]);
+      KB200_CUDA(cudaGetLastError());
+      KB200_CUDA(cudaDeviceSynchronize());
+    }
+    k.launches = st->b_const ? 2 : 3;
+    a_base = st->a16;
+    b_base = st->b16;
+    a_row = k.K; a_batch = k.M * k.K;
+    b_row = k.N; b_batch = k.K * k.N;
+  }
+  if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM) ||
+      !encode_map(&st->map_b, st->bf16, b_base, k.N, k.K, k.batch, b_row, b_batch, chunk_n, slab_k))
+    return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
+  cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->smem_bytes)
+                           : cudaFuncSetAttribute(mm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->smem_bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(mm_tc_kernel)");
+  return KB200_OK;
+}
+
+int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
+  const TcState* st = static_cast<const TcState*>(k.tc);
+  const kb200_kernel_desc& d = k.desc;
+  if (st->bf16) {
+    const DevOperand& A = k.ops[d.a_slot];
+    const DevOperand& B = k.ops[d.b_slot];
+    const int64_t cap = (int64_t)plan.sm_count * 8;
+    int64_t total = k.batch * k.M * (k.K / 4);
+    cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
+        A.ptr, st->a16, k.batch, k.M, k.K, A.stride[0], A.stride[1]);
+    if (!st->b_const) {
+      total = k.batch * k.K * (k.N / 4);
+      cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
+          B.ptr, st->b16, k.batch, k.K, k.N, B.stride[0], B.stride[1]);
+    }
+    mm_tc_kernel<true><<<st->grid, 192, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
+  } else {
+    mm_tc_kernel<false><<<st->grid, 192, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
+  }
+  KB200_CUDA(cudaGetLastError());
+  return KB200_OK;
+}
+
+void tc_destroy(PlanKernel& k) {
+  TcState* st = static_cast<TcState*>(k.tc);
+  if (!st) return;
+  if (st->a16) cudaFree(st->a16);
+  if (st->b16) cudaFree(st->b16);
+  delete st;
+  k.tc = nullptr;
+}
+
+}  // namespace kb200
