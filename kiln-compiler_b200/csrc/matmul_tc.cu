@@ -43,6 +43,8 @@ struct TcParams {
   int slab_k;           // elements of K per slab: 32 (tf32) or 64 (bf16)
   int chunk_n;          // elements of N per B box: 32 (tf32) or 64 (bf16)
   int b_step_bytes;     // bytes between consecutive MMA K steps inside a B chunk
+  int b_sbo_bytes;      // bytes between the row groups of one swizzle atom of B
+  int b_layout;         // descriptor layout type of B (1 = 128-byte swizzle on 32-byte atoms, 2 = 128-byte swizzle)
   int tmem_cols;        // power of two >= bn, >= 32
   uint32_t idesc;
   int kernel_index;
@@ -86,13 +88,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor.  layout: 2 = 128-byte swizzle of 16-byte units, 1 = 128-byte
+// swizzle of 32-byte units (the only swizzled layout an N-major 32-bit operand may use).
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;   // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;   // 128-byte swizzle
+  d |= (uint64_t)layout << 61;
   return d;
 }
 
@@ -256,7 +260,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
         for (int k = 0; k < kSlabBytes / 32; ++k) {
           const uint64_t adesc = make_desc(a_addr + k * 32, 16, 1024);
-          const uint64_t bdesc = make_desc(b_addr + k * p.b_step_bytes, lbo, 1024);
+          const uint64_t bdesc = make_desc(b_addr + k * p.b_step_bytes, lbo, (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
           umma(tmem_base, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u, BF16);
         }
         umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
@@ -353,7 +357,7 @@ struct TcState {
 
 // A 3-D tiled map over [batch, rows, cols] with cols contiguous; box = (box_cols, box_rows, 1).
 bool encode_map(CUtensorMap* map, bool bf16, const void* base, int64_t cols, int64_t rows, int64_t batch,
-                int64_t row_stride_elems, int64_t batch_stride_elems, int box_cols, int box_rows) {
+                int64_t row_stride_elems, int64_t batch_stride_elems, int box_cols, int box_rows, bool atom32) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const int esz = bf16 ? 2 : 4;
@@ -363,7 +367,8 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, int64_t cols, int
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   cuuint32_t elem[3] = {1, 1, 1};
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base),
-                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -417,6 +422,10 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.chunk_n = chunk_n;
   p.num_kb = (int)((k.K + slab_k - 1) / slab_k);
   p.b_step_bytes = (st->bf16 ? 16 : 8) * kSlabBytes;
+  // An N-major operand of 32-bit elements must use the 128-byte swizzle on 32-byte atoms, whose
+  // pattern repeats every 4 rows; 16-bit elements use the ordinary 128-byte swizzle (8 rows).
+  p.b_layout = st->bf16 ? 2 : 1;
+  p.b_sbo_bytes = st->bf16 ? 1024 : 512;
   p.tmem_cols = 32;
   while (p.tmem_cols < bn) p.tmem_cols *= 2;
   // instruction descriptor: D = F32, A/B = TF32 or BF16, A K-major, B MN-major, N = bn, M = 128
@@ -463,8 +472,8 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     a_row = k.K; a_batch = k.M * k.K;
     b_row = k.N; b_batch = k.K * k.N;
   }
-  if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM) ||
-      !encode_map(&st->map_b, st->bf16, b_base, k.N, k.K, k.batch, b_row, b_batch, chunk_n, slab_k))
+  if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
+      !encode_map(&st->map_b, st->bf16, b_base, k.N, k.K, k.batch, b_row, b_batch, chunk_n, slab_k, !st->bf16))
     return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
   cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->smem_bytes)
                            : cudaFuncSetAttribute(mm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->smem_bytes);
