@@ -214,23 +214,24 @@ class GPUExecutable:
             return [o.clone() for o in self.static_outputs]
 
     def profile(self, *inputs, iters=20):
-        """[(launch name, milliseconds)] per device launch, CUDA events around each."""
+        """[(launch name, milliseconds)] per launch of the plan.
+
+        Each launch is timed on its own as GPU time: ``iters`` back-to-back launches of it captured
+        in one CUDA graph and the replay timed with CUDA events (a launch takes microseconds, less
+        than the host needs to enqueue it).  Launches are idempotent -- no kernel writes a buffer it
+        reads -- so repeating one does not disturb the others' inputs.
+        """
         inputs = self._prepare(inputs)
         with torch.cuda.device(self.device):
             for static, t in zip(self.static_inputs, inputs):
                 static.copy_(t)
             self._launch()
             torch.cuda.synchronize(self.device)
-            totals = [0.0] * len(self.kernel_names)
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            for _ in range(iters):
-                for i in range(len(self.kernel_names)):
-                    start.record()
-                    self.launch_kernel(i)
-                    end.record()
-                    end.synchronize()
-                    totals[i] += start.elapsed_time(end)
-        return [(name, total / iters) for name, total in zip(self.kernel_names, totals)]
+            out = []
+            for i, name in enumerate(self.kernel_names):
+                seconds = kernel_seconds(lambda i=i: self.launch_kernel(i), repeats=iters, rounds=3)
+                out.append((name, seconds * 1e3))
+        return out
 
     def close(self):
         if getattr(self, "_plan", None) is not None and self._plan:
