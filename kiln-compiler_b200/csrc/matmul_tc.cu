@@ -33,6 +33,7 @@ constexpr int kTileM = 128;
 constexpr int kSlabBytes = 128;           // bytes of K (A) or N (B) per swizzled row
 constexpr int kATileBytes = kTileM * kSlabBytes;
 constexpr int kMaxStages = 8;
+constexpr int kMaxDynamicSmem = 225 * 1024;   // opt-in ceiling, the same for every launch of the kernel
 constexpr uint32_t kWaitLimit = 1u << 20; // try_wait attempts before giving up (each blocks up to ~1 us..ms)
 
 struct TcParams {
@@ -515,8 +516,10 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
       !encode_map(&st->map_b, st->bf16, b_base, k.N, k.K, k.batch, b_row, b_batch, chunk_n, slab_k, !st->bf16))
     return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
-  cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->smem_bytes)
-                           : cudaFuncSetAttribute(mm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->smem_bytes);
+  // The attribute is per function, not per launch: always ask for the ceiling, so that plans with
+  // different tile configurations can coexist in one process.
+  cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem)
+                           : cudaFuncSetAttribute(mm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(mm_tc_kernel)");
   return KB200_OK;
 }
