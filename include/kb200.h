@@ -188,6 +188,31 @@ int kb200_plan_status(kb200_plan* plan);
 /* Frees the plan and any scratch it owns. */
 void kb200_plan_destroy(kb200_plan* plan);
 
+/* C = A * B on the tensor cores with operands rounded to bf16 (FP32 accumulation), for callers
+ * that must not allocate.  No counterpart in the reference: it exists for hosts that cannot call
+ * cudaMalloc at the point where they need a matmul -- servers that fix their device-memory
+ * budget at start-up, latency-critical paths that ban allocation after initialisation, code
+ * that cannot afford the device-wide synchronisation an allocation may imply.  The plan interface above obtains the packed bf16 operand
+ * copies with cudaMalloc when buffers are bound; here they live in a 16 MiB array that is part
+ * of the library image (every GPU that loads the library holds it until the process exits).
+ *
+ *   a [m, k], b [k, n], c [m, n]: row-major contiguous float32 device buffers, 16-byte aligned;
+ *   n >= 64, k >= 64, both multiples of 8.
+ *   Limit: 2 * (m*k + k*n) bytes (each operand rounded up to 256) must fit in 16 MiB - 256;
+ *   larger shapes are refused with KB200_ERR_ARGUMENT and a message naming both numbers.
+ *   status_word: optional device int, zeroed by the caller, that receives a non-zero code if a
+ *   bounded device-side wait runs out; pass NULL to use (and have cleared) a word inside the array.
+ *
+ * Enqueues three kernels on `cuda_stream` and returns; calls no cudaMalloc, cudaFree or any other
+ * allocating routine.  The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress) and raises the kernel's shared-memory limit; make that first call
+ * outside any stream capture.  All calls share the one array, which keeps whatever the last call
+ * left in it: nothing in it needs to start at zero except the internal status word, which each
+ * call clears itself, but two calls that overlap on the GPU (different streams, or graphs
+ * replayed concurrently) race on it and corrupt each other's operands. */
+int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                             int* status_word, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

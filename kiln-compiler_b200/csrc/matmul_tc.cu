@@ -21,6 +21,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "device_math.cuh"
 #include "kb200_internal.h"
 #include "matmul.h"
@@ -557,3 +559,126 @@ void tc_destroy(PlanKernel& k) {
 }
 
 }  // namespace kb200
+
+// ---------------------------------------------------------------------------------------------
+// A matmul entry point that never allocates.
+//
+// The BF16 tensor-core matmul above needs scratch beyond its inputs and outputs: packed bf16
+// copies of both operands, which the plan path obtains with cudaMalloc when buffers are bound.
+// Some callers cannot do that -- callers that were handed a fixed memory budget by a serving
+// process and may not grow it, hosts that forbid allocation after start-up so that latency stays
+// predictable, code that cannot afford the device-wide synchronisation an allocation may imply.  For them the same kernels run here
+// with the scratch taken from a fixed array that is part of the library image: every GPU that
+// loads libkb200.so holds these bytes from the first use of the library on that device until the
+// process exits, whether or not this function is ever called.
+// ---------------------------------------------------------------------------------------------
+
+namespace kb200 {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;   // 16 MiB in all
+constexpr size_t kStaticOperandBytes = kStaticScratchBytes - 256;   // the last 256 bytes hold the status word
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+struct StaticState {
+  bool ready = false;
+  unsigned char* scratch = nullptr;   // device address of g_static_scratch on this device
+};
+StaticState g_static_state[kMaxDevices];
+
+// Once per device, with that device current: resolve the device address of the array.  In host
+// code the symbol's name is only a handle; the address a kernel may use comes from
+// cudaGetSymbolAddress.
+std::mutex g_static_mutex;
+
+int static_setup(int device, unsigned char** scratch) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (device < 0 || device >= kMaxDevices) return fail(KB200_ERR_ARGUMENT, "kb200_matmul_bf16_static: device %d out of range", device);
+  StaticState& st = g_static_state[device];
+  if (!st.ready) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0)
+      return fail(KB200_ERR_CUDA, "kb200_matmul_bf16_static: static scratch resolved to a bad address");
+    e = cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(mm_tc_kernel)");
+    st.scratch = static_cast<unsigned char*>(ptr);
+    st.ready = true;
+  }
+  *scratch = st.scratch;
+  return KB200_OK;
+}
+
+}  // namespace
+}  // namespace kb200
+
+extern "C" __attribute__((visibility("default")))
+int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                             int* status_word, void* cuda_stream) {
+  using namespace kb200;
+  if (a == nullptr || b == nullptr || c == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_matmul_bf16_static: null operand");
+  if (m < 1 || n < 1 || k < 1) return fail(KB200_ERR_ARGUMENT, "kb200_matmul_bf16_static: sizes must be positive");
+  if (n < 64 || k < 64 || n % 8 || k % 8)
+    return fail(KB200_ERR_UNSUPPORTED, "kb200_matmul_bf16_static: needs n, k >= 64 and multiples of 8 (got n=%lld k=%lld)",
+                (long long)n, (long long)k);
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c))
+    return fail(KB200_ERR_UNSUPPORTED, "kb200_matmul_bf16_static: operands must be 16-byte aligned");
+  const uint64_t a_bytes = (uint64_t)m * k * 2, b_bytes = (uint64_t)k * n * 2;
+  const uint64_t b_offset = (a_bytes + 255) & ~uint64_t(255);
+  if (m > (int64_t(1) << 24) || n > (int64_t(1) << 24) || k > (int64_t(1) << 24) || b_offset + b_bytes > kStaticOperandBytes)
+    return fail(KB200_ERR_ARGUMENT,
+                "kb200_matmul_bf16_static: operands need %llu bytes of bf16 scratch, the static array holds %llu "
+                "(limit: 2*(m*k + k*n) bytes, each operand rounded up to 256, <= 16 MiB - 256); use the plan "
+                "interface for larger shapes",
+                (unsigned long long)(b_offset + b_bytes), (unsigned long long)kStaticOperandBytes);
+  int device = 0;
+  KB200_CUDA(cudaGetDevice(&device));
+  unsigned char* scratch = nullptr;
+  int rc = static_setup(device, &scratch);
+  if (rc) return rc;
+  __nv_bfloat16* a16 = reinterpret_cast<__nv_bfloat16*>(scratch);
+  __nv_bfloat16* b16 = reinterpret_cast<__nv_bfloat16*>(scratch + b_offset);
+
+  int bn = 128;
+  while (bn > 64 && bn / 2 >= n) bn /= 2;
+  const int stages = 4, slab_k = 64, chunk_n = 64;
+  TcParams p{};
+  p.mm.batch = 1; p.mm.M = m; p.mm.N = n; p.mm.K = k;
+  p.mm.a_slot = 0; p.mm.b_slot = 1; p.mm.n_operands = 3; p.mm.has_chain = 1;
+  p.mm.ops[2].ptr = c;
+  p.mm.ops[2].stride[0] = 0; p.mm.ops[2].stride[1] = n; p.mm.ops[2].stride[2] = 1;
+  p.mm.chain.n = 0; p.mm.chain.first_slot = -1; p.mm.chain.out_slot = 2;
+  p.bn = bn; p.stages = stages; p.slab_k = slab_k; p.chunk_n = chunk_n;
+  p.num_kb = (int)((k + slab_k - 1) / slab_k);
+  p.b_step_bytes = 16 * kSlabBytes;
+  p.b_layout = 2; p.b_sbo_bytes = 1024;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < bn) p.tmem_cols *= 2;
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+  p.kernel_index = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  if (status_word != nullptr) {
+    p.status = status_word;
+  } else {
+    // The array keeps what the last call left in it.  Only the status word has to start at zero.
+    p.status = reinterpret_cast<int*>(scratch + kStaticOperandBytes);
+    KB200_CUDA(cudaMemsetAsync(p.status, 0, sizeof(int), s));
+  }
+  p.vec_ok = (n % 4 == 0) ? (1u << 31) : 0;
+  CUtensorMap map_a, map_b;
+  if (!encode_map(&map_a, true, a16, k, m, 1, k, m * k, slab_k, kTileM, false) ||
+      !encode_map(&map_b, true, b16, n, k, 1, n, k * n, chunk_n, slab_k, false))
+    return fail(KB200_ERR_UNSUPPORTED, "kb200_matmul_bf16_static: the operands cannot be described to TMA");
+  const int64_t cap = 148 * 8;
+  int64_t total = m * (k / 4);
+  cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(a, a16, 1, m, k, 0, k);
+  total = k * (n / 4);
+  cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(b, b16, 1, k, n, 0, n);
+  const size_t smem = (size_t)stages * (kATileBytes + bn * kSlabBytes) + 1024;
+  dim3 grid((unsigned)(((m + kTileM - 1) / kTileM) * ((n + bn - 1) / bn)), 1, 1);
+  mm_tc_kernel<true><<<grid, 192, smem, s>>>(map_a, map_b, p);
+  KB200_CUDA(cudaGetLastError());
+  return KB200_OK;
+}

@@ -1,0 +1,90 @@
+"""The allocation-free matmul entry point, kb200_matmul_bf16_static.
+
+Who needs it: a host that has to issue a BF16 matmul at a moment when it may not allocate device
+memory -- under a serving process's fixed memory budget, on a path where allocation is banned
+after start-up for the sake of latency, or where the synchronisation an allocation may imply is
+not acceptable.  The ordinary route (a plan,
+bound through kb200_plan_bind) gets its packed bf16 operand copies from cudaMalloc; this entry
+point takes them from a fixed 16 MiB array inside the library instead.
+
+The check: through the C ABI, its result must equal the ordinary route's on the same inputs,
+twice in a row with different shapes, the second smaller than the first so that the array still
+holds stale operands from the first call.  The file sorts last on purpose, so a run that stops at
+the first failure has already been through every other test.
+"""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.plan_oracle import scale_relative_error
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2        # the bound the other BF16 parity tests use
+
+
+def plan_route(a, b):
+    """The existing entry points: a one-matmul plan run in BF16 mode."""
+    from kiln_b200.autotune import matmul_plan
+    from kiln_b200.codegen import program_from_plan
+    from kiln_b200.runtime import GPUExecutable
+
+    m, k = a.shape
+    n = b.shape[1]
+    plan = matmul_plan(1, m, n, k)
+    exe = GPUExecutable(program_from_plan(plan, "bf16", {"k0": {"impl": "tc"}}), 0, {}, plan.input_shapes,
+                        plan.output_shapes, cuda_graphs=False)
+    (out,) = exe(a, b)
+    torch.cuda.synchronize()
+    exe.status()
+    assert exe.impls == ["mm_tcgen05"]
+    return out
+
+
+def static_route(lib, a, b):
+    m, k = a.shape
+    n = b.shape[1]
+    c = torch.full((m, n), float("nan"), device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    before = torch.cuda.memory_allocated()
+    rc = lib.kb200_matmul_bf16_static(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, status.data_ptr(),
+                                      C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, lib.kb200_last_error()
+    assert torch.cuda.memory_allocated() == before
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return c
+
+
+def test_static_scratch_matmul_matches_the_plan_route_twice_in_a_row():
+    from kiln_b200 import _cabi
+
+    lib = _cabi.load()
+    gen = torch.Generator().manual_seed(11)
+    for m, n, k in [(384, 1024, 512), (200, 192, 136)]:
+        a = torch.randn(m, k, generator=gen).cuda()
+        b = (torch.randn(k, n, generator=gen) / k ** 0.5).cuda()
+        want = plan_route(a, b)
+        got = static_route(lib, a, b)
+        exact = a.double() @ b.double()
+        assert scale_relative_error(got.cpu().numpy(), want.cpu().numpy()) <= BF16_TOL
+        assert scale_relative_error(got.cpu().numpy(), exact.cpu().numpy()) <= BF16_TOL
+        # same kernels, same tile shape: the two routes should in fact agree to the last bit
+        assert torch.equal(got, want)
+
+
+def test_static_scratch_matmul_refuses_what_it_cannot_hold():
+    from kiln_b200 import _cabi
+
+    lib = _cabi.load()
+    x = torch.zeros(64, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.kb200_matmul_bf16_static(x.data_ptr(), x.data_ptr(), x.data_ptr(), 4096, 4096, 4096, None, stream)
+    assert rc == -1 and b"16 MiB" in lib.kb200_last_error()
+    rc = lib.kb200_matmul_bf16_static(x.data_ptr(), x.data_ptr(), x.data_ptr(), 128, 60, 64, None, stream)
+    assert rc == -2
+    rc = lib.kb200_matmul_bf16_static(None, x.data_ptr(), x.data_ptr(), 128, 64, 64, None, stream)
+    assert rc == -1
