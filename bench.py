@@ -357,6 +357,30 @@ def gpu_arm(args, dist, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
+def single_case(args):
+    """One stored plan, launched directly (no CUDA graph) so a profiler sees plain kernel launches."""
+    from gpu_helpers import build_executable
+    from helpers import case_data, load_plan
+
+    plan = load_plan(args.case)
+    inputs, consts, _ = case_data(args.case, plan)
+    exe = build_executable(args.case, args.precision, cuda_graphs=False, plan_json=plan, consts=consts)
+    for static, x in zip(exe.static_inputs, inputs):
+        static.copy_(torch.from_numpy(np.ascontiguousarray(x)))
+    for _ in range(max(1, args.warmup)):
+        exe.run_static()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        exe.run_static()
+    end.record()
+    torch.cuda.synchronize()
+    exe.status()
+    print(json.dumps({"case": args.case, "precision": args.precision, "impls": exe.impls,
+                      "ms_per_call": start.elapsed_time(end) / args.steps, "launches_per_call": exe.device_launches}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -366,7 +390,13 @@ def main():
     ap.add_argument("--precision", default=os.environ.get("KB200_BENCH_PRECISION", "bf16"),
                     choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--case", default=None,
+                    help="run one stored plan (a name under tests/golden/plans) --steps times and print its GPU "
+                         "time per call; the small, single-kernel workload to put under a profiler")
     args = ap.parse_args()
+    if args.case:
+        single_case(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         rank = int(os.environ.get("RANK", 0))
