@@ -2,15 +2,17 @@
 // tcgen05.mma -> TMEM accumulator -> epilogue from TMEM.  Role of the reference's matmul generator
 // with input_precision="tf32" (kiln/gpu/codegen.py:484-530), plus a BF16-operand mode.
 //
-// One CTA computes one 128 x BN tile of C for one batch entry, 192 threads in three roles:
+// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles; 320 threads in three roles:
 //   warp 0      TMA producer: per K slab, one box of A (128 rows x 128 bytes, K-major) and BN/chunk
 //               boxes of B (slab rows x 128 bytes, N-major -- the layout the buffer-assignment pass
 //               guarantees for B, kiln/passes/buffers.py:208-217, so nothing is repacked), both
 //               written with the 128-byte swizzle the MMA descriptors expect.  Plain per-CTA loads.
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = BN, K = 32 bytes per
 //               instruction) on the slab and commits the stage back to the producer.
-//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time (each thread owns one row of the tile),
-//               the fused chain on registers (bias, GELU, residual, scale + mask ...), 128-bit stores.
+//   warps 2..9  epilogue: tcgen05.ld 32 columns at a time, a 32 x 32 transpose through shared memory
+//               so that a warp's loads and stores cover 128 contiguous bytes of a row, the fused
+//               chain on registers (bias, GELU, residual, scale + mask ...).  The accumulator is
+//               double-buffered in TMEM: the epilogue of tile i overlaps the main loop of tile i+1.
 // A is read K-major and B N-major straight from the planned buffers (float32, consumed as TF32).
 // In BF16 mode both operands are first converted into packed bf16 scratch (constants once at
 // bind, activations per launch) and the same kernel runs with kind::f16.
@@ -35,6 +37,9 @@ constexpr int kTileM = 128;
 constexpr int kSlabBytes = 128;           // bytes of K (A) or N (B) per swizzled row
 constexpr int kATileBytes = kTileM * kSlabBytes;
 constexpr int kMaxStages = 8;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;      // producer warp, MMA warp, epilogue warps
+constexpr int kEpiBytes = kEpiWarps * 32 * 33 * 4;  // per-warp 32 x 33 transpose buffers
 constexpr int kMaxDynamicSmem = 225 * 1024;   // opt-in ceiling, the same for every launch of the kernel
 constexpr uint32_t kWaitLimit = 1u << 20; // try_wait attempts before giving up (each blocks up to ~1 us..ms)
 
@@ -48,11 +53,17 @@ struct TcParams {
   int b_step_bytes;     // bytes between consecutive MMA K steps inside a B chunk
   int b_sbo_bytes;      // bytes between the row groups of one swizzle atom of B
   int b_layout;         // descriptor layout type of B (1 = 128-byte swizzle on 32-byte atoms, 2 = 128-byte swizzle)
+  int b_kmajor;         // B is read K-major ([N, K] with K contiguous) like A: one box per slab
+  int debug;            // timing experiments only: 1 = no stores, 2 = no MMA, 4 = no TMA (results are then wrong)
   int tmem_cols;        // power of two >= bn, >= 32
   uint32_t idesc;
   int kernel_index;
   int* status;
-  int vec_ok;           // bit s: side operand of chain step s can be read with float4; bit 31: output
+  int tiles_m, tiles_n, num_tiles;   // tiles per batch entry along M and N; total over the batch
+  int splits;           // split-K factor: a tile's K range is shared by this many work units
+  int num_units;        // num_tiles * splits
+  float* partials;      // splits > 1: [unit][128][bn] float32 partial tiles
+  unsigned* counters;   // splits > 1: [tile][kEpiWarps] arrivals, left at zero by the last arriver
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -67,7 +78,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -187,52 +198,51 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
 #undef KB200_EACH
 }
 
-// The fused chain on 32 consecutive columns of one row.
-__device__ __forceinline__ void epilogue_row32(const TcParams& p, float (&v)[32], int64_t b, int64_t m, int64_t n0) {
+// The fused chain on a 32 x 32 block of the tile, after the block went through shared memory so
+// that a lane owns one COLUMN (x[r] = row r): every global load / store of a warp then covers 128
+// contiguous bytes of one row, and the 32 rows give 32 independent loads in flight per lane.
+__device__ __forceinline__ void epilogue_block32(const TcParams& p, float (&x)[32], int64_t b, int64_t m_first, int64_t n) {
   const MatmulParams& mm = p.mm;
-  const int64_t n_left = mm.N - n0;       // > 0
+  const bool col_ok = n < mm.N;
+  const int64_t rows_left = mm.M - m_first;   // may be <= 0 for a tile hanging over the bottom edge
   for (int s = 0; s < mm.chain.n; ++s) {
     const ChainStep st = mm.chain.steps[s];
     float side[32];
     if (st.slot >= 0) {
       const DevOperand& o = mm.ops[st.slot];
-      const float* base = o.ptr + b * o.stride[0] + m * o.stride[1] + n0 * o.stride[2];
-      if (((p.vec_ok >> s) & 1) && n_left >= 32) {
+      const float* base = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
+      if (o.stride[1] == 0) {                  // one value per column (bias): a single load
+        const float t = (col_ok && rows_left > 0) ? __ldg(base) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 t = __ldg(reinterpret_cast<const float4*>(base + j));
-          side[j] = t.x; side[j + 1] = t.y; side[j + 2] = t.z; side[j + 3] = t.w;
-        }
+        for (int r = 0; r < 32; ++r) side[r] = t;
       } else {
-        const int64_t sn = o.stride[2];
+        const int64_t sm = o.stride[1];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) side[j] = j < n_left ? base[j * sn] : 0.0f;
+        for (int r = 0; r < 32; ++r) side[r] = (col_ok && r < rows_left) ? __ldg(base + r * sm) : 0.0f;
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) side[j] = st.imm;
+      for (int r = 0; r < 32; ++r) side[r] = st.imm;
     }
-    chain_step32(st.op, v, side);
+    chain_step32(st.op, x, side);
   }
+  if (p.debug & 1) return;
   const DevOperand& o = mm.ops[mm.chain.out_slot];
-  float* out = o.ptr + b * o.stride[0] + m * o.stride[1] + n0 * o.stride[2];
-  if (((p.vec_ok >> 31) & 1) && n_left >= 32) {
+  float* out = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
+  const int64_t sm = o.stride[1];
+  if (col_ok) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
-    const int64_t sn = o.stride[2];
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < n_left) out[j * sn] = v[j];
+    for (int r = 0; r < 32; ++r)
+      if (r < rows_left) out[r * sm] = x[r];
   }
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
              const __grid_constant__ TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 1];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -241,13 +251,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const int b_tile_bytes = p.bn * kSlabBytes;
   const int stage_bytes = kATileBytes + b_tile_bytes;
+  float* epi_buf = reinterpret_cast<float*>(smem_raw + (tiles - raw) + (size_t)p.stages * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]), accum_bar = smem_u32(&bars[2 * kMaxStages]);
-
-  const int64_t tiles_n = (p.mm.N + p.bn - 1) / p.bn;
-  const int64_t m0 = (int64_t)(blockIdx.x / tiles_n) * kTileM;
-  const int64_t n0 = (int64_t)(blockIdx.x % tiles_n) * p.bn;
-  const int batch = blockIdx.z;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
+  const uint32_t tfull0 = smem_u32(&bars[2 * kMaxStages]), tempty0 = smem_u32(&bars[2 * kMaxStages + 2]);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -255,7 +262,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, kEpiWarps);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -269,25 +279,41 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int n_chunks = p.bn / p.chunk_n;
       const int chunk_bytes = p.slab_k * kSlabBytes;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t it = kb / p.stages;
-        if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_ptr)) {
-          if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 1); *abort_ptr = 1; }
-          break;
+      uint32_t slab = 0, ring_phase = 0;       // ring position and how often the ring has wrapped (mod 2)
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x) {
+        const int tile = unit / p.splits, ks = unit - tile * p.splits;
+        const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+        const int m0 = (rem / p.tiles_n) * kTileM, n0 = (rem % p.tiles_n) * p.bn;
+        const int kb_end = (ks + 1) * p.num_kb / p.splits;
+        for (int kb = ks * p.num_kb / p.splits; kb < kb_end; ++kb) {
+          const int s = (int)slab;
+          const uint32_t it = ring_phase;
+          if (++slab == (uint32_t)p.stages) { slab = 0; ring_phase ^= 1; }
+          if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_ptr)) {
+            if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 1); *abort_ptr = 1; }
+            ok = false;
+            break;
+          }
+          const uint32_t full = full0 + 8 * s;
+          if (p.debug & 4) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full) : "memory"); continue; }
+          mbar_expect_tx(full, (uint32_t)stage_bytes);
+          const uint32_t a_dst = tiles + s * stage_bytes;
+          tma_load_3d(a_dst, &tma_a, full, kb * p.slab_k, m0, batch);
+          if (p.b_kmajor) {
+            tma_load_3d(a_dst + kATileBytes, &tma_b, full, kb * p.slab_k, n0, batch);
+          } else {
+            for (int c = 0; c < n_chunks; ++c)
+              tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, n0 + c * p.chunk_n, kb * p.slab_k, batch);
+          }
         }
-        const uint32_t full = full0 + 8 * s;
-        mbar_expect_tx(full, (uint32_t)stage_bytes);
-        const uint32_t a_dst = tiles + s * stage_bytes;
-        tma_load_3d(a_dst, &tma_a, full, kb * p.slab_k, (int)m0, batch);
-        for (int c = 0; c < n_chunks; ++c)
-          tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, (int)n0 + c * p.chunk_n, kb * p.slab_k, batch);
       }
     }
   } else if (warp == 1) {
@@ -295,41 +321,116 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     if (lane == 0) {
       const uint32_t lbo = (uint32_t)(p.slab_k * kSlabBytes);   // between N chunks of B
       bool ok = true;
-      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t it = kb / p.stages;
-        if (!mbar_wait(full0 + 8 * s, it & 1, abort_ptr)) {
-          if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
-          ok = false;
+      uint32_t slab = 0, ring_phase = 0;
+      int i = 0;
+      for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
+        const int ks = unit % p.splits;
+        const int kb_begin = ks * p.num_kb / p.splits, kb_end = (ks + 1) * p.num_kb / p.splits;
+        const int acc = i & 1;
+        const uint32_t aph = (i >> 1) & 1;
+        // the epilogue must have drained this accumulator (two tiles ago) before it is overwritten
+        if (!mbar_wait(tempty0 + 8 * acc, aph ^ 1, abort_ptr)) {
+          if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 4); *abort_ptr = 1; }
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = tiles + s * stage_bytes;
-        const uint32_t b_addr = a_addr + kATileBytes;
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.bn);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          const int s = (int)slab;
+          const uint32_t it = ring_phase;
+          if (++slab == (uint32_t)p.stages) { slab = 0; ring_phase ^= 1; }
+          if (!mbar_wait(full0 + 8 * s, it & 1, abort_ptr)) {
+            if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
+            ok = false;
+            break;
+          }
+          const uint32_t a_addr = tiles + s * stage_bytes;
+          const uint32_t b_addr = a_addr + kATileBytes;
 #pragma unroll
-        for (int k = 0; k < kSlabBytes / 32; ++k) {
-          const uint64_t adesc = make_desc(a_addr + k * 32, 16, 1024);
-          const uint64_t bdesc = make_desc(b_addr + k * p.b_step_bytes, lbo, (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
-          umma(tmem_base, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u, BF16);
+          for (int k = 0; k < kSlabBytes / 32; ++k) {
+            if (p.debug & 2) break;
+            const uint64_t adesc = make_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = p.b_kmajor ? make_desc(b_addr + k * 32, 16, 1024)
+                                              : make_desc(b_addr + k * p.b_step_bytes, lbo, (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
+            umma(tmem_d, adesc, bdesc, p.idesc, (kb > kb_begin || k != 0) ? 1u : 0u, BF16);
+          }
+          if (p.debug & 8) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
+          else umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
         }
-        umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+        if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA of this tile has completed
       }
-      umma_commit(accum_bar);          // arrives when every MMA issued so far has completed
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int quad = warp & 3;                      // TMEM lanes 32 * quad .. + 31 belong to this warp
-    const int64_t m = m0 + quad * 32 + lane;
-    bool ok = mbar_wait(accum_bar, 0, abort_ptr);
-    if (!ok && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !*abort_ptr;
-    if (ok) {
+    // ---------------- epilogue (warps 2..9) ----------------
+    // Two warps per TMEM lane quadrant (a warp may only touch lanes 32 * (warp % 4) ..+31); the
+    // pair splits the 32-column chunks of the tile between them.
+    const int e = warp - 2;
+    const int quad = warp & 3;
+    const int half = e >> 2;
+    float* tbuf = epi_buf + e * (32 * 33);
+    int i = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
+      const int tile = unit / p.splits, ks = unit - tile * p.splits;
+      const int acc = i & 1;
+      const uint32_t aph = (i >> 1) & 1;
+      const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const int64_t m0 = (int64_t)(rem / p.tiles_n) * kTileM, n0 = (int64_t)(rem % p.tiles_n) * p.bn;
+      bool got = mbar_wait(tfull0 + 8 * acc, aph, abort_ptr);
+      if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
+      ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
+      if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      for (int c = 0; c < p.bn; c += 32) {
-        if (n0 + c >= p.mm.N) break;              // uniform across the warp
+      // this warp's share of the tile: rows quad*32..+31, column chunks half*32, +64, ...
+      float* part = p.splits > 1 ? p.partials + ((size_t)unit * kTileM + quad * 32) * p.bn : nullptr;
+      for (int c = half * 32; c < p.bn; c += 64) {
+        if (n0 + c >= p.mm.N || (p.debug & 16)) break;   // uniform across the warp
         float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, v);
-        if (m < p.mm.M) epilogue_row32(p, v, batch, m, n0 + c);
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
+        // transpose through shared memory: lane = row  ->  lane = column
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = v[j];
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < 32; ++r) v[r] = tbuf[r * 33 + lane];
+        __syncwarp();
+        if (p.splits == 1) {
+          epilogue_block32(p, v, batch, m0 + quad * 32, n0 + c + lane);
+        } else {
+#pragma unroll
+          for (int r = 0; r < 32; ++r) __stcg(part + r * p.bn + c + lane, v[r]);
+        }
+      }
+      // this warp is done reading the accumulator: hand it back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * acc) : "memory");
+      if (p.splits > 1) {
+        // Split-K: the same warp slot of the other units of this tile owns the same sub-block.  The
+        // last of them to arrive sums the partial sub-blocks in unit order (so the result does not
+        // depend on arrival order), applies the epilogue and resets the counter for the next launch.
+        __threadfence();
+        unsigned prev = 0;
+        if (lane == 0) prev = atomicAdd(p.counters + (size_t)tile * kEpiWarps + e, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == (unsigned)(p.splits - 1)) {
+          __threadfence();
+          const float* first = p.partials + ((size_t)tile * p.splits * kTileM + quad * 32) * p.bn;
+          for (int c = half * 32; c < p.bn; c += 64) {
+            if (n0 + c >= p.mm.N) break;
+            float v[32];
+#pragma unroll
+            for (int r = 0; r < 32; ++r) v[r] = 0.0f;
+            for (int sp = 0; sp < p.splits; ++sp) {
+              const float* src = first + (size_t)sp * kTileM * p.bn + c + lane;
+#pragma unroll
+              for (int r = 0; r < 32; ++r) v[r] += __ldcg(src + r * p.bn);
+            }
+            epilogue_block32(p, v, batch, m0 + quad * 32, n0 + c + lane);
+          }
+          if (lane == 0) p.counters[(size_t)tile * kEpiWarps + e] = 0u;
+        }
+        (void)ks;
       }
     }
   }
@@ -395,6 +496,9 @@ struct TcState {
   __nv_bfloat16* a16 = nullptr;
   __nv_bfloat16* b16 = nullptr;
   bool b_const = false;       // B is a frozen constant: converted once at bind
+  // split-K workspace
+  float* partials = nullptr;
+  unsigned* counters = nullptr;
 };
 
 // A 3-D tiled map over [batch, rows, cols] with cols contiguous; box = (box_cols, box_rows, 1).
@@ -429,10 +533,12 @@ bool tc_eligible(const PlanKernel& k) {
   if (k.M < 32 || k.N < 64 || k.K < 64) return false;
   if (k.N % 4 || k.K % 4) return false;
   if (d.precision == KB200_PREC_BF16 && (k.N % 8 || k.K % 8)) return false;
-  // A: K contiguous; B: N contiguous; 16-byte aligned bases and strides
-  if (A.stride[2] != 1 || B.stride[2] != 1) return false;
-  if (A.stride[1] % 4 || A.stride[0] % 4 || B.stride[1] % 4 || B.stride[0] % 4) return false;
-  if (A.stride[1] == 0 || B.stride[1] == 0) return false;
+  // A: K contiguous; B: N contiguous or K contiguous; 16-byte aligned bases and strides
+  if (A.stride[2] != 1) return false;
+  const bool b_nmajor = B.stride[2] == 1, b_kmajor = !b_nmajor && B.stride[1] == 1 && B.stride[2] != 0;
+  if (!b_nmajor && !b_kmajor) return false;
+  if (A.stride[1] % 4 || A.stride[0] % 4 || B.stride[1] % 4 && b_nmajor || B.stride[2] % 4 && b_kmajor || B.stride[0] % 4) return false;
+  if (A.stride[1] == 0 || (b_nmajor && B.stride[1] == 0)) return false;
   if (k.batch > 1 && (A.stride[0] == 0 || B.stride[0] == 0)) return false;
   if (!aligned16(A.ptr) || !aligned16(B.ptr)) return false;
   return true;
@@ -447,16 +553,22 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   }
   st->bf16 = d.precision == KB200_PREC_BF16;
   const int chunk_n = st->bf16 ? 64 : 32, slab_k = st->bf16 ? 64 : 32;
-  int bn = d.cfg[1] > 0 ? d.cfg[1] : 128;
+  int bn = d.cfg[1];
+  if (bn <= 0) {
+    // widest tile that still gives every SM one; otherwise 128 columns and split K to fill the machine
+    bn = k.N >= 128 ? 128 : 64;
+    const int64_t tiles_m = (k.M + kTileM - 1) / kTileM;
+    if (k.N >= 256 && tiles_m * ((k.N + 255) / 256) * k.batch >= plan.sm_count) bn = 256;
+  }
   if (bn > 256) bn = 256;
-  bn = (bn / chunk_n) * chunk_n;
-  if (bn < chunk_n) bn = chunk_n;
-  while (bn > chunk_n && bn / 2 >= k.N) bn /= 2;          // do not make the tile wider than the problem
-  if (bn % 16) return fail(KB200_ERR_ARGUMENT, "matmul %s: tile width %d is not a multiple of 16", d.name, bn);
+  bn = (bn / 64) * 64;                                    // the two epilogue warps of a quadrant take 32 columns each
+  if (bn < 64) bn = 64;
+  while (bn > 64 && bn / 2 >= k.N) bn /= 2;               // do not make the tile wider than the problem
+  (void)chunk_n;
   int stages = d.cfg[3] > 0 ? d.cfg[3] : 4;
   if (stages > kMaxStages) stages = kMaxStages;
   const int stage_bytes = kATileBytes + bn * kSlabBytes;
-  while (stages > 2 && (size_t)stages * stage_bytes + 1024 > 220 * 1024) --stages;
+  while (stages > 2 && (size_t)stages * stage_bytes + kEpiBytes + 1024 > (size_t)kMaxDynamicSmem) --stages;
   TcParams& p = st->params;
   fill_matmul_params(k, &p.mm);
   p.bn = bn;
@@ -469,31 +581,58 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   // pattern repeats every 4 rows; 16-bit elements use the ordinary 128-byte swizzle (8 rows).
   p.b_layout = st->bf16 ? 2 : 1;
   p.b_sbo_bytes = st->bf16 ? 1024 : 512;
+  p.b_kmajor = k.ops[d.b_slot].stride[2] == 1 ? 0 : 1;
+  p.debug = d.cfg[6];
   p.tmem_cols = 32;
-  while (p.tmem_cols < bn) p.tmem_cols *= 2;
+  while (p.tmem_cols < 2 * bn) p.tmem_cols *= 2;           // two accumulators: the epilogue drains one while the next tile fills the other
+  p.tiles_m = (int)((k.M + kTileM - 1) / kTileM);
+  p.tiles_n = (int)((k.N + bn - 1) / bn);
+  p.num_tiles = p.tiles_m * p.tiles_n * (int)k.batch;
+  // Split K when the tiles alone would leave most SMs idle (128-token projections, the narrow
+  // 768-wide layers): every SM then streams a share of the operands.
+  int splits = d.cfg[4];
+  if (splits <= 0) {
+    splits = 1;
+    if (p.num_tiles * 2 <= plan.sm_count) {
+      splits = plan.sm_count / p.num_tiles;
+      if (splits > p.num_kb / 4) splits = p.num_kb / 4;
+      if (splits > 8) splits = 8;
+      if (splits < 1) splits = 1;
+    }
+  }
+  if (splits > p.num_kb) splits = p.num_kb;
+  if (splits > 16) splits = 16;
+  p.splits = splits;
+  p.num_units = p.num_tiles * splits;
+  p.partials = nullptr;
+  p.counters = nullptr;
+  if (st->partials) { cudaFree(st->partials); st->partials = nullptr; }
+  if (st->counters) { cudaFree(st->counters); st->counters = nullptr; }
+  if (splits > 1) {
+    KB200_CUDA(cudaMalloc(&st->partials, (size_t)p.num_units * kTileM * bn * sizeof(float)));
+    KB200_CUDA(cudaMalloc(&st->counters, (size_t)p.num_tiles * kEpiWarps * sizeof(unsigned)));
+    KB200_CUDA(cudaMemset(st->counters, 0, (size_t)p.num_tiles * kEpiWarps * sizeof(unsigned)));
+    p.partials = st->partials;
+    p.counters = st->counters;
+  }
   // instruction descriptor: D = F32, A/B = TF32 or BF16, A K-major, B MN-major, N = bn, M = 128
   const uint32_t fmt = st->bf16 ? 1u : 2u;
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | ((p.b_kmajor ? 0u : 1u) << 16) | ((uint32_t)(bn >> 3) << 17) |
+            ((uint32_t)(kTileM >> 4) << 24);
   p.kernel_index = kernel_index;
   p.status = plan.d_status;
-  p.vec_ok = 0;
-  if (k.has_chain) {
-    auto vec = [&](int slot) {
-      const DevOperand& o = k.ops[slot];
-      return o.stride[2] == 1 && o.stride[1] % 4 == 0 && o.stride[0] % 4 == 0 && aligned16(o.ptr) && bn % 32 == 0;
-    };
-    for (int s = 0; s < k.chain.n; ++s)
-      if (k.chain.steps[s].slot >= 0 && vec(k.chain.steps[s].slot)) p.vec_ok |= 1 << s;
-    if (vec(k.chain.out_slot)) p.vec_ok |= 1u << 31;
-  }
-  st->smem_bytes = (size_t)stages * stage_bytes + 1024;
-  st->grid = dim3((unsigned)(((k.M + kTileM - 1) / kTileM) * ((k.N + bn - 1) / bn)), 1, (unsigned)k.batch);
+  st->smem_bytes = (size_t)stages * stage_bytes + kEpiBytes + 1024;
+  // persistent CTAs, one per SM: each walks the tile list with a stride of the grid size
+  st->grid = dim3((unsigned)(p.num_units < plan.sm_count ? p.num_units : plan.sm_count), 1, 1);
 
   const DevOperand& A = k.ops[d.a_slot];
   const DevOperand& B = k.ops[d.b_slot];
   const void* a_base = A.ptr;
   const void* b_base = B.ptr;
-  int64_t a_row = A.stride[1], a_batch = A.stride[0], b_row = B.stride[1], b_batch = B.stride[0];
+  // B as a [rows, cols] matrix with cols contiguous: [K, N] when N-major, [N, K] when K-major
+  const int64_t b_rows = p.b_kmajor ? k.N : k.K, b_cols = p.b_kmajor ? k.K : k.N;
+  int64_t a_row = A.stride[1], a_batch = A.stride[0], b_row = p.b_kmajor ? B.stride[2] : B.stride[1], b_batch = B.stride[0];
+  const int64_t b_src_row = b_row;
   k.launches = 1;
   if (st->bf16) {
     if (st->a16) cudaFree(st->a16);
@@ -503,9 +642,9 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     KB200_CUDA(cudaMalloc(&st->b16, (size_t)k.batch * k.K * k.N * 2));
     st->b_const = d.operands[d.b_slot].base_kind == KB200_BASE_CONST;
     if (st->b_const) {
-      const int64_t total = k.batch * k.K * (k.N / 4);
+      const int64_t total = k.batch * b_rows * (b_cols / 4);
       cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256>>>(
-          B.ptr, st->b16, k.batch, k.K, k.N, B.stride[0], B.stride[1]);
+          B.ptr, st->b16, k.batch, b_rows, b_cols, B.stride[0], b_src_row);
       KB200_CUDA(cudaGetLastError());
       KB200_CUDA(cudaDeviceSynchronize());
     }
@@ -513,10 +652,11 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     a_base = st->a16;
     b_base = st->b16;
     a_row = k.K; a_batch = k.M * k.K;
-    b_row = k.N; b_batch = k.K * k.N;
+    b_row = b_cols; b_batch = k.K * k.N;
   }
   if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
-      !encode_map(&st->map_b, st->bf16, b_base, k.N, k.K, k.batch, b_row, b_batch, chunk_n, slab_k, !st->bf16))
+      !encode_map(&st->map_b, st->bf16, b_base, b_cols, b_rows, k.batch, b_row, b_batch, p.b_kmajor ? slab_k : chunk_n,
+                  p.b_kmajor ? bn : slab_k, !st->bf16 && !p.b_kmajor))
     return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
   // The attribute is per function, not per launch: always ask for the ceiling, so that plans with
   // different tile configurations can coexist in one process.
@@ -537,13 +677,15 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
         A.ptr, st->a16, k.batch, k.M, k.K, A.stride[0], A.stride[1]);
     if (!st->b_const) {
-      total = k.batch * k.K * (k.N / 4);
+      const bool km = st->params.b_kmajor != 0;
+      const int64_t rows = km ? k.N : k.K, cols = km ? k.K : k.N;
+      total = k.batch * rows * (cols / 4);
       cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
-          B.ptr, st->b16, k.batch, k.K, k.N, B.stride[0], B.stride[1]);
+          B.ptr, st->b16, k.batch, rows, cols, B.stride[0], km ? B.stride[2] : B.stride[1]);
     }
-    mm_tc_kernel<true><<<st->grid, 192, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
+    mm_tc_kernel<true><<<st->grid, kThreads, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
   } else {
-    mm_tc_kernel<false><<<st->grid, 192, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
+    mm_tc_kernel<false><<<st->grid, kThreads, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
   }
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
@@ -554,6 +696,8 @@ void tc_destroy(PlanKernel& k) {
   if (!st) return;
   if (st->a16) cudaFree(st->a16);
   if (st->b16) cudaFree(st->b16);
+  if (st->partials) cudaFree(st->partials);
+  if (st->counters) cudaFree(st->counters);
   delete st;
   k.tc = nullptr;
 }
@@ -655,7 +799,12 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.b_step_bytes = 16 * kSlabBytes;
   p.b_layout = 2; p.b_sbo_bytes = 1024;
   p.tmem_cols = 32;
-  while (p.tmem_cols < bn) p.tmem_cols *= 2;
+  while (p.tmem_cols < 2 * bn) p.tmem_cols *= 2;
+  p.tiles_m = (int)((m + kTileM - 1) / kTileM);
+  p.tiles_n = (int)((n + bn - 1) / bn);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.splits = 1;
+  p.num_units = p.num_tiles;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
   p.kernel_index = 0;
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
@@ -666,7 +815,6 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
     p.status = reinterpret_cast<int*>(scratch + kStaticOperandBytes);
     KB200_CUDA(cudaMemsetAsync(p.status, 0, sizeof(int), s));
   }
-  p.vec_ok = (n % 4 == 0) ? (1u << 31) : 0;
   CUtensorMap map_a, map_b;
   if (!encode_map(&map_a, true, a16, k, m, 1, k, m * k, slab_k, kTileM, false) ||
       !encode_map(&map_b, true, b16, n, k, 1, n, k * n, chunk_n, slab_k, false))
@@ -676,9 +824,11 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(a, a16, 1, m, k, 0, k);
   total = k * (n / 4);
   cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(b, b16, 1, k, n, 0, n);
-  const size_t smem = (size_t)stages * (kATileBytes + bn * kSlabBytes) + 1024;
-  dim3 grid((unsigned)(((m + kTileM - 1) / kTileM) * ((n + bn - 1) / bn)), 1, 1);
-  mm_tc_kernel<true><<<grid, 192, smem, s>>>(map_a, map_b, p);
+  const size_t smem = (size_t)stages * (kATileBytes + bn * kSlabBytes) + kEpiBytes + 1024;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  dim3 grid((unsigned)(p.num_tiles < sms ? p.num_tiles : sms), 1, 1);
+  mm_tc_kernel<true><<<grid, kThreads, smem, s>>>(map_a, map_b, p);
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }

@@ -68,8 +68,9 @@ def candidates(m, n, k):
     return out
 
 
-def matmul_plan(batch, m, n, k) -> PlanSpec:
-    """A bare [batch,] M x K by K x N matmul reading two inputs and writing one output."""
+def matmul_plan(batch, m, n, k, b_kmajor=False) -> PlanSpec:
+    """A bare [batch,] M x K by K x N matmul reading two inputs and writing one output.
+    With ``b_kmajor`` the second input is stored as [N, K] and read through a transposed view."""
     lead = (batch,) if batch > 1 else ()
 
     def contiguous(shape):
@@ -80,11 +81,16 @@ def matmul_plan(batch, m, n, k) -> PlanSpec:
         return tuple(reversed(strides))
 
     a_shape, b_shape, c_shape = (*lead, m, k), (*lead, k, n), (*lead, m, n)
+    b_stored = (*lead, n, k) if b_kmajor else b_shape
+    b_strides = contiguous(b_shape)
+    if b_kmajor:
+        st = contiguous(b_stored)
+        b_strides = (*st[:-2], st[-1], st[-2])
     kernel = KernelSpec("k0", "matmul", [NodeSpec("matmul", [("operand", 0), ("operand", 1)], c_shape)],
                         [OperandSpec(("input", 0), 0, a_shape, contiguous(a_shape)),
-                         OperandSpec(("input", 1), 0, b_shape, contiguous(b_shape))],
+                         OperandSpec(("input", 1), 0, b_shape, b_strides)],
                         [(0, OperandSpec(("output", 0), 0, c_shape, contiguous(c_shape)))])
-    return PlanSpec("matmul", [a_shape, b_shape], [c_shape], 0, {}, [kernel])
+    return PlanSpec("matmul", [a_shape, b_stored], [c_shape], 0, {}, [kernel])
 
 
 class GPUAutotuner:

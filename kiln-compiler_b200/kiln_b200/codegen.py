@@ -88,27 +88,15 @@ def _matmul_dims(kernel):
 
 
 def default_matmul_config(graph, kernel):
-    """Tile choice without measuring (role of codegen.py:563-598).
+    """The configuration used without measuring (role of codegen.py:563-598).
 
-    A tcgen05 tile is 128 rows of the output by 64..256 columns.  Take the
-    widest column tile that still gives every SM a tile; when even the
-    narrowest cannot (128-token projections), split K so the weight stream is
-    shared by more SMs.  The exact-FP32 path uses 64 x 64 register-tiled CTAs
-    and the same split-K rule.
+    All zeros: the library then applies its own rule when buffers are bound -- the widest
+    tcgen05 tile (128 rows by 256, 128 or 64 columns) that still gives every SM a tile, and,
+    when even that leaves SMs idle (128-token projections, 768-wide layers), a split of K so that
+    every SM streams a share of the operands.  The autotuner searches around this default.
     """
-    batch, m, n, k = _matmul_dims(kernel)
-    sms = sm_count()
-    tiles_m = -(-m // 128)
-    bn = 64
-    for cand in (256, 128, 64):
-        if cand <= max(64, next_pow2(n)) and tiles_m * -(-n // cand) * batch >= sms:
-            bn = cand
-            break
-    ctas = tiles_m * -(-n // bn) * batch
-    split = 1
-    while ctas * split * 2 <= sms and k // (split * 2) >= 256:
-        split *= 2
-    return {"BM": 128, "BN": bn, "BK": 32, "stages": 4, "split_k": split, "impl": "auto"}
+    del graph, kernel
+    return {"BM": 128, "BN": 0, "BK": 0, "stages": 0, "split_k": 0, "impl": "auto"}
 
 
 def _operand(layout, graph):
