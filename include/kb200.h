@@ -163,6 +163,15 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
                     void* const* inputs, const uint64_t* input_bytes, int n_inputs,
                     void* const* outputs, const uint64_t* output_bytes, int n_outputs);
 
+/* Plan options, set between kb200_plan_create and kb200_plan_bind.
+ * KB200_OPT_FUSE_ATTENTION (default 1): when the plan contains the reference's five-kernel
+ * attention chain (K^T copy, QK^T * scale + causal mask, softmax, PV, head merge; see
+ * tests/models/transformer.py:16-25 of the reference) and the matmul precision is not FP32, run
+ * it as one fused kernel.  The kernel list and arena offsets stay the reference's; the score
+ * buffers are then never written.  0 keeps one launch per planned kernel. */
+typedef enum kb200_option { KB200_OPT_FUSE_ATTENTION = 1 } kb200_option;
+int kb200_plan_set_option(kb200_plan* plan, int option, int value);
+
 /* Enqueues every kernel, in order, on `cuda_stream` (a cudaStream_t).
  * Takes the place of the launch loop GPUExecutable._run
  * (kiln/gpu/runtime.py:164-179).  No synchronisation, no allocation. */

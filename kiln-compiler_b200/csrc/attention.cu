@@ -1,0 +1,487 @@
+// Fused causal attention for sm_100a: QK^T -> online softmax -> PV in one kernel on the tensor cores.
+//
+// The fusion pass of the reference leaves attention as five kernels (tests/models/transformer.py:16-25
+// after kiln/passes/fusion.py and buffers.py): a copy that makes K^T N-contiguous, a batched matmul
+// with the scale + mask epilogue that writes [H, T, T] scores, a softmax row kernel over them, a
+// batched matmul with V, and a copy that merges the heads.  The reference lists "no fused attention"
+// as a limitation (README.md:185): the scores cross HBM twice.  When the plan contains exactly that
+// chain, the mask is the causal one, and a reduced-precision matmul mode is selected, this kernel
+// replaces the five launches: it reads Q, K and V as strided views of the QKV projection's output
+// and writes the merged-heads buffer, the only value of the chain that is live afterwards.  The
+// plan itself (kernel list, arena offsets) is untouched; the score buffers are simply never written.
+//
+// One CTA per (head, 128-query tile), 192 threads in three roles:
+//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through 2-deep rings.
+//   warp 1      MMA issuer: S = Q K^T (operands in shared memory, TF32) into one of two S buffers in
+//               TMEM; O_part = P V with P read from TMEM (written there by the softmax warps).
+//   warps 2..5  softmax: each thread owns one query row; scale, causal mask on the diagonal tile,
+//               running max / sum (online softmax), P stored back over S in TMEM, and the running
+//               output O kept in registers, rescaled and accumulated from O_part after each tile.
+// Causal tiles above the diagonal are skipped.  Every mbarrier wait is bounded (see matmul_tc.cu).
+#include <cuda.h>
+
+#include <vector>
+
+#include "device_math.cuh"
+#include "kb200_internal.h"
+#include "tc_common.cuh"
+
+namespace kb200 {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kRows = 128;                   // queries per CTA and keys per tile
+constexpr int kHeadDim = 64;
+constexpr int kSlab = kRows * 128;           // one [128 rows x 128 bytes] swizzled slab
+constexpr int kAttnThreads = 64 + 128;
+constexpr int kAttnSmem = 5 * 2 * kSlab + 1024;   // Q + 2 x K + 2 x V, two slabs each, + alignment slack
+
+struct AttnParams {
+  int T, H, q_tiles;
+  float scale_log2;          // softmax scale times log2(e): exponentials are taken in base 2
+  float* out;                // [T, H * 64] merged heads
+  int64_t out_row_stride;
+  uint32_t idesc_qk, idesc_pv;
+  int kernel_index;
+  int* status;
+};
+
+struct AttnState {
+  CUtensorMap map_q, map_k, map_v;
+  AttnParams params;
+  dim3 grid;
+  // When the planner put the merged-heads buffer over the (by then dead) QKV buffer, the fused
+  // kernel cannot write it while other CTAs still read Q, K and V: it writes here, a copy follows.
+  float* staged_out = nullptr;
+  float* final_out = nullptr;
+  int64_t out_elems = 0;
+};
+
+__global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[14];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t q_smem = (raw + 1023u) & ~1023u;
+  const uint32_t k_smem = q_smem + 2 * kSlab;       // ring of 2, each 2 slabs
+  const uint32_t v_smem = k_smem + 4 * kSlab;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 p_full | 13 o_full
+  const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
+  const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
+  const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull = smem_u32(&bars[13]);
+
+  const int h = blockIdx.x % p.H;
+  const int qt = p.q_tiles - 1 - blockIdx.x / p.H;   // heaviest (longest causal prefix) tiles first
+  const int q0 = qt * kRows;
+  const int n_kv = qt + 1;                           // causal: key tiles 0..qt
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + 8 * s, 1);
+      mbar_init(k_empty + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1);
+      mbar_init(v_empty + 8 * s, 1);
+      mbar_init(sfull0 + 8 * s, 1);
+      mbar_init(pfull0 + 8 * s, 128);
+    }
+    mbar_init(ofull, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tmem_o = tmem_base + 256;           // S0: 0..127, S1: 128..255, O_part: 256..319
+  volatile int* abort_ptr = &abort_flag;
+  auto give_up = [&](int site) {
+    if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | site); *abort_ptr = 1; }
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * kSlab);
+      tma_load_3d(q_smem, &map_q, q_full, 0, q0, h);
+      tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, q0, h);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); break; }
+        mbar_expect_tx(k_full + 8 * s, 2 * kSlab);
+        tma_load_3d(k_smem + s * 2 * kSlab, &map_k, k_full + 8 * s, 0, j * kRows, h);
+        tma_load_3d(k_smem + s * 2 * kSlab + kSlab, &map_k, k_full + 8 * s, 32, j * kRows, h);
+        if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); break; }
+        mbar_expect_tx(v_full + 8 * s, 2 * kSlab);
+        tma_load_3d(v_smem + s * 2 * kSlab, &map_v, v_full + 8 * s, 0, j * kRows, h);
+        tma_load_3d(v_smem + s * 2 * kSlab + kSlab, &map_v, v_full + 8 * s, 32, j * kRows, h);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_ptr);
+      if (!ok) give_up(0x21);
+      auto issue_qk = [&](int j) {
+        const int s = j & 1;
+        if (!mbar_wait(k_full + 8 * s, (j >> 1) & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t kb = k_smem + s * 2 * kSlab;
+#pragma unroll
+        for (int kd = 0; kd < kHeadDim / 8; ++kd) {
+          const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
+          umma(tmem_base + (uint32_t)s * 128, make_desc(q_smem + off, 16, 1024), make_desc(kb + off, 16, 1024), p.idesc_qk,
+               kd != 0 ? 1u : 0u, false);
+        }
+        umma_commit(sfull0 + 8 * s);
+        umma_commit(k_empty + 8 * s);
+      };
+      auto issue_pv = [&](int j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(v_full + 8 * s, ph, abort_ptr)) { give_up(0x23); ok = false; return; }
+        if (!mbar_wait(pfull0 + 8 * s, ph, abort_ptr)) { give_up(0x24); ok = false; return; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vb = v_smem + s * 2 * kSlab;
+#pragma unroll
+        for (int kk = 0; kk < kRows / 8; ++kk)
+          umma_ts(tmem_o, tmem_base + (uint32_t)s * 128 + (uint32_t)kk * 8, make_desc(vb + kk * 1024, kSlab, 512, 1), p.idesc_pv,
+                  kk != 0 ? 1u : 0u, false);
+        umma_commit(ofull);
+        umma_commit(v_empty + 8 * s);
+      };
+      if (ok) issue_qk(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) issue_qk(j + 1);     // the next scores are computed while the softmax warps work on tile j
+        if (ok) issue_pv(j);
+      }
+    }
+  } else {
+    // ---------------- softmax / output (warps 2..5) ----------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;              // row of the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    float o[kHeadDim];
+#pragma unroll
+    for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
+    float m_run = -CUDART_INF_F, l_run = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      bool got = mbar_wait(sfull0 + 8 * s, ph, abort_ptr);
+      if (!got) give_up(0x31);
+      ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)s * 128;
+      const bool diagonal = j == qt;
+      // pass 1: row maximum of the scaled, masked scores
+      float m_tile = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < kRows; c += 32) {
+        float v[32];
+        tmem_ld32(s_addr + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float t = (diagonal && c + i > row) ? -CUDART_INF_F : v[i] * p.scale_log2;
+          m_tile = fmaxf(m_tile, t);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float alpha = exp2f(m_run - m_new);     // 0 on the first tile (m_run = -inf)
+      // pass 2: probabilities, row sum, P back into the S buffer
+      float sum = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < kRows; c += 32) {
+        float v[32];
+        tmem_ld32(s_addr + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float t = (diagonal && c + i > row) ? -CUDART_INF_F : v[i] * p.scale_log2;
+          v[i] = exp2f(t - m_new);
+          sum += v[i];
+        }
+        tmem_st32(s_addr + c, v);
+      }
+      tmem_st_wait();
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(pfull0 + 8 * s);
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      // O = O * alpha + P V
+      got = mbar_wait(ofull, j & 1, abort_ptr);
+      if (!got) give_up(0x32);
+      ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < kHeadDim; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_o + lane_addr + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha + v[i];
+      }
+    }
+    if (ok) {
+      const float inv = 1.0f / l_run;
+      float* dst = p.out + (int64_t)(q0 + row) * p.out_row_stride + h * kHeadDim;
+#pragma unroll
+      for (int i = 0; i < kHeadDim; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+    }
+  }
+
+  // ---------------- common exit ----------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s)
+      for (uint32_t i = 0; i < 4096u; ++i)
+        if ((mbar_try_wait(k_full + 8 * s, 0) || mbar_try_wait(k_full + 8 * s, 1)) &&
+            (mbar_try_wait(v_full + 8 * s, 0) || mbar_try_wait(v_full + 8 * s, 1)))
+          break;
+  }
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+struct Range {
+  const float* lo;
+  const float* hi;
+};
+
+Range out_range(const PlanKernel& k, int slot) {
+  const kb200_kernel_desc& d = k.desc;
+  int64_t span = 0;
+  for (int i = 0; i < d.iter_rank; ++i) span += (d.iter_shape[i] - 1) * k.ops[slot].stride[i];
+  return {k.ops[slot].ptr, k.ops[slot].ptr + span + 1};
+}
+
+bool overlaps(Range a, Range b) { return a.lo < b.hi && b.lo < a.hi; }
+bool covers(Range a, Range b) { return a.lo <= b.lo && a.hi >= b.hi; }
+
+// Operand slots a kernel reads / writes.
+void io_slots(const PlanKernel& k, std::vector<int>* reads, std::vector<int>* writes) {
+  const kb200_kernel_desc& d = k.desc;
+  if (d.kclass == KB200_K_MATMUL) {
+    reads->push_back(d.a_slot);
+    reads->push_back(d.b_slot);
+  }
+  for (int t = 0; t < d.n_tape; ++t) {
+    if (d.tape[t].opcode == KB200_OP_LOAD) reads->push_back(d.tape[t].a);
+    if (d.tape[t].opcode == KB200_OP_STORE) writes->push_back(d.tape[t].b);
+  }
+}
+
+Range operand_range(const PlanKernel& k, int slot) {
+  const kb200_kernel_desc& d = k.desc;
+  int64_t ext[KB200_MAX_RANK];
+  for (int i = 0; i < d.iter_rank; ++i) ext[i] = d.iter_shape[i];
+  if (d.kclass == KB200_K_MATMUL) {
+    if (slot == d.a_slot) ext[2] = d.k_extent;
+    if (slot == d.b_slot) { ext[1] = d.k_extent; ext[2] = d.iter_shape[2]; }
+  }
+  int64_t span = 0;
+  for (int i = 0; i < d.iter_rank; ++i) span += (ext[i] - 1) * k.ops[slot].stride[i];
+  return {k.ops[slot].ptr, k.ops[slot].ptr + span + 1};
+}
+
+bool is_copy(const PlanKernel& k) {
+  return k.desc.kclass == KB200_K_ELEMENTWISE && k.has_chain && k.chain.n == 1 && k.chain.steps[0].op == CH_COPY &&
+         k.chain.first_slot >= 0;
+}
+
+}  // namespace
+
+// Tries to replace kernels i .. i+4 by the fused kernel.  Returns true when it did.
+bool attention_try_fuse(Plan& plan, size_t i) {
+  if (i + 4 >= plan.kernels.size()) return false;
+  PlanKernel& k2 = plan.kernels[i];
+  PlanKernel& k3 = plan.kernels[i + 1];
+  PlanKernel& k4 = plan.kernels[i + 2];
+  PlanKernel& k5 = plan.kernels[i + 3];
+  PlanKernel& k6 = plan.kernels[i + 4];
+  // --- k3: scores = Q K^T * scale + mask ---
+  if (k3.desc.kclass != KB200_K_MATMUL || k3.desc.precision == KB200_PREC_FP32 || !k3.has_chain) return false;
+  const int64_t H = k3.batch, T = k3.M, hd = k3.K;
+  if (hd != kHeadDim || k3.N != T || T % kRows != 0 || T < kRows || H < 1 || H > 65535) return false;
+  const DevOperand& Q = k3.ops[k3.desc.a_slot];
+  const DevOperand& Kt = k3.ops[k3.desc.b_slot];
+  const int64_t rs = Q.stride[1];
+  if (Q.stride[2] != 1 || Q.stride[0] != hd || rs % 4 || rs < H * hd) return false;
+  if (Kt.stride[0] != hd * T || Kt.stride[1] != T || Kt.stride[2] != 1) return false;
+  if (k3.chain.n != 2 || k3.chain.steps[0].op != CH_MUL || k3.chain.steps[0].slot != -1 || k3.chain.steps[1].op != CH_ADD ||
+      k3.chain.steps[1].slot < 0)
+    return false;
+  const float scale = k3.chain.steps[0].imm;
+  const DevOperand& mask = k3.ops[k3.chain.steps[1].slot];
+  if (!(scale > 0.0f) || mask.stride[0] != 0 || mask.stride[1] != T || mask.stride[2] != 1) return false;
+  if (k3.desc.operands[k3.chain.steps[1].slot].base_kind != KB200_BASE_CONST) return false;
+  const DevOperand& S = k3.ops[k3.chain.out_slot];
+  if (S.stride[0] != T * T || S.stride[1] != T || S.stride[2] != 1) return false;
+  // --- k2: K^T = copy of the K view ---
+  if (!is_copy(k2) || k2.desc.iter_rank != 2 || k2.desc.iter_shape[0] != H * hd || k2.desc.iter_shape[1] != T) return false;
+  const DevOperand& Ksrc = k2.ops[k2.chain.first_slot];
+  const DevOperand& Kdst = k2.ops[k2.chain.out_slot];
+  if (Ksrc.stride[0] != 1 || Ksrc.stride[1] != rs || Kdst.stride[0] != T || Kdst.stride[1] != 1 || Kdst.ptr != Kt.ptr) return false;
+  // --- k4: softmax over the last dim ---
+  if (k4.desc.kclass != KB200_K_ROW || k4.impl != IMPL_ROW_SOFTMAX) return false;
+  if (k4.ops[k4.x_slot].ptr != S.ptr || k4.desc.iter_shape[0] != H * T || k4.desc.iter_shape[1] != T) return false;
+  const DevOperand& P = k4.ops[k4.out_slot];
+  if (P.stride[0] != T || P.stride[1] != 1) return false;
+  // --- k5: O = P V ---
+  if (k5.desc.kclass != KB200_K_MATMUL || k5.desc.precision == KB200_PREC_FP32 || !k5.has_chain || k5.chain.n != 0) return false;
+  if (k5.batch != H || k5.M != T || k5.N != hd || k5.K != T) return false;
+  const DevOperand& Pa = k5.ops[k5.desc.a_slot];
+  const DevOperand& V = k5.ops[k5.desc.b_slot];
+  if (Pa.ptr != P.ptr || Pa.stride[0] != T * T || Pa.stride[1] != T || Pa.stride[2] != 1) return false;
+  if (V.stride[0] != hd || V.stride[1] != rs || V.stride[2] != 1) return false;
+  const DevOperand& O = k5.ops[k5.chain.out_slot];
+  if (O.stride[0] != T * hd || O.stride[1] != hd || O.stride[2] != 1) return false;
+  // --- k6: merge heads ---
+  if (!is_copy(k6) || k6.desc.iter_rank != 3 || k6.desc.iter_shape[0] != T || k6.desc.iter_shape[1] != H ||
+      k6.desc.iter_shape[2] != hd)
+    return false;
+  const DevOperand& Osrc = k6.ops[k6.chain.first_slot];
+  const DevOperand& Y = k6.ops[k6.chain.out_slot];
+  if (Osrc.ptr != O.ptr || Osrc.stride[0] != hd || Osrc.stride[1] != T * hd || Osrc.stride[2] != 1) return false;
+  if (Y.stride[0] != H * hd || Y.stride[1] != hd || Y.stride[2] != 1) return false;
+  if (!aligned16(Q.ptr) || !aligned16(Ksrc.ptr) || !aligned16(V.ptr) || !aligned16(Y.ptr)) return false;
+
+  // --- the four intermediates must be dead after k6: nobody may read them before they are rewritten ---
+  Range dead[4] = {out_range(k2, k2.chain.out_slot), operand_range(k3, k3.chain.out_slot), out_range(k4, k4.out_slot),
+                   operand_range(k5, k5.chain.out_slot)};
+  const Range y_range = out_range(k6, k6.chain.out_slot);
+  // A later read that touches one of them is only acceptable if everything it reads was rewritten
+  // after the chain (by the chain's own output Y, whose memory the planner may have taken from
+  // them, or by a later kernel).
+  {
+    std::vector<Range> rewritten{y_range};
+    for (size_t j = i + 5; j < plan.kernels.size(); ++j) {
+      std::vector<int> reads, writes;
+      io_slots(plan.kernels[j], &reads, &writes);
+      for (int slot : reads) {
+        const Range r = operand_range(plan.kernels[j], slot);
+        bool touches = false;
+        for (int b = 0; b < 4; ++b) touches = touches || overlaps(r, dead[b]);
+        if (!touches) continue;
+        bool fresh = false;
+        for (const Range& w : rewritten) fresh = fresh || covers(w, r);
+        if (!fresh) return false;
+      }
+      for (int slot : writes) rewritten.push_back(operand_range(plan.kernels[j], slot));
+    }
+  }
+  // the fused kernel writes Y while other CTAs still read Q, K, V: if the planner reused their
+  // memory for Y, the result is staged in a private buffer and copied afterwards
+  const bool aliased = overlaps(y_range, operand_range(k3, k3.desc.a_slot)) || overlaps(y_range, operand_range(k5, k5.desc.b_slot)) ||
+                       overlaps(y_range, operand_range(k2, k2.chain.first_slot));
+
+  // --- the mask must be the causal one: 0 on and below the diagonal, -inf above ---
+  {
+    std::vector<float> host((size_t)T * T);
+    if (cudaMemcpy(host.data(), mask.ptr, host.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    for (int64_t r = 0; r < T; ++r)
+      for (int64_t c = 0; c < T; ++c) {
+        const float v = host[(size_t)r * T + c];
+        if (c <= r ? v != 0.0f : !(v < 0.0f && isinf(v))) return false;
+      }
+  }
+
+  AttnState* st = new AttnState();
+  if (!encode_map(&st->map_q, false, Q.ptr, hd, T, H, rs, hd, 32, kRows, false) ||
+      !encode_map(&st->map_k, false, Ksrc.ptr, hd, T, H, rs, hd, 32, kRows, false) ||
+      !encode_map(&st->map_v, false, V.ptr, hd, T, H, rs, hd, 32, kRows, true)) {
+    delete st;
+    return false;
+  }
+  if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) {
+    cudaGetLastError();
+    delete st;
+    return false;
+  }
+  AttnParams& p = st->params;
+  p.T = (int)T;
+  p.H = (int)H;
+  p.q_tiles = (int)(T / kRows);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.out = Y.ptr;
+  p.out_row_stride = Y.stride[0];
+  if (aliased) {
+    st->out_elems = T * H * hd;
+    if (cudaMalloc(&st->staged_out, (size_t)st->out_elems * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      delete st;
+      return false;
+    }
+    st->final_out = Y.ptr;
+    p.out = st->staged_out;
+    p.out_row_stride = H * hd;
+  }
+  // D = F32, A/B = TF32, both K-major, N = 128 | B N-major, N = 64; M = 128
+  p.idesc_qk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kRows >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+  p.idesc_pv = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+  p.kernel_index = (int)i;
+  p.status = plan.d_status;
+  st->grid = dim3((unsigned)(H * p.q_tiles), 1, 1);
+
+  destroy_matmul(k3);
+  destroy_matmul(k5);
+  k2.attn = st;
+  k2.impl = IMPL_ATTN_FUSED;
+  k2.launches = aliased ? 2 : 1;
+  for (PlanKernel* k : {&k3, &k4, &k5, &k6}) {
+    k->impl = IMPL_FUSED_AWAY;
+    k->launches = 0;
+  }
+  return true;
+}
+
+int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
+  (void)plan;
+  const AttnState* st = static_cast<const AttnState*>(k.attn);
+  attention_kernel<<<st->grid, kAttnThreads, kAttnSmem, s>>>(st->map_q, st->map_k, st->map_v, st->params);
+  if (st->staged_out) {
+    const int64_t n4 = st->out_elems / 4;
+    const int64_t blocks = (n4 + 255) / 256;
+    copy_rows_kernel<<<(unsigned)(blocks < 1184 ? blocks : 1184), 256, 0, s>>>(reinterpret_cast<const float4*>(st->staged_out),
+                                                                              reinterpret_cast<float4*>(st->final_out), n4);
+  }
+  KB200_CUDA(cudaGetLastError());
+  return KB200_OK;
+}
+
+void attention_destroy(PlanKernel& k) {
+  if (k.attn) {
+    AttnState* st = static_cast<AttnState*>(k.attn);
+    if (st->staged_out) cudaFree(st->staged_out);
+    delete st;
+  }
+  k.attn = nullptr;
+}
+
+}  // namespace kb200

@@ -63,6 +63,8 @@ enum Impl : int {
   IMPL_MM_SIMT,
   IMPL_MM_GEMV,
   IMPL_MM_TC,
+  IMPL_ATTN_FUSED,   // this kernel (the K^T copy) runs the fused attention for itself and the next four
+  IMPL_FUSED_AWAY,   // covered by a fused kernel launched earlier: nothing to launch
   IMPL_COUNT
 };
 const char* impl_name(int impl);
@@ -81,6 +83,7 @@ struct PlanKernel {
   // matmul
   int64_t batch = 1, M = 0, N = 0, K = 0;
   void* tc = nullptr;   // tensor-core state (tensor maps, packed operands), owned by matmul_tc.cu
+  void* attn = nullptr; // fused-attention state, owned by attention.cu
 };
 
 struct Plan {
@@ -89,6 +92,7 @@ struct Plan {
   bool bound = false;
   std::vector<PlanKernel> kernels;
   int* d_status = nullptr;       // device status word for bounded waits
+  bool fuse_attention = true;    // replace the five-kernel attention chain by the fused kernel when it matches
   // bound buffers (for re-validation and the tensor-core path)
   float* arena = nullptr;
   uint64_t arena_bytes = 0;
@@ -112,6 +116,9 @@ int choose_matmul(Plan& plan, PlanKernel& k);
 int bind_matmul(Plan& plan, PlanKernel& k);      // after pointers are resolved
 int launch_matmul(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void destroy_matmul(PlanKernel& k);
+bool attention_try_fuse(Plan& plan, size_t first);   // kernels first .. first+4
+int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s);
+void attention_destroy(PlanKernel& k);
 
 inline int64_t numel_of(const kb200_kernel_desc& d) {
   int64_t n = 1;

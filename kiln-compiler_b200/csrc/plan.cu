@@ -30,7 +30,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 const char* impl_name(int impl) {
   static const char* names[IMPL_COUNT] = {
       "ew_generic", "ew_chain_vec4", "ew_transpose", "row_generic", "row_layernorm", "row_softmax",
-      "reduce_generic", "mm_simt_fp32", "mm_gemv", "mm_tcgen05"};
+      "reduce_generic", "mm_simt_fp32", "mm_gemv", "mm_tcgen05", "attention_fused", "fused_away"};
   return impl >= 0 && impl < IMPL_COUNT ? names[impl] : "?";
 }
 
@@ -348,7 +348,8 @@ static int resolve(Plan& plan, PlanKernel& k, int index) {
 }
 
 static int launch_one(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
-  if (numel_of(k.desc) == 0) return KB200_OK;
+  if (numel_of(k.desc) == 0 || k.impl == IMPL_FUSED_AWAY) return KB200_OK;
+  if (k.impl == IMPL_ATTN_FUSED) return attention_launch(plan, k, s);
   switch (k.desc.kclass) {
     case KB200_K_ELEMENTWISE: return launch_elementwise(plan, k, s);
     case KB200_K_ROW: return launch_row(plan, k, s);
@@ -439,6 +440,7 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
   int rc = KB200_OK;
   for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i) {
     PlanKernel& k = plan.kernels[i];
+    attention_destroy(k);
     rc = resolve(plan, k, (int)i);
     if (rc) break;
     switch (k.desc.kclass) {
@@ -451,10 +453,22 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
         break;
     }
   }
+  if (rc == KB200_OK && plan.fuse_attention)
+    for (size_t i = 0; i + 4 < plan.kernels.size(); ++i)
+      if (attention_try_fuse(plan, i)) i += 4;
   cudaSetDevice(prev);
   if (rc) return rc;
   plan.bound = true;
   return KB200_OK;
+}
+
+KB200_EXPORT int kb200_plan_set_option(kb200_plan* p, int option, int value) {
+  if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: plan is null");
+  Plan& plan = *reinterpret_cast<Plan*>(p);
+  switch (option) {
+    case KB200_OPT_FUSE_ATTENTION: plan.fuse_attention = value != 0; return KB200_OK;
+    default: return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: unknown option %d", option);
+  }
 }
 
 KB200_EXPORT int kb200_plan_launch(kb200_plan* p, void* stream) {
@@ -511,7 +525,10 @@ KB200_EXPORT void kb200_plan_destroy(kb200_plan* p) {
   int prev = 0;
   cudaGetDevice(&prev);
   cudaSetDevice(plan->device);
-  for (PlanKernel& k : plan->kernels) destroy_matmul(k);
+  for (PlanKernel& k : plan->kernels) {
+    destroy_matmul(k);
+    attention_destroy(k);
+  }
   if (plan->d_status) cudaFree(plan->d_status);
   cudaSetDevice(prev);
   delete plan;

@@ -22,6 +22,7 @@ INCLUDE_DIR = PKG_DIR.parent.parent / "include"
 LIB_PATH = PKG_DIR / "_lib" / "libkb200.so"
 
 K_ELEMENTWISE, K_ROW, K_REDUCE, K_MATMUL = 0, 1, 2, 3
+OPT_FUSE_ATTENTION = 1
 BASE_KINDS = {"arena": 0, "const": 1, "input": 2, "output": 3}
 PRECISIONS = {"fp32": 0, "tf32": 1, "bf16": 2}
 OPCODES = {
@@ -59,6 +60,7 @@ EXPORTS = {
                                   C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_int,
                                   C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_int,
                                   C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_int]),
+    "kb200_plan_set_option": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "kb200_plan_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "kb200_kernel_launch": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "kb200_plan_launch_count": (C.c_int, [C.c_void_p]),

@@ -144,6 +144,10 @@ class GPUExecutable:
         self._descs = descs
         _cabi.check(self._lib.kb200_plan_create(descs, len(program.launches), self.device.index,
                                                 C.byref(self._plan)), self._lib)
+        # One launch per planned kernel (KILN_GPU_FUSE_ATTENTION=0), or let the library run the
+        # attention chain as one fused kernel in the reduced-precision modes (default).
+        fuse = os.environ.get("KILN_GPU_FUSE_ATTENTION", "1") not in ("0", "false", "False", "")
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_FUSE_ATTENTION, int(fuse)), self._lib)
         self._bind()
         self.kernel_names = [l.name for l in program.launches]
         self.impls = [self._lib.kb200_kernel_impl(self._plan, i).decode() for i in range(len(program.launches))]

@@ -59,10 +59,13 @@ def test_reduced_precision_matmuls(case, precision):
 
 
 @pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
-def test_every_kernel_of_the_block_matches_the_oracle_step_by_step(precision):
-    """Launch the block's 11 kernels one at a time and compare each kernel's output buffer."""
+def test_every_kernel_of_the_block_matches_the_oracle_step_by_step(precision, monkeypatch):
+    """Launch the block's 11 kernels one at a time and compare each kernel's output buffer
+    (one launch per planned kernel: the attention chain is not fused here)."""
     from gpu_helpers import build_executable
     from helpers import case_data, load_plan
+
+    monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")
 
     case = "gpt2_block_t128"
     plan = load_plan(case)
@@ -85,6 +88,32 @@ def test_every_kernel_of_the_block_matches_the_oracle_step_by_step(precision):
     limit = REL_TOL[precision] * (1 if precision == "fp32" else 2)
     bad = {k: v for k, v in errors.items() if not v <= limit}
     assert not bad, (bad, errors)
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("tokens", [128, 512, 1024])
+def test_fused_attention_equals_the_five_planned_kernels(tokens, precision, monkeypatch):
+    """The fused attention kernel against the unfused plan on the same inputs, and both against float64."""
+    from gpu_helpers import run_case
+
+    case = f"gpt2_block_t{tokens}"
+    fused_exe, fused, (plan, inputs, consts, _) = run_case(case, precision)
+    assert "attention_fused" in fused_exe.impls and fused_exe.impls.count("fused_away") == 4
+    monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")
+    plain_exe, plain, _ = run_case(case, precision)
+    assert "attention_fused" not in plain_exe.impls
+    assert fused_exe.device_launches < plain_exe.device_launches
+    (exact,) = run_plan(plan, inputs, consts, dtype=np.float64)
+    assert scale_relative_error(fused[0], exact) <= REL_TOL[precision]
+    assert scale_relative_error(plain[0], exact) <= REL_TOL[precision]
+    assert scale_relative_error(fused[0], plain[0]) <= REL_TOL[precision]
+
+
+def test_fp32_never_fuses_attention():
+    from gpu_helpers import build_executable
+
+    exe = build_executable("gpt2_block_t128", "fp32")
+    assert "attention_fused" not in exe.impls and exe.device_launches == 11
 
 
 def test_replay_with_new_inputs():
