@@ -23,6 +23,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdio>
 #include <mutex>
 
 #include "device_math.cuh"
@@ -153,6 +154,12 @@ __device__ __forceinline__ void epilogue_block32(const TcParams& p, float (&x)[3
   }
 }
 
+#ifdef KB200_TRACE
+#define KB200_STAMP(role, idx) do { if (blockIdx.x == 0 && (idx) < 160) trace[role][idx] = clock64(); } while (0)
+#else
+#define KB200_STAMP(role, idx) do { } while (0)
+#endif
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -161,6 +168,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+#ifdef KB200_TRACE
+  __shared__ long long trace[6][160];
+  int tp = 0, tm = 0, te = 0;
+#endif
 
   // 1024-byte aligned tile area (the 128-byte swizzle pattern repeats every 1024 bytes)
   const uint32_t raw = smem_u32(smem_raw);
@@ -218,6 +229,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             ok = false;
             break;
           }
+          KB200_STAMP(0, tp);
           const uint32_t full = full0 + 8 * s;
           if (p.debug & 4) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full) : "memory"); continue; }
           mbar_expect_tx(full, (uint32_t)stage_bytes);
@@ -229,6 +241,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             for (int c = 0; c < n_chunks; ++c)
               tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, n0 + c * p.chunk_n, kb * p.slab_k, batch);
           }
+          KB200_STAMP(1, tp);
+#ifdef KB200_TRACE
+          ++tp;
+#endif
         }
       }
     }
@@ -260,6 +276,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             ok = false;
             break;
           }
+          KB200_STAMP(2, tm);
           const uint32_t a_addr = tiles + s * stage_bytes;
           const uint32_t b_addr = a_addr + kATileBytes;
 #pragma unroll
@@ -272,6 +289,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           }
           if (p.debug & 8) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
           else umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+          KB200_STAMP(3, tm);
+#ifdef KB200_TRACE
+          ++tm;
+#endif
         }
         if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA of this tile has completed
       }
@@ -296,6 +317,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
       ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
       if (!ok) break;
+#ifdef KB200_TRACE
+      if (warp == 2 && lane == 0) KB200_STAMP(4, te);
+#endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // this warp's share of the tile: rows quad*32..+31, column chunks half*32, +64, ...
       float* part = p.splits > 1 ? p.partials + ((size_t)unit * kTileM + quad * 32) * p.bn : nullptr;
@@ -321,6 +345,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * acc) : "memory");
+#ifdef KB200_TRACE
+      if (warp == 2 && lane == 0) { KB200_STAMP(5, te); ++te; }
+#endif
       if (p.splits > 1) {
         // Split-K: the same warp slot of the other units of this tile owns the same sub-block.  The
         // last of them to arrive sums the partial sub-blocks in unit order (so the result does not
@@ -354,6 +381,15 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   // ---------------- common exit ----------------
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+#ifdef KB200_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const long long t0 = trace[0][0];
+    for (int i = 0; i < 160 && i < p.num_kb * 3; ++i)
+      printf("slab %3d  prod_wait_done %7lld issued %7lld | mma_full %7lld committed %7lld\n", i, trace[0][i] - t0,
+             trace[1][i] - t0, trace[2][i] - t0, trace[3][i] - t0);
+    for (int i = 0; i < 3; ++i) printf("tile %d epilogue start %7lld end %7lld\n", i, trace[4][i] - t0, trace[5][i] - t0);
+  }
+#endif
   if (abort_flag && threadIdx.x == 0) {
     // give copies that may still be in flight a bounded time to land before shared memory is released
     for (int s = 0; s < p.stages; ++s)

@@ -9,8 +9,8 @@ $KILN_CACHE_DIR/b200_autotune.json (written to a temporary file and renamed; a c
 ignored).
 
 What is searched is this backend's own space, not Triton's: the tcgen05 tile width (BN, with
-BM fixed at the 128 rows one CTA's accumulator spans), the K depth of a pipeline stage, the
-number of stages, and the split-K factor; plus the exact-FP32 SIMT kernel as a candidate.
+BM fixed at the 128 rows one CTA's accumulator spans), the number of pipeline stages and the
+split-K factor; plus the exact-FP32 SIMT kernel as a candidate.
 """
 
 from __future__ import annotations
@@ -32,11 +32,11 @@ MIN_GAIN = 1.03
 FINALISTS = 3
 SHARED_MEMORY_BYTES = 227 * 1024     # per CTA on B200
 
-TC_CANDIDATES = [  # BN, BK (floats per stage row), stages, split_k
-    (256, 32, 4, 1), (256, 32, 3, 1), (128, 32, 4, 1), (128, 32, 6, 1), (128, 64, 3, 1), (64, 32, 6, 1),
-    (64, 64, 4, 1), (128, 32, 4, 2), (128, 32, 4, 4), (64, 32, 6, 2), (64, 32, 6, 4), (64, 32, 6, 8),
-    (32, 32, 8, 1), (32, 32, 8, 4),
+TC_CANDIDATES = [  # BN, stages, split_k
+    (256, 4, 1), (256, 3, 1), (128, 4, 1), (128, 6, 1), (64, 6, 1), (128, 4, 2), (128, 4, 4), (64, 6, 2), (64, 6, 4),
+    (64, 6, 8), (256, 3, 2),
 ]
+EPILOGUE_BYTES = 8 * 32 * 33 * 4     # the epilogue warps' transpose buffers
 
 
 def cache_path() -> Path:
@@ -49,22 +49,22 @@ def device_name():
 
 
 def stage_bytes(cfg):
-    """Shared memory one pipeline stage of a candidate holds (A tile + B tile, 4-byte elements)."""
-    return (cfg["BM"] + cfg["BN"]) * cfg["BK"] * 4
+    """Shared memory one pipeline stage holds: a 128-row A slab and a BN-row B slab of 128 bytes per row."""
+    return (cfg["BM"] + cfg["BN"]) * 128
 
 
 def candidates(m, n, k):
     out = []
-    for bn, bk, stages, split in TC_CANDIDATES:
-        if bn > max(32, next_pow2(n)) or bk > max(32, next_pow2(k)):
+    for bn, stages, split in TC_CANDIDATES:
+        if bn > max(64, next_pow2(n)):
             continue            # a tile much wider than the problem only adds masked-off work
-        if split > 1 and k // split < 2 * bk:
+        if split > 1 and k // split < 128:
             continue
-        cfg = {"BM": 128, "BN": bn, "BK": bk, "stages": stages, "split_k": split, "impl": "tc"}
-        if stage_bytes(cfg) * stages + 1024 > SHARED_MEMORY_BYTES:
+        cfg = {"BM": 128, "BN": bn, "stages": stages, "split_k": split, "impl": "tc"}
+        if stage_bytes(cfg) * stages + EPILOGUE_BYTES + 1024 > SHARED_MEMORY_BYTES:
             continue
         out.append(cfg)
-    out.append({"BM": 64, "BN": 64, "BK": 16, "stages": 1, "split_k": 1, "impl": "simt"})
+    out.append({"BM": 64, "BN": 64, "stages": 1, "split_k": 1, "impl": "simt"})
     return out
 
 

@@ -157,3 +157,35 @@ def test_hot_path_kernels_are_the_specialised_ones():
     assert by_name["k2_ew0"] == "ew_transpose" and by_name["k6_ew0"] == "ew_chain_vec4"
     assert build_executable("bias_gelu_2048x3072").impls == ["ew_chain_vec4"]
     assert build_executable("linear_1x3072x768").impls == ["mm_gemv"]
+
+
+def test_autotune_candidates_fit_shared_memory():
+    from kiln_b200.autotune import EPILOGUE_BYTES, SHARED_MEMORY_BYTES, candidates, stage_bytes
+
+    for m, n, k in [(128, 3072, 768), (1, 768, 768), (7, 13, 5), (2048, 3072, 768)]:
+        cands = candidates(m, n, k)
+        assert cands and cands[-1]["impl"] == "simt"
+        for c in cands[:-1]:
+            assert stage_bytes(c) * c["stages"] + EPILOGUE_BYTES + 1024 <= SHARED_MEMORY_BYTES
+            assert c["BN"] <= max(64, 2 * n)
+
+
+def test_autotuner_is_correct_then_cached(monkeypatch):
+    """Tuned once, then served from the on-disk cache (tests/test_gpu.py:143-158 of the reference)."""
+    from kiln_b200.autotune import GPUAutotuner
+    from kiln_b200.codegen import default_matmul_config
+
+    default = default_matmul_config(None, None)
+    first = GPUAutotuner(allow_tf32=True)
+    cfg = first.config_for_shape(1, 256, 768, 512, default)
+    (entry,) = first.log
+    assert entry["source"] == "tuned" and entry["candidates"] >= 2 and entry["tflops"] > 0
+    assert entry["shape"] == (1, 256, 768, 512)
+    monkeypatch.setattr(GPUAutotuner, "tune", lambda *a, **k: pytest.fail("cached shape re-tuned"))
+    second = GPUAutotuner(allow_tf32=True)
+    assert second.config_for_shape(1, 256, 768, 512, default) == cfg
+    assert second.log[0]["source"] == "cache"
+    exact = GPUAutotuner(allow_tf32=False, use_cache=False)
+    monkeypatch.undo()
+    exact.config_for_shape(1, 64, 96, 80, default)
+    assert exact.log[0]["config"].get("impl") in ("auto", "simt")
