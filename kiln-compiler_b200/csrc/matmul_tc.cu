@@ -44,7 +44,11 @@ constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;      // producer warp, MMA warp, epilogue warps
 constexpr int kEpiBytes = kEpiWarps * 32 * 33 * 4;  // per-warp 32 x 33 transpose buffers
+#ifdef KB200_TRACE
+constexpr int kMaxDynamicSmem = 200 * 1024;   // the trace arrays take static shared memory
+#else
 constexpr int kMaxDynamicSmem = 225 * 1024;   // opt-in ceiling, the same for every launch of the kernel
+#endif
 
 struct TcParams {
   MatmulParams mm;
