@@ -19,6 +19,7 @@
 //               output O kept in registers, rescaled and accumulated from O_part after each tile.
 // Causal tiles above the diagonal are skipped.  Every mbarrier wait is bounded (see matmul_tc.cu).
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include <vector>
 
@@ -43,6 +44,8 @@ struct AttnParams {
   float scale_log2;          // softmax scale times log2(e): exponentials are taken in base 2
   float* out;                // [T, H * 64] merged heads
   int64_t out_row_stride;
+  __nv_bfloat16* out16;      // optional bf16 copy of the merged heads, row stride H * 64, or null
+  int64_t out16_row_stride;
   uint32_t idesc_qk, idesc_pv;
   int kernel_index;
   int* status;
@@ -54,6 +57,8 @@ struct AttnState {
   dim3 grid;
   // When the planner put the merged-heads buffer over the (by then dead) QKV buffer, the fused
   // kernel cannot write it while other CTAs still read Q, K and V: it writes here, a copy follows.
+  const DevOperand* y = nullptr;   // the head-merge kernel's output operand (the chain's only live result)
+  int64_t y_elems = 0;
   float* staged_out = nullptr;
   float* final_out = nullptr;
   int64_t out_elems = 0;
@@ -246,6 +251,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int i = 0; i < kHeadDim; i += 4)
         *reinterpret_cast<float4*>(dst + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+      if (p.out16 != nullptr) {
+        __nv_bfloat16* dst16 = p.out16 + (int64_t)(q0 + row) * p.out16_row_stride + h * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < kHeadDim; i += 8) {
+          __nv_bfloat162 w0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), w1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+          __nv_bfloat162 w2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), w3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+          uint4 packed;
+          packed.x = *reinterpret_cast<uint32_t*>(&w0);
+          packed.y = *reinterpret_cast<uint32_t*>(&w1);
+          packed.z = *reinterpret_cast<uint32_t*>(&w2);
+          packed.w = *reinterpret_cast<uint32_t*>(&w3);
+          *reinterpret_cast<uint4*>(dst16 + i) = packed;
+        }
+      }
     }
   }
 
@@ -431,6 +450,10 @@ bool attention_try_fuse(Plan& plan, size_t i) {
   p.scale_log2 = scale * 1.4426950408889634f;
   p.out = Y.ptr;
   p.out_row_stride = Y.stride[0];
+  p.out16 = nullptr;
+  p.out16_row_stride = H * hd;
+  st->y = &Y;
+  st->y_elems = T * H * hd;
   if (aliased) {
     st->out_elems = T * H * hd;
     if (cudaMalloc(&st->staged_out, (size_t)st->out_elems * sizeof(float)) != cudaSuccess) {
@@ -473,6 +496,16 @@ int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   }
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
+}
+
+void attention_set_shadow(PlanKernel& k, void* shadow_out) {
+  if (k.attn) static_cast<AttnState*>(k.attn)->params.out16 = static_cast<__nv_bfloat16*>(shadow_out);
+}
+
+const DevOperand* attention_output(const Plan& plan, size_t first, int64_t* elems) {
+  const AttnState* st = static_cast<const AttnState*>(plan.kernels[first].attn);
+  *elems = st->y_elems;
+  return st->y;
 }
 
 void attention_destroy(PlanKernel& k) {

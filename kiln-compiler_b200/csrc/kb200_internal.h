@@ -84,6 +84,11 @@ struct PlanKernel {
   int64_t batch = 1, M = 0, N = 0, K = 0;
   void* tc = nullptr;   // tensor-core state (tensor maps, packed operands), owned by matmul_tc.cu
   void* attn = nullptr; // fused-attention state, owned by attention.cu
+  // BF16 mode: a producer may also write its output, rounded to bf16, into the mirror of the arena
+  // (same element offsets) so that the matmul that consumes it needs no conversion pass.
+  void* shadow_out = nullptr;     // producer side: mirror address of this kernel's (single) output, or null
+  const void* a_shadow = nullptr; // consumer side: mirror address of operand A / B, or null (convert per launch)
+  const void* b_shadow = nullptr;
 };
 
 struct Plan {
@@ -93,6 +98,8 @@ struct Plan {
   std::vector<PlanKernel> kernels;
   int* d_status = nullptr;       // device status word for bounded waits
   bool fuse_attention = true;    // replace the five-kernel attention chain by the fused kernel when it matches
+  void* arena16 = nullptr;       // bf16 mirror of the arena (library-owned, only when some matmul reads it)
+  uint64_t arena16_bytes = 0;
   // bound buffers (for re-validation and the tensor-core path)
   float* arena = nullptr;
   uint64_t arena_bytes = 0;
@@ -114,6 +121,9 @@ int choose_reduce(Plan& plan, PlanKernel& k);
 int launch_reduce(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 int choose_matmul(Plan& plan, PlanKernel& k);
 int bind_matmul(Plan& plan, PlanKernel& k);      // after pointers are resolved
+bool matmul_wants_bf16_operands(const PlanKernel& k);
+void attention_set_shadow(PlanKernel& k, void* shadow_out);
+const DevOperand* attention_output(const Plan& plan, size_t first, int64_t* elems);
 int launch_matmul(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void destroy_matmul(PlanKernel& k);
 bool attention_try_fuse(Plan& plan, size_t first);   // kernels first .. first+4

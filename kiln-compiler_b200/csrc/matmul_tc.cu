@@ -67,6 +67,8 @@ struct TcParams {
   int kernel_index;
   int* status;
   int tiles_m, tiles_n, num_tiles;   // tiles per batch entry along M and N; total over the batch
+  int pre_col_step, pre_mat_step;    // chain steps whose operand the epilogue fetches ahead (-1 = none)
+  __nv_bfloat16* out16;              // optional bf16 copy of the output (same strides as the output), or null
   int splits;           // split-K factor: a tile's K range is shared by this many work units
   int num_units;        // num_tiles * splits
   float* partials;      // splits > 1: [unit][128][bn] float32 partial tiles
@@ -119,42 +121,81 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
 #undef KB200_EACH
 }
 
-// The fused chain on a 32 x 32 block of the tile, after the block went through shared memory so
+// The epilogue works on 32 x 32 blocks of the tile after a transpose through shared memory, so
 // that a lane owns one COLUMN (x[r] = row r): every global load / store of a warp then covers 128
-// contiguous bytes of one row, and the 32 rows give 32 independent loads in flight per lane.
-__device__ __forceinline__ void epilogue_block32(const TcParams& p, float (&x)[32], int64_t b, int64_t m_first, int64_t n) {
+// contiguous bytes of one row, and the 32 rows give 32 independent accesses in flight per lane.
+
+// Side operand of chain step `s` for the block (zeros outside the matrix).
+__device__ __forceinline__ void load_side32(const TcParams& p, int s, float (&side)[32], int64_t b, int64_t m_first, int64_t n) {
   const MatmulParams& mm = p.mm;
+  const DevOperand& o = mm.ops[mm.chain.steps[s].slot];
   const bool col_ok = n < mm.N;
   const int64_t rows_left = mm.M - m_first;   // may be <= 0 for a tile hanging over the bottom edge
+  const float* base = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
+  if (o.stride[1] == 0) {                      // one value per column (bias): a single load
+    const float t = (col_ok && rows_left > 0) ? __ldg(base) : 0.0f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) side[r] = t;
+  } else {
+    const int64_t sm = o.stride[1];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) side[r] = (col_ok && r < rows_left) ? __ldg(base + r * sm) : 0.0f;
+  }
+}
+
+// Two operands of the chain are fetched ahead of the accumulator (their L2 latency then overlaps
+// the main loop, the TMEM load and the previous block's stores): the first per-column operand
+// (a bias: one value per lane) and the first full-matrix operand (a residual or a mask).
+__device__ __forceinline__ void prefetch_sides(const TcParams& p, float& pre_col, float (&pre_mat)[32], int64_t b,
+                                               int64_t m_first, int64_t n) {
+  const MatmulParams& mm = p.mm;
+  if (p.pre_col_step >= 0) {
+    const DevOperand& o = mm.ops[mm.chain.steps[p.pre_col_step].slot];
+    pre_col = (n < mm.N) ? __ldg(o.ptr + b * o.stride[0] + n * o.stride[2]) : 0.0f;
+  }
+  if (p.pre_mat_step >= 0) load_side32(p, p.pre_mat_step, pre_mat, b, m_first, n);
+}
+
+__device__ __forceinline__ void epilogue_compute32(const TcParams& p, float (&x)[32], float pre_col, const float (&pre_mat)[32],
+                                                   int64_t b, int64_t m_first, int64_t n) {
+  const MatmulParams& mm = p.mm;
   for (int s = 0; s < mm.chain.n; ++s) {
     const ChainStep st = mm.chain.steps[s];
-    float side[32];
-    if (st.slot >= 0) {
-      const DevOperand& o = mm.ops[st.slot];
-      const float* base = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
-      if (o.stride[1] == 0) {                  // one value per column (bias): a single load
-        const float t = (col_ok && rows_left > 0) ? __ldg(base) : 0.0f;
-#pragma unroll
-        for (int r = 0; r < 32; ++r) side[r] = t;
-      } else {
-        const int64_t sm = o.stride[1];
-#pragma unroll
-        for (int r = 0; r < 32; ++r) side[r] = (col_ok && r < rows_left) ? __ldg(base + r * sm) : 0.0f;
-      }
+    if (s == p.pre_mat_step) {
+      chain_step32(st.op, x, pre_mat);
     } else {
+      float side[32];
+      if (s == p.pre_col_step) {
 #pragma unroll
-      for (int r = 0; r < 32; ++r) side[r] = st.imm;
+        for (int r = 0; r < 32; ++r) side[r] = pre_col;
+      } else if (st.slot >= 0) {
+        load_side32(p, s, side, b, m_first, n);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) side[r] = st.imm;
+      }
+      chain_step32(st.op, x, side);
     }
-    chain_step32(st.op, x, side);
   }
+}
+
+__device__ __forceinline__ void epilogue_store32(const TcParams& p, const float (&x)[32], int64_t b, int64_t m_first, int64_t n) {
   if (p.debug & 1) return;
+  const MatmulParams& mm = p.mm;
   const DevOperand& o = mm.ops[mm.chain.out_slot];
   float* out = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
   const int64_t sm = o.stride[1];
-  if (col_ok) {
+  const int64_t rows_left = mm.M - m_first;
+  if (n < mm.N) {
 #pragma unroll
     for (int r = 0; r < 32; ++r)
       if (r < rows_left) out[r * sm] = x[r];
+    if (p.out16 != nullptr) {
+      __nv_bfloat16* out16 = p.out16 + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
+#pragma unroll
+      for (int r = 0; r < 32; ++r)
+        if (r < rows_left) out16[r * sm] = __float2bfloat16_rn(x[r]);
+    }
   }
 }
 
@@ -317,6 +358,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const uint32_t aph = (i >> 1) & 1;
       const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
       const int64_t m0 = (int64_t)(rem / p.tiles_n) * kTileM, n0 = (int64_t)(rem % p.tiles_n) * p.bn;
+      const int64_t m_first = m0 + quad * 32;
+      const bool direct = p.splits == 1;
+      float pre_col = 0.0f, pre_mat[32];
+      if (direct && n0 + half * 32 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + half * 32 + lane);
       bool got = mbar_wait(tfull0 + 8 * acc, aph, abort_ptr);
       if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
       ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
@@ -338,8 +383,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
         for (int r = 0; r < 32; ++r) v[r] = tbuf[r * 33 + lane];
         __syncwarp();
-        if (p.splits == 1) {
-          epilogue_block32(p, v, batch, m0 + quad * 32, n0 + c + lane);
+        if (direct) {
+          epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + c + lane);
+          if (c + 64 < p.bn && n0 + c + 64 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + c + 64 + lane);
+          epilogue_store32(p, v, batch, m_first, n0 + c + lane);
         } else {
 #pragma unroll
           for (int r = 0; r < 32; ++r) __stcg(part + r * p.bn + c + lane, v[r]);
@@ -373,7 +420,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
               for (int r = 0; r < 32; ++r) v[r] += __ldcg(src + r * p.bn);
             }
-            epilogue_block32(p, v, batch, m0 + quad * 32, n0 + c + lane);
+            prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + c + lane);
+            epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + c + lane);
+            epilogue_store32(p, v, batch, m_first, n0 + c + lane);
           }
           if (lane == 0) p.counters[(size_t)tile * kEpiWarps + e] = 0u;
         }
@@ -434,12 +483,16 @@ struct TcState {
   __nv_bfloat16* a16 = nullptr;
   __nv_bfloat16* b16 = nullptr;
   bool b_const = false;       // B is a frozen constant: converted once at bind
+  bool a_shadow = false;      // A / B is read from the bf16 mirror its producer writes: no conversion launch
+  bool b_shadow = false;
   // split-K workspace
   float* partials = nullptr;
   unsigned* counters = nullptr;
 };
 
 }  // namespace
+
+bool matmul_wants_bf16_operands(const PlanKernel& k) { return k.desc.precision == KB200_PREC_BF16; }
 
 // Can the tensor-core kernel take this matmul as it stands?
 bool tc_eligible(const PlanKernel& k) {
@@ -483,7 +536,7 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   if (bn < 64) bn = 64;
   while (bn > 64 && bn / 2 >= k.N) bn /= 2;               // do not make the tile wider than the problem
   (void)chunk_n;
-  int stages = d.cfg[3] > 0 ? d.cfg[3] : 4;
+  int stages = d.cfg[3] > 0 ? d.cfg[3] : kMaxStages;   // as deep as shared memory allows: the ring hides ~2000 cycles of TMA latency
   if (stages > kMaxStages) stages = kMaxStages;
   const int stage_bytes = kATileBytes + bn * kSlabBytes;
   while (stages > 2 && (size_t)stages * stage_bytes + kEpiBytes + 1024 > (size_t)kMaxDynamicSmem) --stages;
@@ -539,6 +592,15 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
             ((uint32_t)(kTileM >> 4) << 24);
   p.kernel_index = kernel_index;
   p.status = plan.d_status;
+  p.out16 = static_cast<__nv_bfloat16*>(k.shadow_out);
+  p.pre_col_step = p.pre_mat_step = -1;
+  for (int st_i = 0; st_i < k.chain.n; ++st_i) {
+    const int slot = k.chain.steps[st_i].slot;
+    if (slot < 0) continue;
+    const bool per_column = k.ops[slot].stride[1] == 0;
+    if (per_column && p.pre_col_step < 0) p.pre_col_step = st_i;
+    else if (!per_column && p.pre_mat_step < 0) p.pre_mat_step = st_i;
+  }
   st->smem_bytes = (size_t)stages * stage_bytes + kEpiBytes + 1024;
   // persistent CTAs, one per SM: each walks the tile list with a stride of the grid size
   st->grid = dim3((unsigned)(p.num_units < plan.sm_count ? p.num_units : plan.sm_count), 1, 1);
@@ -556,8 +618,10 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     if (st->a16) cudaFree(st->a16);
     if (st->b16) cudaFree(st->b16);
     st->a16 = st->b16 = nullptr;
-    KB200_CUDA(cudaMalloc(&st->a16, (size_t)k.batch * k.M * k.K * 2));
-    KB200_CUDA(cudaMalloc(&st->b16, (size_t)k.batch * k.K * k.N * 2));
+    st->a_shadow = k.a_shadow != nullptr;
+    st->b_shadow = k.b_shadow != nullptr;
+    if (!st->a_shadow) KB200_CUDA(cudaMalloc(&st->a16, (size_t)k.batch * k.M * k.K * 2));
+    if (!st->b_shadow) KB200_CUDA(cudaMalloc(&st->b16, (size_t)k.batch * k.K * k.N * 2));
     st->b_const = d.operands[d.b_slot].base_kind == KB200_BASE_CONST;
     if (st->b_const) {
       const int64_t total = k.batch * b_rows * (b_cols / 4);
@@ -566,11 +630,19 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
       KB200_CUDA(cudaGetLastError());
       KB200_CUDA(cudaDeviceSynchronize());
     }
-    k.launches = st->b_const ? 2 : 3;
-    a_base = st->a16;
-    b_base = st->b16;
-    a_row = k.K; a_batch = k.M * k.K;
-    b_row = b_cols; b_batch = k.K * k.N;
+    k.launches = 1 + (st->a_shadow ? 0 : 1) + ((st->b_const || st->b_shadow) ? 0 : 1);
+    if (st->a_shadow) {
+      a_base = k.a_shadow;              // the mirror has the operand's own strides
+    } else {
+      a_base = st->a16;
+      a_row = k.K; a_batch = k.M * k.K;
+    }
+    if (st->b_shadow) {
+      b_base = k.b_shadow;
+    } else {
+      b_base = st->b16;
+      b_row = b_cols; b_batch = k.K * k.N;
+    }
   }
   if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
       !encode_map(&st->map_b, st->bf16, b_base, b_cols, b_rows, k.batch, b_row, b_batch, p.b_kmajor ? slab_k : chunk_n,
@@ -592,9 +664,10 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     const DevOperand& B = k.ops[d.b_slot];
     const int64_t cap = (int64_t)plan.sm_count * 8;
     int64_t total = k.batch * k.M * (k.K / 4);
-    cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
-        A.ptr, st->a16, k.batch, k.M, k.K, A.stride[0], A.stride[1]);
-    if (!st->b_const) {
+    if (!st->a_shadow)
+      cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
+          A.ptr, st->a16, k.batch, k.M, k.K, A.stride[0], A.stride[1]);
+    if (!st->b_const && !st->b_shadow) {
       const bool km = st->params.b_kmajor != 0;
       const int64_t rows = km ? k.N : k.K, cols = km ? k.K : k.N;
       total = k.batch * rows * (cols / 4);
@@ -723,6 +796,8 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.splits = 1;
   p.num_units = p.num_tiles;
+  p.pre_col_step = p.pre_mat_step = -1;
+  p.out16 = nullptr;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
   p.kernel_index = 0;
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);

@@ -347,6 +347,109 @@ static int resolve(Plan& plan, PlanKernel& k, int index) {
   return KB200_OK;
 }
 
+namespace {
+struct Span {
+  const float* lo;
+  const float* hi;
+};
+Span span_of(const PlanKernel& k, int slot) {
+  const kb200_kernel_desc& d = k.desc;
+  int64_t ext[KB200_MAX_RANK];
+  for (int i = 0; i < d.iter_rank; ++i) ext[i] = d.iter_shape[i];
+  if (d.kclass == KB200_K_MATMUL) {
+    if (slot == d.a_slot) ext[2] = d.k_extent;
+    if (slot == d.b_slot) { ext[1] = d.k_extent; ext[2] = d.iter_shape[2]; }
+  }
+  int64_t last = 0;
+  for (int i = 0; i < d.iter_rank; ++i) last += (ext[i] - 1) * k.ops[slot].stride[i];
+  return {k.ops[slot].ptr, k.ops[slot].ptr + last + 1};
+}
+}  // namespace
+
+// For every BF16 tensor-core matmul operand that lives in the arena: if the last kernel that wrote
+// that memory covers it completely and can also emit bf16, let it write the bf16 mirror and let the
+// matmul read the mirror.  Anything else keeps the per-launch conversion pass.
+static int assign_shadows(Plan& plan) {
+  const float* arena_lo = plan.arena;
+  const float* arena_hi = plan.arena + plan.arena_bytes / 4;
+  bool any = false;
+  for (size_t ki = 0; ki < plan.kernels.size(); ++ki) {
+    PlanKernel& k = plan.kernels[ki];
+    if (k.impl != IMPL_MM_TC || !matmul_wants_bf16_operands(k)) continue;
+    for (int role = 0; role < 2; ++role) {
+      const int slot = role == 0 ? k.desc.a_slot : k.desc.b_slot;
+      if (k.desc.operands[slot].base_kind != KB200_BASE_ARENA) continue;
+      const Span x = span_of(k, slot);
+      if (x.lo < arena_lo || x.hi > arena_hi) continue;
+      // the mirror is read through TMA: 16-byte aligned base and strides in 2-byte elements
+      const DevOperand& xo = k.ops[slot];
+      if ((x.lo - arena_lo) % 8 || xo.stride[0] % 8 || xo.stride[1] % 8 || xo.stride[2] % 8 && xo.stride[2] != 1) continue;
+      // the latest earlier kernel whose output overlaps the operand
+      for (size_t j = ki; j-- > 0;) {
+        PlanKernel& pj = plan.kernels[j];
+        if (pj.impl == IMPL_FUSED_AWAY) continue;
+        const DevOperand* out = nullptr;
+        int64_t out_elems = 0;
+        bool contiguous = false;
+        if (pj.impl == IMPL_ATTN_FUSED) {
+          out = attention_output(plan, j, &out_elems);
+          contiguous = true;
+        } else if (pj.impl == IMPL_ROW_LAYERNORM) {
+          out = &pj.ops[pj.out_slot];
+          out_elems = (pj.desc.iter_shape[0] - 1) * out->stride[0] + pj.desc.iter_shape[1];
+        } else if (pj.impl == IMPL_MM_TC && pj.has_chain) {
+          out = &pj.ops[pj.chain.out_slot];
+          out_elems = (pj.batch - 1) * out->stride[0] + (pj.M - 1) * out->stride[1] + (pj.N - 1) * out->stride[2] + 1;
+        } else {
+          // some other kernel: does it write into the operand at all?
+          bool writes = false;
+          for (int t = 0; t < pj.desc.n_tape; ++t)
+            if (pj.desc.tape[t].opcode == KB200_OP_STORE) {
+              const Span w = span_of(pj, pj.desc.tape[t].b);
+              writes = writes || (w.lo < x.hi && x.lo < w.hi);
+            }
+          if (writes) break;      // written by a kernel that cannot emit bf16: keep the conversion pass
+          continue;
+        }
+        (void)contiguous;
+        const Span w{out->ptr, out->ptr + out_elems};
+        if (!(w.lo < x.hi && x.lo < w.hi)) continue;                 // does not touch the operand
+        if (w.lo <= x.lo && w.hi >= x.hi && w.lo >= arena_lo && w.hi <= arena_hi) {
+          pj.shadow_out = reinterpret_cast<void*>(1);                // marked; the address is filled in below
+          (role == 0 ? k.a_shadow : k.b_shadow) = reinterpret_cast<const void*>(1);
+          any = true;
+        }
+        break;
+      }
+    }
+  }
+  if (!any) return KB200_OK;
+  const uint64_t need = plan.arena_bytes / 2 + 256;
+  if (plan.arena16 == nullptr || plan.arena16_bytes < need) {
+    if (plan.arena16) cudaFree(plan.arena16);
+    plan.arena16 = nullptr;
+    KB200_CUDA(cudaMalloc(&plan.arena16, need));
+    plan.arena16_bytes = need;
+  }
+  uint16_t* mirror = static_cast<uint16_t*>(plan.arena16);
+  auto mirror_of = [&](const float* ptr) { return static_cast<void*>(mirror + (ptr - plan.arena)); };
+  for (size_t ki = 0; ki < plan.kernels.size(); ++ki) {
+    PlanKernel& k = plan.kernels[ki];
+    if (k.shadow_out) {
+      const DevOperand* out;
+      int64_t elems;
+      if (k.impl == IMPL_ATTN_FUSED) out = attention_output(plan, ki, &elems);
+      else if (k.impl == IMPL_ROW_LAYERNORM) out = &k.ops[k.out_slot];
+      else out = &k.ops[k.chain.out_slot];
+      k.shadow_out = mirror_of(out->ptr);
+      if (k.impl == IMPL_ATTN_FUSED) attention_set_shadow(k, k.shadow_out);
+    }
+    if (k.a_shadow) k.a_shadow = mirror_of(k.ops[k.desc.a_slot].ptr);
+    if (k.b_shadow) k.b_shadow = mirror_of(k.ops[k.desc.b_slot].ptr);
+  }
+  return KB200_OK;
+}
+
 static int launch_one(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   if (numel_of(k.desc) == 0 || k.impl == IMPL_FUSED_AWAY) return KB200_OK;
   if (k.impl == IMPL_ATTN_FUSED) return attention_launch(plan, k, s);
@@ -438,24 +541,32 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
   cudaGetDevice(&prev);
   KB200_CUDA(cudaSetDevice(plan.device));
   int rc = KB200_OK;
+  // phase 1: resolve pointers, pick an implementation per kernel
   for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i) {
     PlanKernel& k = plan.kernels[i];
     attention_destroy(k);
+    k.shadow_out = nullptr;
+    k.a_shadow = k.b_shadow = nullptr;
     rc = resolve(plan, k, (int)i);
     if (rc) break;
     switch (k.desc.kclass) {
       case KB200_K_ELEMENTWISE: rc = choose_elementwise(plan, k); break;
       case KB200_K_ROW: rc = choose_row(plan, k); break;
       case KB200_K_REDUCE: rc = choose_reduce(plan, k); break;
-      default:
-        rc = choose_matmul(plan, k);
-        if (rc == KB200_OK) rc = bind_matmul(plan, k);
-        break;
+      default: rc = choose_matmul(plan, k); break;
     }
   }
+  // phase 2: fuse the attention chain where it matches
   if (rc == KB200_OK && plan.fuse_attention)
     for (size_t i = 0; i + 4 < plan.kernels.size(); ++i)
       if (attention_try_fuse(plan, i)) i += 4;
+  // phase 3: BF16 matmuls read activations from the bf16 mirror when their producer can write it
+  if (rc == KB200_OK) rc = assign_shadows(plan);
+  // phase 4: tensor maps, packed weights, split-K workspaces
+  for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i) {
+    PlanKernel& k = plan.kernels[i];
+    if (k.desc.kclass == KB200_K_MATMUL && k.impl != IMPL_FUSED_AWAY) rc = bind_matmul(plan, k);
+  }
   cudaSetDevice(prev);
   if (rc) return rc;
   plan.bound = true;
@@ -530,6 +641,7 @@ KB200_EXPORT void kb200_plan_destroy(kb200_plan* p) {
     attention_destroy(k);
   }
   if (plan->d_status) cudaFree(plan->d_status);
+  if (plan->arena16) cudaFree(plan->arena16);
   cudaSetDevice(prev);
   delete plan;
 }

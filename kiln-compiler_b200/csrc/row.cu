@@ -9,6 +9,8 @@
 //   row_layernorm  two-pass mean / variance LayerNorm with affine, one warp per row, the row held
 //   row_softmax    in registers (128-bit loads, shuffle reductions): one read and one write of
 //                  the tensor, HBM-bound.
+#include <cuda_bf16.h>
+
 #include "device_math.cuh"
 #include "kb200_internal.h"
 
@@ -114,6 +116,7 @@ struct RowFastParams {
   int64_t x_row_stride, out_row_stride;
   int inner;
   float inv_n, eps;
+  __nv_bfloat16* out16;    // optional bf16 copy of the output (same row stride as `out`), or null
 };
 
 enum { ROW_LAYERNORM = 0, ROW_SOFTMAX = 1 };
@@ -164,6 +167,13 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
         y.z = v[i].z * rstd * g.z + b.z;
         y.w = v[i].w * rstd * g.w + b.w;
         o4[j] = y;
+        if (p.out16 != nullptr) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+          uint2 packed;
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(p.out16 + row * p.out_row_stride + 4 * j) = packed;
+        }
       }
     }
   } else {
@@ -261,6 +271,7 @@ int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
       p.beta = k.ops[k.b_slot].ptr;
       p.inv_n = k.ln_inv_n;
       p.eps = k.ln_eps;
+      p.out16 = static_cast<__nv_bfloat16*>(k.shadow_out);
       launch_row_warp<ROW_LAYERNORM>(p, plan.sm_count, s);
     } else {
       launch_row_warp<ROW_SOFTMAX>(p, plan.sm_count, s);
