@@ -51,7 +51,8 @@ constexpr int kMaxDynamicSmem = 225 * 1024;   // opt-in ceiling, the same for ev
 #endif
 
 struct TcParams {
-  MatmulParams mm;
+  // scalars the producer and MMA threads need first come first: the parameter block is read through
+  // the constant cache, and every new line is a miss on the kernel's critical start-up path
   int bn;               // tile width, multiple of 32 (tf32) / 64 (bf16), <= 256
   int stages;
   int num_kb;           // K slabs
@@ -60,7 +61,8 @@ struct TcParams {
   int b_step_bytes;     // bytes between consecutive MMA K steps inside a B chunk
   int b_sbo_bytes;      // bytes between the row groups of one swizzle atom of B
   int b_layout;         // descriptor layout type of B (1 = 128-byte swizzle on 32-byte atoms, 2 = 128-byte swizzle)
-  int b_kmajor;         // B is read K-major ([N, K] with K contiguous) like A: one box per slab
+  int b_kmajor;         // B is read K-major ([N, K] with K contiguous) like A
+  int b_mode;           // how B is fetched: 0 K-major (one box), 1 N-major, all chunks in one 4-D box, 2 N-major, a box per chunk
   int debug;            // timing experiments only: 1 = no stores, 2 = no MMA, 4 = no TMA (results are then wrong)
   int tmem_cols;        // power of two >= bn, >= 32
   uint32_t idesc;
@@ -69,10 +71,9 @@ struct TcParams {
   int tiles_m, tiles_n, num_tiles;   // tiles per batch entry along M and N; total over the batch
   int pre_col_step, pre_mat_step;    // chain steps whose operand the epilogue fetches ahead (-1 = none)
   __nv_bfloat16* out16;              // optional bf16 copy of the output (same strides as the output), or null
-  int splits;           // split-K factor: a tile's K range is shared by this many work units
+  int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
   int num_units;        // num_tiles * splits
-  float* partials;      // splits > 1: [unit][128][bn] float32 partial tiles
-  unsigned* counters;   // splits > 1: [tile][kEpiWarps] arrivals, left at zero by the last arriver
+  MatmulParams mm;      // shapes, operands, the epilogue chain (epilogue warps only)
 };
 
 // Reduced-precision modes only: exp through ex2.approx and division through rcp.approx (relative
@@ -126,11 +127,13 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
 // contiguous bytes of one row, and the 32 rows give 32 independent accesses in flight per lane.
 
 // Side operand of chain step `s` for the block (zeros outside the matrix).
-__device__ __forceinline__ void load_side32(const TcParams& p, int s, float (&side)[32], int64_t b, int64_t m_first, int64_t n) {
+__device__ __forceinline__ void load_side32(const TcParams& p, int s, float (&side)[32], int64_t b, int64_t m_first, int64_t n,
+                                            int row_limit) {
   const MatmulParams& mm = p.mm;
   const DevOperand& o = mm.ops[mm.chain.steps[s].slot];
   const bool col_ok = n < mm.N;
-  const int64_t rows_left = mm.M - m_first;   // may be <= 0 for a tile hanging over the bottom edge
+  int64_t rows_left = mm.M - m_first;         // may be <= 0 for a tile hanging over the bottom edge
+  if (rows_left > row_limit) rows_left = row_limit;
   const float* base = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
   if (o.stride[1] == 0) {                      // one value per column (bias): a single load
     const float t = (col_ok && rows_left > 0) ? __ldg(base) : 0.0f;
@@ -147,17 +150,17 @@ __device__ __forceinline__ void load_side32(const TcParams& p, int s, float (&si
 // the main loop, the TMEM load and the previous block's stores): the first per-column operand
 // (a bias: one value per lane) and the first full-matrix operand (a residual or a mask).
 __device__ __forceinline__ void prefetch_sides(const TcParams& p, float& pre_col, float (&pre_mat)[32], int64_t b,
-                                               int64_t m_first, int64_t n) {
+                                               int64_t m_first, int64_t n, int row_limit = 32) {
   const MatmulParams& mm = p.mm;
   if (p.pre_col_step >= 0) {
     const DevOperand& o = mm.ops[mm.chain.steps[p.pre_col_step].slot];
     pre_col = (n < mm.N) ? __ldg(o.ptr + b * o.stride[0] + n * o.stride[2]) : 0.0f;
   }
-  if (p.pre_mat_step >= 0) load_side32(p, p.pre_mat_step, pre_mat, b, m_first, n);
+  if (p.pre_mat_step >= 0) load_side32(p, p.pre_mat_step, pre_mat, b, m_first, n, row_limit);
 }
 
 __device__ __forceinline__ void epilogue_compute32(const TcParams& p, float (&x)[32], float pre_col, const float (&pre_mat)[32],
-                                                   int64_t b, int64_t m_first, int64_t n) {
+                                                   int64_t b, int64_t m_first, int64_t n, int row_limit = 32) {
   const MatmulParams& mm = p.mm;
   for (int s = 0; s < mm.chain.n; ++s) {
     const ChainStep st = mm.chain.steps[s];
@@ -169,7 +172,7 @@ __device__ __forceinline__ void epilogue_compute32(const TcParams& p, float (&x)
 #pragma unroll
         for (int r = 0; r < 32; ++r) side[r] = pre_col;
       } else if (st.slot >= 0) {
-        load_side32(p, s, side, b, m_first, n);
+        load_side32(p, s, side, b, m_first, n, row_limit);
       } else {
 #pragma unroll
         for (int r = 0; r < 32; ++r) side[r] = st.imm;
@@ -179,13 +182,15 @@ __device__ __forceinline__ void epilogue_compute32(const TcParams& p, float (&x)
   }
 }
 
-__device__ __forceinline__ void epilogue_store32(const TcParams& p, const float (&x)[32], int64_t b, int64_t m_first, int64_t n) {
+__device__ __forceinline__ void epilogue_store32(const TcParams& p, const float (&x)[32], int64_t b, int64_t m_first, int64_t n,
+                                                 int row_limit = 32) {
   if (p.debug & 1) return;
   const MatmulParams& mm = p.mm;
   const DevOperand& o = mm.ops[mm.chain.out_slot];
   float* out = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
   const int64_t sm = o.stride[1];
-  const int64_t rows_left = mm.M - m_first;
+  int64_t rows_left = mm.M - m_first;
+  if (rows_left > row_limit) rows_left = row_limit;
   if (n < mm.N) {
 #pragma unroll
     for (int r = 0; r < 32; ++r)
@@ -215,7 +220,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   __shared__ int abort_flag;
 #ifdef KB200_TRACE
   __shared__ long long trace[6][160];
+  __shared__ long long marks[8];
   int tp = 0, tm = 0, te = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    marks[0] = (long long)g;
+    marks[1] = clock64();
+  }
 #endif
 
   // 1024-byte aligned tile area (the 128-byte swizzle pattern repeats every 1024 bytes)
@@ -252,57 +264,75 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
+#ifdef KB200_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) marks[2] = clock64();
+#endif
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const int n_chunks = p.bn / p.chunk_n;
-      const int chunk_bytes = p.slab_k * kSlabBytes;
-      uint32_t slab = 0, ring_phase = 0;       // ring position and how often the ring has wrapped (mod 2)
+      // everything the loop needs in registers: a lone thread pays full latency for every
+      // dependent instruction, so the per-slab instruction count is what bounds the issue rate
+      const int stages = p.stages, num_kb = p.num_kb, splits = p.splits, num_units = p.num_units, slab_k = p.slab_k;
+      const int tiles_n = p.tiles_n, bn = p.bn, chunk_n = p.chunk_n, b_mode = p.b_mode;
+      const int n_chunks = bn / chunk_n;
+      const uint32_t chunk_bytes = (uint32_t)slab_k * kSlabBytes;
+      const uint32_t tx_bytes = (uint32_t)stage_bytes;
+      int s = 0;
+      uint32_t wait_parity = 1;                // parity to wait for on the empty barriers of this pass over the ring
       bool ok = true;
-      for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x) {
-        const int tile = unit / p.splits, ks = unit - tile * p.splits;
-        const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-        const int m0 = (rem / p.tiles_n) * kTileM, n0 = (rem % p.tiles_n) * p.bn;
-        const int kb_end = (ks + 1) * p.num_kb / p.splits;
-        for (int kb = ks * p.num_kb / p.splits; kb < kb_end; ++kb) {
-          const int s = (int)slab;
-          const uint32_t it = ring_phase;
-          if (++slab == (uint32_t)p.stages) { slab = 0; ring_phase ^= 1; }
-          if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_ptr)) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit / splits, ks = unit - tile * splits;
+        const int batch = tile / tiles_per_batch, rem = tile - batch * tiles_per_batch;
+        const int tm_i = rem / tiles_n;
+        const int m0 = tm_i * kTileM, n0 = (rem - tm_i * tiles_n) * bn;
+        const int kb_end = (ks + 1) * num_kb / splits;
+        int k_elem = (ks * num_kb / splits) * slab_k;
+        for (int kb = ks * num_kb / splits; kb < kb_end; ++kb, k_elem += slab_k) {
+          const uint32_t full = full0 + 8 * s;
+          if (!mbar_wait(empty0 + 8 * s, wait_parity, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 1); *abort_ptr = 1; }
             ok = false;
             break;
           }
           KB200_STAMP(0, tp);
-          const uint32_t full = full0 + 8 * s;
-          if (p.debug & 4) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full) : "memory"); continue; }
-          mbar_expect_tx(full, (uint32_t)stage_bytes);
+          mbar_expect_tx(full, tx_bytes);
           const uint32_t a_dst = tiles + s * stage_bytes;
-          tma_load_3d(a_dst, &tma_a, full, kb * p.slab_k, m0, batch);
-          if (p.b_kmajor) {
-            tma_load_3d(a_dst + kATileBytes, &tma_b, full, kb * p.slab_k, n0, batch);
-          } else {
+          tma_load_3d(a_dst, &tma_a, full, k_elem, m0, batch);
+          if (b_mode == 0) {                     // K-major B: one box, like A
+            tma_load_3d(a_dst + kATileBytes, &tma_b, full, k_elem, n0, batch);
+          } else if (b_mode == 1) {              // N-major B, all column chunks of the tile in one 4-D box
+            tma_load_4d(a_dst + kATileBytes, &tma_b, full, 0, k_elem, n0 / chunk_n, batch);
+          } else {                               // N-major B, N not a multiple of the chunk: one box per chunk
             for (int c = 0; c < n_chunks; ++c)
-              tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, n0 + c * p.chunk_n, kb * p.slab_k, batch);
+              tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, n0 + c * chunk_n, k_elem, batch);
           }
           KB200_STAMP(1, tp);
 #ifdef KB200_TRACE
           ++tp;
 #endif
+          if (++s == stages) { s = 0; wait_parity ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t lbo = (uint32_t)(p.slab_k * kSlabBytes);   // between N chunks of B
+      const int stages = p.stages, num_kb = p.num_kb, splits = p.splits, num_units = p.num_units, bn = p.bn;
+      const uint32_t idesc = p.idesc;
+      // descriptors: everything but the 14-bit start address is fixed; advancing along K adds to it
+      const uint64_t a_fixed = make_desc(0, 16, 1024);
+      const uint64_t b_fixed = p.b_mode == 0 ? make_desc(0, 16, 1024)
+                                             : make_desc(0, (uint32_t)(p.slab_k * kSlabBytes), (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
+      const uint32_t b_step16 = (p.b_mode == 0 ? 32u : (uint32_t)p.b_step_bytes) >> 4;
+      const uint32_t tiles16 = tiles >> 4, stage16 = (uint32_t)stage_bytes >> 4, a_tile16 = kATileBytes >> 4;
       bool ok = true;
-      uint32_t slab = 0, ring_phase = 0;
+      int s = 0;
+      uint32_t wait_parity = 0;
       int i = 0;
-      for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
-        const int ks = unit % p.splits;
-        const int kb_begin = ks * p.num_kb / p.splits, kb_end = (ks + 1) * p.num_kb / p.splits;
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++i) {
+        const int ks = unit % splits;
+        const int kb_begin = ks * num_kb / splits, kb_end = (ks + 1) * num_kb / splits;
         const int acc = i & 1;
         const uint32_t aph = (i >> 1) & 1;
         // the epilogue must have drained this accumulator (two tiles ago) before it is overwritten
@@ -311,33 +341,31 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.bn);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * bn);
+        uint32_t accumulate = 0;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          const int s = (int)slab;
-          const uint32_t it = ring_phase;
-          if (++slab == (uint32_t)p.stages) { slab = 0; ring_phase ^= 1; }
-          if (!mbar_wait(full0 + 8 * s, it & 1, abort_ptr)) {
+          if (!mbar_wait(full0 + 8 * s, wait_parity, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
             ok = false;
             break;
           }
           KB200_STAMP(2, tm);
-          const uint32_t a_addr = tiles + s * stage_bytes;
-          const uint32_t b_addr = a_addr + kATileBytes;
+          const uint32_t a16 = tiles16 + (uint32_t)s * stage16;
+          const uint32_t b16 = a16 + a_tile16;
 #pragma unroll
           for (int k = 0; k < kSlabBytes / 32; ++k) {
-            if (p.debug & 2) break;
-            const uint64_t adesc = make_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t bdesc = p.b_kmajor ? make_desc(b_addr + k * 32, 16, 1024)
-                                              : make_desc(b_addr + k * p.b_step_bytes, lbo, (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
-            umma(tmem_d, adesc, bdesc, p.idesc, (kb > kb_begin || k != 0) ? 1u : 0u, BF16);
+            // 14-bit start-address field: in a cluster the shared window address carries the CTA rank in
+            // its upper bits, which must not spill into the neighbouring descriptor fields
+            umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu), idesc,
+                 accumulate, BF16);
+            accumulate = 1;
           }
-          if (p.debug & 8) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
-          else umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+          umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
           KB200_STAMP(3, tm);
 #ifdef KB200_TRACE
           ++tm;
 #endif
+          if (++s == stages) { s = 0; wait_parity ^= 1; }
         }
         if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA of this tile has completed
       }
@@ -371,7 +399,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // this warp's share of the tile: rows quad*32..+31, column chunks half*32, +64, ...
-      float* part = p.splits > 1 ? p.partials + ((size_t)unit * kTileM + quad * 32) * p.bn : nullptr;
+      // split K: the partial tile goes into this CTA's (now idle) pipeline memory, row-major [128][bn]
+      float* part = reinterpret_cast<float*>(smem_raw + (tiles - raw)) + (size_t)(quad * 32) * p.bn;
       for (int c = half * 32; c < p.bn; c += 64) {
         if (n0 + c >= p.mm.N || (p.debug & 16)) break;   // uniform across the warp
         float v[32];
@@ -389,7 +418,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           epilogue_store32(p, v, batch, m_first, n0 + c + lane);
         } else {
 #pragma unroll
-          for (int r = 0; r < 32; ++r) __stcg(part + r * p.bn + c + lane, v[r]);
+          for (int r = 0; r < 32; ++r) part[r * p.bn + c + lane] = v[r];
         }
       }
       // this warp is done reading the accumulator: hand it back to the MMA issuer
@@ -399,36 +428,63 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #ifdef KB200_TRACE
       if (warp == 2 && lane == 0) { KB200_STAMP(5, te); ++te; }
 #endif
-      if (p.splits > 1) {
-        // Split-K: the same warp slot of the other units of this tile owns the same sub-block.  The
-        // last of them to arrive sums the partial sub-blocks in unit order (so the result does not
-        // depend on arrival order), applies the epilogue and resets the counter for the next launch.
-        __threadfence();
-        unsigned prev = 0;
-        if (lane == 0) prev = atomicAdd(p.counters + (size_t)tile * kEpiWarps + e, 1u);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == (unsigned)(p.splits - 1)) {
-          __threadfence();
-          const float* first = p.partials + ((size_t)tile * p.splits * kTileM + quad * 32) * p.bn;
-          for (int c = half * 32; c < p.bn; c += 64) {
-            if (n0 + c >= p.mm.N) break;
-            float v[32];
+    }
+  }
+
+  // ---------------- split K: reduce across the cluster through distributed shared memory ----------------
+  // The `splits` CTAs of a cluster hold partial sums of the same tile.  After a cluster barrier each
+  // CTA takes a band of rows, adds the partial bands of all CTAs in rank order (so the result does
+  // not depend on timing), applies the epilogue and stores.  Every thread of every CTA reaches both
+  // barriers, also after an aborted wait: all loops above are bounded.
+  if (p.splits > 1) {
+    __syncthreads();
+#ifdef KB200_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) marks[3] = clock64();
+#endif
+    cluster_sync();
+#ifdef KB200_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) marks[4] = clock64();
+#endif
+    if (warp >= 2 && !abort_flag) {
+      const int e = warp - 2;
+      uint32_t rank;
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+      const int unit = blockIdx.x;
+      const int tile = unit / p.splits;
+      const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const int64_t m0 = (int64_t)(rem / p.tiles_n) * kTileM, n0 = (int64_t)(rem % p.tiles_n) * p.bn;
+      const int row_lo = (int)rank * kTileM / p.splits, row_hi = ((int)rank + 1) * kTileM / p.splits;
+      const int col_blocks = p.bn / 32;
+      const int n_blocks = ((row_hi - row_lo + 31) / 32) * col_blocks;
+      for (int blk = e; blk < n_blocks; blk += kEpiWarps) {
+        const int rb = blk / col_blocks, cb = blk - rb * col_blocks;
+        const int row_base = row_lo + rb * 32;
+        const int nrows = row_hi - row_base < 32 ? row_hi - row_base : 32;
+        const int64_t n = n0 + cb * 32 + lane;
+        if (n0 + cb * 32 >= p.mm.N) continue;
+        float pre_col = 0.0f, pre_mat[32];
+        prefetch_sides(p, pre_col, pre_mat, batch, m0 + row_base, n, nrows);
+        float v[32];
 #pragma unroll
-            for (int r = 0; r < 32; ++r) v[r] = 0.0f;
-            for (int sp = 0; sp < p.splits; ++sp) {
-              const float* src = first + (size_t)sp * kTileM * p.bn + c + lane;
+        for (int r = 0; r < 32; ++r) v[r] = 0.0f;
+        const uint32_t local = tiles + (uint32_t)((row_base * p.bn + cb * 32 + lane) * 4);
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const uint32_t remote = map_to_cta(local, (uint32_t)sp);
 #pragma unroll
-              for (int r = 0; r < 32; ++r) v[r] += __ldcg(src + r * p.bn);
-            }
-            prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + c + lane);
-            epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + c + lane);
-            epilogue_store32(p, v, batch, m_first, n0 + c + lane);
-          }
-          if (lane == 0) p.counters[(size_t)tile * kEpiWarps + e] = 0u;
+          for (int r = 0; r < 32; ++r)
+            if (r < nrows) v[r] += ld_cluster_f32(remote + (uint32_t)(r * p.bn * 4));
         }
-        (void)ks;
+        epilogue_compute32(p, v, pre_col, pre_mat, batch, m0 + row_base, n, nrows);
+        epilogue_store32(p, v, batch, m0 + row_base, n, nrows);
       }
     }
+#ifdef KB200_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 64) marks[5] = clock64();
+#endif
+    cluster_sync();     // nobody leaves (and frees its shared memory) while a neighbour still reads it
+#ifdef KB200_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) marks[6] = clock64();
+#endif
   }
 
   // ---------------- common exit ----------------
@@ -436,6 +492,13 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   __syncthreads();
 #ifdef KB200_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    printf("KERNEL block0 globaltimer start %lld end %lld (ns) dur %lld | cycles: entry 0 setup_done %lld first_prod %lld exit %lld | units/CTA~%d splits %d num_kb %d bn %d stages %d\n",
+           marks[0], (long long)g, (long long)g - marks[0], marks[2] - marks[1], trace[0][0] - marks[1], clock64() - marks[1],
+           (p.num_units + (int)gridDim.x - 1) / (int)gridDim.x, p.splits, p.num_kb, p.bn, p.stages);
+    printf("split phase: before cluster sync %lld after %lld warp2 reduce done %lld after 2nd sync %lld (cycles since entry)\n",
+           marks[3] - marks[1], marks[4] - marks[1], marks[5] - marks[1], marks[6] - marks[1]);
     const long long t0 = trace[0][0];
     for (int i = 0; i < 160 && i < p.num_kb * 3; ++i)
       printf("slab %3d  prod_wait_done %7lld issued %7lld | mma_full %7lld committed %7lld\n", i, trace[0][i] - t0,
@@ -485,9 +548,6 @@ struct TcState {
   bool b_const = false;       // B is a frozen constant: converted once at bind
   bool a_shadow = false;      // A / B is read from the bf16 mirror its producer writes: no conversion launch
   bool b_shadow = false;
-  // split-K workspace
-  float* partials = nullptr;
-  unsigned* counters = nullptr;
 };
 
 }  // namespace
@@ -526,10 +586,16 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   const int chunk_n = st->bf16 ? 64 : 32, slab_k = st->bf16 ? 64 : 32;
   int bn = d.cfg[1];
   if (bn <= 0) {
-    // widest tile that still gives every SM one; otherwise 128 columns and split K to fill the machine
-    bn = k.N >= 128 ? 128 : 64;
+    // the widest tile that still gives most SMs a tile of their own (measured: a second, partial
+    // wave costs more than narrower tiles); 64 columns when even that leaves SMs idle
     const int64_t tiles_m = (k.M + kTileM - 1) / kTileM;
-    if (k.N >= 256 && tiles_m * ((k.N + 255) / 256) * k.batch >= plan.sm_count) bn = 256;
+    bn = 64;
+    for (int cand : {256, 128}) {
+      if (k.N >= cand && tiles_m * ((k.N + cand - 1) / cand) * k.batch * 5 >= (int64_t)plan.sm_count * 3) {
+        bn = cand;
+        break;
+      }
+    }
   }
   if (bn > 256) bn = 256;
   bn = (bn / 64) * 64;                                    // the two epilogue warps of a quadrant take 32 columns each
@@ -553,6 +619,7 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.b_layout = st->bf16 ? 2 : 1;
   p.b_sbo_bytes = st->bf16 ? 1024 : 512;
   p.b_kmajor = k.ops[d.b_slot].stride[2] == 1 ? 0 : 1;
+  p.b_mode = p.b_kmajor ? 0 : (k.N % chunk_n == 0 ? 1 : 2);
   p.debug = d.cfg[6];
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * bn) p.tmem_cols *= 2;           // two accumulators: the epilogue drains one while the next tile fills the other
@@ -563,29 +630,21 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   // 768-wide layers): every SM then streams a share of the operands.
   int splits = d.cfg[4];
   if (splits <= 0) {
+    // Split K over a cluster only when the tiles leave more than half of the SMs idle and K is long:
+    // the cluster reduction costs about as much as 8 K slabs.
     splits = 1;
-    if (p.num_tiles * 2 <= plan.sm_count) {
-      splits = plan.sm_count / p.num_tiles;
-      if (splits > p.num_kb / 4) splits = p.num_kb / 4;
-      if (splits > 8) splits = 8;
-      if (splits < 1) splits = 1;
+    if (p.num_tiles * 2 <= plan.sm_count && p.num_kb >= 16) {
+      splits = 2;
+      if (p.num_tiles * 4 <= plan.sm_count && p.num_kb >= 32) splits = 4;
     }
   }
   if (splits > p.num_kb) splits = p.num_kb;
-  if (splits > 16) splits = 16;
+  // the reduction runs over a thread-block cluster (<= 8 CTAs) and parks the partial tile in the
+  // pipeline's shared memory
+  if (splits > 8) splits = 8;
+  while (splits > 1 && (size_t)stages * stage_bytes < (size_t)kTileM * bn * sizeof(float)) splits = 1;
   p.splits = splits;
   p.num_units = p.num_tiles * splits;
-  p.partials = nullptr;
-  p.counters = nullptr;
-  if (st->partials) { cudaFree(st->partials); st->partials = nullptr; }
-  if (st->counters) { cudaFree(st->counters); st->counters = nullptr; }
-  if (splits > 1) {
-    KB200_CUDA(cudaMalloc(&st->partials, (size_t)p.num_units * kTileM * bn * sizeof(float)));
-    KB200_CUDA(cudaMalloc(&st->counters, (size_t)p.num_tiles * kEpiWarps * sizeof(unsigned)));
-    KB200_CUDA(cudaMemset(st->counters, 0, (size_t)p.num_tiles * kEpiWarps * sizeof(unsigned)));
-    p.partials = st->partials;
-    p.counters = st->counters;
-  }
   // instruction descriptor: D = F32, A/B = TF32 or BF16, A K-major, B MN-major, N = bn, M = 128
   const uint32_t fmt = st->bf16 ? 1u : 2u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | ((p.b_kmajor ? 0u : 1u) << 16) | ((uint32_t)(bn >> 3) << 17) |
@@ -603,7 +662,8 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   }
   st->smem_bytes = (size_t)stages * stage_bytes + kEpiBytes + 1024;
   // persistent CTAs, one per SM: each walks the tile list with a stride of the grid size
-  st->grid = dim3((unsigned)(p.num_units < plan.sm_count ? p.num_units : plan.sm_count), 1, 1);
+  st->grid = p.splits > 1 ? dim3((unsigned)p.num_units, 1, 1)     // one unit per CTA, clusters of `splits`
+                          : dim3((unsigned)(p.num_units < plan.sm_count ? p.num_units : plan.sm_count), 1, 1);
 
   const DevOperand& A = k.ops[d.a_slot];
   const DevOperand& B = k.ops[d.b_slot];
@@ -645,8 +705,10 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     }
   }
   if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
-      !encode_map(&st->map_b, st->bf16, b_base, b_cols, b_rows, k.batch, b_row, b_batch, p.b_kmajor ? slab_k : chunk_n,
-                  p.b_kmajor ? bn : slab_k, !st->bf16 && !p.b_kmajor))
+      !(p.b_mode == 1 ? encode_map4(&st->map_b, st->bf16, b_base, chunk_n, b_rows, b_cols / chunk_n, k.batch, b_row, b_batch, slab_k,
+                                    bn / chunk_n, !st->bf16)
+                      : encode_map(&st->map_b, st->bf16, b_base, b_cols, b_rows, k.batch, b_row, b_batch, p.b_kmajor ? slab_k : chunk_n,
+                                   p.b_kmajor ? bn : slab_k, !st->bf16 && !p.b_kmajor)))
     return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
   // The attribute is per function, not per launch: always ask for the ceiling, so that plans with
   // different tile configurations can coexist in one process.
@@ -674,10 +736,21 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
       cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
           B.ptr, st->b16, k.batch, rows, cols, B.stride[0], km ? B.stride[2] : B.stride[1]);
     }
-    mm_tc_kernel<true><<<st->grid, kThreads, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
-  } else {
-    mm_tc_kernel<false><<<st->grid, kThreads, st->smem_bytes, s>>>(st->map_a, st->map_b, st->params);
   }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = st->grid;
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = st->smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)st->params.splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = st->params.splits > 1 ? 1 : 0;
+  if (st->bf16) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<true>, st->map_a, st->map_b, st->params));
+  else KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false>, st->map_a, st->map_b, st->params));
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }
@@ -687,8 +760,6 @@ void tc_destroy(PlanKernel& k) {
   if (!st) return;
   if (st->a16) cudaFree(st->a16);
   if (st->b16) cudaFree(st->b16);
-  if (st->partials) cudaFree(st->partials);
-  if (st->counters) cudaFree(st->counters);
   delete st;
   k.tc = nullptr;
 }
@@ -789,6 +860,8 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.num_kb = (int)((k + slab_k - 1) / slab_k);
   p.b_step_bytes = 16 * kSlabBytes;
   p.b_layout = 2; p.b_sbo_bytes = 1024;
+  p.b_kmajor = 0;
+  p.b_mode = 2;
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * bn) p.tmem_cols *= 2;
   p.tiles_m = (int)((m + kTileM - 1) / kTileM);

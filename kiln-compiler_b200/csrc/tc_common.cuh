@@ -49,6 +49,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 
 // Shared-memory matrix descriptor.  layout: 2 = 128-byte swizzle of 16-byte units, 1 = 128-byte
 // swizzle of 32-byte units (the only swizzled layout an N-major 32-bit operand may use).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3FFF);
@@ -139,6 +146,23 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- thread-block clusters ----
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-memory address of the same location in the CTA with rank `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // ---- host side ----
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -173,6 +197,27 @@ inline bool encode_map(CUtensorMap* map, bool bf16, const void* base, int64_t co
                   dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// A 4-D tiled map over an N-major matrix [batch, rows, n_chunks * chunk] seen as
+// (chunk, rows, n_chunks, batch): one box (chunk, box_rows, box_chunks, 1) lands in shared memory as
+// box_chunks consecutive blocks of [box_rows x chunk], the layout the N-major MMA descriptor walks.
+inline bool encode_map4(CUtensorMap* map, bool bf16, const void* base, int chunk, int64_t rows, int64_t n_chunks, int64_t batch,
+                        int64_t row_stride_elems, int64_t batch_stride_elems, int box_rows, int box_chunks, bool atom32) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const int esz = bf16 ? 2 : 4;
+  cuuint64_t dims[4] = {(cuuint64_t)chunk, (cuuint64_t)rows, (cuuint64_t)n_chunks, (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)row_stride_elems * esz, (cuuint64_t)chunk * esz,
+                           (cuuint64_t)(batch > 1 ? batch_stride_elems : row_stride_elems * rows) * esz};
+  if (strides[2] == 0) strides[2] = strides[0] * rows;
+  cuuint32_t box[4] = {(cuuint32_t)chunk, (cuuint32_t)box_rows, (cuuint32_t)box_chunks, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base),
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
