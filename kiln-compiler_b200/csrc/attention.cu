@@ -10,13 +10,17 @@
 // and writes the merged-heads buffer, the only value of the chain that is live afterwards.  The
 // plan itself (kernel list, arena offsets) is untouched; the score buffers are simply never written.
 //
-// One CTA per (head, 128-query tile), 192 threads in three roles:
+// One CTA per (head, 128-query tile), 320 threads in three roles:
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through 2-deep rings.
 //   warp 1      MMA issuer: S = Q K^T (operands in shared memory, TF32) into one of two S buffers in
 //               TMEM; O_part = P V with P read from TMEM (written there by the softmax warps).
-//   warps 2..5  softmax: each thread owns one query row; scale, causal mask on the diagonal tile,
-//               running max / sum (online softmax), P stored back over S in TMEM, and the running
-//               output O kept in registers, rescaled and accumulated from O_part after each tile.
+//   warps 2..9  softmax, as two groups of 128 threads.  Group g owns keys g*64 .. g*64+63 of every
+//               tile and keeps its OWN online-softmax state (running max, sum and output) for them,
+//               one query row per thread: scale, causal mask on the diagonal tile, P stored back
+//               over S in TMEM, then P V of its 64 keys accumulates into its own O_part buffer.  The
+//               two partial results are merged once, at the end, through shared memory.  O_part is
+//               double-buffered and folded into the running output one tile late, so the P V of
+//               tile j runs under the softmax of tile j+1.
 // Causal tiles above the diagonal are skipped.  Every mbarrier wait is bounded (see matmul_tc.cu).
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -36,8 +40,9 @@ using namespace tc;
 constexpr int kRows = 128;                   // queries per CTA and keys per tile
 constexpr int kHeadDim = 64;
 constexpr int kSlab = kRows * 128;           // one [128 rows x 128 bytes] swizzled slab
-constexpr int kAttnThreads = 64 + 128;
+constexpr int kAttnThreads = 64 + 256;
 constexpr int kAttnSmem = 5 * 2 * kSlab + 1024;   // Q + 2 x K + 2 x V, two slabs each, + alignment slack
+constexpr int kXStride = 35;                 // floats per row of the merge buffers: odd, so rows spread over the banks
 
 struct AttnParams {
   int T, H, q_tiles;
@@ -68,23 +73,59 @@ __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
+// Scores of one 32-column block -> probabilities, in place; returns their sum.  `first_col` is the
+// block's first key relative to the query tile's first row (only used on the diagonal tile).
+template <bool DIAGONAL>
+__device__ __forceinline__ float probabilities32(float (&v)[32], float scale_log2, float m_use, int first_col, int row) {
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float pr = exp2f(fmaf(v[i], scale_log2, -m_use));
+    if (DIAGONAL && first_col + i > row) pr = 0.0f;
+    v[i] = pr;
+    sum += pr;
+  }
+  return sum;
+}
+template <bool DIAGONAL>
+__device__ __forceinline__ float row_max32(const float (&v)[32], float m, int first_col, int row) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (!DIAGONAL || first_col + i <= row) m = fmaxf(m, v[i]);
+  return m;
+}
+
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[14];
+  __shared__ __align__(8) uint64_t bars[19];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+#ifdef KB200_TRACE
+  __shared__ long long trace[4][16];
+  __shared__ long long marks[4];
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    marks[0] = (long long)g;
+    marks[1] = clock64();
+  }
+#define ATTN_STAMP(role, idx) do { if (blockIdx.x == 0 && threadIdx.x == 64 && (idx) < 16) trace[role][idx] = clock64(); } while (0)
+#else
+#define ATTN_STAMP(role, idx) do { } while (0)
+#endif
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t q_smem = (raw + 1023u) & ~1023u;
   const uint32_t k_smem = q_smem + 2 * kSlab;       // ring of 2, each 2 slabs
   const uint32_t v_smem = k_smem + 4 * kSlab;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 p_full | 13 o_full
+  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
+  //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer]
   const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
   const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
-  const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull = smem_u32(&bars[13]);
+  const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull0 = smem_u32(&bars[15]);
 
   const int h = blockIdx.x % p.H;
   const int qt = p.q_tiles - 1 - blockIdx.x / p.H;   // heaviest (longest causal prefix) tiles first
@@ -100,9 +141,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(v_full + 8 * s, 1);
       mbar_init(v_empty + 8 * s, 1);
       mbar_init(sfull0 + 8 * s, 1);
-      mbar_init(pfull0 + 8 * s, 128);
     }
-    mbar_init(ofull, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(pfull0 + 8 * i, 128);
+      mbar_init(ofull0 + 8 * i, 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -114,7 +157,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tmem_o = tmem_base + 256;           // S0: 0..127, S1: 128..255, O_part: 256..319
+  // columns: S0 0..127 | S1 128..255 | O_part[group][buffer] 256 + (group * 2 + buffer) * 64
+  const uint32_t tmem_o0 = tmem_base + 256;
   volatile int* abort_ptr = &abort_flag;
   auto give_up = [&](int site) {
     if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | site); *abort_ptr = 1; }
@@ -158,18 +202,25 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         umma_commit(sfull0 + 8 * s);
         umma_commit(k_empty + 8 * s);
       };
+      // P V of tile j: each group's 64 keys into that group's O_part buffer (j & 1).  In-order execution
+      // of the tensor pipe keeps S[s] intact until these reads of P are done (the next Q K^T into S[s]
+      // is issued later), and the buffer (j & 1) was folded by the softmax threads before they
+      // published P of tile j.
       auto issue_pv = [&](int j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(v_full + 8 * s, ph, abort_ptr)) { give_up(0x23); ok = false; return; }
-        if (!mbar_wait(pfull0 + 8 * s, ph, abort_ptr)) { give_up(0x24); ok = false; return; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t vb = v_smem + s * 2 * kSlab;
+        for (int g = 0; g < 2; ++g) {
+          if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t o_addr = tmem_o0 + (uint32_t)(g * 2 + (j & 1)) * 64;
 #pragma unroll
-        for (int kk = 0; kk < kRows / 8; ++kk)
-          umma_ts(tmem_o, tmem_base + (uint32_t)s * 128 + (uint32_t)kk * 8, make_desc(vb + kk * 1024, kSlab, 512, 1), p.idesc_pv,
-                  kk != 0 ? 1u : 0u, false);
-        umma_commit(ofull);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
+                    make_desc(vb + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1), p.idesc_pv, kk != 0 ? 1u : 0u, false);
+          umma_commit(ofull0 + 8 * (g * 2 + (j & 1)));
+        }
         umma_commit(v_empty + 8 * s);
       };
       if (ok) issue_qk(0);
@@ -179,15 +230,33 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
     }
   } else {
-    // ---------------- softmax / output (warps 2..5) ----------------
+    // ---------------- softmax / output (warps 2..9) ----------------
     const int quad = warp & 3;
+    const int group = (warp - 2) >> 2;             // which 64 keys of every tile
     const int row = quad * 32 + lane;              // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const int c0 = group * 64;
     float o[kHeadDim];
 #pragma unroll
     for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
-    float m_run = -CUDART_INF_F, l_run = 0.0f;
+    float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
     bool ok = true;
+    // running output <- running output * alpha + O_part of tile j
+    auto fold = [&](int j, float alpha) {
+      bool got = mbar_wait(ofull0 + 8 * (group * 2 + (j & 1)), (j >> 1) & 1, abort_ptr);
+      if (!got) give_up(0x32);
+      ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
+      if (!ok) return;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t o_addr = tmem_o0 + lane_addr + (uint32_t)(group * 2 + (j & 1)) * 64;
+#pragma unroll
+      for (int c = 0; c < kHeadDim; c += 32) {
+        float v[32];
+        tmem_ld32(o_addr + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, v[i]);
+      }
+    };
     for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
@@ -195,68 +264,91 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (!got) give_up(0x31);
       ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
       if (!ok) break;
+      ATTN_STAMP(0, j);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)s * 128;
+      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
       const bool diagonal = j == qt;
-      // pass 1: row maximum of the scaled, masked scores
-      float m_tile = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < kRows; c += 32) {
-        float v[32];
-        tmem_ld32(s_addr + c, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float t = (diagonal && c + i > row) ? -CUDART_INF_F : v[i] * p.scale_log2;
-          m_tile = fmaxf(m_tile, t);
-        }
+      float va[32], vb[32];
+      tmem_ld32(s_addr, va);
+      tmem_ld32(s_addr + 32, vb);
+      // the scale is positive (checked when the chain was matched), so the maximum commutes with it
+      float mx = -CUDART_INF_F;
+      if (diagonal) {
+        mx = row_max32<true>(va, mx, c0, row);
+        mx = row_max32<true>(vb, mx, c0 + 32, row);
+      } else {
+        mx = row_max32<false>(va, mx, 0, 0);
+        mx = row_max32<false>(vb, mx, 0, 0);
       }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float alpha = exp2f(m_run - m_new);     // 0 on the first tile (m_run = -inf)
-      // pass 2: probabilities, row sum, P back into the S buffer
-      float sum = 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < kRows; c += 32) {
-        float v[32];
-        tmem_ld32(s_addr + c, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float t = (diagonal && c + i > row) ? -CUDART_INF_F : v[i] * p.scale_log2;
-          v[i] = exp2f(t - m_new);
-          sum += v[i];
-        }
-        tmem_st32(s_addr + c, v);
+      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      // a row with every key of this group masked so far keeps m = -inf: use 0 as the reference point
+      const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;
+      const float alpha = exp2f(m_run - m_use);     // 0 while m_run = -inf
+      float sum;
+      if (diagonal) {
+        sum = probabilities32<true>(va, p.scale_log2, m_use, c0, row);
+        sum += probabilities32<true>(vb, p.scale_log2, m_use, c0 + 32, row);
+      } else {
+        sum = probabilities32<false>(va, p.scale_log2, m_use, 0, 0);
+        sum += probabilities32<false>(vb, p.scale_log2, m_use, 0, 0);
       }
+      tmem_st32(s_addr, va);
+      tmem_st32(s_addr + 32, vb);
       tmem_st_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(pfull0 + 8 * s);
+      mbar_arrive(pfull0 + 8 * (group * 2 + s));
+      ATTN_STAMP(1, j);
+      // fold the PREVIOUS tile's O_part while the tensor pipe works on this one
+      if (j > 0) {
+        fold(j - 1, alpha_prev);
+        if (!ok) break;
+      }
+      ATTN_STAMP(3, j);
+      alpha_prev = alpha;
       l_run = l_run * alpha + sum;
       m_run = m_new;
-      // O = O * alpha + P V
-      got = mbar_wait(ofull, j & 1, abort_ptr);
-      if (!got) give_up(0x32);
-      ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < kHeadDim; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_o + lane_addr + c, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha + v[i];
-      }
     }
+    if (ok) fold(n_kv - 1, alpha_prev);
+    // ---- merge the two groups' states; group g finishes head dims g*32 .. g*32+31 ----
+    // Every MMA has completed (the last O_part arrived after all of them), so the K ring is free.
+    float* xbuf = reinterpret_cast<float*>(smem_raw + (k_smem - raw));      // [2][128][kXStride]
+    float* mine = xbuf + (size_t)(group * kRows + row) * kXStride;          // what this thread gives away
+    const float* theirs = xbuf + (size_t)((group ^ 1) * kRows + row) * kXStride;
     if (ok) {
-      const float inv = 1.0f / l_run;
-      float* dst = p.out + (int64_t)(q0 + row) * p.out_row_stride + h * kHeadDim;
+      if (group == 0) {
 #pragma unroll
-      for (int i = 0; i < kHeadDim; i += 4)
-        *reinterpret_cast<float4*>(dst + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+        for (int i = 0; i < 32; ++i) mine[i] = o[32 + i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mine[i] = o[i];
+      }
+      mine[32] = m_run;
+      mine[33] = l_run;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight softmax warps only
+    if (ok && !*abort_ptr) {
+      const float m_other = theirs[32], l_other = theirs[33];
+      const float m_all = fmaxf(m_run, m_other);       // finite: key 0 is visible to every row
+      const float w_mine = exp2f(m_run - m_all), w_other = exp2f(m_other - m_all);
+      const float inv = 1.0f / (l_run * w_mine + l_other * w_other);
+      const float a = w_mine * inv, b = w_other * inv;
+      float r[32];
+      if (group == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = o[i] * a + theirs[i] * b;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = o[32 + i] * a + theirs[i] * b;
+      }
+      float* dst = p.out + (int64_t)(q0 + row) * p.out_row_stride + h * kHeadDim + group * 32;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(r[i], r[i + 1], r[i + 2], r[i + 3]);
       if (p.out16 != nullptr) {
-        __nv_bfloat16* dst16 = p.out16 + (int64_t)(q0 + row) * p.out16_row_stride + h * kHeadDim;
+        __nv_bfloat16* dst16 = p.out16 + (int64_t)(q0 + row) * p.out16_row_stride + h * kHeadDim + group * 32;
 #pragma unroll
-        for (int i = 0; i < kHeadDim; i += 8) {
-          __nv_bfloat162 w0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), w1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-          __nv_bfloat162 w2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), w3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+        for (int i = 0; i < 32; i += 8) {
+          __nv_bfloat162 w0 = __floats2bfloat162_rn(r[i], r[i + 1]), w1 = __floats2bfloat162_rn(r[i + 2], r[i + 3]);
+          __nv_bfloat162 w2 = __floats2bfloat162_rn(r[i + 4], r[i + 5]), w3 = __floats2bfloat162_rn(r[i + 6], r[i + 7]);
           uint4 packed;
           packed.x = *reinterpret_cast<uint32_t*>(&w0);
           packed.y = *reinterpret_cast<uint32_t*>(&w1);
@@ -271,6 +363,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   // ---------------- common exit ----------------
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+#ifdef KB200_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    printf("ATTN block0 globaltimer start %lld end %lld (ns) dur %lld | exit cycles %lld n_kv %d\n", marks[0], (long long)g,
+           (long long)g - marks[0], clock64() - marks[1], n_kv);
+    for (int j = 0; j < n_kv && j < 16; ++j)
+      printf("kv %2d  s_ready %7lld p_stored %7lld folded %7lld\n", j, trace[0][j] - marks[1], trace[1][j] - marks[1],
+             trace[3][j] - marks[1]);
+  }
+#endif
   if (abort_flag && threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s)
       for (uint32_t i = 0; i < 4096u; ++i)

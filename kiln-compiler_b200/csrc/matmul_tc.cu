@@ -43,7 +43,11 @@ constexpr int kATileBytes = kTileM * kSlabBytes;
 constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;      // producer warp, MMA warp, epilogue warps
-constexpr int kEpiBytes = kEpiWarps * 32 * 33 * 4;  // per-warp 32 x 33 transpose buffers
+// per epilogue warp: a 32 x 33 float transpose buffer, reused (as dense 32 x 32) as the staging block of
+// the bulk store, then a 32 x 32 bf16 staging block; both 128-byte aligned
+constexpr int kEpiStage16Offset = 4352;
+constexpr int kEpiWarpBytes = kEpiStage16Offset + 32 * 32 * 2;
+constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
 #ifdef KB200_TRACE
 constexpr int kMaxDynamicSmem = 200 * 1024;   // the trace arrays take static shared memory
 #else
@@ -73,6 +77,7 @@ struct TcParams {
   __nv_bfloat16* out16;              // optional bf16 copy of the output (same strides as the output), or null
   int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
   int num_units;        // num_tiles * splits
+  int store_mode;       // 0: the epilogue warps store with ordinary global stores; 1: bulk tensor stores from shared memory
   MatmulParams mm;      // shapes, operands, the epilogue chain (epilogue warps only)
 };
 
@@ -213,6 +218,7 @@ __device__ __forceinline__ void epilogue_store32(const TcParams& p, const float 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+             const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_out16,
              const __grid_constant__ TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
@@ -235,7 +241,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const int b_tile_bytes = p.bn * kSlabBytes;
   const int stage_bytes = kATileBytes + b_tile_bytes;
-  float* epi_buf = reinterpret_cast<float*>(smem_raw + (tiles - raw) + (size_t)p.stages * stage_bytes);
+  uint8_t* epi_buf = smem_raw + (tiles - raw) + (size_t)p.stages * stage_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
   const uint32_t tfull0 = smem_u32(&bars[2 * kMaxStages]), tempty0 = smem_u32(&bars[2 * kMaxStages + 2]);
@@ -377,7 +383,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     const int e = warp - 2;
     const int quad = warp & 3;
     const int half = e >> 2;
-    float* tbuf = epi_buf + e * (32 * 33);
+    float* tbuf = reinterpret_cast<float*>(epi_buf + e * kEpiWarpBytes);
+    __nv_bfloat16* stage16 = reinterpret_cast<__nv_bfloat16*>(epi_buf + e * kEpiWarpBytes + kEpiStage16Offset);
+    const bool bulk = p.store_mode == 1 && p.splits == 1;
     int i = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
@@ -395,7 +403,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
       if (!ok) break;
 #ifdef KB200_TRACE
-      if (warp == 2 && lane == 0) KB200_STAMP(4, te);
+      if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
 #endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // this warp's share of the tile: rows quad*32..+31, column chunks half*32, +64, ...
@@ -405,6 +413,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         if (n0 + c >= p.mm.N || (p.debug & 16)) break;   // uniform across the warp
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
+        if (bulk) {
+          // the bulk stores of the previous block must have read the staging memory before it is rewritten
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        }
+#ifdef KB200_TRACE
+        if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+#endif
         // transpose through shared memory: lane = row  ->  lane = column
 #pragma unroll
         for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = v[j];
@@ -412,10 +428,37 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
         for (int r = 0; r < 32; ++r) v[r] = tbuf[r * 33 + lane];
         __syncwarp();
+#ifdef KB200_TRACE
+        if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+#endif
         if (direct) {
           epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + c + lane);
+#ifdef KB200_TRACE
+          if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+#endif
           if (c + 64 < p.bn && n0 + c + 64 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + c + 64 + lane);
-          epilogue_store32(p, v, batch, m_first, n0 + c + lane);
+          if (bulk) {
+            // dense row-major 32 x 32 blocks in shared memory, then one bulk tensor store each: the
+            // store engine writes whole 128-byte lines and clips the block at the matrix edges
+#pragma unroll
+            for (int r = 0; r < 32; ++r) tbuf[r * 32 + lane] = v[r];
+            if (p.out16 != nullptr) {
+#pragma unroll
+              for (int r = 0; r < 32; ++r) stage16[r * 32 + lane] = __float2bfloat16_rn(v[r]);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && m_first < p.mm.M && !(p.debug & 1)) {
+              tma_store_3d(&tma_out, smem_u32(tbuf), (int)(n0 + c), (int)m_first, batch);
+              if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(stage16), (int)(n0 + c), (int)m_first, batch);
+              tma_store_commit();
+            }
+          } else {
+            epilogue_store32(p, v, batch, m_first, n0 + c + lane);
+          }
+#ifdef KB200_TRACE
+          if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+#endif
         } else {
 #pragma unroll
           for (int r = 0; r < 32; ++r) part[r * p.bn + c + lane] = v[r];
@@ -426,9 +469,10 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * acc) : "memory");
 #ifdef KB200_TRACE
-      if (warp == 2 && lane == 0) { KB200_STAMP(5, te); ++te; }
+      if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
 #endif
     }
+    if (bulk && lane == 0) tma_store_wait_all();   // shared memory must outlive the stores that read it
   }
 
   // ---------------- split K: reduce across the cluster through distributed shared memory ----------------
@@ -497,13 +541,15 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     printf("KERNEL block0 globaltimer start %lld end %lld (ns) dur %lld | cycles: entry 0 setup_done %lld first_prod %lld exit %lld | units/CTA~%d splits %d num_kb %d bn %d stages %d\n",
            marks[0], (long long)g, (long long)g - marks[0], marks[2] - marks[1], trace[0][0] - marks[1], clock64() - marks[1],
            (p.num_units + (int)gridDim.x - 1) / (int)gridDim.x, p.splits, p.num_kb, p.bn, p.stages);
-    printf("split phase: before cluster sync %lld after %lld warp2 reduce done %lld after 2nd sync %lld (cycles since entry)\n",
+    if (p.splits > 1) printf("split phase: before cluster sync %lld after %lld warp2 reduce done %lld after 2nd sync %lld (cycles since entry)\n",
            marks[3] - marks[1], marks[4] - marks[1], marks[5] - marks[1], marks[6] - marks[1]);
     const long long t0 = trace[0][0];
     for (int i = 0; i < 160 && i < p.num_kb * 3; ++i)
       printf("slab %3d  prod_wait_done %7lld issued %7lld | mma_full %7lld committed %7lld\n", i, trace[0][i] - t0,
              trace[1][i] - t0, trace[2][i] - t0, trace[3][i] - t0);
-    for (int i = 0; i < 3; ++i) printf("tile %d epilogue start %7lld end %7lld\n", i, trace[4][i] - t0, trace[5][i] - t0);
+    printf("epilogue stamps (tile ready, then per chunk: loaded, transposed, computed, stored; then accumulator released):");
+    for (int i = 0; i < 20; ++i) printf(" %lld", trace[4][i] - t0);
+    printf("\n");
   }
 #endif
   if (abort_flag && threadIdx.x == 0) {
@@ -538,6 +584,7 @@ __global__ void __launch_bounds__(256) cvt_bf16_kernel(const float* __restrict__
 
 struct TcState {
   CUtensorMap map_a, map_b;
+  CUtensorMap map_out, map_out16;   // bulk-store maps of the output and of its bf16 mirror (store_mode 1)
   TcParams params;
   size_t smem_bytes = 0;
   dim3 grid;
@@ -710,6 +757,19 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
                       : encode_map(&st->map_b, st->bf16, b_base, b_cols, b_rows, k.batch, b_row, b_batch, p.b_kmajor ? slab_k : chunk_n,
                                    p.b_kmajor ? bn : slab_k, !st->bf16 && !p.b_kmajor)))
     return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
+  // Bulk tensor stores need a column-contiguous output with 16-byte aligned base and strides (and the
+  // same of the bf16 mirror when there is one); anything else keeps the ordinary stores.
+  {
+    const DevOperand& O = k.ops[k.chain.out_slot];
+    bool ok = d.cfg[7] != 1 && O.stride[2] == 1 && O.stride[1] % 4 == 0 && O.stride[1] >= k.N && aligned16(O.ptr) &&
+              (k.batch == 1 || (O.stride[0] % 4 == 0 && O.stride[0] > 0));
+    if (ok && p.out16 != nullptr) ok = O.stride[1] % 8 == 0 && (k.batch == 1 || O.stride[0] % 8 == 0) && aligned16(p.out16);
+    st->map_out = st->map_a;
+    st->map_out16 = st->map_a;
+    if (ok) ok = encode_map_plain(&st->map_out, false, O.ptr, k.N, k.M, k.batch, O.stride[1], O.stride[0], 32, 32);
+    if (ok && p.out16 != nullptr) ok = encode_map_plain(&st->map_out16, true, p.out16, k.N, k.M, k.batch, O.stride[1], O.stride[0], 32, 32);
+    p.store_mode = ok ? 1 : 0;
+  }
   // The attribute is per function, not per launch: always ask for the ceiling, so that plans with
   // different tile configurations can coexist in one process.
   cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem)
@@ -749,8 +809,8 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = st->params.splits > 1 ? 1 : 0;
-  if (st->bf16) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<true>, st->map_a, st->map_b, st->params));
-  else KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false>, st->map_a, st->map_b, st->params));
+  if (st->bf16) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<true>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
+  else KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }
@@ -894,7 +954,8 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   dim3 grid((unsigned)(p.num_tiles < sms ? p.num_tiles : sms), 1, 1);
-  mm_tc_kernel<true><<<grid, kThreads, smem, s>>>(map_a, map_b, p);
+  p.store_mode = 0;   // ordinary stores: the two store maps are unused placeholders
+  mm_tc_kernel<true><<<grid, kThreads, smem, s>>>(map_a, map_b, map_a, map_a, p);
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }

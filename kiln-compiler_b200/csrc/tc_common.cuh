@@ -47,8 +47,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-// Shared-memory matrix descriptor.  layout: 2 = 128-byte swizzle of 16-byte units, 1 = 128-byte
-// swizzle of 32-byte units (the only swizzled layout an N-major 32-bit operand may use).
+// Bulk tensor store shared -> global of one box (bulk async-group completion).  The part of the box
+// that lies outside the tensor is not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All earlier store groups of this thread have finished READING shared memory (it may be rewritten).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All earlier store groups of this thread are complete.
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Makes this thread's shared-memory writes visible to the async proxy (TMA) before a store is issued.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -218,6 +231,24 @@ inline bool encode_map4(CUtensorMap* map, bool bf16, const void* base, int chunk
                   dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// An un-swizzled 3-D map over [batch, rows, cols] (cols contiguous) for bulk stores of
+// (box_cols x box_rows) blocks that sit row-major and dense in shared memory.
+inline bool encode_map_plain(CUtensorMap* map, bool bf16, const void* base, int64_t cols, int64_t rows, int64_t batch,
+                             int64_t row_stride_elems, int64_t batch_stride_elems, int box_cols, int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const int esz = bf16 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * esz, (cuuint64_t)(batch > 1 ? batch_stride_elems : row_stride_elems * rows) * esz};
+  if (strides[1] == 0) strides[1] = strides[0] * rows;
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base),
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 

@@ -147,6 +147,21 @@ def test_wrong_shape_and_memory_errors(monkeypatch):
         build_executable("gpt2_block_t128")
 
 
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("case", ["gpt2_block_t128", "odd_k", "wide_bmm", "tf32_linear", "transformer_block", "erf_gelu_mlp"])
+def test_bulk_tensor_stores_equal_plain_stores(case, precision, monkeypatch):
+    """The tensor-core matmul's epilogue writes through bulk tensor stores where the output allows it
+    and through ordinary stores otherwise: the same arithmetic, so the same bits."""
+    from gpu_helpers import build_executable, run_case
+
+    monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")   # keep every planned matmul on the GPU's kernel list
+    names = [n for n in build_executable(case, precision).kernel_names if "matmul" in n]
+    _, bulk, _ = run_case(case, precision)
+    _, plain, _ = run_case(case, precision, configs={n.split("_")[0]: {"stores": "plain"} for n in names})
+    for a, b in zip(bulk, plain):
+        assert np.array_equal(a, b), (case, precision)
+
+
 def test_hot_path_kernels_are_the_specialised_ones():
     from gpu_helpers import build_executable
 
