@@ -132,6 +132,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const int q0 = qt * kRows;
   const int n_kv = qt + 1;                           // causal: key tiles 0..qt
 
+  if (threadIdx.x == 32) {
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(q_full, 1);

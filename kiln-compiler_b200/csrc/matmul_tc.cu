@@ -48,6 +48,7 @@ constexpr int kThreads = 64 + 32 * kEpiWarps;      // producer warp, MMA warp, e
 constexpr int kEpiStage16Offset = 4352;
 constexpr int kEpiWarpBytes = kEpiStage16Offset + 32 * 32 * 2;
 constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
+constexpr int kEpiSlotBytes = 4096 + 2048;   // one float block + one bf16 block of the rotating staging slots
 #ifdef KB200_TRACE
 constexpr int kMaxDynamicSmem = 200 * 1024;   // the trace arrays take static shared memory
 #else
@@ -78,8 +79,37 @@ struct TcParams {
   int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
   int num_units;        // num_tiles * splits
   int store_mode;       // 0: the epilogue warps store with ordinary global stores; 1: bulk tensor stores from shared memory
+  int n_chunks;         // bn / chunk_n
+  int tiles_per_batch;  // tiles_m * tiles_n
+  uint64_t magic_tn, magic_tpb;   // ceil(2^40 / tiles_n), ceil(2^40 / tiles_per_batch): division by multiplication
   MatmulParams mm;      // shapes, operands, the epilogue chain (epilogue warps only)
 };
+
+// x / d for x, d < 2^20 with magic = ceil(2^40 / d): a lone thread pays ~100 cycles for a real division.
+__device__ __forceinline__ int fast_div(int x, uint64_t magic) { return (int)(((uint64_t)(uint32_t)x * magic) >> 40); }
+
+// Work unit -> (K split, batch entry, tile row, tile column).
+__device__ __forceinline__ void unit_coords(const TcParams& p, int unit, int& tile, int& ks, int& batch, int& tm, int& tn) {
+  tile = unit;
+  ks = 0;
+  if (p.splits > 1) {
+    tile = unit / p.splits;
+    ks = unit - tile * p.splits;
+  }
+  batch = fast_div(tile, p.magic_tpb);
+  const int rem = tile - batch * p.tiles_per_batch;
+  tm = fast_div(rem, p.magic_tn);
+  tn = rem - tm * p.tiles_n;
+}
+// K slabs [begin, end) of split `ks`.
+__device__ __forceinline__ void slab_range(const TcParams& p, int ks, int& begin, int& end) {
+  begin = 0;
+  end = p.num_kb;
+  if (p.splits > 1) {
+    begin = ks * p.num_kb / p.splits;
+    end = (ks + 1) * p.num_kb / p.splits;
+  }
+}
 
 // Reduced-precision modes only: exp through ex2.approx and division through rcp.approx (relative
 // error ~1e-6, far inside the 2e-3 / 2e-2 budgets of TF32 / BF16 operands).  The closed forms stay
@@ -154,14 +184,21 @@ __device__ __forceinline__ void load_side32(const TcParams& p, int s, float (&si
 // Two operands of the chain are fetched ahead of the accumulator (their L2 latency then overlaps
 // the main loop, the TMEM load and the previous block's stores): the first per-column operand
 // (a bias: one value per lane) and the first full-matrix operand (a residual or a mask).
-__device__ __forceinline__ void prefetch_sides(const TcParams& p, float& pre_col, float (&pre_mat)[32], int64_t b,
-                                               int64_t m_first, int64_t n, int row_limit = 32) {
+__device__ __forceinline__ void prefetch_col(const TcParams& p, float& pre_col, int64_t b, int64_t n) {
   const MatmulParams& mm = p.mm;
   if (p.pre_col_step >= 0) {
     const DevOperand& o = mm.ops[mm.chain.steps[p.pre_col_step].slot];
     pre_col = (n < mm.N) ? __ldg(o.ptr + b * o.stride[0] + n * o.stride[2]) : 0.0f;
   }
+}
+__device__ __forceinline__ void prefetch_mat(const TcParams& p, float (&pre_mat)[32], int64_t b, int64_t m_first, int64_t n,
+                                             int row_limit = 32) {
   if (p.pre_mat_step >= 0) load_side32(p, p.pre_mat_step, pre_mat, b, m_first, n, row_limit);
+}
+__device__ __forceinline__ void prefetch_sides(const TcParams& p, float& pre_col, float (&pre_mat)[32], int64_t b,
+                                               int64_t m_first, int64_t n, int row_limit = 32) {
+  prefetch_col(p, pre_col, b, n);
+  prefetch_mat(p, pre_mat, b, m_first, n, row_limit);
 }
 
 __device__ __forceinline__ void epilogue_compute32(const TcParams& p, float (&x)[32], float pre_col, const float (&pre_mat)[32],
@@ -246,16 +283,19 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
   const uint32_t tfull0 = smem_u32(&bars[2 * kMaxStages]), tempty0 = smem_u32(&bars[2 * kMaxStages + 2]);
 
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, 1);
+  if (threadIdx.x == 32) {
+    // descriptor fetches overlap the set-up below instead of delaying the first copy
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+    if (p.store_mode == 1) {
+      prefetch_tensormap(&tma_out);
+      if (p.out16 != nullptr) prefetch_tensormap(&tma_out16);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(tfull0 + 8 * a, 1);
-      mbar_init(tempty0 + 8 * a, kEpiWarps);
-    }
+  }
+  if (warp == 0) {
+    // one barrier per lane: full[0..7] | empty[0..7] | tfull[0..1] | tempty[0..1]
+    if (lane == 0) abort_flag = 0;
+    if (lane < 2 * kMaxStages + 4) mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -269,7 +309,6 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
-  const int tiles_per_batch = p.tiles_m * p.tiles_n;
 #ifdef KB200_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) marks[2] = clock64();
 #endif
@@ -279,22 +318,20 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     if (lane == 0) {
       // everything the loop needs in registers: a lone thread pays full latency for every
       // dependent instruction, so the per-slab instruction count is what bounds the issue rate
-      const int stages = p.stages, num_kb = p.num_kb, splits = p.splits, num_units = p.num_units, slab_k = p.slab_k;
-      const int tiles_n = p.tiles_n, bn = p.bn, chunk_n = p.chunk_n, b_mode = p.b_mode;
-      const int n_chunks = bn / chunk_n;
+      const int stages = p.stages, num_units = p.num_units, slab_k = p.slab_k;
+      const int bn = p.bn, chunk_n = p.chunk_n, b_mode = p.b_mode, n_chunks = p.n_chunks;
       const uint32_t chunk_bytes = (uint32_t)slab_k * kSlabBytes;
       const uint32_t tx_bytes = (uint32_t)stage_bytes;
       int s = 0;
       uint32_t wait_parity = 1;                // parity to wait for on the empty barriers of this pass over the ring
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-        const int tile = unit / splits, ks = unit - tile * splits;
-        const int batch = tile / tiles_per_batch, rem = tile - batch * tiles_per_batch;
-        const int tm_i = rem / tiles_n;
-        const int m0 = tm_i * kTileM, n0 = (rem - tm_i * tiles_n) * bn;
-        const int kb_end = (ks + 1) * num_kb / splits;
-        int k_elem = (ks * num_kb / splits) * slab_k;
-        for (int kb = ks * num_kb / splits; kb < kb_end; ++kb, k_elem += slab_k) {
+        int tile, ks, batch, tm_i, tn_i, kb_begin, kb_end;
+        unit_coords(p, unit, tile, ks, batch, tm_i, tn_i);
+        slab_range(p, ks, kb_begin, kb_end);
+        const int m0 = tm_i * kTileM, n0 = tn_i * bn;
+        int k_elem = kb_begin * slab_k;
+        for (int kb = kb_begin; kb < kb_end; ++kb, k_elem += slab_k) {
           const uint32_t full = full0 + 8 * s;
           if (!mbar_wait(empty0 + 8 * s, wait_parity, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 1); *abort_ptr = 1; }
@@ -324,7 +361,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const int stages = p.stages, num_kb = p.num_kb, splits = p.splits, num_units = p.num_units, bn = p.bn;
+      const int stages = p.stages, splits = p.splits, num_units = p.num_units, bn = p.bn;
       const uint32_t idesc = p.idesc;
       // descriptors: everything but the 14-bit start address is fixed; advancing along K adds to it
       const uint64_t a_fixed = make_desc(0, 16, 1024);
@@ -337,8 +374,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       uint32_t wait_parity = 0;
       int i = 0;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++i) {
-        const int ks = unit % splits;
-        const int kb_begin = ks * num_kb / splits, kb_end = (ks + 1) * num_kb / splits;
+        const int ks = splits > 1 ? unit % splits : 0;
+        int kb_begin, kb_end;
+        slab_range(p, ks, kb_begin, kb_end);
         const int acc = i & 1;
         const uint32_t aph = (i >> 1) & 1;
         // the epilogue must have drained this accumulator (two tiles ago) before it is overwritten
@@ -389,37 +427,53 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     int i = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
-      const int tile = unit / p.splits, ks = unit - tile * p.splits;
+      int tile, ks, batch, tm_i, tn_i;
+      unit_coords(p, unit, tile, ks, batch, tm_i, tn_i);
       const int acc = i & 1;
       const uint32_t aph = (i >> 1) & 1;
-      const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-      const int64_t m0 = (int64_t)(rem / p.tiles_n) * kTileM, n0 = (int64_t)(rem % p.tiles_n) * p.bn;
+      const int64_t m0 = (int64_t)tm_i * kTileM, n0 = (int64_t)tn_i * p.bn;
       const int64_t m_first = m0 + quad * 32;
       const bool direct = p.splits == 1;
+      // three staging slots per warp fit in the ring, and no later tile of this CTA will refill it
+      const bool ring_staging = bulk && unit + (int)gridDim.x >= p.num_units && p.stages * stage_bytes >= kEpiWarps * 3 * kEpiSlotBytes;
+      uint8_t* ring_slice = smem_raw + (tiles - raw) + (size_t)e * (3 * kEpiSlotBytes);
+      int slot_i = 0;
       float pre_col = 0.0f, pre_mat[32];
       if (direct && n0 + half * 32 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + half * 32 + lane);
-      bool got = mbar_wait(tfull0 + 8 * acc, aph, abort_ptr);
-      if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
-      ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
-      if (!ok) break;
-#ifdef KB200_TRACE
-      if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
-#endif
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // this warp's share of the tile: rows quad*32..+31, column chunks half*32, +64, ...
       // split K: the partial tile goes into this CTA's (now idle) pipeline memory, row-major [128][bn]
       float* part = reinterpret_cast<float*>(smem_raw + (tiles - raw)) + (size_t)(quad * 32) * p.bn;
-      for (int c = half * 32; c < p.bn; c += 64) {
-        if (n0 + c >= p.mm.N || (p.debug & 16)) break;   // uniform across the warp
+      // Before its first tile is ready a CTA has nothing for these warps to do, and their code (the
+      // unrolled chain, some kilobytes) is not in the instruction cache yet: one dry pass of the loop
+      // body over zeros, with nothing stored, takes those misses off the critical path.
+      const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32);
+      for (int c = half * 32 - (dry_pass ? 64 : 0); c < p.bn; c += 64) {
+        const bool dry = c < 0;
+        if (c == half * 32) {
+          bool got = mbar_wait(tfull0 + 8 * acc, aph, abort_ptr);
+          if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
+          ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
+          if (!ok) break;
+#ifdef KB200_TRACE
+          if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+#endif
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        if (!dry && (n0 + c >= p.mm.N || (p.debug & 16))) break;   // uniform across the warp
         float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
-        if (bulk) {
+        if (dry) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+        } else {
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
+        }
+        if (bulk && !ring_staging) {
           // the bulk stores of the previous block must have read the staging memory before it is rewritten
           if (lane == 0) tma_store_wait_read();
           __syncwarp();
         }
 #ifdef KB200_TRACE
-        if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+        if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
         // transpose through shared memory: lane = row  ->  lane = column
 #pragma unroll
@@ -429,35 +483,55 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         for (int r = 0; r < 32; ++r) v[r] = tbuf[r * 33 + lane];
         __syncwarp();
 #ifdef KB200_TRACE
-        if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+        if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
         if (direct) {
-          epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + c + lane);
+          // The next block's operands are fetched where their latency hides and no fence waits on them:
+          // the per-column value before this block's arithmetic, the matrix operand (whose registers
+          // are busy until then) after this block's stores have been issued.
+          const bool more = !dry && c + 64 < p.bn && n0 + c + 64 < p.mm.N;
+          float next_col = pre_col;
+          if (more) prefetch_col(p, next_col, batch, n0 + c + 64 + lane);
+          epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + (dry ? half * 32 : c) + lane);
+          pre_col = next_col;
 #ifdef KB200_TRACE
-          if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+          if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
-          if (c + 64 < p.bn && n0 + c + 64 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + c + 64 + lane);
+          if (more && !bulk) prefetch_mat(p, pre_mat, batch, m_first, n0 + c + 64 + lane);
           if (bulk) {
             // dense row-major 32 x 32 blocks in shared memory, then one bulk tensor store each: the
             // store engine writes whole 128-byte lines and clips the block at the matrix edges
+            float* sf = tbuf;
+            __nv_bfloat16* sh = stage16;
+            if (ring_staging && !dry) {
+              // last tile of this CTA: the operand ring is idle, so the staging blocks rotate through
+              // this warp's slice of it and a store drains while the next blocks are computed
+              uint8_t* slot = ring_slice + (size_t)slot_i * kEpiSlotBytes;
+              slot_i = slot_i == 2 ? 0 : slot_i + 1;
+              sf = reinterpret_cast<float*>(slot);
+              sh = reinterpret_cast<__nv_bfloat16*>(slot + 4096);
+              if (lane == 0) tma_store_wait_read2();
+              __syncwarp();
+            }
 #pragma unroll
-            for (int r = 0; r < 32; ++r) tbuf[r * 32 + lane] = v[r];
+            for (int r = 0; r < 32; ++r) sf[r * 32 + lane] = v[r];
             if (p.out16 != nullptr) {
 #pragma unroll
-              for (int r = 0; r < 32; ++r) stage16[r * 32 + lane] = __float2bfloat16_rn(v[r]);
+              for (int r = 0; r < 32; ++r) sh[r * 32 + lane] = __float2bfloat16_rn(v[r]);
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0 && m_first < p.mm.M && !(p.debug & 1)) {
-              tma_store_3d(&tma_out, smem_u32(tbuf), (int)(n0 + c), (int)m_first, batch);
-              if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(stage16), (int)(n0 + c), (int)m_first, batch);
+            if (lane == 0 && m_first < p.mm.M && !(p.debug & 1) && !dry) {
+              tma_store_3d(&tma_out, smem_u32(sf), (int)(n0 + c), (int)m_first, batch);
+              if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(sh), (int)(n0 + c), (int)m_first, batch);
               tma_store_commit();
             }
+            if (more) prefetch_mat(p, pre_mat, batch, m_first, n0 + c + 64 + lane);
           } else {
             epilogue_store32(p, v, batch, m_first, n0 + c + lane);
           }
 #ifdef KB200_TRACE
-          if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
+          if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
         } else {
 #pragma unroll
@@ -472,7 +546,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       if (warp == 2 && lane == 0) { KB200_STAMP(4, te); ++te; }
 #endif
     }
-    if (bulk && lane == 0) tma_store_wait_all();   // shared memory must outlive the stores that read it
+    if (bulk && lane == 0) tma_store_wait_read();   // shared memory must outlive the stores that read it
   }
 
   // ---------------- split K: reduce across the cluster through distributed shared memory ----------------
@@ -494,9 +568,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       uint32_t rank;
       asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
       const int unit = blockIdx.x;
-      const int tile = unit / p.splits;
-      const int batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-      const int64_t m0 = (int64_t)(rem / p.tiles_n) * kTileM, n0 = (int64_t)(rem % p.tiles_n) * p.bn;
+      int tile, ks_unused, batch, tm_i, tn_i;
+      unit_coords(p, unit, tile, ks_unused, batch, tm_i, tn_i);
+      const int64_t m0 = (int64_t)tm_i * kTileM, n0 = (int64_t)tn_i * p.bn;
       const int row_lo = (int)rank * kTileM / p.splits, row_hi = ((int)rank + 1) * kTileM / p.splits;
       const int col_blocks = p.bn / 32;
       const int n_blocks = ((row_hi - row_lo + 31) / 32) * col_blocks;
@@ -609,6 +683,8 @@ bool tc_eligible(const PlanKernel& k) {
   const DevOperand& A = k.ops[d.a_slot];
   const DevOperand& B = k.ops[d.b_slot];
   if (k.M < 32 || k.N < 64 || k.K < 64) return false;
+  // tile indices are divided by multiplication, exact below 2^20 tiles (and every TMA coordinate fits an int)
+  if (((k.M + 127) / 128) * ((k.N + 63) / 64) * k.batch >= (int64_t(1) << 20)) return false;
   if (k.N % 4 || k.K % 4) return false;
   if (d.precision == KB200_PREC_BF16 && (k.N % 8 || k.K % 8)) return false;
   // A: K contiguous; B: N contiguous or K contiguous; 16-byte aligned bases and strides
@@ -673,6 +749,10 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.tiles_m = (int)((k.M + kTileM - 1) / kTileM);
   p.tiles_n = (int)((k.N + bn - 1) / bn);
   p.num_tiles = p.tiles_m * p.tiles_n * (int)k.batch;
+  p.n_chunks = bn / chunk_n;
+  p.tiles_per_batch = p.tiles_m * p.tiles_n;
+  p.magic_tn = ((uint64_t(1) << 40) + p.tiles_n - 1) / p.tiles_n;
+  p.magic_tpb = ((uint64_t(1) << 40) + p.tiles_per_batch - 1) / p.tiles_per_batch;
   // Split K when the tiles alone would leave most SMs idle (128-token projections, the narrow
   // 768-wide layers): every SM then streams a share of the operands.
   int splits = d.cfg[4];
@@ -927,6 +1007,10 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.tiles_m = (int)((m + kTileM - 1) / kTileM);
   p.tiles_n = (int)((n + bn - 1) / bn);
   p.num_tiles = p.tiles_m * p.tiles_n;
+  p.n_chunks = bn / chunk_n;
+  p.tiles_per_batch = p.num_tiles;
+  p.magic_tn = ((uint64_t(1) << 40) + p.tiles_n - 1) / p.tiles_n;
+  p.magic_tpb = ((uint64_t(1) << 40) + p.tiles_per_batch - 1) / p.tiles_per_batch;
   p.splits = 1;
   p.num_units = p.num_tiles;
   p.pre_col_step = p.pre_mat_step = -1;
