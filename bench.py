@@ -231,6 +231,14 @@ def kernel_flops(kernel):
     return flops, byts
 
 
+# DRAM bytes (read + write) per launch of the 1024-token block's kernels in BF16 mode, from the
+# `ncu --set full` capture summarised in profiles/gpt2_block_t1024_bf16_launches_and_top_kernels.md.
+NCU_DRAM_BYTES = {
+    ("bf16", "k0_row"): 3.16e6, ("bf16", "k1_matmul"): 5.21e6, ("bf16", "k2_ew0"): 9.50e6, ("bf16", "k7_matmul"): 5.99e6,
+    ("bf16", "k8_row"): 3.16e6, ("bf16", "k9_matmul"): 6.40e6, ("bf16", "k10_matmul"): 14.25e6,
+}
+
+
 def roofline_of(exe, plan, precision, iters=20):
     """Per-launch CUDA-event times of every kernel; roofline of the one with the largest share."""
     pk, pk_kind = peaks()
@@ -249,7 +257,8 @@ def roofline_of(exe, plan, precision, iters=20):
     else:
         achieved, unit, bound, peak, peak_note = byts / (ms * 1e-3) / 1e9, "GB/s", "hbm", pk["hbm_gbs"], f"{pk_kind} copy"
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-            "traffic": None, "kernel": f"{name} ({exe.impls[i]})", "ms_per_launch": ms, "share": ms / total,
+            "traffic": NCU_DRAM_BYTES.get((precision, name)) if TOKENS == 1024 else None,
+            "traffic_unit": "bytes per launch (ncu dram read + write)", "kernel": f"{name} ({exe.impls[i]})", "ms_per_launch": ms, "share": ms / total,
             "peak_source": peak_note,
             "per_kernel_ms": {n: round(t, 5) for n, t in times}}
 
