@@ -144,8 +144,8 @@ def cpu_block_tokens_per_s(seconds_budget=12.0, threads=None):
     from kiln_b200 import workloads as W
     from oracle.torch_block import block_forward, to_torch
 
-    if threads:
-        torch.set_num_threads(threads)
+    # every core this process may run on, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+    torch.set_num_threads(threads or len(os.sched_getaffinity(0)))
     p = to_torch(W.block_params(SEED, TOKENS))
     xs = [torch.from_numpy(W.block_input(SEED, TOKENS, index=i)) for i in range(2)]
     with torch.no_grad():
@@ -173,7 +173,7 @@ def reference_arm(args, dist, rank):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": SEQS * TOKENS / value * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config("fp32", 1),
+        "config": dict(workload_config(args.precision, args.gpus), cpu_arithmetic="f32, one process on rank 0's host cores"),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
