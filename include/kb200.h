@@ -133,7 +133,8 @@ typedef struct kb200_kernel_desc {
    * cfg[0] tile M, cfg[1] tile N, cfg[2] tile K, cfg[3] pipeline stages,
    * cfg[4] split-K factor, cfg[5] implementation override (0 = library picks),
    * cfg[6] reserved, cfg[7] epilogue stores of the tensor-core matmul (0 = library picks,
-   * 1 = ordinary global stores, never bulk tensor stores), all 0 = library default. */
+   * 1 = ordinary global stores, never bulk tensor stores, 2 = bulk stores but always the
+   * transposing lane-per-column epilogue), all 0 = library default. */
   int32_t cfg[8];
   char name[32];       /* the Kiln kernel it comes from, e.g. "k3" (diagnostics only) */
 } kb200_kernel_desc;

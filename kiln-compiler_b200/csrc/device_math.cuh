@@ -1,6 +1,8 @@
 // Scalar math of the fused kernels.  The closed forms are the ones the reference's generated
 // kernels use (kiln/gpu/codegen.py:53-88): tanh through exp(-2|x|), erf by Abramowitz & Stegun
-// 7.1.26, GELU in tanh or erf form.  Everything is IEEE float32 (no fast-math intrinsics): the
+// 7.1.26, GELU in tanh or erf form.  Inside those forms exp and the division are the hardware
+// approximations (ex2.approx, rcp.approx: relative error ~2^-22), which is also what the
+// reference's `tl.exp` and `/` lower to; explicit DIV / EXP / SQRT ops of a graph stay IEEE.  The
 // FP32 mode has to stay within 1e-5 of a float64 evaluation.
 #pragma once
 
@@ -12,18 +14,18 @@
 namespace kb200 {
 
 __device__ __forceinline__ float d_tanh(float x) {
-  float e = expf(-2.0f * fabsf(x));
-  float t = (1.0f - e) / (1.0f + e);
+  float e = __expf(-2.0f * fabsf(x));
+  float t = __fdividef(1.0f - e, 1.0f + e);
   return x < 0.0f ? -t : t;
 }
 
-__device__ __forceinline__ float d_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float d_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float d_erf(float x) {
   float a = fabsf(x);
-  float t = 1.0f / (1.0f + 0.3275911f * a);
+  float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
   float p = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
-  float y = 1.0f - p * expf(-a * a);
+  float y = 1.0f - p * __expf(-a * a);
   return x < 0.0f ? -y : y;
 }
 
@@ -82,6 +84,37 @@ __device__ __forceinline__ float apply_chain(int op, float v, float s) {
     case CH_SQRT: return sqrtf(v);
     default: return v;
   }
+}
+
+// One chain step on N register-resident values: the switch is outside the element loop and every
+// index is a compile-time constant, so v[] and side[] stay in registers and the N independent
+// elements give the instruction-level parallelism.
+template <int N>
+__device__ __forceinline__ void chain_step(int op, float (&v)[N], const float (&side)[N]) {
+#define KB200_EACH(expr)                  \
+  _Pragma("unroll") for (int j = 0; j < N; ++j) { const float x = v[j]; const float s = side[j]; (void)s; v[j] = (expr); }
+  switch (op) {
+    case CH_ADD: KB200_EACH(x + s) break;
+    case CH_SUB: KB200_EACH(x - s) break;
+    case CH_RSUB: KB200_EACH(s - x) break;
+    case CH_MUL: KB200_EACH(x * s) break;
+    case CH_DIV: KB200_EACH(x / s) break;
+    case CH_RDIV: KB200_EACH(s / x) break;
+    case CH_MAX: KB200_EACH(d_max(x, s)) break;
+    case CH_MIN: KB200_EACH(d_min(x, s)) break;
+    case CH_NEG: KB200_EACH(-x) break;
+    case CH_RELU: KB200_EACH(d_max(x, 0.0f)) break;
+    case CH_EXP: KB200_EACH(expf(x)) break;
+    case CH_TANH: KB200_EACH(d_tanh(x)) break;
+    case CH_SIGMOID: KB200_EACH(d_sigmoid(x)) break;
+    case CH_ERF: KB200_EACH(d_erf(x)) break;
+    case CH_GELU_TANH: KB200_EACH(d_gelu_tanh(x)) break;
+    case CH_GELU_ERF: KB200_EACH(d_gelu_erf(x)) break;
+    case CH_RSQRT: KB200_EACH(1.0f / sqrtf(x)) break;
+    case CH_SQRT: KB200_EACH(sqrtf(x)) break;
+    default: break;
+  }
+#undef KB200_EACH
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

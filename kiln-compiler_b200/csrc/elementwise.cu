@@ -50,67 +50,76 @@ __global__ void __launch_bounds__(256) ew_generic_kernel(const __grid_constant__
 constexpr int kVecRank = 4;
 
 struct EwChainParams {
-  int rank;                      // <= kVecRank; last dim counted in float4
-  int64_t nvec;
-  int64_t shape[kVecRank];       // last entry = inner / 4
-  DevOperand ops[KB200_MAX_OPERANDS];   // strides in elements; inner stride is 1 (vector) or 0 (scalar)
+  uint32_t nvec;
+  uint32_t shape[kVecRank];      // last entry = inner / 4
+  float* ptr[KB200_MAX_OPERANDS];
+  // element strides as 32-bit numbers (the host takes this kernel only when every offset fits),
+  // the innermost one already multiplied by 4: 4 (a float4 per index) or 0 (one scalar per row)
+  int32_t stride[KB200_MAX_OPERANDS][kVecRank];
   Chain chain;
 };
 
-__device__ __forceinline__ int64_t ew_offset(const EwChainParams& p, int slot, const int64_t* idx) {
-  int64_t off = 0;
+template <int RANK>
+__device__ __forceinline__ uint32_t ew_offset(const EwChainParams& p, int slot, const uint32_t* idx) {
+  uint32_t off = 0;
 #pragma unroll
-  for (int d = 0; d < kVecRank; ++d)
-    if (d < p.rank) off += idx[d] * p.ops[slot].stride[d] * (d == p.rank - 1 ? 4 : 1);
+  for (int d = 0; d < RANK; ++d) off += idx[d] * (uint32_t)p.stride[slot][d];
   return off;
 }
 
-__device__ __forceinline__ float4 ew_load4(const EwChainParams& p, int slot, const int64_t* idx) {
-  const float* ptr = p.ops[slot].ptr + ew_offset(p, slot, idx);
-  if (p.ops[slot].stride[p.rank - 1] == 0) {
+template <int RANK>
+__device__ __forceinline__ float4 ew_load4(const EwChainParams& p, int slot, const uint32_t* idx) {
+  const float* ptr = p.ptr[slot] + ew_offset<RANK>(p, slot, idx);
+  if (p.stride[slot][RANK - 1] == 0) {
     float s = __ldg(ptr);
     return make_float4(s, s, s, s);
   }
   return *reinterpret_cast<const float4*>(ptr);
 }
 
-template <int U>
+// U float4 per thread, a block's vectors contiguous per u (coalesced).  The rank is a template
+// parameter and all index arithmetic is 32-bit: at 8 bytes moved per element the kernel must stay
+// far below the instruction budget of the memory system (a generic 64-bit version of the same loop
+// spent 75 instructions per element and ran at a third of the copy bandwidth).
+template <int RANK, int U>
 __global__ void __launch_bounds__(256) ew_chain_vec4_kernel(const __grid_constant__ EwChainParams p) {
-  const int64_t step = (int64_t)gridDim.x * blockDim.x * U;
-  for (int64_t base = (int64_t)blockIdx.x * blockDim.x * U + threadIdx.x; base < p.nvec; base += step) {
-    float4 v[U];
-    int64_t idx[U][kVecRank];
+  const uint32_t nvec = p.nvec;
+  const uint32_t step = gridDim.x * blockDim.x * U;
+  for (uint32_t base = blockIdx.x * blockDim.x * U + threadIdx.x; base < nvec; base += step) {
+    float v[4 * U];
+    uint32_t idx[U][RANK];
     bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      int64_t i = base + (int64_t)u * blockDim.x;
-      live[u] = i < p.nvec;
-      int64_t rest = live[u] ? i : 0;
+      const uint32_t i = base + (uint32_t)u * blockDim.x;
+      live[u] = i < nvec;
+      uint32_t rest = live[u] ? i : 0;
 #pragma unroll
-      for (int d = kVecRank - 1; d >= 0; --d) {
-        if (d < p.rank) {
-          idx[u][d] = rest % p.shape[d];
-          rest /= p.shape[d];
-        } else {
-          idx[u][d] = 0;
-        }
+      for (int d = RANK - 1; d > 0; --d) {
+        const uint32_t q = rest / p.shape[d];
+        idx[u][d] = rest - q * p.shape[d];
+        rest = q;
       }
-      if (live[u]) v[u] = ew_load4(p, p.chain.first_slot, idx[u]);
+      idx[u][0] = rest;
+      const float4 x = live[u] ? ew_load4<RANK>(p, p.chain.first_slot, idx[u]) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[4 * u] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
+    }
+    for (int s = 0; s < p.chain.n; ++s) {
+      const ChainStep st = p.chain.steps[s];
+      float side[4 * U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float4 x = make_float4(st.imm, st.imm, st.imm, st.imm);
+        if (st.slot >= 0 && live[u]) x = ew_load4<RANK>(p, st.slot, idx[u]);
+        side[4 * u] = x.x; side[4 * u + 1] = x.y; side[4 * u + 2] = x.z; side[4 * u + 3] = x.w;
+      }
+      chain_step<4 * U>(st.op, v, side);
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!live[u]) continue;
-      for (int s = 0; s < p.chain.n; ++s) {
-        const ChainStep st = p.chain.steps[s];
-        float4 side = make_float4(st.imm, st.imm, st.imm, st.imm);
-        if (st.slot >= 0) side = ew_load4(p, st.slot, idx[u]);
-        v[u].x = apply_chain(st.op, v[u].x, side.x);
-        v[u].y = apply_chain(st.op, v[u].y, side.y);
-        v[u].z = apply_chain(st.op, v[u].z, side.z);
-        v[u].w = apply_chain(st.op, v[u].w, side.w);
-      }
-      *reinterpret_cast<float4*>(p.ops[p.chain.out_slot].ptr + ew_offset(p, p.chain.out_slot, idx[u])) = v[u];
-    }
+    for (int u = 0; u < U; ++u)
+      if (live[u])
+        *reinterpret_cast<float4*>(p.ptr[p.chain.out_slot] + ew_offset<RANK>(p, p.chain.out_slot, idx[u])) =
+            make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
   }
 }
 
@@ -210,10 +219,18 @@ int choose_elementwise(Plan& plan, PlanKernel& k) {
   const int last = d.iter_rank - 1;
   const int64_t inner = d.iter_shape[last];
   // vec4: every operand contiguous or constant along the innermost dim, everything 16-byte aligned
-  bool vec = inner % 4 == 0;
+  bool vec = inner % 4 == 0 && numel_of(d) / 4 < (int64_t(1) << 31);   // the kernel's indices are 32-bit
   for (int i = 0; i < n_slots && vec; ++i) {
     const DevOperand& o = k.ops[slots[i]];
     const bool is_out = slots[i] == k.chain.out_slot;
+    // every element offset (and stride) of the operand fits the kernel's 32-bit arithmetic
+    int64_t span = 0;
+    for (int dd = 0; dd <= last && vec; ++dd) {
+      if (o.stride[dd] < 0) vec = false;
+      span += (d.iter_shape[dd] - 1) * o.stride[dd];
+    }
+    if (span >= (int64_t(1) << 31)) vec = false;
+    if (!vec) break;
     if (o.stride[last] == 1) {
       vec = (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0;
       for (int dd = 0; dd < last && vec; ++dd) vec = o.stride[dd] % 4 == 0;
@@ -247,16 +264,25 @@ int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   const int64_t numel = numel_of(d);
   if (k.impl == IMPL_EW_CHAIN_VEC4) {
     EwChainParams p{};
-    p.rank = d.iter_rank;
-    for (int i = 0; i < d.iter_rank; ++i) p.shape[i] = d.iter_shape[i];
-    p.shape[d.iter_rank - 1] /= 4;
-    p.nvec = numel / 4;
-    for (int o = 0; o < d.n_operands; ++o) p.ops[o] = k.ops[o];
+    const int rank = d.iter_rank;
+    for (int i = 0; i < rank; ++i) p.shape[i] = (uint32_t)d.iter_shape[i];
+    p.shape[rank - 1] /= 4;
+    p.nvec = (uint32_t)(numel / 4);
+    for (int o = 0; o < d.n_operands; ++o) {
+      p.ptr[o] = k.ops[o].ptr;
+      for (int i = 0; i < rank; ++i) p.stride[o][i] = (int32_t)(k.ops[o].stride[i] * (i == rank - 1 ? 4 : 1));
+    }
     p.chain = k.chain;
-    constexpr int U = 2;
-    int64_t blocks = (p.nvec + 256 * U - 1) / (256 * U);
+    constexpr int U = 4;
+    int64_t blocks = ((int64_t)p.nvec + 256 * U - 1) / (256 * U);
     int64_t cap = (int64_t)plan.sm_count * 16;
-    ew_chain_vec4_kernel<U><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(p);
+    const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+    switch (rank) {
+      case 1: ew_chain_vec4_kernel<1, U><<<grid, 256, 0, s>>>(p); break;
+      case 2: ew_chain_vec4_kernel<2, U><<<grid, 256, 0, s>>>(p); break;
+      case 3: ew_chain_vec4_kernel<3, U><<<grid, 256, 0, s>>>(p); break;
+      default: ew_chain_vec4_kernel<4, U><<<grid, 256, 0, s>>>(p); break;
+    }
   } else if (k.impl == IMPL_EW_TRANSPOSE) {
     EwTransposeParams p{};
     p.rank = d.iter_rank;

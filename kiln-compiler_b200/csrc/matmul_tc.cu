@@ -45,8 +45,8 @@ constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;      // producer warp, MMA warp, epilogue warps
 // per epilogue warp: a 32 x 33 float transpose buffer, reused (as dense 32 x 32) as the staging block of
 // the bulk store, then a 32 x 32 bf16 staging block; both 128-byte aligned
-constexpr int kEpiStage16Offset = 4352;
-constexpr int kEpiWarpBytes = kEpiStage16Offset + 32 * 32 * 2;
+constexpr int kEpiStage16Offset = 4608;        // 512-byte aligned (64-byte swizzle); the float block is 1024-byte aligned
+constexpr int kEpiWarpBytes = 7168;
 constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
 constexpr int kEpiSlotBytes = 4096 + 2048;   // one float block + one bf16 block of the rotating staging slots
 #ifdef KB200_TRACE
@@ -79,6 +79,7 @@ struct TcParams {
   int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
   int num_units;        // num_tiles * splits
   int store_mode;       // 0: the epilogue warps store with ordinary global stores; 1: bulk tensor stores from shared memory
+  int epi_rowwise;      // the epilogue keeps a lane per ROW (no transpose): the chain has no matrix operand
   int n_chunks;         // bn / chunk_n
   int tiles_per_batch;  // tiles_m * tiles_n
   uint64_t magic_tn, magic_tpb;   // ceil(2^40 / tiles_n), ceil(2^40 / tiles_per_batch): division by multiplication
@@ -252,6 +253,63 @@ __device__ __forceinline__ void epilogue_store32(const TcParams& p, const float 
 #define KB200_STAMP(role, idx) do { } while (0)
 #endif
 
+// The chain on a block held a lane per ROW (v[j] = column n + j of this lane's row): every operand is
+// an immediate or one value per column, read as eight 128-bit loads from an address all lanes share.
+__device__ __forceinline__ void epilogue_compute_rows(const TcParams& p, float (&v)[32], int64_t b, int64_t n) {
+  const MatmulParams& mm = p.mm;
+  for (int s = 0; s < mm.chain.n; ++s) {
+    const ChainStep st = mm.chain.steps[s];
+    float side[32];
+    if (st.slot >= 0) {
+      const DevOperand& o = mm.ops[st.slot];
+      const float4* base = reinterpret_cast<const float4*>(o.ptr + b * o.stride[0] + n);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 t = n + 4 * q < mm.N ? __ldg(base + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        side[4 * q] = t.x; side[4 * q + 1] = t.y; side[4 * q + 2] = t.z; side[4 * q + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) side[j] = st.imm;
+    }
+    chain_step32(st.op, v, side);
+  }
+}
+
+// Staging of a 32 x 32 block for the bulk stores, in the swizzled layouts of the store maps: float
+// rows of 128 bytes with the 16-byte unit index XORed by (row & 7), bf16 rows of 64 bytes with the
+// unit index XORed by ((row >> 1) & 3).  Lane = column (x[r] = row r) ...
+__device__ __forceinline__ void stage_columns(uint8_t* sf, uint8_t* sh, const float (&x)[32], int lane, bool with16) {
+#pragma unroll
+  for (int r = 0; r < 32; ++r)
+    *reinterpret_cast<float*>(sf + r * 128 + ((((lane >> 2) ^ (r & 7)) << 4) | ((lane & 3) << 2))) = x[r];
+  if (with16) {
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+      *reinterpret_cast<__nv_bfloat16*>(sh + r * 64 + ((((lane >> 3) ^ ((r >> 1) & 3)) << 4) | ((lane & 7) << 1))) =
+          __float2bfloat16_rn(x[r]);
+  }
+}
+// ... or lane = row (v[j] = column j): 128-bit stores.
+__device__ __forceinline__ void stage_rows(uint8_t* sf, uint8_t* sh, const float (&v)[32], int lane, bool with16) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    *reinterpret_cast<float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  if (with16) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      __nv_bfloat162 w0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]), w1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+      __nv_bfloat162 w2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]), w3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+      uint4 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&w0);
+      packed.y = *reinterpret_cast<uint32_t*>(&w1);
+      packed.z = *reinterpret_cast<uint32_t*>(&w2);
+      packed.w = *reinterpret_cast<uint32_t*>(&w3);
+      *reinterpret_cast<uint4*>(sh + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = packed;
+    }
+  }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -424,6 +482,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     float* tbuf = reinterpret_cast<float*>(epi_buf + e * kEpiWarpBytes);
     __nv_bfloat16* stage16 = reinterpret_cast<__nv_bfloat16*>(epi_buf + e * kEpiWarpBytes + kEpiStage16Offset);
     const bool bulk = p.store_mode == 1 && p.splits == 1;
+    const bool rowwise = bulk && p.epi_rowwise != 0;
     int i = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
@@ -439,7 +498,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       uint8_t* ring_slice = smem_raw + (tiles - raw) + (size_t)e * (3 * kEpiSlotBytes);
       int slot_i = 0;
       float pre_col = 0.0f, pre_mat[32];
-      if (direct && n0 + half * 32 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + half * 32 + lane);
+      if (direct && !rowwise && n0 + half * 32 < p.mm.N) prefetch_sides(p, pre_col, pre_mat, batch, m_first, n0 + half * 32 + lane);
       // this warp's share of the tile: rows quad*32..+31, column chunks half*32, +64, ...
       // split K: the partial tile goes into this CTA's (now idle) pipeline memory, row-major [128][bn]
       float* part = reinterpret_cast<float*>(smem_raw + (tiles - raw)) + (size_t)(quad * 32) * p.bn;
@@ -475,13 +534,15 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #ifdef KB200_TRACE
         if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
-        // transpose through shared memory: lane = row  ->  lane = column
+        if (!rowwise) {
+          // transpose through shared memory: lane = row  ->  lane = column
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = v[j];
-        __syncwarp();
+          for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = v[j];
+          __syncwarp();
 #pragma unroll
-        for (int r = 0; r < 32; ++r) v[r] = tbuf[r * 33 + lane];
-        __syncwarp();
+          for (int r = 0; r < 32; ++r) v[r] = tbuf[r * 33 + lane];
+          __syncwarp();
+        }
 #ifdef KB200_TRACE
         if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
@@ -489,10 +550,11 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           // The next block's operands are fetched where their latency hides and no fence waits on them:
           // the per-column value before this block's arithmetic, the matrix operand (whose registers
           // are busy until then) after this block's stores have been issued.
-          const bool more = !dry && c + 64 < p.bn && n0 + c + 64 < p.mm.N;
+          const bool more = !dry && !rowwise && c + 64 < p.bn && n0 + c + 64 < p.mm.N;
           float next_col = pre_col;
           if (more) prefetch_col(p, next_col, batch, n0 + c + 64 + lane);
-          epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + (dry ? half * 32 : c) + lane);
+          if (rowwise) epilogue_compute_rows(p, v, batch, n0 + (dry ? half * 32 : c));
+          else epilogue_compute32(p, v, pre_col, pre_mat, batch, m_first, n0 + (dry ? half * 32 : c) + lane);
           pre_col = next_col;
 #ifdef KB200_TRACE
           if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
@@ -501,24 +563,20 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           if (bulk) {
             // dense row-major 32 x 32 blocks in shared memory, then one bulk tensor store each: the
             // store engine writes whole 128-byte lines and clips the block at the matrix edges
-            float* sf = tbuf;
-            __nv_bfloat16* sh = stage16;
+            uint8_t* sf = reinterpret_cast<uint8_t*>(tbuf);
+            uint8_t* sh = reinterpret_cast<uint8_t*>(stage16);
             if (ring_staging && !dry) {
               // last tile of this CTA: the operand ring is idle, so the staging blocks rotate through
               // this warp's slice of it and a store drains while the next blocks are computed
               uint8_t* slot = ring_slice + (size_t)slot_i * kEpiSlotBytes;
               slot_i = slot_i == 2 ? 0 : slot_i + 1;
-              sf = reinterpret_cast<float*>(slot);
-              sh = reinterpret_cast<__nv_bfloat16*>(slot + 4096);
+              sf = slot;
+              sh = slot + 4096;
               if (lane == 0) tma_store_wait_read2();
               __syncwarp();
             }
-#pragma unroll
-            for (int r = 0; r < 32; ++r) sf[r * 32 + lane] = v[r];
-            if (p.out16 != nullptr) {
-#pragma unroll
-              for (int r = 0; r < 32; ++r) sh[r * 32 + lane] = __float2bfloat16_rn(v[r]);
-            }
+            if (rowwise) stage_rows(sf, sh, v, lane, p.out16 != nullptr);
+            else stage_columns(sf, sh, v, lane, p.out16 != nullptr);
             fence_async_smem();
             __syncwarp();
             if (lane == 0 && m_first < p.mm.M && !(p.debug & 1) && !dry) {
@@ -846,9 +904,19 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     if (ok && p.out16 != nullptr) ok = O.stride[1] % 8 == 0 && (k.batch == 1 || O.stride[0] % 8 == 0) && aligned16(p.out16);
     st->map_out = st->map_a;
     st->map_out16 = st->map_a;
-    if (ok) ok = encode_map_plain(&st->map_out, false, O.ptr, k.N, k.M, k.batch, O.stride[1], O.stride[0], 32, 32);
-    if (ok && p.out16 != nullptr) ok = encode_map_plain(&st->map_out16, true, p.out16, k.N, k.M, k.batch, O.stride[1], O.stride[0], 32, 32);
+    if (ok) ok = encode_map_store(&st->map_out, false, O.ptr, k.N, k.M, k.batch, O.stride[1], O.stride[0]);
+    if (ok && p.out16 != nullptr) ok = encode_map_store(&st->map_out16, true, p.out16, k.N, k.M, k.batch, O.stride[1], O.stride[0]);
     p.store_mode = ok ? 1 : 0;
+    // Without a matrix operand in the chain (only immediates and per-column vectors that 128-bit loads
+    // can read) the epilogue needs no transpose: a lane keeps its accumulator row.
+    bool rowwise = ok && splits == 1 && d.cfg[7] != 2;
+    for (int s_i = 0; s_i < k.chain.n && rowwise; ++s_i) {
+      const int slot = k.chain.steps[s_i].slot;
+      if (slot < 0) continue;
+      const DevOperand& o = k.ops[slot];
+      rowwise = o.stride[1] == 0 && o.stride[2] == 1 && o.stride[0] % 4 == 0 && aligned16(o.ptr);
+    }
+    p.epi_rowwise = rowwise ? 1 : 0;
   }
   // The attribute is per function, not per launch: always ask for the ceiling, so that plans with
   // different tile configurations can coexist in one process.
@@ -1039,6 +1107,7 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   dim3 grid((unsigned)(p.num_tiles < sms ? p.num_tiles : sms), 1, 1);
   p.store_mode = 0;   // ordinary stores: the two store maps are unused placeholders
+  p.epi_rowwise = 0;
   mm_tc_kernel<true><<<grid, kThreads, smem, s>>>(map_a, map_b, map_a, map_a, p);
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;

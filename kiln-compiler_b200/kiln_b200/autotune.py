@@ -36,7 +36,7 @@ TC_CANDIDATES = [  # BN, stages, split_k
     (256, 4, 1), (256, 3, 1), (128, 4, 1), (128, 6, 1), (64, 6, 1), (128, 4, 2), (128, 4, 4), (64, 6, 2), (64, 6, 4),
     (64, 6, 8), (256, 3, 2),
 ]
-EPILOGUE_BYTES = 8 * 32 * 33 * 4     # the epilogue warps' transpose buffers
+EPILOGUE_BYTES = 8 * 7168            # the epilogue warps' transpose / staging buffers
 
 
 def cache_path() -> Path:

@@ -156,7 +156,7 @@ def _fill(desc, kclass, precision, iter_shape, operands, tape, name, n_kept=0, k
     config = config or {}
     cfg = [config.get("BM", 0), config.get("BN", 0), config.get("BK", 0), config.get("stages", 0),
            config.get("split_k", 0), IMPL_CODES.get(config.get("impl", "auto"), 0), config.get("debug", 0),
-           1 if config.get("stores", "auto") == "plain" else 0]
+           {"auto": 0, "plain": 1, "bulk_columns": 2}[config.get("stores", "auto")]]
     for i, c in enumerate(cfg):
         desc.cfg[i] = int(c)
     desc.name = name.encode()[:31]

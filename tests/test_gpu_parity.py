@@ -157,9 +157,10 @@ def test_bulk_tensor_stores_equal_plain_stores(case, precision, monkeypatch):
     monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")   # keep every planned matmul on the GPU's kernel list
     names = [n for n in build_executable(case, precision).kernel_names if "matmul" in n]
     _, bulk, _ = run_case(case, precision)
-    _, plain, _ = run_case(case, precision, configs={n.split("_")[0]: {"stores": "plain"} for n in names})
-    for a, b in zip(bulk, plain):
-        assert np.array_equal(a, b), (case, precision)
+    for stores in ("plain", "bulk_columns"):     # "auto" keeps a lane per row where the chain allows it
+        _, other, _ = run_case(case, precision, configs={n.split("_")[0]: {"stores": stores} for n in names})
+        for a, b in zip(bulk, other):
+            assert np.array_equal(a, b), (case, precision, stores)
 
 
 def test_hot_path_kernels_are_the_specialised_ones():
