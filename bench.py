@@ -181,6 +181,81 @@ def reference_arm(args, dist, rank):
     print(json.dumps(line), flush=True)
 
 
+def device_call_ms(fn, calls=200, rounds=5):
+    """Milliseconds per call of a compiled module on device tensors, back-to-back calls between two
+    CUDA events, best of `rounds` (how the reference's benchmark times a block: bench_gpu.py:54-81)."""
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(rounds):
+        start.record()
+        for _ in range(calls):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(end) / calls)
+    return best
+
+
+def reference_triton_arm(args):
+    """The reference's own Triton GPU backend on this GPU, same block and inputs, timed the way the
+    reference's benchmark does (benchmarks/bench_gpu.py:43-49, 54-81): GPU time per call as a CUDA-graph
+    replay, and host-to-host p50 latency.  Needs the reference installed under baseline/_ref (a
+    git-ignored pip --target directory); prints an `unavailable` line otherwise.  Not the
+    `--impl reference` arm: an extra comparison point."""
+    from kiln_b200 import workloads as W
+    from kiln_b200.install import register_mlir_stub
+
+    def fail(why):
+        print(json.dumps(dict(line, unavailable=why)), flush=True)
+
+    root = ROOT / "baseline" / "_ref"
+    line = {"impl": "reference-triton", "precision": "tf32" if args.precision != "fp32" else "fp32"}
+    if not (root / "kiln" / "gpu").is_dir():
+        print(json.dumps(dict(line, unavailable="the reference is not installed under baseline/_ref")), flush=True)
+        return
+    if not torch.cuda.is_available():
+        print(json.dumps(dict(line, unavailable="no CUDA device")), flush=True)
+        return
+    try:
+        sys.path.insert(0, str(root))
+        register_mlir_stub()
+        import kiln
+
+        allow_tf32 = args.precision != "fp32"
+        out = {}
+        for tokens, seed in ((128, 0), (1024, SEED), (2048, SEED)):
+            model = W.block_module(seed, tokens)
+            x = torch.from_numpy(W.block_input(seed, tokens, index=0))
+            t0 = time.perf_counter()
+            compiled = kiln.compile(model, (x,), device="cuda", allow_tf32=allow_tf32, autotune=args.autotune)
+            compile_s = time.perf_counter() - t0
+            xd = x.cuda()
+            with torch.no_grad():
+                want = model(x).double()
+                got = compiled(xd).cpu().double()
+                err = float((got - want).abs().max() / want.abs().max())
+                call_ms = device_call_ms(lambda: compiled(xd))
+                xp = x.pin_memory()
+                for _ in range(5):
+                    compiled(xp)
+                torch.cuda.synchronize()
+                lat = []
+                for _ in range(50):
+                    t0 = time.perf_counter()
+                    compiled(xp).cpu()
+                    lat.append((time.perf_counter() - t0) * 1e3)
+            out[f"block_t{tokens}"] = {"call_ms": round(call_ms, 4), "e2e_p50_ms": round(float(np.median(lat)), 4),
+                                       "tokens_per_s": round(tokens / call_ms * 1e3), "rel_err_vs_eager": err,
+                                       "compile_s": round(compile_s, 1)}
+        line.update(out, autotune=bool(args.autotune))
+    except Exception as err:   # noqa: BLE001  (an extra: report, never fail the run)
+        line["unavailable"] = f"{type(err).__name__}: {err}"[:300]
+    print(json.dumps(line), flush=True)
+
+
 def workload_config(precision, n):
     return {"workload": f"GPT-2-small block (d_model {D}, {HEADS} heads), {SEQS} sequences x {TOKENS} tokens per GPU "
                         f"per step, independent replicas", "sequences_per_gpu": SEQS, "tokens": TOKENS,
@@ -286,6 +361,8 @@ def extras(precision):
         kernel_ms = kernel_seconds(direct.run_static) * 1e3
         direct.close()
         exe, _ = build_block(precision, t, seed)
+        xd = torch.randn(t, D, device="cuda")
+        call_ms = device_call_ms(lambda: exe(xd))
         x = torch.randn(t, D).pin_memory()
         for _ in range(5):
             exe(x)
@@ -296,8 +373,8 @@ def extras(precision):
             y = exe(x)[0]
             y.cpu()
             lat.append((time.perf_counter() - t0) * 1e3)
-        out[f"block_t{t}"] = {"e2e_p50_ms": round(float(np.median(lat)), 4),
-                              "kernel_ms": round(kernel_ms, 4)}
+        out[f"block_t{t}"] = {"e2e_p50_ms": round(float(np.median(lat)), 4), "e2e_best_ms": round(float(np.min(lat)), 4),
+                              "call_ms": round(call_ms, 4), "kernel_ms": round(kernel_ms, 4)}
         exe.close()
     return out
 
@@ -422,7 +499,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"])
+    ap.add_argument("--autotune", action="store_true", help="reference-triton only: let the reference autotune its matmuls")
     ap.add_argument("--precision", default=os.environ.get("KB200_BENCH_PRECISION", "bf16"),
                     choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--no-extras", action="store_true")
@@ -434,6 +512,10 @@ def main():
         single_case(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference-triton":
+        if int(os.environ.get("RANK", 0)) == 0:
+            reference_triton_arm(args)
+        return
     if args.impl == "reference":
         rank = int(os.environ.get("RANK", 0))
         reference_arm(args, None, rank)

@@ -170,8 +170,11 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
  * attention chain (K^T copy, QK^T * scale + causal mask, softmax, PV, head merge; see
  * tests/models/transformer.py:16-25 of the reference) and the matmul precision is not FP32, run
  * it as one fused kernel.  The kernel list and arena offsets stay the reference's; the score
- * buffers are then never written.  0 keeps one launch per planned kernel. */
-typedef enum kb200_option { KB200_OPT_FUSE_ATTENTION = 1 } kb200_option;
+ * buffers are then never written.  0 keeps one launch per planned kernel.
+ * KB200_OPT_DEPENDENT_LAUNCH (default 1): kernels are enqueued with programmatic stream
+ * serialization, so that a kernel's start-up overlaps the tail of the one before it (each kernel
+ * waits for its predecessor before it touches global memory).  0 = plain stream order. */
+typedef enum kb200_option { KB200_OPT_FUSE_ATTENTION = 1, KB200_OPT_DEPENDENT_LAUNCH = 2 } kb200_option;
 int kb200_plan_set_option(kb200_plan* plan, int option, int value);
 
 /* Enqueues every kernel, in order, on `cuda_stream` (a cudaStream_t).

@@ -70,6 +70,8 @@ struct AttnState {
 };
 
 __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
@@ -161,6 +163,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // Everything above overlapped the previous kernel's tail; Q, K and V are its output.
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tmem_base = tmem_base_slot;
   // columns: S0 0..127 | S1 128..255 | O_part[group][buffer] 256 + (group * 2 + buffer) * 64
   const uint32_t tmem_o0 = tmem_base + 256;
@@ -593,14 +598,14 @@ bool attention_try_fuse(Plan& plan, size_t i) {
 }
 
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
-  (void)plan;
   const AttnState* st = static_cast<const AttnState*>(k.attn);
-  attention_kernel<<<st->grid, kAttnThreads, kAttnSmem, s>>>(st->map_q, st->map_k, st->map_v, st->params);
+  KB200_CUDA(launch_kernel(plan.pdl, attention_kernel, st->grid, dim3(kAttnThreads), kAttnSmem, s, st->map_q, st->map_k, st->map_v,
+                           st->params));
   if (st->staged_out) {
     const int64_t n4 = st->out_elems / 4;
     const int64_t blocks = (n4 + 255) / 256;
-    copy_rows_kernel<<<(unsigned)(blocks < 1184 ? blocks : 1184), 256, 0, s>>>(reinterpret_cast<const float4*>(st->staged_out),
-                                                                              reinterpret_cast<float4*>(st->final_out), n4);
+    KB200_CUDA(launch_kernel(plan.pdl, copy_rows_kernel, dim3((unsigned)(blocks < 1184 ? blocks : 1184)), dim3(256), 0, s,
+                             reinterpret_cast<const float4*>(st->staged_out), reinterpret_cast<float4*>(st->final_out), n4));
   }
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;

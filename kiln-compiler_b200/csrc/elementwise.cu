@@ -23,6 +23,8 @@ struct EwParams {
 };
 
 __global__ void __launch_bounds__(256) ew_generic_kernel(const __grid_constant__ EwParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   float r[KB200_MAX_TAPE];
   int64_t off[KB200_MAX_OPERANDS];
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
@@ -83,6 +85,8 @@ __device__ __forceinline__ float4 ew_load4(const EwChainParams& p, int slot, con
 // spent 75 instructions per element and ran at a third of the copy bandwidth).
 template <int RANK, int U>
 __global__ void __launch_bounds__(256) ew_chain_vec4_kernel(const __grid_constant__ EwChainParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   const uint32_t nvec = p.nvec;
   const uint32_t step = gridDim.x * blockDim.x * U;
   for (uint32_t base = blockIdx.x * blockDim.x * U + threadIdx.x; base < nvec; base += step) {
@@ -134,6 +138,8 @@ struct EwTransposeParams {
 };
 
 __global__ void __launch_bounds__(256) ew_transpose_kernel(const __grid_constant__ EwTransposeParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   __shared__ float tile[32][33];
   const int last = p.rank - 1;
   const int64_t n_t = p.shape[p.tdim], n_l = p.shape[last];
@@ -278,10 +284,10 @@ int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     int64_t cap = (int64_t)plan.sm_count * 16;
     const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
     switch (rank) {
-      case 1: ew_chain_vec4_kernel<1, U><<<grid, 256, 0, s>>>(p); break;
-      case 2: ew_chain_vec4_kernel<2, U><<<grid, 256, 0, s>>>(p); break;
-      case 3: ew_chain_vec4_kernel<3, U><<<grid, 256, 0, s>>>(p); break;
-      default: ew_chain_vec4_kernel<4, U><<<grid, 256, 0, s>>>(p); break;
+      case 1: launch_kernel(plan.pdl, ew_chain_vec4_kernel<1, U>, dim3(grid), dim3(256), 0, s, p); break;
+      case 2: launch_kernel(plan.pdl, ew_chain_vec4_kernel<2, U>, dim3(grid), dim3(256), 0, s, p); break;
+      case 3: launch_kernel(plan.pdl, ew_chain_vec4_kernel<3, U>, dim3(grid), dim3(256), 0, s, p); break;
+      default: launch_kernel(plan.pdl, ew_chain_vec4_kernel<4, U>, dim3(grid), dim3(256), 0, s, p); break;
     }
   } else if (k.impl == IMPL_EW_TRANSPOSE) {
     EwTransposeParams p{};
@@ -296,7 +302,7 @@ int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     p.chain = k.chain;
     int64_t tiles = ((p.shape[p.tdim] + 31) / 32) * ((p.shape[p.rank - 1] + 31) / 32) * p.outer;
     int64_t cap = (int64_t)plan.sm_count * 16;
-    ew_transpose_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 256, 0, s>>>(p);
+    launch_kernel(plan.pdl, ew_transpose_kernel, dim3((unsigned)(tiles < cap ? tiles : cap)), dim3(256), 0, s, p);
   } else {
     EwParams p{};
     p.rank = d.iter_rank;
@@ -307,7 +313,7 @@ int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     p.tape = k.tape;
     int64_t blocks = (numel + 255) / 256;
     int64_t cap = (int64_t)plan.sm_count * 8;
-    ew_generic_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(p);
+    launch_kernel(plan.pdl, ew_generic_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, s, p);
   }
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;

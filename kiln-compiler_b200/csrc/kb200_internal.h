@@ -98,6 +98,7 @@ struct Plan {
   std::vector<PlanKernel> kernels;
   int* d_status = nullptr;       // device status word for bounded waits
   bool fuse_attention = true;    // replace the five-kernel attention chain by the fused kernel when it matches
+  bool pdl = true;               // programmatic dependent launch: a kernel's start-up overlaps its predecessor's tail
   void* arena16 = nullptr;       // bf16 mirror of the arena (library-owned, only when some matmul reads it)
   uint64_t arena16_bytes = 0;
   // bound buffers (for re-validation and the tensor-core path)
@@ -129,6 +130,32 @@ void destroy_matmul(PlanKernel& k);
 bool attention_try_fuse(Plan& plan, size_t first);   // kernels first .. first+4
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void attention_destroy(PlanKernel& k);
+
+// Every kernel of the library is launched through this: with programmatic stream serialization the
+// next kernel in the stream may start (barrier set-up, TMEM allocation, descriptor prefetch) while
+// this one is still running; it touches global memory only after pdl_wait() below, which returns
+// once the preceding grid has completed and its writes are visible.  Without the attribute (plan
+// option off) the two device calls are no-ops.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 inline int64_t numel_of(const kb200_kernel_desc& d) {
   int64_t n = 1;

@@ -12,6 +12,8 @@ namespace kb200 {
 
 template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN)) mm_simt_kernel(const __grid_constant__ MatmulParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   constexpr int NT = (BM / TM) * (BN / TN);
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Bs[BK][BN + 4];
@@ -88,6 +90,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) mm_simt_kernel(const __
 // Each CTA owns 64 output columns (two per lane, 256-byte coalesced rows of B); its 8 warps split
 // K and combine through shared memory, which keeps the result deterministic.
 __global__ void __launch_bounds__(256) mm_gemv_kernel(const __grid_constant__ MatmulParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   __shared__ float part[8][64];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t b = blockIdx.z;
@@ -158,15 +162,15 @@ int launch_matmul_simt(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   fill_matmul_params(k, &p);
   if (k.impl == IMPL_MM_GEMV) {
     dim3 grid((unsigned)((p.N + 63) / 64), 1, (unsigned)p.batch);
-    mm_gemv_kernel<<<grid, 256, 0, s>>>(p);
+    launch_kernel(plan.pdl, mm_gemv_kernel, grid, dim3(256), 0, s, p);
   } else {
     const int64_t big_tiles = ((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batch;
     if (big_tiles >= plan.sm_count) {
       dim3 grid((unsigned)(((p.M + 127) / 128) * ((p.N + 127) / 128)), 1, (unsigned)p.batch);
-      mm_simt_kernel<128, 128, 8, 8, 8><<<grid, 256, 0, s>>>(p);
+      launch_kernel(plan.pdl, mm_simt_kernel<128, 128, 8, 8, 8>, grid, dim3(256), 0, s, p);
     } else {
       dim3 grid((unsigned)(((p.M + 63) / 64) * ((p.N + 63) / 64)), 1, (unsigned)p.batch);
-      mm_simt_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(p);
+      launch_kernel(plan.pdl, mm_simt_kernel<64, 64, 16, 4, 4>, grid, dim3(256), 0, s, p);
     }
   }
   KB200_CUDA(cudaGetLastError());

@@ -42,7 +42,8 @@ constexpr int kSlabBytes = 128;           // bytes of K (A) or N (B) per swizzle
 constexpr int kATileBytes = kTileM * kSlabBytes;
 constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpiWarps;      // producer warp, MMA warp, epilogue warps
+constexpr int kProducerBWarp = 2 + kEpiWarps;      // the last warp fetches operand B
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32; // producer (A) warp, MMA warp, epilogue warps, producer (B) warp
 // per epilogue warp: a 32 x 33 float transpose buffer, reused (as dense 32 x 32) as the staging block of
 // the bulk store, then a 32 x 32 bf16 staging block; both 128-byte aligned
 constexpr int kEpiStage16Offset = 4608;        // 512-byte aligned (64-byte swizzle); the float block is 1024-byte aligned
@@ -316,14 +317,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
              const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_out16,
              const __grid_constant__ TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 6];   // + two cluster hand-shake barriers (split K)
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 #ifdef KB200_TRACE
   __shared__ long long trace[6][160];
   __shared__ long long marks[8];
   int tp = 0, tm = 0, te = 0;
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
+  if (blockIdx.x <= 1 && threadIdx.x == 0) {
     unsigned long long g;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
     marks[0] = (long long)g;
@@ -353,7 +354,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   if (warp == 0) {
     // one barrier per lane: full[0..7] | empty[0..7] | tfull[0..1] | tempty[0..1]
     if (lane == 0) abort_flag = 0;
-    if (lane < 2 * kMaxStages + 4) mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : 1);
+    if (lane < 2 * kMaxStages + 4) mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : (lane < kMaxStages ? 2 : 1));
+    else if (lane < 2 * kMaxStages + 6) mbar_init(full0 + 8 * lane, (uint32_t)p.splits);   // one arrival per CTA of the cluster
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -366,20 +368,32 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  // Split K: the hand-shake barriers of every CTA of the cluster must exist before a neighbour arrives
+  // on them.  Arrive on the hardware cluster barrier now, wait for it only when the main loop is over
+  // (the barrier itself takes thousands of cycles to complete; they pass under the main loop).
+  if (p.splits > 1) cluster_arrive();
+  // Everything above (barriers, TMEM, descriptor prefetch) may have overlapped the previous kernel's
+  // tail; from here on its output is read.
+  pdl_wait();
+  pdl_launch_dependents();
   volatile int* abort_ptr = &abort_flag;
 #ifdef KB200_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) marks[2] = clock64();
+  if (blockIdx.x <= 1 && threadIdx.x == 0) marks[2] = clock64();
 #endif
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
+  if (warp == 0 || warp == kProducerBWarp) {
+    // ---------------- TMA producers ----------------
+    // Two threads in two warps, one per operand: issuing a bulk tensor copy costs a lone thread a few
+    // hundred cycles, and with narrow tiles that issue time, not the tensor pipe, bounded the K loop.
+    // Both wait on the stage's empty barrier and each arrives on its full barrier with its own bytes.
     if (lane == 0) {
+      const bool load_a = warp == 0;
       // everything the loop needs in registers: a lone thread pays full latency for every
       // dependent instruction, so the per-slab instruction count is what bounds the issue rate
       const int stages = p.stages, num_units = p.num_units, slab_k = p.slab_k;
       const int bn = p.bn, chunk_n = p.chunk_n, b_mode = p.b_mode, n_chunks = p.n_chunks;
       const uint32_t chunk_bytes = (uint32_t)slab_k * kSlabBytes;
-      const uint32_t tx_bytes = (uint32_t)stage_bytes;
+      const uint32_t tx_bytes = load_a ? (uint32_t)kATileBytes : (uint32_t)b_tile_bytes;
       int s = 0;
       uint32_t wait_parity = 1;                // parity to wait for on the empty barriers of this pass over the ring
       bool ok = true;
@@ -388,6 +402,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         unit_coords(p, unit, tile, ks, batch, tm_i, tn_i);
         slab_range(p, ks, kb_begin, kb_end);
         const int m0 = tm_i * kTileM, n0 = tn_i * bn;
+        const int n0_chunk = tn_i * n_chunks;
         int k_elem = kb_begin * slab_k;
         for (int kb = kb_begin; kb < kb_end; ++kb, k_elem += slab_k) {
           const uint32_t full = full0 + 8 * s;
@@ -396,19 +411,20 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             ok = false;
             break;
           }
-          KB200_STAMP(0, tp);
+          if (load_a) KB200_STAMP(0, tp);
           mbar_expect_tx(full, tx_bytes);
           const uint32_t a_dst = tiles + s * stage_bytes;
-          tma_load_3d(a_dst, &tma_a, full, k_elem, m0, batch);
-          if (b_mode == 0) {                     // K-major B: one box, like A
+          if (load_a) {
+            tma_load_3d(a_dst, &tma_a, full, k_elem, m0, batch);
+          } else if (b_mode == 0) {              // K-major B: one box, like A
             tma_load_3d(a_dst + kATileBytes, &tma_b, full, k_elem, n0, batch);
           } else if (b_mode == 1) {              // N-major B, all column chunks of the tile in one 4-D box
-            tma_load_4d(a_dst + kATileBytes, &tma_b, full, 0, k_elem, n0 / chunk_n, batch);
+            tma_load_4d(a_dst + kATileBytes, &tma_b, full, 0, k_elem, n0_chunk, batch);
           } else {                               // N-major B, N not a multiple of the chunk: one box per chunk
             for (int c = 0; c < n_chunks; ++c)
               tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, n0 + c * chunk_n, k_elem, batch);
           }
-          KB200_STAMP(1, tp);
+          if (load_a) KB200_STAMP(1, tp);
 #ifdef KB200_TRACE
           ++tp;
 #endif
@@ -472,7 +488,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA of this tile has completed
       }
     }
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     // ---------------- epilogue (warps 2..9) ----------------
     // Two warps per TMEM lane quadrant (a warp may only touch lanes 32 * (warp % 4) ..+31); the
     // pair splits the 32-column chunks of the tile between them.
@@ -608,20 +624,29 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   }
 
   // ---------------- split K: reduce across the cluster through distributed shared memory ----------------
-  // The `splits` CTAs of a cluster hold partial sums of the same tile.  After a cluster barrier each
-  // CTA takes a band of rows, adds the partial bands of all CTAs in rank order (so the result does
-  // not depend on timing), applies the epilogue and stores.  Every thread of every CTA reaches both
-  // barriers, also after an aborted wait: all loops above are bounded.
+  // The `splits` CTAs of a cluster hold partial sums of the same tile.  Each tells every CTA of the
+  // cluster "my partial tile is parked" by arriving on that CTA's `parked` mbarrier, waits until all
+  // have arrived on its own, then takes a band of rows, adds the partial bands of all CTAs in rank
+  // order (so the result does not depend on timing), applies the epilogue and stores.  A second
+  // round of arrivals (`released`) keeps every CTA resident until no neighbour reads its shared
+  // memory any more.  (A hardware cluster barrier at these two points cost 5500 cycles each time.)
+  // Every CTA sends both rounds also after an aborted wait: all loops above are bounded.
   if (p.splits > 1) {
-    __syncthreads();
+    const uint32_t parked = smem_u32(&bars[2 * kMaxStages + 4]), released = smem_u32(&bars[2 * kMaxStages + 5]);
+    cluster_wait();          // completes the arrive made before the main loop: every CTA's barriers are initialised
+    __syncthreads();         // every warp of this CTA has parked its part
 #ifdef KB200_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) marks[3] = clock64();
+    if (blockIdx.x <= 1 && threadIdx.x == 0) marks[3] = clock64();
 #endif
-    cluster_sync();
+    if (threadIdx.x < (unsigned)p.splits) mbar_arrive_cluster(map_to_cta(parked, threadIdx.x));
+    if (!mbar_wait_cluster(parked, 0, abort_ptr) && threadIdx.x == 0 && !*abort_ptr) {
+      atomicCAS(p.status, 0, (p.kernel_index << 8) | 5);
+      *abort_ptr = 1;
+    }
 #ifdef KB200_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) marks[4] = clock64();
+    if (blockIdx.x <= 1 && threadIdx.x == 0) marks[4] = clock64();
 #endif
-    if (warp >= 2 && !abort_flag) {
+    if (warp >= 2 && warp < 2 + kEpiWarps && !abort_flag) {
       const int e = warp - 2;
       uint32_t rank;
       asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -651,21 +676,49 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             if (r < nrows) v[r] += ld_cluster_f32(remote + (uint32_t)(r * p.bn * 4));
         }
         epilogue_compute32(p, v, pre_col, pre_mat, batch, m0 + row_base, n, nrows);
-        epilogue_store32(p, v, batch, m0 + row_base, n, nrows);
+        if (p.store_mode == 1 && nrows == 32) {
+          // full 32-row block: staged and written with bulk tensor stores like the unsplit epilogue
+          uint8_t* sf = epi_buf + e * kEpiWarpBytes;
+          uint8_t* sh = sf + kEpiStage16Offset;
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          stage_columns(sf, sh, v, lane, p.out16 != nullptr);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && m0 + row_base < p.mm.M && !(p.debug & 1)) {
+            tma_store_3d(&tma_out, smem_u32(sf), (int)(n0 + cb * 32), (int)(m0 + row_base), batch);
+            if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(sh), (int)(n0 + cb * 32), (int)(m0 + row_base), batch);
+            tma_store_commit();
+          }
+        } else {
+          epilogue_store32(p, v, batch, m0 + row_base, n, nrows);
+        }
       }
+      if (lane == 0) tma_store_wait_read();
     }
 #ifdef KB200_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 64) marks[5] = clock64();
+    if (blockIdx.x <= 1 && threadIdx.x == 64) marks[5] = clock64();
 #endif
-    cluster_sync();     // nobody leaves (and frees its shared memory) while a neighbour still reads it
+    __syncthreads();         // this CTA no longer reads its neighbours' shared memory ...
+    if (threadIdx.x < (unsigned)p.splits) mbar_arrive_cluster(map_to_cta(released, threadIdx.x));
+    // ... and leaves (frees its own) only when no neighbour reads it any more
+    if (threadIdx.x == 0 && !mbar_wait_cluster(released, 0, abort_ptr) && !*abort_ptr) {
+      atomicCAS(p.status, 0, (p.kernel_index << 8) | 6);
+      *abort_ptr = 1;
+    }
 #ifdef KB200_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) marks[6] = clock64();
+    if (blockIdx.x <= 1 && threadIdx.x == 0) marks[6] = clock64();
 #endif
   }
 
   // ---------------- common exit ----------------
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+#ifdef KB200_TRACE
+  if (blockIdx.x == 1 && threadIdx.x == 0 && p.splits > 1)
+    printf("block1 split phase: entry globaltimer %lld setup_done %lld before cluster sync %lld after %lld reduce done %lld after 2nd sync %lld\n",
+           marks[0], marks[2] - marks[1], marks[3] - marks[1], marks[4] - marks[1], marks[5] - marks[1], marks[6] - marks[1]);
+#endif
 #ifdef KB200_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned long long g;
@@ -701,6 +754,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 __global__ void __launch_bounds__(256) cvt_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                                        int64_t batch, int64_t rows, int64_t cols, int64_t s_batch,
                                                        int64_t s_row) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   const int64_t cols4 = cols >> 2;
   const int64_t total = batch * rows * cols4;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -935,14 +990,15 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     const int64_t cap = (int64_t)plan.sm_count * 8;
     int64_t total = k.batch * k.M * (k.K / 4);
     if (!st->a_shadow)
-      cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
-          A.ptr, st->a16, k.batch, k.M, k.K, A.stride[0], A.stride[1]);
+      KB200_CUDA(launch_kernel(plan.pdl, cvt_bf16_kernel, dim3((unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap)),
+                               dim3(256), 0, s, (const float*)A.ptr, st->a16, k.batch, k.M, k.K, A.stride[0], A.stride[1]));
     if (!st->b_const && !st->b_shadow) {
       const bool km = st->params.b_kmajor != 0;
       const int64_t rows = km ? k.N : k.K, cols = km ? k.K : k.N;
       total = k.batch * rows * (cols / 4);
-      cvt_bf16_kernel<<<(unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap), 256, 0, s>>>(
-          B.ptr, st->b16, k.batch, rows, cols, B.stride[0], km ? B.stride[2] : B.stride[1]);
+      KB200_CUDA(launch_kernel(plan.pdl, cvt_bf16_kernel, dim3((unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap)),
+                               dim3(256), 0, s, (const float*)B.ptr, st->b16, k.batch, rows, cols, B.stride[0],
+                               km ? B.stride[2] : B.stride[1]));
     }
   }
   cudaLaunchConfig_t cfg = {};
@@ -950,13 +1006,22 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = st->smem_bytes;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)st->params.splits;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (st->params.splits > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = (unsigned)st->params.splits;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (plan.pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = st->params.splits > 1 ? 1 : 0;
+  cfg.numAttrs = n_attr;
   if (st->bf16) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<true>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
   else KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
   KB200_CUDA(cudaGetLastError());

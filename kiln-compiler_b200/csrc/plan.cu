@@ -578,6 +578,7 @@ KB200_EXPORT int kb200_plan_set_option(kb200_plan* p, int option, int value) {
   Plan& plan = *reinterpret_cast<Plan*>(p);
   switch (option) {
     case KB200_OPT_FUSE_ATTENTION: plan.fuse_attention = value != 0; return KB200_OK;
+    case KB200_OPT_DEPENDENT_LAUNCH: plan.pdl = value != 0; return KB200_OK;
     default: return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: unknown option %d", option);
   }
 }

@@ -19,6 +19,8 @@ struct ReduceParams {
 };
 
 __global__ void __launch_bounds__(256) reduce_generic_kernel(const __grid_constant__ ReduceParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   __shared__ float partial[8][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t groups = (p.n_out + 31) / 32;
@@ -87,7 +89,7 @@ int launch_reduce(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   p.out = k.ops[out_slot].ptr;
   const int64_t groups = (p.n_out + 31) / 32;
   const int64_t cap = (int64_t)plan.sm_count * 8;
-  reduce_generic_kernel<<<(unsigned)(groups < cap ? groups : cap), 256, 0, s>>>(p);
+  launch_kernel(plan.pdl, reduce_generic_kernel, dim3((unsigned)(groups < cap ? groups : cap)), dim3(256), 0, s, p);
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }

@@ -42,6 +42,8 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* scrat
 }
 
 __global__ void __launch_bounds__(kRowThreads) row_generic_kernel(const __grid_constant__ RowParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   __shared__ float s_red[KB200_MAX_TAPE];
   __shared__ float s_scratch[kRowThreads / 32];
   float r[KB200_MAX_TAPE];
@@ -124,6 +126,8 @@ enum { ROW_LAYERNORM = 0, ROW_SOFTMAX = 1 };
 // One warp per row; lane l owns float4 number l + 32 * i, i < VPL.
 template <int MODE, int VPL>
 __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ RowFastParams p) {
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int64_t row = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5);
@@ -203,12 +207,12 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
 }
 
 template <int MODE>
-static void launch_row_warp(const RowFastParams& p, int sm_count, cudaStream_t s) {
+static void launch_row_warp(const RowFastParams& p, int sm_count, bool pdl, cudaStream_t s) {
   const int vpl = (p.inner / 4 + 31) / 32;
   int warps = p.n_rows >= (int64_t)sm_count * 16 ? 8 : (p.n_rows >= (int64_t)sm_count * 4 ? 4 : 1);
   const unsigned grid = (unsigned)((p.n_rows + warps - 1) / warps);
   const unsigned block = warps * 32;
-#define KB200_ROW_CASE(V) row_warp_kernel<MODE, V><<<grid, block, 0, s>>>(p)
+#define KB200_ROW_CASE(V) launch_kernel(pdl, row_warp_kernel<MODE, V>, dim3(grid), dim3(block), 0, s, p)
   if (vpl <= 1) KB200_ROW_CASE(1);
   else if (vpl <= 2) KB200_ROW_CASE(2);
   else if (vpl <= 4) KB200_ROW_CASE(4);
@@ -272,9 +276,9 @@ int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
       p.inv_n = k.ln_inv_n;
       p.eps = k.ln_eps;
       p.out16 = static_cast<__nv_bfloat16*>(k.shadow_out);
-      launch_row_warp<ROW_LAYERNORM>(p, plan.sm_count, s);
+      launch_row_warp<ROW_LAYERNORM>(p, plan.sm_count, plan.pdl, s);
     } else {
-      launch_row_warp<ROW_SOFTMAX>(p, plan.sm_count, s);
+      launch_row_warp<ROW_SOFTMAX>(p, plan.sm_count, plan.pdl, s);
     }
   } else {
     RowParams p{};
@@ -289,7 +293,7 @@ int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     for (int o = 0; o < d.n_operands; ++o) p.ops[o] = k.ops[o];
     p.tape = k.tape;
     int64_t cap = (int64_t)plan.sm_count * 8;
-    row_generic_kernel<<<(unsigned)(n_rows < cap ? n_rows : cap), kRowThreads, 0, s>>>(p);
+    launch_kernel(plan.pdl, row_generic_kernel, dim3((unsigned)(n_rows < cap ? n_rows : cap)), dim3(kRowThreads), 0, s, p);
   }
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;

@@ -36,7 +36,8 @@ class _Missing(types.ModuleType):
         return _Absent
 
 
-def _stub_mlir():
+def register_mlir_stub():
+    """Register an empty ``mlir`` package when LLVM's Python bindings are absent. True if it did."""
     if importlib.util.find_spec("mlir") is not None:
         return False
     for name in ("mlir", "mlir.ir", "mlir.passmanager", "mlir.execution_engine", "mlir.dialects",
@@ -55,7 +56,7 @@ def install(stub_mlir=True):
     from kiln_b200 import autotune, codegen, runtime
 
     if stub_mlir:
-        _stub_mlir()
+        register_mlir_stub()
     pkg = types.ModuleType("kiln.gpu")
     pkg.__path__ = []
     pkg.__doc__ = "Kiln's GPU backend, provided by kiln_b200 (hand-written sm_100a kernels)."

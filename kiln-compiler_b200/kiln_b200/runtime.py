@@ -148,6 +148,9 @@ class GPUExecutable:
         # attention chain as one fused kernel in the reduced-precision modes (default).
         fuse = os.environ.get("KILN_GPU_FUSE_ATTENTION", "1") not in ("0", "false", "False", "")
         _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_FUSE_ATTENTION, int(fuse)), self._lib)
+        # Programmatic dependent launch between the plan's kernels (KILN_GPU_DEPENDENT_LAUNCH=0: plain stream order).
+        pdl = os.environ.get("KILN_GPU_DEPENDENT_LAUNCH", "1") not in ("0", "false", "False", "")
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_DEPENDENT_LAUNCH, int(pdl)), self._lib)
         self._bind()
         self.kernel_names = [l.name for l in program.launches]
         self.impls = [self._lib.kb200_kernel_impl(self._plan, i).decode() for i in range(len(program.launches))]

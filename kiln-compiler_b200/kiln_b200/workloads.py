@@ -111,3 +111,42 @@ def block_flops(t, d=768, heads=12):
     """Algorithmic FLOPs of one block call as the reference computes it (full T x T attention)."""
     del heads
     return 2 * t * d * (3 * d) + 2 * t * d * d + 2 * 2 * t * d * (4 * d) + 2 * 2 * t * t * d
+
+
+def block_module(seed, t, d=768, heads=12):
+    """The same block as a ``torch.nn.Module`` holding ``block_params(seed, t)``: what a user hands to
+    ``kiln.compile``.  Written with the operations the Kiln frontend imports (Linear, LayerNorm,
+    view / transpose / split, matmul, softmax, tanh-GELU; architecture of the reference's test model,
+    tests/models/transformer.py:5-29) and with its parameter names, so that the compiled plan is the
+    11-kernel plan stored under tests/golden/plans."""
+    import math
+
+    import torch
+    from torch import nn
+    from torch.nn import functional as F
+
+    class PreLNBlock(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.heads = heads
+            self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            self.c_attn, self.c_proj = nn.Linear(d, 3 * d), nn.Linear(d, d)
+            self.fc, self.proj = nn.Linear(d, 4 * d), nn.Linear(4 * d, d)
+            self.register_buffer("mask", torch.zeros(t, t))
+
+        def attention(self, h):
+            tokens, width = h.shape
+            hd = width // self.heads
+            q, k, v = (z.view(tokens, self.heads, hd).transpose(0, 1) for z in self.c_attn(h).split(width, dim=1))
+            scores = (q @ k.transpose(-2, -1)) * (1.0 / math.sqrt(hd)) + self.mask[:tokens, :tokens]
+            merged = (F.softmax(scores, dim=-1) @ v).transpose(0, 1).contiguous().view(tokens, width)
+            return self.c_proj(merged)
+
+        def forward(self, x):
+            x = x + self.attention(self.ln1(x))
+            return x + self.proj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+    model = PreLNBlock().eval()
+    state = {k: torch.from_numpy(v.copy()) for k, v in block_params(seed, t, d, heads).items()}
+    model.load_state_dict(state)
+    return model

@@ -145,6 +145,37 @@ except RuntimeError as e:
     assert got == json.loads(json.dumps(load_plan("gpt2_block_t128"), sort_keys=True))
 
 
+@needs_reference
+def test_the_package_s_own_block_module_compiles_to_the_golden_plan():
+    """workloads.block_module (what bench.py hands to the reference's Triton backend for the side-by-side
+    run) goes through the reference's frontend and passes to the same 11-kernel plan as the reference's
+    own test model, and evaluates like the functional restatement the CPU baseline times."""
+    code = f"""
+import sys, json
+sys.path[:0] = [{str(ROOT / 'kiln-compiler_b200')!r}, {str(ROOT)!r}, {str(REFERENCE)!r}]
+import numpy as np, torch, kiln_b200
+from kiln_b200 import workloads as W
+from oracle.torch_block import block_forward, to_torch
+kiln = kiln_b200.install()
+from kiln.api import Options, build_passes
+from kiln.frontend.fx_import import import_exported
+from kiln.passes.manager import PassManager
+from kiln.gpu.codegen import generate
+model = W.block_module(0, 128)
+x = torch.from_numpy(W.block_input(0, 128))
+with torch.no_grad():
+    assert torch.allclose(model(x), block_forward(to_torch(W.block_params(0, 128)), x), rtol=1e-5, atol=1e-6)
+g = import_exported(torch.export.export(model, (x,)).run_decompositions())
+PassManager(build_passes(Options(tiling=False))).run(g)
+plan = generate(g, allow_tf32=True).plan.to_json(); plan["name"] = "gpt2_block_t128"
+print(json.dumps(plan, sort_keys=True))
+"""
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert got == json.loads(json.dumps(load_plan("gpt2_block_t128"), sort_keys=True))
+
+
 def test_chain_and_collapse_helpers():
     shape, strides, segs = lowering.collapse([2, 16, 8], [[16, 1, 96], [128, 8, 1]])
     assert shape == [32, 8] and strides == [[1, 96], [8, 1]] and segs == [2]
