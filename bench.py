@@ -338,27 +338,108 @@ def roofline_of(exe, plan, precision, iters=20):
             "per_kernel_ms": {n: round(t, 5) for n, t in times}}
 
 
+def graph_times(fn, repeats=20, replays=200):
+    """(best, median) seconds per call of ``fn``: ``repeats`` calls captured in one CUDA graph, the
+    replay timed with CUDA events ``replays`` times (the reference's kernel_seconds, runtime.py:93-132,
+    with a p50 beside the best)."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(repeats):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    samples = []
+    for _ in range(replays):
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(end) / 1e3 / repeats)
+    return float(np.min(samples)), float(np.median(samples))
+
+
+def tf32_peak_tflops(n=8192):
+    """cuBLAS TF32 GEMM throughput measured the way MEASURED_PEAKS.json measures BF16 (torch.matmul, n^3, burst)."""
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a, b = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+        for _ in range(3):
+            a @ b
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(10):
+            start.record()
+            a @ b
+            end.record()
+            torch.cuda.synchronize()
+            best = min(best, start.elapsed_time(end))
+        return 2 * n ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
 def extras(precision):
     """The reference's other headline numbers: block latency, Linear TFLOP/s, fused-op GB/s."""
     from gpu_helpers import build_executable
-    from kiln_b200.runtime import kernel_seconds
+    from helpers import case_data, load_plan
+
+    def filled(case, prec):
+        plan = load_plan(case)
+        inputs, consts, _ = case_data(case, plan)
+        exe = build_executable(case, prec, cuda_graphs=False, plan_json=plan, consts=consts)
+        for static, x in zip(exe.static_inputs, inputs):
+            static.copy_(torch.from_numpy(np.ascontiguousarray(x)))
+        return exe
 
     out = {}
+    pk, _ = peaks()
     for case, byts in (("bias_gelu_2048x3072", 50343936), ("layernorm_2048x768", 12589056),
                        ("softmax_12x512x512", 25165824)):
-        exe = build_executable(case, "fp32", cuda_graphs=False)
-        out[case] = {"warm_gbs": round(byts / kernel_seconds(exe.run_static) / 1e9, 1), "impl": exe.impls}
-        exe.close()
+        exe = filled(case, "fp32")
+        best, p50 = graph_times(exe.run_static)
+        # cold: rotate through enough copies of the operands that nothing is left in the 126 MB L2
+        n_sets = max(2, -(-2 * 126 * 2**20 // byts) + 1)
+        sets = [exe] + [filled(case, "fp32") for _ in range(n_sets - 1)]
+
+        def rotate():
+            for e in sets:
+                e.run_static()
+
+        cold_best, cold_p50 = graph_times(rotate, repeats=2, replays=50)
+        out[case] = {"warm_gbs": round(byts / best / 1e9, 1), "warm_p50_gbs": round(byts / p50 / 1e9, 1),
+                     "cold_gbs": round(byts * n_sets / cold_best / 1e9, 1), "cold_p50_gbs": round(byts * n_sets / cold_p50 / 1e9, 1),
+                     "frac_of_measured_hbm": round(byts * n_sets / cold_best / 1e9 / pk["hbm_gbs"], 3),
+                     "buffer_sets": n_sets, "impl": exe.impls}
+        for e in sets:
+            e.close()
     from kiln_b200 import workloads as W
     mm_prec = precision if precision != "fp32" else "fp32"
+    mm_peak = pk["bf16_tflops"] if mm_prec == "bf16" else (tf32_peak_tflops() if mm_prec == "tf32" else None)
+    if mm_prec == "tf32":
+        out["tf32_peak_tflops_measured"] = round(mm_peak, 1)
     for m, n, k in W.LINEAR_SHAPES:
-        exe = build_executable(f"linear_{m}x{n}x{k}", mm_prec, cuda_graphs=False)
-        out[f"linear_{m}x{n}x{k}"] = {"tflops": round(2 * m * n * k / kernel_seconds(exe.run_static) / 1e12, 2),
-                                      "precision": mm_prec, "impl": exe.impls}
+        exe = filled(f"linear_{m}x{n}x{k}", mm_prec)
+        best, p50 = graph_times(exe.run_static)
+        row = {"tflops": round(2 * m * n * k / best / 1e12, 2), "p50_tflops": round(2 * m * n * k / p50 / 1e12, 2),
+               "us": round(best * 1e6, 2), "precision": mm_prec, "impl": exe.impls}
+        if mm_peak and m > 1:
+            row["frac_of_measured_peak"] = round(row["tflops"] / mm_peak, 3)
+        if m == 1:      # decode GEMV: weights streamed once
+            row["gbs"] = round((4 * k * n + 4 * n + 4 * k) / best / 1e9, 1)
+        out[f"linear_{m}x{n}x{k}"] = row
         exe.close()
     for t, seed in ((128, 0), (2048, 4)):
         direct, _ = build_block(precision, t, seed, cuda_graphs=False)
-        kernel_ms = kernel_seconds(direct.run_static) * 1e3
+        kernel_best, kernel_p50 = graph_times(direct.run_static)
         direct.close()
         exe, _ = build_block(precision, t, seed)
         xd = torch.randn(t, D, device="cuda")
@@ -368,15 +449,31 @@ def extras(precision):
             exe(x)
         torch.cuda.synchronize()
         lat = []
-        for _ in range(50):
+        for _ in range(200):
             t0 = time.perf_counter()
             y = exe(x)[0]
             y.cpu()
             lat.append((time.perf_counter() - t0) * 1e3)
         out[f"block_t{t}"] = {"e2e_p50_ms": round(float(np.median(lat)), 4), "e2e_best_ms": round(float(np.min(lat)), 4),
-                              "call_ms": round(call_ms, 4), "kernel_ms": round(kernel_ms, 4)}
+                              "call_ms": round(call_ms, 4), "kernel_ms": round(kernel_best * 1e3, 4),
+                              "kernel_p50_ms": round(kernel_p50 * 1e3, 4)}
         exe.close()
     return out
+
+
+def reference_triton_extra(precision):
+    """The reference's Triton backend on this GPU, in a process of its own (it registers the same
+    module names this package does); its one JSON line, or why it could not run."""
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference-triton", "--autotune",
+           "--precision", "fp32" if precision == "fp32" else "tf32"]
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=420)
+        for text in reversed(proc.stdout.strip().splitlines()):
+            if text.startswith("{"):
+                return json.loads(text)
+        return {"impl": "reference-triton", "unavailable": (proc.stderr or "no output")[-200:]}
+    except Exception as err:   # noqa: BLE001
+        return {"impl": "reference-triton", "unavailable": f"{type(err).__name__}: {err}"[:200]}
 
 
 def dtype_of(precision, impls):
@@ -460,11 +557,15 @@ def gpu_arm(args, dist, rank, world, local):
     line["roofline"] = roofline_of(exe, plan, precision)
     if world == 1:
         v, done, cores = cpu_block_tokens_per_s(seconds_budget=12.0)
+        v1, done1, _ = cpu_block_tokens_per_s(seconds_budget=6.0, threads=1)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": f"{done} of {SEQS} sequences x {TOKENS} tokens, eager PyTorch float32 (oneDNN)"}
+                                "sample": f"{done} of {SEQS} sequences x {TOKENS} tokens, eager PyTorch float32 (oneDNN)",
+                                "one_thread": {"value": v1, "unit": UNIT, "cores": 1,
+                                               "sample": f"{done1} sequences x {TOKENS} tokens"}}
         if not args.no_extras:
             try:
                 line["extras"] = extras(precision)
+                line["extras"]["reference_triton"] = reference_triton_extra(precision)
             except Exception as err:   # noqa: BLE001  (extras never invalidate the headline line)
                 line["extras"] = {"error": f"{type(err).__name__}: {err}"[:200]}
     print(json.dumps(line), flush=True)

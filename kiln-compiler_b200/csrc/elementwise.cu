@@ -279,10 +279,12 @@ int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
       for (int i = 0; i < rank; ++i) p.stride[o][i] = (int32_t)(k.ops[o].stride[i] * (i == rank - 1 ? 4 : 1));
     }
     p.chain = k.chain;
-    constexpr int U = 4;
+    constexpr int U = 2;
     int64_t blocks = ((int64_t)p.nvec + 256 * U - 1) / (256 * U);
-    int64_t cap = (int64_t)plan.sm_count * 16;
-    const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+    // beyond the cap every block takes the same number of grid-stride steps (no ragged last wave)
+    const int64_t cap = (int64_t)plan.sm_count * 64;
+    const int64_t steps = (blocks + cap - 1) / cap;
+    const unsigned grid = (unsigned)((blocks + steps - 1) / (steps > 0 ? steps : 1));
     switch (rank) {
       case 1: launch_kernel(plan.pdl, ew_chain_vec4_kernel<1, U>, dim3(grid), dim3(256), 0, s, p); break;
       case 2: launch_kernel(plan.pdl, ew_chain_vec4_kernel<2, U>, dim3(grid), dim3(256), 0, s, p); break;
