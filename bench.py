@@ -276,7 +276,9 @@ def build_block(precision, tokens, seed, cuda_graphs=True):
 
     plan = PlanSpec.from_json(load_plan(f"gpt2_block_t{tokens}"))
     consts = W.plan_constants(plan.const_shapes, W.block_params(seed, tokens))
-    program = program_from_plan(plan, precision)
+    # per-kernel matmul configurations, e.g. KB200_BENCH_CONFIGS='{"k10": {"BN": 256}}' (experiments; default: the library's choice)
+    configs = json.loads(os.environ.get("KB200_BENCH_CONFIGS", "null"))
+    program = program_from_plan(plan, precision, configs)
     return GPUExecutable(program, plan.arena_bytes, consts, plan.input_shapes, plan.output_shapes,
                          cuda_graphs=cuda_graphs), plan
 

@@ -130,7 +130,7 @@ typedef struct kb200_kernel_desc {
   kb200_operand operands[KB200_MAX_OPERANDS];
   kb200_tape_op tape[KB200_MAX_TAPE];
   /* Tuner configuration, opaque to the reference seam (kiln/api.py:155-162):
-   * cfg[0] tile M, cfg[1] tile N, cfg[2] tile K, cfg[3] pipeline stages,
+   * cfg[0] tile M, cfg[1] tile N, cfg[2] 128-byte K slabs per pipeline stage (1 or 2), cfg[3] pipeline stages,
    * cfg[4] split-K factor, cfg[5] implementation override (0 = library picks),
    * cfg[6] reserved, cfg[7] epilogue stores of the tensor-core matmul (0 = library picks,
    * 1 = ordinary global stores, never bulk tensor stores, 2 = bulk stores but always the

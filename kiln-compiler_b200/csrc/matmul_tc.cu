@@ -62,7 +62,9 @@ struct TcParams {
   int bn;               // tile width, multiple of 32 (tf32) / 64 (bf16), <= 256
   int stages;
   int num_kb;           // K slabs
-  int slab_k;           // elements of K per slab: 32 (tf32) or 64 (bf16)
+  int slab_k;           // elements of K per slab (128 bytes): 32 (tf32) or 64 (bf16)
+  int kps;              // K slabs per pipeline stage (1 or 2): narrow tiles are bound by the issue cost of a stage, not its size
+  int step_k;           // elements of K per stage: kps * slab_k
   int chunk_n;          // elements of N per B box: 32 (tf32) or 64 (bf16)
   int b_step_bytes;     // bytes between consecutive MMA K steps inside a B chunk
   int b_sbo_bytes;      // bytes between the row groups of one swizzle atom of B
@@ -335,8 +337,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   // 1024-byte aligned tile area (the 128-byte swizzle pattern repeats every 1024 bytes)
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
-  const int b_tile_bytes = p.bn * kSlabBytes;
-  const int stage_bytes = kATileBytes + b_tile_bytes;
+  const int b_tile_bytes = p.kps * p.bn * kSlabBytes;      // B part of one stage (kps K slabs)
+  const int a_stage_bytes = p.kps * kATileBytes;           // A part of one stage
+  const int stage_bytes = a_stage_bytes + b_tile_bytes;
   uint8_t* epi_buf = smem_raw + (tiles - raw) + (size_t)p.stages * stage_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
@@ -390,10 +393,11 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const bool load_a = warp == 0;
       // everything the loop needs in registers: a lone thread pays full latency for every
       // dependent instruction, so the per-slab instruction count is what bounds the issue rate
-      const int stages = p.stages, num_units = p.num_units, slab_k = p.slab_k;
+      const int stages = p.stages, num_units = p.num_units, slab_k = p.slab_k, step_k = p.step_k, kps = p.kps;
       const int bn = p.bn, chunk_n = p.chunk_n, b_mode = p.b_mode, n_chunks = p.n_chunks;
-      const uint32_t chunk_bytes = (uint32_t)slab_k * kSlabBytes;
-      const uint32_t tx_bytes = load_a ? (uint32_t)kATileBytes : (uint32_t)b_tile_bytes;
+      const uint32_t chunk_bytes = (uint32_t)step_k * kSlabBytes;          // one column chunk of B: step_k rows of 128 bytes
+      const uint32_t b_slab_bytes = (uint32_t)bn * kSlabBytes;             // K-major B: one slab of bn rows
+      const uint32_t tx_bytes = load_a ? (uint32_t)a_stage_bytes : (uint32_t)b_tile_bytes;
       int s = 0;
       uint32_t wait_parity = 1;                // parity to wait for on the empty barriers of this pass over the ring
       bool ok = true;
@@ -403,8 +407,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         slab_range(p, ks, kb_begin, kb_end);
         const int m0 = tm_i * kTileM, n0 = tn_i * bn;
         const int n0_chunk = tn_i * n_chunks;
-        int k_elem = kb_begin * slab_k;
-        for (int kb = kb_begin; kb < kb_end; ++kb, k_elem += slab_k) {
+        int k_elem = kb_begin * step_k;
+        for (int kb = kb_begin; kb < kb_end; ++kb, k_elem += step_k) {
           const uint32_t full = full0 + 8 * s;
           if (!mbar_wait(empty0 + 8 * s, wait_parity, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 1); *abort_ptr = 1; }
@@ -414,15 +418,18 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           if (load_a) KB200_STAMP(0, tp);
           mbar_expect_tx(full, tx_bytes);
           const uint32_t a_dst = tiles + s * stage_bytes;
+          // a slab past the end of K (odd slab count with two slabs per stage) is a box outside the
+          // tensor: it arrives as zeros and adds nothing
           if (load_a) {
-            tma_load_3d(a_dst, &tma_a, full, k_elem, m0, batch);
-          } else if (b_mode == 0) {              // K-major B: one box, like A
-            tma_load_3d(a_dst + kATileBytes, &tma_b, full, k_elem, n0, batch);
-          } else if (b_mode == 1) {              // N-major B, all column chunks of the tile in one 4-D box
-            tma_load_4d(a_dst + kATileBytes, &tma_b, full, 0, k_elem, n0_chunk, batch);
+            for (int j = 0; j < kps; ++j) tma_load_3d(a_dst + j * kATileBytes, &tma_a, full, k_elem + j * slab_k, m0, batch);
+          } else if (b_mode == 0) {              // K-major B: one box per slab, like A
+            for (int j = 0; j < kps; ++j)
+              tma_load_3d(a_dst + a_stage_bytes + j * b_slab_bytes, &tma_b, full, k_elem + j * slab_k, n0, batch);
+          } else if (b_mode == 1) {              // N-major B, all column chunks of the tile and all slabs of the stage in one 4-D box
+            tma_load_4d(a_dst + a_stage_bytes, &tma_b, full, 0, k_elem, n0_chunk, batch);
           } else {                               // N-major B, N not a multiple of the chunk: one box per chunk
             for (int c = 0; c < n_chunks; ++c)
-              tma_load_3d(a_dst + kATileBytes + c * chunk_bytes, &tma_b, full, n0 + c * chunk_n, k_elem, batch);
+              tma_load_3d(a_dst + a_stage_bytes + c * chunk_bytes, &tma_b, full, n0 + c * chunk_n, k_elem, batch);
           }
           if (load_a) KB200_STAMP(1, tp);
 #ifdef KB200_TRACE
@@ -440,9 +447,13 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       // descriptors: everything but the 14-bit start address is fixed; advancing along K adds to it
       const uint64_t a_fixed = make_desc(0, 16, 1024);
       const uint64_t b_fixed = p.b_mode == 0 ? make_desc(0, 16, 1024)
-                                             : make_desc(0, (uint32_t)(p.slab_k * kSlabBytes), (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
+                                             : make_desc(0, (uint32_t)(p.step_k * kSlabBytes), (uint32_t)p.b_sbo_bytes, (uint32_t)p.b_layout);
       const uint32_t b_step16 = (p.b_mode == 0 ? 32u : (uint32_t)p.b_step_bytes) >> 4;
+      // K-major B keeps its slabs apart (bn rows each); N-major B continues down the rows of its chunks
+      const uint32_t b_slab16 = p.b_mode == 0 ? (uint32_t)(p.bn * kSlabBytes) >> 4 : 4u * b_step16;
       const uint32_t tiles16 = tiles >> 4, stage16 = (uint32_t)stage_bytes >> 4, a_tile16 = kATileBytes >> 4;
+      const uint32_t a_stage16 = (uint32_t)a_stage_bytes >> 4;
+      const int kps = p.kps;
       bool ok = true;
       int s = 0;
       uint32_t wait_parity = 0;
@@ -468,15 +479,17 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             break;
           }
           KB200_STAMP(2, tm);
-          const uint32_t a16 = tiles16 + (uint32_t)s * stage16;
-          const uint32_t b16 = a16 + a_tile16;
+          for (int j = 0; j < kps; ++j) {
+            const uint32_t a16 = tiles16 + (uint32_t)s * stage16 + (uint32_t)j * a_tile16;
+            const uint32_t b16 = tiles16 + (uint32_t)s * stage16 + a_stage16 + (uint32_t)j * b_slab16;
 #pragma unroll
-          for (int k = 0; k < kSlabBytes / 32; ++k) {
-            // 14-bit start-address field: in a cluster the shared window address carries the CTA rank in
-            // its upper bits, which must not spill into the neighbouring descriptor fields
-            umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu), idesc,
-                 accumulate, BF16);
-            accumulate = 1;
+            for (int k = 0; k < kSlabBytes / 32; ++k) {
+              // 14-bit start-address field: in a cluster the shared window address carries the CTA rank in
+              // its upper bits, which must not spill into the neighbouring descriptor fields
+              umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu), idesc,
+                   accumulate, BF16);
+              accumulate = 1;
+            }
           }
           umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
           KB200_STAMP(3, tm);
@@ -840,15 +853,20 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   (void)chunk_n;
   int stages = d.cfg[3] > 0 ? d.cfg[3] : kMaxStages;   // as deep as shared memory allows: the ring hides ~2000 cycles of TMA latency
   if (stages > kMaxStages) stages = kMaxStages;
-  const int stage_bytes = kATileBytes + bn * kSlabBytes;
+  // Two K slabs per stage for narrow tiles: a stage costs the producers and the MMA thread a fixed
+  // ~350 cycles of waits and commits on top of 62 per MMA, more than the tensor time of a narrow slab.
+  int kps = d.cfg[2] == 1 || d.cfg[2] == 2 ? d.cfg[2] : (bn <= 128 && k.K >= 4 * slab_k ? 2 : 1);
+  const int stage_bytes = kps * (kATileBytes + bn * kSlabBytes);
   while (stages > 2 && (size_t)stages * stage_bytes + kEpiBytes + 1024 > (size_t)kMaxDynamicSmem) --stages;
   TcParams& p = st->params;
   fill_matmul_params(k, &p.mm);
   p.bn = bn;
   p.stages = stages;
   p.slab_k = slab_k;
+  p.kps = kps;
+  p.step_k = kps * slab_k;
   p.chunk_n = chunk_n;
-  p.num_kb = (int)((k.K + slab_k - 1) / slab_k);
+  p.num_kb = (int)((k.K + p.step_k - 1) / p.step_k);      // pipeline steps along K
   p.b_step_bytes = (st->bf16 ? 16 : 8) * kSlabBytes;
   // An N-major operand of 32-bit elements must use the 128-byte swizzle on 32-byte atoms, whose
   // pattern repeats every 4 rows; 16-bit elements use the ordinary 128-byte swizzle (8 rows).
@@ -870,12 +888,12 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   // 768-wide layers): every SM then streams a share of the operands.
   int splits = d.cfg[4];
   if (splits <= 0) {
-    // Split K over a cluster only when the tiles leave more than half of the SMs idle and K is long:
-    // the cluster reduction costs about as much as 8 K slabs.
+    // Split K over a cluster only when the tiles leave more than half of the SMs idle and K is long
+    // (48 slabs and more, measured): parking, hand-shake and reduction cost about as much as 20 slabs.
     splits = 1;
-    if (p.num_tiles * 2 <= plan.sm_count && p.num_kb >= 16) {
+    if (p.num_tiles * 2 <= plan.sm_count && p.num_kb * kps >= 48) {
       splits = 2;
-      if (p.num_tiles * 4 <= plan.sm_count && p.num_kb >= 32) splits = 4;
+      if (p.num_tiles * 4 <= plan.sm_count) splits = 4;
     }
   }
   if (splits > p.num_kb) splits = p.num_kb;
@@ -945,10 +963,10 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     }
   }
   if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
-      !(p.b_mode == 1 ? encode_map4(&st->map_b, st->bf16, b_base, chunk_n, b_rows, b_cols / chunk_n, k.batch, b_row, b_batch, slab_k,
+      !(p.b_mode == 1 ? encode_map4(&st->map_b, st->bf16, b_base, chunk_n, b_rows, b_cols / chunk_n, k.batch, b_row, b_batch, p.step_k,
                                     bn / chunk_n, !st->bf16)
                       : encode_map(&st->map_b, st->bf16, b_base, b_cols, b_rows, k.batch, b_row, b_batch, p.b_kmajor ? slab_k : chunk_n,
-                                   p.b_kmajor ? bn : slab_k, !st->bf16 && !p.b_kmajor)))
+                                   p.b_kmajor ? bn : p.step_k, !st->bf16 && !p.b_kmajor)))
     return fail(KB200_ERR_UNSUPPORTED, "matmul %s: the operands cannot be described to TMA", d.name);
   // Bulk tensor stores need a column-contiguous output with 16-byte aligned base and strides (and the
   // same of the bf16 mirror when there is one); anything else keeps the ordinary stores.
@@ -1130,6 +1148,7 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.mm.ops[2].stride[0] = 0; p.mm.ops[2].stride[1] = n; p.mm.ops[2].stride[2] = 1;
   p.mm.chain.n = 0; p.mm.chain.first_slot = -1; p.mm.chain.out_slot = 2;
   p.bn = bn; p.stages = stages; p.slab_k = slab_k; p.chunk_n = chunk_n;
+  p.kps = 1; p.step_k = slab_k;
   p.num_kb = (int)((k + slab_k - 1) / slab_k);
   p.b_step_bytes = 16 * kSlabBytes;
   p.b_layout = 2; p.b_sbo_bytes = 1024;
