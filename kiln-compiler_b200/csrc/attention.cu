@@ -41,8 +41,9 @@ constexpr int kRows = 128;                   // queries per CTA and keys per til
 constexpr int kHeadDim = 64;
 constexpr int kSlab = kRows * 128;           // one [128 rows x 128 bytes] swizzled slab
 constexpr int kAttnThreads = 64 + 256;
-constexpr int kAttnSmem = 5 * 2 * kSlab + 1024;   // Q + 2 x K + 2 x V, two slabs each, + alignment slack
 constexpr int kXStride = 35;                 // floats per row of the merge buffers: odd, so rows spread over the banks
+// Q + 2 x K + 2 x V tiles (two 16 KB slabs each in float32, one in bf16), the two merge buffers, alignment slack
+constexpr int attn_smem(bool bf16) { return 5 * (bf16 ? 1 : 2) * kSlab + 2 * kRows * kXStride * 4 + 1024; }
 
 struct AttnParams {
   int T, H, q_tiles;
@@ -58,6 +59,13 @@ struct AttnParams {
 
 struct AttnState {
   CUtensorMap map_q, map_k, map_v;
+  // BF16 mode: Q, K and V are read from the bf16 mirror of the QKV projection's output (set after the
+  // mirror is allocated); the kernel then runs its matmuls with bf16 operands and P rounded to bf16.
+  bool bf16 = false;
+  const float* q_ptr = nullptr;
+  const float* k_ptr = nullptr;
+  const float* v_ptr = nullptr;
+  int64_t row_stride = 0;
   AttnParams params;
   dim3 grid;
   // When the planner put the merged-heads buffer over the (by then dead) QKV buffer, the fused
@@ -97,9 +105,13 @@ __device__ __forceinline__ float row_max32(const float (&v)[32], float m, int fi
   return m;
 }
 
+template <bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
+  // a [128 rows x 64 dims] operand tile is two 128-byte-wide slabs in float32, one in bf16
+  constexpr int kTileSlabs = BF16 ? 1 : 2;
+  constexpr int kTileBytes = kTileSlabs * kSlab;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[19];
   __shared__ uint32_t tmem_base_slot;
@@ -120,8 +132,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #endif
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t q_smem = (raw + 1023u) & ~1023u;
-  const uint32_t k_smem = q_smem + 2 * kSlab;       // ring of 2, each 2 slabs
-  const uint32_t v_smem = k_smem + 4 * kSlab;
+  const uint32_t k_smem = q_smem + kTileBytes;      // ring of 2 tiles
+  const uint32_t v_smem = k_smem + 2 * kTileBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
   //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer]
@@ -177,20 +189,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * kSlab);
+      mbar_expect_tx(q_full, kTileBytes);
       tma_load_3d(q_smem, &map_q, q_full, 0, q0, h);
-      tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, q0, h);
+      if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, q0, h);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); break; }
-        mbar_expect_tx(k_full + 8 * s, 2 * kSlab);
-        tma_load_3d(k_smem + s * 2 * kSlab, &map_k, k_full + 8 * s, 0, j * kRows, h);
-        tma_load_3d(k_smem + s * 2 * kSlab + kSlab, &map_k, k_full + 8 * s, 32, j * kRows, h);
+        mbar_expect_tx(k_full + 8 * s, kTileBytes);
+        tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, j * kRows, h);
+        if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, j * kRows, h);
         if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); break; }
-        mbar_expect_tx(v_full + 8 * s, 2 * kSlab);
-        tma_load_3d(v_smem + s * 2 * kSlab, &map_v, v_full + 8 * s, 0, j * kRows, h);
-        tma_load_3d(v_smem + s * 2 * kSlab + kSlab, &map_v, v_full + 8 * s, 32, j * kRows, h);
+        mbar_expect_tx(v_full + 8 * s, kTileBytes);
+        tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, j * kRows, h);
+        if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, j * kRows, h);
       }
     }
   } else if (warp == 1) {
@@ -202,12 +214,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int s = j & 1;
         if (!mbar_wait(k_full + 8 * s, (j >> 1) & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kb = k_smem + s * 2 * kSlab;
+        const uint32_t kb = k_smem + s * kTileBytes;
+        // 32 bytes of the head dimension per instruction: 8 float32 (TF32) or 16 bf16
 #pragma unroll
-        for (int kd = 0; kd < kHeadDim / 8; ++kd) {
+        for (int kd = 0; kd < kTileSlabs * 4; ++kd) {
           const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
           umma(tmem_base + (uint32_t)s * 128, make_desc(q_smem + off, 16, 1024), make_desc(kb + off, 16, 1024), p.idesc_qk,
-               kd != 0 ? 1u : 0u, false);
+               kd != 0 ? 1u : 0u, BF16);
         }
         umma_commit(sfull0 + 8 * s);
         umma_commit(k_empty + 8 * s);
@@ -220,15 +233,24 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(v_full + 8 * s, ph, abort_ptr)) { give_up(0x23); ok = false; return; }
-        const uint32_t vb = v_smem + s * 2 * kSlab;
+        const uint32_t vb = v_smem + s * kTileBytes;
         for (int g = 0; g < 2; ++g) {
           if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t o_addr = tmem_o0 + (uint32_t)(g * 2 + (j & 1)) * 64;
+          if (BF16) {
+            // P: two bf16 per TMEM column, 16 keys = 8 columns per instruction; V: [keys x 64 dims] bf16,
+            // one 128-byte swizzled row per key, 16 rows per instruction
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
-                    make_desc(vb + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1), p.idesc_pv, kk != 0 ? 1u : 0u, false);
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
+                      make_desc(vb + (uint32_t)(g * 4 + kk) * 2048, kSlab, 1024, 2), p.idesc_pv, kk != 0 ? 1u : 0u, true);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
+                      make_desc(vb + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1), p.idesc_pv, kk != 0 ? 1u : 0u, false);
+          }
           umma_commit(ofull0 + 8 * (g * 2 + (j & 1)));
         }
         umma_commit(v_empty + 8 * s);
@@ -302,8 +324,22 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         sum = probabilities32<false>(va, p.scale_log2, m_use, 0, 0);
         sum += probabilities32<false>(vb, p.scale_log2, m_use, 0, 0);
       }
-      tmem_st32(s_addr, va);
-      tmem_st32(s_addr + 32, vb);
+      if (BF16) {
+        // P rounded to bf16, two keys per 32-bit column: the group's 64 keys take the first 32 columns of
+        // its own 64-column share of the S buffer
+        float packed[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(va[2 * i], va[2 * i + 1]);
+          __nv_bfloat162 hi = __floats2bfloat162_rn(vb[2 * i], vb[2 * i + 1]);
+          packed[i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&lo));
+          packed[16 + i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&hi));
+        }
+        tmem_st32(s_addr, packed);
+      } else {
+        tmem_st32(s_addr, va);
+        tmem_st32(s_addr + 32, vb);
+      }
       tmem_st_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(pfull0 + 8 * (group * 2 + s));
@@ -321,7 +357,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (ok) fold(n_kv - 1, alpha_prev);
     // ---- merge the two groups' states; group g finishes head dims g*32 .. g*32+31 ----
     // Every MMA has completed (the last O_part arrived after all of them), so the K ring is free.
-    float* xbuf = reinterpret_cast<float*>(smem_raw + (k_smem - raw));      // [2][128][kXStride]
+    float* xbuf = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);   // [2][128][kXStride], its own 36 KB
     float* mine = xbuf + (size_t)(group * kRows + row) * kXStride;          // what this thread gives away
     const float* theirs = xbuf + (size_t)((group ^ 1) * kRows + row) * kXStride;
     if (ok) {
@@ -551,11 +587,16 @@ bool attention_try_fuse(Plan& plan, size_t i) {
     delete st;
     return false;
   }
-  if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) {
+  if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
+      cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess) {
     cudaGetLastError();
     delete st;
     return false;
   }
+  st->q_ptr = Q.ptr;
+  st->k_ptr = Ksrc.ptr;
+  st->v_ptr = V.ptr;
+  st->row_stride = rs;
   AttnParams& p = st->params;
   p.T = (int)T;
   p.H = (int)H;
@@ -599,8 +640,12 @@ bool attention_try_fuse(Plan& plan, size_t i) {
 
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   const AttnState* st = static_cast<const AttnState*>(k.attn);
-  KB200_CUDA(launch_kernel(plan.pdl, attention_kernel, st->grid, dim3(kAttnThreads), kAttnSmem, s, st->map_q, st->map_k, st->map_v,
-                           st->params));
+  if (st->bf16)
+    KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q, st->map_k,
+                             st->map_v, st->params));
+  else
+    KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
+                             st->map_k, st->map_v, st->params));
   if (st->staged_out) {
     const int64_t n4 = st->out_elems / 4;
     const int64_t blocks = (n4 + 255) / 256;
@@ -609,6 +654,48 @@ int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   }
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
+}
+
+// The span of the QKV projection's output the fused kernel reads (Q, K and V are views of it).
+bool attention_operand_span(const PlanKernel& k, const float** lo, const float** hi) {
+  const AttnState* st = static_cast<const AttnState*>(k.attn);
+  if (!st) return false;
+  const float* first = st->q_ptr < st->k_ptr ? st->q_ptr : st->k_ptr;
+  if (st->v_ptr < first) first = st->v_ptr;
+  const float* last = st->q_ptr > st->k_ptr ? st->q_ptr : st->k_ptr;
+  if (st->v_ptr > last) last = st->v_ptr;
+  *lo = first;
+  *hi = last + (int64_t)(st->params.T - 1) * st->row_stride + (int64_t)st->params.H * kHeadDim;
+  return true;
+}
+
+// BF16 mode: the producer of Q, K and V also writes them as bf16 into the mirror at `mirror_base +
+// (ptr - arena_base)`; read them from there (half the bytes, twice the tensor rate, P rounded to bf16).
+bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mirror_base) {
+  AttnState* st = static_cast<AttnState*>(k.attn);
+  if (!st) return false;
+  // When the planner put the output over the QKV buffer, the output's mirror lies over the operands'
+  // mirror as well: CTAs would overwrite bf16 operands others still read.  Keep the float32 operands then.
+  if (st->staged_out != nullptr) return false;
+  const __nv_bfloat16* m = static_cast<const __nv_bfloat16*>(mirror_base);
+  const __nv_bfloat16* q = m + (st->q_ptr - arena_base);
+  const __nv_bfloat16* kk = m + (st->k_ptr - arena_base);
+  const __nv_bfloat16* v = m + (st->v_ptr - arena_base);
+  const int64_t T = st->params.T, H = st->params.H, rs = st->row_stride;
+  if (!aligned16(q) || !aligned16(kk) || !aligned16(v) || rs % 8) return false;
+  CUtensorMap mq, mk, mv;
+  if (!encode_map(&mq, true, q, kHeadDim, T, H, rs, kHeadDim, 64, kRows, false) ||
+      !encode_map(&mk, true, kk, kHeadDim, T, H, rs, kHeadDim, 64, kRows, false) ||
+      !encode_map(&mv, true, v, kHeadDim, T, H, rs, kHeadDim, 64, kRows, false))
+    return false;
+  st->map_q = mq;
+  st->map_k = mk;
+  st->map_v = mv;
+  st->bf16 = true;
+  // D = F32, A/B = BF16: Q K^T both K-major, N = 128; P V with B N-major, N = 64; M = 128
+  st->params.idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kRows >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+  st->params.idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+  return true;
 }
 
 void attention_set_shadow(PlanKernel& k, void* shadow_out) {

@@ -2,20 +2,22 @@
 // tcgen05.mma -> TMEM accumulator -> epilogue from TMEM.  Role of the reference's matmul generator
 // with input_precision="tf32" (kiln/gpu/codegen.py:484-530), plus a BF16-operand mode.
 //
-// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles; 320 threads in three roles:
-//   warp 0      TMA producer: per K slab, one box of A (128 rows x 128 bytes, K-major) and BN/chunk
-//               boxes of B (slab rows x 128 bytes, N-major -- the layout the buffer-assignment pass
-//               guarantees for B, kiln/passes/buffers.py:208-217, so nothing is repacked), both
-//               written with the 128-byte swizzle the MMA descriptors expect.  Plain per-CTA loads.
-//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = BN, K = 32 bytes per
-//               instruction) on the slab and commits the stage back to the producer.
-//   warps 2..9  epilogue: tcgen05.ld 32 columns at a time, a 32 x 32 transpose through shared memory
-//               so that a warp's loads and stores cover 128 contiguous bytes of a row, the fused
-//               chain on registers (bias, GELU, residual, scale + mask ...).  The accumulator is
-//               double-buffered in TMEM: the epilogue of tile i overlaps the main loop of tile i+1.
+// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles; 384 threads in three roles:
+//   warps 0, 10  TMA producers, one thread per operand: per pipeline stage (one or two K slabs of 128
+//               bytes) boxes of A (128 rows x 128 bytes, K-major) and of B (N-major -- the layout the
+//               buffer-assignment pass guarantees for B, kiln/passes/buffers.py:208-217, so nothing is
+//               repacked -- or K-major), written with the 128-byte swizzle the MMA descriptors expect.
+//               Plain per-CTA loads.
+//   warps 1, 11  MMA issuers: one elected lane issues tcgen05.mma (M = 128, N = BN, K = 32 bytes per
+//               instruction) on a stage and commits it back to the producers.  Tiles up to 128
+//               columns use both, on alternate stages, each with an accumulator of its own.
+//   warps 2..9  epilogue: tcgen05.ld 32 columns at a time, the fused chain on registers (bias, GELU,
+//               residual, scale + mask ...), 32 x 32 blocks staged in shared memory and written with
+//               bulk tensor stores.  The accumulators are double-buffered in TMEM: the epilogue of
+//               tile i overlaps the main loop of tile i+1.
 // A is read K-major and B N-major straight from the planned buffers (float32, consumed as TF32).
-// In BF16 mode both operands are first converted into packed bf16 scratch (constants once at
-// bind, activations per launch) and the same kernel runs with kind::f16.
+// In BF16 mode the operands are bf16: read from the mirror their producers write, or converted
+// (constants once at bind, unmirrored activations per launch), and the same kernel runs with kind::f16.
 //
 // Every wait on an mbarrier is bounded.  When one runs out the thread records the site in the
 // plan's status word, raises a CTA-wide abort flag, and every role falls through to the common
@@ -43,7 +45,8 @@ constexpr int kATileBytes = kTileM * kSlabBytes;
 constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;
 constexpr int kProducerBWarp = 2 + kEpiWarps;      // the last warp fetches operand B
-constexpr int kThreads = 64 + 32 * kEpiWarps + 32; // producer (A) warp, MMA warp, epilogue warps, producer (B) warp
+constexpr int kIssuerBWarp = kProducerBWarp + 1;   // second MMA issuer (narrow tiles only)
+constexpr int kThreads = 64 + 32 * kEpiWarps + 64; // producer (A) warp, MMA warp, epilogue warps, producer (B) warp, second MMA warp
 // per epilogue warp: a 32 x 33 float transpose buffer, reused (as dense 32 x 32) as the staging block of
 // the bulk store, then a 32 x 32 bf16 staging block; both 128-byte aligned
 constexpr int kEpiStage16Offset = 4608;        // 512-byte aligned (64-byte swizzle); the float block is 1024-byte aligned
@@ -82,6 +85,8 @@ struct TcParams {
   int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
   int num_units;        // num_tiles * splits
   int store_mode;       // 0: the epilogue warps store with ordinary global stores; 1: bulk tensor stores from shared memory
+  int issuers;          // 1, or 2: two threads issue the MMAs of alternate pipeline stages into accumulators of their own
+  uint64_t magic_stages;   // ceil(2^40 / stages)
   int epi_rowwise;      // the epilogue keeps a lane per ROW (no transpose): the chain has no matrix operand
   int n_chunks;         // bn / chunk_n
   int tiles_per_batch;  // tiles_m * tiles_n
@@ -357,7 +362,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   if (warp == 0) {
     // one barrier per lane: full[0..7] | empty[0..7] | tfull[0..1] | tempty[0..1]
     if (lane == 0) abort_flag = 0;
-    if (lane < 2 * kMaxStages + 4) mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : (lane < kMaxStages ? 2 : 1));
+    if (lane < 2 * kMaxStages + 4)
+      mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : (lane < kMaxStages ? 2 : (lane >= 2 * kMaxStages ? (uint32_t)p.issuers : 1)));
     else if (lane < 2 * kMaxStages + 6) mbar_init(full0 + 8 * lane, (uint32_t)p.splits);   // one arrival per CTA of the cluster
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -439,10 +445,16 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+  } else if (warp == 1 || warp == kIssuerBWarp) {
+    // ---------------- MMA issuers ----------------
+    // One thread issues all MMAs, or (narrow tiles, where the ~62 cycles an MMA instruction costs
+    // its issuing thread exceed its tensor time) two threads in two warps issue alternate pipeline
+    // stages, each into an accumulator of its own; the epilogue adds the two.
+    const int q = warp == 1 ? 0 : 1;
+    if (lane == 0 && q < p.issuers) {
+      const int nq = p.issuers;
       const int stages = p.stages, splits = p.splits, num_units = p.num_units, bn = p.bn;
+      const uint64_t magic_stages = p.magic_stages;
       const uint32_t idesc = p.idesc;
       // descriptors: everything but the 14-bit start address is fixed; advancing along K adds to it
       const uint64_t a_fixed = make_desc(0, 16, 1024);
@@ -455,13 +467,13 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const uint32_t a_stage16 = (uint32_t)a_stage_bytes >> 4;
       const int kps = p.kps;
       bool ok = true;
-      int s = 0;
-      uint32_t wait_parity = 0;
+      int g0 = 0;          // pipeline steps of this CTA before the current tile: step g uses stage g % stages
       int i = 0;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++i) {
         const int ks = splits > 1 ? unit % splits : 0;
         int kb_begin, kb_end;
         slab_range(p, ks, kb_begin, kb_end);
+        const int n_steps = kb_end - kb_begin;
         const int acc = i & 1;
         const uint32_t aph = (i >> 1) & 1;
         // the epilogue must have drained this accumulator (two tiles ago) before it is overwritten
@@ -470,15 +482,18 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * bn);
+        const uint32_t tmem_d = tmem_base + (uint32_t)((acc * nq + q) * bn);
         uint32_t accumulate = 0;
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(full0 + 8 * s, wait_parity, abort_ptr)) {
+        // this issuer's steps of the tile: the global step numbers congruent to q modulo nq
+        for (int g = g0 + ((q - g0) & (nq - 1)); g < g0 + n_steps; g += nq) {
+          const int round = fast_div(g, magic_stages);
+          const int s = g - round * stages;
+          if (!mbar_wait(full0 + 8 * s, (uint32_t)round & 1u, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
             ok = false;
             break;
           }
-          KB200_STAMP(2, tm);
+          if (q == 0) KB200_STAMP(2, tm);
           for (int j = 0; j < kps; ++j) {
             const uint32_t a16 = tiles16 + (uint32_t)s * stage16 + (uint32_t)j * a_tile16;
             const uint32_t b16 = tiles16 + (uint32_t)s * stage16 + a_stage16 + (uint32_t)j * b_slab16;
@@ -492,13 +507,13 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             }
           }
           umma_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
-          KB200_STAMP(3, tm);
+          if (q == 0) KB200_STAMP(3, tm);
 #ifdef KB200_TRACE
           ++tm;
 #endif
-          if (++s == stages) { s = 0; wait_parity ^= 1; }
         }
-        if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA of this tile has completed
+        g0 += n_steps;
+        if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA this thread issued for the tile has completed
       }
     }
   } else if (warp < 2 + kEpiWarps) {
@@ -522,6 +537,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const int64_t m0 = (int64_t)tm_i * kTileM, n0 = (int64_t)tn_i * p.bn;
       const int64_t m_first = m0 + quad * 32;
       const bool direct = p.splits == 1;
+      int kb_begin_e, kb_end_e;
+      slab_range(p, ks, kb_begin_e, kb_end_e);
+      const bool two_accumulators = p.issuers == 2 && kb_end_e - kb_begin_e >= 2;   // with one step the second issuer had nothing to do
       // three staging slots per warp fit in the ring, and no later tile of this CTA will refill it
       const bool ring_staging = bulk && unit + (int)gridDim.x >= p.num_units && p.stages * stage_bytes >= kEpiWarps * 3 * kEpiSlotBytes;
       uint8_t* ring_slice = smem_raw + (tiles - raw) + (size_t)e * (3 * kEpiSlotBytes);
@@ -553,7 +571,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.0f;
         } else {
-          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
+          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.issuers * p.bn + c);
+          tmem_ld32(t_addr, v);
+          if (two_accumulators) {        // the second issuer's share of the K steps
+            float w[32];
+            tmem_ld32(t_addr + (uint32_t)p.bn, w);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += w[j];
+          }
         }
         if (bulk && !ring_staging) {
           // the bulk stores of the previous block must have read the staging memory before it is rewritten
@@ -875,8 +900,12 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.b_kmajor = k.ops[d.b_slot].stride[2] == 1 ? 0 : 1;
   p.b_mode = p.b_kmajor ? 0 : (k.N % chunk_n == 0 ? 1 : 2);
   p.debug = d.cfg[6];
+  // Narrow tiles are bound by the MMA issue rate of one thread: two issuers, an accumulator each.
+  // (measured: a gain at 64 columns, a loss at 128 where an MMA's tensor time already matches its issue cost)
+  p.issuers = ((d.cfg[6] & 256) || bn > 64) ? 1 : 2;       // debug bit 256: one issuer always
   p.tmem_cols = 32;
-  while (p.tmem_cols < 2 * bn) p.tmem_cols *= 2;           // two accumulators: the epilogue drains one while the next tile fills the other
+  while (p.tmem_cols < 2 * p.issuers * bn) p.tmem_cols *= 2;   // per issuer two accumulators: the epilogue drains one while the next tile fills the other
+  p.magic_stages = 0;     // set below, once the stage count is final
   p.tiles_m = (int)((k.M + kTileM - 1) / kTileM);
   p.tiles_n = (int)((k.N + bn - 1) / bn);
   p.num_tiles = p.tiles_m * p.tiles_n * (int)k.batch;
@@ -889,9 +918,9 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   int splits = d.cfg[4];
   if (splits <= 0) {
     // Split K over a cluster only when the tiles leave more than half of the SMs idle and K is long
-    // (48 slabs and more, measured): parking, hand-shake and reduction cost about as much as 20 slabs.
+    // (64 slabs and more, measured): parking, hand-shake and reduction cost about as much as 20 slabs.
     splits = 1;
-    if (p.num_tiles * 2 <= plan.sm_count && p.num_kb * kps >= 48) {
+    if (p.num_tiles * 2 <= plan.sm_count && p.num_kb * kps >= 64) {
       splits = 2;
       if (p.num_tiles * 4 <= plan.sm_count) splits = 4;
     }
@@ -903,6 +932,14 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   while (splits > 1 && (size_t)stages * stage_bytes < (size_t)kTileM * bn * sizeof(float)) splits = 1;
   p.splits = splits;
   p.num_units = p.num_tiles * splits;
+  p.magic_stages = ((uint64_t(1) << 40) + stages - 1) / stages;
+  {
+    // step numbers of one CTA are divided by multiplication, exact below 2^20
+    const int64_t grid_ctas = splits > 1 ? p.num_units : (p.num_units < plan.sm_count ? p.num_units : plan.sm_count);
+    const int64_t steps_per_cta = ((p.num_units + grid_ctas - 1) / grid_ctas) * (int64_t)p.num_kb;
+    if (steps_per_cta >= (int64_t(1) << 20))
+      return fail(KB200_ERR_UNSUPPORTED, "matmul %s: K loop too long for the tensor-core kernel", d.name);
+  }
   // instruction descriptor: D = F32, A/B = TF32 or BF16, A K-major, B MN-major, N = bn, M = 128
   const uint32_t fmt = st->bf16 ? 1u : 2u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | ((p.b_kmajor ? 0u : 1u) << 16) | ((uint32_t)(bn >> 3) << 17) |
@@ -1149,6 +1186,8 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.mm.chain.n = 0; p.mm.chain.first_slot = -1; p.mm.chain.out_slot = 2;
   p.bn = bn; p.stages = stages; p.slab_k = slab_k; p.chunk_n = chunk_n;
   p.kps = 1; p.step_k = slab_k;
+  p.issuers = 1;
+  p.magic_stages = ((uint64_t(1) << 40) + stages - 1) / stages;
   p.num_kb = (int)((k + slab_k - 1) / slab_k);
   p.b_step_bytes = 16 * kSlabBytes;
   p.b_layout = 2; p.b_sbo_bytes = 1024;

@@ -373,8 +373,56 @@ static int assign_shadows(Plan& plan) {
   const float* arena_lo = plan.arena;
   const float* arena_hi = plan.arena + plan.arena_bytes / 4;
   bool any = false;
+  // The latest kernel before `ki` that writes into the span x: returned when it is one that can also
+  // emit bf16 (LayerNorm, tensor-core matmul, fused attention) and its output covers x inside the arena.
+  auto mirroring_producer = [&](size_t ki, const Span& x) -> PlanKernel* {
+    for (size_t j = ki; j-- > 0;) {
+      PlanKernel& pj = plan.kernels[j];
+      if (pj.impl == IMPL_FUSED_AWAY) continue;
+      const DevOperand* out = nullptr;
+      int64_t out_elems = 0;
+      if (pj.impl == IMPL_ATTN_FUSED) {
+        out = attention_output(plan, j, &out_elems);
+      } else if (pj.impl == IMPL_ROW_LAYERNORM) {
+        out = &pj.ops[pj.out_slot];
+        out_elems = (pj.desc.iter_shape[0] - 1) * out->stride[0] + pj.desc.iter_shape[1];
+      } else if (pj.impl == IMPL_MM_TC && pj.has_chain) {
+        out = &pj.ops[pj.chain.out_slot];
+        out_elems = (pj.batch - 1) * out->stride[0] + (pj.M - 1) * out->stride[1] + (pj.N - 1) * out->stride[2] + 1;
+      } else {
+        // some other kernel: does it write into the operand at all?
+        bool writes = false;
+        for (int t = 0; t < pj.desc.n_tape; ++t)
+          if (pj.desc.tape[t].opcode == KB200_OP_STORE) {
+            const Span w = span_of(pj, pj.desc.tape[t].b);
+            writes = writes || (w.lo < x.hi && x.lo < w.hi);
+          }
+        if (writes) return nullptr;      // written by a kernel that cannot emit bf16: keep the conversion pass
+        continue;
+      }
+      const Span w{out->ptr, out->ptr + out_elems};
+      if (!(w.lo < x.hi && x.lo < w.hi)) continue;                 // does not touch the operand
+      if (w.lo <= x.lo && w.hi >= x.hi && w.lo >= arena_lo && w.hi <= arena_hi) return &pj;
+      return nullptr;
+    }
+    return nullptr;
+  };
+  std::vector<size_t> attention_readers;
   for (size_t ki = 0; ki < plan.kernels.size(); ++ki) {
     PlanKernel& k = plan.kernels[ki];
+    if (k.impl == IMPL_ATTN_FUSED && ki + 1 < plan.kernels.size() && plan.kernels[ki + 1].desc.precision == KB200_PREC_BF16) {
+      // the fused attention reads Q, K and V (views of one projection's output) as bf16 when that
+      // projection can write them so
+      Span x{nullptr, nullptr};
+      if (attention_operand_span(k, &x.lo, &x.hi) && x.lo >= arena_lo && x.hi <= arena_hi && (x.lo - arena_lo) % 8 == 0) {
+        if (PlanKernel* pj = mirroring_producer(ki, x)) {
+          pj->shadow_out = reinterpret_cast<void*>(1);
+          attention_readers.push_back(ki);
+          any = true;
+        }
+      }
+      continue;
+    }
     if (k.impl != IMPL_MM_TC || !matmul_wants_bf16_operands(k)) continue;
     for (int role = 0; role < 2; ++role) {
       const int slot = role == 0 ? k.desc.a_slot : k.desc.b_slot;
@@ -384,42 +432,10 @@ static int assign_shadows(Plan& plan) {
       // the mirror is read through TMA: 16-byte aligned base and strides in 2-byte elements
       const DevOperand& xo = k.ops[slot];
       if ((x.lo - arena_lo) % 8 || xo.stride[0] % 8 || xo.stride[1] % 8 || xo.stride[2] % 8 && xo.stride[2] != 1) continue;
-      // the latest earlier kernel whose output overlaps the operand
-      for (size_t j = ki; j-- > 0;) {
-        PlanKernel& pj = plan.kernels[j];
-        if (pj.impl == IMPL_FUSED_AWAY) continue;
-        const DevOperand* out = nullptr;
-        int64_t out_elems = 0;
-        bool contiguous = false;
-        if (pj.impl == IMPL_ATTN_FUSED) {
-          out = attention_output(plan, j, &out_elems);
-          contiguous = true;
-        } else if (pj.impl == IMPL_ROW_LAYERNORM) {
-          out = &pj.ops[pj.out_slot];
-          out_elems = (pj.desc.iter_shape[0] - 1) * out->stride[0] + pj.desc.iter_shape[1];
-        } else if (pj.impl == IMPL_MM_TC && pj.has_chain) {
-          out = &pj.ops[pj.chain.out_slot];
-          out_elems = (pj.batch - 1) * out->stride[0] + (pj.M - 1) * out->stride[1] + (pj.N - 1) * out->stride[2] + 1;
-        } else {
-          // some other kernel: does it write into the operand at all?
-          bool writes = false;
-          for (int t = 0; t < pj.desc.n_tape; ++t)
-            if (pj.desc.tape[t].opcode == KB200_OP_STORE) {
-              const Span w = span_of(pj, pj.desc.tape[t].b);
-              writes = writes || (w.lo < x.hi && x.lo < w.hi);
-            }
-          if (writes) break;      // written by a kernel that cannot emit bf16: keep the conversion pass
-          continue;
-        }
-        (void)contiguous;
-        const Span w{out->ptr, out->ptr + out_elems};
-        if (!(w.lo < x.hi && x.lo < w.hi)) continue;                 // does not touch the operand
-        if (w.lo <= x.lo && w.hi >= x.hi && w.lo >= arena_lo && w.hi <= arena_hi) {
-          pj.shadow_out = reinterpret_cast<void*>(1);                // marked; the address is filled in below
-          (role == 0 ? k.a_shadow : k.b_shadow) = reinterpret_cast<const void*>(1);
-          any = true;
-        }
-        break;
+      if (PlanKernel* pj = mirroring_producer(ki, x)) {
+        pj->shadow_out = reinterpret_cast<void*>(1);                // marked; the address is filled in below
+        (role == 0 ? k.a_shadow : k.b_shadow) = reinterpret_cast<const void*>(1);
+        any = true;
       }
     }
   }
@@ -447,6 +463,7 @@ static int assign_shadows(Plan& plan) {
     if (k.a_shadow) k.a_shadow = mirror_of(k.ops[k.desc.a_slot].ptr);
     if (k.b_shadow) k.b_shadow = mirror_of(k.ops[k.desc.b_slot].ptr);
   }
+  for (size_t ki : attention_readers) attention_use_mirror(plan.kernels[ki], plan.arena, plan.arena16);
   return KB200_OK;
 }
 
