@@ -311,8 +311,8 @@ def kernel_flops(kernel):
 # DRAM bytes (read + write) per launch of the 1024-token block's kernels in BF16 mode, from the
 # `ncu --set full` capture summarised in profiles/gpt2_block_t1024_bf16_launches_and_top_kernels.md.
 NCU_DRAM_BYTES = {
-    ("bf16", "k0_row"): 3.16e6, ("bf16", "k1_matmul"): 5.21e6, ("bf16", "k2_ew0"): 9.50e6, ("bf16", "k7_matmul"): 5.99e6,
-    ("bf16", "k8_row"): 3.16e6, ("bf16", "k9_matmul"): 6.40e6, ("bf16", "k10_matmul"): 14.25e6,
+    ("bf16", "k0_row"): 3.16e6, ("bf16", "k1_matmul"): 5.21e6, ("bf16", "k2_ew0"): 4.77e6, ("bf16", "k7_matmul"): 6.00e6,
+    ("bf16", "k8_row"): 3.16e6, ("bf16", "k9_matmul"): 6.41e6, ("bf16", "k10_matmul"): 14.26e6,
 }
 
 
@@ -493,53 +493,35 @@ def gpu_arm(args, dist, rank, world, local):
         raise SystemExit("bench.py: no CUDA device (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     precision = args.precision
-    exe, plan = build_block(precision, TOKENS, SEED)
     host = [torch.from_numpy(W.block_input(SEED, TOKENS, index=rank * SEQS + i)).pin_memory() for i in range(SEQS)]
     dev_in = torch.stack([h.cuda(non_blocking=True) for h in host])
     dev_out = torch.empty_like(dev_in)
     host_out = [torch.empty(TOKENS, D).pin_memory() for _ in range(SEQS)]
     torch.cuda.synchronize()
 
-    # INFLIGHT compiled modules (each with its own arena and CUDA graph) run round-robin on their own
-    # streams, as a server keeps several requests in flight: kernels of one sequence fill the SMs
-    # another leaves idle, and copies overlap kernels.
-    exes = [exe] + [build_block(precision, TOKENS, SEED)[0] for _ in range(INFLIGHT - 1)]
-    streams = [torch.cuda.Stream() for _ in range(INFLIGHT)]
+    # INFLIGHT compiled modules (own arena, static buffers and stream each) run round-robin, as a server
+    # keeps several requests in flight: kernels of one sequence fill the SMs another leaves idle, and
+    # copies overlap kernels.  A whole step of 64 sequences is one CUDA graph (kiln_b200.runtime.
+    # StreamedBatch), so a busy host does not starve the GPU of launches.
+    from kiln_b200.runtime import StreamedBatch
 
-    def fan_out(body):
-        cur = torch.cuda.current_stream()
-        for st in streams:
-            st.wait_stream(cur)
-        for i in range(SEQS):
-            j = i % INFLIGHT
-            with torch.cuda.stream(streams[j]):
-                body(i, exes[j])
-        for st in streams:
-            cur.wait_stream(st)
-
-    def resident_one(i, e):
-        e.static_inputs[0].copy_(dev_in[i], non_blocking=True)
-        e.run_static()
-        dev_out[i].copy_(e.static_outputs[0], non_blocking=True)
-
-    def e2e_one(i, e):
-        (y,) = e(host[i])
-        host_out[i].copy_(y, non_blocking=True)
-
-    def step_resident():
-        fan_out(resident_one)
-
-    def step_e2e():
-        fan_out(e2e_one)
+    exe, plan = build_block(precision, TOKENS, SEED, cuda_graphs=False)
+    exes = [exe] + [build_block(precision, TOKENS, SEED, cuda_graphs=False)[0] for _ in range(INFLIGHT - 1)]
+    resident = StreamedBatch(exes).capture(list(dev_in), list(dev_out))
+    step_resident = resident.run
 
     for _ in range(args.warmup):
         step_resident()
     with ClockSampler(local) as clocks:
         ms = time_region(dist, step_resident, args.steps)
-    exe.status()
+    resident.status()
+    # end to end: the same step with pinned host tensors as sources and sinks (201 MB each way per step)
+    e2e = StreamedBatch(exes).capture(host, host_out)
+    step_e2e = e2e.run
     for _ in range(max(1, args.warmup // 2)):
         step_e2e()
     ms_e2e = time_region(dist, step_e2e, args.steps)
+    e2e.status()
     tokens = world * SEQS * TOKENS * args.steps
     value, e2e_value = tokens / (ms * 1e-3), tokens / (ms_e2e * 1e-3)
     if rank != 0:

@@ -880,9 +880,20 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   if (stages > kMaxStages) stages = kMaxStages;
   // Two K slabs per stage for narrow tiles: a stage costs the producers and the MMA thread a fixed
   // ~350 cycles of waits and commits on top of 62 per MMA, more than the tensor time of a narrow slab.
-  int kps = d.cfg[2] == 1 || d.cfg[2] == 2 ? d.cfg[2] : (bn <= 128 && k.K >= 4 * slab_k ? 2 : 1);
+  // Two MMA issuers (alternate pipeline steps, an accumulator each) are built in for 64-column tiles,
+  // whose MMAs cost more to issue than to execute, but off unless asked for (debug bit 512): they need an
+  // even stage count (below), and with the shallower or finer ring that leaves, they measured slower
+  // than one issuer with two slabs per stage (k10 of the block: 19.5 against 17.8 us).
+  const int issuers = ((d.cfg[6] & 512) && bn <= 64) ? 2 : 1;
+  // With two issuers one slab per stage (so that the ring can be deep and even), else two for tiles up to 128 columns.
+  int kps = d.cfg[2] == 1 || d.cfg[2] == 2 ? d.cfg[2] : (issuers == 2 ? 1 : (bn <= 128 && k.K >= 4 * slab_k ? 2 : 1));
   const int stage_bytes = kps * (kATileBytes + bn * kSlabBytes);
   while (stages > 2 && (size_t)stages * stage_bytes + kEpiBytes + 1024 > (size_t)kMaxDynamicSmem) --stages;
+  // Two issuers take alternate pipeline steps.  A wait on an mbarrier tells apart only two consecutive
+  // phases, so every stage must belong to ONE issuer, who then sees each of its phases in turn: with an
+  // even stage count step g and stage g % stages have the same parity.  (With an odd count ownership
+  // alternates, and an issuer a full round ahead takes the phase before last for its own.)
+  if (issuers == 2) stages &= ~1;
   TcParams& p = st->params;
   fill_matmul_params(k, &p.mm);
   p.bn = bn;
@@ -900,9 +911,7 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.b_kmajor = k.ops[d.b_slot].stride[2] == 1 ? 0 : 1;
   p.b_mode = p.b_kmajor ? 0 : (k.N % chunk_n == 0 ? 1 : 2);
   p.debug = d.cfg[6];
-  // Narrow tiles are bound by the MMA issue rate of one thread: two issuers, an accumulator each.
-  // (measured: a gain at 64 columns, a loss at 128 where an MMA's tensor time already matches its issue cost)
-  p.issuers = ((d.cfg[6] & 256) || bn > 64) ? 1 : 2;       // debug bit 256: one issuer always
+  p.issuers = issuers;
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * p.issuers * bn) p.tmem_cols *= 2;   // per issuer two accumulators: the epilogue drains one while the next tile fills the other
   p.magic_stages = 0;     // set below, once the stage count is final

@@ -250,3 +250,83 @@ class GPUExecutable:
             self.close()
         except Exception:   # noqa: BLE001  (interpreter shutdown)
             pass
+
+
+class StreamedBatch:
+    """Many independent requests through copies of one compiled module, as ONE CUDA graph.
+
+    A server that keeps several requests in flight gives each its own module (arena, weights'
+    tensor maps, static buffers) and stream, so that kernels of one request fill the SMs another
+    leaves idle and copies overlap kernels.  Enqueueing that from Python costs three calls per
+    request; under a busy host the GPU then waits for the launches.  Here the whole step -- for
+    request ``i``: copy ``sources[i]`` into module ``i % in_flight``'s input, run its kernels, copy
+    its output to ``sinks[i]`` -- is captured once, across ``in_flight`` streams, and replayed with
+    a single launch.  ``sources`` / ``sinks`` may be device tensors or pinned host tensors (the
+    copies are then host<->device copies inside the graph); their addresses are part of the graph,
+    so a caller refills the same tensors for the next step.
+
+    The reference has no counterpart: its executable replays one graph per call
+    (kiln/gpu/runtime.py:181-217).
+    """
+
+    def __init__(self, executables):
+        if not executables:
+            raise ValueError("StreamedBatch needs at least one executable")
+        for e in executables:
+            if e.use_cuda_graphs:
+                raise ValueError("StreamedBatch captures the launches itself: build the executables with cuda_graphs=False")
+        self.executables = list(executables)
+        self.device = executables[0].device
+        self.streams = [torch.cuda.Stream(device=self.device) for _ in executables]
+        self.graph = None
+        self.requests = 0
+
+    def _enqueue(self, sources, sinks):
+        cur = torch.cuda.current_stream(self.device)
+        for st in self.streams:
+            st.wait_stream(cur)
+        n = len(self.executables)
+        for i, (src, dst) in enumerate(zip(sources, sinks)):
+            exe = self.executables[i % n]
+            with torch.cuda.stream(self.streams[i % n]):
+                exe.static_inputs[0].copy_(src, non_blocking=True)
+                exe.run_static()
+                dst.copy_(exe.static_outputs[0], non_blocking=True)
+        for st in self.streams:
+            cur.wait_stream(st)
+
+    def capture(self, sources, sinks):
+        """Capture one step over these tensors (single-input, single-output modules)."""
+        if len(sources) != len(sinks):
+            raise ValueError("one sink per source")
+        for t in list(sources) + list(sinks):
+            if not t.is_cuda and not t.is_pinned():
+                raise ValueError("host tensors of a StreamedBatch must be pinned")
+        with torch.cuda.device(self.device):
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self._enqueue(sources, sinks)          # warm-up outside capture (lazy initialisation)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._enqueue(sources, sinks)
+        self.graph = graph
+        self.requests = len(sources)
+        return self
+
+    def run(self):
+        """Replay the captured step on the current stream (one launch)."""
+        if self.graph is None:
+            raise RuntimeError("StreamedBatch.run before capture")
+        self.graph.replay()
+
+    def status(self):
+        for e in self.executables:
+            e.status()
+
+    def close(self):
+        self.graph = None
+        for e in self.executables:
+            e.close()

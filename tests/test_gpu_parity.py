@@ -133,6 +133,53 @@ def test_replay_with_new_inputs():
     assert exe.graph is not None
 
 
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("case", ["gpt2_block_t1024", "gpt2_block_t128", "mlp_2048"])
+def test_second_mma_issuer_and_dependent_launch(case, precision, monkeypatch):
+    """64-column tiles with two MMA issuers (opt-in, even ring), with and without programmatic dependent
+    launch between kernels, against the float64 oracle."""
+    from gpu_helpers import build_executable, run_case
+
+    monkeypatch.setenv("KILN_GPU_DEPENDENT_LAUNCH", "0" if case == "mlp_2048" else "1")      # both launch orders
+    names = [n for n in build_executable(case, precision).kernel_names if "matmul" in n]
+    exe, outs, (plan, inputs, consts, _) = run_case(
+        case, precision, configs={n.split("_")[0]: {"BN": 64, "debug": 512, "impl": "tc"} for n in names})
+    exact = run_plan(plan, inputs, consts, dtype=np.float64)
+    for got, ref64 in zip(outs, exact):
+        assert scale_relative_error(got, ref64) <= REL_TOL[precision], (case, precision, exe.impls)
+
+
+def test_streamed_batch_equals_one_call_per_request():
+    """Seven requests through three modules in flight, the step captured as one CUDA graph, device and
+    pinned-host tensors as sources and sinks: the same bits as one __call__ per request."""
+    from gpu_helpers import build_executable
+    from kiln_b200 import workloads as W
+    from kiln_b200.runtime import StreamedBatch
+
+    case = "gpt2_block_t128"
+    xs = [torch.from_numpy(W.block_input(0, 128, index=i)) for i in range(7)]
+    single = build_executable(case, "tf32")
+    want = [single(x)[0].cpu() for x in xs]
+    batch = StreamedBatch([build_executable(case, "tf32", cuda_graphs=False) for _ in range(3)])
+    with pytest.raises(ValueError):
+        batch.capture(xs, [torch.empty_like(x) for x in xs])          # pageable host memory
+    dev_in, dev_out = [x.cuda() for x in xs], [torch.empty(128, 768, device="cuda") for _ in xs]
+    batch.capture(dev_in, dev_out).run()
+    torch.cuda.synchronize()
+    batch.status()
+    for got, ref in zip(dev_out, want):
+        assert torch.equal(got.cpu(), ref)
+    host_in, host_out = [x.pin_memory() for x in xs], [torch.empty(128, 768).pin_memory() for _ in xs]
+    batch.capture(host_in, host_out)
+    for _ in range(2):
+        batch.run()
+    torch.cuda.synchronize()
+    for got, ref in zip(host_out, want):
+        assert torch.equal(got, ref)
+    with pytest.raises(ValueError):
+        StreamedBatch([single])                                       # modules that replay their own graph
+
+
 def test_wrong_shape_and_memory_errors(monkeypatch):
     from gpu_helpers import build_executable
     from kiln_b200.runtime import check_memory
