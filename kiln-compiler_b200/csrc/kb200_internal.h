@@ -36,7 +36,9 @@ struct DevTape {
 // tape when every value feeds only the next op; lets the vectorised kernels keep v in registers.
 enum ChainOp : int {
   CH_ADD = 0, CH_SUB, CH_RSUB, CH_MUL, CH_DIV, CH_RDIV, CH_MAX, CH_MIN,
-  CH_NEG, CH_RELU, CH_EXP, CH_TANH, CH_SIGMOID, CH_ERF, CH_GELU_TANH, CH_GELU_ERF, CH_RSQRT, CH_SQRT, CH_COPY
+  CH_NEG, CH_RELU, CH_EXP, CH_TANH, CH_SIGMOID, CH_ERF, CH_GELU_TANH, CH_GELU_ERF, CH_RSQRT, CH_SQRT, CH_COPY,
+  // BF16-mode matmul epilogues only (set at bind): tanh through the one-instruction approximation
+  CH_TANH_APPROX, CH_GELU_TANH_APPROX
 };
 constexpr int kMaxChain = 8;
 struct ChainStep {

@@ -128,6 +128,14 @@ __device__ __forceinline__ float f_tanh(float x) {
   const float t = __fdividef(1.0f - e, 1.0f + e);
   return x < 0.0f ? -t : t;
 }
+// BF16 mode only: one MUFU instruction (relative error 2^-11; the block's output moves by 1e-3 of its
+// scale, against a budget of 2e-2) instead of ex2 + rcp.  The GELU epilogue of a 128 x 256 tile is bound
+// by the MUFU and issue rates of its eight warps: this takes 2 us off the block's 768 -> 3072 layer.
+__device__ __forceinline__ float f_tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float f_erf(float x) {
   const float a = fabsf(x);
   const float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
@@ -159,6 +167,8 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
     case CH_ERF: KB200_EACH(f_erf(x)) break;
     case CH_GELU_TANH: KB200_EACH(0.5f * x * (1.0f + f_tanh(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
     case CH_GELU_ERF: KB200_EACH(0.5f * x * (1.0f + f_erf(x * 0.7071067811865476f))) break;
+    case CH_TANH_APPROX: KB200_EACH(f_tanh_approx(x)) break;
+    case CH_GELU_TANH_APPROX: KB200_EACH(0.5f * x * (1.0f + f_tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
     case CH_RSQRT: KB200_EACH(rsqrtf(x)) break;
     case CH_SQRT: KB200_EACH(sqrtf(x)) break;
     default: break;
@@ -896,6 +906,13 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   if (issuers == 2) stages &= ~1;
   TcParams& p = st->params;
   fill_matmul_params(k, &p.mm);
+  if (st->bf16) {
+    for (int s_i = 0; s_i < p.mm.chain.n; ++s_i) {
+      int& op = p.mm.chain.steps[s_i].op;
+      if (op == CH_TANH) op = CH_TANH_APPROX;
+      else if (op == CH_GELU_TANH) op = CH_GELU_TANH_APPROX;
+    }
+  }
   p.bn = bn;
   p.stages = stages;
   p.slab_k = slab_k;
