@@ -534,7 +534,7 @@ def gpu_arm(args, dist, rank, world, local):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": SEQS * TOKENS * D * 4,
                 "d2h_bytes_per_step": SEQS * TOKENS * D * 4, "ms_per_step": ms_e2e / args.steps,
                 "modules_in_flight": INFLIGHT},
-        "gpu_launches": args.steps * SEQS * exe.device_launches, "modules_in_flight": INFLIGHT,
+        "gpu_launches": world * args.steps * SEQS * exe.device_launches, "modules_in_flight": INFLIGHT,
         "clocks": clocks.summary(),
         "impls": dict(zip(exe.kernel_names, exe.impls)),
     }
