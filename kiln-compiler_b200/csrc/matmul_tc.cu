@@ -74,7 +74,7 @@ struct TcParams {
   int b_layout;         // descriptor layout type of B (1 = 128-byte swizzle on 32-byte atoms, 2 = 128-byte swizzle)
   int b_kmajor;         // B is read K-major ([N, K] with K contiguous) like A
   int b_mode;           // how B is fetched: 0 K-major (one box), 1 N-major, all chunks in one 4-D box, 2 N-major, a box per chunk
-  int debug;            // timing experiments only: 1 = no stores, 2 = no MMA, 4 = no TMA (results are then wrong)
+  int debug;            // experiments: 1 = no stores, 16 = no epilogue (results are then wrong); 32 = no warm-up pass, 512 = two MMA issuers
   int tmem_cols;        // power of two >= bn, >= 32
   uint32_t idesc;
   int kernel_index;
