@@ -495,9 +495,11 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         const uint32_t tmem_d = tmem_base + (uint32_t)((acc * nq + q) * bn);
         uint32_t accumulate = 0;
         // this issuer's steps of the tile: the global step numbers congruent to q modulo nq
-        for (int g = g0 + ((q - g0) & (nq - 1)); g < g0 + n_steps; g += nq) {
-          const int round = fast_div(g, magic_stages);
-          const int s = g - round * stages;
+        // (stage, round) of step g: counted along with one issuer, by multiplication for two
+        int g_first = g0 + ((q - g0) & (nq - 1));
+        int round = fast_div(g_first, magic_stages);
+        int s = g_first - round * stages;
+        for (int g = g_first; g < g0 + n_steps; g += nq) {
           if (!mbar_wait(full0 + 8 * s, (uint32_t)round & 1u, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
             ok = false;
@@ -521,6 +523,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #ifdef KB200_TRACE
           ++tm;
 #endif
+          s += nq;
+          if (s >= stages) { s -= stages; ++round; }
         }
         g0 += n_steps;
         if (ok) umma_commit(tfull0 + 8 * acc);   // arrives when every MMA this thread issued for the tile has completed
