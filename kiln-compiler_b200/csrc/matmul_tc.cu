@@ -602,7 +602,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #ifdef KB200_TRACE
         if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
-        if (!rowwise) {
+        if (!rowwise && direct) {
           // transpose through shared memory: lane = row  ->  lane = column
 #pragma unroll
           for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = v[j];
@@ -660,8 +660,11 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           if (warp == 2 && lane == 0 && !dry) { KB200_STAMP(4, te); ++te; }
 #endif
         } else {
+          // split K: park this lane's row of the partial tile, eight 128-bit stores whose 16-byte slot
+          // within the 32-column group is XORed with the row (no bank conflicts; the reduction undoes it)
+          float4* dst = reinterpret_cast<float4*>(part + (size_t)lane * p.bn + c);
 #pragma unroll
-          for (int r = 0; r < 32; ++r) part[r * p.bn + c + lane] = v[r];
+          for (int q = 0; q < 8; ++q) dst[q ^ (lane & 7)] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
       }
       // this warp is done reading the accumulator: hand it back to the MMA issuer
@@ -690,7 +693,13 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && threadIdx.x == 0) marks[3] = clock64();
 #endif
-    if (threadIdx.x < (unsigned)p.splits) mbar_arrive_cluster(map_to_cta(parked, threadIdx.x));
+    // (measured: the cluster-scope release carried by this first arrival takes 5500-6200 cycles, whichever
+    // warp makes it and however the tile was parked; the second one below ~1000.  It is the fixed cost
+    // that keeps split K from paying below ~64 slabs of K.)
+    if (warp == kIssuerBWarp && lane < p.splits) mbar_arrive_cluster(map_to_cta(parked, (uint32_t)lane));
+#ifdef KB200_TRACE
+    if (blockIdx.x <= 1 && warp == kIssuerBWarp && lane == 0) marks[7] = clock64();
+#endif
     if (!mbar_wait_cluster(parked, 0, abort_ptr) && threadIdx.x == 0 && !*abort_ptr) {
       atomicCAS(p.status, 0, (p.kernel_index << 8) | 5);
       *abort_ptr = 1;
@@ -720,12 +729,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         float v[32];
 #pragma unroll
         for (int r = 0; r < 32; ++r) v[r] = 0.0f;
-        const uint32_t local = tiles + (uint32_t)((row_base * p.bn + cb * 32 + lane) * 4);
+        const uint32_t local = tiles + (uint32_t)((row_base * p.bn + cb * 32) * 4);
         for (int sp = 0; sp < p.splits; ++sp) {
           const uint32_t remote = map_to_cta(local, (uint32_t)sp);
 #pragma unroll
           for (int r = 0; r < 32; ++r)
-            if (r < nrows) v[r] += ld_cluster_f32(remote + (uint32_t)(r * p.bn * 4));
+            if (r < nrows)
+              v[r] += ld_cluster_f32(remote + (uint32_t)(r * p.bn * 4) +
+                                     (uint32_t)((((lane >> 2) ^ ((row_base + r) & 7)) << 4) | ((lane & 3) << 2)));
         }
         epilogue_compute32(p, v, pre_col, pre_mat, batch, m0 + row_base, n, nrows);
         if (p.store_mode == 1 && nrows == 32) {
@@ -752,7 +763,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     if (blockIdx.x <= 1 && threadIdx.x == 64) marks[5] = clock64();
 #endif
     __syncthreads();         // this CTA no longer reads its neighbours' shared memory ...
-    if (threadIdx.x < (unsigned)p.splits) mbar_arrive_cluster(map_to_cta(released, threadIdx.x));
+    if (warp == kIssuerBWarp && lane < p.splits) mbar_arrive_cluster(map_to_cta(released, (uint32_t)lane));
     // ... and leaves (frees its own) only when no neighbour reads it any more
     if (threadIdx.x == 0 && !mbar_wait_cluster(released, 0, abort_ptr) && !*abort_ptr) {
       atomicCAS(p.status, 0, (p.kernel_index << 8) | 6);
@@ -768,8 +779,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   __syncthreads();
 #ifdef KB200_TRACE
   if (blockIdx.x == 1 && threadIdx.x == 0 && p.splits > 1)
-    printf("block1 split phase: entry globaltimer %lld setup_done %lld before cluster sync %lld after %lld reduce done %lld after 2nd sync %lld\n",
-           marks[0], marks[2] - marks[1], marks[3] - marks[1], marks[4] - marks[1], marks[5] - marks[1], marks[6] - marks[1]);
+    printf("block1 split phase: entry globaltimer %lld setup_done %lld before cluster sync %lld arrived %lld after %lld reduce done %lld after 2nd sync %lld\n",
+           marks[0], marks[2] - marks[1], marks[3] - marks[1], marks[7] - marks[1], marks[4] - marks[1], marks[5] - marks[1], marks[6] - marks[1]);
 #endif
 #ifdef KB200_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) {
