@@ -44,7 +44,7 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 SEQS, TOKENS, D, HEADS, SEED = 64, 1024, 768, 12, 4
-INFLIGHT = 6          # compiled modules kept in flight (own stream, arena and CUDA graph each); 6 reaches the host-link bound
+INFLIGHT = int(os.environ.get("KB200_BENCH_INFLIGHT", "6"))          # compiled modules kept in flight (own stream, arena and CUDA graph each); 6 reaches the host-link bound
 METRIC, UNIT = "gpt2_block_tokens_per_s", "tokens/s"
 
 
