@@ -56,15 +56,55 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event (throttle) reasons through NVML every few milliseconds while
+    the timed region runs (read-only queries; `nvidia-smi -lms` is too slow for a 40 ms region), with
+    nvidia-smi as the fallback when the NVML bindings are missing."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.stop = threading.Event()
+        self.nvml = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        self.nvml = pynvml
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:   # noqa: BLE001
+            return pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll_nvml(self, handle):
+        n = self.nvml
+        bits = {"hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        mx = n.nvmlDeviceGetMaxClockInfo(handle, n.NVML_CLOCK_SM)
+        while not self.stop.is_set():
+            try:
+                sm = n.nvmlDeviceGetClockInfo(handle, n.NVML_CLOCK_SM)
+                mask = reasons_fn(handle)
+                self.rows.append([str(sm), str(mx)] + ["Active" if mask & bits[k] else "Not Active" for k in self.NAMES])
+            except Exception:   # noqa: BLE001
+                break
+            time.sleep(0.002)
 
     def __enter__(self):
+        try:
+            handle = self._nvml_handle()
+            self.thread = threading.Thread(target=self._poll_nvml, args=(handle,), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:   # noqa: BLE001  (no NVML bindings: fall back to the command-line tool)
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -80,17 +120,18 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self):
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             if len(r) < 6:
                 continue
@@ -99,11 +140,11 @@ class ClockSampler:
                 mx.append(float(r[1]))
             except ValueError:
                 continue
-            for name, flag in zip(names, r[2:6]):
+            for name, flag in zip(self.NAMES, r[2:6]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 def dist_setup(n):
