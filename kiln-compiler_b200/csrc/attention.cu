@@ -646,7 +646,7 @@ int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   else
     KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
                              st->map_k, st->map_v, st->params));
-  if (st->staged_out) {
+  if (st->staged_out && st->final_out) {
     const int64_t n4 = st->out_elems / 4;
     const int64_t blocks = (n4 + 255) / 256;
     KB200_CUDA(launch_kernel(plan.pdl, copy_rows_kernel, dim3((unsigned)(blocks < 1184 ? blocks : 1184)), dim3(256), 0, s,
@@ -696,6 +696,52 @@ bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mi
   st->params.idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kRows >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
   st->params.idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
   return true;
+}
+
+// When the output was staged (the planner put it over the QKV buffer), the copy back into the arena
+// is only needed if someone reads the float32 output there.  Later readers that take the bf16 mirror
+// do not; a tensor-core matmul whose A operand is exactly the output can read the staging buffer
+// instead.  If that accounts for every reader until the buffer is rewritten (or the plan ends: arena
+// contents are dead then), the copy launch is dropped.  Runs after the mirrors are assigned and
+// before the matmuls build their tensor maps.
+void attention_elide_copy(Plan& plan, size_t first) {
+  PlanKernel& holder = plan.kernels[first];
+  AttnState* st = static_cast<AttnState*>(holder.attn);
+  if (!st || !st->staged_out || !st->final_out || first + 4 >= plan.kernels.size()) return;
+  const PlanKernel& k6 = plan.kernels[first + 4];
+  if (k6.desc.operands[k6.chain.out_slot].base_kind != KB200_BASE_ARENA) return;     // a plan output must land where the caller looks
+  const int64_t width = (int64_t)st->params.H * kHeadDim;
+  if (st->y->stride[0] != width) return;
+  const Range y{st->final_out, st->final_out + st->out_elems};
+  std::vector<std::pair<PlanKernel*, int>> redirect;
+  bool rewritten = false;
+  for (size_t j = first + 5; j < plan.kernels.size() && !rewritten; ++j) {
+    PlanKernel& k = plan.kernels[j];
+    if (k.impl == IMPL_FUSED_AWAY) continue;
+    std::vector<int> reads, writes;
+    io_slots(k, &reads, &writes);
+    for (int slot : reads) {
+      const Range r = operand_range(k, slot);
+      if (!overlaps(r, y)) continue;
+      const bool is_a = k.desc.kclass == KB200_K_MATMUL && slot == k.desc.a_slot;
+      const bool is_b = k.desc.kclass == KB200_K_MATMUL && slot == k.desc.b_slot;
+      if (k.impl == IMPL_MM_TC && ((is_a && k.a_shadow) || (is_b && k.b_shadow))) continue;      // reads the mirror
+      if (k.impl == IMPL_MM_TC && is_a && k.batch == 1 && r.lo == y.lo && r.hi == y.hi && k.ops[slot].stride[1] == width &&
+          k.ops[slot].stride[2] == 1) {
+        redirect.push_back({&k, slot});
+        continue;
+      }
+      return;          // someone needs the float32 output where the plan put it
+    }
+    for (int slot : writes) {
+      const Range w = operand_range(k, slot);
+      if (covers(w, y)) rewritten = true;
+      else if (overlaps(w, y)) return;                 // partly rewritten: keep it simple, keep the copy
+    }
+  }
+  for (auto& [k, slot] : redirect) k->ops[slot].ptr = st->staged_out;
+  st->final_out = nullptr;
+  holder.launches = 1;
 }
 
 void attention_set_shadow(PlanKernel& k, void* shadow_out) {

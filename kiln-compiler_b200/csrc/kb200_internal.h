@@ -127,6 +127,7 @@ int bind_matmul(Plan& plan, PlanKernel& k);      // after pointers are resolved
 bool matmul_wants_bf16_operands(const PlanKernel& k);
 void attention_set_shadow(PlanKernel& k, void* shadow_out);
 bool attention_operand_span(const PlanKernel& k, const float** lo, const float** hi);
+void attention_elide_copy(Plan& plan, size_t first);
 bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mirror_base);
 const DevOperand* attention_output(const Plan& plan, size_t first, int64_t* elems);
 int launch_matmul(const Plan& plan, const PlanKernel& k, cudaStream_t s);

@@ -579,6 +579,8 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
       if (attention_try_fuse(plan, i)) i += 4;
   // phase 3: BF16 matmuls read activations from the bf16 mirror when their producer can write it
   if (rc == KB200_OK) rc = assign_shadows(plan);
+  for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i)
+    if (plan.kernels[i].impl == IMPL_ATTN_FUSED) attention_elide_copy(plan, i);
   // phase 4: tensor maps, packed weights, split-K workspaces
   for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i) {
     PlanKernel& k = plan.kernels[i];
