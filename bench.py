@@ -572,8 +572,8 @@ def gpu_arm(args, dist, rank, world, local):
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": dtype_of(precision, exe.impls), "data": "synthetic",
         "config": workload_config(precision, world),
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": SEQS * TOKENS * D * 4,
-                "d2h_bytes_per_step": SEQS * TOKENS * D * 4, "ms_per_step": ms_e2e / args.steps,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * SEQS * TOKENS * D * 4,
+                "d2h_bytes_per_step": world * SEQS * TOKENS * D * 4, "ms_per_step": ms_e2e / args.steps,
                 "modules_in_flight": INFLIGHT},
         "gpu_launches": world * args.steps * SEQS * exe.device_launches, "modules_in_flight": INFLIGHT,
         "clocks": clocks.summary(),
