@@ -476,8 +476,21 @@ def extras(precision):
                "us": round(best * 1e6, 2), "precision": mm_prec, "impl": exe.impls}
         if mm_peak and m > 1:
             row["frac_of_measured_peak"] = round(row["tflops"] / mm_peak, 3)
-        if m == 1:      # decode GEMV: weights streamed once
-            row["gbs"] = round((4 * k * n + 4 * n + 4 * k) / best / 1e9, 1)
+        if m == 1:      # decode GEMV: weights streamed once; cold = weight sets rotated through more than twice the L2
+            byts = 4 * k * n + 4 * n + 4 * k
+            row["gbs"] = round(byts / best / 1e9, 1)
+            n_sets = -(-2 * 126 * 2**20 // byts) + 1
+            sets = [exe] + [filled(f"linear_{m}x{n}x{k}", mm_prec) for _ in range(n_sets - 1)]
+
+            def rotate():
+                for e in sets:
+                    e.run_static()
+
+            cold_best, _ = graph_times(rotate, repeats=2, replays=50)
+            row["cold_gbs"] = round(byts * n_sets / cold_best / 1e9, 1)
+            row["cold_frac_of_measured_hbm"] = round(byts * n_sets / cold_best / 1e9 / pk["hbm_gbs"], 3)
+            for e in sets[1:]:
+                e.close()
         out[f"linear_{m}x{n}x{k}"] = row
         exe.close()
     for t, seed in ((128, 0), (2048, 4)):

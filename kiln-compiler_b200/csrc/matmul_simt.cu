@@ -88,10 +88,11 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) mm_simt_kernel(const __
 
 // Decode shape, M == 1: the weight matrix is read exactly once, so the kernel is bound by how many
 // bytes it keeps in flight.  Each CTA owns 32 output columns (one per lane: a warp reads 128
-// contiguous bytes of a row of B); its 16 warps split K, each with eight rows in flight, and combine
-// through shared memory in warp order, which keeps the result deterministic.  (64 columns and 8 warps
-// gave N / 64 = 48 CTAs for the 3072-wide layer: 0.9 TB/s.)
-constexpr int kGemvWarps = 16;
+// contiguous bytes of a row of B); its 32 warps split K, each with up to sixteen rows in flight (6 MB
+// over the 96 CTAs of a 3072-wide layer), and combine through shared memory in warp order, which
+// keeps the result deterministic.  (64 columns and 8 warps with four rows in flight gave 48 CTAs and
+// 0.9 TB/s; staging the vector in shared memory to have 32 rows in flight measured slower.)
+constexpr int kGemvWarps = 32;
 constexpr int kGemvCols = 32;
 __global__ void __launch_bounds__(kGemvWarps * 32) mm_gemv_kernel(const __grid_constant__ MatmulParams p) {
   pdl_wait();                 // the producer of this kernel's inputs has completed
@@ -109,6 +110,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) mm_gemv_kernel(const __grid_c
   float acc = 0.0f;
   if (n < p.N) {
     int64_t k = k_lo;
+    for (; k + 16 <= k_hi; k += 16) {
+      float w[16], a[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        w[u] = __ldg(B + (k + u) * b_sk + n);
+        a[u] = __ldg(A + (k + u) * a_sk);
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) acc = fmaf(a[u], w[u], acc);
+    }
     for (; k + 8 <= k_hi; k += 8) {
       float w[8], a[8];
 #pragma unroll
