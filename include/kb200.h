@@ -174,8 +174,15 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
  * buffers are then never written.  0 keeps one launch per planned kernel.
  * KB200_OPT_DEPENDENT_LAUNCH (default 1): kernels are enqueued with programmatic stream
  * serialization, so that a kernel's start-up overlaps the tail of the one before it (each kernel
- * waits for its predecessor before it touches global memory).  0 = plain stream order. */
-typedef enum kb200_option { KB200_OPT_FUSE_ATTENTION = 1, KB200_OPT_DEPENDENT_LAUNCH = 2 } kb200_option;
+ * waits for its predecessor before it touches global memory).  0 = plain stream order.
+ * KB200_OPT_FOLD_OPERAND_COPIES (default 1): where the plan makes a matmul's B operand N-contiguous
+ * with a copy kernel (kiln/passes/buffers.py:208-217) that feeds only that matmul, the matmul reads
+ * the copy's source as a K-contiguous operand and the copy is not launched.  0 launches every copy. */
+typedef enum kb200_option {
+  KB200_OPT_FUSE_ATTENTION = 1,
+  KB200_OPT_DEPENDENT_LAUNCH = 2,
+  KB200_OPT_FOLD_OPERAND_COPIES = 3
+} kb200_option;
 int kb200_plan_set_option(kb200_plan* plan, int option, int value);
 
 /* Enqueues every kernel, in order, on `cuda_stream` (a cudaStream_t).

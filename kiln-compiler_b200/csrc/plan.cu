@@ -366,6 +366,125 @@ Span span_of(const PlanKernel& k, int slot) {
 }
 }  // namespace
 
+namespace {
+void reads_and_writes(const PlanKernel& k, std::vector<int>* reads, std::vector<int>* writes) {
+  const kb200_kernel_desc& d = k.desc;
+  if (d.kclass == KB200_K_MATMUL) {
+    reads->push_back(d.a_slot);
+    reads->push_back(d.b_slot);
+  }
+  for (int t = 0; t < d.n_tape; ++t) {
+    if (d.tape[t].opcode == KB200_OP_LOAD) reads->push_back(d.tape[t].a);
+    if (d.tape[t].opcode == KB200_OP_STORE) writes->push_back(d.tape[t].b);
+  }
+}
+bool spans_overlap(const Span& a, const Span& b) { return a.lo < b.hi && b.lo < a.hi; }
+}  // namespace
+
+// The buffer-assignment pass of the reference makes every matmul's B operand N-contiguous, with a
+// copy kernel where the value is not (kiln/passes/buffers.py:208-217): unfrozen weights, `x @ y.T`
+// on an intermediate, the K^T of attention.  The matmuls here also read a K-contiguous B (the
+// tensor-core kernel as a K-major operand, the SIMT kernel through its strides), so when such a copy
+// feeds exactly one matmul and nothing else, the matmul reads the copy's SOURCE and the copy is not
+// launched.  The plan itself (kernel list, offsets) is untouched.
+static void fold_operand_copies(Plan& plan) {
+  for (size_t j = 0; j < plan.kernels.size(); ++j) {
+    PlanKernel& m = plan.kernels[j];
+    if (m.desc.kclass != KB200_K_MATMUL || m.impl == IMPL_FUSED_AWAY) continue;
+    const int bs = m.desc.b_slot;
+    if (m.desc.operands[bs].base_kind != KB200_BASE_ARENA) continue;
+    const DevOperand B = m.ops[bs];
+    const Span b_span = span_of(m, bs);
+    // B as the matmul sees it: dense [batch, K, N]
+    if (B.stride[2] != 1 || B.stride[1] != m.N || (m.batch > 1 && B.stride[0] != m.K * m.N)) continue;
+    // the kernel that wrote it: the nearest earlier one whose output touches it
+    size_t ci = plan.kernels.size();
+    for (size_t i = j; i-- > 0 && ci == plan.kernels.size();) {
+      const PlanKernel& c = plan.kernels[i];
+      if (c.impl == IMPL_FUSED_AWAY) continue;
+      if (c.impl == IMPL_ATTN_FUSED) break;
+      std::vector<int> reads, writes;
+      reads_and_writes(c, &reads, &writes);
+      for (int slot : writes)
+        if (spans_overlap(span_of(c, slot), b_span)) ci = i;
+      if (ci == i) break;
+    }
+    if (ci == plan.kernels.size()) continue;
+    PlanKernel& c = plan.kernels[ci];
+    const kb200_kernel_desc& cd = c.desc;
+    if (cd.kclass != KB200_K_ELEMENTWISE || !c.has_chain || c.chain.n != 1 || c.chain.steps[0].op != CH_COPY || c.chain.first_slot < 0)
+      continue;
+    {
+      std::vector<int> reads, writes;
+      reads_and_writes(c, &reads, &writes);
+      if (writes.size() != 1) continue;
+    }
+    const DevOperand& out = c.ops[c.chain.out_slot];
+    const DevOperand& src = c.ops[c.chain.first_slot];
+    if (out.ptr != B.ptr || numel_of(cd) != m.batch * m.K * m.N) continue;
+    // the copy's output must be dense row-major over its iteration space
+    int64_t dense = 1;
+    bool ok = true;
+    for (int d = cd.iter_rank - 1; d >= 0; --d) {
+      if (cd.iter_shape[d] > 1 && out.stride[d] != dense) ok = false;
+      dense *= cd.iter_shape[d];
+    }
+    if (!ok) continue;
+    // offset in the source of the element that lands `delta` elements into the output
+    auto src_offset = [&](int64_t delta) {
+      int64_t off = 0;
+      for (int d = cd.iter_rank - 1; d >= 0; --d) {
+        off += (delta % cd.iter_shape[d]) * src.stride[d];
+        delta /= cd.iter_shape[d];
+      }
+      return off;
+    };
+    const int64_t s_n = m.N > 1 ? src_offset(1) : 0, s_k = m.K > 1 ? src_offset(m.N) : 0,
+                  s_b = m.batch > 1 ? src_offset(m.K * m.N) : 0;
+    // ... which must be linear in (batch, k, n): checked on the corners and their neighbours
+    for (int64_t bb : {int64_t(0), m.batch - 1})
+      for (int64_t kk : {int64_t(0), m.K > 1 ? int64_t(1) : int64_t(0), m.K - 1})
+        for (int64_t nn : {int64_t(0), m.N > 1 ? int64_t(1) : int64_t(0), m.N - 1})
+          ok = ok && src_offset(bb * m.K * m.N + kk * m.N + nn) == bb * s_b + kk * s_k + nn * s_n;
+    if (!ok || s_n < 0 || s_k < 0 || s_b < 0) continue;
+    // nothing between the copy and the matmul may rewrite the source, and nobody but this matmul may
+    // read the copy before it is rewritten
+    const Span src_span = span_of(c, c.chain.first_slot);
+    for (size_t i = ci + 1; i < j && ok; ++i) {
+      if (plan.kernels[i].impl == IMPL_FUSED_AWAY) continue;
+      std::vector<int> reads, writes;
+      reads_and_writes(plan.kernels[i], &reads, &writes);
+      for (int slot : writes) ok = ok && !spans_overlap(span_of(plan.kernels[i], slot), src_span);
+    }
+    bool rewritten = false;
+    for (size_t i = ci + 1; i < plan.kernels.size() && ok && !rewritten; ++i) {
+      const PlanKernel& k = plan.kernels[i];
+      if (k.impl == IMPL_FUSED_AWAY) continue;
+      std::vector<int> reads, writes;
+      reads_and_writes(k, &reads, &writes);
+      for (int slot : reads)
+        if (!(i == j && slot == bs) && spans_overlap(span_of(k, slot), b_span)) ok = false;
+      for (int slot : writes) {
+        const Span w = span_of(k, slot);
+        if (w.lo <= b_span.lo && w.hi >= b_span.hi) rewritten = true;
+        else if (spans_overlap(w, b_span) && i != j) ok = false;
+      }
+    }
+    if (!ok) continue;
+    const PlanKernel saved = m;
+    m.ops[bs].ptr = src.ptr;
+    m.ops[bs].stride[0] = s_b;
+    m.ops[bs].stride[1] = s_k;
+    m.ops[bs].stride[2] = s_n;
+    if (choose_matmul(plan, m) != KB200_OK) {      // (only a forced implementation can refuse the new strides)
+      m = saved;
+      continue;
+    }
+    c.impl = IMPL_FUSED_AWAY;
+    c.launches = 0;
+  }
+}
+
 // For every BF16 tensor-core matmul operand that lives in the arena: if the last kernel that wrote
 // that memory covers it completely and can also emit bf16, let it write the bf16 mirror and let the
 // matmul read the mirror.  Anything else keeps the per-launch conversion pass.
@@ -577,6 +696,8 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
   if (rc == KB200_OK && plan.fuse_attention)
     for (size_t i = 0; i + 4 < plan.kernels.size(); ++i)
       if (attention_try_fuse(plan, i)) i += 4;
+  // phase 2b: matmuls read a K-contiguous B at its source instead of through the plan's transposing copy
+  if (rc == KB200_OK && plan.fold_copies) fold_operand_copies(plan);
   // phase 3: BF16 matmuls read activations from the bf16 mirror when their producer can write it
   if (rc == KB200_OK) rc = assign_shadows(plan);
   for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i)
@@ -598,6 +719,7 @@ KB200_EXPORT int kb200_plan_set_option(kb200_plan* p, int option, int value) {
   switch (option) {
     case KB200_OPT_FUSE_ATTENTION: plan.fuse_attention = value != 0; return KB200_OK;
     case KB200_OPT_DEPENDENT_LAUNCH: plan.pdl = value != 0; return KB200_OK;
+    case KB200_OPT_FOLD_OPERAND_COPIES: plan.fold_copies = value != 0; return KB200_OK;
     default: return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: unknown option %d", option);
   }
 }

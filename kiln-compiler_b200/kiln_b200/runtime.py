@@ -151,6 +151,10 @@ class GPUExecutable:
         # Programmatic dependent launch between the plan's kernels (KILN_GPU_DEPENDENT_LAUNCH=0: plain stream order).
         pdl = os.environ.get("KILN_GPU_DEPENDENT_LAUNCH", "1") not in ("0", "false", "False", "")
         _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_DEPENDENT_LAUNCH, int(pdl)), self._lib)
+        # One launch per planned kernel also for the copies that only transpose a matmul operand
+        # (KILN_GPU_FOLD_COPIES=0); by default the matmul reads the copy's source and the copy is skipped.
+        fold = os.environ.get("KILN_GPU_FOLD_COPIES", "1") not in ("0", "false", "False", "")
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_FOLD_OPERAND_COPIES, int(fold)), self._lib)
         self._bind()
         self.kernel_names = [l.name for l in program.launches]
         self.impls = [self._lib.kb200_kernel_impl(self._plan, i).decode() for i in range(len(program.launches))]

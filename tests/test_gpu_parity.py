@@ -61,11 +61,12 @@ def test_reduced_precision_matmuls(case, precision):
 @pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
 def test_every_kernel_of_the_block_matches_the_oracle_step_by_step(precision, monkeypatch):
     """Launch the block's 11 kernels one at a time and compare each kernel's output buffer
-    (one launch per planned kernel: the attention chain is not fused here)."""
+    (one launch per planned kernel: no fused attention, no folded operand copies here)."""
     from gpu_helpers import build_executable
     from helpers import case_data, load_plan
 
     monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")
+    monkeypatch.setenv("KILN_GPU_FOLD_COPIES", "0")
 
     case = "gpt2_block_t128"
     plan = load_plan(case)
@@ -113,7 +114,7 @@ def test_fp32_never_fuses_attention():
     from gpu_helpers import build_executable
 
     exe = build_executable("gpt2_block_t128", "fp32")
-    assert "attention_fused" not in exe.impls and exe.device_launches == 11
+    assert "attention_fused" not in exe.impls and exe.device_launches == 10      # 11 planned, the K^T copy is folded
 
 
 def test_replay_with_new_inputs():
@@ -147,6 +148,26 @@ def test_second_mma_issuer_and_dependent_launch(case, precision, monkeypatch):
     exact = run_plan(plan, inputs, consts, dtype=np.float64)
     for got, ref64 in zip(outs, exact):
         assert scale_relative_error(got, ref64) <= REL_TOL[precision], (case, precision, exe.impls)
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
+@pytest.mark.parametrize("case", ["unfrozen_linear", "gpt2_block_t128", "transformer_block", "bmm_transposed_operand", "block_d64"])
+def test_folded_operand_copies_change_nothing(case, precision, monkeypatch):
+    """A matmul that reads its B operand at the source of the plan's transposing copy, against the same
+    plan with the copy launched, and against float64."""
+    from gpu_helpers import run_case
+
+    monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")
+    folded_exe, folded, (plan, inputs, consts, _) = run_case(case, precision)
+    monkeypatch.setenv("KILN_GPU_FOLD_COPIES", "0")
+    plain_exe, plain, _ = run_case(case, precision)
+    assert "fused_away" not in plain_exe.impls and folded_exe.device_launches <= plain_exe.device_launches
+    if case in ("unfrozen_linear", "gpt2_block_t128", "transformer_block", "block_d64"):
+        assert "fused_away" in folded_exe.impls, folded_exe.impls
+    exact = run_plan(plan, inputs, consts, dtype=np.float64)
+    for a, b, ref64 in zip(folded, plain, exact):
+        assert scale_relative_error(a, ref64) <= REL_TOL[precision]
+        assert scale_relative_error(a, b) <= REL_TOL[precision]
 
 
 def test_streamed_batch_equals_one_call_per_request():
@@ -210,14 +231,20 @@ def test_bulk_tensor_stores_equal_plain_stores(case, precision, monkeypatch):
             assert np.array_equal(a, b), (case, precision, stores)
 
 
-def test_hot_path_kernels_are_the_specialised_ones():
+def test_hot_path_kernels_are_the_specialised_ones(monkeypatch):
     from gpu_helpers import build_executable
 
     exe = build_executable("gpt2_block_t128")
     by_name = dict(zip(exe.kernel_names, exe.impls))
     assert by_name["k0_row"] == "row_layernorm" and by_name["k8_row"] == "row_layernorm"
     assert by_name["k4_row"] == "row_softmax"
-    assert by_name["k2_ew0"] == "ew_transpose" and by_name["k6_ew0"] == "ew_chain_vec4"
+    # the K^T copy feeds only the score matmul, which reads K where it lies instead
+    assert by_name["k2_ew0"] == "fused_away" and by_name["k6_ew0"] == "ew_chain_vec4"
+    assert exe.device_launches == 10
+    monkeypatch.setenv("KILN_GPU_FOLD_COPIES", "0")
+    unfolded = build_executable("gpt2_block_t128")
+    assert dict(zip(unfolded.kernel_names, unfolded.impls))["k2_ew0"] == "ew_transpose" and unfolded.device_launches == 11
+    monkeypatch.delenv("KILN_GPU_FOLD_COPIES")
     assert build_executable("bias_gelu_2048x3072").impls == ["ew_chain_vec4"]
     assert build_executable("linear_1x3072x768").impls == ["mm_gemv"]
 
