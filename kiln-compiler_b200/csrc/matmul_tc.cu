@@ -76,6 +76,7 @@ struct TcParams {
   int b_mode;           // how B is fetched: 0 K-major (one box), 1 N-major, all chunks in one 4-D box, 2 N-major, a box per chunk
   int debug;            // experiments: 1 = no stores, 16 = no epilogue (results are then wrong); 32 = no warm-up pass, 512 = two MMA issuers
   int tmem_cols;        // power of two >= bn, >= 32
+  int nacc;             // exact-FP32 mode: accumulators a tile's K steps rotate over (1 otherwise)
   uint32_t idesc;
   int kernel_index;
   int* status;
@@ -85,6 +86,8 @@ struct TcParams {
   int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
   int num_units;        // num_tiles * splits
   int store_mode;       // 0: the epilogue warps store with ordinary global stores; 1: bulk tensor stores from shared memory
+  int split3;           // exact-FP32 mode: every operand is split in shared memory into a TF32 head and a TF32 tail,
+                        // and three MMAs per K step (head x head, head x tail, tail x head) give float32 products
   int issuers;          // 1, or 2: two threads issue the MMAs of alternate pipeline stages into accumulators of their own
   uint64_t magic_stages;   // ceil(2^40 / stages)
   int epi_rowwise;      // the epilogue keeps a lane per ROW (no transpose): the chain has no matrix operand
@@ -136,6 +139,16 @@ __device__ __forceinline__ float f_tanh_approx(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// a = head + tail to 2^-22 |a|: both rounded to nearest TF32, so that the tensor core's truncation of
+// its operands drops nothing and the error of a product has no preferred sign.
+__device__ __forceinline__ void split_tf32(float a, float& head, float& tail) {
+  uint32_t h, t;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+  head = __uint_as_float(h);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(a - head));
+  tail = __uint_as_float(t);
+}
+
 __device__ __forceinline__ float f_erf(float x) {
   const float a = fabsf(x);
   const float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
@@ -334,7 +347,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
              const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_out16,
              const __grid_constant__ TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 6];   // + two cluster hand-shake barriers (split K)
+  __shared__ __align__(8) uint64_t bars[3 * kMaxStages + 6];   // + two cluster hand-shake barriers (split K) + per-stage "operands split" barriers
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 #ifdef KB200_TRACE
@@ -354,11 +367,13 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const int b_tile_bytes = p.kps * p.bn * kSlabBytes;      // B part of one stage (kps K slabs)
   const int a_stage_bytes = p.kps * kATileBytes;           // A part of one stage
-  const int stage_bytes = a_stage_bytes + b_tile_bytes;
+  const int raw_bytes = a_stage_bytes + b_tile_bytes;       // what TMA delivers per stage
+  const int stage_bytes = p.split3 ? 2 * raw_bytes : raw_bytes;   // exact-FP32 mode: the tails of both operands follow
   uint8_t* epi_buf = smem_raw + (tiles - raw) + (size_t)p.stages * stage_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
   const uint32_t tfull0 = smem_u32(&bars[2 * kMaxStages]), tempty0 = smem_u32(&bars[2 * kMaxStages + 2]);
+  const uint32_t split0 = smem_u32(&bars[2 * kMaxStages + 6]);
 
   if (threadIdx.x == 32) {
     // descriptor fetches overlap the set-up below instead of delaying the first copy
@@ -375,6 +390,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     if (lane < 2 * kMaxStages + 4)
       mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : (lane < kMaxStages ? 2 : (lane >= 2 * kMaxStages ? (uint32_t)p.issuers : 1)));
     else if (lane < 2 * kMaxStages + 6) mbar_init(full0 + 8 * lane, (uint32_t)p.splits);   // one arrival per CTA of the cluster
+    if (lane < kMaxStages) mbar_init(full0 + 8 * (2 * kMaxStages + 6 + lane), kEpiWarps);  // split done: one arrival per epilogue warp
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -475,6 +491,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const uint32_t b_slab16 = p.b_mode == 0 ? (uint32_t)(p.bn * kSlabBytes) >> 4 : 4u * b_step16;
       const uint32_t tiles16 = tiles >> 4, stage16 = (uint32_t)stage_bytes >> 4, a_tile16 = kATileBytes >> 4;
       const uint32_t a_stage16 = (uint32_t)a_stage_bytes >> 4;
+      const uint32_t raw16 = (uint32_t)raw_bytes >> 4;      // from an operand's heads to its tails (exact-FP32 mode)
+      const bool split3 = p.split3 != 0;
       const int kps = p.kps;
       bool ok = true;
       int g0 = 0;          // pipeline steps of this CTA before the current tile: step g uses stage g % stages
@@ -492,20 +510,31 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)((acc * nq + q) * bn);
-        uint32_t accumulate = 0;
+        // Exact-FP32 mode: the tensor core truncates every accumulation, an error that grows with the
+        // number of steps summed into one accumulator; the steps rotate over nacc accumulators which
+        // the epilogue adds in float32.  The whole allocation is one buffer then: the warps that drain
+        // a tile are the ones that prepare the next tile's first stage, so nothing overlaps anyway.
+        const int nacc = p.nacc;
+        const uint32_t tmem_t = tmem_base + (split3 ? 0u : (uint32_t)((acc * nq + q) * bn));
+        int rot = 0, n_done = 0;
         // this issuer's steps of the tile: the global step numbers congruent to q modulo nq
         // (stage, round) of step g: counted along with one issuer, by multiplication for two
         int g_first = g0 + ((q - g0) & (nq - 1));
         int round = fast_div(g_first, magic_stages);
         int s = g_first - round * stages;
         for (int g = g_first; g < g0 + n_steps; g += nq) {
-          if (!mbar_wait(full0 + 8 * s, (uint32_t)round & 1u, abort_ptr)) {
+          // exact-FP32 mode: the stage is ready when the epilogue warps have split it, not when it lands
+          if (!mbar_wait((split3 ? split0 : full0) + 8 * s, (uint32_t)round & 1u, abort_ptr)) {
             if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 2); *abort_ptr = 1; }
             ok = false;
             break;
           }
+          if (split3) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (q == 0) KB200_STAMP(2, tm);
+          const uint32_t tmem_d = tmem_t + (uint32_t)(rot * bn);
+          uint32_t accumulate = n_done >= nacc ? 1u : 0u;
+          if (++rot == nacc) rot = 0;
+          ++n_done;
           for (int j = 0; j < kps; ++j) {
             const uint32_t a16 = tiles16 + (uint32_t)s * stage16 + (uint32_t)j * a_tile16;
             const uint32_t b16 = tiles16 + (uint32_t)s * stage16 + a_stage16 + (uint32_t)j * b_slab16;
@@ -513,6 +542,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             for (int k = 0; k < kSlabBytes / 32; ++k) {
               // 14-bit start-address field: in a cluster the shared window address carries the CTA rank in
               // its upper bits, which must not spill into the neighbouring descriptor fields
+              if (split3) {
+                // a*b = (ah + al)(bh + bl) ~ al*bh + ah*bl + ah*bh: the small terms first, al*bl (2^-22 a*b) dropped
+                umma(tmem_d, a_fixed | (uint64_t)((a16 + raw16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu),
+                     idesc, accumulate, false);
+                umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + raw16 + k * b_step16) & 0x3FFFu),
+                     idesc, 1u, false);
+                accumulate = 1;
+              }
               umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu), idesc,
                    accumulate, BF16);
               accumulate = 1;
@@ -541,6 +578,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     __nv_bfloat16* stage16 = reinterpret_cast<__nv_bfloat16*>(epi_buf + e * kEpiWarpBytes + kEpiStage16Offset);
     const bool bulk = p.store_mode == 1 && p.splits == 1;
     const bool rowwise = bulk && p.epi_rowwise != 0;
+    int sp_s = 0;                 // exact-FP32 mode: the stage these warps split next, and its parity
+    uint32_t sp_parity = 0;
     int i = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
@@ -566,7 +605,39 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       // Before its first tile is ready a CTA has nothing for these warps to do, and their code (the
       // unrolled chain, some kilobytes) is not in the instruction cache yet: one dry pass of the loop
       // body over zeros, with nothing stored, takes those misses off the critical path.
-      const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32);
+      const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32) && !p.split3;
+      if (p.split3) {
+        // Exact-FP32 mode: before the tile can be drained its operands have to be prepared.  For every
+        // pipeline step, once the copies have landed, each float a of the stage is replaced by its TF32
+        // head (rounded to nearest, so that the tensor core takes it as it is) and the TF32 rounding of
+        // a - head goes to the second half of the stage; the MMA thread waits for all eight warps.
+        const int n4 = raw_bytes / 16;
+        for (int kb = kb_begin_e; kb < kb_end_e; ++kb) {
+          bool got = mbar_wait(full0 + 8 * sp_s, sp_parity, abort_ptr);
+          if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 7); *abort_ptr = 1; }
+          ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
+          if (!ok) break;
+          float4* head = reinterpret_cast<float4*>(smem_raw + (tiles - raw) + (size_t)sp_s * stage_bytes);
+          float4* tail = head + n4;
+          for (int idx = e * 32 + lane; idx < n4; idx += kEpiWarps * 32) {
+            const float4 v = head[idx];
+            float4 h, t;
+            split_tf32(v.x, h.x, t.x);
+            split_tf32(v.y, h.y, t.y);
+            split_tf32(v.z, h.z, t.z);
+            split_tf32(v.w, h.w, t.w);
+            head[idx] = h;
+            tail[idx] = t;
+          }
+          fence_async_smem();
+          // also orders this warp's reads of the previous tile's accumulators before the MMAs that follow
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(split0 + 8 * sp_s);
+          if (++sp_s == p.stages) { sp_s = 0; sp_parity ^= 1u; }
+        }
+        if (!ok) break;
+      }
       for (int c = half * 32 - (dry_pass ? 64 : 0); c < p.bn; c += 64) {
         const bool dry = c < 0;
         if (c == half * 32) {
@@ -585,8 +656,17 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.0f;
         } else {
-          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.issuers * p.bn + c);
+          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((p.split3 ? 0 : acc * p.issuers * p.bn) + c);
           tmem_ld32(t_addr, v);
+          if (p.split3) {                // the other accumulators the tile's K steps rotated over
+            const int used = min(p.nacc, kb_end_e - kb_begin_e);
+            for (int a = 1; a < used; ++a) {
+              float w[32];
+              tmem_ld32(t_addr + (uint32_t)(a * p.bn), w);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += w[j];
+            }
+          }
           if (two_accumulators) {        // the second issuer's share of the K steps
             float w[32];
             tmem_ld32(t_addr + (uint32_t)p.bn, w);
@@ -854,7 +934,7 @@ bool matmul_wants_bf16_operands(const PlanKernel& k) { return k.desc.precision =
 // Can the tensor-core kernel take this matmul as it stands?
 bool tc_eligible(const PlanKernel& k) {
   const kb200_kernel_desc& d = k.desc;
-  if (d.precision == KB200_PREC_FP32) return false;
+  if (d.precision == KB200_PREC_FP32 && (d.cfg[6] & 1024)) return false;   // experiment bit 1024: FP32 stays on the SIMT kernel
   if (!k.has_chain) return false;        // any other epilogue DAG runs on the SIMT kernel's tape path
   const DevOperand& A = k.ops[d.a_slot];
   const DevOperand& B = k.ops[d.b_slot];
@@ -896,6 +976,8 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
       }
     }
   }
+  const bool split3 = d.precision == KB200_PREC_FP32;     // exact FP32: three TF32 MMAs on split operands
+  if (split3 && bn > 128) bn = 128;                        // a stage holds heads and tails of both operands
   if (bn > 256) bn = 256;
   bn = (bn / 64) * 64;                                    // the two epilogue warps of a quadrant take 32 columns each
   if (bn < 64) bn = 64;
@@ -909,10 +991,11 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   // whose MMAs cost more to issue than to execute, but off unless asked for (debug bit 512): they need an
   // even stage count (below), and with the shallower or finer ring that leaves, they measured slower
   // than one issuer with two slabs per stage (k10 of the block: 19.5 against 17.8 us).
-  const int issuers = ((d.cfg[6] & 512) && bn <= 64) ? 2 : 1;
+  const int issuers = ((d.cfg[6] & 512) && bn <= 64 && !split3) ? 2 : 1;
   // With two issuers one slab per stage (so that the ring can be deep and even), else two for tiles up to 128 columns.
   int kps = d.cfg[2] == 1 || d.cfg[2] == 2 ? d.cfg[2] : (issuers == 2 ? 1 : (bn <= 128 && k.K >= 4 * slab_k ? 2 : 1));
-  const int stage_bytes = kps * (kATileBytes + bn * kSlabBytes);
+  if (split3) kps = 1;
+  const int stage_bytes = (split3 ? 2 : 1) * kps * (kATileBytes + bn * kSlabBytes);
   while (stages > 2 && (size_t)stages * stage_bytes + kEpiBytes + 1024 > (size_t)kMaxDynamicSmem) --stages;
   // Two issuers take alternate pipeline steps.  A wait on an mbarrier tells apart only two consecutive
   // phases, so every stage must belong to ONE issuer, who then sees each of its phases in turn: with an
@@ -944,8 +1027,15 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.b_mode = p.b_kmajor ? 0 : (k.N % chunk_n == 0 ? 1 : 2);
   p.debug = d.cfg[6];
   p.issuers = issuers;
+  p.split3 = split3 ? 1 : 0;
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * p.issuers * bn) p.tmem_cols *= 2;   // per issuer two accumulators: the epilogue drains one while the next tile fills the other
+  p.nacc = 1;
+  if (split3) {
+    // all 512 columns, one buffer: up to eight accumulators, no more than the tile has K steps
+    p.tmem_cols = 512;
+    p.nacc = 512 / bn < 8 ? 512 / bn : 8;
+  }
   p.magic_stages = 0;     // set below, once the stage count is final
   p.tiles_m = (int)((k.M + kTileM - 1) / kTileM);
   p.tiles_n = (int)((k.N + bn - 1) / bn);
@@ -1228,6 +1318,8 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.bn = bn; p.stages = stages; p.slab_k = slab_k; p.chunk_n = chunk_n;
   p.kps = 1; p.step_k = slab_k;
   p.issuers = 1;
+  p.split3 = 0;
+  p.nacc = 1;
   p.magic_stages = ((uint64_t(1) << 40) + stages - 1) / stages;
   p.num_kb = (int)((k + slab_k - 1) / slab_k);
   p.b_step_bytes = 16 * kSlabBytes;
