@@ -139,14 +139,13 @@ __device__ __forceinline__ float f_tanh_approx(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// a = head + tail to 2^-22 |a|: both rounded to nearest TF32, so that the tensor core's truncation of
-// its operands drops nothing and the error of a product has no preferred sign.
+// a = head + tail: head is a rounded to the nearest TF32 (on the bit pattern: conversion instructions run
+// at a quarter of the integer rate and this loop is on the critical path of every pipeline step), tail
+// the exact remainder, of which the tensor core keeps the leading 11 bits; its sign varies, so what is
+// cut off (2^-22 |a| at most) has no preferred direction.
 __device__ __forceinline__ void split_tf32(float a, float& head, float& tail) {
-  uint32_t h, t;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
-  head = __uint_as_float(h);
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(a - head));
-  tail = __uint_as_float(t);
+  head = __uint_as_float((__float_as_uint(a) + 0x1000u) & 0xFFFFE000u);
+  tail = a - head;
 }
 
 __device__ __forceinline__ float f_erf(float x) {
@@ -1032,9 +1031,13 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   while (p.tmem_cols < 2 * p.issuers * bn) p.tmem_cols *= 2;   // per issuer two accumulators: the epilogue drains one while the next tile fills the other
   p.nacc = 1;
   if (split3) {
-    // all 512 columns, one buffer: up to eight accumulators, no more than the tile has K steps
+    // all 512 columns, one buffer: an accumulator per 384 of K (measured: 6.5e-6 of the largest output
+    // per 768 summed into one accumulator, growing in proportion), eight at most; every further
+    // accumulator costs the epilogue one more pass of TMEM loads
     p.tmem_cols = 512;
-    p.nacc = 512 / bn < 8 ? 512 / bn : 8;
+    const int most = 512 / bn < 8 ? 512 / bn : 8;
+    const int64_t want = (k.K + 383) / 384;
+    p.nacc = want < 1 ? 1 : (want > most ? most : (int)want);
   }
   p.magic_stages = 0;     // set below, once the stage count is final
   p.tiles_m = (int)((k.M + kTileM - 1) / kTileM);
