@@ -1058,6 +1058,13 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
       splits = 2;
       if (p.num_tiles * 4 <= plan.sm_count) splits = 4;
     }
+    // Exact-FP32 mode: a pipeline step costs three times the MMAs plus the split, so sharing K pays
+    // from 16 slabs on (measured on the 128-token projections: 768 of K over 36 or 48 tiles 27 -> 20 us
+    // in halves, over 12 tiles 28 -> 19 us in quarters; 3072 of K over 12 tiles 34 -> 29 us in eighths)
+    if (split3 && p.num_tiles * 2 <= plan.sm_count && p.num_kb >= 16) {
+      splits = 2;
+      if (p.num_tiles * 8 <= plan.sm_count) splits = p.num_kb >= 64 ? 8 : 4;
+    }
   }
   if (splits > p.num_kb) splits = p.num_kb;
   // the reduction runs over a thread-block cluster (<= 8 CTAs) and parks the partial tile in the
