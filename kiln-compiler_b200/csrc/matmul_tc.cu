@@ -18,6 +18,10 @@
 // A is read K-major and B N-major straight from the planned buffers (float32, consumed as TF32).
 // In BF16 mode the operands are bf16: read from the mirror their producers write, or converted
 // (constants once at bind, unmirrored activations per launch), and the same kernel runs with kind::f16.
+// In exact-FP32 mode (allow_tf32=False: input_precision="ieee", kiln/gpu/codegen.py:515) the
+// epilogue warps split every landed stage into TF32 heads and tails in shared memory, the issuer
+// runs tail x head, head x tail and head x head, and a tile's K steps rotate over several TMEM
+// accumulators which the epilogue adds in float32 (the tensor core truncates every accumulation).
 //
 // Every wait on an mbarrier is bounded.  When one runs out the thread records the site in the
 // plan's status word, raises a CTA-wide abort flag, and every role falls through to the common
