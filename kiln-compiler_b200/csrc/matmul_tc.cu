@@ -344,7 +344,7 @@ __device__ __forceinline__ void stage_rows(uint8_t* sf, uint8_t* sh, const float
   }
 }
 
-template <bool BF16>
+template <bool BF16, bool SPLIT3>
 __global__ void __launch_bounds__(kThreads, 1)
 mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
              const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_out16,
@@ -371,7 +371,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   const int b_tile_bytes = p.kps * p.bn * kSlabBytes;      // B part of one stage (kps K slabs)
   const int a_stage_bytes = p.kps * kATileBytes;           // A part of one stage
   const int raw_bytes = a_stage_bytes + b_tile_bytes;       // what TMA delivers per stage
-  const int stage_bytes = p.split3 ? 2 * raw_bytes : raw_bytes;   // exact-FP32 mode: the tails of both operands follow
+  const int stage_bytes = SPLIT3 ? 2 * raw_bytes : raw_bytes;   // exact-FP32 mode: the tails of both operands follow
   uint8_t* epi_buf = smem_raw + (tiles - raw) + (size_t)p.stages * stage_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
@@ -495,7 +495,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const uint32_t tiles16 = tiles >> 4, stage16 = (uint32_t)stage_bytes >> 4, a_tile16 = kATileBytes >> 4;
       const uint32_t a_stage16 = (uint32_t)a_stage_bytes >> 4;
       const uint32_t raw16 = (uint32_t)raw_bytes >> 4;      // from an operand's heads to its tails (exact-FP32 mode)
-      const bool split3 = p.split3 != 0;
+      constexpr bool split3 = SPLIT3;
       const int kps = p.kps;
       bool ok = true;
       int g0 = 0;          // pipeline steps of this CTA before the current tile: step g uses stage g % stages
@@ -517,7 +517,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         // number of steps summed into one accumulator; the steps rotate over nacc accumulators which
         // the epilogue adds in float32.  The whole allocation is one buffer then: the warps that drain
         // a tile are the ones that prepare the next tile's first stage, so nothing overlaps anyway.
-        const int nacc = p.nacc;
+        const int nacc = SPLIT3 ? p.nacc : 1;
         const uint32_t tmem_t = tmem_base + (split3 ? 0u : (uint32_t)((acc * nq + q) * bn));
         int rot = 0, n_done = 0;
         // this issuer's steps of the tile: the global step numbers congruent to q modulo nq
@@ -608,8 +608,8 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       // Before its first tile is ready a CTA has nothing for these warps to do, and their code (the
       // unrolled chain, some kilobytes) is not in the instruction cache yet: one dry pass of the loop
       // body over zeros, with nothing stored, takes those misses off the critical path.
-      const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32) && !p.split3;
-      if (p.split3) {
+      const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32) && !SPLIT3;
+      if (SPLIT3) {
         // Exact-FP32 mode: before the tile can be drained its operands have to be prepared.  For every
         // pipeline step, once the copies have landed, each float a of the stage is replaced by its TF32
         // head (rounded to nearest, so that the tensor core takes it as it is) and the TF32 rounding of
@@ -659,9 +659,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.0f;
         } else {
-          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((p.split3 ? 0 : acc * p.issuers * p.bn) + c);
+          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((SPLIT3 ? 0 : acc * p.issuers * p.bn) + c);
           tmem_ld32(t_addr, v);
-          if (p.split3) {                // the other accumulators the tile's K steps rotated over
+          if (SPLIT3) {                  // the other accumulators the tile's K steps rotated over
             const int used = min(p.nacc, kb_end_e - kb_begin_e);
             for (int a = 1; a < used; ++a) {
               float w[32];
@@ -1175,8 +1175,9 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   }
   // The attribute is per function, not per launch: always ask for the ceiling, so that plans with
   // different tile configurations can coexist in one process.
-  cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem)
-                           : cudaFuncSetAttribute(mm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+  cudaError_t e = st->bf16 ? cudaFuncSetAttribute(mm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem)
+                  : st->params.split3 ? cudaFuncSetAttribute(mm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem)
+                           : cudaFuncSetAttribute(mm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(mm_tc_kernel)");
   return KB200_OK;
 }
@@ -1222,8 +1223,9 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  if (st->bf16) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<true>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
-  else KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
+  if (st->bf16) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<true, false>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
+  else if (st->params.split3) KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false, true>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
+  else KB200_CUDA(cudaLaunchKernelEx(&cfg, mm_tc_kernel<false, false>, st->map_a, st->map_b, st->map_out, st->map_out16, st->params));
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }
@@ -1281,7 +1283,7 @@ int static_setup(int device, unsigned char** scratch) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
     if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0)
       return fail(KB200_ERR_CUDA, "kb200_matmul_bf16_static: static scratch resolved to a bad address");
-    e = cudaFuncSetAttribute(mm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+    e = cudaFuncSetAttribute(mm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(mm_tc_kernel)");
     st.scratch = static_cast<unsigned char*>(ptr);
     st.ready = true;
@@ -1378,7 +1380,7 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   dim3 grid((unsigned)(p.num_tiles < sms ? p.num_tiles : sms), 1, 1);
   p.store_mode = 0;   // ordinary stores: the two store maps are unused placeholders
   p.epi_rowwise = 0;
-  mm_tc_kernel<true><<<grid, kThreads, smem, s>>>(map_a, map_b, map_a, map_a, p);
+  mm_tc_kernel<true, false><<<grid, kThreads, smem, s>>>(map_a, map_b, map_a, map_a, p);
   KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }
