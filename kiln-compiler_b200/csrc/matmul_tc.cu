@@ -143,13 +143,11 @@ __device__ __forceinline__ float f_tanh_approx(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// a = head + tail: head is a rounded to the nearest TF32 (on the bit pattern: conversion instructions run
-// at a quarter of the integer rate and this loop is on the critical path of every pipeline step), tail
-// the exact remainder, of which the tensor core keeps the leading 11 bits; its sign varies, so what is
-// cut off (2^-22 |a| at most) has no preferred direction.
-__device__ __forceinline__ void split_tf32(float a, float& head, float& tail) {
-  head = __uint_as_float((__float_as_uint(a) + 0x1000u) & 0xFFFFE000u);
-  tail = a - head;
+// a = head + tail, head the 19 leading bits of a.  The tensor core reads only those bits of a TF32
+// operand, so the landed float serves as its own head and only the tail (exact in float32, of which the
+// tensor core again keeps the leading 11 significant bits) has to be written.
+__device__ __forceinline__ float tf32_tail(float a) {
+  return a - __uint_as_float(__float_as_uint(a) & 0xFFFFE000u);
 }
 
 __device__ __forceinline__ float f_erf(float x) {
@@ -514,9 +512,12 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // Exact-FP32 mode: the tensor core truncates every accumulation, an error that grows with the
-        // number of steps summed into one accumulator; the steps rotate over nacc accumulators which
-        // the epilogue adds in float32.  The whole allocation is one buffer then: the warps that drain
-        // a tile are the ones that prepare the next tile's first stage, so nothing overlaps anyway.
+        // number of MMAs summed into one accumulator (whatever the size of the addend).  The two small
+        // products of every step go into an accumulator of their own (at column 0; 2^-11 of the
+        // magnitude, so its truncations do not count), and the head x head products of the steps rotate
+        // over nacc more; the epilogue adds them all in float32.  The whole allocation is one buffer
+        // then: the warps that drain a tile are the ones that prepare the next tile's first stage, so
+        // nothing overlaps anyway.
         const int nacc = SPLIT3 ? p.nacc : 1;
         const uint32_t tmem_t = tmem_base + (split3 ? 0u : (uint32_t)((acc * nq + q) * bn));
         int rot = 0, n_done = 0;
@@ -534,8 +535,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           }
           if (split3) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (q == 0) KB200_STAMP(2, tm);
-          const uint32_t tmem_d = tmem_t + (uint32_t)(rot * bn);
+          const uint32_t tmem_d = tmem_t + (uint32_t)((rot + (split3 ? 1 : 0)) * bn);
           uint32_t accumulate = n_done >= nacc ? 1u : 0u;
+          uint32_t accumulate_small = n_done > 0 ? 1u : 0u;
           if (++rot == nacc) rot = 0;
           ++n_done;
           for (int j = 0; j < kps; ++j) {
@@ -547,11 +549,11 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
               // its upper bits, which must not spill into the neighbouring descriptor fields
               if (split3) {
                 // a*b = (ah + al)(bh + bl) ~ al*bh + ah*bl + ah*bh: the small terms first, al*bl (2^-22 a*b) dropped
-                umma(tmem_d, a_fixed | (uint64_t)((a16 + raw16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu),
-                     idesc, accumulate, false);
-                umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + raw16 + k * b_step16) & 0x3FFFu),
+                umma(tmem_t, a_fixed | (uint64_t)((a16 + raw16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu),
+                     idesc, accumulate_small, false);
+                umma(tmem_t, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + raw16 + k * b_step16) & 0x3FFFu),
                      idesc, 1u, false);
-                accumulate = 1;
+                accumulate_small = 1;
               }
               umma(tmem_d, a_fixed | (uint64_t)((a16 + 2 * k) & 0x3FFFu), b_fixed | (uint64_t)((b16 + k * b_step16) & 0x3FFFu), idesc,
                    accumulate, BF16);
@@ -624,12 +626,11 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           float4* tail = head + n4;
           for (int idx = e * 32 + lane; idx < n4; idx += kEpiWarps * 32) {
             const float4 v = head[idx];
-            float4 h, t;
-            split_tf32(v.x, h.x, t.x);
-            split_tf32(v.y, h.y, t.y);
-            split_tf32(v.z, h.z, t.z);
-            split_tf32(v.w, h.w, t.w);
-            head[idx] = h;
+            float4 t;
+            t.x = tf32_tail(v.x);
+            t.y = tf32_tail(v.y);
+            t.z = tf32_tail(v.z);
+            t.w = tf32_tail(v.w);
             tail[idx] = t;
           }
           fence_async_smem();
@@ -661,9 +662,9 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         } else {
           const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((SPLIT3 ? 0 : acc * p.issuers * p.bn) + c);
           tmem_ld32(t_addr, v);
-          if (SPLIT3) {                  // the other accumulators the tile's K steps rotated over
+          if (SPLIT3) {                  // v holds the small products; the accumulators the K steps rotated over
             const int used = min(p.nacc, kb_end_e - kb_begin_e);
-            for (int a = 1; a < used; ++a) {
+            for (int a = 1; a <= used; ++a) {
               float w[32];
               tmem_ld32(t_addr + (uint32_t)(a * p.bn), w);
 #pragma unroll
@@ -1035,12 +1036,12 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   while (p.tmem_cols < 2 * p.issuers * bn) p.tmem_cols *= 2;   // per issuer two accumulators: the epilogue drains one while the next tile fills the other
   p.nacc = 1;
   if (split3) {
-    // all 512 columns, one buffer: an accumulator per 384 of K (measured: 6.5e-6 of the largest output
-    // per 768 summed into one accumulator, growing in proportion), eight at most; every further
-    // accumulator costs the epilogue one more pass of TMEM loads
+    // all 512 columns, one buffer: an accumulator for the small products and one per 512 of K for the
+    // large ones (measured with all three products in one: 6.5e-6 of the largest output per 768 of K,
+    // growing in proportion), eight at most; every accumulator costs the epilogue a pass of TMEM loads
     p.tmem_cols = 512;
-    const int most = 512 / bn < 8 ? 512 / bn : 8;
-    const int64_t want = (k.K + 383) / 384;
+    const int most = (512 / bn < 8 ? 512 / bn : 8) - 1;   // one is the small products'
+    const int64_t want = (k.K + 511) / 512;
     p.nacc = want < 1 ? 1 : (want > most ? most : (int)want);
   }
   p.magic_stages = 0;     // set below, once the stage count is final
