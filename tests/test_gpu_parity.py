@@ -150,6 +150,28 @@ def test_second_mma_issuer_and_dependent_launch(case, precision, monkeypatch):
         assert scale_relative_error(got, ref64) <= REL_TOL[precision], (case, precision, exe.impls)
 
 
+@pytest.mark.parametrize("config", [{}, {"split_k": 2}, {"split_k": 4, "BN": 64}, {"BN": 128}, {"debug": 1024}],
+                         ids=["auto", "split2", "split4_bn64", "bn128", "cuda_cores"])
+@pytest.mark.parametrize("case", ["gpt2_block_t128", "mlp_2048", "odd_k", "wide_bmm", "transformer_block",
+                                  "bmm_transposed_operand", "linear_128x768x3072"])
+def test_exact_fp32_matmuls_on_the_tensor_cores(case, config):
+    """allow_tf32=False (tl.dot with input_precision="ieee", kiln/gpu/codegen.py:515): three TF32 products
+    of operands split into head and tail, K steps spread over several accumulators, alone or with K
+    shared over a cluster; and the CUDA-core kernel that config bit 1024 selects.  All within 1e-5 of
+    float64."""
+    from gpu_helpers import build_executable, run_case
+
+    names = [n for n in build_executable(case, "fp32").kernel_names if "matmul" in n]
+    exe, outs, (plan, inputs, consts, _) = run_case(case, "fp32", configs={n.split("_")[0]: dict(config) for n in names})
+    if config.get("debug") == 1024:
+        assert "mm_tcgen05" not in exe.impls, exe.impls
+    elif case in ("gpt2_block_t128", "mlp_2048", "linear_128x768x3072"):
+        assert "mm_tcgen05" in exe.impls and "mm_simt_fp32" not in exe.impls, exe.impls
+    exact = run_plan(plan, inputs, consts, dtype=np.float64)
+    for got, ref64 in zip(outs, exact):
+        assert scale_relative_error(got, ref64) <= REL_TOL["fp32"], (case, config, exe.impls)
+
+
 @pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
 @pytest.mark.parametrize("case", ["unfrozen_linear", "gpt2_block_t128", "transformer_block", "bmm_transposed_operand", "block_d64"])
 def test_folded_operand_copies_change_nothing(case, precision, monkeypatch):
