@@ -10,7 +10,8 @@ ignored).
 
 What is searched is this backend's own space, not Triton's: the tcgen05 tile width (BN, with
 BM fixed at the 128 rows one CTA's accumulator spans), the number of pipeline stages and the
-split-K factor; plus the exact-FP32 SIMT kernel as a candidate.
+split-K factor (in exact-FP32 mode the library narrows tiles to 128 columns and fits the stage
+count itself); plus the CUDA-core FP32 kernel as a candidate.
 """
 
 from __future__ import annotations
@@ -164,8 +165,6 @@ class GPUAutotuner:
         runs, seconds, rejected = {}, {}, []
         default = dict(default)
         configs = [default] + [c for c in candidates(m, n, k) if c != default]
-        if self.precision == "fp32":
-            configs = [c for c in configs if c.get("impl") != "tc"]
         for cfg in configs:
             key = tuple(sorted(cfg.items()))
             try:

@@ -300,4 +300,7 @@ def test_autotuner_is_correct_then_cached(monkeypatch):
     exact = GPUAutotuner(allow_tf32=False, use_cache=False)
     monkeypatch.undo()
     exact.config_for_shape(1, 64, 96, 80, default)
-    assert exact.log[0]["config"].get("impl") in ("auto", "simt")
+    assert exact.log[0]["config"].get("impl") in ("auto", "simt", "tc")
+    # exact FP32 searches the tensor-core configurations too, and they win where there is work to share
+    exact.config_for_shape(1, 128, 768, 768, default)
+    assert exact.log[1]["candidates"] >= 3 and exact.log[1]["config"].get("impl") != "simt", exact.log[1]
