@@ -81,6 +81,7 @@ struct TcParams {
   int debug;            // experiments: 1 = no stores, 16 = no epilogue (results are then wrong); 32 = no warm-up pass, 512 = two MMA issuers
   int tmem_cols;        // power of two >= bn, >= 32
   int nacc;             // exact-FP32 mode: accumulators a tile's K steps rotate over (1 otherwise)
+  int acc2;             // exact-FP32 mode: the accumulators of a tile fit twice (256 columns each): two buffers
   uint32_t idesc;
   int kernel_index;
   int* status;
@@ -519,7 +520,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         // then: the warps that drain a tile are the ones that prepare the next tile's first stage, so
         // nothing overlaps anyway.
         const int nacc = SPLIT3 ? p.nacc : 1;
-        const uint32_t tmem_t = tmem_base + (split3 ? 0u : (uint32_t)((acc * nq + q) * bn));
+        const uint32_t tmem_t = tmem_base + (split3 ? (p.acc2 ? (uint32_t)(acc * 256) : 0u) : (uint32_t)((acc * nq + q) * bn));
         int rot = 0, n_done = 0;
         // this issuer's steps of the tile: the global step numbers congruent to q modulo nq
         // (stage, round) of step g: counted along with one issuer, by multiplication for two
@@ -587,6 +588,44 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     uint32_t sp_parity = 0;
     int i = 0;
     bool ok = true;
+    // Exact-FP32 mode: before a pipeline step can be multiplied its operands have to be prepared.  Once
+    // the copies of a stage have landed, the exact remainder a - head of every float a (head: the 19
+    // leading bits, which is all the tensor core reads of the landed float) goes to the second half of
+    // the stage; the MMA thread waits for all eight warps.  Steps are taken in the order of the ring.
+    auto split_steps = [&](int count) {
+      const int n4 = raw_bytes / 16;
+      for (int n = 0; n < count; ++n) {
+        bool got = mbar_wait(full0 + 8 * sp_s, sp_parity, abort_ptr);
+        if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 7); *abort_ptr = 1; }
+        if (__shfl_sync(0xffffffffu, got ? 1 : 0, 0) == 0 || *abort_ptr) return false;
+        float4* head = reinterpret_cast<float4*>(smem_raw + (tiles - raw) + (size_t)sp_s * stage_bytes);
+        float4* tail = head + n4;
+        for (int idx = e * 32 + lane; idx < n4; idx += kEpiWarps * 32) {
+          const float4 v = head[idx];
+          float4 t;
+          t.x = tf32_tail(v.x);
+          t.y = tf32_tail(v.y);
+          t.z = tf32_tail(v.z);
+          t.w = tf32_tail(v.w);
+          tail[idx] = t;
+        }
+        fence_async_smem();
+        // with one accumulator buffer this also orders the warp's reads of the previous tile's
+        // accumulators before the MMAs that follow
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(split0 + 8 * sp_s);
+        if (++sp_s == p.stages) { sp_s = 0; sp_parity ^= 1u; }
+      }
+      return true;
+    };
+    auto steps_of = [&](int unit) {
+      int tile, ks, batch, tm_i, tn_i, kb0, kb1;
+      unit_coords(p, unit, tile, ks, batch, tm_i, tn_i);
+      slab_range(p, ks, kb0, kb1);
+      return kb1 - kb0;
+    };
+    int unsplit = SPLIT3 && (int)blockIdx.x < p.num_units ? steps_of(blockIdx.x) : 0;   // steps of the current tile still to split
     for (int unit = blockIdx.x; unit < p.num_units && ok; unit += gridDim.x, ++i) {
       int tile, ks, batch, tm_i, tn_i;
       unit_coords(p, unit, tile, ks, batch, tm_i, tn_i);
@@ -612,35 +651,18 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       // body over zeros, with nothing stored, takes those misses off the critical path.
       const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32) && !SPLIT3;
       if (SPLIT3) {
-        // Exact-FP32 mode: before the tile can be drained its operands have to be prepared.  For every
-        // pipeline step, once the copies have landed, each float a of the stage is replaced by its TF32
-        // head (rounded to nearest, so that the tensor core takes it as it is) and the TF32 rounding of
-        // a - head goes to the second half of the stage; the MMA thread waits for all eight warps.
-        const int n4 = raw_bytes / 16;
-        for (int kb = kb_begin_e; kb < kb_end_e; ++kb) {
-          bool got = mbar_wait(full0 + 8 * sp_s, sp_parity, abort_ptr);
-          if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 7); *abort_ptr = 1; }
-          ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
-          if (!ok) break;
-          float4* head = reinterpret_cast<float4*>(smem_raw + (tiles - raw) + (size_t)sp_s * stage_bytes);
-          float4* tail = head + n4;
-          for (int idx = e * 32 + lane; idx < n4; idx += kEpiWarps * 32) {
-            const float4 v = head[idx];
-            float4 t;
-            t.x = tf32_tail(v.x);
-            t.y = tf32_tail(v.y);
-            t.z = tf32_tail(v.z);
-            t.w = tf32_tail(v.w);
-            tail[idx] = t;
-          }
-          fence_async_smem();
-          // also orders this warp's reads of the previous tile's accumulators before the MMAs that follow
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(split0 + 8 * sp_s);
-          if (++sp_s == p.stages) { sp_s = 0; sp_parity ^= 1u; }
-        }
+        ok = split_steps(unsplit);
         if (!ok) break;
+        // With two accumulator buffers the next tile's first steps are split before this tile is
+        // drained, so that its MMAs run under this epilogue; the rest follows after the drain.
+        const int next = unit + (int)gridDim.x;
+        unsplit = next < p.num_units ? steps_of(next) : 0;
+        if (p.acc2 && unsplit > 0) {
+          const int ahead = unsplit < p.stages ? unsplit : p.stages;
+          ok = split_steps(ahead);
+          if (!ok) break;
+          unsplit -= ahead;
+        }
       }
       for (int c = half * 32 - (dry_pass ? 64 : 0); c < p.bn; c += 64) {
         const bool dry = c < 0;
@@ -660,7 +682,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.0f;
         } else {
-          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((SPLIT3 ? 0 : acc * p.issuers * p.bn) + c);
+          const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((SPLIT3 ? (p.acc2 ? acc * 256 : 0) : acc * p.issuers * p.bn) + c);
           tmem_ld32(t_addr, v);
           if (SPLIT3) {                  // v holds the small products; the accumulators the K steps rotated over
             const int used = min(p.nacc, kb_end_e - kb_begin_e);
@@ -1035,6 +1057,7 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * p.issuers * bn) p.tmem_cols *= 2;   // per issuer two accumulators: the epilogue drains one while the next tile fills the other
   p.nacc = 1;
+  p.acc2 = 0;
   if (split3) {
     // all 512 columns, one buffer: an accumulator for the small products and one per 512 of K for the
     // large ones (measured with all three products in one: 6.5e-6 of the largest output per 768 of K,
@@ -1043,6 +1066,7 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     const int most = (512 / bn < 8 ? 512 / bn : 8) - 1;   // one is the small products'
     const int64_t want = (k.K + 511) / 512;
     p.nacc = want < 1 ? 1 : (want > most ? most : (int)want);
+    p.acc2 = (1 + p.nacc) * bn <= 256 ? 1 : 0;
   }
   p.magic_stages = 0;     // set below, once the stage count is final
   p.tiles_m = (int)((k.M + kTileM - 1) / kTileM);
@@ -1337,6 +1361,7 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.issuers = 1;
   p.split3 = 0;
   p.nacc = 1;
+  p.acc2 = 0;
   p.magic_stages = ((uint64_t(1) << 40) + stages - 1) / stages;
   p.num_kb = (int)((k + slab_k - 1) / slab_k);
   p.b_step_bytes = 16 * kSlabBytes;
