@@ -133,7 +133,8 @@ typedef struct kb200_kernel_desc {
    * cfg[0] tile M, cfg[1] tile N, cfg[2] 128-byte K slabs per pipeline stage (1 or 2), cfg[3] pipeline stages,
    * cfg[4] split-K factor, cfg[5] implementation override (0 = library picks),
    * cfg[6] experiment bits of the tensor-core matmul (0 in production; 512 = two MMA issuers for 64-column
-   * tiles), cfg[7] epilogue stores of the tensor-core matmul (0 = library picks,
+   * tiles; 1024 = an FP32-precision matmul runs on the CUDA cores instead of as three TF32 products of
+   * split operands, for operands that may hold infinities), cfg[7] epilogue stores of the tensor-core matmul (0 = library picks,
    * 1 = ordinary global stores, never bulk tensor stores, 2 = bulk stores but always the
    * transposing lane-per-column epilogue), all 0 = library default. */
   int32_t cfg[8];

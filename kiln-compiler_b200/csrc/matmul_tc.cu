@@ -960,7 +960,7 @@ bool matmul_wants_bf16_operands(const PlanKernel& k) { return k.desc.precision =
 // Can the tensor-core kernel take this matmul as it stands?
 bool tc_eligible(const PlanKernel& k) {
   const kb200_kernel_desc& d = k.desc;
-  if (d.precision == KB200_PREC_FP32 && (d.cfg[6] & 1024)) return false;   // experiment bit 1024: FP32 stays on the SIMT kernel
+  if (d.precision == KB200_PREC_FP32 && (d.cfg[6] & 1024)) return false;   // config bit 1024: FP32 stays on the CUDA-core kernel (IEEE on non-finite operands)
   if (!k.has_chain) return false;        // any other epilogue DAG runs on the SIMT kernel's tape path
   const DevOperand& A = k.ops[d.a_slot];
   const DevOperand& B = k.ops[d.b_slot];
