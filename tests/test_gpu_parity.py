@@ -172,6 +172,34 @@ def test_exact_fp32_matmuls_on_the_tensor_cores(case, config):
         assert scale_relative_error(got, ref64) <= REL_TOL["fp32"], (case, config, exe.impls)
 
 
+def test_infinite_matmul_operands_on_the_cuda_cores():
+    """An infinite element of a matmul OPERAND has no finite head and tail, so the split-operand FP32 mode
+    cannot carry it (it yields NaN); config bit 1024 selects the CUDA-core kernel, which multiplies as
+    float32 does: the row that holds +inf comes out +inf, every other row as usual."""
+    from kiln_b200.autotune import GPUAutotuner
+
+    tuner = GPUAutotuner(allow_tf32=False, use_cache=False)
+    gen = torch.Generator(device="cpu").manual_seed(3)
+    a = torch.randn(128, 256, generator=gen)
+    b = torch.rand(256, 192, generator=gen) + 0.5          # positive: inf * b stays +inf
+    a[5, 17] = float("inf")
+    exe = tuner._compile(1, 128, 192, 256, {"debug": 1024})
+    (out,) = exe(a.cuda(), b.cuda())
+    exe.status()
+    out = out.cpu()
+    assert "mm_tcgen05" not in exe.impls
+    assert torch.isinf(out[5]).all() and (out[5] > 0).all()
+    keep = [r for r in range(128) if r != 5]
+    want = (a[keep].double() @ b.double()).float()
+    assert torch.isfinite(out[keep]).all()
+    assert (out[keep] - want).abs().max().item() <= 1e-5 * want.abs().max().item()
+    split = tuner._compile(1, 128, 192, 256, {})
+    (other,) = split(a.cuda(), b.cuda())
+    split.status()
+    assert "mm_tcgen05" in split.impls and torch.isfinite(other.cpu()[keep]).all()
+    assert (other.cpu()[keep] - want).abs().max().item() <= 1e-5 * want.abs().max().item()
+
+
 @pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
 @pytest.mark.parametrize("case", ["unfrozen_linear", "gpt2_block_t128", "transformer_block", "bmm_transposed_operand", "block_d64"])
 def test_folded_operand_copies_change_nothing(case, precision, monkeypatch):
