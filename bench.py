@@ -354,6 +354,9 @@ def kernel_flops(kernel):
 NCU_DRAM_BYTES = {
     ("bf16", "k0_row"): 3.16e6, ("bf16", "k1_matmul"): 5.21e6, ("bf16", "k2_ew0"): 4.77e6, ("bf16", "k7_matmul"): 6.00e6,
     ("bf16", "k8_row"): 3.16e6, ("bf16", "k9_matmul"): 6.41e6, ("bf16", "k10_matmul"): 14.26e6,
+    ("fp32", "k0_row"): 3.16e6, ("fp32", "k1_matmul"): 10.33e6, ("fp32", "k3_matmul"): 10.81e6, ("fp32", "k4_row"): 51.88e6,
+    ("fp32", "k5_matmul"): 53.57e6, ("fp32", "k6_ew0"): 3.18e6, ("fp32", "k7_matmul"): 8.75e6, ("fp32", "k8_row"): 3.16e6,
+    ("fp32", "k9_matmul"): 12.70e6, ("fp32", "k10_matmul"): 25.28e6,
 }
 
 
