@@ -1004,6 +1004,13 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   }
   const bool split3 = d.precision == KB200_PREC_FP32;     // exact FP32: three TF32 MMAs on split operands
   if (split3 && bn > 128) bn = 128;                        // a stage holds heads and tails of both operands
+  if (split3 && d.cfg[1] <= 0 && bn == 64 && k.N >= 128) {
+    // Exact-FP32 mode is bound by shared-memory traffic, of which a 128-column tile needs a third less
+    // per FLOP: it pays from ~45 tiles on (measured on 768 <- 3072 projections: 48 tiles of 128 columns
+    // 66 us against 96 of 64 columns 80 us; but 24 against 48: 64 us against 48 us)
+    const int64_t tiles128 = ((k.M + kTileM - 1) / kTileM) * ((k.N + 127) / 128) * k.batch;
+    if (tiles128 * 10 >= (int64_t)plan.sm_count * 3) bn = 128;
+  }
   if (bn > 256) bn = 256;
   bn = (bn / 64) * 64;                                    // the two epilogue warps of a quadrant take 32 columns each
   if (bn < 64) bn = 64;
