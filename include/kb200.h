@@ -178,11 +178,16 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
  * waits for its predecessor before it touches global memory).  0 = plain stream order.
  * KB200_OPT_FOLD_OPERAND_COPIES (default 1): where the plan makes a matmul's B operand N-contiguous
  * with a copy kernel (kiln/passes/buffers.py:208-217) that feeds only that matmul, the matmul reads
- * the copy's source as a K-contiguous operand and the copy is not launched.  0 launches every copy. */
+ * the copy's source as a K-contiguous operand and the copy is not launched.  0 launches every copy.
+ * KB200_OPT_CONCURRENCY (default 1): how many plans the caller keeps in flight on this GPU at the
+ * same time (a server overlapping requests on several streams).  Only a hint for the tile
+ * heuristics, which the reference leaves to its autotuner (kiln/gpu/codegen.py:563-598): with n > 1 a
+ * matmul counts on 1/n of the SMs and prefers fewer, wider tiles.  Results do not depend on it. */
 typedef enum kb200_option {
   KB200_OPT_FUSE_ATTENTION = 1,
   KB200_OPT_DEPENDENT_LAUNCH = 2,
-  KB200_OPT_FOLD_OPERAND_COPIES = 3
+  KB200_OPT_FOLD_OPERAND_COPIES = 3,
+  KB200_OPT_CONCURRENCY = 4
 } kb200_option;
 int kb200_plan_set_option(kb200_plan* plan, int option, int value);
 

@@ -102,6 +102,7 @@ struct Plan {
   bool fuse_attention = true;    // replace the five-kernel attention chain by the fused kernel when it matches
   bool fold_copies = true;       // a matmul reads a K-contiguous B at its source; the plan's transposing copy is not launched
   bool pdl = true;               // programmatic dependent launch: a kernel's start-up overlaps its predecessor's tail
+  int concurrency = 1;           // plans the caller keeps in flight on this GPU at once (tile heuristics assume their share of the SMs)
   void* arena16 = nullptr;       // bf16 mirror of the arena (library-owned, only when some matmul reads it)
   uint64_t arena16_bytes = 0;
   // bound buffers (for re-validation and the tensor-core path)

@@ -35,7 +35,9 @@
 #include "device_math.cuh"
 #include "kb200_internal.h"
 #include "matmul.h"
+#include "matmul_pair.h"
 #include "tc_common.cuh"
+#include "tc_epilogue.cuh"
 
 namespace kb200 {
 
@@ -128,22 +130,6 @@ __device__ __forceinline__ void slab_range(const TcParams& p, int ks, int& begin
   }
 }
 
-// Reduced-precision modes only: exp through ex2.approx and division through rcp.approx (relative
-// error ~1e-6, far inside the 2e-3 / 2e-2 budgets of TF32 / BF16 operands).  The closed forms stay
-// the reference's (kiln/gpu/codegen.py:53-88).
-__device__ __forceinline__ float f_tanh(float x) {
-  const float e = __expf(-2.0f * fabsf(x));
-  const float t = __fdividef(1.0f - e, 1.0f + e);
-  return x < 0.0f ? -t : t;
-}
-// BF16 mode only: one MUFU instruction (relative error 2^-11; the block's output moves by 1e-3 of its
-// scale, against a budget of 2e-2) instead of ex2 + rcp.  The GELU epilogue of a 128 x 256 tile is bound
-// by the MUFU and issue rates of its eight warps: this takes 2 us off the block's 768 -> 3072 layer.
-__device__ __forceinline__ float f_tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 // a = head + tail, head the 19 leading bits of a.  The tensor core reads only those bits of a TF32
 // operand, so the landed float serves as its own head and only the tail (exact in float32, of which the
 // tensor core again keeps the leading 11 significant bits) has to be written.
@@ -151,45 +137,7 @@ __device__ __forceinline__ float tf32_tail(float a) {
   return a - __uint_as_float(__float_as_uint(a) & 0xFFFFE000u);
 }
 
-__device__ __forceinline__ float f_erf(float x) {
-  const float a = fabsf(x);
-  const float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
-  const float p = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
-  const float y = 1.0f - p * __expf(-a * a);
-  return x < 0.0f ? -y : y;
-}
 
-// One chain step on 32 register-resident values.  The switch is outside the element loop and
-// every index is a compile-time constant, so v[] and side[] never leave the register file and the
-// 32 independent elements give the few epilogue warps the instruction-level parallelism they need.
-__device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float (&side)[32]) {
-#define KB200_EACH(expr)                  \
-  _Pragma("unroll") for (int j = 0; j < 32; ++j) { const float x = v[j]; const float s = side[j]; (void)s; v[j] = (expr); }
-  switch (op) {
-    case CH_ADD: KB200_EACH(x + s) break;
-    case CH_SUB: KB200_EACH(x - s) break;
-    case CH_RSUB: KB200_EACH(s - x) break;
-    case CH_MUL: KB200_EACH(x * s) break;
-    case CH_DIV: KB200_EACH(__fdividef(x, s)) break;
-    case CH_RDIV: KB200_EACH(__fdividef(s, x)) break;
-    case CH_MAX: KB200_EACH(d_max(x, s)) break;
-    case CH_MIN: KB200_EACH(d_min(x, s)) break;
-    case CH_NEG: KB200_EACH(-x) break;
-    case CH_RELU: KB200_EACH(d_max(x, 0.0f)) break;
-    case CH_EXP: KB200_EACH(__expf(x)) break;
-    case CH_TANH: KB200_EACH(f_tanh(x)) break;
-    case CH_SIGMOID: KB200_EACH(__fdividef(1.0f, 1.0f + __expf(-x))) break;
-    case CH_ERF: KB200_EACH(f_erf(x)) break;
-    case CH_GELU_TANH: KB200_EACH(0.5f * x * (1.0f + f_tanh(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
-    case CH_GELU_ERF: KB200_EACH(0.5f * x * (1.0f + f_erf(x * 0.7071067811865476f))) break;
-    case CH_TANH_APPROX: KB200_EACH(f_tanh_approx(x)) break;
-    case CH_GELU_TANH_APPROX: KB200_EACH(0.5f * x * (1.0f + f_tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
-    case CH_RSQRT: KB200_EACH(rsqrtf(x)) break;
-    case CH_SQRT: KB200_EACH(sqrtf(x)) break;
-    default: break;
-  }
-#undef KB200_EACH
-}
 
 // The epilogue works on 32 x 32 blocks of the tile after a transpose through shared memory, so
 // that a lane owns one COLUMN (x[r] = row r): every global load / store of a warp then covers 128
@@ -321,25 +269,6 @@ __device__ __forceinline__ void stage_columns(uint8_t* sf, uint8_t* sh, const fl
     for (int r = 0; r < 32; ++r)
       *reinterpret_cast<__nv_bfloat16*>(sh + r * 64 + ((((lane >> 3) ^ ((r >> 1) & 3)) << 4) | ((lane & 7) << 1))) =
           __float2bfloat16_rn(x[r]);
-  }
-}
-// ... or lane = row (v[j] = column j): 128-bit stores.
-__device__ __forceinline__ void stage_rows(uint8_t* sf, uint8_t* sh, const float (&v)[32], int lane, bool with16) {
-#pragma unroll
-  for (int q = 0; q < 8; ++q)
-    *reinterpret_cast<float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-  if (with16) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      __nv_bfloat162 w0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]), w1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
-      __nv_bfloat162 w2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]), w3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
-      uint4 packed;
-      packed.x = *reinterpret_cast<uint32_t*>(&w0);
-      packed.y = *reinterpret_cast<uint32_t*>(&w1);
-      packed.z = *reinterpret_cast<uint32_t*>(&w2);
-      packed.w = *reinterpret_cast<uint32_t*>(&w3);
-      *reinterpret_cast<uint4*>(sh + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = packed;
-    }
   }
 }
 
@@ -951,6 +880,7 @@ struct TcState {
   bool b_const = false;       // B is a frozen constant: converted once at bind
   bool a_shadow = false;      // A / B is read from the bf16 mirror its producer writes: no conversion launch
   bool b_shadow = false;
+  void* pair = nullptr;       // state of the CTA-pair kernel (matmul_pair.cu) when it runs this matmul
 };
 
 }  // namespace
@@ -1176,6 +1106,17 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
       b_row = b_cols; b_batch = k.K * k.N;
     }
   }
+  // More than 128 rows: 256-row tiles on SM pairs (matmul_pair.cu) when that kernel covers the epilogue.
+  if (st->pair) {
+    pair_destroy(st->pair);
+    st->pair = nullptr;
+  }
+  if (pair_eligible(plan, k)) {
+    const PairOperands po{st->bf16, a_base, a_row, a_batch, b_base, b_row, b_batch, p.b_kmajor != 0};
+    const int rc = pair_bind(plan, k, kernel_index, po, &st->pair);
+    if (rc) return rc;
+    if (st->pair) return KB200_OK;
+  }
   if (!encode_map(&st->map_a, st->bf16, a_base, k.K, k.M, k.batch, a_row, a_batch, slab_k, kTileM, false) ||
       !(p.b_mode == 1 ? encode_map4(&st->map_b, st->bf16, b_base, chunk_n, b_rows, b_cols / chunk_n, k.batch, b_row, b_batch, p.step_k,
                                     bn / chunk_n, !st->bf16)
@@ -1234,6 +1175,7 @@ int tc_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
                                km ? B.stride[2] : B.stride[1]));
     }
   }
+  if (st->pair) return pair_launch(plan, st->pair, s);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = st->grid;
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1267,6 +1209,7 @@ void tc_destroy(PlanKernel& k) {
   if (!st) return;
   if (st->a16) cudaFree(st->a16);
   if (st->b16) cudaFree(st->b16);
+  if (st->pair) pair_destroy(st->pair);
   delete st;
   k.tc = nullptr;
 }

@@ -720,6 +720,7 @@ KB200_EXPORT int kb200_plan_set_option(kb200_plan* p, int option, int value) {
     case KB200_OPT_FUSE_ATTENTION: plan.fuse_attention = value != 0; return KB200_OK;
     case KB200_OPT_DEPENDENT_LAUNCH: plan.pdl = value != 0; return KB200_OK;
     case KB200_OPT_FOLD_OPERAND_COPIES: plan.fold_copies = value != 0; return KB200_OK;
+    case KB200_OPT_CONCURRENCY: plan.concurrency = value < 1 ? 1 : value; return KB200_OK;
     default: return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: unknown option %d", option);
   }
 }

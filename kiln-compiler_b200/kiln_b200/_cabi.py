@@ -25,6 +25,7 @@ K_ELEMENTWISE, K_ROW, K_REDUCE, K_MATMUL = 0, 1, 2, 3
 OPT_FUSE_ATTENTION = 1
 OPT_DEPENDENT_LAUNCH = 2
 OPT_FOLD_OPERAND_COPIES = 3
+OPT_CONCURRENCY = 4
 BASE_KINDS = {"arena": 0, "const": 1, "input": 2, "output": 3}
 PRECISIONS = {"fp32": 0, "tf32": 1, "bf16": 2}
 OPCODES = {

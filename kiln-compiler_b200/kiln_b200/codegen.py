@@ -90,13 +90,14 @@ def _matmul_dims(kernel):
 def default_matmul_config(graph, kernel):
     """The configuration used without measuring (role of codegen.py:563-598).
 
-    All zeros: the library then applies its own rule when buffers are bound -- the widest
-    tcgen05 tile (128 rows by 256, 128 or 64 columns) that still gives every SM a tile, and,
-    when even that leaves SMs idle (128-token projections, 768-wide layers), a split of K so that
-    every SM streams a share of the operands.  The autotuner searches around this default.
+    All zeros: the library then applies its own rule when buffers are bound -- with more than 128
+    rows, 256-row tiles on SM pairs (256 or 128 columns by a cost model of rounds, issue and
+    tensor time); otherwise the widest 128-row tile that still gives every SM a tile, and, when
+    even that leaves SMs idle (128-token projections, 768-wide layers), a split of K so that every
+    SM streams a share of the operands.  The autotuner searches around this default.
     """
     del graph, kernel
-    return {"BM": 128, "BN": 0, "BK": 0, "stages": 0, "split_k": 0, "impl": "auto"}
+    return {"BM": 0, "BN": 0, "BK": 0, "stages": 0, "split_k": 0, "impl": "auto"}
 
 
 def _operand(layout, graph):

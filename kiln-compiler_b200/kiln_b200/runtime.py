@@ -173,6 +173,13 @@ class GPUExecutable:
             _cabi.check(self._lib.kb200_plan_bind(self._plan, self.arena.data_ptr(), self.arena.numel(),
                                                   cp, cs, cn, ip, is_, in_, op, os_, on), self._lib)
 
+    def set_concurrency(self, plans_in_flight):
+        """Tell the library how many plans share the GPU at once (a hint for its tile heuristics:
+        each matmul then counts on its share of the SMs and prefers fewer, wider tiles); re-binds."""
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_CONCURRENCY, int(plans_in_flight)), self._lib)
+        self._bind()
+        self.graph = None
+
     def _launch(self):
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _cabi.check(self._lib.kb200_plan_launch(self._plan, C.c_void_p(stream)), self._lib)
@@ -280,6 +287,8 @@ class StreamedBatch:
             if e.use_cuda_graphs:
                 raise ValueError("StreamedBatch captures the launches itself: build the executables with cuda_graphs=False")
         self.executables = list(executables)
+        for e in self.executables:
+            e.set_concurrency(len(self.executables))
         self.device = executables[0].device
         self.streams = [torch.cuda.Stream(device=self.device) for _ in executables]
         self.graph = None
