@@ -363,7 +363,7 @@ NCU_DRAM_BYTES = {
 def roofline_of(exe, plan, precision, iters=20):
     """Per-launch CUDA-event times of every kernel; roofline of the one with the largest share."""
     pk, pk_kind = peaks()
-    times = exe.profile(exe.static_inputs[0], iters=iters)
+    times = exe.profile_launches(exe.static_inputs[0], iters=iters)
     total = sum(ms for _, ms in times)
     i = max(range(len(times)), key=lambda j: times[j][1])
     name, ms = times[i]
@@ -593,7 +593,7 @@ def gpu_arm(args, dist, rank, world, local):
                 "modules_in_flight": INFLIGHT},
         "gpu_launches": world * args.steps * SEQS * exe.device_launches, "modules_in_flight": INFLIGHT,
         "clocks": clocks.summary(),
-        "impls": dict(zip(exe.kernel_names, exe.impls)),
+        "impls": dict(zip(exe.launch_names, exe.impls)),
     }
     line["roofline"] = roofline_of(exe, plan, precision)
     if world == 1:

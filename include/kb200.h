@@ -11,10 +11,15 @@
  * reference's GPUExecutable (kiln/gpu/runtime.py:135-136).  All functions
  * return 0 on success and a negative kb200_status otherwise; the text of the
  * last failure on the calling thread is returned by kb200_last_error().
- * Nothing here aborts, throws, synchronises the device or (with the one
- * documented exception of plan-owned scratch created in kb200_plan_create)
- * allocates device memory; kb200_plan_launch is therefore capturable into a
- * CUDA graph.
+ * Nothing here aborts or throws.  Device memory is allocated, and the device
+ * synchronised, only while a plan is set up: kb200_plan_create allocates the
+ * plan's status word, and kb200_plan_bind allocates the library-owned scratch
+ * (in BF16 mode a bf16 mirror of the arena and packed bf16 copies of constant
+ * matmul operands; a staging buffer for a fused attention whose output aliases
+ * its inputs), converts the constants (cudaDeviceSynchronize) and reads the
+ * attention mask back once (a blocking copy).  kb200_plan_launch and
+ * kb200_kernel_launch neither allocate nor synchronise and are therefore
+ * capturable into a CUDA graph; kb200_plan_status is a blocking 4-byte copy.
  */
 #ifndef KB200_H
 #define KB200_H
@@ -60,7 +65,10 @@ typedef enum kb200_kclass {
 
 /* Arithmetic mode of a matmul's operands (accumulation is always FP32).
  * FP32 corresponds to input_precision="ieee", TF32 to "tf32"
- * (codegen.py:515-516); BF16 is a backend-internal mode with no IR dtype. */
+ * (codegen.py:515-516); BF16 is a backend-internal mode with no IR dtype.
+ * FP32 on the tensor cores is three TF32 products of split operands: within 1e-5 of exact for
+ * finite operands, but NOT IEEE for non-finite ones (an infinite operand element yields NaN, see
+ * cfg[6] bit 1024 below for the CUDA-core kernel that is). */
 typedef enum kb200_precision {
   KB200_PREC_FP32 = 0,
   KB200_PREC_TF32 = 1,
@@ -132,9 +140,13 @@ typedef struct kb200_kernel_desc {
   /* Tuner configuration, opaque to the reference seam (kiln/api.py:155-162):
    * cfg[0] tile M, cfg[1] tile N, cfg[2] 128-byte K slabs per pipeline stage (1 or 2), cfg[3] pipeline stages,
    * cfg[4] split-K factor, cfg[5] implementation override (0 = library picks),
-   * cfg[6] experiment bits of the tensor-core matmul (0 in production; 512 = two MMA issuers for 64-column
-   * tiles; 1024 = an FP32-precision matmul runs on the CUDA cores instead of as three TF32 products of
-   * split operands, for operands that may hold infinities), cfg[7] epilogue stores of the tensor-core matmul (0 = library picks,
+   * cfg[0] also selects the tensor-core kernel: 0 = library picks, 128 = single-CTA 128-row tiles,
+   * 256 = 256-row tiles on SM pairs (cfg[1] then 128 or 256 columns, cfg[2] slabs per step).
+   * cfg[6] option bits of the tensor-core matmul (0 = defaults): 512 = two MMA issuers for 64-column
+   * single-CTA tiles; 1024 = an FP32-precision matmul runs on the CUDA cores instead of as three TF32
+   * products of split operands -- needed when an OPERAND may hold +-inf: the split gives inf - inf = NaN
+   * tails, so the product is NaN where IEEE arithmetic gives +-inf (the Python side sets this bit on every
+   * matmul when KILN_GPU_FP32_MATMUL=ieee), cfg[7] epilogue stores of the tensor-core matmul (0 = library picks,
    * 1 = ordinary global stores, never bulk tensor stores, 2 = bulk stores but always the
    * transposing lane-per-column epilogue), all 0 = library default. */
   int32_t cfg[8];
@@ -213,6 +225,14 @@ const char* kb200_kernel_impl(const kb200_plan* plan, int i);
  * kernel records it here and returns normally. */
 int kb200_plan_status(kb200_plan* plan);
 
+/* Failure-path self-test (no counterpart in the reference): enqueues a one-warp kernel whose only
+ * wait cannot succeed -- an mbarrier that expects two arrivals and receives one, polled a few
+ * thousand times, with no copy in flight.  On expiry it records its site in the plan's status word
+ * exactly as the tensor-core kernels do and returns normally; after a synchronise,
+ * kb200_plan_status then returns KB200_ERR_DEVICE_WAIT (kernel 0xffff, site 0x7f) and the plan, the
+ * context and the GPU stay usable.  Nothing traps, faults or spins without bound. */
+int kb200_plan_selftest_wait(kb200_plan* plan, void* cuda_stream);
+
 /* Frees the plan and any scratch it owns. */
 void kb200_plan_destroy(kb200_plan* plan);
 
@@ -229,7 +249,8 @@ void kb200_plan_destroy(kb200_plan* plan);
  *   Limit: 2 * (m*k + k*n) bytes (each operand rounded up to 256) must fit in 16 MiB - 256;
  *   larger shapes are refused with KB200_ERR_ARGUMENT and a message naming both numbers.
  *   status_word: optional device int, zeroed by the caller, that receives a non-zero code if a
- *   bounded device-side wait runs out; pass NULL to use (and have cleared) a word inside the array.
+ *   bounded device-side wait runs out; pass NULL to use (and have cleared) a word inside the array,
+ *   which kb200_matmul_bf16_static_status() reads back.
  *
  * Enqueues three kernels on `cuda_stream` and returns; calls no cudaMalloc, cudaFree or any other
  * allocating routine.  The first call on a device resolves the array's device address
@@ -240,6 +261,11 @@ void kb200_plan_destroy(kb200_plan* plan);
  * replayed concurrently) race on it and corrupt each other's operands. */
 int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                              int* status_word, void* cuda_stream);
+
+/* After the caller synchronised with the stream: 0, or KB200_ERR_DEVICE_WAIT if a bounded wait of the
+ * last kb200_matmul_bf16_static call that passed status_word == NULL ran out on the current device
+ * (a blocking 4-byte copy; allocates nothing).  No counterpart in the reference. */
+int kb200_matmul_bf16_static_status(void);
 
 #ifdef __cplusplus
 }

@@ -537,7 +537,15 @@ bool attention_try_fuse(Plan& plan, size_t i) {
   if (Y.stride[0] != H * hd || Y.stride[1] != hd || Y.stride[2] != 1) return false;
   if (!aligned16(Q.ptr) || !aligned16(Ksrc.ptr) || !aligned16(V.ptr) || !aligned16(Y.ptr)) return false;
 
-  // --- the four intermediates must be dead after k6: nobody may read them before they are rewritten ---
+  // --- the four intermediates (K^T, scores, probabilities, per-head O) must be arena buffers: a graph
+  // result lives in a caller's output buffer (kiln/passes/buffers.py:161,193), which the fused kernel
+  // would never write ---
+  if (k2.desc.operands[k2.chain.out_slot].base_kind != KB200_BASE_ARENA ||
+      k3.desc.operands[k3.chain.out_slot].base_kind != KB200_BASE_ARENA ||
+      k4.desc.operands[k4.out_slot].base_kind != KB200_BASE_ARENA ||
+      k5.desc.operands[k5.chain.out_slot].base_kind != KB200_BASE_ARENA)
+    return false;
+  // --- and dead after k6: nobody may read them before they are rewritten ---
   Range dead[4] = {out_range(k2, k2.chain.out_slot), operand_range(k3, k3.chain.out_slot), out_range(k4, k4.out_slot),
                    operand_range(k5, k5.chain.out_slot)};
   const Range y_range = out_range(k6, k6.chain.out_slot);

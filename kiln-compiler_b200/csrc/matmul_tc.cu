@@ -45,6 +45,14 @@ namespace {
 
 using namespace tc;
 
+// Experiments that change results exist in trace builds only; a shipped library ignores the bits.
+#ifdef KB200_TRACE
+#define KB200_EXPERIMENT(bit) (p.debug & (bit))
+#else
+#define KB200_EXPERIMENT(bit) false
+#endif
+
+
 constexpr int kTileM = 128;
 constexpr int kSlabBytes = 128;           // bytes of K (A) or N (B) per swizzled row
 constexpr int kATileBytes = kTileM * kSlabBytes;
@@ -80,7 +88,7 @@ struct TcParams {
   int b_layout;         // descriptor layout type of B (1 = 128-byte swizzle on 32-byte atoms, 2 = 128-byte swizzle)
   int b_kmajor;         // B is read K-major ([N, K] with K contiguous) like A
   int b_mode;           // how B is fetched: 0 K-major (one box), 1 N-major, all chunks in one 4-D box, 2 N-major, a box per chunk
-  int debug;            // experiments: 1 = no stores, 16 = no epilogue (results are then wrong); 32 = no warm-up pass, 512 = two MMA issuers
+  int debug;            // trace builds only: 1 = no stores, 16 = no epilogue (results are then wrong), 32 = no warm-up pass
   int tmem_cols;        // power of two >= bn, >= 32
   int nacc;             // exact-FP32 mode: accumulators a tile's K steps rotate over (1 otherwise)
   int acc2;             // exact-FP32 mode: the accumulators of a tile fit twice (256 columns each): two buffers
@@ -208,7 +216,7 @@ __device__ __forceinline__ void epilogue_compute32(const TcParams& p, float (&x)
 
 __device__ __forceinline__ void epilogue_store32(const TcParams& p, const float (&x)[32], int64_t b, int64_t m_first, int64_t n,
                                                  int row_limit = 32) {
-  if (p.debug & 1) return;
+  if (KB200_EXPERIMENT(1)) return;
   const MatmulParams& mm = p.mm;
   const DevOperand& o = mm.ops[mm.chain.out_slot];
   float* out = o.ptr + b * o.stride[0] + m_first * o.stride[1] + n * o.stride[2];
@@ -578,7 +586,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       // Before its first tile is ready a CTA has nothing for these warps to do, and their code (the
       // unrolled chain, some kilobytes) is not in the instruction cache yet: one dry pass of the loop
       // body over zeros, with nothing stored, takes those misses off the critical path.
-      const bool dry_pass = i == 0 && direct && bulk && !(p.debug & 32) && !SPLIT3;
+      const bool dry_pass = i == 0 && direct && bulk && !KB200_EXPERIMENT(32) && !SPLIT3;
       if (SPLIT3) {
         ok = split_steps(unsplit);
         if (!ok) break;
@@ -605,7 +613,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #endif
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        if (!dry && (n0 + c >= p.mm.N || (p.debug & 16))) break;   // uniform across the warp
+        if (!dry && (n0 + c >= p.mm.N || KB200_EXPERIMENT(16))) break;   // uniform across the warp
         float v[32];
         if (dry) {
 #pragma unroll
@@ -682,7 +690,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             else stage_columns(sf, sh, v, lane, p.out16 != nullptr);
             fence_async_smem();
             __syncwarp();
-            if (lane == 0 && m_first < p.mm.M && !(p.debug & 1) && !dry) {
+            if (lane == 0 && m_first < p.mm.M && !KB200_EXPERIMENT(1) && !dry) {
               tma_store_3d(&tma_out, smem_u32(sf), (int)(n0 + c), (int)m_first, batch);
               if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(sh), (int)(n0 + c), (int)m_first, batch);
               tma_store_commit();
@@ -783,7 +791,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           stage_columns(sf, sh, v, lane, p.out16 != nullptr);
           fence_async_smem();
           __syncwarp();
-          if (lane == 0 && m0 + row_base < p.mm.M && !(p.debug & 1)) {
+          if (lane == 0 && m0 + row_base < p.mm.M && !KB200_EXPERIMENT(1)) {
             tma_store_3d(&tma_out, smem_u32(sf), (int)(n0 + cb * 32), (int)(m0 + row_base), batch);
             if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(sh), (int)(n0 + cb * 32), (int)(m0 + row_base), batch);
             tma_store_commit();
@@ -1358,5 +1366,23 @@ int kb200_matmul_bf16_static(const float* a, const float* b, float* c, int64_t m
   p.epi_rowwise = 0;
   mm_tc_kernel<true, false><<<grid, kThreads, smem, s>>>(map_a, map_b, map_a, map_a, p);
   KB200_CUDA(cudaGetLastError());
+  return KB200_OK;
+}
+
+
+// Reads back the status word that calls with status_word == NULL use on the current device (a
+// blocking 4-byte copy: call it after synchronising with the stream the matmul ran on).
+extern "C" __attribute__((visibility("default")))
+int kb200_matmul_bf16_static_status(void) {
+  using namespace kb200;
+  int device = 0;
+  KB200_CUDA(cudaGetDevice(&device));
+  unsigned char* scratch = nullptr;
+  int rc = static_setup(device, &scratch);
+  if (rc) return rc;
+  int word = 0;
+  KB200_CUDA(cudaMemcpy(&word, scratch + kStaticOperandBytes, sizeof(int), cudaMemcpyDeviceToHost));
+  if (word != 0)
+    return fail(KB200_ERR_DEVICE_WAIT, "kb200_matmul_bf16_static: a bounded device-side wait ran out (code 0x%x, site %d)", word, word & 0xff);
   return KB200_OK;
 }

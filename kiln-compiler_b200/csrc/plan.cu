@@ -388,6 +388,13 @@ bool spans_overlap(const Span& a, const Span& b) { return a.lo < b.hi && b.lo < 
 // feeds exactly one matmul and nothing else, the matmul reads the copy's SOURCE and the copy is not
 // launched.  The plan itself (kernel list, offsets) is untouched.
 static void fold_operand_copies(Plan& plan) {
+  // A kernel the fused attention covers still stands for reads and writes the fused kernel makes
+  // (Q, K, V; the merged output): only copies this pass folded itself may be ignored by the scans below.
+  auto covered_by_attention = [&](size_t i) {
+    for (size_t back = 1; back <= 4 && back <= i; ++back)
+      if (plan.kernels[i - back].impl == IMPL_ATTN_FUSED) return true;
+    return false;
+  };
   for (size_t j = 0; j < plan.kernels.size(); ++j) {
     PlanKernel& m = plan.kernels[j];
     if (m.desc.kclass != KB200_K_MATMUL || m.impl == IMPL_FUSED_AWAY) continue;
@@ -451,7 +458,7 @@ static void fold_operand_copies(Plan& plan) {
     // read the copy before it is rewritten
     const Span src_span = span_of(c, c.chain.first_slot);
     for (size_t i = ci + 1; i < j && ok; ++i) {
-      if (plan.kernels[i].impl == IMPL_FUSED_AWAY) continue;
+      if (plan.kernels[i].impl == IMPL_FUSED_AWAY && !covered_by_attention(i)) continue;
       std::vector<int> reads, writes;
       reads_and_writes(plan.kernels[i], &reads, &writes);
       for (int slot : writes) ok = ok && !spans_overlap(span_of(plan.kernels[i], slot), src_span);
@@ -459,7 +466,7 @@ static void fold_operand_copies(Plan& plan) {
     bool rewritten = false;
     for (size_t i = ci + 1; i < plan.kernels.size() && ok && !rewritten; ++i) {
       const PlanKernel& k = plan.kernels[i];
-      if (k.impl == IMPL_FUSED_AWAY) continue;
+      if (k.impl == IMPL_FUSED_AWAY && !covered_by_attention(i)) continue;
       std::vector<int> reads, writes;
       reads_and_writes(k, &reads, &writes);
       for (int slot : reads)
@@ -770,6 +777,43 @@ KB200_EXPORT int kb200_plan_status(kb200_plan* p) {
     return fail(KB200_ERR_DEVICE_WAIT, "a bounded device-side wait ran out (code 0x%x: kernel %d, site %d)", word,
                 (word >> 8) & 0xffff, word & 0xff);
   }
+  return KB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Failure-path self-test: a wait that is MEANT to run out, in the only safe form -- one warp, one
+// mbarrier that expects two arrivals and gets one, no copy in flight, a few thousand polls.  The
+// kernel then does what the tensor-core kernels do when a wait expires: records (kernel, site) in the
+// plan's status word and returns normally, so the context stays usable and kb200_plan_status reports
+// KB200_ERR_DEVICE_WAIT.
+// ---------------------------------------------------------------------------------------------
+namespace kb200 {
+namespace {
+__global__ void expiring_wait_kernel(int* status, int polls) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&bar);
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(2));
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");   // one of the two arrivals
+    bool done = false;
+    for (int i = 0; i < polls && !done; ++i) {
+      uint32_t ok;
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(ok) : "r"(addr), "r"(0) : "memory");
+      done = ok != 0;
+    }
+    if (!done) atomicCAS(status, 0, (0xFFFF << 8) | 0x7F);
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(addr) : "memory");
+  }
+}
+}  // namespace
+}  // namespace kb200
+
+KB200_EXPORT int kb200_plan_selftest_wait(kb200_plan* p, void* stream) {
+  if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_selftest_wait: plan is null");
+  Plan& plan = *reinterpret_cast<Plan*>(p);
+  expiring_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(plan.d_status, 4096);
+  KB200_CUDA(cudaGetLastError());
   return KB200_OK;
 }
 

@@ -230,13 +230,17 @@ int choose_row(Plan& plan, PlanKernel& k) {
   const kb200_kernel_desc& d = k.desc;
   k.impl = IMPL_ROW_GENERIC;
   k.launches = 1;
-  int reds = 0, levels = 0;
+  // the generic kernel keeps at most kMaxRowRed running reductions per pass (one pass per level)
+  int per_level[KB200_MAX_TAPE + 1] = {0};
   for (int t = 0; t < d.n_tape; ++t) {
     const int oc = d.tape[t].opcode;
-    if (oc == KB200_OP_RSUM || oc == KB200_OP_RMAX) ++reds;
-    if (d.tape[t].level > levels) levels = d.tape[t].level;
+    if (oc != KB200_OP_RSUM && oc != KB200_OP_RMAX) continue;
+    const int level = d.tape[t].level;
+    if (level < 0 || level > KB200_MAX_TAPE)
+      return fail(KB200_ERR_ARGUMENT, "row kernel %s: reduction level %d out of range", d.name, level);
+    if (++per_level[level] > kMaxRowRed)
+      return fail(KB200_ERR_UNSUPPORTED, "row kernel %s: more than %d reductions at one level of the chain", d.name, kMaxRowRed);
   }
-  (void)reds;
   const int64_t inner = d.iter_shape[d.iter_rank - 1];
   const bool shape_ok = d.iter_rank == 2 && inner % 4 == 0 && inner <= 2048 && inner >= 4;
   if (!shape_ok) return KB200_OK;

@@ -69,9 +69,11 @@ EXPORTS = {
     "kb200_plan_launch_count": (C.c_int, [C.c_void_p]),
     "kb200_kernel_impl": (C.c_char_p, [C.c_void_p, C.c_int]),
     "kb200_plan_status": (C.c_int, [C.c_void_p]),
+    "kb200_plan_selftest_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "kb200_plan_destroy": (None, [C.c_void_p]),
     "kb200_matmul_bf16_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                            C.c_void_p, C.c_void_p]),
+    "kb200_matmul_bf16_static_status": (C.c_int, []),
 }
 
 _lib = None

@@ -9,6 +9,8 @@ Which hand-written kernel runs a descriptor is decided inside the library.
 
 from __future__ import annotations
 
+import os
+
 from kiln_b200 import _cabi
 from kiln_b200.codegen import Launch
 from kiln_b200.spec import REDUCTION_OPS, KernelSpec, OperandSpec, PlanSpec, input_shape_of
@@ -157,6 +159,8 @@ def _fill(desc, kclass, precision, iter_shape, operands, tape, name, n_kept=0, k
     cfg = [config.get("BM", 0), config.get("BN", 0), config.get("BK", 0), config.get("stages", 0),
            config.get("split_k", 0), IMPL_CODES.get(config.get("impl", "auto"), 0), config.get("debug", 0),
            {"auto": 0, "plain": 1, "bulk_columns": 2}[config.get("stores", "auto")]]
+    if precision == "fp32" and os.environ.get("KILN_GPU_FP32_MATMUL", "").lower() == "ieee":
+        cfg[6] = int(cfg[6]) | 1024     # CUDA-core FP32 matmul: IEEE results also for infinite operand elements
     for i, c in enumerate(cfg):
         desc.cfg[i] = int(c)
     desc.name = name.encode()[:31]

@@ -45,61 +45,94 @@ def cache_dir() -> Path:
     return Path(base) / "b200"
 
 
+class PlanDump:
+    """The readable plan dump that ``Report.lowering['source']`` points at, stored under the cache
+    directory by content hash (what kiln/gpu/runtime.py:58-79 does for generated Triton source;
+    here nothing is imported from the file, it is for people and for the reference's tests)."""
+
+    def __init__(self, text: str):
+        self.text = text
+        self.path = cache_dir() / ("plan_" + hashlib.sha256(text.encode()).hexdigest()[:16] + ".txt")
+
+    def stored(self) -> bool:
+        try:
+            return self.path.read_text() == self.text
+        except OSError:
+            return False
+
+    def store(self) -> Path:
+        """Write-then-rename, so a concurrent reader never sees half a file; a damaged copy is replaced."""
+        if self.stored():
+            return self.path
+        self.path.parent.mkdir(parents=True, exist_ok=True)
+        scratch = self.path.with_name(f"{self.path.name}.{os.getpid()}.part")
+        with open(scratch, "w") as out:
+            out.write(self.text)
+            out.flush()
+            os.fsync(out.fileno())
+        os.replace(scratch, self.path)
+        return self.path
+
+
 def write_source(source: str) -> Path:
-    """Store the plan dump where Report.lowering['source'] points (atomic, verified on reuse)."""
-    digest = hashlib.sha256(source.encode()).hexdigest()[:16]
-    path = cache_dir() / f"plan_{digest}.txt"
-    path.parent.mkdir(parents=True, exist_ok=True)
-    try:
-        intact = path.read_text() == source
-    except OSError:
-        intact = False
-    if not intact:
-        tmp = path.with_suffix(f".{os.getpid()}.tmp")
-        with open(tmp, "w") as f:
-            f.write(source)
-            f.flush()
-            os.fsync(f.fileno())
-        tmp.replace(path)
-    return path
+    return PlanDump(source).store()
+
+
+def _mib(n_bytes) -> str:
+    return f"{n_bytes / 2**20:.1f} MiB"
 
 
 def check_memory(dev, needed_bytes, what):
-    if dev.type != "cuda":
+    """MemoryError naming the sizes involved when ``needed_bytes`` exceed the device's free memory
+    (same message as kiln/gpu/runtime.py:82-90, which the reference's tests match on)."""
+    if torch.device(dev).type != "cuda":
         return
-    free, total = torch.cuda.mem_get_info(dev)
-    if needed_bytes > free:
-        mib = lambda b: f"{b / 2**20:.1f} MiB"
-        raise MemoryError(f"Kiln needs {mib(needed_bytes)} of GPU memory for {what}, but only "
-                          f"{mib(free)} of {mib(total)} is free (other processes may be using the GPU). "
-                          f"Try a smaller batch or sequence length, or free GPU memory.")
+    free_bytes, total_bytes = torch.cuda.mem_get_info(dev)
+    if needed_bytes <= free_bytes:
+        return
+    raise MemoryError(f"Kiln needs {_mib(needed_bytes)} of GPU memory for {what}, but only {_mib(free_bytes)} of "
+                      f"{_mib(total_bytes)} is free (other processes may be using the GPU). Try a smaller batch or "
+                      f"sequence length, or free GPU memory.")
+
+
+class GraphTimer:
+    """GPU time of a callable without the host's launch overhead: ``repeats`` back-to-back calls are
+    captured in one CUDA graph (after a warm-up on a side stream, which also loads every kernel) and
+    whole replays are timed with CUDA events.  Role of kiln/gpu/runtime.py:93-132."""
+
+    def __init__(self, fn, repeats=20, warmup_calls=3):
+        device()
+        self.repeats = repeats
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup_calls):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            for _ in range(repeats):
+                fn()
+        self.graph.replay()                      # first replay: instantiation, not measured
+        torch.cuda.synchronize()
+        self._begin = torch.cuda.Event(enable_timing=True)
+        self._end = torch.cuda.Event(enable_timing=True)
+
+    def sample(self) -> float:
+        """Seconds per call over one replay."""
+        self._begin.record()
+        self.graph.replay()
+        self._end.record()
+        torch.cuda.synchronize()
+        return self._begin.elapsed_time(self._end) * 1e-3 / self.repeats
+
+    def samples(self, n):
+        return [self.sample() for _ in range(n)]
 
 
 def kernel_seconds(fn, repeats=20, rounds=5):
-    """GPU time per call of ``fn`` without CPU launch overhead: ``repeats`` calls captured in one
-    CUDA graph, the replay timed with CUDA events, best of ``rounds`` (kiln/gpu/runtime.py:93-132)."""
-    device()
-    stream = torch.cuda.Stream()
-    stream.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            fn()
-    torch.cuda.current_stream().wait_stream(stream)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for _ in range(repeats):
-            fn()
-    graph.replay()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    best = float("inf")
-    for _ in range(rounds):
-        start.record()
-        graph.replay()
-        end.record()
-        torch.cuda.synchronize()
-        best = min(best, start.elapsed_time(end) / 1e3 / repeats)
-    return best
+    """Best-of-``rounds`` GPU seconds per call of ``fn`` (see GraphTimer)."""
+    return min(GraphTimer(fn, repeats).samples(rounds))
 
 
 def _ptr_array(tensors):
@@ -115,7 +148,7 @@ class GPUExecutable:
     def __init__(self, program, arena_bytes, constants, input_shapes, output_shapes, cuda_graphs=True):
         self.device = device()
         self.program = program
-        self.source_path = write_source(program.source)
+        self.source_path = PlanDump(program.source).store()
         self.input_shapes = [tuple(s) for s in input_shapes]
         self.output_shapes = [tuple(s) for s in output_shapes]
         self._lib = _cabi.load()
@@ -125,7 +158,13 @@ class GPUExecutable:
         const_bytes = sum(int(np.prod(constants[name].shape)) * 4 for name in used)
         io_bytes = sum(4 * int(np.prod(s)) for s in self.input_shapes + self.output_shapes)
         out_bytes = sum(4 * int(np.prod(s)) for s in self.output_shapes)
-        check_memory(self.device, arena_bytes + const_bytes + io_bytes + out_bytes,
+        # what the library allocates itself when buffers are bound, in BF16 mode: a bf16 mirror of the
+        # arena, packed bf16 copies of the constant matmul operands, and (worst case) bf16 copies of
+        # unmirrored activations no larger than the inputs and the arena together
+        library_bytes = 0
+        if program.precision == "bf16":
+            library_bytes = arena_bytes // 2 + 256 + const_bytes // 2 + (io_bytes + arena_bytes) // 2
+        check_memory(self.device, arena_bytes + const_bytes + io_bytes + out_bytes + library_bytes,
                      f"the arena ({arena_bytes / 2**20:.1f} MiB), weights ({const_bytes / 2**20:.1f} MiB) "
                      f"and outputs")
         self.arena = torch.empty(max(arena_bytes, 4), dtype=torch.uint8, device=self.device)
@@ -156,7 +195,10 @@ class GPUExecutable:
         fold = os.environ.get("KILN_GPU_FOLD_COPIES", "1") not in ("0", "false", "False", "")
         _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_FOLD_OPERAND_COPIES, int(fold)), self._lib)
         self._bind()
-        self.kernel_names = [l.name for l in program.launches]
+        # launch_names: one per device launch of the plan (k3_matmul, k2_ew0 ...); kernel_names: the Kiln
+        # kernels they come from, which is what CompiledModule.profile keys on (kiln/api.py:204-211)
+        self.launch_names = [l.name for l in program.launches]
+        self.kernel_names = list(dict.fromkeys(l.kernel for l in program.launches))
         self.impls = [self._lib.kb200_kernel_impl(self._plan, i).decode() for i in range(len(program.launches))]
         self.device_launches = self._lib.kb200_plan_launch_count(self._plan)
         self.graph = None
@@ -231,13 +273,14 @@ class GPUExecutable:
             self.run_static()
             return [o.clone() for o in self.static_outputs]
 
-    def profile(self, *inputs, iters=20):
-        """[(launch name, milliseconds)] per launch of the plan.
+    def profile_launches(self, *inputs, iters=20):
+        """[(launch name, milliseconds)] for every launch of the plan, in order.
 
         Each launch is timed on its own as GPU time: ``iters`` back-to-back launches of it captured
         in one CUDA graph and the replay timed with CUDA events (a launch takes microseconds, less
         than the host needs to enqueue it).  Launches are idempotent -- no kernel writes a buffer it
-        reads -- so repeating one does not disturb the others' inputs.
+        reads -- so repeating one does not disturb the others' inputs.  A launch that a fused kernel
+        covers (implementation ``fused_away``) enqueues nothing and is reported as 0.
         """
         inputs = self._prepare(inputs)
         with torch.cuda.device(self.device):
@@ -246,10 +289,22 @@ class GPUExecutable:
             self._launch()
             torch.cuda.synchronize(self.device)
             out = []
-            for i, name in enumerate(self.kernel_names):
+            for i, name in enumerate(self.launch_names):
+                if self.impls[i] == "fused_away":
+                    out.append((name, 0.0))
+                    continue
                 seconds = kernel_seconds(lambda i=i: self.launch_kernel(i), repeats=iters, rounds=3)
                 out.append((name, seconds * 1e3))
         return out
+
+    def profile(self, *inputs, iters=20):
+        """[(Kiln kernel name, milliseconds)], the form ``CompiledModule.profile`` expects
+        (kiln/api.py:204-211): the launches of one kernel (one per output of an elementwise kernel)
+        are summed; the fused attention is booked on the kernel that launches it."""
+        by_kernel = dict.fromkeys(self.kernel_names, 0.0)
+        for launch, (_, ms) in zip(self.program.launches, self.profile_launches(*inputs, iters=iters)):
+            by_kernel[launch.kernel] += ms
+        return list(by_kernel.items())
 
     def close(self):
         if getattr(self, "_plan", None) is not None and self._plan:

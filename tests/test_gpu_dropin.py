@@ -117,6 +117,60 @@ def test_unfrozen_weights_are_read_at_call_time(kiln):
         torch.testing.assert_close(compiled(x), model(x), rtol=1e-4, atol=1e-5)
 
 
+def test_profile_through_the_reference_api(kiln):
+    """CompiledModule.profile (kiln/api.py:204-211) looks every returned name up among the graph's
+    kernels: the executable must report Kiln kernel names, one entry per kernel, fused kernels included."""
+    from kiln_b200 import workloads as W
+
+    model, x = W.block_module(3, 128), torch.from_numpy(W.block_input(3, 128))
+    compiled = kiln.compile(model, (x,), device="cuda", allow_tf32=True)
+    rows = compiled.profile(x, iters=5)
+    assert [r[0] for r in rows] == [k.name for k in compiled.graph.kernels]
+    assert {r[1] for r in rows} == {k.kind for k in compiled.graph.kernels}
+    assert all(ms >= 0.0 for *_, ms in rows) and sum(ms for *_, ms in rows) > 0.0
+    # the fused attention is booked on the kernel that launches it; the four it covers take no time
+    impls = dict(zip(compiled._exe.launch_names, compiled._exe.impls))
+    covered = [launch.kernel for launch in compiled._exe.program.launches if impls[launch.name] == "fused_away"]
+    assert len(covered) == 4 and all(ms == 0.0 for name, _, _, ms in rows if name in covered)
+    compile_and_compare(kiln, model, x, allow_tf32=True, rtol=1e-2, atol=1e-2)
+
+
+def test_attention_that_also_returns_its_weights_is_not_fused(kiln):
+    """A model that returns the softmax weights beside the block output keeps them in a caller's
+    output buffer: the fused attention kernel never writes the scores, so the library must run the
+    planned kernels for such a graph (in the reduced-precision modes too)."""
+    import torch.nn as nn
+
+    class Attention(nn.Module):
+        def __init__(self, t=128, d=128, heads=2):
+            super().__init__()
+            self.heads, self.qkv, self.proj = heads, nn.Linear(d, 3 * d), nn.Linear(d, d)
+            self.register_buffer("mask", torch.full((t, t), float("-inf")).triu(1))
+
+        def forward(self, x):
+            t, c = x.shape
+            hd = c // self.heads
+            q, k, v = (z.view(t, self.heads, hd).transpose(0, 1) for z in self.qkv(x).split(c, dim=1))
+            weights = F.softmax((q @ k.transpose(-2, -1)) * (1.0 / math.sqrt(hd)) + self.mask, dim=-1)
+            return self.proj((weights @ v).transpose(0, 1).contiguous().view(t, c)), weights
+
+    torch.manual_seed(5)
+    model, x = Attention().eval(), torch.randn(128, 128)
+    compiled = compile_and_compare(kiln, model, x, allow_tf32=True, rtol=1e-2, atol=1e-2)
+    assert "attention_fused" not in compiled._exe.impls
+    # and the same model without the second result does fuse (64-wide heads, 128 tokens)
+    class Only(nn.Module):
+        def __init__(self, inner):
+            super().__init__()
+            self.inner = inner
+
+        def forward(self, x):
+            return self.inner(x)[0]
+
+    fused = compile_and_compare(kiln, Only(model).eval(), x, allow_tf32=True, rtol=1e-2, atol=1e-2)
+    assert "attention_fused" in fused._exe.impls
+
+
 def test_wrong_shape_is_a_value_error(kiln):
     compiled = kiln.compile(torch.nn.Linear(8, 4).eval(), (torch.randn(3, 8),), device="cuda")
     with pytest.raises(ValueError):

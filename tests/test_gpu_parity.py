@@ -142,7 +142,7 @@ def test_second_mma_issuer_and_dependent_launch(case, precision, monkeypatch):
     from gpu_helpers import build_executable, run_case
 
     monkeypatch.setenv("KILN_GPU_DEPENDENT_LAUNCH", "0" if case == "mlp_2048" else "1")      # both launch orders
-    names = [n for n in build_executable(case, precision).kernel_names if "matmul" in n]
+    names = [n for n in build_executable(case, precision).launch_names if "matmul" in n]
     exe, outs, (plan, inputs, consts, _) = run_case(
         case, precision, configs={n.split("_")[0]: {"BN": 64, "debug": 512, "impl": "tc"} for n in names})
     exact = run_plan(plan, inputs, consts, dtype=np.float64)
@@ -161,7 +161,7 @@ def test_exact_fp32_matmuls_on_the_tensor_cores(case, config):
     float64."""
     from gpu_helpers import build_executable, run_case
 
-    names = [n for n in build_executable(case, "fp32").kernel_names if "matmul" in n]
+    names = [n for n in build_executable(case, "fp32").launch_names if "matmul" in n]
     exe, outs, (plan, inputs, consts, _) = run_case(case, "fp32", configs={n.split("_")[0]: dict(config) for n in names})
     if config.get("debug") == 1024:
         assert "mm_tcgen05" not in exe.impls, exe.impls
@@ -273,7 +273,7 @@ def test_bulk_tensor_stores_equal_plain_stores(case, precision, monkeypatch):
     from gpu_helpers import build_executable, run_case
 
     monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")   # keep every planned matmul on the GPU's kernel list
-    names = [n for n in build_executable(case, precision).kernel_names if "matmul" in n]
+    names = [n for n in build_executable(case, precision).launch_names if "matmul" in n]
     _, bulk, _ = run_case(case, precision)
     for stores in ("plain", "bulk_columns"):     # "auto" keeps a lane per row where the chain allows it
         _, other, _ = run_case(case, precision, configs={n.split("_")[0]: {"stores": stores} for n in names})
@@ -285,7 +285,7 @@ def test_hot_path_kernels_are_the_specialised_ones(monkeypatch):
     from gpu_helpers import build_executable
 
     exe = build_executable("gpt2_block_t128")
-    by_name = dict(zip(exe.kernel_names, exe.impls))
+    by_name = dict(zip(exe.launch_names, exe.impls))
     assert by_name["k0_row"] == "row_layernorm" and by_name["k8_row"] == "row_layernorm"
     assert by_name["k4_row"] == "row_softmax"
     # the K^T copy feeds only the score matmul, which reads K where it lies instead
@@ -293,7 +293,7 @@ def test_hot_path_kernels_are_the_specialised_ones(monkeypatch):
     assert exe.device_launches == 10
     monkeypatch.setenv("KILN_GPU_FOLD_COPIES", "0")
     unfolded = build_executable("gpt2_block_t128")
-    assert dict(zip(unfolded.kernel_names, unfolded.impls))["k2_ew0"] == "ew_transpose" and unfolded.device_launches == 11
+    assert dict(zip(unfolded.launch_names, unfolded.impls))["k2_ew0"] == "ew_transpose" and unfolded.device_launches == 11
     monkeypatch.delenv("KILN_GPU_FOLD_COPIES")
     assert build_executable("bias_gelu_2048x3072").impls == ["ew_chain_vec4"]
     assert build_executable("linear_1x3072x768").impls == ["mm_gemv"]
@@ -332,3 +332,57 @@ def test_autotuner_is_correct_then_cached(monkeypatch):
     # exact FP32 searches the tensor-core configurations too, and they win where there is work to share
     exact.config_for_shape(1, 128, 768, 768, default)
     assert exact.log[1]["candidates"] >= 3 and exact.log[1]["config"].get("impl") != "simt", exact.log[1]
+
+
+def test_nine_reductions_at_one_level_are_refused_not_dropped():
+    """The generic row kernel keeps eight running reductions per pass; a ninth must be a clear
+    NotImplementedError at bind time, never a silently missing term."""
+    from kiln_b200.codegen import program_from_plan
+    from kiln_b200.runtime import GPUExecutable
+    from kiln_b200.spec import KernelSpec, NodeSpec, OperandSpec, PlanSpec
+
+    rows, cols = 4, 24
+
+    def plan_with(n_reductions):
+        nodes = [NodeSpec("mul", [("operand", 0), ("scalar", float(i + 1))], (rows, cols)) for i in range(n_reductions)]
+        nodes += [NodeSpec("reduce_sum", [("node", i)], (rows, 1), {"dims": [1], "keepdim": True}) for i in range(n_reductions)]
+        acc = n_reductions
+        for i in range(1, n_reductions):
+            nodes.append(NodeSpec("add", [("node", acc), ("node", n_reductions + i)], (rows, 1)))
+            acc = len(nodes) - 1
+        kernel = KernelSpec("k0", "reduction", nodes, [OperandSpec(("input", 0), 0, (rows, cols), (cols, 1))],
+                            [(acc, OperandSpec(("output", 0), 0, (rows, 1), (1, 1)))])
+        return PlanSpec("many_reductions", [(rows, cols)], [(rows, 1)], 0, {}, [kernel])
+
+    x = torch.randn(rows, cols)
+    ok = plan_with(8)
+    exe = GPUExecutable(program_from_plan(ok, "fp32"), 0, {}, ok.input_shapes, ok.output_shapes, cuda_graphs=False)
+    (got,) = exe(x)
+    want = sum((i + 1) * x.double().sum(1, keepdim=True) for i in range(8))
+    torch.testing.assert_close(got.cpu().double(), want, rtol=1e-5, atol=1e-5)
+    too_many = plan_with(9)
+    with pytest.raises(NotImplementedError, match="reductions at one level"):
+        GPUExecutable(program_from_plan(too_many, "fp32"), 0, {}, too_many.input_shapes, too_many.output_shapes, cuda_graphs=False)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_plan_stays_usable():
+    """Failure detection on the device without faulting it: a wait that nothing can satisfy gives up
+    after its limit, the status word names it, and the same plan then runs correctly."""
+    import ctypes as C
+
+    from gpu_helpers import run_case
+    from kiln_b200 import _cabi
+
+    lib = _cabi.load()
+    exe, outs, (plan, inputs, consts, expected) = run_case("mlp", "fp32", cuda_graphs=False)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.kb200_plan_selftest_wait(exe._plan, stream) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bounded device-side wait ran out.*kernel 65535, site 127"):
+        exe.status()
+    exe.status()                      # reading the word cleared it
+    again = exe(*[torch.from_numpy(np.ascontiguousarray(x)) for x in inputs])
+    torch.cuda.synchronize()
+    exe.status()
+    np.testing.assert_allclose(again[0].cpu().numpy(), outs[0], rtol=0, atol=0)
+    np.testing.assert_allclose(again[0].cpu().numpy(), expected["out"][0], rtol=1e-4, atol=1e-5)
