@@ -8,16 +8,26 @@ N(0, 0.02), inputs N(0, 1), seed 4 -- synthetic tensors of the benchmark's shape
 (one process per GPU, independent replicas, no collective on the data path) processes its own
 64 sequences per step, so the job is weak-scaled: tokens/s = N * 64 * 1024 / step time.
 
-Two timed regions, both K steps bracketed by barrier + synchronize, CUDA events, max over ranks:
-  value  inputs already resident in HBM; each sequence is copied device-to-device into a compiled
-         module's static input, its captured CUDA graph is replayed, the result copied out.
-  e2e    the public call ``executable(x)`` with pinned host tensors: host-to-device copy of every
-         sequence and device-to-host read of every result inside the timed region.
-In both regions three compiled modules (own arena, own CUDA graph) are kept in flight on separate
-streams, the way a server overlaps requests: copies overlap kernels, and one sequence's kernels fill
-SMs another leaves idle.
-A step touches 64 x 3 MiB of inputs plus a 105 MiB arena, more than the 126 MB L2, so no explicit
-L2 flush is needed between iterations; the weights (14-28 MB) stay L2-resident, as in serving.
+The block is compiled through the reference's own ``kiln.compile(model, inputs, device="cuda")``
+(frontend and passes from the pip --target copy under baseline/_ref) with this package
+registered as ``kiln.gpu``; where that copy is absent the plan those passes produce is loaded
+from kiln_b200/plans.  Six modules (own arena, static buffers and stream each) are kept in
+flight, the way a server overlaps requests, and the whole step of 64 sequences is captured as
+ONE CUDA graph (kiln_b200.runtime.StreamedBatch).
+
+Timed regions, each K steps bracketed by barrier + synchronize, CUDA events, max over ranks:
+  value   inputs already resident in HBM (device-to-device copies into the modules' inputs);
+  e2e     the same graph with pinned HOST tensors as sources and sinks: every sequence's
+          host-to-device copy and every result's device-to-host copy inside the timed region;
+          e2e.copy_only_ms is the same step with the kernels left out (the host link alone);
+  extras.strong_scaling   64 sequences in total, 64 / N per GPU (BASELINE config 4's sharding).
+A step touches 64 x 3 MiB of inputs plus six 10-17 MiB arenas, more than the 126 MB L2, so no
+explicit flush is needed between iterations; the weights stay L2-resident, as in serving.
+
+``extras`` (rank 0 of a one-GPU run) measures every other BASELINE configuration at its stated
+precision whatever --precision says: the 128-token block in FP32, the 2048-token MLP in TF32,
+the six Linear shapes in TF32 and BF16, the fused memory-bound ops in FP32, the 2048-token
+block; and, in a process of its own, the reference's Triton backend on the same shapes.
 
 --impl reference times the CPU implementation of the same block (eager PyTorch float32 on the
 host cores, the stand-in for the reference's MLIR CPU backend, see oracle/torch_block.py) on a
@@ -36,7 +46,7 @@ import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
-for _p in (ROOT / "kiln-compiler_b200", ROOT, ROOT / "tests"):
+for _p in (ROOT / "kiln-compiler_b200", ROOT):
     if str(_p) not in sys.path:
         sys.path.insert(0, str(_p))
 
@@ -44,8 +54,9 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 SEQS, TOKENS, D, HEADS, SEED = 64, 1024, 768, 12, 4
-INFLIGHT = int(os.environ.get("KB200_BENCH_INFLIGHT", "6"))          # compiled modules kept in flight (own stream, arena and CUDA graph each); 6 reaches the host-link bound
+INFLIGHT = 6          # compiled modules kept in flight (own stream, arena and CUDA graph each); 6 reaches the host-link bound
 METRIC, UNIT = "gpt2_block_tokens_per_s", "tokens/s"
+REF_INSTALL = ROOT / "baseline" / "_ref"
 
 
 def peaks():
@@ -176,6 +187,26 @@ def max_over_ranks(dist, ms):
     return float(t.item())
 
 
+def bind_to_the_gpu_s_cores(local):
+    """Run this rank (and so first-touch its pinned buffers) on the cores next to its GPU: the host
+    side of every copy then stays on that NUMA node.  Reads the PCI device's local_cpulist; silently
+    keeps the current affinity where sysfs does not say."""
+    try:
+        prop = torch.cuda.get_device_properties(local)
+        bdf = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        text = Path(f"/sys/bus/pci/devices/{bdf}/local_cpulist").read_text().strip()
+        cores = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cores.update(range(int(lo), int(hi or lo) + 1))
+        cores &= os.sched_getaffinity(0)
+        if cores:
+            os.sched_setaffinity(0, cores)
+        return text
+    except Exception:   # noqa: BLE001
+        return None
+
+
 # ---------------------------------------------------------------------------------------------
 # CPU arm
 # ---------------------------------------------------------------------------------------------
@@ -201,7 +232,7 @@ def cpu_block_tokens_per_s(seconds_budget=12.0, threads=None):
     return done * TOKENS / dt, done, torch.get_num_threads()
 
 
-def reference_arm(args, dist, rank):
+def reference_arm(args, rank):
     if rank != 0:
         return
     values = []
@@ -209,91 +240,16 @@ def reference_arm(args, dist, rank):
         v, done, cores = cpu_block_tokens_per_s(seconds_budget=max(2.0, 60.0 / (args.warmup + args.steps)))
         values.append(v)
     value = float(np.mean(values[args.warmup:]))
-    sample = f"{done} of {SEQS} sequences x {TOKENS} tokens per step, eager PyTorch float32 (oneDNN)"
+    sample = (f"{done} of {SEQS} sequences x {TOKENS} tokens per step, eager PyTorch float32 (oneDNN) in one process "
+              f"on rank 0's host cores")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": SEQS * TOKENS / value * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": dict(workload_config(args.precision, args.gpus), cpu_arithmetic="f32, one process on rank 0's host cores"),
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.precision, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
-
-
-def device_call_ms(fn, calls=200, rounds=5):
-    """Milliseconds per call of a compiled module on device tensors, back-to-back calls between two
-    CUDA events, best of `rounds` (how the reference's benchmark times a block: bench_gpu.py:54-81)."""
-    for _ in range(5):
-        fn()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    best = float("inf")
-    for _ in range(rounds):
-        start.record()
-        for _ in range(calls):
-            fn()
-        end.record()
-        torch.cuda.synchronize()
-        best = min(best, start.elapsed_time(end) / calls)
-    return best
-
-
-def reference_triton_arm(args):
-    """The reference's own Triton GPU backend on this GPU, same block and inputs, timed the way the
-    reference's benchmark does (benchmarks/bench_gpu.py:43-49, 54-81): GPU time per call as a CUDA-graph
-    replay, and host-to-host p50 latency.  Needs the reference installed under baseline/_ref (a
-    git-ignored pip --target directory); prints an `unavailable` line otherwise.  Not the
-    `--impl reference` arm: an extra comparison point."""
-    from kiln_b200 import workloads as W
-    from kiln_b200.install import register_mlir_stub
-
-    def fail(why):
-        print(json.dumps(dict(line, unavailable=why)), flush=True)
-
-    root = ROOT / "baseline" / "_ref"
-    line = {"impl": "reference-triton", "precision": "tf32" if args.precision != "fp32" else "fp32"}
-    if not (root / "kiln" / "gpu").is_dir():
-        print(json.dumps(dict(line, unavailable="the reference is not installed under baseline/_ref")), flush=True)
-        return
-    if not torch.cuda.is_available():
-        print(json.dumps(dict(line, unavailable="no CUDA device")), flush=True)
-        return
-    try:
-        sys.path.insert(0, str(root))
-        register_mlir_stub()
-        import kiln
-
-        allow_tf32 = args.precision != "fp32"
-        out = {}
-        for tokens, seed in ((128, 0), (1024, SEED), (2048, SEED)):
-            model = W.block_module(seed, tokens)
-            x = torch.from_numpy(W.block_input(seed, tokens, index=0))
-            t0 = time.perf_counter()
-            compiled = kiln.compile(model, (x,), device="cuda", allow_tf32=allow_tf32, autotune=args.autotune)
-            compile_s = time.perf_counter() - t0
-            xd = x.cuda()
-            with torch.no_grad():
-                want = model(x).double()
-                got = compiled(xd).cpu().double()
-                err = float((got - want).abs().max() / want.abs().max())
-                call_ms = device_call_ms(lambda: compiled(xd))
-                xp = x.pin_memory()
-                for _ in range(5):
-                    compiled(xp)
-                torch.cuda.synchronize()
-                lat = []
-                for _ in range(50):
-                    t0 = time.perf_counter()
-                    compiled(xp).cpu()
-                    lat.append((time.perf_counter() - t0) * 1e3)
-            out[f"block_t{tokens}"] = {"call_ms": round(call_ms, 4), "e2e_p50_ms": round(float(np.median(lat)), 4),
-                                       "tokens_per_s": round(tokens / call_ms * 1e3), "rel_err_vs_eager": err,
-                                       "compile_s": round(compile_s, 1)}
-        line.update(out, autotune=bool(args.autotune))
-    except Exception as err:   # noqa: BLE001  (an extra: report, never fail the run)
-        line["unavailable"] = f"{type(err).__name__}: {err}"[:300]
     print(json.dumps(line), flush=True)
 
 
@@ -305,23 +261,88 @@ def workload_config(precision, n):
 
 
 # ---------------------------------------------------------------------------------------------
-# GPU arm
+# Building modules: through kiln.compile when the reference is installed, else from the stored plan
 # ---------------------------------------------------------------------------------------------
 
-def build_block(precision, tokens, seed, cuda_graphs=True):
-    from helpers import load_plan
-    from kiln_b200 import workloads as W
-    from kiln_b200.codegen import program_from_plan
-    from kiln_b200.runtime import GPUExecutable
-    from kiln_b200.spec import PlanSpec
+_KILN = None
 
-    plan = PlanSpec.from_json(load_plan(f"gpt2_block_t{tokens}"))
-    consts = W.plan_constants(plan.const_shapes, W.block_params(seed, tokens))
-    # per-kernel matmul configurations, e.g. KB200_BENCH_CONFIGS='{"k10": {"BN": 256}}' (experiments; default: the library's choice)
-    configs = json.loads(os.environ.get("KB200_BENCH_CONFIGS", "null"))
-    program = program_from_plan(plan, precision, configs)
-    return GPUExecutable(program, plan.arena_bytes, consts, plan.input_shapes, plan.output_shapes,
-                         cuda_graphs=cuda_graphs), plan
+
+def kiln_frontend():
+    """The reference's ``kiln`` module with this package registered as its GPU backend, or None."""
+    global _KILN
+    if _KILN is None:
+        _KILN = False
+        if (REF_INSTALL / "kiln" / "api.py").exists():
+            try:
+                sys.path.insert(0, str(REF_INSTALL))
+                import kiln_b200
+
+                _KILN = kiln_b200.install()
+            except Exception:   # noqa: BLE001
+                _KILN = False
+    return _KILN or None
+
+
+class Built:
+    """Executables of one benchmark configuration: the first compiled, further copies bound to
+    arenas of their own from the same program and constants."""
+
+    def __init__(self, case, precision, cuda_graphs=False):
+        from kiln_b200 import workloads as W
+        from kiln_b200.codegen import program_from_plan
+        from kiln_b200.runtime import GPUExecutable
+        from kiln_b200.spec import PlanSpec
+
+        self.case, self.precision, self.cuda_graphs = case, precision, cuda_graphs
+        kiln = kiln_frontend()
+        self.inputs = None
+        if kiln is not None:
+            module, x = W.case_module(case)
+            old = os.environ.get("KILN_GPU_PRECISION")
+            if precision == "bf16":
+                os.environ["KILN_GPU_PRECISION"] = "bf16"
+            try:
+                compiled = kiln.compile(module, (x,), device="cuda", allow_tf32=precision != "fp32", cuda_graphs=cuda_graphs)
+            finally:
+                if precision == "bf16":
+                    os.environ.pop("KILN_GPU_PRECISION", None) if old is None else os.environ.__setitem__("KILN_GPU_PRECISION", old)
+            first = compiled._exe
+            self.program, self.constants = first.program, compiled.graph.constants
+            self.arena_bytes = compiled.graph.attrs.get("arena_bytes", 0)
+            self.plan, self.source, self.inputs = first.program.plan, "kiln.compile (baseline/_ref frontend and passes)", [x]
+        else:
+            plan_json = W.stored_plan(case)
+            self.plan = PlanSpec.from_json(plan_json)
+            params, x = W.case_tensors(case)
+            self.constants = W.plan_constants(self.plan.const_shapes, params)
+            self.program = program_from_plan(self.plan, precision)
+            self.arena_bytes = self.plan.arena_bytes
+            first = GPUExecutable(self.program, self.arena_bytes, self.constants, self.plan.input_shapes,
+                                  self.plan.output_shapes, cuda_graphs=cuda_graphs)
+            self.source, self.inputs = "stored plan (kiln_b200/plans)", [torch.from_numpy(x)]
+        self.executables = [first]
+        self.fill(first)
+
+    def fill(self, exe):
+        for static, x in zip(exe.static_inputs, self.inputs):
+            static.copy_(x)
+
+    @property
+    def exe(self):
+        return self.executables[0]
+
+    def another(self):
+        from kiln_b200.runtime import GPUExecutable
+
+        exe = GPUExecutable(self.program, self.arena_bytes, self.constants, self.plan.input_shapes,
+                            self.plan.output_shapes, cuda_graphs=self.cuda_graphs)
+        self.fill(exe)
+        self.executables.append(exe)
+        return exe
+
+    def close(self):
+        for e in self.executables:
+            e.close()
 
 
 def time_region(dist, fn, steps):
@@ -349,20 +370,17 @@ def kernel_flops(kernel):
     return flops, byts
 
 
-# DRAM bytes (read + write) per launch of the 1024-token block's kernels in BF16 mode, from the
-# `ncu --set full` capture summarised in profiles/gpt2_block_t1024_bf16_launches_and_top_kernels.md.
-NCU_DRAM_BYTES = {
-    ("bf16", "k0_row"): 3.16e6, ("bf16", "k1_matmul"): 5.21e6, ("bf16", "k2_ew0"): 4.77e6, ("bf16", "k7_matmul"): 6.00e6,
-    ("bf16", "k8_row"): 3.16e6, ("bf16", "k9_matmul"): 6.41e6, ("bf16", "k10_matmul"): 14.26e6,
-    ("fp32", "k0_row"): 3.16e6, ("fp32", "k1_matmul"): 10.33e6, ("fp32", "k3_matmul"): 10.81e6, ("fp32", "k4_row"): 51.88e6,
-    ("fp32", "k5_matmul"): 53.57e6, ("fp32", "k6_ew0"): 3.18e6, ("fp32", "k7_matmul"): 8.75e6, ("fp32", "k8_row"): 3.16e6,
-    ("fp32", "k9_matmul"): 12.70e6, ("fp32", "k10_matmul"): 25.28e6,
-}
+# DRAM bytes (read + write) per launch of the 1024-token block's matmuls, from the `ncu` captures
+# summarised under profiles/ (one kernel, a few launches each; same shapes as the bench).
+NCU_DRAM_BYTES = json.loads((ROOT / "profiles" / "dram_bytes_per_launch.json").read_text()) \
+    if (ROOT / "profiles" / "dram_bytes_per_launch.json").exists() else {}
 
 
-def roofline_of(exe, plan, precision, iters=20):
-    """Per-launch CUDA-event times of every kernel; roofline of the one with the largest share."""
+def roofline_of(built, precision, iters=20):
+    """Per-launch CUDA-event times of every kernel; roofline of the one with the largest share.
+    The module is profiled as it runs in the step (tile choice for six plans in flight)."""
     pk, pk_kind = peaks()
+    exe, plan = built.exe, built.plan
     times = exe.profile_launches(exe.static_inputs[0], iters=iters)
     total = sum(ms for _, ms in times)
     i = max(range(len(times)), key=lambda j: times[j][1])
@@ -378,36 +396,17 @@ def roofline_of(exe, plan, precision, iters=20):
     else:
         achieved, unit, bound, peak, peak_note = byts / (ms * 1e-3) / 1e9, "GB/s", "hbm", pk["hbm_gbs"], f"{pk_kind} copy"
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-            "traffic": NCU_DRAM_BYTES.get((precision, name)) if TOKENS == 1024 else None,
-            "traffic_unit": "bytes per launch (ncu dram read + write)", "kernel": f"{name} ({exe.impls[i]})", "ms_per_launch": ms, "share": ms / total,
-            "peak_source": peak_note,
-            "per_kernel_ms": {n: round(t, 5) for n, t in times}}
+            "traffic": NCU_DRAM_BYTES.get(f"{precision}:{name}") if TOKENS == 1024 else None,
+            "traffic_unit": "bytes per launch (ncu dram read + write)", "kernel": f"{name} ({exe.impls[i]})", "ms_per_launch": ms,
+            "share": ms / total, "peak_source": peak_note,
+            "per_kernel_ms": {n: round(t, 5) for n, t in times if t > 0.0}}
 
 
 def graph_times(fn, repeats=20, replays=200):
-    """(best, median) seconds per call of ``fn``: ``repeats`` calls captured in one CUDA graph, the
-    replay timed with CUDA events ``replays`` times (the reference's kernel_seconds, runtime.py:93-132,
-    with a p50 beside the best)."""
-    stream = torch.cuda.Stream()
-    stream.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            fn()
-    torch.cuda.current_stream().wait_stream(stream)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for _ in range(repeats):
-            fn()
-    graph.replay()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    samples = []
-    for _ in range(replays):
-        start.record()
-        graph.replay()
-        end.record()
-        torch.cuda.synchronize()
-        samples.append(start.elapsed_time(end) / 1e3 / repeats)
+    """(best, median) seconds per call of ``fn`` over ``replays`` timed replays of a graph of ``repeats`` calls."""
+    from kiln_b200.runtime import GraphTimer
+
+    samples = GraphTimer(fn, repeats).samples(replays)
     return float(np.min(samples)), float(np.median(samples))
 
 
@@ -433,30 +432,71 @@ def tf32_peak_tflops(n=8192):
         torch.backends.cuda.matmul.allow_tf32 = old
 
 
-def extras(precision):
-    """The reference's other headline numbers: block latency, Linear TFLOP/s, fused-op GB/s."""
-    from gpu_helpers import build_executable
-    from helpers import case_data, load_plan
+def host_latency(exe, x_host, calls=200):
+    """p50 / best milliseconds of ``exe(x).cpu()`` with a pinned host input: what a caller waits for."""
+    for _ in range(5):
+        exe(x_host)
+    torch.cuda.synchronize()
+    lat = []
+    for _ in range(calls):
+        t0 = time.perf_counter()
+        exe(x_host)[0].cpu()
+        lat.append((time.perf_counter() - t0) * 1e3)
+    return float(np.median(lat)), float(np.min(lat))
 
-    def filled(case, prec):
-        plan = load_plan(case)
-        inputs, consts, _ = case_data(case, plan)
-        exe = build_executable(case, prec, cuda_graphs=False, plan_json=plan, consts=consts)
-        for static, x in zip(exe.static_inputs, inputs):
-            static.copy_(torch.from_numpy(np.ascontiguousarray(x)))
-        return exe
+
+def device_call_ms(fn, calls=200, rounds=5):
+    """Milliseconds per call of a compiled module on device tensors, back-to-back calls between two
+    CUDA events, best of `rounds` (how the reference's benchmark times a block: bench_gpu.py:54-81)."""
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(rounds):
+        start.record()
+        for _ in range(calls):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(end) / calls)
+    return best
+
+
+def block_numbers(case, precision):
+    """One sequence through the block: GPU time of its kernels, per call on device tensors, host to host."""
+    direct = Built(case, precision, cuda_graphs=False)
+    kernel_best, kernel_p50 = graph_times(direct.exe.run_static)
+    direct.close()
+    graphed = Built(case, precision, cuda_graphs=True)
+    t = graphed.plan.input_shapes[0][0]
+    xd = torch.randn(t, D, device="cuda")
+    call_ms = device_call_ms(lambda: graphed.exe(xd))
+    p50, best = host_latency(graphed.exe, torch.randn(t, D).pin_memory())
+    graphed.close()
+    return {"precision": precision, "e2e_p50_ms": round(p50, 4), "e2e_best_ms": round(best, 4), "call_ms": round(call_ms, 4),
+            "kernel_ms": round(kernel_best * 1e3, 4), "kernel_p50_ms": round(kernel_p50 * 1e3, 4),
+            "tokens_per_s": round(t / call_ms * 1e3), "built_from": graphed.source}
+
+
+def extras(precision):
+    """Every other BASELINE configuration at its stated precision: fused-op GB/s (config 3), Linear
+    TFLOP/s in TF32 and BF16 (config 2), the 2048-token MLP in TF32 (config 1), the 128-token block in
+    FP32 (config 0), the 128- and 2048-token blocks in the run's precision (config 4, one GPU)."""
+    from kiln_b200 import workloads as W
 
     out = {}
     pk, _ = peaks()
     for case, byts in (("bias_gelu_2048x3072", 50343936), ("layernorm_2048x768", 12589056),
                        ("softmax_12x512x512", 25165824)):
-        exe = filled(case, "fp32")
-        best, p50 = graph_times(exe.run_static)
+        built = Built(case, "fp32")
+        best, p50 = graph_times(built.exe.run_static)
         # cold: rotate through enough copies of the operands that nothing is left in the 126 MB L2
         n_sets = max(2, -(-2 * 126 * 2**20 // byts) + 1)
-        sets = [exe] + [filled(case, "fp32") for _ in range(n_sets - 1)]
+        for _ in range(n_sets - 1):
+            built.another()
 
-        def rotate():
+        def rotate(sets=built.executables):
             for e in sets:
                 e.run_static()
 
@@ -464,75 +504,157 @@ def extras(precision):
         out[case] = {"warm_gbs": round(byts / best / 1e9, 1), "warm_p50_gbs": round(byts / p50 / 1e9, 1),
                      "cold_gbs": round(byts * n_sets / cold_best / 1e9, 1), "cold_p50_gbs": round(byts * n_sets / cold_p50 / 1e9, 1),
                      "frac_of_measured_hbm": round(byts * n_sets / cold_best / 1e9 / pk["hbm_gbs"], 3),
-                     "buffer_sets": n_sets, "impl": exe.impls}
-        for e in sets:
-            e.close()
-    from kiln_b200 import workloads as W
-    mm_prec = precision if precision != "fp32" else "fp32"
-    mm_peak = pk["bf16_tflops"] if mm_prec == "bf16" else (tf32_peak_tflops() if mm_prec == "tf32" else None)
-    if mm_prec == "tf32":
-        out["tf32_peak_tflops_measured"] = round(mm_peak, 1)
-    for m, n, k in W.LINEAR_SHAPES:
-        exe = filled(f"linear_{m}x{n}x{k}", mm_prec)
-        best, p50 = graph_times(exe.run_static)
-        row = {"tflops": round(2 * m * n * k / best / 1e12, 2), "p50_tflops": round(2 * m * n * k / p50 / 1e12, 2),
-               "us": round(best * 1e6, 2), "precision": mm_prec, "impl": exe.impls}
-        if mm_peak and m > 1:
-            row["frac_of_measured_peak"] = round(row["tflops"] / mm_peak, 3)
-        if m == 1:      # decode GEMV: weights streamed once; cold = weight sets rotated through more than twice the L2
-            byts = 4 * k * n + 4 * n + 4 * k
-            row["gbs"] = round(byts / best / 1e9, 1)
-            n_sets = -(-2 * 126 * 2**20 // byts) + 1
-            sets = [exe] + [filled(f"linear_{m}x{n}x{k}", mm_prec) for _ in range(n_sets - 1)]
+                     "buffer_sets": n_sets, "impl": built.exe.impls}
+        built.close()
+    tf32_peak = tf32_peak_tflops()
+    out["tf32_peak_tflops_measured"] = round(tf32_peak, 1)
+    for mm_prec, mm_peak in (("tf32", tf32_peak), ("bf16", pk["bf16_tflops"])):
+        table = {}
+        for m, n, k in W.LINEAR_SHAPES:
+            built = Built(f"linear_{m}x{n}x{k}", mm_prec)
+            best, p50 = graph_times(built.exe.run_static)
+            row = {"tflops": round(2 * m * n * k / best / 1e12, 2), "p50_tflops": round(2 * m * n * k / p50 / 1e12, 2),
+                   "us": round(best * 1e6, 2), "impl": built.exe.impls}
+            if m > 1:
+                row["frac_of_measured_peak"] = round(row["tflops"] / mm_peak, 3)
+            else:      # decode GEMV: weights streamed once; cold = weight sets rotated through more than twice the L2
+                byts = 4 * k * n + 4 * n + 4 * k
+                row["gbs"] = round(byts / best / 1e9, 1)
+                n_sets = -(-2 * 126 * 2**20 // byts) + 1
+                for _ in range(n_sets - 1):
+                    built.another()
 
-            def rotate():
-                for e in sets:
-                    e.run_static()
+                def rotate(sets=built.executables):
+                    for e in sets:
+                        e.run_static()
 
-            cold_best, _ = graph_times(rotate, repeats=2, replays=50)
-            row["cold_gbs"] = round(byts * n_sets / cold_best / 1e9, 1)
-            row["cold_frac_of_measured_hbm"] = round(byts * n_sets / cold_best / 1e9 / pk["hbm_gbs"], 3)
-            for e in sets[1:]:
-                e.close()
-        out[f"linear_{m}x{n}x{k}"] = row
-        exe.close()
-    for t, seed in ((128, 0), (2048, 4)):
-        direct, _ = build_block(precision, t, seed, cuda_graphs=False)
-        kernel_best, kernel_p50 = graph_times(direct.run_static)
-        direct.close()
-        exe, _ = build_block(precision, t, seed)
-        xd = torch.randn(t, D, device="cuda")
-        call_ms = device_call_ms(lambda: exe(xd))
-        x = torch.randn(t, D).pin_memory()
-        for _ in range(5):
-            exe(x)
-        torch.cuda.synchronize()
-        lat = []
-        for _ in range(200):
-            t0 = time.perf_counter()
-            y = exe(x)[0]
-            y.cpu()
-            lat.append((time.perf_counter() - t0) * 1e3)
-        out[f"block_t{t}"] = {"e2e_p50_ms": round(float(np.median(lat)), 4), "e2e_best_ms": round(float(np.min(lat)), 4),
-                              "call_ms": round(call_ms, 4), "kernel_ms": round(kernel_best * 1e3, 4),
-                              "kernel_p50_ms": round(kernel_p50 * 1e3, 4)}
-        exe.close()
+                cold_best, _ = graph_times(rotate, repeats=2, replays=50)
+                row["cold_gbs"] = round(byts * n_sets / cold_best / 1e9, 1)
+                row["cold_frac_of_measured_hbm"] = round(byts * n_sets / cold_best / 1e9 / pk["hbm_gbs"], 3)
+            table[f"{m}x{n}x{k}"] = row
+            built.close()
+        out[f"linear_{mm_prec}"] = table
+    built = Built("mlp_2048", "tf32")
+    best, p50 = graph_times(built.exe.run_static)
+    flops = 2 * 2 * 2048 * 768 * 3072
+    out["mlp_2048_tf32"] = {"tflops": round(flops / best / 1e12, 2), "p50_tflops": round(flops / p50 / 1e12, 2), "us": round(best * 1e6, 2),
+                            "frac_of_measured_peak": round(flops / best / 1e12 / tf32_peak, 3), "impl": built.exe.impls,
+                            "built_from": built.source}
+    built.close()
+    out["block_t128_fp32"] = block_numbers("gpt2_block_t128", "fp32")
+    if precision != "fp32":
+        out["block_t128"] = block_numbers("gpt2_block_t128", precision)
+    out["block_t2048"] = block_numbers("gpt2_block_t2048", precision)
     return out
 
 
-def reference_triton_extra(precision):
-    """The reference's Triton backend on this GPU, in a process of its own (it registers the same
-    module names this package does); its one JSON line, or why it could not run."""
-    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference-triton", "--autotune",
-           "--precision", "fp32" if precision == "fp32" else "tf32"]
+# ---------------------------------------------------------------------------------------------
+# The reference's own Triton backend on this GPU (an extra comparison point, not `--impl reference`)
+# ---------------------------------------------------------------------------------------------
+
+def reference_triton_arm(args):
+    """The reference's Triton GPU backend, stock ``kiln.compile`` from baseline/_ref, on the same
+    shapes and inputs, timed the way the reference's benchmark does (benchmarks/bench_gpu.py:43-81,
+    114-192): kernel time as a CUDA-graph replay for the Linears, the MLP and the fused ops, ms per
+    call and host-to-host p50 for the block.  Prints one JSON line per finished section, so that a
+    caller with a time limit keeps what was done."""
+    from kiln_b200 import workloads as W
+    from kiln_b200.install import register_mlir_stub
+
+    tag = {"impl": "reference-triton"}
+    if not (REF_INSTALL / "kiln" / "gpu").is_dir():
+        print(json.dumps(dict(tag, unavailable="the reference is not installed under baseline/_ref")), flush=True)
+        return
+    if not torch.cuda.is_available():
+        print(json.dumps(dict(tag, unavailable="no CUDA device")), flush=True)
+        return
+    sys.path.insert(0, str(REF_INSTALL))
+    register_mlir_stub()
+    import kiln
+    from kiln.gpu.runtime import kernel_seconds as reference_kernel_seconds
+
+    def section(name, fn):
+        try:
+            print(json.dumps(dict(tag, section=name, **fn())), flush=True)
+        except Exception as err:   # noqa: BLE001  (an extra: report, never fail the run)
+            print(json.dumps(dict(tag, section=name, unavailable=f"{type(err).__name__}: {err}"[:300])), flush=True)
+
+    def block(tokens, seed, allow_tf32):
+        def run():
+            model = W.block_module(seed, tokens)
+            x = torch.from_numpy(W.block_input(seed, tokens, index=0))
+            t0 = time.perf_counter()
+            compiled = kiln.compile(model, (x,), device="cuda", allow_tf32=allow_tf32, autotune=args.autotune)
+            compile_s = time.perf_counter() - t0
+            xd = x.cuda()
+            with torch.no_grad():
+                want = model(x).double()
+                err = float((compiled(xd).cpu().double() - want).abs().max() / want.abs().max())
+                call_ms = device_call_ms(lambda: compiled(xd))
+                xp = x.pin_memory()
+                for _ in range(5):
+                    compiled(xp)
+                torch.cuda.synchronize()
+                lat = []
+                for _ in range(50):
+                    t0 = time.perf_counter()
+                    compiled(xp).cpu()
+                    lat.append((time.perf_counter() - t0) * 1e3)
+            return {"precision": "tf32" if allow_tf32 else "fp32", "call_ms": round(call_ms, 4),
+                    "e2e_p50_ms": round(float(np.median(lat)), 4), "tokens_per_s": round(tokens / call_ms * 1e3),
+                    "rel_err_vs_eager": err, "compile_s": round(compile_s, 1), "autotune": bool(args.autotune)}
+        return run
+
+    def kernel_case(case, allow_tf32, autotune, flops=None, byts=None):
+        def run():
+            module, x = W.case_module(case)
+            compiled = kiln.compile(module, (x,), device="cuda", allow_tf32=allow_tf32, cuda_graphs=False, autotune=autotune)
+            xd = x.cuda()
+            with torch.no_grad():
+                seconds = reference_kernel_seconds(lambda: compiled(xd))
+            row = {"precision": "tf32" if allow_tf32 else "fp32", "us": round(seconds * 1e6, 2), "autotune": bool(autotune)}
+            if flops:
+                row["tflops"] = round(flops / seconds / 1e12, 2)
+            if byts:
+                row["warm_gbs"] = round(byts / seconds / 1e9, 1)
+            return row
+        return run
+
+    section("block_t128_fp32", block(128, 0, False))
+    section("block_t128", block(128, 0, True))
+    section("block_t2048", block(2048, SEED, True))
+    section("block_t1024", block(1024, SEED, True))
+    for m, n, k in W.LINEAR_SHAPES:
+        section(f"linear_tf32_{m}x{n}x{k}", kernel_case(f"linear_{m}x{n}x{k}", True, args.autotune, flops=2 * m * n * k))
+    section("mlp_2048_tf32", kernel_case("mlp_2048", True, args.autotune, flops=2 * 2 * 2048 * 768 * 3072))
+    for case, byts in (("bias_gelu_2048x3072", 50343936), ("layernorm_2048x768", 12589056), ("softmax_12x512x512", 25165824)):
+        section(case, kernel_case(case, False, False, byts=byts))
+
+
+def reference_triton_extra(budget_s=300):
+    """Runs the arm above in a process of its own (it registers the same module names this package
+    does) and keeps every section that finished within the budget."""
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference-triton", "--autotune"]
+    out = {"impl": "reference-triton", "budget_s": budget_s}
     try:
-        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=420)
-        for text in reversed(proc.stdout.strip().splitlines()):
-            if text.startswith("{"):
-                return json.loads(text)
-        return {"impl": "reference-triton", "unavailable": (proc.stderr or "no output")[-200:]}
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        try:
+            stdout, _ = proc.communicate(timeout=budget_s)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            stdout, _ = proc.communicate()
+            out["stopped_at_budget"] = True
+        for text in stdout.splitlines():
+            if not text.startswith("{"):
+                continue
+            row = json.loads(text)
+            if "section" in row:
+                out[row.pop("section")] = {k: v for k, v in row.items() if k != "impl"}
+            elif "unavailable" in row:
+                out["unavailable"] = row["unavailable"]
     except Exception as err:   # noqa: BLE001
-        return {"impl": "reference-triton", "unavailable": f"{type(err).__name__}: {err}"[:200]}
+        out["unavailable"] = f"{type(err).__name__}: {err}"[:200]
+    return out
 
 
 def dtype_of(precision, impls):
@@ -543,12 +665,18 @@ def dtype_of(precision, impls):
     return precision
 
 
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
 def gpu_arm(args, dist, rank, world, local):
     from kiln_b200 import workloads as W
+    from kiln_b200.runtime import StreamedBatch
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
+    cpulist = bind_to_the_gpu_s_cores(local)
     precision = args.precision
     host = [torch.from_numpy(W.block_input(SEED, TOKENS, index=rank * SEQS + i)).pin_memory() for i in range(SEQS)]
     dev_in = torch.stack([h.cuda(non_blocking=True) for h in host])
@@ -558,27 +686,35 @@ def gpu_arm(args, dist, rank, world, local):
 
     # INFLIGHT compiled modules (own arena, static buffers and stream each) run round-robin, as a server
     # keeps several requests in flight: kernels of one sequence fill the SMs another leaves idle, and
-    # copies overlap kernels.  A whole step of 64 sequences is one CUDA graph (kiln_b200.runtime.
-    # StreamedBatch), so a busy host does not starve the GPU of launches.
-    from kiln_b200.runtime import StreamedBatch
-
-    exe, plan = build_block(precision, TOKENS, SEED, cuda_graphs=False)
-    exes = [exe] + [build_block(precision, TOKENS, SEED, cuda_graphs=False)[0] for _ in range(INFLIGHT - 1)]
+    # copies overlap kernels.  A whole step of 64 sequences is one CUDA graph, so a busy host does not
+    # starve the GPU of launches.
+    built = Built(f"gpt2_block_t{TOKENS}", precision)
+    for _ in range(INFLIGHT - 1):
+        built.another()
+    exes, exe = built.executables, built.exe
     resident = StreamedBatch(exes).capture(list(dev_in), list(dev_out))
-    step_resident = resident.run
-
     for _ in range(args.warmup):
-        step_resident()
+        resident.run()
     with ClockSampler(local) as clocks:
-        ms = time_region(dist, step_resident, args.steps)
+        ms = time_region(dist, resident.run, args.steps)
     resident.status()
     # end to end: the same step with pinned host tensors as sources and sinks (201 MB each way per step)
     e2e = StreamedBatch(exes).capture(host, host_out)
-    step_e2e = e2e.run
     for _ in range(max(1, args.warmup // 2)):
-        step_e2e()
-    ms_e2e = time_region(dist, step_e2e, args.steps)
+        e2e.run()
+    ms_e2e = time_region(dist, e2e.run, args.steps)
     e2e.status()
+    # ... and the same copies with no kernels between them: the host link's share of that step
+    copies = StreamedBatch(exes).capture(host, host_out, kernels=False)
+    copies.run()
+    ms_copies = time_region(dist, copies.run, args.steps)
+    # strong scaling (BASELINE config 4): 64 sequences in total, 64 / world per GPU
+    share = max(1, SEQS // world)
+    strong = StreamedBatch(exes).capture(list(dev_in[:share]), list(dev_out[:share]))
+    for _ in range(args.warmup):
+        strong.run()
+    ms_strong = time_region(dist, strong.run, args.steps)
+    strong.status()
     tokens = world * SEQS * TOKENS * args.steps
     value, e2e_value = tokens / (ms * 1e-3), tokens / (ms_e2e * 1e-3)
     if rank != 0:
@@ -590,12 +726,16 @@ def gpu_arm(args, dist, rank, world, local):
         "config": workload_config(precision, world),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * SEQS * TOKENS * D * 4,
                 "d2h_bytes_per_step": world * SEQS * TOKENS * D * 4, "ms_per_step": ms_e2e / args.steps,
-                "modules_in_flight": INFLIGHT},
+                "copy_only_ms": ms_copies / args.steps, "modules_in_flight": INFLIGHT, "host_cores_near_gpu": cpulist},
         "gpu_launches": world * args.steps * SEQS * exe.device_launches, "modules_in_flight": INFLIGHT,
         "clocks": clocks.summary(),
         "impls": dict(zip(exe.launch_names, exe.impls)),
+        "built_from": built.source,
     }
-    line["roofline"] = roofline_of(exe, plan, precision)
+    line["roofline"] = roofline_of(built, precision)
+    line["extras"] = {"strong_scaling": {"sequences_total": share * world, "sequences_per_gpu": share,
+                                         "ms_per_step": ms_strong / args.steps,
+                                         "tokens_per_s": share * world * TOKENS * args.steps / (ms_strong * 1e-3)}}
     if world == 1:
         v, done, cores = cpu_block_tokens_per_s(seconds_budget=12.0)
         v1, done1, _ = cpu_block_tokens_per_s(seconds_budget=6.0, threads=1)
@@ -604,24 +744,19 @@ def gpu_arm(args, dist, rank, world, local):
                                 "one_thread": {"value": v1, "unit": UNIT, "cores": 1,
                                                "sample": f"{done1} sequences x {TOKENS} tokens"}}
         if not args.no_extras:
+            built.close()
             try:
-                line["extras"] = extras(precision)
-                line["extras"]["reference_triton"] = reference_triton_extra(precision)
+                line["extras"].update(extras(precision))
             except Exception as err:   # noqa: BLE001  (extras never invalidate the headline line)
-                line["extras"] = {"error": f"{type(err).__name__}: {err}"[:200]}
+                line["extras"]["error"] = f"{type(err).__name__}: {err}"[:200]
+            line["extras"]["reference_triton"] = reference_triton_extra()
     print(json.dumps(line), flush=True)
 
 
 def single_case(args):
-    """One stored plan, launched directly (no CUDA graph) so a profiler sees plain kernel launches."""
-    from gpu_helpers import build_executable
-    from helpers import case_data, load_plan
-
-    plan = load_plan(args.case)
-    inputs, consts, _ = case_data(args.case, plan)
-    exe = build_executable(args.case, args.precision, cuda_graphs=False, plan_json=plan, consts=consts)
-    for static, x in zip(exe.static_inputs, inputs):
-        static.copy_(torch.from_numpy(np.ascontiguousarray(x)))
+    """One configuration, launched directly (no CUDA graph) so a profiler sees plain kernel launches."""
+    built = Built(args.case, args.precision)
+    exe = built.exe
     for _ in range(max(1, args.warmup)):
         exe.run_static()
     torch.cuda.synchronize()
@@ -632,7 +767,7 @@ def single_case(args):
     end.record()
     torch.cuda.synchronize()
     exe.status()
-    print(json.dumps({"case": args.case, "precision": args.precision, "impls": exe.impls,
+    print(json.dumps({"case": args.case, "precision": args.precision, "impls": exe.impls, "built_from": built.source,
                       "ms_per_call": start.elapsed_time(end) / args.steps, "launches_per_call": exe.device_launches}))
 
 
@@ -643,12 +778,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"])
     ap.add_argument("--autotune", action="store_true", help="reference-triton only: let the reference autotune its matmuls")
-    ap.add_argument("--precision", default=os.environ.get("KB200_BENCH_PRECISION", "bf16"),
-                    choices=["fp32", "tf32", "bf16"])
+    ap.add_argument("--precision", default="bf16", choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--case", default=None,
-                    help="run one stored plan (a name under tests/golden/plans) --steps times and print its GPU "
-                         "time per call; the small, single-kernel workload to put under a profiler")
+                    help="run one benchmark configuration (a name under kiln_b200/plans) --steps times and print its "
+                         "GPU time per call; the small, single-kernel workload to put under a profiler")
     args = ap.parse_args()
     if args.case:
         single_case(args)
@@ -659,8 +793,7 @@ def main():
             reference_triton_arm(args)
         return
     if args.impl == "reference":
-        rank = int(os.environ.get("RANK", 0))
-        reference_arm(args, None, rank)
+        reference_arm(args, int(os.environ.get("RANK", 0)))
         return
     dist, rank, world, local = dist_setup(args.gpus)
     try:

@@ -349,7 +349,7 @@ class StreamedBatch:
         self.graph = None
         self.requests = 0
 
-    def _enqueue(self, sources, sinks):
+    def _enqueue(self, sources, sinks, kernels=True):
         cur = torch.cuda.current_stream(self.device)
         for st in self.streams:
             st.wait_stream(cur)
@@ -358,13 +358,16 @@ class StreamedBatch:
             exe = self.executables[i % n]
             with torch.cuda.stream(self.streams[i % n]):
                 exe.static_inputs[0].copy_(src, non_blocking=True)
-                exe.run_static()
+                if kernels:
+                    exe.run_static()
                 dst.copy_(exe.static_outputs[0], non_blocking=True)
         for st in self.streams:
             cur.wait_stream(st)
 
-    def capture(self, sources, sinks):
-        """Capture one step over these tensors (single-input, single-output modules)."""
+    def capture(self, sources, sinks, kernels=True):
+        """Capture one step over these tensors (single-input, single-output modules).  With
+        ``kernels=False`` only the copies in and out are captured: the same traffic over the host
+        link with no compute, which tells how much of an end-to-end step is the link's."""
         if len(sources) != len(sinks):
             raise ValueError("one sink per source")
         for t in list(sources) + list(sinks):
@@ -374,12 +377,12 @@ class StreamedBatch:
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
-                self._enqueue(sources, sinks)          # warm-up outside capture (lazy initialisation)
+                self._enqueue(sources, sinks, kernels)          # warm-up outside capture (lazy initialisation)
             torch.cuda.current_stream(self.device).wait_stream(side)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self._enqueue(sources, sinks)
+                self._enqueue(sources, sinks, kernels)
         self.graph = graph
         self.requests = len(sources)
         return self

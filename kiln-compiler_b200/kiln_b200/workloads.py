@@ -150,3 +150,87 @@ def block_module(seed, t, d=768, heads=12):
     state = {k: torch.from_numpy(v.copy()) for k, v in block_params(seed, t, d, heads).items()}
     model.load_state_dict(state)
     return model
+
+
+# ---------------------------------------------------------------------------------------------
+# The benchmark configurations by name: tensors, modules, stored launch plans
+# ---------------------------------------------------------------------------------------------
+
+BENCHMARK_PREFIXES = ("gpt2_block_t", "mlp_2048", "linear_", "bias_gelu_", "layernorm_2048", "softmax_12x")
+PLAN_DIR = __import__("pathlib").Path(__file__).resolve().parent / "plans"
+
+
+def is_benchmark_case(case):
+    return case.startswith(BENCHMARK_PREFIXES)
+
+
+def benchmark_cases():
+    return sorted(p.stem for p in PLAN_DIR.glob("*.json"))
+
+
+def stored_plan(case):
+    """The launch plan of a benchmark configuration as the reference's passes produce it (written by
+    tests/golden/make_golden.py from the imported reference; a test compares it with a live compile
+    where the reference is importable).  Lets the backend run a configuration on a machine that has
+    no copy of the reference's frontend."""
+    import json
+
+    return json.loads((PLAN_DIR / f"{case}.json").read_text())
+
+
+def case_tensors(case):
+    """(parameters by module path, input array) of a benchmark configuration."""
+    if case.startswith("gpt2_block_t"):
+        t = int(case[len("gpt2_block_t"):])
+        seed = 0 if t == 128 else 4
+        return block_params(seed, t), block_input(seed, t)
+    if case == "mlp_2048":
+        return mlp_params(), mlp_input()
+    if case.startswith("linear_"):
+        m, n, k = (int(v) for v in case[len("linear_"):].split("x"))
+        return linear_params(m, n, k)
+    if case.startswith("bias_gelu"):
+        return bias_gelu_data()
+    if case.startswith("layernorm_2048"):
+        return layernorm_data()
+    if case.startswith("softmax_12x"):
+        return softmax_data()
+    raise KeyError(case)
+
+
+def case_module(case):
+    """(torch.nn.Module, input tensor) of a benchmark configuration: what a user hands to
+    ``kiln.compile``.  Parameter names match ``case_tensors`` and the stored plans' constants."""
+    import torch
+    from torch import nn
+    from torch.nn import functional as F
+
+    params, x = case_tensors(case)
+    state = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in params.items()}
+    if case.startswith("gpt2_block_t"):
+        t = int(case[len("gpt2_block_t"):])
+        return block_module(0 if t == 128 else 4, t), torch.from_numpy(x)
+    if case == "mlp_2048":
+        module = nn.Sequential(nn.Linear(768, 3072), nn.GELU(approximate="tanh"), nn.Linear(3072, 768))
+    elif case.startswith("linear_"):
+        module = nn.Linear(x.shape[1], params["weight"].shape[0])
+    elif case.startswith("bias_gelu"):
+        class BiasGelu(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.register_buffer("bias", torch.zeros(x.shape[1]))
+
+            def forward(self, t):
+                return F.gelu(t + self.bias, approximate="tanh")
+
+        module = BiasGelu()
+    elif case.startswith("layernorm_2048"):
+        module = nn.LayerNorm(x.shape[1], eps=1e-5)
+    else:
+        class Softmax(nn.Module):
+            def forward(self, t):
+                return F.softmax(t, -1)
+
+        module = Softmax()
+    module.load_state_dict(state)
+    return module.eval(), torch.from_numpy(x)

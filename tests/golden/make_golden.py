@@ -7,7 +7,8 @@ to this repository root's parent).  It imports the reference's frontend, passes,
 NumPy interpreter and its test models, runs them on seeded inputs, and writes:
 
   plans/<case>.json      the launch plan kiln_b200.codegen.plan_of derives from the
-                         reference's optimised graph (kernels, layouts, arena offsets)
+                         reference's optimised graph (kernels, layouts, arena offsets); the
+                         benchmark configurations' plans go to kiln_b200/plans/ in the package
   vectors/<case>.npz     inputs, constants and the reference's own results:
                          out<i>  eager PyTorch (what tests/test_gpu.py of the reference
                                  compares against), interp<i>  kiln.ir.interpret
@@ -84,7 +85,10 @@ def main():
     def record(case, graph, pm):
         plan = plan_of(graph)
         plan.name = case
-        (HERE / "plans" / f"{case}.json").write_text(plan.dumps() + "\n")
+        # the benchmark configurations' plans ship with the package (the benchmark runs them where the
+        # reference is not installed); every other plan is a test fixture
+        plan_dir = W.PLAN_DIR if W.is_benchmark_case(case) else HERE / "plans"
+        (plan_dir / f"{case}.json").write_text(plan.dumps() + "\n")
         program = reference_generate(graph)
         stats = pm.stats.get("memory-plan", {})
         summary[case] = {

@@ -11,15 +11,15 @@ from kiln_b200 import workloads as W
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
-BIG_PREFIXES = ("gpt2_block_t", "mlp_2048", "linear_", "bias_gelu_", "layernorm_2048", "softmax_12x")
+BIG_PREFIXES = W.BENCHMARK_PREFIXES
 
 
 def is_big(case):
-    return case.startswith(BIG_PREFIXES)
+    return W.is_benchmark_case(case)
 
 
 def all_cases():
-    return sorted(p.stem for p in (GOLDEN / "plans").glob("*.json"))
+    return sorted([p.stem for p in (GOLDEN / "plans").glob("*.json")] + W.benchmark_cases())
 
 
 def small_cases():
@@ -31,6 +31,9 @@ def big_cases():
 
 
 def load_plan(case):
+    """Plans of the benchmark configurations ship with the package (kiln_b200/plans); the rest are fixtures here."""
+    if is_big(case):
+        return W.stored_plan(case)
     return json.loads((GOLDEN / "plans" / f"{case}.json").read_text())
 
 
@@ -55,23 +58,7 @@ def case_data(case, plan=None):
         return inputs, consts, {"out": [vec[f"out{i}"] for i in range(n_out)],
                                 "interp": [vec[f"interp{i}"] for i in range(n_out)]}
     shapes = plan["const_shapes"]
-    if case.startswith("gpt2_block_t"):
-        t = int(case[len("gpt2_block_t"):])
-        seed = 0 if t == 128 else 4
-        params, x = W.block_params(seed, t), W.block_input(seed, t)
-    elif case == "mlp_2048":
-        params, x = W.mlp_params(), W.mlp_input()
-    elif case.startswith("linear_"):
-        m, n, k = (int(v) for v in case[len("linear_"):].split("x"))
-        params, x = W.linear_params(m, n, k)
-    elif case.startswith("bias_gelu"):
-        params, x = W.bias_gelu_data()
-    elif case.startswith("layernorm_2048"):
-        params, x = W.layernorm_data()
-    elif case.startswith("softmax_12x"):
-        params, x = W.softmax_data()
-    else:
-        raise KeyError(case)
+    params, x = W.case_tensors(case)
     consts = W.plan_constants(shapes, params)
     return [x], consts, {"sub": [vec["sub0"]], "step": [int(vec["step0"])]}
 
