@@ -649,7 +649,7 @@ def reference_triton_extra(budget_s=300):
                 continue
             row = json.loads(text)
             if "section" in row:
-                out[row.pop("section")] = {k: v for k, v in row.items() if k != "impl"}
+                out[row["section"]] = {k: v for k, v in row.items() if k not in ("impl", "section")}
             elif "unavailable" in row:
                 out["unavailable"] = row["unavailable"]
     except Exception as err:   # noqa: BLE001

@@ -29,8 +29,17 @@ __device__ __forceinline__ float d_erf(float x) {
   return x < 0.0f ? -y : y;
 }
 
+// tanh-GELU: 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3)  (kiln/gpu/codegen.py:70-75).
+// Evaluated through the identity 0.5 (1 + tanh(u)) = 1 / (1 + exp(-2u)): the same function, in five
+// FP32 instructions and two special-function ones (ex2, rcp) instead of seventeen and two -- the
+// bias+GELU kernel was bound by instruction issue, not by memory.  exp(-2u) = 2^(x (k1 + k3 x^2)).
 __device__ __forceinline__ float d_gelu_tanh(float x) {
-  return 0.5f * x * (1.0f + d_tanh(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  const float k3 = k1 * 0.044715f;
+  const float t = x * x;
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * fmaf(t, k3, k1)));   // +inf for very negative x, where the result is -0
+  return __fdividef(x, 1.0f + e);
 }
 
 __device__ __forceinline__ float d_gelu_erf(float x) { return 0.5f * x * (1.0f + d_erf(x * 0.7071067811865476f)); }

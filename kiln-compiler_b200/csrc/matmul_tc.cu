@@ -99,6 +99,7 @@ struct TcParams {
   int pre_col_step, pre_mat_step;    // chain steps whose operand the epilogue fetches ahead (-1 = none)
   __nv_bfloat16* out16;              // optional bf16 copy of the output (same strides as the output), or null
   int splits;           // split-K factor: a tile's K range is shared by the CTAs of one cluster of this size
+  int recv_offset;      // split K: byte offset (from the aligned tile area) of the area the neighbours push their partial bands into
   int num_units;        // num_tiles * splits
   int store_mode;       // 0: the epilogue warps store with ordinary global stores; 1: bulk tensor stores from shared memory
   int split3;           // exact-FP32 mode: every operand is split in shared memory into a TF32 head and a TF32 tail,
@@ -328,10 +329,15 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     if (lane == 0) abort_flag = 0;
     if (lane < 2 * kMaxStages + 4)
       mbar_init(full0 + 8 * lane, lane >= 2 * kMaxStages + 2 ? kEpiWarps : (lane < kMaxStages ? 2 : (lane >= 2 * kMaxStages ? (uint32_t)p.issuers : 1)));
-    else if (lane < 2 * kMaxStages + 6) mbar_init(full0 + 8 * lane, (uint32_t)p.splits);   // one arrival per CTA of the cluster
+    else if (lane < 2 * kMaxStages + 6) mbar_init(full0 + 8 * lane, 1);   // split K: `received`, completed by the bytes the neighbours push
     if (lane < kMaxStages) mbar_init(full0 + 8 * (2 * kMaxStages + 6 + lane), kEpiWarps);  // split done: one arrival per epilogue warp
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // The parameter block is read through the constant cache, cold at kernel start: touch the lines the
+  // producers and the MMA thread need now, under the set-up, instead of in front of the first copy.
+  if (lane == 0 && (warp <= 1 || warp >= kProducerBWarp))
+    asm volatile("" ::"r"(p.bn), "r"(p.tmem_cols), "r"(p.idesc), "r"(p.num_tiles), "l"(p.magic_stages), "l"(p.magic_tn), "l"(p.magic_tpb)
+                 : "memory");
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                  "r"((uint32_t)p.tmem_cols)
@@ -708,6 +714,7 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           float4* dst = reinterpret_cast<float4*>(part + (size_t)lane * p.bn + c);
 #pragma unroll
           for (int q = 0; q < 8; ++q) dst[q ^ (lane & 7)] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          fence_async_smem();      // the bands are pushed to the neighbours by bulk copies (async proxy)
         }
       }
       // this warp is done reading the accumulator: hand it back to the MMA issuer
@@ -721,97 +728,125 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     if (bulk && lane == 0) tma_store_wait_read();   // shared memory must outlive the stores that read it
   }
 
-  // ---------------- split K: reduce across the cluster through distributed shared memory ----------------
-  // The `splits` CTAs of a cluster hold partial sums of the same tile.  Each tells every CTA of the
-  // cluster "my partial tile is parked" by arriving on that CTA's `parked` mbarrier, waits until all
-  // have arrived on its own, then takes a band of rows, adds the partial bands of all CTAs in rank
-  // order (so the result does not depend on timing), applies the epilogue and stores.  A second
-  // round of arrivals (`released`) keeps every CTA resident until no neighbour reads its shared
-  // memory any more.  (A hardware cluster barrier at these two points cost 5500 cycles each time.)
-  // Every CTA sends both rounds also after an aborted wait: all loops above are bounded.
+  // ---------------- split K: reduce across the cluster ----------------
+  // The `splits` CTAs of a cluster hold partial sums of the same tile, parked row-major in their
+  // idle operand rings.  CTA r finishes the band of 128 / splits rows number r: every other CTA
+  // PUSHES its part of that band into r's receive area with one bulk shared-to-shared copy that
+  // completes on r's `received` barrier -- data and signal in one asynchronous operation, no release
+  // fence after the parked tile and no loads over the cluster network (a first version had every
+  // CTA announce its parked tile and read the neighbours' bands: the announcing release cost 5500
+  // cycles and the scalar remote loads 6000).  r then adds the bands in rank order, its own in its
+  // place (so the result does not depend on timing), applies the epilogue and stores.  The hardware
+  // cluster barrier, split into arrive and wait, brackets the exchange: nobody pushes before every
+  // CTA's barriers exist, nobody leaves before every push out of its shared memory has landed.
+  // Every CTA goes through all of it also after an aborted wait: all loops are bounded.
   if (p.splits > 1) {
-    const uint32_t parked = smem_u32(&bars[2 * kMaxStages + 4]), released = smem_u32(&bars[2 * kMaxStages + 5]);
+    const uint32_t received = smem_u32(&bars[2 * kMaxStages + 4]);
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int band_rows = kTileM / p.splits;
+    const uint32_t band_bytes = (uint32_t)(band_rows * p.bn * 4);
+    const uint32_t recv0 = tiles + (uint32_t)p.recv_offset;
+    if (threadIdx.x == 0) mbar_expect_tx(received, (uint32_t)(p.splits - 1) * band_bytes);
     cluster_wait();          // completes the arrive made before the main loop: every CTA's barriers are initialised
-    __syncthreads();         // every warp of this CTA has parked its part
+    __syncthreads();         // every warp of this CTA has parked its part (and fenced it to the async proxy)
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && threadIdx.x == 0) marks[3] = clock64();
 #endif
-    // (measured: the cluster-scope release carried by this first arrival takes 5500-6200 cycles, whichever
-    // warp makes it and however the tile was parked; the second one below ~1000.  It is the fixed cost
-    // that keeps split K from paying below ~64 slabs of K.)
-    if (warp == kIssuerBWarp && lane < p.splits) mbar_arrive_cluster(map_to_cta(parked, (uint32_t)lane));
+    if (warp == kIssuerBWarp && lane < p.splits && lane != (int)rank && !abort_flag) {
+      // my partial of band `lane` -> slot `rank` of CTA `lane`'s receive area
+      const uint32_t dst = map_to_cta(recv0 + rank * band_bytes, (uint32_t)lane);
+      const uint32_t bar = map_to_cta(received, (uint32_t)lane);
+      asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(dst), "r"(tiles + (uint32_t)lane * band_bytes), "r"(band_bytes), "r"(bar)
+                   : "memory");
+    }
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && warp == kIssuerBWarp && lane == 0) marks[7] = clock64();
 #endif
-    if (!mbar_wait_cluster(parked, 0, abort_ptr) && threadIdx.x == 0 && !*abort_ptr) {
+    if (!mbar_wait(received, 0, abort_ptr) && threadIdx.x == 0 && !*abort_ptr) {
       atomicCAS(p.status, 0, (p.kernel_index << 8) | 5);
       *abort_ptr = 1;
     }
+    cluster_arrive();        // what this CTA was to receive has landed (or it gave up): see the wait below
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && threadIdx.x == 0) marks[4] = clock64();
 #endif
     if (warp >= 2 && warp < 2 + kEpiWarps && !abort_flag) {
+      // The band is small (128 / splits rows): all eight warps walk it as float4 items in row-major
+      // order, so every load of a side operand and every store covers whole 128-byte lines, and an
+      // item costs a handful of instructions (the 32 x 32 block machinery of the unsplit epilogue took
+      // ~5000 cycles for a band that two of the eight warps then handled alone).
       const int e = warp - 2;
-      uint32_t rank;
-      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
       const int unit = blockIdx.x;
       int tile, ks_unused, batch, tm_i, tn_i;
       unit_coords(p, unit, tile, ks_unused, batch, tm_i, tn_i);
       const int64_t m0 = (int64_t)tm_i * kTileM, n0 = (int64_t)tn_i * p.bn;
-      const int row_lo = (int)rank * kTileM / p.splits, row_hi = ((int)rank + 1) * kTileM / p.splits;
-      const int col_blocks = p.bn / 32;
-      const int n_blocks = ((row_hi - row_lo + 31) / 32) * col_blocks;
-      for (int blk = e; blk < n_blocks; blk += kEpiWarps) {
-        const int rb = blk / col_blocks, cb = blk - rb * col_blocks;
-        const int row_base = row_lo + rb * 32;
-        const int nrows = row_hi - row_base < 32 ? row_hi - row_base : 32;
-        const int64_t n = n0 + cb * 32 + lane;
-        if (n0 + cb * 32 >= p.mm.N) continue;
-        float pre_col = 0.0f, pre_mat[32];
-        prefetch_sides(p, pre_col, pre_mat, batch, m0 + row_base, n, nrows);
-        float v[32];
-#pragma unroll
-        for (int r = 0; r < 32; ++r) v[r] = 0.0f;
-        const uint32_t local = tiles + (uint32_t)((row_base * p.bn + cb * 32) * 4);
+      const int row_lo = (int)rank * band_rows;
+      const int cols4 = p.bn >> 2;
+      const int items = band_rows * cols4;
+      const uint8_t* const ring = smem_raw + (tiles - raw);
+      const MatmulParams& mm = p.mm;
+      const DevOperand& out_op = mm.ops[mm.chain.out_slot];
+      for (int it = e * 32 + lane; it < items; it += kEpiWarps * 32) {
+        const int r = it / cols4, c4 = it - r * cols4;
+        const int row = row_lo + r;
+        const int64_t m = m0 + row, n = n0 + 4 * c4;
+        if (m >= mm.M || n >= mm.N) continue;
+        // the parked layout XORs the 16-byte slot within a 32-column group with the row
+        const int slot = (c4 & ~7) | ((c4 & 7) ^ (row & 7));
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
         for (int sp = 0; sp < p.splits; ++sp) {
-          const uint32_t remote = map_to_cta(local, (uint32_t)sp);
-#pragma unroll
-          for (int r = 0; r < 32; ++r)
-            if (r < nrows)
-              v[r] += ld_cluster_f32(remote + (uint32_t)(r * p.bn * 4) +
-                                     (uint32_t)((((lane >> 2) ^ ((row_base + r) & 7)) << 4) | ((lane & 3) << 2)));
+          const float4* src = reinterpret_cast<const float4*>(sp == (int)rank ? ring + (size_t)rank * band_bytes
+                                                                             : ring + p.recv_offset + (size_t)sp * band_bytes);
+          const float4 t = src[r * cols4 + slot];
+          v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
         }
-        epilogue_compute32(p, v, pre_col, pre_mat, batch, m0 + row_base, n, nrows);
-        if (p.store_mode == 1 && nrows == 32) {
-          // full 32-row block: staged and written with bulk tensor stores like the unsplit epilogue
-          uint8_t* sf = epi_buf + e * kEpiWarpBytes;
-          uint8_t* sh = sf + kEpiStage16Offset;
-          if (lane == 0) tma_store_wait_read();
-          __syncwarp();
-          stage_columns(sf, sh, v, lane, p.out16 != nullptr);
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0 && m0 + row_base < p.mm.M && !KB200_EXPERIMENT(1)) {
-            tma_store_3d(&tma_out, smem_u32(sf), (int)(n0 + cb * 32), (int)(m0 + row_base), batch);
-            if (p.out16 != nullptr) tma_store_3d(&tma_out16, smem_u32(sh), (int)(n0 + cb * 32), (int)(m0 + row_base), batch);
-            tma_store_commit();
+        for (int s = 0; s < mm.chain.n; ++s) {
+          const ChainStep st = mm.chain.steps[s];
+          float side[4] = {st.imm, st.imm, st.imm, st.imm};
+          if (st.slot >= 0) {
+            const DevOperand& o = mm.ops[st.slot];
+            const float* src = o.ptr + batch * o.stride[0] + m * o.stride[1] + n * o.stride[2];
+            if (o.stride[2] == 1 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+              const float4 t = __ldg(reinterpret_cast<const float4*>(src));
+              side[0] = t.x; side[1] = t.y; side[2] = t.z; side[3] = t.w;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) side[j] = __ldg(src + j * o.stride[2]);
+            }
           }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = chain_apply_scalar(st.op, v[j], side[j]);
+        }
+        if (KB200_EXPERIMENT(1)) continue;
+        float* dst = out_op.ptr + batch * out_op.stride[0] + m * out_op.stride[1] + n * out_op.stride[2];
+        if (out_op.stride[2] == 1 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
         } else {
-          epilogue_store32(p, v, batch, m0 + row_base, n, nrows);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j * out_op.stride[2]] = v[j];
+        }
+        if (p.out16 != nullptr) {
+          __nv_bfloat16* dst16 = p.out16 + batch * out_op.stride[0] + m * out_op.stride[1] + n * out_op.stride[2];
+          if (out_op.stride[2] == 1 && (reinterpret_cast<uintptr_t>(dst16) & 7) == 0) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst16) = packed;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst16[j * out_op.stride[2]] = __float2bfloat16_rn(v[j]);
+          }
         }
       }
-      if (lane == 0) tma_store_wait_read();
     }
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && threadIdx.x == 64) marks[5] = clock64();
 #endif
-    __syncthreads();         // this CTA no longer reads its neighbours' shared memory ...
-    if (warp == kIssuerBWarp && lane < p.splits) mbar_arrive_cluster(map_to_cta(released, (uint32_t)lane));
-    // ... and leaves (frees its own) only when no neighbour reads it any more
-    if (threadIdx.x == 0 && !mbar_wait_cluster(released, 0, abort_ptr) && !*abort_ptr) {
-      atomicCAS(p.status, 0, (p.kernel_index << 8) | 6);
-      *abort_ptr = 1;
-    }
+    // every CTA of the cluster has received everything: so every push out of THIS shared memory has landed
+    cluster_wait();
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && threadIdx.x == 0) marks[6] = clock64();
 #endif
@@ -1025,26 +1060,41 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
   // 768-wide layers): every SM then streams a share of the operands.
   int splits = d.cfg[4];
   if (splits <= 0) {
-    // Split K over a cluster only when the tiles leave more than half of the SMs idle and K is long
-    // (64 slabs and more, measured): parking, hand-shake and reduction cost about as much as 20 slabs.
+    // Split K over a cluster when the tiles leave SMs idle: the widest split (2, 4, 8) whose CTAs still
+    // fit the GPU in one wave with room to place whole clusters (36 clusters of 4 on 148 SMs ran as
+    // two waves: 17 us against 10), that leaves every CTA at least three 128-byte slabs of K, and that
+    // takes at least 18 slabs off a CTA's serial K loop -- the exchange (park, push the bands, add,
+    // store) costs about 3 us, a slab ~0.2 us (measured, TF32: 768 of K over 12 tiles 10.1 -> 7.3 us
+    // in eighths, but over 48 tiles 12.5 -> 15.1 us in halves; 3072 of K over 12 tiles 28 -> 9.7 us).
+    // In exact-FP32 mode a slab costs three times the MMAs and the operand split: 8 slabs suffice.
     splits = 1;
-    if (p.num_tiles * 2 <= plan.sm_count && p.num_kb * kps >= 64) {
-      splits = 2;
-      if (p.num_tiles * 4 <= plan.sm_count) splits = 4;
-    }
-    // Exact-FP32 mode: a pipeline step costs three times the MMAs plus the split, so sharing K pays
-    // from 16 slabs on (measured on the 128-token projections: 768 of K over 36 or 48 tiles 27 -> 20 us
-    // in halves, over 12 tiles 28 -> 19 us in quarters; 3072 of K over 12 tiles 34 -> 29 us in eighths)
-    if (split3 && p.num_tiles * 2 <= plan.sm_count && p.num_kb >= 16) {
-      splits = 2;
-      if (p.num_tiles * 8 <= plan.sm_count) splits = p.num_kb >= 64 ? 8 : 4;
-    }
+    const int64_t slabs = (k.K + slab_k - 1) / slab_k;
+    for (int cand : {2, 4, 8})
+      if ((int64_t)p.num_tiles * cand * 10 <= (int64_t)plan.sm_count * 7 && slabs / cand >= 3 &&
+          slabs - slabs / cand >= (split3 ? 8 : 18))
+        splits = cand;
   }
   if (splits > p.num_kb) splits = p.num_kb;
   // the reduction runs over a thread-block cluster (<= 8 CTAs) and parks the partial tile in the
   // pipeline's shared memory
   if (splits > 8) splits = 8;
-  while (splits > 1 && (size_t)stages * stage_bytes < (size_t)kTileM * bn * sizeof(float)) splits = 1;
+  // split K needs the partial tile to fit the ring, and a receive area of the same size behind the
+  // epilogue buffers (tiles up to 128 columns: 64 KB); the ring gives up stages for it, down to two
+  if (splits > 1 && bn > 128) splits = 1;
+  p.recv_offset = 0;
+  if (splits > 1) {
+    const size_t tile_bytes = (size_t)kTileM * bn * sizeof(float);
+    int fit = stages;
+    while (fit > 2 && (size_t)fit * stage_bytes + kEpiBytes + tile_bytes + 1024 > (size_t)kMaxDynamicSmem) --fit;
+    if ((size_t)fit * stage_bytes + kEpiBytes + tile_bytes + 1024 > (size_t)kMaxDynamicSmem || (size_t)fit * stage_bytes < tile_bytes) {
+      splits = 1;
+    } else {
+      stages = fit;
+      if (issuers == 2) stages &= ~1;
+      p.stages = stages;
+      p.recv_offset = stages * stage_bytes + kEpiBytes;
+    }
+  }
   p.splits = splits;
   p.num_units = p.num_tiles * splits;
   p.magic_stages = ((uint64_t(1) << 40) + stages - 1) / stages;
@@ -1070,7 +1120,7 @@ int tc_bind(Plan& plan, PlanKernel& k, int kernel_index) {
     if (per_column && p.pre_col_step < 0) p.pre_col_step = st_i;
     else if (!per_column && p.pre_mat_step < 0) p.pre_mat_step = st_i;
   }
-  st->smem_bytes = (size_t)stages * stage_bytes + kEpiBytes + 1024;
+  st->smem_bytes = (size_t)stages * stage_bytes + kEpiBytes + 1024 + (splits > 1 ? (size_t)kTileM * bn * sizeof(float) : 0);
   // persistent CTAs, one per SM: each walks the tile list with a stride of the grid size
   st->grid = p.splits > 1 ? dim3((unsigned)p.num_units, 1, 1)     // one unit per CTA, clusters of `splits`
                           : dim3((unsigned)(p.num_units < plan.sm_count ? p.num_units : plan.sm_count), 1, 1);

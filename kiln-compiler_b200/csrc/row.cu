@@ -126,15 +126,28 @@ enum { ROW_LAYERNORM = 0, ROW_SOFTMAX = 1 };
 // One warp per row; lane l owns float4 number l + 32 * i, i < VPL.
 template <int MODE, int VPL>
 __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ RowFastParams p) {
-  pdl_wait();                 // the producer of this kernel's inputs has completed
-  pdl_launch_dependents();    // the next kernel may begin its start-up
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int64_t row = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5);
+  const int nvec = p.inner >> 2;
+  // The affine parameters of a LayerNorm are constants of the plan, not outputs of the previous
+  // kernel: they are fetched before this kernel waits for its producer, so their latency is off the
+  // path (fetched after the two reductions they added a dependent memory round trip to every row).
+  float4 g[MODE == ROW_LAYERNORM ? VPL : 1], b[MODE == ROW_LAYERNORM ? VPL : 1];
+  if (MODE == ROW_LAYERNORM) {
+    const float4* g4 = reinterpret_cast<const float4*>(p.gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(p.beta);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int j = lane + 32 * i;
+      if (j < nvec) { g[i] = __ldg(g4 + j); b[i] = __ldg(b4 + j); }
+    }
+  }
+  pdl_wait();                 // the producer of this kernel's inputs has completed
+  pdl_launch_dependents();    // the next kernel may begin its start-up
   if (row >= p.n_rows) return;
   const float4* x4 = reinterpret_cast<const float4*>(p.x + row * p.x_row_stride);
   float4* o4 = reinterpret_cast<float4*>(p.out + row * p.out_row_stride);
-  const int nvec = p.inner >> 2;
   float4 v[VPL];
   bool live[VPL];
 #pragma unroll
@@ -158,18 +171,15 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
       }
     }
     const float rstd = 1.0f / sqrtf(warp_sum(q) * p.inv_n + p.eps);
-    const float4* g4 = reinterpret_cast<const float4*>(p.gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(p.beta);
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       if (live[i]) {
         const int j = lane + 32 * i;
-        const float4 g = __ldg(g4 + j), b = __ldg(b4 + j);
         float4 y;
-        y.x = v[i].x * rstd * g.x + b.x;
-        y.y = v[i].y * rstd * g.y + b.y;
-        y.z = v[i].z * rstd * g.z + b.z;
-        y.w = v[i].w * rstd * g.w + b.w;
+        y.x = v[i].x * rstd * g[i].x + b[i].x;
+        y.y = v[i].y * rstd * g[i].y + b[i].y;
+        y.z = v[i].z * rstd * g[i].z + b[i].z;
+        y.w = v[i].w * rstd * g[i].w + b[i].w;
         o4[j] = y;
         if (p.out16 != nullptr) {
           __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
@@ -190,16 +200,18 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       if (live[i]) {
-        v[i].x = expf(v[i].x - m); v[i].y = expf(v[i].y - m); v[i].z = expf(v[i].z - m); v[i].w = expf(v[i].w - m);
+        // exp through ex2.approx (relative error 2^-22, what the reference's tl.exp lowers to as well)
+        v[i].x = __expf(v[i].x - m); v[i].y = __expf(v[i].y - m); v[i].z = __expf(v[i].z - m); v[i].w = __expf(v[i].w - m);
         s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
       }
     }
     s = warp_sum(s);
+    const float inv = 1.0f / s;     // one IEEE division per row; the elements are scaled by it (within an ulp of dividing)
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       if (live[i]) {
         float4 y;
-        y.x = v[i].x / s; y.y = v[i].y / s; y.z = v[i].z / s; y.w = v[i].w / s;
+        y.x = v[i].x * inv; y.y = v[i].y * inv; y.z = v[i].z * inv; y.w = v[i].w * inv;
         o4[lane + 32 * i] = y;
       }
     }

@@ -35,6 +35,14 @@ __device__ __forceinline__ float f_erf(float x) {
   return x < 0.0f ? -y : y;
 }
 
+// One chain step on a single value (the split-K reduction works on float4 items): the BF16-mode
+// approximations here, everything else as the CUDA-core kernels evaluate it.
+__device__ __forceinline__ float chain_apply_scalar(int op, float v, float s) {
+  if (op == CH_TANH_APPROX) return f_tanh_approx(v);
+  if (op == CH_GELU_TANH_APPROX) return 0.5f * v * (1.0f + f_tanh_approx(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  return apply_chain(op, v, s);
+}
+
 // One chain step on 32 register-resident values.  The switch is outside the element loop and
 // every index is a compile-time constant, so v[] and side[] never leave the register file and the
 // 32 independent elements give the few epilogue warps the instruction-level parallelism they need.
@@ -56,7 +64,7 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
     case CH_TANH: KB200_EACH(f_tanh(x)) break;
     case CH_SIGMOID: KB200_EACH(__fdividef(1.0f, 1.0f + __expf(-x))) break;
     case CH_ERF: KB200_EACH(f_erf(x)) break;
-    case CH_GELU_TANH: KB200_EACH(0.5f * x * (1.0f + f_tanh(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
+    case CH_GELU_TANH: KB200_EACH(d_gelu_tanh(x)) break;
     case CH_GELU_ERF: KB200_EACH(0.5f * x * (1.0f + f_erf(x * 0.7071067811865476f))) break;
     case CH_TANH_APPROX: KB200_EACH(f_tanh_approx(x)) break;
     case CH_GELU_TANH_APPROX: KB200_EACH(0.5f * x * (1.0f + f_tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;

@@ -300,13 +300,17 @@ def test_hot_path_kernels_are_the_specialised_ones(monkeypatch):
 
 
 def test_autotune_candidates_fit_shared_memory():
-    from kiln_b200.autotune import EPILOGUE_BYTES, SHARED_MEMORY_BYTES, candidates, stage_bytes
+    from kiln_b200.autotune import SHARED_MEMORY_BYTES, SINGLE_CTA_EPILOGUE_BYTES, candidates, stage_bytes
 
     for m, n, k in [(128, 3072, 768), (1, 768, 768), (7, 13, 5), (2048, 3072, 768)]:
         cands = candidates(m, n, k)
         assert cands and cands[-1]["impl"] == "simt"
+        assert any(c["BM"] == 256 for c in cands) == (m > 128 and n >= 128)      # SM-pair tiles only above 128 rows
         for c in cands[:-1]:
-            assert stage_bytes(c) * c["stages"] + EPILOGUE_BYTES + 1024 <= SHARED_MEMORY_BYTES
+            if c["BM"] == 256:        # the pair kernel fits its ring to what is left beside its staging slots
+                assert c["BN"] in (128, 256) and 2 * stage_bytes(c) + 8 * 2 * 6144 + 1024 <= SHARED_MEMORY_BYTES
+            else:
+                assert stage_bytes(c) * c["stages"] + SINGLE_CTA_EPILOGUE_BYTES + 1024 <= SHARED_MEMORY_BYTES
             assert c["BN"] <= max(64, 2 * n)
 
 
