@@ -747,7 +747,12 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
   if ((size_t)stages * stage_bytes + epi_bytes + 1024 > (size_t)kPairSmemCeiling) { delete st; return KB200_OK; }
   p.stages = stages;
   st->smem_bytes = (size_t)stages * stage_bytes + epi_bytes + 1024;
-  const int n_pairs = p.num_tiles < pairs ? p.num_tiles : pairs;
+  // Persistent pairs: as many as there are tiles, up to this plan's share of the GPU.  With several
+  // plans in flight a kernel that spread one tile to every pair would leave each pair's tensor cores
+  // idle through its epilogue (bound by the store path, longer than the main loop at K = 768); on its
+  // share of the pairs every pair walks several tiles and drains one while it multiplies the next.
+  const int rounds = (p.num_tiles + share - 1) / share;
+  const int n_pairs = (p.num_tiles + rounds - 1) / rounds;
   st->grid = dim3((unsigned)(2 * n_pairs), 1, 1);
 
   bool ok = encode_map(&st->map_a, ops.bf16, ops.a_base, k.K, k.M, k.batch, ops.a_row, ops.a_batch, slab_k, 128, false);
