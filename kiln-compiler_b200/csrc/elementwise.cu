@@ -127,83 +127,6 @@ __global__ void __launch_bounds__(256) ew_chain_vec4_kernel(const __grid_constan
   }
 }
 
-// Rank 2 (rows x columns), which is what bias + GELU, scale + residual and the like collapse to: a
-// thread owns one float4 COLUMN and walks down rows, U rows per step.  No division per vector (the
-// generic kernel above spends one, ~20 instructions, and measured issue-bound on bias + GELU: 64 % of
-// issue slots, 57 % of the copy bandwidth), an operand that is constant along the rows (a bias: row
-// stride 0) is read ONCE per thread, and the U loads of a step are in flight together.
-template <int U>
-__global__ void __launch_bounds__(256) ew_rows_vec4_kernel(const __grid_constant__ EwChainParams p) {
-  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t rows = p.shape[0];
-  const bool in_range = c < p.shape[1];
-  // per-column operands that are plan constants could be read before the wait; whether an operand is
-  // one is not known here, so everything is read after it
-  pdl_wait();                 // the producer of this kernel's inputs has completed
-  pdl_launch_dependents();    // the next kernel may begin its start-up
-  if (!in_range) return;
-  float4 fixed[kMaxChain];
-#pragma unroll
-  for (int s = 0; s < kMaxChain; ++s) {
-    fixed[s] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (s < p.chain.n) {
-      const ChainStep st = p.chain.steps[s];
-      if (st.slot < 0) {
-        fixed[s] = make_float4(st.imm, st.imm, st.imm, st.imm);
-      } else if (p.stride[st.slot][0] == 0) {
-        const float* ptr = p.ptr[st.slot] + c * (uint32_t)p.stride[st.slot][1];
-        if (p.stride[st.slot][1] == 0) {
-          const float v = __ldg(ptr);
-          fixed[s] = make_float4(v, v, v, v);
-        } else {
-          fixed[s] = __ldg(reinterpret_cast<const float4*>(ptr));
-        }
-      }
-    }
-  }
-  const int first = p.chain.first_slot, out = p.chain.out_slot;
-  for (uint32_t r0 = blockIdx.y * U; r0 < rows; r0 += gridDim.y * U) {
-    float v[4 * U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint32_t r = r0 + u;
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < rows) {
-        const float* ptr = p.ptr[first] + r * (uint32_t)p.stride[first][0] + c * (uint32_t)p.stride[first][1];
-        if (p.stride[first][1] == 0) { const float t = __ldg(ptr); x = make_float4(t, t, t, t); }
-        else x = *reinterpret_cast<const float4*>(ptr);
-      }
-      v[4 * u] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
-    }
-#pragma unroll
-    for (int s = 0; s < kMaxChain; ++s) {
-      if (s >= p.chain.n) break;
-      const ChainStep st = p.chain.steps[s];
-      float side[4 * U];
-      const bool per_row = st.slot >= 0 && p.stride[st.slot][0] != 0;
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float4 x = fixed[s];
-        const uint32_t r = r0 + u;
-        if (per_row && r < rows) {
-          const float* ptr = p.ptr[st.slot] + r * (uint32_t)p.stride[st.slot][0] + c * (uint32_t)p.stride[st.slot][1];
-          if (p.stride[st.slot][1] == 0) { const float t = __ldg(ptr); x = make_float4(t, t, t, t); }
-          else x = *reinterpret_cast<const float4*>(ptr);
-        }
-        side[4 * u] = x.x; side[4 * u + 1] = x.y; side[4 * u + 2] = x.z; side[4 * u + 3] = x.w;
-      }
-      chain_step<4 * U>(st.op, v, side);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint32_t r = r0 + u;
-      if (r < rows)
-        *reinterpret_cast<float4*>(p.ptr[out] + r * (uint32_t)p.stride[out][0] + c * (uint32_t)p.stride[out][1]) =
-            make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-    }
-  }
-}
-
 // ---- tiled transpose + chain ----
 struct EwTransposeParams {
   int rank;                      // 2..kVecRank
@@ -362,19 +285,6 @@ int launch_elementwise(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     const int64_t cap = (int64_t)plan.sm_count * 64;
     const int64_t steps = (blocks + cap - 1) / cap;
     const unsigned grid = (unsigned)((blocks + steps - 1) / (steps > 0 ? steps : 1));
-    if (rank == 2 && p.shape[0] >= 16 && p.shape[1] >= 64) {
-      // column-resident variant: blocks along the columns, and enough row groups that every SM holds
-      // several blocks (each thread then walks rows / groups rows, four at a time)
-      constexpr int UR = 4;
-      const unsigned col_blocks = (p.shape[1] + 255) / 256;
-      int64_t groups = ((int64_t)plan.sm_count * 8 + col_blocks - 1) / col_blocks;
-      const int64_t max_groups = ((int64_t)p.shape[0] + UR - 1) / UR;
-      if (groups > max_groups) groups = max_groups;
-      if (groups > 65535) groups = 65535;
-      launch_kernel(plan.pdl, ew_rows_vec4_kernel<UR>, dim3(col_blocks, (unsigned)groups), dim3(256), 0, s, p);
-      KB200_CUDA(cudaGetLastError());
-      return KB200_OK;
-    }
     switch (rank) {
       case 1: launch_kernel(plan.pdl, ew_chain_vec4_kernel<1, U>, dim3(grid), dim3(256), 0, s, p); break;
       case 2: launch_kernel(plan.pdl, ew_chain_vec4_kernel<2, U>, dim3(grid), dim3(256), 0, s, p); break;
