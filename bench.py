@@ -370,10 +370,28 @@ def kernel_flops(kernel):
     return flops, byts
 
 
-# DRAM bytes (read + write) per launch of the 1024-token block's matmuls, from the `ncu` captures
-# summarised under profiles/ (one kernel, a few launches each; same shapes as the bench).
-NCU_DRAM_BYTES = json.loads((ROOT / "profiles" / "dram_bytes_per_launch.json").read_text()) \
-    if (ROOT / "profiles" / "dram_bytes_per_launch.json").exists() else {}
+# DRAM bytes (read + write) per launch of the 1024-token block's kernels, copied from the `ncu --set full`
+# captures summarised in profiles/gpt2_block_t1024_bf16_launches_and_top_kernels.md (BF16 rows) and
+# profiles/linear_2048x3072x768_fp32_exact_mm_tc.md (FP32 rows); same shapes as the bench, so no scaling.
+NCU_DRAM_BYTES = {
+    "bf16:k0_row": 3162880,
+    "bf16:k10_matmul": 14245632,
+    "bf16:k1_matmul": 5206528,
+    "bf16:k2_ew0": 4774912,
+    "bf16:k7_matmul": 5987584,
+    "bf16:k8_row": 3162880,
+    "bf16:k9_matmul": 6403072,
+    "fp32:k0_row": 3160000,
+    "fp32:k10_matmul": 25280000,
+    "fp32:k1_matmul": 10330000,
+    "fp32:k3_matmul": 10810000,
+    "fp32:k4_row": 51880000,
+    "fp32:k5_matmul": 53570000,
+    "fp32:k6_ew0": 3180000,
+    "fp32:k7_matmul": 8750000,
+    "fp32:k8_row": 3160000,
+    "fp32:k9_matmul": 12700000,
+}
 
 
 def roofline_of(built, precision, iters=20):
