@@ -497,6 +497,35 @@ def block_numbers(case, precision):
             "tokens_per_s": round(t / call_ms * 1e3), "built_from": graphed.source}
 
 
+def batched_graph_numbers(precision, batch=8):
+    """Eight 1024-token sequences as ONE compiled graph ([batch, tokens, d] through kiln.compile; the
+    projections are 8192-row matmuls) beside the same eight through StreamedBatch.  Needs the
+    reference's frontend (baseline/_ref)."""
+    from kiln_b200 import workloads as W
+
+    kiln = kiln_frontend()
+    if kiln is None:
+        return {"unavailable": "the reference's frontend is not installed under baseline/_ref"}
+    x = torch.stack([torch.from_numpy(W.block_input(SEED, TOKENS, index=i)) for i in range(batch)])
+    old = os.environ.get("KILN_GPU_PRECISION")
+    if precision == "bf16":
+        os.environ["KILN_GPU_PRECISION"] = "bf16"
+    try:
+        compiled = kiln.compile(W.batched_block_module(SEED, TOKENS), (x,), device="cuda", allow_tf32=precision != "fp32",
+                                cuda_graphs=False)
+    finally:
+        if precision == "bf16":
+            os.environ.pop("KILN_GPU_PRECISION", None) if old is None else os.environ.__setitem__("KILN_GPU_PRECISION", old)
+    exe = compiled._exe
+    exe.static_inputs[0].copy_(x)
+    best, _ = graph_times(exe.run_static, repeats=3, replays=20)
+    out = {"batch": batch, "tokens": TOKENS, "precision": precision, "kernels": len(compiled.graph.kernels),
+           "arena_mib": round(compiled.report.arena_bytes / 2**20, 1), "ms_per_call": round(best * 1e3, 3),
+           "tokens_per_s": round(batch * TOKENS / best), "impls": sorted(set(exe.impls))}
+    exe.close()
+    return out
+
+
 def extras(precision):
     """Every other BASELINE configuration at its stated precision: fused-op GB/s (config 3), Linear
     TFLOP/s in TF32 and BF16 (config 2), the 2048-token MLP in TF32 (config 1), the 128-token block in
@@ -559,6 +588,7 @@ def extras(precision):
                             "frac_of_measured_peak": round(flops / best / 1e12 / tf32_peak, 3), "impl": built.exe.impls,
                             "built_from": built.source}
     built.close()
+    out["batched_graph"] = batched_graph_numbers(precision)
     out["block_t128_fp32"] = block_numbers("gpt2_block_t128", "fp32")
     if precision != "fp32":
         out["block_t128"] = block_numbers("gpt2_block_t128", precision)

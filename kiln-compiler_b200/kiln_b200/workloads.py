@@ -152,6 +152,43 @@ def block_module(seed, t, d=768, heads=12):
     return model
 
 
+def batched_block_module(seed, t, d=768, heads=12):
+    """The block of ``block_module`` taking ``[batch, tokens, d]``: every sequence of the batch in ONE
+    compiled graph.  The frontend flattens the leading dims of every Linear (kiln/frontend/
+    fx_import.py:150-153), so the projections become ``batch * tokens``-row matmuls; attention stays
+    per sequence and head through ``[batch, heads, tokens, head_dim]`` views."""
+    import math
+
+    import torch
+    from torch import nn
+    from torch.nn import functional as F
+
+    class BatchedPreLNBlock(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.heads = heads
+            self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            self.c_attn, self.c_proj = nn.Linear(d, 3 * d), nn.Linear(d, d)
+            self.fc, self.proj = nn.Linear(d, 4 * d), nn.Linear(4 * d, d)
+            self.register_buffer("mask", torch.zeros(t, t))
+
+        def attention(self, h):
+            batch, tokens, width = h.shape
+            hd = width // self.heads
+            q, k, v = (z.view(batch, tokens, self.heads, hd).transpose(1, 2) for z in self.c_attn(h).split(width, dim=2))
+            scores = (q @ k.transpose(-2, -1)) * (1.0 / math.sqrt(hd)) + self.mask[:tokens, :tokens]
+            merged = (F.softmax(scores, dim=-1) @ v).transpose(1, 2).contiguous().view(batch, tokens, width)
+            return self.c_proj(merged)
+
+        def forward(self, x):
+            x = x + self.attention(self.ln1(x))
+            return x + self.proj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+    model = BatchedPreLNBlock().eval()
+    model.load_state_dict({k: torch.from_numpy(v.copy()) for k, v in block_params(seed, t, d, heads).items()})
+    return model
+
+
 # ---------------------------------------------------------------------------------------------
 # The benchmark configurations by name: tensors, modules, stored launch plans
 # ---------------------------------------------------------------------------------------------

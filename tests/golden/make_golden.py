@@ -57,6 +57,7 @@ class FnModule(torch.nn.Module):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("KILN_REFERENCE", str(ROOT.parent / "reference")))
+    ap.add_argument("--only", default=None, help="regenerate just this case (its slug), keeping every other fixture as it is")
     args = ap.parse_args()
     ref = Path(args.reference)
     sys.path.insert(0, str(ref))
@@ -109,8 +110,13 @@ def main():
         expected = list(expected) if isinstance(expected, (tuple, list)) else [expected]
         return import_exported(ep), expected, module
 
+    def wanted(case):
+        return args.only is None or args.only == case
+
     def small_case(name, fn, xs, **flags):
         case = slug(name)
+        if not wanted(case):
+            return
         torch.manual_seed(0)
         graph, expected, module = export(fn, xs)
         options = Options(device="cuda", **flags)
@@ -165,6 +171,9 @@ def main():
         "erf gelu mlp": (torch.nn.Sequential(torch.nn.Linear(40, 72), torch.nn.GELU(), torch.nn.Linear(72, 24)),
                          (torch.randn(130, 40),)),
         "wide bmm": (lambda a, b: torch.bmm(a, b) * 0.5, (torch.randn(3, 70, 130), torch.randn(3, 130, 96))),
+        # a whole batch of sequences as ONE graph: Linear flattens the leading dims, attention runs on
+        # [batch, heads, tokens, head_dim] views (the "batched models" row of the scope)
+        "batched block": (W.batched_block_module(7, 16, d=64, heads=4), (torch.randn(3, 16, 64),)),
     }
     for name, (fn, xs) in cases.items():
         small_case(name, fn, xs)
@@ -176,6 +185,8 @@ def main():
     for seed in range(6):
         for fusion in (False, True):
             case = f"random_s{seed}_{'fused' if fusion else 'unfused'}"
+            if not wanted(case):
+                continue
             rng = random.Random(seed)
             g = random_graph(rng, n_ops=rng.randint(6, 22))
             x = np.random.default_rng(seed).standard_normal(g.args[0].shape).astype(np.float32) * 0.5
@@ -189,6 +200,8 @@ def main():
 
     # ---- the benchmark configurations: plans + subsampled float64 results ----
     def big_case(case, module, x, step):
+        if not wanted(case):
+            return
         graph, _, _ = export(module, (torch.from_numpy(x),))
         pm = optimise(graph, Options(device="cuda"))
         record(case, graph, pm)
@@ -235,6 +248,8 @@ def main():
     _, x = W.softmax_data()
     big_case("softmax_12x512x512", FnModule(lambda t: F.softmax(t, -1)).eval(), x, 192)
 
+    if args.only is not None:
+        summary = {**json.loads((HERE / "reference_plans.json").read_text()), **summary}
     (HERE / "reference_plans.json").write_text(json.dumps(summary, indent=1, sort_keys=True) + "\n")
     print(f"wrote {len(summary)} cases")
 

@@ -171,6 +171,28 @@ def test_attention_that_also_returns_its_weights_is_not_fused(kiln):
     assert "attention_fused" in fused._exe.impls
 
 
+def test_a_batch_of_sequences_as_one_graph(kiln):
+    """[batch, tokens, d] through kiln.compile: the Linears become batch * tokens-row matmuls (256-row
+    tiles on SM pairs here), attention runs on [batch, heads, tokens, head_dim] views; results match
+    eager per sequence and match the single-sequence module on every sequence of the batch."""
+    from kiln_b200 import workloads as W
+
+    batch, tokens = 4, 128
+    model = W.batched_block_module(6, tokens)
+    x = torch.stack([torch.from_numpy(W.block_input(6, tokens, index=i)) for i in range(batch)])
+    compiled = compile_and_compare(kiln, model, x, rtol=1e-3, atol=1e-3)
+    assert "mm_tcgen05" in compiled._exe.impls
+    fast = kiln.compile(model, (x,), device="cuda", allow_tf32=True)
+    single = kiln.compile(W.block_module(6, tokens), (x[0],), device="cuda", allow_tf32=True)
+    got = fast(x).cpu().double()
+    with torch.no_grad():
+        want = model(x).double()
+    assert float((got - want).abs().max() / want.abs().max()) <= 2e-3
+    for i in range(batch):
+        one = single(x[i]).cpu().double()
+        assert float((got[i] - one).abs().max() / want.abs().max()) <= 2e-3
+
+
 def test_wrong_shape_is_a_value_error(kiln):
     compiled = kiln.compile(torch.nn.Linear(8, 4).eval(), (torch.randn(3, 8),), device="cuda")
     with pytest.raises(ValueError):
