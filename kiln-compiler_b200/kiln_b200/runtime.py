@@ -387,6 +387,35 @@ class StreamedBatch:
         self.requests = len(sources)
         return self
 
+    def capture_launch(self, index, requests):
+        """Capture ``requests`` launches of plan launch ``index`` alone, spread over the modules and
+        their streams exactly like the launches of a whole step (profiling: what one kernel of the
+        step costs when the modules in flight share the GPU, rather than alone on it)."""
+        def enqueue():
+            cur = torch.cuda.current_stream(self.device)
+            for st in self.streams:
+                st.wait_stream(cur)
+            n = len(self.executables)
+            for i in range(requests):
+                with torch.cuda.stream(self.streams[i % n]):
+                    self.executables[i % n].launch_kernel(index)
+            for st in self.streams:
+                cur.wait_stream(st)
+
+        with torch.cuda.device(self.device):
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                enqueue()
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                enqueue()
+        self.graph = graph
+        self.requests = requests
+        return self
+
     def run(self):
         """Replay the captured step on the current stream (one launch)."""
         if self.graph is None:
