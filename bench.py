@@ -607,7 +607,8 @@ def extras(precision):
     built.close()
     out["batched_graph"] = batched_graph_numbers(precision)
     out["block_t128_fp32"] = block_numbers("gpt2_block_t128", "fp32")
-    if precision != "fp32":
+    out["block_t128_tf32"] = block_numbers("gpt2_block_t128", "tf32")      # the precision the reference's Triton arm is timed in
+    if precision not in ("fp32", "tf32"):
         out["block_t128"] = block_numbers("gpt2_block_t128", precision)
     out["block_t2048"] = block_numbers("gpt2_block_t2048", precision)
     return out
