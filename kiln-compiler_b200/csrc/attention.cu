@@ -83,6 +83,14 @@ __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
+// 2^x for x <= 0 through the bare special-function instruction (exp2f adds a range fix-up for
+// denormal results, which a probability does not need; the softmax is bound by this pipe).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Scores of one 32-column block -> probabilities, in place; returns their sum.  `first_col` is the
 // block's first key relative to the query tile's first row (only used on the diagonal tile).
 template <bool DIAGONAL>
@@ -90,7 +98,7 @@ __device__ __forceinline__ float probabilities32(float (&v)[32], float scale_log
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    float pr = exp2f(fmaf(v[i], scale_log2, -m_use));
+    float pr = ex2(fmaf(v[i], scale_log2, -m_use));
     if (DIAGONAL && first_col + i > row) pr = 0.0f;
     v[i] = pr;
     sum += pr;
@@ -315,7 +323,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       // a row with every key of this group masked so far keeps m = -inf: use 0 as the reference point
       const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;
-      const float alpha = exp2f(m_run - m_use);     // 0 while m_run = -inf
+      const float alpha = ex2(m_run - m_use);       // 0 while m_run = -inf
       float sum;
       if (diagonal) {
         sum = probabilities32<true>(va, p.scale_log2, m_use, c0, row);
@@ -386,21 +394,39 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = o[32 + i] * a + theirs[i] * b;
       }
-      float* dst = p.out + (int64_t)(q0 + row) * p.out_row_stride + h * kHeadDim + group * 32;
+      // A lane holds 32 dims of ONE row: stored from here, a warp instruction would touch 32 lines of 16
+      // bytes each.  The rows go through shared memory instead (the K ring is idle: 128 bytes per row,
+      // the 16-byte slot XORed with the row against bank conflicts) and every store instruction of a
+      // warp then writes four whole 128-byte rows (eight 64-byte rows of the bf16 copy).  Each warp
+      // stores the 32 rows it staged itself, so a warp-level barrier is all it takes.
+      uint8_t* stage = smem_raw + (k_smem - raw) + (size_t)(group * kRows + quad * 32) * 128;
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(r[i], r[i + 1], r[i + 2], r[i + 3]);
-      if (p.out16 != nullptr) {
-        __nv_bfloat16* dst16 = p.out16 + (int64_t)(q0 + row) * p.out16_row_stride + h * kHeadDim + group * 32;
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(stage + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+      __syncwarp();
+      const int64_t first_row = q0 + quad * 32;
+      float* dst = p.out + first_row * p.out_row_stride + h * kHeadDim + group * 32;
+      __nv_bfloat16* dst16 = p.out16 != nullptr ? p.out16 + first_row * p.out16_row_stride + h * kHeadDim + group * 32 : nullptr;
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          __nv_bfloat162 w0 = __floats2bfloat162_rn(r[i], r[i + 1]), w1 = __floats2bfloat162_rn(r[i + 2], r[i + 3]);
-          __nv_bfloat162 w2 = __floats2bfloat162_rn(r[i + 4], r[i + 5]), w3 = __floats2bfloat162_rn(r[i + 6], r[i + 7]);
+      for (int it = 0; it < 8; ++it) {
+        const int rr = it * 4 + (lane >> 3), q = lane & 7;
+        const float4 t = *reinterpret_cast<const float4*>(stage + rr * 128 + ((q ^ (rr & 7)) << 4));
+        *reinterpret_cast<float4*>(dst + (int64_t)rr * p.out_row_stride + 4 * q) = t;
+      }
+      if (dst16 != nullptr) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int rr = it * 8 + (lane >> 2), c = lane & 3;       // 8 dims = 16 bytes of bf16 per lane
+          const float4 lo = *reinterpret_cast<const float4*>(stage + rr * 128 + (((2 * c) ^ (rr & 7)) << 4));
+          const float4 hi = *reinterpret_cast<const float4*>(stage + rr * 128 + (((2 * c + 1) ^ (rr & 7)) << 4));
+          __nv_bfloat162 w0 = __floats2bfloat162_rn(lo.x, lo.y), w1 = __floats2bfloat162_rn(lo.z, lo.w);
+          __nv_bfloat162 w2 = __floats2bfloat162_rn(hi.x, hi.y), w3 = __floats2bfloat162_rn(hi.z, hi.w);
           uint4 packed;
           packed.x = *reinterpret_cast<uint32_t*>(&w0);
           packed.y = *reinterpret_cast<uint32_t*>(&w1);
           packed.z = *reinterpret_cast<uint32_t*>(&w2);
           packed.w = *reinterpret_cast<uint32_t*>(&w3);
-          *reinterpret_cast<uint4*>(dst16 + i) = packed;
+          *reinterpret_cast<uint4*>(dst16 + (int64_t)rr * p.out16_row_stride + 8 * c) = packed;
         }
       }
     }
