@@ -82,6 +82,10 @@ struct PlanKernel {
   // row specialisations
   int x_slot = -1, g_slot = -1, b_slot = -1, out_slot = -1;
   float ln_inv_n = 0.f, ln_eps = 0.f;
+  // ... whose input may be a short elementwise chain on the loaded row (x * scale + mask before a
+  // softmax, a + b before a LayerNorm), and that value may itself be an output of the kernel
+  Chain row_pre;          // steps applied to x_slot's row before the reductions (n == 0: none)
+  int pre_out_slot = -1;  // operand that receives the chain's value, or -1
   // matmul
   int64_t batch = 1, M = 0, N = 0, K = 0;
   void* tc = nullptr;   // tensor-core state (tensor maps, packed operands), owned by matmul_tc.cu
@@ -116,6 +120,7 @@ struct Plan {
 bool extract_chain(const kb200_kernel_desc& d, Chain* out);
 bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k);
 bool match_softmax(const kb200_kernel_desc& d, PlanKernel* k);
+constexpr int kMaxRowPre = 4;   // chain steps in front of a register-resident row kernel
 
 // ---- per-class entry points ----
 int choose_elementwise(Plan& plan, PlanKernel& k);

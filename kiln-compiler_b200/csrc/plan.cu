@@ -161,16 +161,60 @@ struct Matcher {
 };
 }  // namespace
 
+// The value `z` a row kernel reduces over: a LOAD, or a short chain of elementwise ops on one (every
+// step a unary op, or a binary op whose other argument is a LOAD or an immediate), as in
+// softmax(x * scale + mask) or LayerNorm(a + b).  Fills first slot and steps; *entries counts the
+// tape entries the chain consists of (the first LOAD, the ops, their leaves).
+static bool row_pre_chain(const kb200_kernel_desc& d, int z, Chain* out, int* entries) {
+  ChainStep rev[kMaxRowPre];
+  int n = 0, count = 0, cur = z;
+  auto leaf = [&](int i) { return d.tape[i].opcode == KB200_OP_LOAD || d.tape[i].opcode == KB200_OP_IMM; };
+  while (d.tape[cur].opcode != KB200_OP_LOAD) {
+    const kb200_tape_op& e = d.tape[cur];
+    if (n >= kMaxRowPre) return false;
+    ChainStep s{};
+    if (is_unary(e.opcode)) {
+      s.op = chain_unary(e.opcode);
+      s.slot = -2;
+      cur = e.a;
+    } else if (is_binary(e.opcode)) {
+      int main_i, side_i;
+      bool reversed;
+      if (leaf(e.b) && d.tape[e.a].opcode != KB200_OP_IMM) { main_i = e.a; side_i = e.b; reversed = false; }
+      else if (leaf(e.a) && d.tape[e.b].opcode != KB200_OP_IMM) { main_i = e.b; side_i = e.a; reversed = true; }
+      else return false;
+      s.op = chain_binary(e.opcode, reversed);
+      if (d.tape[side_i].opcode == KB200_OP_IMM) { s.slot = -1; s.imm = d.tape[side_i].imm; }
+      else { s.slot = d.tape[side_i].a; }
+      ++count;                      // the leaf
+      cur = main_i;
+    } else {
+      return false;
+    }
+    ++count;                        // the op
+    rev[n++] = s;
+  }
+  out->first_slot = d.tape[cur].a;
+  out->n = n;
+  for (int i = 0; i < n; ++i) out->steps[i] = rev[n - 1 - i];
+  *entries = count + 1;             // + the first LOAD
+  return true;
+}
+
 // y = (x - mean) * rsqrt(var + eps) * gamma + beta with the two-pass mean / variance the frontend
-// emits (kiln/frontend/fx_import.py:217-230).
+// emits (kiln/frontend/fx_import.py:217-230); x a loaded row or a short chain on one (a residual add
+// fused in front), which may itself be stored as a second output.
 bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k) {
   Matcher m{d};
   int stores = 0, st = -1, reduces = 0;
   for (int i = 0; i < d.n_tape; ++i) {
-    if (m.is(i, KB200_OP_STORE)) { ++stores; st = i; }
+    if (m.is(i, KB200_OP_STORE)) ++stores;
     if (is_reduce(d.tape[i].opcode)) ++reduces;
   }
-  if (stores != 1 || reduces != 2 || d.n_tape != 17) return false;
+  if (stores < 1 || stores > 2 || reduces != 2) return false;
+  // the LayerNorm's own store is the one at the deepest level (after both reductions)
+  for (int i = 0; i < d.n_tape; ++i)
+    if (m.is(i, KB200_OP_STORE) && (st < 0 || d.tape[i].level > d.tape[st].level)) st = i;
   auto is_load = [&](int i) { return m.is(i, KB200_OP_LOAD); };
   auto is_imm = [&](int i) { return m.is(i, KB200_OP_IMM); };
   int beta, y1, gamma, y0;
@@ -181,7 +225,17 @@ bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k) {
   if (!m.is(xc, KB200_OP_SUB)) { int t = xc; xc = rstd; rstd = t; }
   if (!m.is(xc, KB200_OP_SUB) || !m.is(rstd, KB200_OP_RSQRT)) return false;
   int x = m.at(xc).a, mean = m.at(xc).b;
-  if (!is_load(x)) return false;
+  Chain pre{};
+  int pre_entries = 0;
+  if (!row_pre_chain(d, x, &pre, &pre_entries)) return false;
+  int pre_out = -1;
+  for (int i = 0; i < d.n_tape; ++i)
+    if (m.is(i, KB200_OP_STORE) && i != st) {
+      if (m.at(i).a != x || pre.n == 0) return false;      // the second output must be the chain's value
+      pre_out = m.at(i).b;
+    }
+  // nothing else in the tape: 16 entries of the LayerNorm proper beside x, the chain, the stores
+  if (d.n_tape != 16 + pre_entries + (stores - 1)) return false;
   int c1, s1;
   if (!m.split(mean, KB200_OP_MUL, is_imm, &c1, &s1)) return false;
   if (!m.is(s1, KB200_OP_RSUM) || m.at(s1).a != x) return false;
@@ -193,7 +247,9 @@ bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k) {
   int sq = m.at(s2).a;
   if (!m.is(sq, KB200_OP_MUL) || m.at(sq).a != xc || m.at(sq).b != xc) return false;
   if (m.at(c1).imm != m.at(c2).imm) return false;
-  k->x_slot = m.at(x).a;
+  k->x_slot = pre.first_slot;
+  k->row_pre = pre;
+  k->pre_out_slot = pre_out;
   k->g_slot = m.at(gamma).a;
   k->b_slot = m.at(beta).a;
   k->out_slot = m.at(st).b;
@@ -205,9 +261,10 @@ bool match_layernorm(const kb200_kernel_desc& d, PlanKernel* k) {
 // out = exp(x - max(x)) / sum(exp(x - max(x))) (kiln/frontend/fx_import.py:212-216).
 bool match_softmax(const kb200_kernel_desc& d, PlanKernel* k) {
   Matcher m{d};
-  if (d.n_tape != 7) return false;
-  int st = 6;
-  if (!m.is(st, KB200_OP_STORE)) return false;
+  int st = d.n_tape - 1, stores = 0;
+  for (int i = 0; i < d.n_tape; ++i)
+    if (m.is(i, KB200_OP_STORE)) ++stores;
+  if (stores != 1 || !m.is(st, KB200_OP_STORE)) return false;
   int dv = m.at(st).a;
   if (!m.is(dv, KB200_OP_DIV)) return false;
   int e = m.at(dv).a, s = m.at(dv).b;
@@ -215,8 +272,15 @@ bool match_softmax(const kb200_kernel_desc& d, PlanKernel* k) {
   int sub = m.at(e).a;
   if (!m.is(sub, KB200_OP_SUB)) return false;
   int x = m.at(sub).a, mx = m.at(sub).b;
-  if (!m.is(x, KB200_OP_LOAD) || !m.is(mx, KB200_OP_RMAX) || m.at(mx).a != x) return false;
-  k->x_slot = m.at(x).a;
+  if (!m.is(mx, KB200_OP_RMAX) || m.at(mx).a != x) return false;
+  // x: the loaded row, or a short chain on it (scale and additive mask fused in front)
+  Chain pre{};
+  int pre_entries = 0;
+  if (!row_pre_chain(d, x, &pre, &pre_entries)) return false;
+  if (d.n_tape != 6 + pre_entries) return false;
+  k->x_slot = pre.first_slot;
+  k->row_pre = pre;
+  k->pre_out_slot = -1;
   k->out_slot = m.at(st).b;
   return true;
 }
@@ -509,7 +573,7 @@ static int assign_shadows(Plan& plan) {
       int64_t out_elems = 0;
       if (pj.impl == IMPL_ATTN_FUSED) {
         out = attention_output(plan, j, &out_elems);
-      } else if (pj.impl == IMPL_ROW_LAYERNORM) {
+      } else if (pj.impl == IMPL_ROW_LAYERNORM && pj.desc.iter_rank == 2) {
         out = &pj.ops[pj.out_slot];
         out_elems = (pj.desc.iter_shape[0] - 1) * out->stride[0] + pj.desc.iter_shape[1];
       } else if (pj.impl == IMPL_MM_TC && pj.has_chain) {

@@ -119,6 +119,23 @@ struct RowFastParams {
   int inner;
   float inv_n, eps;
   __nv_bfloat16* out16;    // optional bf16 copy of the output (same row stride as `out`), or null
+  // Two row dims (a [batch * heads, tokens, inner] softmax whose mask varies with the token only):
+  // row = i0 * rows_inner + i1, and every tensor has a stride for each.  rows_inner == 0: one row dim.
+  int64_t rows_inner;
+  int64_t x_stride1, out_stride1;
+  // A short elementwise chain applied to the loaded row before the reductions (scale and additive
+  // mask in front of a softmax, a residual add in front of a LayerNorm), and where to store its value.
+  int n_pre;
+  struct Pre {
+    int op;                // ChainOp
+    int kind;              // 0 unary, 1 immediate, 2 tensor
+    float imm;
+    const float* ptr;
+    int64_t stride0, stride1;
+    int inner_stride;      // 1, or 0 for one value per row
+  } pre[kMaxRowPre];
+  float* pre_out;          // receives the chain's value (same shape as x), or null
+  int64_t pre_out_stride0, pre_out_stride1;
 };
 
 enum { ROW_LAYERNORM = 0, ROW_SOFTMAX = 1 };
@@ -146,8 +163,11 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
   pdl_wait();                 // the producer of this kernel's inputs has completed
   pdl_launch_dependents();    // the next kernel may begin its start-up
   if (row >= p.n_rows) return;
-  const float4* x4 = reinterpret_cast<const float4*>(p.x + row * p.x_row_stride);
-  float4* o4 = reinterpret_cast<float4*>(p.out + row * p.out_row_stride);
+  int64_t i0 = row, i1 = 0;
+  if (p.rows_inner > 0) { i0 = row / p.rows_inner; i1 = row - i0 * p.rows_inner; }
+  const float4* x4 = reinterpret_cast<const float4*>(p.x + i0 * p.x_row_stride + i1 * p.x_stride1);
+  float4* o4 = reinterpret_cast<float4*>(p.out + i0 * p.out_row_stride + i1 * p.out_stride1);
+  const int64_t out16_off = i0 * p.out_row_stride + i1 * p.out_stride1;
   float4 v[VPL];
   bool live[VPL];
 #pragma unroll
@@ -155,6 +175,29 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
     const int j = lane + 32 * i;
     live[i] = j < nvec;
     if (live[i]) v[i] = x4[j];
+  }
+  for (int s = 0; s < p.n_pre; ++s) {
+    const RowFastParams::Pre st = p.pre[s];
+    const float* side = st.kind == 2 ? st.ptr + i0 * st.stride0 + i1 * st.stride1 : nullptr;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      if (!live[i]) continue;
+      float4 t = make_float4(st.imm, st.imm, st.imm, st.imm);
+      if (st.kind == 2) {
+        if (st.inner_stride == 1) t = *reinterpret_cast<const float4*>(side + 4 * (lane + 32 * i));
+        else { const float one = __ldg(side); t = make_float4(one, one, one, one); }
+      }
+      v[i].x = apply_chain(st.op, v[i].x, t.x);
+      v[i].y = apply_chain(st.op, v[i].y, t.y);
+      v[i].z = apply_chain(st.op, v[i].z, t.z);
+      v[i].w = apply_chain(st.op, v[i].w, t.w);
+    }
+  }
+  if (p.pre_out != nullptr) {
+    float4* z4 = reinterpret_cast<float4*>(p.pre_out + i0 * p.pre_out_stride0 + i1 * p.pre_out_stride1);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      if (live[i]) z4[lane + 32 * i] = v[i];
   }
   if (MODE == ROW_LAYERNORM) {
     float s = 0.0f;
@@ -186,7 +229,7 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
           uint2 packed;
           packed.x = *reinterpret_cast<uint32_t*>(&lo);
           packed.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(p.out16 + row * p.out_row_stride + 4 * j) = packed;
+          *reinterpret_cast<uint2*>(p.out16 + out16_off + 4 * j) = packed;
         }
       }
     }
@@ -254,21 +297,42 @@ int choose_row(Plan& plan, PlanKernel& k) {
       return fail(KB200_ERR_UNSUPPORTED, "row kernel %s: more than %d reductions at one level of the chain", d.name, kMaxRowRed);
   }
   const int64_t inner = d.iter_shape[d.iter_rank - 1];
-  const bool shape_ok = d.iter_rank == 2 && inner % 4 == 0 && inner <= 2048 && inner >= 4;
+  // register-resident rows: one or two row dims, rows of 4..2048 floats in 128-bit units
+  const int last = d.iter_rank - 1;
+  const bool shape_ok = (d.iter_rank == 2 || d.iter_rank == 3) && inner % 4 == 0 && inner <= 2048 && inner >= 4;
   if (!shape_ok) return KB200_OK;
   auto row_tensor_ok = [&](int slot) {
     const DevOperand& o = k.ops[slot];
-    return o.stride[1] == 1 && o.stride[0] % 4 == 0 && aligned16(o.ptr);
+    if (o.stride[last] != 1 || !aligned16(o.ptr)) return false;
+    for (int dd = 0; dd < last; ++dd)
+      if (o.stride[dd] % 4) return false;
+    return true;
   };
   auto vector_ok = [&](int slot) {
     const DevOperand& o = k.ops[slot];
-    return o.stride[1] == 1 && o.stride[0] == 0 && aligned16(o.ptr);
+    if (o.stride[last] != 1 || !aligned16(o.ptr)) return false;
+    for (int dd = 0; dd < last; ++dd)
+      if (o.stride[dd] != 0) return false;
+    return true;
   };
+  // operands of the chain in front of the reductions: a tensor like x, or one value per row
+  auto pre_ok = [&]() {
+    for (int st = 0; st < k.row_pre.n; ++st) {
+      const int slot = k.row_pre.steps[st].slot;
+      if (slot < 0) continue;
+      const DevOperand& o = k.ops[slot];
+      if (o.stride[last] == 0) continue;
+      if (!row_tensor_ok(slot)) return false;
+    }
+    return k.pre_out_slot < 0 || row_tensor_ok(k.pre_out_slot);
+  };
+  k.row_pre.n = 0;
+  k.pre_out_slot = -1;
   if (match_layernorm(d, &k)) {
-    if (row_tensor_ok(k.x_slot) && row_tensor_ok(k.out_slot) && vector_ok(k.g_slot) && vector_ok(k.b_slot))
+    if (row_tensor_ok(k.x_slot) && row_tensor_ok(k.out_slot) && vector_ok(k.g_slot) && vector_ok(k.b_slot) && pre_ok())
       k.impl = IMPL_ROW_LAYERNORM;
   } else if (match_softmax(d, &k)) {
-    if (row_tensor_ok(k.x_slot) && row_tensor_ok(k.out_slot)) k.impl = IMPL_ROW_SOFTMAX;
+    if (row_tensor_ok(k.x_slot) && row_tensor_ok(k.out_slot) && pre_ok()) k.impl = IMPL_ROW_SOFTMAX;
   }
   return KB200_OK;
 }
@@ -286,6 +350,28 @@ int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     p.x_row_stride = k.ops[k.x_slot].stride[0];
     p.out_row_stride = k.ops[k.out_slot].stride[0];
     p.inner = (int)inner;
+    const bool two = d.iter_rank == 3;
+    p.rows_inner = two ? d.iter_shape[1] : 0;
+    p.x_stride1 = two ? k.ops[k.x_slot].stride[1] : 0;
+    p.out_stride1 = two ? k.ops[k.out_slot].stride[1] : 0;
+    p.n_pre = k.row_pre.n;
+    for (int st = 0; st < k.row_pre.n; ++st) {
+      const ChainStep& cs = k.row_pre.steps[st];
+      RowFastParams::Pre& pr = p.pre[st];
+      pr.op = cs.op;
+      pr.imm = cs.imm;
+      pr.kind = cs.slot == -2 ? 0 : (cs.slot == -1 ? 1 : 2);
+      if (cs.slot >= 0) {
+        const DevOperand& o = k.ops[cs.slot];
+        pr.ptr = o.ptr;
+        pr.stride0 = o.stride[0];
+        pr.stride1 = two ? o.stride[1] : 0;
+        pr.inner_stride = (int)o.stride[d.iter_rank - 1];
+      }
+    }
+    p.pre_out = k.pre_out_slot >= 0 ? k.ops[k.pre_out_slot].ptr : nullptr;
+    p.pre_out_stride0 = k.pre_out_slot >= 0 ? k.ops[k.pre_out_slot].stride[0] : 0;
+    p.pre_out_stride1 = k.pre_out_slot >= 0 && two ? k.ops[k.pre_out_slot].stride[1] : 0;
     if (k.impl == IMPL_ROW_LAYERNORM) {
       p.gamma = k.ops[k.g_slot].ptr;
       p.beta = k.ops[k.b_slot].ptr;

@@ -58,6 +58,19 @@ SIDE = torch.randn(4, 1)
 PROJ = torch.randn(41, 66)
 
 
+ROW_MASK = torch.full((40, 512), float("-inf")).triu(1)
+
+
+class ResidualNorm(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.norm = torch.nn.LayerNorm(256)
+
+    def forward(self, a, b):
+        s = a + b
+        return s, self.norm(s)
+
+
 def small_models():
     from kiln_b200 import workloads as W
 
@@ -75,6 +88,9 @@ def small_models():
         "broadcast side input": (lambda x: x / (x.sum(-1, keepdim=True) ** 2 + 1.0) + SIDE, (torch.randn(4, 44),)),
         "unary ops": (lambda x: torch.tanh(x) + torch.sigmoid(x) + torch.erf(x) + F.gelu(x) + torch.relu(-x), (torch.randn(5, 26) * 3,)),
         "small block": (W.block_module(5, 16, d=64, heads=4), (torch.randn(16, 64),)),
+        # row kernels with a chain in front of the reductions (register-resident rows, two row dims)
+        "scaled masked softmax": (lambda x: F.softmax(x * 0.125 + ROW_MASK, -1), (torch.randn(6, 40, 512),)),
+        "residual add, layernorm, both results": (ResidualNorm().eval(), (torch.randn(3, 50, 256), torch.randn(3, 50, 256))),
     }
 
 
