@@ -47,6 +47,7 @@ constexpr int attn_smem(bool bf16) { return 5 * (bf16 ? 1 : 2) * kSlab + 2 * kRo
 
 struct AttnParams {
   int T, H, q_tiles;
+  int B;                     // sequences in the graph (1 for the two-dimensional block); rows of Q, K, V and of the output are b * T + t
   float scale_log2;          // softmax scale times log2(e): exponentials are taken in base 2
   float* out;                // [T, H * 64] merged heads
   int64_t out_row_stride;
@@ -75,6 +76,8 @@ struct AttnState {
   float* staged_out = nullptr;
   float* final_out = nullptr;
   int64_t out_elems = 0;
+  int chain = 5;                   // plan kernels this launch stands for: 5 (one sequence) or 7 (a batch of sequences)
+  bool wants_bf16 = false;         // the chain's matmuls are in BF16 mode
 };
 
 __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
@@ -150,9 +153,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull0 = smem_u32(&bars[15]);
 
   const int h = blockIdx.x % p.H;
-  const int qt = p.q_tiles - 1 - blockIdx.x / p.H;   // heaviest (longest causal prefix) tiles first
+  const int seq = (blockIdx.x / p.H) % p.B;
+  const int qt = p.q_tiles - 1 - blockIdx.x / (p.H * p.B);   // heaviest (longest causal prefix) tiles first, of every sequence
   const int q0 = qt * kRows;
   const int n_kv = qt + 1;                           // causal: key tiles 0..qt
+  const int row0 = seq * p.T;                        // this sequence's first row in Q, K, V and the output
 
   if (threadIdx.x == 32) {
     prefetch_tensormap(&map_q);
@@ -198,19 +203,19 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       mbar_expect_tx(q_full, kTileBytes);
-      tma_load_3d(q_smem, &map_q, q_full, 0, q0, h);
-      if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, q0, h);
+      tma_load_3d(q_smem, &map_q, q_full, 0, row0 + q0, h);
+      if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, row0 + q0, h);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); break; }
         mbar_expect_tx(k_full + 8 * s, kTileBytes);
-        tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, j * kRows, h);
-        if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, j * kRows, h);
+        tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, row0 + j * kRows, h);
+        if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, row0 + j * kRows, h);
         if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); break; }
         mbar_expect_tx(v_full + 8 * s, kTileBytes);
-        tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, j * kRows, h);
-        if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, j * kRows, h);
+        tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, row0 + j * kRows, h);
+        if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, row0 + j * kRows, h);
       }
     }
   } else if (warp == 1) {
@@ -404,7 +409,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int q = 0; q < 8; ++q)
         *reinterpret_cast<float4*>(stage + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
       __syncwarp();
-      const int64_t first_row = q0 + quad * 32;
+      const int64_t first_row = row0 + q0 + quad * 32;
       float* dst = p.out + first_row * p.out_row_stride + h * kHeadDim + group * 32;
       __nv_bfloat16* dst16 = p.out16 != nullptr ? p.out16 + first_row * p.out16_row_stride + h * kHeadDim + group * 32 : nullptr;
 #pragma unroll
@@ -508,8 +513,134 @@ bool is_copy(const PlanKernel& k) {
 
 }  // namespace
 
-// Tries to replace kernels i .. i+4 by the fused kernel.  Returns true when it did.
-bool attention_try_fuse(Plan& plan, size_t i) {
+namespace {
+
+// What both matchers below hand to the common part.
+struct AttnChain {
+  size_t first = 0;
+  int count = 0;                      // plan kernels covered: first .. first + count - 1
+  int64_t B = 1, H = 0, T = 0, rs = 0; // sequences, heads, tokens, row stride of the Q / K / V views
+  const float* q = nullptr;
+  const float* k = nullptr;
+  const float* v = nullptr;
+  float scale = 0.f;
+  const DevOperand* mask = nullptr;
+  const DevOperand* y = nullptr;      // the merged-heads output, rows of H * 64
+  Range y_range{nullptr, nullptr};
+  std::vector<Range> dead;            // intermediates the fused kernel never writes
+  std::vector<Range> sources;         // what the fused kernel reads (Q, K, V views)
+  std::vector<PlanKernel*> matmuls;   // tensor-core state to drop
+  bool bf16 = false;
+};
+
+// Shared tail of the two matchers: the intermediates must be dead afterwards, the mask causal; then
+// the state is built and the plan kernels are marked.
+bool finish_fusion(Plan& plan, const AttnChain& c) {
+  const int64_t T = c.T, H = c.H, B = c.B, hd = kHeadDim, rs = c.rs;
+  if (!aligned16(c.q) || !aligned16(c.k) || !aligned16(c.v) || !aligned16(c.y->ptr)) return false;
+  if (B * H * (T / kRows) >= (int64_t(1) << 31)) return false;
+  // A later read that touches an intermediate is only acceptable if everything it reads was rewritten
+  // after the chain (by the chain's own output Y, whose memory the planner may have taken from
+  // them, or by a later kernel).
+  {
+    std::vector<Range> rewritten{c.y_range};
+    for (size_t j = c.first + c.count; j < plan.kernels.size(); ++j) {
+      std::vector<int> reads, writes;
+      io_slots(plan.kernels[j], &reads, &writes);
+      for (int slot : reads) {
+        const Range r = operand_range(plan.kernels[j], slot);
+        bool touches = false;
+        for (const Range& d : c.dead) touches = touches || overlaps(r, d);
+        if (!touches) continue;
+        bool fresh = false;
+        for (const Range& w : rewritten) fresh = fresh || covers(w, r);
+        if (!fresh) return false;
+      }
+      for (int slot : writes) rewritten.push_back(operand_range(plan.kernels[j], slot));
+    }
+  }
+  // the fused kernel writes Y while other CTAs still read Q, K, V: if the planner reused their
+  // memory for Y, the result is staged in a private buffer and copied afterwards
+  bool aliased = false;
+  for (const Range& src : c.sources) aliased = aliased || overlaps(c.y_range, src);
+
+  // --- the mask must be the causal one: 0 on and below the diagonal, -inf above ---
+  {
+    std::vector<float> host((size_t)T * T);
+    if (cudaMemcpy(host.data(), c.mask->ptr, host.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    for (int64_t r = 0; r < T; ++r)
+      for (int64_t col = 0; col < T; ++col) {
+        const float v = host[(size_t)r * T + col];
+        if (col <= r ? v != 0.0f : !(v < 0.0f && isinf(v))) return false;
+      }
+  }
+
+  // Q, K, V as [head, row, 64] views with rows b * T + t: a batch of sequences is more rows of the same map
+  AttnState* st = new AttnState();
+  if (!encode_map(&st->map_q, false, c.q, hd, B * T, H, rs, hd, 32, kRows, false) ||
+      !encode_map(&st->map_k, false, c.k, hd, B * T, H, rs, hd, 32, kRows, false) ||
+      !encode_map(&st->map_v, false, c.v, hd, B * T, H, rs, hd, 32, kRows, true)) {
+    delete st;
+    return false;
+  }
+  if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
+      cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess) {
+    cudaGetLastError();
+    delete st;
+    return false;
+  }
+  st->q_ptr = c.q;
+  st->k_ptr = c.k;
+  st->v_ptr = c.v;
+  st->row_stride = rs;
+  st->chain = c.count;
+  st->wants_bf16 = c.bf16;
+  AttnParams& p = st->params;
+  p.T = (int)T;
+  p.H = (int)H;
+  p.B = (int)B;
+  p.q_tiles = (int)(T / kRows);
+  p.scale_log2 = c.scale * 1.4426950408889634f;
+  p.out = c.y->ptr;
+  p.out_row_stride = H * hd;
+  p.out16 = nullptr;
+  p.out16_row_stride = H * hd;
+  st->y = c.y;
+  st->y_elems = B * T * H * hd;
+  if (aliased) {
+    st->out_elems = B * T * H * hd;
+    if (cudaMalloc(&st->staged_out, (size_t)st->out_elems * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      delete st;
+      return false;
+    }
+    st->final_out = c.y->ptr;
+    p.out = st->staged_out;
+  }
+  // D = F32, A/B = TF32, both K-major, N = 128 | B N-major, N = 64; M = 128
+  p.idesc_qk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kRows >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+  p.idesc_pv = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+  p.kernel_index = (int)c.first;
+  p.status = plan.d_status;
+  st->grid = dim3((unsigned)(B * H * p.q_tiles), 1, 1);
+
+  for (PlanKernel* k : c.matmuls) destroy_matmul(*k);
+  PlanKernel& holder = plan.kernels[c.first];
+  holder.attn = st;
+  holder.impl = IMPL_ATTN_FUSED;
+  holder.launches = aliased ? 2 : 1;
+  for (int j = 1; j < c.count; ++j) {
+    plan.kernels[c.first + j].impl = IMPL_FUSED_AWAY;
+    plan.kernels[c.first + j].launches = 0;
+  }
+  return true;
+}
+
+// One sequence: kernels i .. i+4 (K^T copy, Q K^T * scale + mask, softmax, P V, head merge).
+bool try_fuse_single(Plan& plan, size_t i) {
   if (i + 4 >= plan.kernels.size()) return false;
   PlanKernel& k2 = plan.kernels[i];
   PlanKernel& k3 = plan.kernels[i + 1];
@@ -540,8 +671,8 @@ bool attention_try_fuse(Plan& plan, size_t i) {
   const DevOperand& Kdst = k2.ops[k2.chain.out_slot];
   if (Ksrc.stride[0] != 1 || Ksrc.stride[1] != rs || Kdst.stride[0] != T || Kdst.stride[1] != 1 || Kdst.ptr != Kt.ptr) return false;
   // --- k4: softmax over the last dim ---
-  if (k4.desc.kclass != KB200_K_ROW || k4.impl != IMPL_ROW_SOFTMAX) return false;
-  if (k4.ops[k4.x_slot].ptr != S.ptr || k4.desc.iter_shape[0] != H * T || k4.desc.iter_shape[1] != T) return false;
+  if (k4.desc.kclass != KB200_K_ROW || k4.impl != IMPL_ROW_SOFTMAX || k4.row_pre.n != 0) return false;
+  if (k4.ops[k4.x_slot].ptr != S.ptr || k4.desc.iter_rank != 2 || k4.desc.iter_shape[0] != H * T || k4.desc.iter_shape[1] != T) return false;
   const DevOperand& P = k4.ops[k4.out_slot];
   if (P.stride[0] != T || P.stride[1] != 1) return false;
   // --- k5: O = P V ---
@@ -561,8 +692,6 @@ bool attention_try_fuse(Plan& plan, size_t i) {
   const DevOperand& Y = k6.ops[k6.chain.out_slot];
   if (Osrc.ptr != O.ptr || Osrc.stride[0] != hd || Osrc.stride[1] != T * hd || Osrc.stride[2] != 1) return false;
   if (Y.stride[0] != H * hd || Y.stride[1] != hd || Y.stride[2] != 1) return false;
-  if (!aligned16(Q.ptr) || !aligned16(Ksrc.ptr) || !aligned16(V.ptr) || !aligned16(Y.ptr)) return false;
-
   // --- the four intermediates (K^T, scores, probabilities, per-head O) must be arena buffers: a graph
   // result lives in a caller's output buffer (kiln/passes/buffers.py:161,193), which the fused kernel
   // would never write ---
@@ -571,106 +700,143 @@ bool attention_try_fuse(Plan& plan, size_t i) {
       k4.desc.operands[k4.out_slot].base_kind != KB200_BASE_ARENA ||
       k5.desc.operands[k5.chain.out_slot].base_kind != KB200_BASE_ARENA)
     return false;
-  // --- and dead after k6: nobody may read them before they are rewritten ---
-  Range dead[4] = {out_range(k2, k2.chain.out_slot), operand_range(k3, k3.chain.out_slot), out_range(k4, k4.out_slot),
-                   operand_range(k5, k5.chain.out_slot)};
-  const Range y_range = out_range(k6, k6.chain.out_slot);
-  // A later read that touches one of them is only acceptable if everything it reads was rewritten
-  // after the chain (by the chain's own output Y, whose memory the planner may have taken from
-  // them, or by a later kernel).
-  {
-    std::vector<Range> rewritten{y_range};
-    for (size_t j = i + 5; j < plan.kernels.size(); ++j) {
-      std::vector<int> reads, writes;
-      io_slots(plan.kernels[j], &reads, &writes);
-      for (int slot : reads) {
-        const Range r = operand_range(plan.kernels[j], slot);
-        bool touches = false;
-        for (int b = 0; b < 4; ++b) touches = touches || overlaps(r, dead[b]);
-        if (!touches) continue;
-        bool fresh = false;
-        for (const Range& w : rewritten) fresh = fresh || covers(w, r);
-        if (!fresh) return false;
-      }
-      for (int slot : writes) rewritten.push_back(operand_range(plan.kernels[j], slot));
-    }
-  }
-  // the fused kernel writes Y while other CTAs still read Q, K, V: if the planner reused their
-  // memory for Y, the result is staged in a private buffer and copied afterwards
-  const bool aliased = overlaps(y_range, operand_range(k3, k3.desc.a_slot)) || overlaps(y_range, operand_range(k5, k5.desc.b_slot)) ||
-                       overlaps(y_range, operand_range(k2, k2.chain.first_slot));
-
-  // --- the mask must be the causal one: 0 on and below the diagonal, -inf above ---
-  {
-    std::vector<float> host((size_t)T * T);
-    if (cudaMemcpy(host.data(), mask.ptr, host.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
-      cudaGetLastError();
-      return false;
-    }
-    for (int64_t r = 0; r < T; ++r)
-      for (int64_t c = 0; c < T; ++c) {
-        const float v = host[(size_t)r * T + c];
-        if (c <= r ? v != 0.0f : !(v < 0.0f && isinf(v))) return false;
-      }
-  }
-
-  AttnState* st = new AttnState();
-  if (!encode_map(&st->map_q, false, Q.ptr, hd, T, H, rs, hd, 32, kRows, false) ||
-      !encode_map(&st->map_k, false, Ksrc.ptr, hd, T, H, rs, hd, 32, kRows, false) ||
-      !encode_map(&st->map_v, false, V.ptr, hd, T, H, rs, hd, 32, kRows, true)) {
-    delete st;
-    return false;
-  }
-  if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
-      cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess) {
-    cudaGetLastError();
-    delete st;
-    return false;
-  }
-  st->q_ptr = Q.ptr;
-  st->k_ptr = Ksrc.ptr;
-  st->v_ptr = V.ptr;
-  st->row_stride = rs;
-  AttnParams& p = st->params;
-  p.T = (int)T;
-  p.H = (int)H;
-  p.q_tiles = (int)(T / kRows);
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.out = Y.ptr;
-  p.out_row_stride = Y.stride[0];
-  p.out16 = nullptr;
-  p.out16_row_stride = H * hd;
-  st->y = &Y;
-  st->y_elems = T * H * hd;
-  if (aliased) {
-    st->out_elems = T * H * hd;
-    if (cudaMalloc(&st->staged_out, (size_t)st->out_elems * sizeof(float)) != cudaSuccess) {
-      cudaGetLastError();
-      delete st;
-      return false;
-    }
-    st->final_out = Y.ptr;
-    p.out = st->staged_out;
-    p.out_row_stride = H * hd;
-  }
-  // D = F32, A/B = TF32, both K-major, N = 128 | B N-major, N = 64; M = 128
-  p.idesc_qk = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kRows >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
-  p.idesc_pv = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
-  p.kernel_index = (int)i;
-  p.status = plan.d_status;
-  st->grid = dim3((unsigned)(H * p.q_tiles), 1, 1);
-
-  destroy_matmul(k3);
-  destroy_matmul(k5);
-  k2.attn = st;
-  k2.impl = IMPL_ATTN_FUSED;
-  k2.launches = aliased ? 2 : 1;
-  for (PlanKernel* k : {&k3, &k4, &k5, &k6}) {
-    k->impl = IMPL_FUSED_AWAY;
-    k->launches = 0;
-  }
-  return true;
+  AttnChain c;
+  c.first = i;
+  c.count = 5;
+  c.H = H; c.T = T; c.rs = rs;
+  c.q = Q.ptr; c.k = Ksrc.ptr; c.v = V.ptr;
+  c.scale = scale;
+  c.mask = &mask;
+  c.y = &Y;
+  c.y_range = out_range(k6, k6.chain.out_slot);
+  c.dead = {out_range(k2, k2.chain.out_slot), operand_range(k3, k3.chain.out_slot), out_range(k4, k4.out_slot),
+            operand_range(k5, k5.chain.out_slot)};
+  c.sources = {operand_range(k3, k3.desc.a_slot), operand_range(k5, k5.desc.b_slot), operand_range(k2, k2.chain.first_slot)};
+  c.matmuls = {&k3, &k5};
+  c.bf16 = k3.desc.precision == KB200_PREC_BF16;
+  return finish_fusion(plan, c);
 }
+
+// A batch of sequences in one graph ([batch, tokens, d] models): kernels i .. i+6.  The buffer pass
+// makes every operand of the two batched matmuls contiguous first (kiln/passes/buffers.py:208-217), and
+// the fusion pass puts scale and mask in front of the softmax instead of behind the matmul:
+//   i    copy  Q view   [B, H, T, 64] of the QKV projection's [B * T, 3 d] output -> contiguous
+//   i+1  copy  K^T view [B, H * 64, T]                                            -> contiguous
+//   i+2  matmul [B * H, T, T] = Q K^T, no epilogue
+//   i+3  row    softmax(S * scale + mask)
+//   i+4  copy  V view   [B, H, T, 64]                                             -> contiguous
+//   i+5  matmul [B * H, T, 64] = P V
+//   i+6  copy  merge heads [B, T, H, 64] -> [B * T, d]
+// The fused kernel reads the three VIEWS (rows b * T + t of one [B * T, 3 d] buffer) and writes the
+// merged output; none of the six intermediates is ever written.
+bool try_fuse_batched(Plan& plan, size_t i) {
+  if (i + 6 >= plan.kernels.size()) return false;
+  PlanKernel& cq = plan.kernels[i];
+  PlanKernel& ck = plan.kernels[i + 1];
+  PlanKernel& mm1 = plan.kernels[i + 2];
+  PlanKernel& sm = plan.kernels[i + 3];
+  PlanKernel& cv = plan.kernels[i + 4];
+  PlanKernel& mm2 = plan.kernels[i + 5];
+  PlanKernel& merge = plan.kernels[i + 6];
+  const int64_t hd = kHeadDim;
+  // --- scores ---
+  if (mm1.desc.kclass != KB200_K_MATMUL || mm1.desc.precision == KB200_PREC_FP32 || !mm1.has_chain || mm1.chain.n != 0) return false;
+  const int64_t BH = mm1.batch, T = mm1.M;
+  if (mm1.K != hd || mm1.N != T || T % kRows != 0 || T < kRows) return false;
+  const DevOperand& Qc = mm1.ops[mm1.desc.a_slot];
+  const DevOperand& Ktc = mm1.ops[mm1.desc.b_slot];
+  const DevOperand& S = mm1.ops[mm1.chain.out_slot];
+  if (Qc.stride[0] != T * hd || Qc.stride[1] != hd || Qc.stride[2] != 1) return false;
+  if (Ktc.stride[0] != hd * T || Ktc.stride[1] != T || Ktc.stride[2] != 1) return false;
+  if (S.stride[0] != T * T || S.stride[1] != T || S.stride[2] != 1) return false;
+  // --- the copy of Q: [B, H, T, 64] ---
+  if (!is_copy(cq) || cq.desc.iter_rank != 4 || cq.desc.iter_shape[2] != T || cq.desc.iter_shape[3] != hd) return false;
+  const int64_t B = cq.desc.iter_shape[0], H = cq.desc.iter_shape[1];
+  if (B < 1 || H < 1 || H > 65535 || B * H != BH) return false;
+  const DevOperand& Qsrc = cq.ops[cq.chain.first_slot];
+  const DevOperand& Qdst = cq.ops[cq.chain.out_slot];
+  const int64_t rs = Qsrc.stride[2];
+  if (Qdst.ptr != Qc.ptr || Qdst.stride[0] != H * T * hd || Qdst.stride[1] != T * hd || Qdst.stride[2] != hd || Qdst.stride[3] != 1) return false;
+  if (Qsrc.stride[3] != 1 || Qsrc.stride[1] != hd || rs % 4 || rs < H * hd || Qsrc.stride[0] != T * rs) return false;
+  // --- the copy of K^T: [B, H * 64, T] ---
+  if (!is_copy(ck) || ck.desc.iter_rank != 3 || ck.desc.iter_shape[0] != B || ck.desc.iter_shape[1] != H * hd || ck.desc.iter_shape[2] != T)
+    return false;
+  const DevOperand& Ksrc = ck.ops[ck.chain.first_slot];
+  const DevOperand& Kdst = ck.ops[ck.chain.out_slot];
+  if (Kdst.ptr != Ktc.ptr || Kdst.stride[0] != H * hd * T || Kdst.stride[1] != T || Kdst.stride[2] != 1) return false;
+  if (Ksrc.stride[0] != T * rs || Ksrc.stride[1] != 1 || Ksrc.stride[2] != rs) return false;
+  // --- softmax(S * scale + mask) over [B * H, T, T] ---
+  if (sm.desc.kclass != KB200_K_ROW || sm.impl != IMPL_ROW_SOFTMAX || sm.desc.iter_rank != 3) return false;
+  if (sm.desc.iter_shape[0] != BH || sm.desc.iter_shape[1] != T || sm.desc.iter_shape[2] != T || sm.ops[sm.x_slot].ptr != S.ptr) return false;
+  if (sm.row_pre.n != 2 || sm.row_pre.steps[0].op != CH_MUL || sm.row_pre.steps[0].slot != -1 || sm.row_pre.steps[1].op != CH_ADD ||
+      sm.row_pre.steps[1].slot < 0)
+    return false;
+  const float scale = sm.row_pre.steps[0].imm;
+  const int mask_slot = sm.row_pre.steps[1].slot;
+  const DevOperand& mask = sm.ops[mask_slot];
+  if (!(scale > 0.0f) || mask.stride[0] != 0 || mask.stride[1] != T || mask.stride[2] != 1) return false;
+  if (sm.desc.operands[mask_slot].base_kind != KB200_BASE_CONST) return false;
+  const DevOperand& P = sm.ops[sm.out_slot];
+  if (P.stride[0] != T * T || P.stride[1] != T || P.stride[2] != 1) return false;
+  // --- the copy of V: [B, H, T, 64] ---
+  if (!is_copy(cv) || cv.desc.iter_rank != 4 || cv.desc.iter_shape[0] != B || cv.desc.iter_shape[1] != H || cv.desc.iter_shape[2] != T ||
+      cv.desc.iter_shape[3] != hd)
+    return false;
+  const DevOperand& Vsrc = cv.ops[cv.chain.first_slot];
+  const DevOperand& Vdst = cv.ops[cv.chain.out_slot];
+  if (Vsrc.stride[0] != T * rs || Vsrc.stride[1] != hd || Vsrc.stride[2] != rs || Vsrc.stride[3] != 1) return false;
+  if (Vdst.stride[0] != H * T * hd || Vdst.stride[1] != T * hd || Vdst.stride[2] != hd || Vdst.stride[3] != 1) return false;
+  // --- O = P V ---
+  if (mm2.desc.kclass != KB200_K_MATMUL || mm2.desc.precision == KB200_PREC_FP32 || !mm2.has_chain || mm2.chain.n != 0) return false;
+  if (mm2.batch != BH || mm2.M != T || mm2.N != hd || mm2.K != T) return false;
+  const DevOperand& Pa = mm2.ops[mm2.desc.a_slot];
+  const DevOperand& Vc = mm2.ops[mm2.desc.b_slot];
+  const DevOperand& O = mm2.ops[mm2.chain.out_slot];
+  if (Pa.ptr != P.ptr || Pa.stride[0] != T * T || Pa.stride[1] != T || Pa.stride[2] != 1) return false;
+  if (Vc.ptr != Vdst.ptr || Vc.stride[0] != T * hd || Vc.stride[1] != hd || Vc.stride[2] != 1) return false;
+  if (O.stride[0] != T * hd || O.stride[1] != hd || O.stride[2] != 1) return false;
+  // --- merge heads: [B, T, H, 64] ---
+  if (!is_copy(merge) || merge.desc.iter_rank != 4 || merge.desc.iter_shape[0] != B || merge.desc.iter_shape[1] != T ||
+      merge.desc.iter_shape[2] != H || merge.desc.iter_shape[3] != hd)
+    return false;
+  const DevOperand& Osrc = merge.ops[merge.chain.first_slot];
+  const DevOperand& Y = merge.ops[merge.chain.out_slot];
+  if (Osrc.ptr != O.ptr || Osrc.stride[0] != H * T * hd || Osrc.stride[1] != hd || Osrc.stride[2] != T * hd || Osrc.stride[3] != 1) return false;
+  if (Y.stride[0] != T * H * hd || Y.stride[1] != H * hd || Y.stride[2] != hd || Y.stride[3] != 1) return false;
+  // --- the six intermediates must be arena buffers ---
+  for (const auto& [k, slot] : {std::pair<const PlanKernel*, int>{&cq, cq.chain.out_slot}, {&ck, ck.chain.out_slot},
+                                {&mm1, mm1.chain.out_slot}, {&sm, sm.out_slot}, {&cv, cv.chain.out_slot}, {&mm2, mm2.chain.out_slot}})
+    if (k->desc.operands[slot].base_kind != KB200_BASE_ARENA) return false;
+  AttnChain c;
+  c.first = i;
+  c.count = 7;
+  c.B = B; c.H = H; c.T = T; c.rs = rs;
+  c.q = Qsrc.ptr; c.k = Ksrc.ptr; c.v = Vsrc.ptr;
+  c.scale = scale;
+  c.mask = &mask;
+  c.y = &Y;
+  c.y_range = out_range(merge, merge.chain.out_slot);
+  c.dead = {out_range(cq, cq.chain.out_slot), out_range(ck, ck.chain.out_slot), operand_range(mm1, mm1.chain.out_slot),
+            out_range(sm, sm.out_slot), out_range(cv, cv.chain.out_slot), operand_range(mm2, mm2.chain.out_slot)};
+  c.sources = {out_range(cq, cq.chain.first_slot), out_range(ck, ck.chain.first_slot), out_range(cv, cv.chain.first_slot)};
+  c.matmuls = {&mm1, &mm2};
+  c.bf16 = mm1.desc.precision == KB200_PREC_BF16;
+  return finish_fusion(plan, c);
+}
+
+}  // namespace
+
+// Tries to replace the attention chain that starts at kernel i by the fused kernel.  Returns the
+// number of plan kernels it replaced (5: one sequence, 7: a batch of sequences), or 0.
+int attention_try_fuse(Plan& plan, size_t i) {
+  if (try_fuse_single(plan, i)) return 5;
+  if (try_fuse_batched(plan, i)) return 7;
+  return 0;
+}
+
+// Plan kernels the fused launch held by `k` stands for (0 if it holds none).
+int attention_chain_length(const PlanKernel& k) { return k.attn ? static_cast<const AttnState*>(k.attn)->chain : 0; }
+bool attention_wants_bf16(const PlanKernel& k) { return k.attn && static_cast<const AttnState*>(k.attn)->wants_bf16; }
 
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   const AttnState* st = static_cast<const AttnState*>(k.attn);
@@ -699,7 +865,7 @@ bool attention_operand_span(const PlanKernel& k, const float** lo, const float**
   const float* last = st->q_ptr > st->k_ptr ? st->q_ptr : st->k_ptr;
   if (st->v_ptr > last) last = st->v_ptr;
   *lo = first;
-  *hi = last + (int64_t)(st->params.T - 1) * st->row_stride + (int64_t)st->params.H * kHeadDim;
+  *hi = last + ((int64_t)st->params.B * st->params.T - 1) * st->row_stride + (int64_t)st->params.H * kHeadDim;
   return true;
 }
 
@@ -715,7 +881,7 @@ bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mi
   const __nv_bfloat16* q = m + (st->q_ptr - arena_base);
   const __nv_bfloat16* kk = m + (st->k_ptr - arena_base);
   const __nv_bfloat16* v = m + (st->v_ptr - arena_base);
-  const int64_t T = st->params.T, H = st->params.H, rs = st->row_stride;
+  const int64_t T = (int64_t)st->params.B * st->params.T, H = st->params.H, rs = st->row_stride;   // rows of all sequences
   if (!aligned16(q) || !aligned16(kk) || !aligned16(v) || rs % 8) return false;
   CUtensorMap mq, mk, mv;
   if (!encode_map(&mq, true, q, kHeadDim, T, H, rs, kHeadDim, 64, kRows, false) ||
@@ -741,15 +907,15 @@ bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mi
 void attention_elide_copy(Plan& plan, size_t first) {
   PlanKernel& holder = plan.kernels[first];
   AttnState* st = static_cast<AttnState*>(holder.attn);
-  if (!st || !st->staged_out || !st->final_out || first + 4 >= plan.kernels.size()) return;
-  const PlanKernel& k6 = plan.kernels[first + 4];
+  if (!st || !st->staged_out || !st->final_out || first + st->chain - 1 >= plan.kernels.size()) return;
+  const PlanKernel& k6 = plan.kernels[first + st->chain - 1];      // the head merge, whose output the fused kernel writes
   if (k6.desc.operands[k6.chain.out_slot].base_kind != KB200_BASE_ARENA) return;     // a plan output must land where the caller looks
   const int64_t width = (int64_t)st->params.H * kHeadDim;
-  if (st->y->stride[0] != width) return;
+  if (st->y->stride[st->chain == 7 ? 1 : 0] != width) return;
   const Range y{st->final_out, st->final_out + st->out_elems};
   std::vector<std::pair<PlanKernel*, int>> redirect;
   bool rewritten = false;
-  for (size_t j = first + 5; j < plan.kernels.size() && !rewritten; ++j) {
+  for (size_t j = first + st->chain; j < plan.kernels.size() && !rewritten; ++j) {
     PlanKernel& k = plan.kernels[j];
     if (k.impl == IMPL_FUSED_AWAY) continue;
     std::vector<int> reads, writes;

@@ -139,7 +139,9 @@ bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mi
 const DevOperand* attention_output(const Plan& plan, size_t first, int64_t* elems);
 int launch_matmul(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void destroy_matmul(PlanKernel& k);
-bool attention_try_fuse(Plan& plan, size_t first);   // kernels first .. first+4
+int attention_try_fuse(Plan& plan, size_t first);    // plan kernels replaced from `first` on: 5, 7 or 0
+int attention_chain_length(const PlanKernel& k);
+bool attention_wants_bf16(const PlanKernel& k);
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void attention_destroy(PlanKernel& k);
 

@@ -455,8 +455,8 @@ static void fold_operand_copies(Plan& plan) {
   // A kernel the fused attention covers still stands for reads and writes the fused kernel makes
   // (Q, K, V; the merged output): only copies this pass folded itself may be ignored by the scans below.
   auto covered_by_attention = [&](size_t i) {
-    for (size_t back = 1; back <= 4 && back <= i; ++back)
-      if (plan.kernels[i - back].impl == IMPL_ATTN_FUSED) return true;
+    for (size_t back = 1; back <= 6 && back <= i; ++back)
+      if (plan.kernels[i - back].impl == IMPL_ATTN_FUSED) return (int)back < attention_chain_length(plan.kernels[i - back]);
     return false;
   };
   for (size_t j = 0; j < plan.kernels.size(); ++j) {
@@ -600,7 +600,7 @@ static int assign_shadows(Plan& plan) {
   std::vector<size_t> attention_readers;
   for (size_t ki = 0; ki < plan.kernels.size(); ++ki) {
     PlanKernel& k = plan.kernels[ki];
-    if (k.impl == IMPL_ATTN_FUSED && ki + 1 < plan.kernels.size() && plan.kernels[ki + 1].desc.precision == KB200_PREC_BF16) {
+    if (k.impl == IMPL_ATTN_FUSED && attention_wants_bf16(k)) {
       // the fused attention reads Q, K and V (views of one projection's output) as bf16 when that
       // projection can write them so
       Span x{nullptr, nullptr};
@@ -765,8 +765,10 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
   }
   // phase 2: fuse the attention chain where it matches
   if (rc == KB200_OK && plan.fuse_attention)
-    for (size_t i = 0; i + 4 < plan.kernels.size(); ++i)
-      if (attention_try_fuse(plan, i)) i += 4;
+    for (size_t i = 0; i + 4 < plan.kernels.size(); ++i) {
+      const int fused = attention_try_fuse(plan, i);
+      if (fused > 0) i += fused - 1;
+    }
   // phase 2b: matmuls read a K-contiguous B at its source instead of through the plan's transposing copy
   if (rc == KB200_OK && plan.fold_copies) fold_operand_copies(plan);
   // phase 3: BF16 matmuls read activations from the bf16 mirror when their producer can write it
