@@ -11,9 +11,13 @@ N(0, 0.02), inputs N(0, 1), seed 4 -- synthetic tensors of the benchmark's shape
 The block is compiled through the reference's own ``kiln.compile(model, inputs, device="cuda")``
 (frontend and passes from the pip --target copy under baseline/_ref) with this package
 registered as ``kiln.gpu``; where that copy is absent the plan those passes produce is loaded
-from kiln_b200/plans.  Six modules (own arena, static buffers and stream each) are kept in
-flight, the way a server overlaps requests, and the whole step of 64 sequences is captured as
-ONE CUDA graph (kiln_b200.runtime.StreamedBatch).
+from kiln_b200/plans.  It is compiled for a GROUP of eight sequences, ``[8, 1024, 768]``: the
+frontend flattens the leading dims of every Linear, so the projections are 8192-row matmuls (256-row
+tiles on SM pairs) and the fused attention kernel takes the sequence as one more grid dimension.
+Four such modules (own arena, static buffers and stream each) are kept in flight, the way a server
+overlaps requests, and the whole step of 64 sequences -- eight groups -- is captured as ONE CUDA
+graph (kiln_b200.runtime.StreamedBatch).  ``extras.single_sequence_graphs`` is the same step as 64
+one-sequence graphs over six modules.
 
 Timed regions, each K steps bracketed by barrier + synchronize, CUDA events, max over ranks:
   value   inputs already resident in HBM (device-to-device copies into the modules' inputs);
@@ -54,7 +58,9 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 SEQS, TOKENS, D, HEADS, SEED = 64, 1024, 768, 12, 4
-INFLIGHT = 6          # compiled modules kept in flight (own stream, arena and CUDA graph each); 6 reaches the host-link bound
+GROUP = 8             # sequences per compiled graph: the block is compiled for [8, 1024, 768] (eight independent sequences)
+INFLIGHT = 4          # compiled modules kept in flight (own stream, arena and CUDA graph each)
+HEAD_CASE = f"gpt2_block_b{GROUP}_t{TOKENS}"
 METRIC, UNIT = "gpt2_block_tokens_per_s", "tokens/s"
 REF_INSTALL = ROOT / "baseline" / "_ref"
 
@@ -256,7 +262,7 @@ def reference_arm(args, rank):
 def workload_config(precision, n):
     return {"workload": f"GPT-2-small block (d_model {D}, {HEADS} heads), {SEQS} sequences x {TOKENS} tokens per GPU "
                         f"per step, independent replicas", "sequences_per_gpu": SEQS, "tokens": TOKENS,
-            "precision": precision, "parallelism": f"replicas x{n}", "l2": "inputs larger than L2 (no flush)",
+            "sequences_per_graph": GROUP, "precision": precision, "parallelism": f"replicas x{n}", "l2": "inputs larger than L2 (no flush)",
             "seed": SEED}
 
 
@@ -394,46 +400,37 @@ NCU_DRAM_BYTES = {
 }
 
 
-def roofline_of(built, precision, iters=20):
-    """Roofline of the kernel with the largest share of the step's kernel time.
-
-    Two measurements, both CUDA events inside this run.  ``isolated_ms_per_launch``: the launch alone
-    on the GPU (20 launches per graph), as every row of ``per_kernel_ms``.  ``ms_per_launch``, which
-    ``achieved`` is computed from: 64 launches of that kernel spread over the six modules and their
-    streams exactly as in the timed step, time per launch = graph time / 64.  In the step a matmul
-    deliberately occupies only its plan's share of the SM pairs (wide tiles, several per pair, so that
-    each pair multiplies one tile while it stores the previous one) and six of them run side by side;
-    alone on the GPU the same launch leaves five sixths of the SMs idle, which says nothing about
-    the kernel."""
-    from kiln_b200.runtime import StreamedBatch
-
+def roofline_of(built, precision, iters=10):
+    """Per-launch CUDA-event times of every kernel of the module (each launch alone on the GPU, `iters`
+    launches per CUDA graph); roofline of the one with the largest share."""
     pk, pk_kind = peaks()
     exe, plan = built.exe, built.plan
     times = exe.profile_launches(exe.static_inputs[0], iters=iters)
     total = sum(ms for _, ms in times)
     i = max(range(len(times)), key=lambda j: times[j][1])
-    name, isolated_ms = times[i]
+    name, ms = times[i]
     ki = exe.program.launches[i].kernel_index
     flops, byts = kernel_flops(plan.kernels[ki])
-    if exe.impls[i] == "attention_fused":      # this launch stands for the whole five-kernel attention chain
-        flops = sum(kernel_flops(k)[0] for k in plan.kernels[ki:ki + 5])
-    in_step = StreamedBatch(built.executables).capture_launch(i, SEQS)
-    for _ in range(3):
-        in_step.run()
-    ms = time_region(None, in_step.run, 10) / 10 / SEQS
-    in_step.status()
+    if exe.impls[i] == "attention_fused":      # this launch stands for the whole attention chain of the plan
+        covered = 1
+        while i + covered < len(exe.impls) and exe.impls[i + covered] == "fused_away":
+            covered += 1
+        flops = sum(kernel_flops(k)[0] for k in plan.kernels[ki:ki + covered])
     if flops:
         achieved, unit, bound = flops / (ms * 1e-3) / 1e12, "TFLOP/s", "tensor"
         peak = pk["bf16_tflops"] if precision == "bf16" else pk["bf16_tflops"] / 2
         peak_note = f"{pk_kind} bf16 burst" + ("" if precision == "bf16" else " / 2 (tf32 and fp32 tensor rate)")
     else:
         achieved, unit, bound, peak, peak_note = byts / (ms * 1e-3) / 1e9, "GB/s", "hbm", pk["hbm_gbs"], f"{pk_kind} copy"
+    matmuls = {}
+    for j, (n, t) in enumerate(times):
+        f = kernel_flops(plan.kernels[exe.program.launches[j].kernel_index])[0]
+        if exe.impls[j] == "mm_tcgen05" and t > 0:
+            matmuls[n] = round(f / (t * 1e-3) / 1e12 / peak, 3)
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-            "traffic": NCU_DRAM_BYTES.get(f"{precision}:{name}") if TOKENS == 1024 else None,
+            "traffic": NCU_DRAM_BYTES.get(f"{precision}:b{GROUP}:{name}"),
             "traffic_unit": "bytes per launch (ncu dram read + write)", "kernel": f"{name} ({exe.impls[i]})", "ms_per_launch": ms,
-            "ms_per_launch_is": f"{SEQS} launches over {len(built.executables)} modules in flight, as in the timed step; graph time / {SEQS}",
-            "isolated_ms_per_launch": isolated_ms, "isolated_frac": (flops / (isolated_ms * 1e-3) / 1e12 / peak) if flops else None,
-            "share": isolated_ms / total, "peak_source": peak_note,
+            "share": ms / total, "peak_source": peak_note, "matmul_frac_of_peak": matmuls,
             "per_kernel_ms": {n: round(t, 5) for n, t in times if t > 0.0}}
 
 
@@ -514,32 +511,26 @@ def block_numbers(case, precision):
             "tokens_per_s": round(t / call_ms * 1e3), "built_from": graphed.source}
 
 
-def batched_graph_numbers(precision, batch=8):
-    """Eight 1024-token sequences as ONE compiled graph ([batch, tokens, d] through kiln.compile; the
-    projections are 8192-row matmuls) beside the same eight through StreamedBatch.  Needs the
-    reference's frontend (baseline/_ref)."""
+def single_sequence_step(precision, in_flight=6):
+    """The same 64 sequences as 64 one-sequence graphs ([1024, 768] modules, the reference's own test
+    model shape) over six modules in flight: what the step costs without batching sequences into
+    one graph.  Each plan is told how many share the GPU (wide tiles on its share of the SM pairs)."""
     from kiln_b200 import workloads as W
+    from kiln_b200.runtime import StreamedBatch
 
-    kiln = kiln_frontend()
-    if kiln is None:
-        return {"unavailable": "the reference's frontend is not installed under baseline/_ref"}
-    x = torch.stack([torch.from_numpy(W.block_input(SEED, TOKENS, index=i)) for i in range(batch)])
-    old = os.environ.get("KILN_GPU_PRECISION")
-    if precision == "bf16":
-        os.environ["KILN_GPU_PRECISION"] = "bf16"
-    try:
-        compiled = kiln.compile(W.batched_block_module(SEED, TOKENS), (x,), device="cuda", allow_tf32=precision != "fp32",
-                                cuda_graphs=False)
-    finally:
-        if precision == "bf16":
-            os.environ.pop("KILN_GPU_PRECISION", None) if old is None else os.environ.__setitem__("KILN_GPU_PRECISION", old)
-    exe = compiled._exe
-    exe.static_inputs[0].copy_(x)
-    best, _ = graph_times(exe.run_static, repeats=3, replays=20)
-    out = {"batch": batch, "tokens": TOKENS, "precision": precision, "kernels": len(compiled.graph.kernels),
-           "arena_mib": round(compiled.report.arena_bytes / 2**20, 1), "ms_per_call": round(best * 1e3, 3),
-           "tokens_per_s": round(batch * TOKENS / best), "impls": sorted(set(exe.impls))}
-    exe.close()
+    built = Built(f"gpt2_block_t{TOKENS}", precision)
+    for _ in range(in_flight - 1):
+        built.another()
+    dev_in = torch.stack([torch.from_numpy(W.block_input(SEED, TOKENS, index=i)) for i in range(SEQS)]).cuda()
+    dev_out = torch.empty_like(dev_in)
+    step = StreamedBatch(built.executables).capture(list(dev_in), list(dev_out))
+    for _ in range(3):
+        step.run()
+    ms = time_region(None, step.run, 10) / 10
+    step.status()
+    out = {"modules_in_flight": in_flight, "ms_per_step": round(ms, 4), "tokens_per_s": round(SEQS * TOKENS / (ms * 1e-3)),
+           "launches_per_step": SEQS * built.exe.device_launches}
+    built.close()
     return out
 
 
@@ -605,7 +596,7 @@ def extras(precision):
                             "frac_of_measured_peak": round(flops / best / 1e12 / tf32_peak, 3), "impl": built.exe.impls,
                             "built_from": built.source}
     built.close()
-    out["batched_graph"] = batched_graph_numbers(precision)
+    out["single_sequence_graphs"] = single_sequence_step(precision)
     out["block_t128_fp32"] = block_numbers("gpt2_block_t128", "fp32")
     out["block_t128_tf32"] = block_numbers("gpt2_block_t128", "tf32")      # the precision the reference's Triton arm is timed in
     if precision not in ("fp32", "tf32"):
@@ -645,10 +636,14 @@ def reference_triton_arm(args):
         except Exception as err:   # noqa: BLE001  (an extra: report, never fail the run)
             print(json.dumps(dict(tag, section=name, unavailable=f"{type(err).__name__}: {err}"[:300])), flush=True)
 
-    def block(tokens, seed, allow_tf32):
+    def block(tokens, seed, allow_tf32, batch=0):
         def run():
-            model = W.block_module(seed, tokens)
-            x = torch.from_numpy(W.block_input(seed, tokens, index=0))
+            if batch:
+                model = W.batched_block_module(seed, tokens)
+                x = torch.from_numpy(np.stack([W.block_input(seed, tokens, index=i) for i in range(batch)]))
+            else:
+                model = W.block_module(seed, tokens)
+                x = torch.from_numpy(W.block_input(seed, tokens, index=0))
             t0 = time.perf_counter()
             compiled = kiln.compile(model, (x,), device="cuda", allow_tf32=allow_tf32, autotune=args.autotune)
             compile_s = time.perf_counter() - t0
@@ -667,7 +662,7 @@ def reference_triton_arm(args):
                     compiled(xp).cpu()
                     lat.append((time.perf_counter() - t0) * 1e3)
             return {"precision": "tf32" if allow_tf32 else "fp32", "call_ms": round(call_ms, 4),
-                    "e2e_p50_ms": round(float(np.median(lat)), 4), "tokens_per_s": round(tokens / call_ms * 1e3),
+                    "e2e_p50_ms": round(float(np.median(lat)), 4), "tokens_per_s": round(max(1, batch) * tokens / call_ms * 1e3),
                     "rel_err_vs_eager": err, "compile_s": round(compile_s, 1), "autotune": bool(args.autotune)}
         return run
 
@@ -695,6 +690,7 @@ def reference_triton_arm(args):
     section("mlp_2048_tf32", kernel_case("mlp_2048", True, args.autotune, flops=2 * 2 * 2048 * 768 * 3072))
     for case, byts in (("bias_gelu_2048x3072", 50343936), ("layernorm_2048x768", 12589056), ("softmax_12x512x512", 25165824)):
         section(case, kernel_case(case, False, False, byts=byts))
+    section(f"block_b{GROUP}_t1024", block(1024, SEED, True, batch=GROUP))
 
 
 def reference_triton_extra(budget_s=300):
@@ -744,39 +740,41 @@ def gpu_arm(args, dist, rank, world, local):
     torch.cuda.set_device(local)
     cpulist = bind_to_the_gpu_s_cores(local)
     precision = args.precision
-    host = [torch.from_numpy(W.block_input(SEED, TOKENS, index=rank * SEQS + i)).pin_memory() for i in range(SEQS)]
-    dev_in = torch.stack([h.cuda(non_blocking=True) for h in host])
-    dev_out = torch.empty_like(dev_in)
-    host_out = [torch.empty(TOKENS, D).pin_memory() for _ in range(SEQS)]
+    groups = SEQS // GROUP
+    host = [torch.from_numpy(np.stack([W.block_input(SEED, TOKENS, index=rank * SEQS + g * GROUP + i) for i in range(GROUP)])).pin_memory()
+            for g in range(groups)]
+    dev_in = [h.cuda(non_blocking=True) for h in host]
+    dev_out = [torch.empty_like(t) for t in dev_in]
+    host_out = [torch.empty(GROUP, TOKENS, D).pin_memory() for _ in range(groups)]
     torch.cuda.synchronize()
 
     # INFLIGHT compiled modules (own arena, static buffers and stream each) run round-robin, as a server
-    # keeps several requests in flight: kernels of one sequence fill the SMs another leaves idle, and
-    # copies overlap kernels.  A whole step of 64 sequences is one CUDA graph, so a busy host does not
-    # starve the GPU of launches.
-    built = Built(f"gpt2_block_t{TOKENS}", precision)
+    # keeps several requests in flight: copies of one group overlap kernels of another.  A whole step of
+    # 64 sequences is one CUDA graph, so a busy host does not starve the GPU of launches.  Every kernel
+    # of an eight-sequence graph is large enough for the whole GPU, so the plans are not told to share it.
+    built = Built(HEAD_CASE, precision)
     for _ in range(INFLIGHT - 1):
         built.another()
     exes, exe = built.executables, built.exe
-    resident = StreamedBatch(exes).capture(list(dev_in), list(dev_out))
+    resident = StreamedBatch(exes, concurrency=1).capture(dev_in, dev_out)
     for _ in range(args.warmup):
         resident.run()
     with ClockSampler(local) as clocks:
         ms = time_region(dist, resident.run, args.steps)
     resident.status()
     # end to end: the same step with pinned host tensors as sources and sinks (201 MB each way per step)
-    e2e = StreamedBatch(exes).capture(host, host_out)
+    e2e = StreamedBatch(exes, concurrency=1).capture(host, host_out)
     for _ in range(max(1, args.warmup // 2)):
         e2e.run()
     ms_e2e = time_region(dist, e2e.run, args.steps)
     e2e.status()
     # ... and the same copies with no kernels between them: the host link's share of that step
-    copies = StreamedBatch(exes).capture(host, host_out, kernels=False)
+    copies = StreamedBatch(exes, concurrency=1).capture(host, host_out, kernels=False)
     copies.run()
     ms_copies = time_region(dist, copies.run, args.steps)
     # strong scaling (BASELINE config 4): 64 sequences in total, 64 / world per GPU
-    share = max(1, SEQS // world)
-    strong = StreamedBatch(exes).capture(list(dev_in[:share]), list(dev_out[:share]))
+    share = max(1, groups // world)
+    strong = StreamedBatch(exes, concurrency=1).capture(dev_in[:share], dev_out[:share])
     for _ in range(args.warmup):
         strong.run()
     ms_strong = time_region(dist, strong.run, args.steps)
@@ -793,15 +791,16 @@ def gpu_arm(args, dist, rank, world, local):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * SEQS * TOKENS * D * 4,
                 "d2h_bytes_per_step": world * SEQS * TOKENS * D * 4, "ms_per_step": ms_e2e / args.steps,
                 "copy_only_ms": ms_copies / args.steps, "modules_in_flight": INFLIGHT, "host_cores_near_gpu": cpulist},
-        "gpu_launches": world * args.steps * SEQS * exe.device_launches, "modules_in_flight": INFLIGHT,
+        "gpu_launches": world * args.steps * groups * exe.device_launches, "modules_in_flight": INFLIGHT,
+        "sequences_per_graph": GROUP,
         "clocks": clocks.summary(),
         "impls": dict(zip(exe.launch_names, exe.impls)),
         "built_from": built.source,
     }
     line["roofline"] = roofline_of(built, precision)
-    line["extras"] = {"strong_scaling": {"sequences_total": share * world, "sequences_per_gpu": share,
+    line["extras"] = {"strong_scaling": {"sequences_total": share * GROUP * world, "sequences_per_gpu": share * GROUP,
                                          "ms_per_step": ms_strong / args.steps,
-                                         "tokens_per_s": share * world * TOKENS * args.steps / (ms_strong * 1e-3)}}
+                                         "tokens_per_s": share * GROUP * world * TOKENS * args.steps / (ms_strong * 1e-3)}}
     if world == 1:
         v, done, cores = cpu_block_tokens_per_s(seconds_budget=12.0)
         v1, done1, _ = cpu_block_tokens_per_s(seconds_budget=6.0, threads=1)

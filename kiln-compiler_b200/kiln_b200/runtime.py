@@ -335,7 +335,9 @@ class StreamedBatch:
     (kiln/gpu/runtime.py:181-217).
     """
 
-    def __init__(self, executables):
+    def __init__(self, executables, concurrency=None):
+        """``concurrency``: what the plans are told about how many of them share the GPU (default: their
+        number; 1 when every kernel of a module is large enough for the whole GPU by itself)."""
         if not executables:
             raise ValueError("StreamedBatch needs at least one executable")
         for e in executables:
@@ -343,7 +345,7 @@ class StreamedBatch:
                 raise ValueError("StreamedBatch captures the launches itself: build the executables with cuda_graphs=False")
         self.executables = list(executables)
         for e in self.executables:
-            e.set_concurrency(len(self.executables))
+            e.set_concurrency(len(self.executables) if concurrency is None else concurrency)
         self.device = executables[0].device
         self.streams = [torch.cuda.Stream(device=self.device) for _ in executables]
         self.graph = None

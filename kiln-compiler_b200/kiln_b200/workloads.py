@@ -193,7 +193,7 @@ def batched_block_module(seed, t, d=768, heads=12):
 # The benchmark configurations by name: tensors, modules, stored launch plans
 # ---------------------------------------------------------------------------------------------
 
-BENCHMARK_PREFIXES = ("gpt2_block_t", "mlp_2048", "linear_", "bias_gelu_", "layernorm_2048", "softmax_12x")
+BENCHMARK_PREFIXES = ("gpt2_block_t", "gpt2_block_b", "mlp_2048", "linear_", "bias_gelu_", "layernorm_2048", "softmax_12x")
 PLAN_DIR = __import__("pathlib").Path(__file__).resolve().parent / "plans"
 
 
@@ -215,8 +215,19 @@ def stored_plan(case):
     return json.loads((PLAN_DIR / f"{case}.json").read_text())
 
 
+def batched_case(case):
+    """(batch, tokens) of a ``gpt2_block_b<batch>_t<tokens>`` case name, or None."""
+    import re
+
+    m = re.fullmatch(r"gpt2_block_b(\d+)_t(\d+)", case)
+    return (int(m.group(1)), int(m.group(2))) if m else None
+
+
 def case_tensors(case):
     """(parameters by module path, input array) of a benchmark configuration."""
+    if batched_case(case):
+        batch, t = batched_case(case)
+        return block_params(4, t), np.stack([block_input(4, t, index=i) for i in range(batch)])
     if case.startswith("gpt2_block_t"):
         t = int(case[len("gpt2_block_t"):])
         seed = 0 if t == 128 else 4
@@ -244,6 +255,8 @@ def case_module(case):
 
     params, x = case_tensors(case)
     state = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in params.items()}
+    if batched_case(case):
+        return batched_block_module(4, batched_case(case)[1]), torch.from_numpy(x)
     if case.startswith("gpt2_block_t"):
         t = int(case[len("gpt2_block_t"):])
         return block_module(0 if t == 128 else 4, t), torch.from_numpy(x)

@@ -217,6 +217,10 @@ def main():
         model.load_state_dict({k: torch.from_numpy(v) for k, v in params.items()})
         big_case(f"gpt2_block_t{t}", model, W.block_input(0 if t == 128 else 4, t), step)
 
+    # the benchmark's step: eight 1024-token sequences as one [8, 1024, 768] graph
+    _, xb = W.case_tensors("gpt2_block_b8_t1024")
+    big_case("gpt2_block_b8_t1024", W.batched_block_module(4, 1024), xb, 512)
+
     mp = W.mlp_params()
     mlp = torch.nn.Sequential(torch.nn.Linear(768, 3072), torch.nn.GELU(approximate="tanh"),
                               torch.nn.Linear(3072, 768)).eval()

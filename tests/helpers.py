@@ -27,7 +27,10 @@ def small_cases():
 
 
 def big_cases():
-    return [c for c in all_cases() if is_big(c)]
+    """The benchmark configurations the parity tests evaluate with the NumPy oracle (the batched block
+    of the benchmark step is 8 x 1024 tokens: the oracle checks the batched chain on the small
+    `batched_block` case, and the big one is compared with its stored eager result only)."""
+    return [c for c in all_cases() if is_big(c) and not W.batched_case(c)]
 
 
 def load_plan(case):

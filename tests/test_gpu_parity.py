@@ -390,3 +390,16 @@ def test_a_wait_that_runs_out_is_reported_and_the_plan_stays_usable():
     exe.status()
     np.testing.assert_allclose(again[0].cpu().numpy(), outs[0], rtol=0, atol=0)
     np.testing.assert_allclose(again[0].cpu().numpy(), expected["out"][0], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_the_benchmark_s_eight_sequence_graph_matches_the_stored_eager_result(precision):
+    """[8, 1024, 768] through the stored plan of the benchmark step: 8192-row matmuls on SM pairs, the
+    attention chain of a batched graph fused; against the float64 eager result stored with the plan."""
+    from gpu_helpers import run_case
+
+    case = "gpt2_block_b8_t1024"
+    exe, outs, (plan, inputs, consts, expected) = run_case(case, precision)
+    assert "attention_fused" in exe.impls and exe.impls.count("fused_away") == 6
+    got = subsample(outs[0], expected["step"][0])
+    assert scale_relative_error(got, expected["sub"][0]) <= REL_TOL[precision], (precision, exe.impls)
