@@ -194,12 +194,24 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
  * KB200_OPT_CONCURRENCY (default 1): how many plans the caller keeps in flight on this GPU at the
  * same time (a server overlapping requests on several streams).  Only a hint for the tile
  * heuristics, which the reference leaves to its autotuner (kiln/gpu/codegen.py:563-598): with n > 1 a
- * matmul counts on 1/n of the SMs and prefers fewer, wider tiles.  Results do not depend on it. */
+ * matmul counts on 1/n of the SMs and prefers fewer, wider tiles.  Results do not depend on it.
+ * KB200_OPT_ABSORB_ELEMENTWISE (default 1): an elementwise kernel that directly follows a tensor-core
+ * matmul and only continues it -- its one arena input is exactly the matmul's output, which nothing
+ * else reads -- runs as the tail of the matmul's epilogue, and the matmul writes that kernel's output.
+ * This is what the reference's plans contain behind every Linear on a [batch, tokens, d] input: its
+ * fusion pass cannot take the activation or the residual add into the matmul's kernel across the
+ * reshape between them (kiln/passes/fusion.py:26-35).  0 launches every planned kernel.
+ * KB200_OPT_MIRROR_ONLY (default 1, BF16 mode): a LayerNorm or matmul whose output is read only by
+ * kernels that take its bf16 mirror (tensor-core matmul operands, the fused attention) does not store
+ * the float32 values: that arena region then holds stale data, which no planned kernel reads.  0 stores
+ * both, for a caller that inspects intermediate buffers. */
 typedef enum kb200_option {
   KB200_OPT_FUSE_ATTENTION = 1,
   KB200_OPT_DEPENDENT_LAUNCH = 2,
   KB200_OPT_FOLD_OPERAND_COPIES = 3,
-  KB200_OPT_CONCURRENCY = 4
+  KB200_OPT_CONCURRENCY = 4,
+  KB200_OPT_ABSORB_ELEMENTWISE = 5,
+  KB200_OPT_MIRROR_ONLY = 6
 } kb200_option;
 int kb200_plan_set_option(kb200_plan* plan, int option, int value);
 

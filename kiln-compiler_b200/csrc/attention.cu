@@ -491,6 +491,7 @@ void io_slots(const PlanKernel& k, std::vector<int>* reads, std::vector<int>* wr
     if (d.tape[t].opcode == KB200_OP_LOAD) reads->push_back(d.tape[t].a);
     if (d.tape[t].opcode == KB200_OP_STORE) writes->push_back(d.tape[t].b);
   }
+  for (int slot = d.n_operands; slot < k.n_ops; ++slot) reads->push_back(slot);   // side operands of an absorbed kernel
 }
 
 Range operand_range(const PlanKernel& k, int slot) {
@@ -943,6 +944,8 @@ void attention_elide_copy(Plan& plan, size_t first) {
   st->final_out = nullptr;
   holder.launches = 1;
 }
+
+bool attention_reads_mirror(const PlanKernel& k) { return k.attn && static_cast<const AttnState*>(k.attn)->bf16; }
 
 void attention_set_shadow(PlanKernel& k, void* shadow_out) {
   if (k.attn) static_cast<AttnState*>(k.attn)->params.out16 = static_cast<__nv_bfloat16*>(shadow_out);

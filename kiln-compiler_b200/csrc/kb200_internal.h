@@ -76,6 +76,7 @@ struct PlanKernel {
   int impl = 0;
   int launches = 1;
   DevOperand ops[KB200_MAX_OPERANDS];
+  int n_ops = 0;        // operand slots in use: the descriptor's, then the side operands of an absorbed kernel (below)
   DevTape tape;
   Chain chain;          // valid when the impl uses it
   bool has_chain = false;
@@ -95,6 +96,12 @@ struct PlanKernel {
   void* shadow_out = nullptr;     // producer side: mirror address of this kernel's (single) output, or null
   const void* a_shadow = nullptr; // consumer side: mirror address of operand A / B, or null (convert per launch)
   const void* b_shadow = nullptr;
+  bool mirror_only = false;       // producer side: every reader of the output takes the mirror, the float32 store is dropped
+  // An elementwise kernel that only continues the matmul in front of it (the activation or the residual
+  // add behind a Linear on a [batch, tokens, d] input, which the reference's fusion pass cannot put into
+  // the matmul's kernel because a reshape sits between them, kiln/passes/fusion.py:26-35) runs as the
+  // tail of that matmul's epilogue chain: the matmul writes the elementwise kernel's output.
+  int absorbed_by = -1;           // on the elementwise kernel: index of the matmul that runs it
 };
 
 struct Plan {
@@ -106,6 +113,8 @@ struct Plan {
   bool fuse_attention = true;    // replace the five-kernel attention chain by the fused kernel when it matches
   bool fold_copies = true;       // a matmul reads a K-contiguous B at its source; the plan's transposing copy is not launched
   bool pdl = true;               // programmatic dependent launch: a kernel's start-up overlaps its predecessor's tail
+  bool absorb_elementwise = true; // a tensor-core matmul also runs the elementwise kernel that only continues it
+  bool mirror_only = true;       // BF16 mode: an output that only mirror readers consume is not stored as float32
   int concurrency = 1;           // plans the caller keeps in flight on this GPU at once (tile heuristics assume their share of the SMs)
   void* arena16 = nullptr;       // bf16 mirror of the arena (library-owned, only when some matmul reads it)
   uint64_t arena16_bytes = 0;
@@ -142,6 +151,8 @@ void destroy_matmul(PlanKernel& k);
 int attention_try_fuse(Plan& plan, size_t first);    // plan kernels replaced from `first` on: 5, 7 or 0
 int attention_chain_length(const PlanKernel& k);
 bool attention_wants_bf16(const PlanKernel& k);
+bool attention_reads_mirror(const PlanKernel& k);
+bool tc_eligible(const PlanKernel& k);
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void attention_destroy(PlanKernel& k);
 

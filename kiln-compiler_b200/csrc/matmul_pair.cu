@@ -89,6 +89,7 @@ struct PairParams {
   // epilogue
   int64_t M, N;
   __nv_bfloat16* out16;  // bf16 mirror of the output (same strides), or null
+  int store32;           // 0: only the mirror is stored (every reader of this output takes the mirror)
   int slots, slot_bytes;
   int res_step;          // chain step whose operand arrives by bulk tensor load, or -1
   int res_batched;       // that operand has one matrix per batch entry (else the same for all)
@@ -366,7 +367,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     uint8_t* const slot0_ptr = smem_raw + (slot0 - raw);
     const uint32_t res0 = smem_u32(&bars[kBarRes + e * kPairMaxSlots]);
     const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
-    const bool has_res = p.res_step >= 0, with16 = p.out16 != nullptr;
+    const bool has_res = p.res_step >= 0, with16 = p.out16 != nullptr, with32 = p.store32 != 0;
     const int allowed = has_res ? slots - 2 : slots - 1;   // store groups that may be in flight when a slot is reused
     // The first per-column operand of the chain (a bias) is fetched for the whole tile before its
     // accumulator is ready: lane l holds column l of each of this warp's blocks, and the chain takes
@@ -389,7 +390,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
     };
     // The fused chain on one 32 x 32 block held a lane per row (v[q] = column n + q of this lane's row).
-    auto run_chain = [&](float (&v)[32], int j, int n, int batch, const uint8_t* sf, int res_slot) {
+    auto run_chain = [&](float (&v)[32], int j, int n, int batch, const uint8_t* sf, int res_slot, const float4* col_smem = nullptr) {
       for (int s = 0; s < p.n_steps; ++s) {
         const PairStep st = p.steps[s];
         float side[32];
@@ -400,6 +401,12 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const float4 t = *reinterpret_cast<const float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4));
+            side[4 * q] = t.x; side[4 * q + 1] = t.y; side[4 * q + 2] = t.z; side[4 * q + 3] = t.w;
+          }
+        } else if (s == col_step && col_smem != nullptr) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {        // every lane reads the same 16 bytes: a broadcast
+            const float4 t = col_smem[q];
             side[4 * q] = t.x; side[4 * q + 1] = t.y; side[4 * q + 2] = t.z; side[4 * q + 3] = t.w;
           }
         } else if (s == col_step) {
@@ -431,10 +438,14 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int n0 = tn_i * p.bn;
       const bool rows_ok = m_first < p.M;
       if (col_step >= 0 && rows_ok) {
-        const float* src = p.steps[col_step].ptr + (int64_t)batch * p.steps[col_step].batch_stride + n0 + half * 32 + lane;
+        const float* src = p.steps[col_step].ptr + (int64_t)batch * p.steps[col_step].batch_stride + n0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (j < nblk) col_pre[j] = n0 + half * 32 + 64 * j + lane < p.N ? __ldg(src + 64 * j) : 0.0f;
+        for (int j = 0; j < 4; ++j) {
+          // block j of this warp: alternate 32-column blocks with a matrix operand, else the halves of
+          // alternate 64-column strips
+          const int c = has_res ? half * 32 + 64 * j + lane : half * 64 + 128 * (j >> 1) + 32 * (j & 1) + lane;
+          if (j < nblk) col_pre[j] = n0 + c < p.N ? __ldg(src + c) : 0.0f;
+        }
       }
       // the first block's residual is requested before the accumulator is ready
       if (has_res && !res_ready && rows_ok && n0 + half * 32 < p.N) {
@@ -451,14 +462,16 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #ifdef KB200_TRACE
       if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-      // Without a matrix operand two blocks are in flight per pass (both of this warp's staging
-      // slots): the fixed latencies of a pass -- tensor-memory load, the wait for the slots' last
-      // stores, the proxy fence, the store issue -- are paid once per 64 columns.
+      // Without a matrix operand a pass takes a strip of 64 columns (the warps of a quadrant take
+      // alternate strips): the fixed latencies of a pass -- tensor-memory load, the wait for the
+      // staging area's last stores, the proxy fence, the store issue -- are paid once per strip, and
+      // the strip's bf16 mirror is one box of 128-byte rows.  Staging area of a warp: two float32
+      // blocks (unless only the mirror is stored), then the bf16 box.
       for (int j = 0; !has_res && j < nblk; j += 2) {
-        const int c = half * 32 + 64 * j;
+        const int c = half * 64 + 64 * j;
         const int n = n0 + c;
         if (!rows_ok || n >= p.N) break;             // uniform across the warp
-        const bool two = j + 1 < nblk && n + 64 < p.N;
+        const bool two = n + 32 < p.N;
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c);
         float v[32], w[32];
 #ifdef KB200_TRACE
@@ -467,32 +480,48 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int q = 0; q < 32; ++q) v[q] = w[q] = 1.0f;
         } else
 #endif
-        if (two) tmem_ld32x2(t_addr, t_addr + 64, v, w);
-        else tmem_ld32(t_addr, v);
+        if (two) {
+          tmem_ld32x2(t_addr, t_addr + 32, v, w);
+        } else {
+          tmem_ld32(t_addr, v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) w[q] = 0.0f;
+        }
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-        uint8_t* const sa = slot0_ptr;
-        uint8_t* const sb = slot0_ptr + slot_bytes;
-        run_chain(v, j, n, batch, sa, 0);
-        if (two) run_chain(w, j + 1, n + 64, batch, sb, 1);
-#ifdef KB200_TRACE
-        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
-#endif
-        // the slots' last bulk stores had the load and the arithmetic above to finish reading them
+        // the staging area's last bulk stores had the load above to finish reading it
         if (lane == 0) store_wait_read(0);
         __syncwarp();
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
+        // the strip's per-column operand goes through the (still free) staging area: written once by
+        // the lanes that fetched it, read back as broadcasts
+        float* const col_smem = reinterpret_cast<float*>(slot0_ptr);
+        if (col_step >= 0) {
+          col_smem[lane] = j == 0 ? col_pre[0] : col_pre[2];
+          col_smem[32 + lane] = j == 0 ? col_pre[1] : col_pre[3];
+          __syncwarp();
+        }
+        run_chain(v, j, n, batch, slot0_ptr, 0, reinterpret_cast<const float4*>(col_smem));
+        if (two) run_chain(w, j + 1, n + 32, batch, slot0_ptr, 0, reinterpret_cast<const float4*>(col_smem + 32));
+        __syncwarp();
+#ifdef KB200_TRACE
+        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
+#endif
+        uint8_t* const sh = slot0_ptr + (with32 ? 8192 : 0);
 #ifdef KB200_TRACE
         if (!(p.debug & 2)) {
 #endif
-        stage_rows(sa, sa + 4096, v, lane, with16);
-        if (two) stage_rows(sb, sb + 4096, w, lane, with16);
+        if (with32) {
+          stage_rows(slot0_ptr, nullptr, v, lane, false);
+          if (two) stage_rows(slot0_ptr + 4096, nullptr, w, lane, false);
+        }
+        if (with16) stage_rows_bf16x64(sh, v, w, lane);
         fence_async_smem();
 #ifdef KB200_TRACE
-        } else if (v[0] + w[1] == 12345.0f) sa[lane] = 1;
+        } else if (v[0] + w[1] == 12345.0f) slot0_ptr[lane] = 1;
 #endif
         __syncwarp();
 #ifdef KB200_TRACE
@@ -500,12 +529,11 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #else
         if (lane == 0) {
 #endif
-          tma_store_3d(&tma_out, slot0, n, m_first, batch);
-          if (with16) tma_store_3d(&tma_out16, slot0 + 4096, n, m_first, batch);
-          if (two) {
-            tma_store_3d(&tma_out, slot0 + (uint32_t)slot_bytes, n + 64, m_first, batch);
-            if (with16) tma_store_3d(&tma_out16, slot0 + (uint32_t)slot_bytes + 4096, n + 64, m_first, batch);
+          if (with32) {
+            tma_store_3d(&tma_out, slot0, n, m_first, batch);
+            if (two) tma_store_3d(&tma_out, slot0 + 4096, n + 32, m_first, batch);
           }
+          if (with16) tma_store_3d(&tma_out16, slot0 + (with32 ? 8192u : 0u), n, m_first, batch);
           tma_store_commit();
         }
 #ifdef KB200_TRACE
@@ -539,12 +567,12 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-        stage_rows(sf, sf + 4096, v, lane, with16);
+        stage_rows(sf, sf + 4096, v, lane, with16, with32);
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
           const uint32_t src = slot0 + (uint32_t)(slot * slot_bytes);
-          tma_store_3d(&tma_out, src, n, m_first, batch);
+          if (with32) tma_store_3d(&tma_out, src, n, m_first, batch);
           if (with16) tma_store_3d(&tma_out16, src + 4096, n, m_first, batch);
           tma_store_commit();
         }
@@ -697,10 +725,15 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
     }
   }
   while (bn > 128 && bn / 2 >= k.N) bn /= 2;
+  // Staging per epilogue warp.  With a matrix operand: rotating slots of one float32 block and its
+  // bf16 copy.  Without: one area for a 64-column strip, two float32 blocks (unless only the mirror is
+  // stored) and the strip's bf16 box.
+  const bool store32 = !(k.mirror_only && out16 != nullptr);
+  const int slot_bytes_wanted = p.res_step >= 0 ? (out16 ? 4096 + 2048 : 4096) : (store32 ? 8192 : 0) + (out16 ? 4096 : 0);
+  const int min_slots = p.res_step >= 0 ? 2 : 1;
   // two slabs per step where the ring still has three stages beside the staging slots
-  const int slot_bytes_wanted = out16 ? 4096 + 2048 : 4096;
   if (kps == 0)
-    kps = bn <= 128 && slabs >= 4 && 3 * 2 * (kPairATileBytes + bn / 2 * 128) + kPairEpiWarps * 2 * slot_bytes_wanted + 1024 <= kPairSmemCeiling ? 2 : 1;
+    kps = bn <= 128 && slabs >= 4 && 3 * 2 * (kPairATileBytes + bn / 2 * 128) + kPairEpiWarps * min_slots * slot_bytes_wanted + 1024 <= kPairSmemCeiling ? 2 : 1;
   p.bn = bn;
   p.half_bn = bn / 2;
   p.slab_k = slab_k;
@@ -735,8 +768,9 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
   p.M = k.M;
   p.N = k.N;
   p.out16 = out16;
+  p.store32 = store32 ? 1 : 0;
   p.slot_bytes = slot_bytes_wanted;
-  p.slots = (out16 || p.res_step < 0) ? 2 : 3;     // the third slot lets a residual fly one block ahead
+  p.slots = p.res_step < 0 ? 1 : (out16 ? 2 : 3);   // the third slot lets a residual fly one block ahead
   const int stage_bytes = kps * (kPairATileBytes + p.half_bn * 128);
   // a third slot only where it does not cost the ring its third stage
   if (p.slots == 3 && 3 * stage_bytes + kPairEpiWarps * 3 * p.slot_bytes + 1024 > kPairSmemCeiling) p.slots = 2;
@@ -766,7 +800,7 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
   if (ok) ok = encode_map_store(&st->map_out, false, O.ptr, k.N, k.M, k.batch, O.stride[1], O.stride[0]);
   st->map_out16 = st->map_out;
   st->map_res = st->map_out;
-  if (ok && out16) ok = encode_map_store(&st->map_out16, true, out16, k.N, k.M, k.batch, O.stride[1], O.stride[0]);
+  if (ok && out16) ok = encode_map_store(&st->map_out16, true, out16, k.N, k.M, k.batch, O.stride[1], O.stride[0], p.res_step < 0);
   if (ok && res) ok = encode_map_store(&st->map_res, false, res->ptr, k.N, k.M, p.res_batched ? k.batch : 1, res->stride[1], res->stride[0]);
   if (!ok) { delete st; return KB200_OK; }
   st->kernel = ops.bf16 ? (kps == 2 ? mm_pair_kernel<true, 2> : mm_pair_kernel<true, 1>)

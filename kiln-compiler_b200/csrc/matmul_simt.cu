@@ -153,8 +153,8 @@ void fill_matmul_params(const PlanKernel& k, MatmulParams* p) {
   p->K = k.K;
   p->a_slot = d.a_slot;
   p->b_slot = d.b_slot;
-  p->n_operands = d.n_operands;
-  for (int o = 0; o < d.n_operands; ++o) p->ops[o] = k.ops[o];
+  p->n_operands = k.n_ops;
+  for (int o = 0; o < k.n_ops; ++o) p->ops[o] = k.ops[o];
   p->has_chain = k.has_chain ? 1 : 0;
   p->chain = k.chain;
   p->tape = k.tape;

@@ -441,6 +441,7 @@ void reads_and_writes(const PlanKernel& k, std::vector<int>* reads, std::vector<
     if (d.tape[t].opcode == KB200_OP_LOAD) reads->push_back(d.tape[t].a);
     if (d.tape[t].opcode == KB200_OP_STORE) writes->push_back(d.tape[t].b);
   }
+  for (int slot = d.n_operands; slot < k.n_ops; ++slot) reads->push_back(slot);   // side operands of an absorbed kernel
 }
 bool spans_overlap(const Span& a, const Span& b) { return a.lo < b.hi && b.lo < a.hi; }
 }  // namespace
@@ -556,6 +557,197 @@ static void fold_operand_copies(Plan& plan) {
   }
 }
 
+
+// An elementwise kernel that directly follows a tensor-core matmul and only continues it becomes the
+// tail of the matmul's epilogue chain.  The conditions: the matmul's accumulator chain and the
+// elementwise kernel's chain fit one chain; exactly one input of the elementwise kernel is the
+// matmul's whole output, element for element; its other inputs and its output are linear in the
+// matmul's (row, column); nothing else reads the matmul's output before it is rewritten; and the
+// output does not lie over anything the matmul still reads (variants (a) and (b) below).  The plan
+// (kernel list, offsets) is untouched: the elementwise kernel stays in it and launches nothing.
+static void absorb_elementwise(Plan& plan) {
+  // from the last matmul to the first: what a later matmul no longer writes (its own output, once it
+  // has taken over an elementwise kernel's) is known when an earlier one looks at its readers
+  for (size_t j = plan.kernels.size() > 1 ? plan.kernels.size() - 1 : 0; j-- > 0;) {
+    PlanKernel& m = plan.kernels[j];
+    PlanKernel& e = plan.kernels[j + 1];
+    if (m.impl != IMPL_MM_TC || !m.has_chain || m.chain.first_slot != -1 || m.batch != 1) continue;
+    if (e.desc.kclass != KB200_K_ELEMENTWISE || e.impl == IMPL_FUSED_AWAY || !e.has_chain || e.chain.first_slot < 0) continue;
+    if (numel_of(e.desc) != m.M * m.N || m.chain.n + e.chain.n > kMaxChain) continue;
+    if (m.desc.operands[m.chain.out_slot].base_kind != KB200_BASE_ARENA) continue;   // a plan output must be written
+    {
+      std::vector<int> reads, writes;
+      reads_and_writes(e, &reads, &writes);
+      if (writes.size() != 1) continue;
+    }
+    const DevOperand mo = m.ops[m.chain.out_slot];
+    if (mo.stride[2] != 1 || mo.stride[1] != m.N) continue;
+    const Span mo_span = span_of(m, m.chain.out_slot);
+    // An operand of the elementwise kernel as a function of the matmul's (row, column): element
+    // `delta` of the flat iteration space is row delta / N, column delta % N.
+    const kb200_kernel_desc& ed = e.desc;
+    auto offset_of = [&](const DevOperand& o, int64_t delta) {
+      int64_t off = 0;
+      for (int d = ed.iter_rank - 1; d >= 0; --d) {
+        off += (delta % ed.iter_shape[d]) * o.stride[d];
+        delta /= ed.iter_shape[d];
+      }
+      return off;
+    };
+    auto linear = [&](const DevOperand& o, int64_t* s_m, int64_t* s_n) {
+      *s_n = m.N > 1 ? offset_of(o, 1) : 0;
+      *s_m = m.M > 1 ? offset_of(o, m.N) : 0;
+      // every iteration dim must then agree with (s_m, s_n): a dim inside a row, a dim of whole rows, or
+      // one that runs across row ends (contiguous dims the host collapsed into one)
+      int64_t inner = 1;
+      for (int d = ed.iter_rank - 1; d >= 0; --d) {
+        const int64_t sh = ed.iter_shape[d], st = o.stride[d];
+        if (sh > 1) {
+          if (inner >= m.N) {
+            if (inner % m.N || st != inner / m.N * *s_m) return false;
+          } else if (inner * sh <= m.N) {
+            if (m.N % (inner * sh) || st != inner * *s_n) return false;
+          } else {
+            if (m.N % inner || (inner * sh) % m.N || st != inner * *s_n || *s_m != m.N / inner * st) return false;
+          }
+        }
+        inner *= sh;
+      }
+      return true;
+    };
+    auto is_matmul_output = [&](int slot) {
+      int64_t s_m, s_n;
+      return e.ops[slot].ptr == mo.ptr && linear(e.ops[slot], &s_m, &s_n) && s_n == 1 && s_m == m.N;
+    };
+    // where the matmul's value enters the elementwise chain: as its first value, or as the other
+    // argument of its first step
+    Chain tail = e.chain;
+    if (!is_matmul_output(tail.first_slot)) {
+      if (tail.n < 1 || tail.steps[0].slot < 0 || !is_matmul_output(tail.steps[0].slot)) continue;
+      int swapped;
+      switch (tail.steps[0].op) {
+        case CH_ADD: case CH_MUL: case CH_MAX: case CH_MIN: swapped = tail.steps[0].op; break;
+        case CH_SUB: swapped = CH_RSUB; break;
+        case CH_RSUB: swapped = CH_SUB; break;
+        case CH_DIV: swapped = CH_RDIV; break;
+        case CH_RDIV: swapped = CH_DIV; break;
+        default: swapped = -1; break;
+      }
+      if (swapped < 0) continue;
+      tail.steps[0].op = swapped;
+      tail.steps[0].slot = tail.first_slot;
+    }
+    bool ok = true;
+    for (int s = 0; s < tail.n; ++s)
+      if (tail.steps[s].slot >= 0 && spans_overlap(span_of(e, tail.steps[s].slot), mo_span)) ok = false;   // reads it a second time
+    // nobody else reads the matmul's output before it is rewritten
+    bool rewritten = false;
+    for (size_t i = j + 2; i < plan.kernels.size() && ok && !rewritten; ++i) {
+      const PlanKernel& k = plan.kernels[i];
+      if (k.impl == IMPL_FUSED_AWAY && k.absorbed_by < 0) {
+        // folded copies read nothing; kernels the fused attention covers stand for its reads and writes
+        bool covered = false;
+        for (size_t back = 1; back <= 6 && back <= i && !covered; ++back)
+          covered = plan.kernels[i - back].impl == IMPL_ATTN_FUSED && (int)back < attention_chain_length(plan.kernels[i - back]);
+        if (!covered) continue;
+      } else if (k.impl == IMPL_FUSED_AWAY) {
+        continue;
+      }
+      std::vector<int> reads, writes;
+      reads_and_writes(k, &reads, &writes);
+      for (int slot : reads) ok = ok && !spans_overlap(span_of(k, slot), mo_span);
+      for (int slot : writes) {
+        const Span w = span_of(k, slot);
+        if (w.lo <= mo_span.lo && w.hi >= mo_span.hi) rewritten = true;
+        else if (spans_overlap(w, mo_span)) ok = false;
+      }
+    }
+    if (!ok) continue;
+    // the new chain, its side operands in fresh slots of the matmul
+    PlanKernel merged = m;
+    int64_t s_m, s_n;
+    for (int s = 0; s < tail.n && ok; ++s) {
+      ChainStep step = tail.steps[s];
+      if (step.slot >= 0) {
+        const DevOperand& o = e.ops[step.slot];
+        if (merged.n_ops >= KB200_MAX_OPERANDS || !linear(o, &s_m, &s_n)) { ok = false; break; }
+        DevOperand side{};
+        side.ptr = o.ptr;
+        side.stride[1] = s_m;
+        side.stride[2] = s_n;
+        step.slot = merged.n_ops;
+        merged.ops[merged.n_ops++] = side;
+      }
+      merged.chain.steps[merged.chain.n++] = step;
+    }
+    if (!ok || !linear(e.ops[e.chain.out_slot], &s_m, &s_n)) continue;
+    // While the matmul runs its operands are still being read: its output may coincide with a side
+    // operand element for element (an add in place), and must not touch anything else the kernel reads.
+    auto output_is_safe = [&](const PlanKernel& cand) {
+      const DevOperand& o = cand.ops[cand.chain.out_slot];
+      const Span o_span = span_of(cand, cand.chain.out_slot);
+      std::vector<int> reads, writes;
+      reads_and_writes(cand, &reads, &writes);
+      for (int slot : reads) {
+        const DevOperand& r = cand.ops[slot];
+        const bool same = slot >= m.desc.n_operands && r.ptr == o.ptr && r.stride[1] == o.stride[1] && r.stride[2] == o.stride[2];
+        if (!same && spans_overlap(span_of(cand, slot), o_span)) return false;
+      }
+      return true;
+    };
+    // (a) the matmul writes the elementwise kernel's output where the plan put it
+    PlanKernel direct = merged;
+    DevOperand out{};
+    out.ptr = e.ops[e.chain.out_slot].ptr;
+    out.stride[1] = s_m;
+    out.stride[2] = s_n;
+    direct.ops[direct.chain.out_slot] = out;
+    if (output_is_safe(direct) && tc_eligible(direct)) {
+      m = direct;
+      e.impl = IMPL_FUSED_AWAY;
+      e.launches = 0;
+      e.absorbed_by = (int)j;
+      continue;
+    }
+    // (b) the planner reused memory the matmul still reads (its A operand, typically) for that output:
+    // the value stays in the matmul's own output buffer instead, and the kernels that read the
+    // elementwise kernel's output read it there.  Needs the same layout in both buffers, every such
+    // reader inside that output, and the matmul's buffer untouched for as long as the value is live.
+    const DevOperand eo = e.ops[e.chain.out_slot];
+    if (e.desc.operands[e.chain.out_slot].base_kind != KB200_BASE_ARENA || s_n != 1 || s_m != m.N || (mo.ptr - eo.ptr) % 32 != 0) continue;
+    if (!output_is_safe(merged) || !tc_eligible(merged)) continue;
+    const Span eo_span = span_of(e, e.chain.out_slot);
+    std::vector<std::pair<size_t, int>> redirect;
+    bool dead = false;
+    for (size_t i = j + 2; i < plan.kernels.size() && ok && !dead; ++i) {
+      const PlanKernel& k = plan.kernels[i];
+      if (k.impl == IMPL_FUSED_AWAY && k.absorbed_by >= 0) continue;
+      if (k.impl == IMPL_ATTN_FUSED) { ok = false; break; }      // its operand pointers are already bound
+      if (k.impl == IMPL_FUSED_AWAY) continue;                   // a folded copy
+      std::vector<int> reads, writes;
+      reads_and_writes(k, &reads, &writes);
+      for (int slot : reads) {
+        const Span x = span_of(k, slot);
+        if (!spans_overlap(x, eo_span)) continue;
+        if (x.lo >= eo_span.lo && x.hi <= eo_span.hi) redirect.push_back({i, slot});
+        else ok = false;
+      }
+      for (int slot : writes) {
+        const Span x = span_of(k, slot);
+        if (spans_overlap(x, mo_span)) ok = false;
+        if (x.lo <= eo_span.lo && x.hi >= eo_span.hi) dead = true;
+        else if (spans_overlap(x, eo_span)) ok = false;
+      }
+    }
+    if (!ok) continue;
+    m = merged;
+    for (auto& [i, slot] : redirect) plan.kernels[i].ops[slot].ptr += mo.ptr - eo.ptr;
+    e.impl = IMPL_FUSED_AWAY;
+    e.launches = 0;
+    e.absorbed_by = (int)j;
+  }
+}
+
 // For every BF16 tensor-core matmul operand that lives in the arena: if the last kernel that wrote
 // that memory covers it completely and can also emit bf16, let it write the bf16 mirror and let the
 // matmul read the mirror.  Anything else keeps the per-launch conversion pass.
@@ -654,6 +846,50 @@ static int assign_shadows(Plan& plan) {
     if (k.b_shadow) k.b_shadow = mirror_of(k.ops[k.desc.b_slot].ptr);
   }
   for (size_t ki : attention_readers) attention_use_mirror(plan.kernels[ki], plan.arena, plan.arena16);
+  if (!plan.mirror_only) return KB200_OK;
+  // A LayerNorm or matmul that writes the mirror drops its float32 store when, until that memory is
+  // rewritten (or the plan ends: arena contents are dead then), every reader takes the mirror.
+  for (size_t ki = 0; ki < plan.kernels.size(); ++ki) {
+    PlanKernel& k = plan.kernels[ki];
+    if (!k.shadow_out || (k.impl != IMPL_ROW_LAYERNORM && k.impl != IMPL_MM_TC)) continue;
+    const int out_slot = k.impl == IMPL_ROW_LAYERNORM ? k.out_slot : k.chain.out_slot;
+    const Span w = span_of(k, out_slot);
+    bool only = true, rewritten = false;
+    int readers = 0;
+    for (size_t i = ki + 1; i < plan.kernels.size() && only && !rewritten; ++i) {
+      const PlanKernel& r = plan.kernels[i];
+      if (r.impl == IMPL_FUSED_AWAY) continue;     // folded, absorbed, or stood for by the fused attention's own kernel
+      if (r.impl == IMPL_ATTN_FUSED) {
+        Span x{nullptr, nullptr};
+        if (!attention_operand_span(r, &x.lo, &x.hi)) { only = false; break; }
+        if (spans_overlap(x, w)) {
+          if (attention_reads_mirror(r) && w.lo <= x.lo && w.hi >= x.hi) ++readers;
+          else only = false;
+        }
+        int64_t elems = 0;
+        const DevOperand* y = attention_output(plan, i, &elems);
+        const Span yw{y->ptr, y->ptr + elems};
+        if (yw.lo <= w.lo && yw.hi >= w.hi) rewritten = true;
+        else if (spans_overlap(yw, w)) only = false;
+        continue;
+      }
+      std::vector<int> reads, writes;
+      reads_and_writes(r, &reads, &writes);
+      for (int slot : reads) {
+        const Span x = span_of(r, slot);
+        if (!spans_overlap(x, w)) continue;
+        const bool mirrored = r.impl == IMPL_MM_TC && ((slot == r.desc.a_slot && r.a_shadow) || (slot == r.desc.b_slot && r.b_shadow));
+        if (mirrored && w.lo <= x.lo && w.hi >= x.hi) ++readers;
+        else only = false;
+      }
+      for (int slot : writes) {
+        const Span x = span_of(r, slot);
+        if (x.lo <= w.lo && x.hi >= w.hi) rewritten = true;
+        else if (spans_overlap(x, w)) only = false;
+      }
+    }
+    k.mirror_only = only && readers > 0;
+  }
   return KB200_OK;
 }
 
@@ -754,6 +990,9 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
     attention_destroy(k);
     k.shadow_out = nullptr;
     k.a_shadow = k.b_shadow = nullptr;
+    k.mirror_only = false;
+    k.absorbed_by = -1;
+    k.n_ops = k.desc.n_operands;
     rc = resolve(plan, k, (int)i);
     if (rc) break;
     switch (k.desc.kclass) {
@@ -771,6 +1010,8 @@ KB200_EXPORT int kb200_plan_bind(kb200_plan* p, void* arena, uint64_t arena_byte
     }
   // phase 2b: matmuls read a K-contiguous B at its source instead of through the plan's transposing copy
   if (rc == KB200_OK && plan.fold_copies) fold_operand_copies(plan);
+  // phase 2c: a tensor-core matmul also runs the elementwise kernel that only continues it
+  if (rc == KB200_OK && plan.absorb_elementwise) absorb_elementwise(plan);
   // phase 3: BF16 matmuls read activations from the bf16 mirror when their producer can write it
   if (rc == KB200_OK) rc = assign_shadows(plan);
   for (size_t i = 0; i < plan.kernels.size() && rc == KB200_OK; ++i)
@@ -794,6 +1035,8 @@ KB200_EXPORT int kb200_plan_set_option(kb200_plan* p, int option, int value) {
     case KB200_OPT_DEPENDENT_LAUNCH: plan.pdl = value != 0; return KB200_OK;
     case KB200_OPT_FOLD_OPERAND_COPIES: plan.fold_copies = value != 0; return KB200_OK;
     case KB200_OPT_CONCURRENCY: plan.concurrency = value < 1 ? 1 : value; return KB200_OK;
+    case KB200_OPT_ABSORB_ELEMENTWISE: plan.absorb_elementwise = value != 0; return KB200_OK;
+    case KB200_OPT_MIRROR_ONLY: plan.mirror_only = value != 0; return KB200_OK;
     default: return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: unknown option %d", option);
   }
 }

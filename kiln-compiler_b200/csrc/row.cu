@@ -119,6 +119,7 @@ struct RowFastParams {
   int inner;
   float inv_n, eps;
   __nv_bfloat16* out16;    // optional bf16 copy of the output (same row stride as `out`), or null
+  int store32;             // 0: only that copy is stored (every reader of the output takes it)
   // Two row dims (a [batch * heads, tokens, inner] softmax whose mask varies with the token only):
   // row = i0 * rows_inner + i1, and every tensor has a stride for each.  rows_inner == 0: one row dim.
   int64_t rows_inner;
@@ -223,7 +224,7 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const __grid_constant__ R
         y.y = v[i].y * rstd * g[i].y + b[i].y;
         y.z = v[i].z * rstd * g[i].z + b[i].z;
         y.w = v[i].w * rstd * g[i].w + b[i].w;
-        o4[j] = y;
+        if (p.store32) o4[j] = y;
         if (p.out16 != nullptr) {
           __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
           uint2 packed;
@@ -344,6 +345,7 @@ int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   for (int i = 0; i < d.iter_rank - 1; ++i) n_rows *= d.iter_shape[i];
   if (k.impl == IMPL_ROW_LAYERNORM || k.impl == IMPL_ROW_SOFTMAX) {
     RowFastParams p{};
+    p.store32 = 1;
     p.x = k.ops[k.x_slot].ptr;
     p.out = k.ops[k.out_slot].ptr;
     p.n_rows = n_rows;
@@ -378,6 +380,7 @@ int launch_row(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
       p.inv_n = k.ln_inv_n;
       p.eps = k.ln_eps;
       p.out16 = static_cast<__nv_bfloat16*>(k.shadow_out);
+      p.store32 = (k.mirror_only && p.out16 != nullptr) ? 0 : 1;
       launch_row_warp<ROW_LAYERNORM>(p, plan.sm_count, plan.pdl, s);
     } else {
       launch_row_warp<ROW_SOFTMAX>(p, plan.sm_count, plan.pdl, s);

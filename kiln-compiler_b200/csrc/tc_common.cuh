@@ -278,19 +278,21 @@ inline bool encode_map4(CUtensorMap* map, bool bf16, const void* base, int chunk
 // A 3-D map over [batch, rows, cols] (cols contiguous) for bulk stores of 32 x 32 blocks staged in
 // shared memory with rows of 128 bytes (float, 128-byte swizzle) or 64 bytes (bf16, 64-byte swizzle):
 // the swizzle lets both a lane-per-row and a lane-per-column writer fill the block without bank conflicts.
+// Bulk-store map over [batch, rows, cols] with boxes of 32 rows x 128 bytes (32 floats; `wide`: 64 bf16)
+// under the 128-byte swizzle, or 32 rows x 32 bf16 under the 64-byte swizzle.
 inline bool encode_map_store(CUtensorMap* map, bool bf16, const void* base, int64_t cols, int64_t rows, int64_t batch,
-                             int64_t row_stride_elems, int64_t batch_stride_elems) {
+                             int64_t row_stride_elems, int64_t batch_stride_elems, bool wide = false) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const int esz = bf16 ? 2 : 4;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
   cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * esz, (cuuint64_t)(batch > 1 ? batch_stride_elems : row_stride_elems * rows) * esz};
   if (strides[1] == 0) strides[1] = strides[0] * rows;
-  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t box[3] = {bf16 && wide ? 64u : 32u, 32, 1};
   cuuint32_t elem[3] = {1, 1, 1};
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base),
                   dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  bf16 && !wide ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }

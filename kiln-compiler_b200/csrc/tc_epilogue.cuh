@@ -78,10 +78,12 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
 // Staging of a 32 x 32 block for the bulk stores with a lane per ROW (v[j] = column j), in the swizzled
 // layouts of the store maps: float rows of 128 bytes with the 16-byte unit index XORed by (row & 7),
 // bf16 rows of 64 bytes with the unit index XORed by ((row >> 1) & 3).  128-bit stores, no bank conflicts.
-__device__ __forceinline__ void stage_rows(uint8_t* sf, uint8_t* sh, const float (&v)[32], int lane, bool with16) {
+__device__ __forceinline__ void stage_rows(uint8_t* sf, uint8_t* sh, const float (&v)[32], int lane, bool with16, bool with32 = true) {
+  if (with32) {
 #pragma unroll
-  for (int q = 0; q < 8; ++q)
-    *reinterpret_cast<float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  }
   if (with16) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -94,6 +96,23 @@ __device__ __forceinline__ void stage_rows(uint8_t* sf, uint8_t* sh, const float
       packed.w = *reinterpret_cast<uint32_t*>(&w3);
       *reinterpret_cast<uint4*>(sh + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = packed;
     }
+  }
+}
+
+// Two 32 x 32 blocks side by side (columns 0-31 in v, 32-63 in w) as one 32 x 64 bf16 box: rows of 128
+// bytes, the 16-byte unit index XORed by (row & 7).
+__device__ __forceinline__ void stage_rows_bf16x64(uint8_t* sh, const float (&v)[32], const float (&w)[32], int lane) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float* x = q < 4 ? &v[8 * q] : &w[8 * (q - 4)];
+    __nv_bfloat162 w0 = __floats2bfloat162_rn(x[0], x[1]), w1 = __floats2bfloat162_rn(x[2], x[3]);
+    __nv_bfloat162 w2 = __floats2bfloat162_rn(x[4], x[5]), w3 = __floats2bfloat162_rn(x[6], x[7]);
+    uint4 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&w0);
+    packed.y = *reinterpret_cast<uint32_t*>(&w1);
+    packed.z = *reinterpret_cast<uint32_t*>(&w2);
+    packed.w = *reinterpret_cast<uint32_t*>(&w3);
+    *reinterpret_cast<uint4*>(sh + lane * 128 + ((q ^ (lane & 7)) << 4)) = packed;
   }
 }
 

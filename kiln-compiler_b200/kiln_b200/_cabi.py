@@ -26,6 +26,8 @@ OPT_FUSE_ATTENTION = 1
 OPT_DEPENDENT_LAUNCH = 2
 OPT_FOLD_OPERAND_COPIES = 3
 OPT_CONCURRENCY = 4
+OPT_ABSORB_ELEMENTWISE = 5
+OPT_MIRROR_ONLY = 6
 BASE_KINDS = {"arena": 0, "const": 1, "input": 2, "output": 3}
 PRECISIONS = {"fp32": 0, "tf32": 1, "bf16": 2}
 OPCODES = {

@@ -194,6 +194,14 @@ class GPUExecutable:
         # (KILN_GPU_FOLD_COPIES=0); by default the matmul reads the copy's source and the copy is skipped.
         fold = os.environ.get("KILN_GPU_FOLD_COPIES", "1") not in ("0", "false", "False", "")
         _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_FOLD_OPERAND_COPIES, int(fold)), self._lib)
+        # An elementwise kernel that only continues the matmul in front of it runs in that matmul's epilogue
+        # (KILN_GPU_ABSORB_ELEMENTWISE=0: one launch per planned kernel); in BF16 mode an intermediate that
+        # only bf16 readers consume is not stored as float32 (KILN_GPU_MIRROR_ONLY=0: every planned buffer
+        # holds its float32 values, for a caller that looks at intermediates).
+        absorb = os.environ.get("KILN_GPU_ABSORB_ELEMENTWISE", "1") not in ("0", "false", "False", "")
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_ABSORB_ELEMENTWISE, int(absorb)), self._lib)
+        mirror_only = os.environ.get("KILN_GPU_MIRROR_ONLY", "1") not in ("0", "false", "False", "")
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_MIRROR_ONLY, int(mirror_only)), self._lib)
         self._bind()
         # launch_names: one per device launch of the plan (k3_matmul, k2_ew0 ...); kernel_names: the Kiln
         # kernels they come from, which is what CompiledModule.profile keys on (kiln/api.py:204-211)

@@ -209,6 +209,53 @@ def test_a_batch_of_sequences_as_one_graph(kiln):
         assert float((got[i] - one).abs().max() / want.abs().max()) <= 2e-3
 
 
+class BatchedMlp(torch.nn.Module):
+    """A Linear on a [batch, tokens, d] input: the reference plans matmul + bias, a reshape, then the
+    activation / residual add as an elementwise kernel of its own."""
+
+    def __init__(self, keep_hidden=False, reuse_hidden=False):
+        super().__init__()
+        torch.manual_seed(21)
+        self.fc, self.proj = torch.nn.Linear(256, 512), torch.nn.Linear(512, 256)
+        self.keep_hidden, self.reuse_hidden = keep_hidden, reuse_hidden
+
+    def forward(self, x):
+        h = self.fc(x)
+        a = torch.nn.functional.gelu(h, approximate="tanh")
+        y = x - self.proj(a)                     # the matmul's value is the second argument of the sub
+        if self.reuse_hidden:
+            y = y + h.mean(dim=-1, keepdim=True)  # a later kernel reads the first matmul's own output
+        return (y, h) if self.keep_hidden else y
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
+def test_elementwise_kernels_that_continue_a_matmul_run_in_its_epilogue(kiln, precision, monkeypatch):
+    if precision == "bf16":
+        monkeypatch.setenv("KILN_GPU_PRECISION", "bf16")
+    tol = {"fp32": 1e-4, "tf32": 1e-2, "bf16": 5e-2}[precision]
+    x = torch.randn(3, 128, 256, generator=torch.Generator().manual_seed(5))
+    model = BatchedMlp().eval()
+    fused = compile_and_compare(kiln, model, x, allow_tf32=precision != "fp32", rtol=tol, atol=tol)
+    impls = fused._exe.impls
+    assert impls.count("mm_tcgen05") == 2 and impls.count("fused_away") == 2, impls
+    monkeypatch.setenv("KILN_GPU_ABSORB_ELEMENTWISE", "0")
+    plain = compile_and_compare(kiln, model, x, allow_tf32=precision != "fp32", rtol=tol, atol=tol)
+    assert "fused_away" not in plain._exe.impls and plain._exe.device_launches > fused._exe.device_launches
+    a, b = fused(x).cpu(), plain(x).cpu()
+    torch.testing.assert_close(a, b, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("variant", ["output", "read again"])
+def test_a_matmul_whose_own_value_is_needed_keeps_its_output(kiln, variant):
+    """Not absorbed: the matmul's result is a plan output, or a later kernel reads it."""
+    x = torch.randn(3, 128, 256, generator=torch.Generator().manual_seed(6))
+    model = BatchedMlp(keep_hidden=variant == "output", reuse_hidden=variant == "read again").eval()
+    compiled = compile_and_compare(kiln, model, x, allow_tf32=True, rtol=1e-2, atol=1e-2)
+    names = dict(zip(compiled._exe.launch_names, compiled._exe.impls))
+    gelu = [n for n, impl in names.items() if "ew" in n][0]
+    assert names[gelu] != "fused_away", names
+
+
 def test_wrong_shape_is_a_value_error(kiln):
     compiled = kiln.compile(torch.nn.Linear(8, 4).eval(), (torch.randn(3, 8),), device="cuda")
     with pytest.raises(ValueError):

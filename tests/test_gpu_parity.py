@@ -67,6 +67,8 @@ def test_every_kernel_of_the_block_matches_the_oracle_step_by_step(precision, mo
 
     monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")
     monkeypatch.setenv("KILN_GPU_FOLD_COPIES", "0")
+    monkeypatch.setenv("KILN_GPU_ABSORB_ELEMENTWISE", "0")
+    monkeypatch.setenv("KILN_GPU_MIRROR_ONLY", "0")      # every planned buffer holds its float32 values
 
     case = "gpt2_block_t128"
     plan = load_plan(case)
@@ -400,6 +402,27 @@ def test_the_benchmark_s_eight_sequence_graph_matches_the_stored_eager_result(pr
 
     case = "gpt2_block_b8_t1024"
     exe, outs, (plan, inputs, consts, expected) = run_case(case, precision)
-    assert "attention_fused" in exe.impls and exe.impls.count("fused_away") == 6
+    # six kernels of the attention chain, the GELU and the last residual add launch nothing of their own
+    assert "attention_fused" in exe.impls and exe.impls.count("fused_away") == 8
     got = subsample(outs[0], expected["step"][0])
     assert scale_relative_error(got, expected["sub"][0]) <= REL_TOL[precision], (precision, exe.impls)
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_batched_block_with_and_without_cross_kernel_fusion(precision, monkeypatch):
+    """The batched block: activation and residual add in the matmuls' epilogues and (BF16) intermediates
+    stored as bf16 only, against one launch per planned kernel with every float32 buffer written."""
+    from gpu_helpers import run_case
+
+    fused_exe, fused, (plan, inputs, consts, _) = run_case("batched_block", precision)
+    names = dict(zip(fused_exe.launch_names, fused_exe.impls))
+    absorbed = [n for n, impl in names.items() if "_ew" in n and impl == "fused_away"]
+    assert len(absorbed) == 2, names
+    monkeypatch.setenv("KILN_GPU_ABSORB_ELEMENTWISE", "0")
+    monkeypatch.setenv("KILN_GPU_MIRROR_ONLY", "0")
+    plain_exe, plain, _ = run_case("batched_block", precision)
+    assert plain_exe.device_launches >= fused_exe.device_launches + 2   # and a bf16 conversion pass behind an elementwise producer
+    (exact,) = run_plan(plan, inputs, consts, dtype=np.float64)
+    assert scale_relative_error(fused[0], exact) <= REL_TOL[precision]
+    assert scale_relative_error(plain[0], exact) <= REL_TOL[precision]
+    assert scale_relative_error(fused[0], plain[0]) <= REL_TOL[precision]
