@@ -14,7 +14,7 @@ registered as ``kiln.gpu``; where that copy is absent the plan those passes prod
 from kiln_b200/plans.  It is compiled for a GROUP of eight sequences, ``[8, 1024, 768]``: the
 frontend flattens the leading dims of every Linear, so the projections are 8192-row matmuls (256-row
 tiles on SM pairs) and the fused attention kernel takes the sequence as one more grid dimension.
-Four such modules (own arena, static buffers and stream each) are kept in flight, the way a server
+Eight such modules (own arena, static buffers and stream each) are kept in flight, the way a server
 overlaps requests, and the whole step of 64 sequences -- eight groups -- is captured as ONE CUDA
 graph (kiln_b200.runtime.StreamedBatch).  ``extras.single_sequence_graphs`` is the same step as 64
 one-sequence graphs over six modules.
@@ -59,7 +59,7 @@ import torch  # noqa: E402
 
 SEQS, TOKENS, D, HEADS, SEED = 64, 1024, 768, 12, 4
 GROUP = 8             # sequences per compiled graph: the block is compiled for [8, 1024, 768] (eight independent sequences)
-INFLIGHT = 4          # compiled modules kept in flight (own stream, arena and CUDA graph each)
+INFLIGHT = 8          # compiled modules kept in flight (own stream, arena and static buffers each): one per group
 HEAD_CASE = f"gpt2_block_b{GROUP}_t{TOKENS}"
 METRIC, UNIT = "gpt2_block_tokens_per_s", "tokens/s"
 REF_INSTALL = ROOT / "baseline" / "_ref"

@@ -162,6 +162,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   __shared__ __align__(8) uint64_t bars[kBarCount];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ PairStep chain_steps[kMaxChain];     // looked up by a run-time index for every block
 #ifdef KB200_TRACE
   __shared__ long long trace[5][128];
   __shared__ long long marks[8];
@@ -202,6 +203,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   cluster_arrive();
   if (lane == 0 && warp < 2)
     asm volatile("" ::"r"(p.bn), "r"(p.idesc), "r"(p.num_tiles), "l"(p.magic_tn), "l"(p.magic_tpb), "l"(p.status) : "memory");
+  if (warp == 3 && lane < kMaxChain) chain_steps[lane] = p.steps[lane];
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                  "r"((uint32_t)p.tmem_cols)
@@ -340,10 +342,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           umma_pair_commit(empty0 + 8 * s);
 #ifdef KB200_TRACE
           fine[5] = clock64();
-          if (blockIdx.x == 0 && tq >= 4 && tq < 10) {
-            printf("  fine step %d: after-wait->mma1 %lld mma2 %lld mma3 %lld mma4 %lld commit %lld | prev commit -> this wait done %lld\n", tq,
-                   fine[1] - fine[0], fine[2] - fine[1], fine[3] - fine[2], fine[4] - fine[3], fine[5] - fine[4], fine[0] - trace[3][tq - 1]);
-          }
+          (void)fine;
 #endif
           PAIR_STAMP(3, tq);
 #ifdef KB200_TRACE
@@ -373,15 +372,17 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     // accumulator is ready: lane l holds column l of each of this warp's blocks, and the chain takes
     // value q from lane q by shuffle (one coalesced 128-byte load per block instead of eight
     // broadcast loads whose L2 latency sat in front of every block's arithmetic).
+    const int n_steps = p.n_steps;
     int col_step = -1;
-    for (int s = 0; s < p.n_steps && col_step < 0; ++s)
-      if (p.steps[s].kind == SIDE_COL) col_step = s;
+    for (int s = 0; s < n_steps && col_step < 0; ++s)
+      if (chain_steps[s].kind == SIDE_COL) col_step = s;
     float col_pre[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t res_phase = 0;        // one parity bit per slot
     int slot = 0;                  // slot of the next block this warp stages
     bool res_ready = false;        // the residual of the next block has been requested into `slot`
     bool ok = true;
     int i = 0;
+    bool dry = true;               // the rehearsal pass described at the tile loop
     auto request_residual = [&](int into, int n, int m_first, int batch) {
       if (lane == 0) {
         const uint32_t bar = res0 + 8 * into;
@@ -391,13 +392,15 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     };
     // The fused chain on one 32 x 32 block held a lane per row (v[q] = column n + q of this lane's row).
     auto run_chain = [&](float (&v)[32], int j, int n, int batch, const uint8_t* sf, int res_slot, const float4* col_smem = nullptr) {
-      for (int s = 0; s < p.n_steps; ++s) {
-        const PairStep st = p.steps[s];
+      for (int s = 0; s < n_steps; ++s) {
+        const PairStep st = chain_steps[s];
         float side[32];
         if (st.kind == SIDE_RES) {
-          bool landed = mbar_wait(res0 + 8 * res_slot, (res_phase >> res_slot) & 1u, abort_ptr);
-          if (!landed && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 5); *abort_ptr = 1; }
-          res_phase ^= 1u << res_slot;
+          if (!dry) {
+            bool landed = mbar_wait(res0 + 8 * res_slot, (res_phase >> res_slot) & 1u, abort_ptr);
+            if (!landed && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 5); *abort_ptr = 1; }
+            res_phase ^= 1u << res_slot;
+          }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const float4 t = *reinterpret_cast<const float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4));
@@ -427,18 +430,23 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         chain_step32(st.op, v, side);
       }
     };
-    for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++i) {
+    // The first pass over the loop body is a rehearsal: while the first tile is still being multiplied
+    // the warp runs one strip (or block) of the same instructions on whatever tensor memory holds, waits
+    // for nothing, requests nothing and stores nothing.  The kernel's code is cold at every launch, and
+    // the instruction-cache misses of the first real epilogue (~10 000 cycles against ~4 000 warm) would
+    // otherwise hold back the accumulator the main loop needs two tiles later.
+    for (int tile = pair; tile < p.num_tiles && ok;) {
       const int batch = pair_div(tile, p.magic_tpb);
       const int rem = tile - batch * p.tiles_per_batch;
       const int tm_i = pair_div(rem, p.magic_tn);
       const int tn_i = rem - tm_i * p.tiles_n;
-      const int acc = i & 1;
+      const int acc = dry ? 1 : (i & 1);
       const uint32_t aph = (i >> 1) & 1;
       const int m_first = tm_i * 256 + (int)rank * 128 + quad * 32;
       const int n0 = tn_i * p.bn;
       const bool rows_ok = m_first < p.M;
       if (col_step >= 0 && rows_ok) {
-        const float* src = p.steps[col_step].ptr + (int64_t)batch * p.steps[col_step].batch_stride + n0;
+        const float* src = chain_steps[col_step].ptr + (int64_t)batch * chain_steps[col_step].batch_stride + n0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           // block j of this warp: alternate 32-column blocks with a matrix operand, else the halves of
@@ -448,16 +456,18 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       }
       // the first block's residual is requested before the accumulator is ready
-      if (has_res && !res_ready && rows_ok && n0 + half * 32 < p.N) {
+      if (has_res && !dry && !res_ready && rows_ok && n0 + half * 32 < p.N) {
         if (lane == 0) store_wait_read(allowed);
         __syncwarp();
         request_residual(slot, n0 + half * 32, m_first, batch);
         res_ready = true;
       }
-      bool got = mbar_wait_cluster(tfull0 + 8 * acc, aph, abort_ptr);
-      if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
-      ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
-      if (!ok) break;
+      if (!dry) {
+        bool got = mbar_wait_cluster(tfull0 + 8 * acc, aph, abort_ptr);
+        if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
+        ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
+        if (!ok) break;
+      }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #ifdef KB200_TRACE
       if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
@@ -525,9 +535,9 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #endif
         __syncwarp();
 #ifdef KB200_TRACE
-        if (lane == 0 && !(p.debug & 1)) {
+        if (lane == 0 && !dry && !(p.debug & 1)) {
 #else
-        if (lane == 0) {
+        if (lane == 0 && !dry) {
 #endif
           if (with32) {
             tma_store_3d(&tma_out, slot0, n, m_first, batch);
@@ -539,6 +549,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
+        if (dry) break;
       }
       for (int j = 0; has_res && j < nblk; ++j) {
         const int c = half * 32 + 64 * j;
@@ -555,10 +566,10 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-        if (has_res && !res_ready) request_residual(slot, n, m_first, batch);
+        if (!dry && !res_ready) request_residual(slot, n, m_first, batch);
         res_ready = false;
         const int next_slot = slot + 1 == slots ? 0 : slot + 1;
-        if (has_res && j + 1 < nblk && n + 64 < p.N) {   // the next block's residual flies under this block's arithmetic
+        if (!dry && j + 1 < nblk && n + 64 < p.N) {       // the next block's residual flies under this block's arithmetic
           request_residual(next_slot, n + 64, m_first, batch);
           res_ready = true;
         }
@@ -570,7 +581,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         stage_rows(sf, sf + 4096, v, lane, with16, with32);
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) {
+        if (lane == 0 && !dry) {
           const uint32_t src = slot0 + (uint32_t)(slot * slot_bytes);
           if (with32) tma_store_3d(&tma_out, src, n, m_first, batch);
           if (with16) tma_store_3d(&tma_out16, src + 4096, n, m_first, batch);
@@ -579,12 +590,19 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
+        if (dry) break;
         slot = next_slot;
+      }
+      if (dry) {
+        dry = false;
+        continue;
       }
       // this warp has read the accumulator: hand it back to the leader's MMA thread
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
+      tile += num_pairs;
+      ++i;
     }
     if (lane == 0) store_wait_read(0);   // shared memory must outlive the stores that read it
   }
@@ -597,11 +615,11 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const long long t0 = marks[0];
     printf("PAIR block %d: alloc+sync done %lld cluster barrier done %lld after pdl %lld exit %lld | tiles %d bn %d stages %d num_kb %d grid %d\n",
            (int)blockIdx.x, marks[1] - t0, marks[2] - t0, marks[3] - t0, clock64() - t0, p.num_tiles, p.bn, p.stages, p.num_kb, (int)gridDim.x);
-    for (int i2 = 0; i2 < 40; ++i2)
+    for (int i2 = 0; i2 < 64; ++i2)
       printf("  b%d step %3d  prod_wait_done %7lld issued %7lld | mma_full %7lld committed %7lld\n", (int)blockIdx.x, i2, trace[0][i2] - t0,
              trace[1][i2] - t0, trace[2][i2] - t0, trace[3][i2] - t0);
     printf("  b%d epilogue warp 4 (tile ready; per block: loaded, slot free, computed, stored):", (int)blockIdx.x);
-    for (int i2 = 0; i2 < 40; ++i2) printf(" %lld", trace[4][i2] - t0);
+    for (int i2 = 0; i2 < 80; ++i2) printf(" %lld", trace[4][i2] - t0);
     printf("\n");
   }
 #endif

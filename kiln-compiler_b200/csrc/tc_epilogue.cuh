@@ -27,6 +27,15 @@ __device__ __forceinline__ float f_tanh_approx(float x) {
   return y;
 }
 
+// 0.5 x (1 + tanh(k (x + c x^3))) in six instructions: the polynomial by one multiply-add on x^2, the
+// final product as h + h t with h = x / 2.
+__device__ __forceinline__ float f_gelu_tanh_approx(float x) {
+  const float x2 = x * x;
+  const float u = x * fmaf(x2, 0.7978845608028654f * 0.044715f, 0.7978845608028654f);
+  const float h = 0.5f * x;
+  return fmaf(h, f_tanh_approx(u), h);
+}
+
 __device__ __forceinline__ float f_erf(float x) {
   const float a = fabsf(x);
   const float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
@@ -39,16 +48,17 @@ __device__ __forceinline__ float f_erf(float x) {
 // approximations here, everything else as the CUDA-core kernels evaluate it.
 __device__ __forceinline__ float chain_apply_scalar(int op, float v, float s) {
   if (op == CH_TANH_APPROX) return f_tanh_approx(v);
-  if (op == CH_GELU_TANH_APPROX) return 0.5f * v * (1.0f + f_tanh_approx(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  if (op == CH_GELU_TANH_APPROX) return f_gelu_tanh_approx(v);
   return apply_chain(op, v, s);
 }
 
-// One chain step on 32 register-resident values.  The switch is outside the element loop and
+// One chain step on W register-resident values.  The switch is outside the element loop and
 // every index is a compile-time constant, so v[] and side[] never leave the register file and the
-// 32 independent elements give the few epilogue warps the instruction-level parallelism they need.
-__device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float (&side)[32]) {
+// W independent elements give the few epilogue warps the instruction-level parallelism they need.
+template <int W>
+__device__ __forceinline__ void chain_step_n(int op, float (&v)[W], const float (&side)[W]) {
 #define KB200_EACH(expr)                  \
-  _Pragma("unroll") for (int j = 0; j < 32; ++j) { const float x = v[j]; const float s = side[j]; (void)s; v[j] = (expr); }
+  _Pragma("unroll") for (int j = 0; j < W; ++j) { const float x = v[j]; const float s = side[j]; (void)s; v[j] = (expr); }
   switch (op) {
     case CH_ADD: KB200_EACH(x + s) break;
     case CH_SUB: KB200_EACH(x - s) break;
@@ -67,13 +77,14 @@ __device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float
     case CH_GELU_TANH: KB200_EACH(d_gelu_tanh(x)) break;
     case CH_GELU_ERF: KB200_EACH(0.5f * x * (1.0f + f_erf(x * 0.7071067811865476f))) break;
     case CH_TANH_APPROX: KB200_EACH(f_tanh_approx(x)) break;
-    case CH_GELU_TANH_APPROX: KB200_EACH(0.5f * x * (1.0f + f_tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
+    case CH_GELU_TANH_APPROX: KB200_EACH(f_gelu_tanh_approx(x)) break;
     case CH_RSQRT: KB200_EACH(rsqrtf(x)) break;
     case CH_SQRT: KB200_EACH(sqrtf(x)) break;
     default: break;
   }
 #undef KB200_EACH
 }
+__device__ __forceinline__ void chain_step32(int op, float (&v)[32], const float (&side)[32]) { chain_step_n<32>(op, v, side); }
 
 // Staging of a 32 x 32 block for the bulk stores with a lane per ROW (v[j] = column j), in the swizzled
 // layouts of the store maps: float rows of 128 bytes with the 16-byte unit index XORed by (row & 7),
