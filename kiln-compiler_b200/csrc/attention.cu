@@ -10,7 +10,10 @@
 // and writes the merged-heads buffer, the only value of the chain that is live afterwards.  The
 // plan itself (kernel list, arena offsets) is untouched; the score buffers are simply never written.
 //
-// One CTA per (head, 128-query tile), 320 threads in three roles:
+// Persistent CTAs (one per SM) walk the (sequence, head, 128-query tile) work items, heaviest first, in
+// steps of the grid size: barrier set-up, the TMEM allocation and the latency of an item's first
+// loads are paid once per CTA or hidden under the previous item's tail, not once per item.  Ring
+// slots and barrier phases run on a tile counter that continues across items.  320 threads in three roles:
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through 2-deep rings.
 //   warp 1      MMA issuer: S = Q K^T (operands in shared memory, TF32) into one of two S buffers in
 //               TMEM; O_part = P V with P read from TMEM (written there by the softmax warps).
@@ -41,7 +44,7 @@ constexpr int kRows = 128;                   // queries per CTA and keys per til
 constexpr int kHeadDim = 64;
 constexpr int kSlab = kRows * 128;           // one [128 rows x 128 bytes] swizzled slab
 constexpr int kAttnThreads = 64 + 256;
-constexpr int kXStride = 35;                 // floats per row of the merge buffers: odd, so rows spread over the banks
+constexpr int kXStride = 36;                 // floats per row of the merge buffers: 32 dims, max, sum; 144 bytes, so 128-bit accesses of eight rows spread over the banks
 // Q + 2 x K + 2 x V tiles (two 16 KB slabs each in float32, one in bf16), the two merge buffers, alignment slack
 constexpr int attn_smem(bool bf16) { return 5 * (bf16 ? 1 : 2) * kSlab + 2 * kRows * kXStride * 4 + 1024; }
 
@@ -124,7 +127,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   constexpr int kTileSlabs = BF16 ? 1 : 2;
   constexpr int kTileBytes = kTileSlabs * kSlab;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[19];
+  __shared__ __align__(8) uint64_t bars[20];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -147,17 +150,32 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t v_smem = k_smem + 2 * kTileBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
-  //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer]
+  //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer] | 19 q_empty
   const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
   const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
   const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull0 = smem_u32(&bars[15]);
+  const uint32_t q_empty = smem_u32(&bars[19]);
 
-  const int h = blockIdx.x % p.H;
-  const int seq = (blockIdx.x / p.H) % p.B;
-  const int qt = p.q_tiles - 1 - blockIdx.x / (p.H * p.B);   // heaviest (longest causal prefix) tiles first, of every sequence
-  const int q0 = qt * kRows;
-  const int n_kv = qt + 1;                           // causal: key tiles 0..qt
-  const int row0 = seq * p.T;                        // this sequence's first row in Q, K, V and the output
+  // work item w -> (head, sequence, query tile): heaviest (longest causal prefix) tiles first, of every sequence
+  const int n_items = p.B * p.H * p.q_tiles;
+  // This CTA's r-th item (-1: none).  Rounds alternate direction over the CTAs, so that the CTA with the
+  // heaviest item of one round takes the lightest of the next (24 key tiles at most per CTA instead of
+  // 27 for 8 x 12 x 8 items on 148 CTAs).
+  auto nth_item = [&](int r) {
+    const int w = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return w < n_items ? w : -1;
+  };
+  struct Item { int h, q0, n_kv, row0, qt; };
+  auto item_of = [&](int w) {
+    Item it;
+    it.h = w % p.H;
+    const int seq = (w / p.H) % p.B;
+    it.qt = p.q_tiles - 1 - w / (p.H * p.B);
+    it.q0 = it.qt * kRows;
+    it.n_kv = it.qt + 1;                               // causal: key tiles 0..qt
+    it.row0 = seq * p.T;                               // this sequence's first row in Q, K, V and the output
+    return it;
+  };
 
   if (threadIdx.x == 32) {
     prefetch_tensormap(&map_q);
@@ -167,6 +185,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full + 8 * s, 1);
       mbar_init(k_empty + 8 * s, 1);
@@ -202,30 +221,39 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(q_full, kTileBytes);
-      tma_load_3d(q_smem, &map_q, q_full, 0, row0 + q0, h);
-      if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, row0 + q0, h);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); break; }
-        mbar_expect_tx(k_full + 8 * s, kTileBytes);
-        tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, row0 + j * kRows, h);
-        if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, row0 + j * kRows, h);
-        if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); break; }
-        mbar_expect_tx(v_full + 8 * s, kTileBytes);
-        tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, row0 + j * kRows, h);
-        if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, row0 + j * kRows, h);
+      int t = 0;                                     // key tiles loaded so far, over all items
+      bool ok = true;
+      for (int ii = 0; ok; ++ii) {
+        const int w = nth_item(ii);
+        if (w < 0) break;
+        const Item it = item_of(w);
+        // the Q tile is free once every Q K^T of the previous item has been executed
+        if (!mbar_wait(q_empty, (ii & 1) ^ 1, abort_ptr)) { give_up(0x13); break; }
+        mbar_expect_tx(q_full, kTileBytes);
+        tma_load_3d(q_smem, &map_q, q_full, 0, it.row0 + it.q0, it.h);
+        if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, it.row0 + it.q0, it.h);
+        for (int j = 0; j < it.n_kv; ++j, ++t) {
+          const int s = t & 1;
+          const uint32_t ph = (t >> 1) & 1;
+          if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
+          mbar_expect_tx(k_full + 8 * s, kTileBytes);
+          tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, it.row0 + j * kRows, it.h);
+          if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, it.row0 + j * kRows, it.h);
+          if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
+          mbar_expect_tx(v_full + 8 * s, kTileBytes);
+          tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, it.row0 + j * kRows, it.h);
+          if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, it.row0 + j * kRows, it.h);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, abort_ptr);
-      if (!ok) give_up(0x21);
-      auto issue_qk = [&](int j) {
-        const int s = j & 1;
-        if (!mbar_wait(k_full + 8 * s, (j >> 1) & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
+      bool ok = true;
+      // Tiles are numbered over all items (t): ring slot, S buffer and O_part buffer are t & 1, phases (t >> 1) & 1.
+      auto issue_qk = [&](int t) {
+        const int s = t & 1;
+        if (!mbar_wait(k_full + 8 * s, (t >> 1) & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t kb = k_smem + s * kTileBytes;
         // 32 bytes of the head dimension per instruction: 8 float32 (TF32) or 16 bf16
@@ -238,19 +266,19 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         umma_commit(sfull0 + 8 * s);
         umma_commit(k_empty + 8 * s);
       };
-      // P V of tile j: each group's 64 keys into that group's O_part buffer (j & 1).  In-order execution
+      // P V of tile t: each group's 64 keys into that group's O_part buffer (t & 1).  In-order execution
       // of the tensor pipe keeps S[s] intact until these reads of P are done (the next Q K^T into S[s]
-      // is issued later), and the buffer (j & 1) was folded by the softmax threads before they
-      // published P of tile j.
-      auto issue_pv = [&](int j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      // is issued later), and the buffer (t & 1) was folded by the softmax threads before they
+      // published P of tile t.
+      auto issue_pv = [&](int t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
         if (!mbar_wait(v_full + 8 * s, ph, abort_ptr)) { give_up(0x23); ok = false; return; }
         const uint32_t vb = v_smem + s * kTileBytes;
         for (int g = 0; g < 2; ++g) {
           if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t o_addr = tmem_o0 + (uint32_t)(g * 2 + (j & 1)) * 64;
+          const uint32_t o_addr = tmem_o0 + (uint32_t)(g * 2 + s) * 64;
           if (BF16) {
             // P: two bf16 per TMEM column, 16 keys = 8 columns per instruction; V: [keys x 64 dims] bf16,
             // one 128-byte swizzled row per key, 16 rows per instruction
@@ -264,14 +292,38 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
               umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
                       make_desc(vb + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1), p.idesc_pv, kk != 0 ? 1u : 0u, false);
           }
-          umma_commit(ofull0 + 8 * (g * 2 + (j & 1)));
+          umma_commit(ofull0 + 8 * (g * 2 + s));
         }
         umma_commit(v_empty + 8 * s);
       };
-      if (ok) issue_qk(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) issue_qk(j + 1);     // the next scores are computed while the softmax warps work on tile j
-        if (ok) issue_pv(j);
+      // An item's first scores: its Q must have landed; once its last scores are issued, the Q tile is handed back.
+      auto first_qk = [&](int ii, int t, int n_kv) {
+        if (!mbar_wait(q_full, ii & 1, abort_ptr)) { give_up(0x21); ok = false; return; }
+        issue_qk(t);
+        if (ok && n_kv == 1) umma_commit(q_empty);
+      };
+      int t = 0;
+      bool started = false;                          // the current item's first scores were issued under the previous item
+      for (int ii = 0; ok; ++ii) {
+        const int w = nth_item(ii);
+        if (w < 0) break;
+        const int w_next = nth_item(ii + 1);
+        const int n_kv = item_of(w).n_kv;
+        if (!started) first_qk(ii, t, n_kv);
+        started = false;
+        for (int j = 0; j < n_kv && ok; ++j) {
+          if (j + 1 < n_kv) {
+            issue_qk(t + j + 1);                     // the next scores are computed while the softmax warps work on tile j
+            if (ok && j + 2 == n_kv) umma_commit(q_empty);
+          } else if (w_next >= 0 && mbar_try_wait(q_full, (ii + 1) & 1) &&
+                     mbar_try_wait(k_full + 8 * ((t + n_kv) & 1), ((t + n_kv) >> 1) & 1)) {
+            // last tile, and the next item's Q and first keys are already here: its first scores go ahead of this P V
+            first_qk(ii + 1, t + n_kv, item_of(w_next).n_kv);
+            started = true;
+          }
+          if (ok) issue_pv(t + j);
+        }
+        t += n_kv;
       }
     }
   } else {
@@ -281,157 +333,182 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int row = quad * 32 + lane;              // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int c0 = group * 64;
-    float o[kHeadDim];
-#pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
-    float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
+    // Merge buffers [2][128][kXStride] behind the rings: a thread leaves the half of its state the other
+    // group finishes in its own row, and later puts its merged result where it read the other group's.
+    float* const xbuf = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
+    float* const mine = xbuf + (size_t)(group * kRows + row) * kXStride;
+    float* const theirs = xbuf + (size_t)((group ^ 1) * kRows + row) * kXStride;
+    const float* const warp_rows = xbuf + (size_t)((group ^ 1) * kRows + quad * 32) * kXStride;   // the 32 rows this warp stores
     bool ok = true;
-    // running output <- running output * alpha + O_part of tile j
-    auto fold = [&](int j, float alpha) {
-      bool got = mbar_wait(ofull0 + 8 * (group * 2 + (j & 1)), (j >> 1) & 1, abort_ptr);
-      if (!got) give_up(0x32);
-      ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
-      if (!ok) return;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t o_addr = tmem_o0 + lane_addr + (uint32_t)(group * 2 + (j & 1)) * 64;
+    int t0 = 0;                                      // tiles of the items before this one
+    for (int ii = 0; ok; ++ii) {
+      const int w = nth_item(ii);
+      if (w < 0) break;
+      const Item it = item_of(w);
+      const int n_kv = it.n_kv;
+      float o[kHeadDim];
 #pragma unroll
-      for (int c = 0; c < kHeadDim; c += 32) {
-        float v[32];
-        tmem_ld32(o_addr + c, v);
+      for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
+      float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
+      // running output <- running output * alpha + O_part of tile t
+      auto fold = [&](int t, float alpha) {
+        bool got = mbar_wait(ofull0 + 8 * (group * 2 + (t & 1)), (t >> 1) & 1, abort_ptr);
+        if (!got) give_up(0x32);
+        ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
+        if (!ok) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t o_addr = tmem_o0 + lane_addr + (uint32_t)(group * 2 + (t & 1)) * 64;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, v[i]);
-      }
-    };
-    for (int j = 0; j < n_kv; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      bool got = mbar_wait(sfull0 + 8 * s, ph, abort_ptr);
-      if (!got) give_up(0x31);
-      ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
-      if (!ok) break;
-      ATTN_STAMP(0, j);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
-      const bool diagonal = j == qt;
-      float va[32], vb[32];
-      tmem_ld32(s_addr, va);
-      tmem_ld32(s_addr + 32, vb);
-      // the scale is positive (checked when the chain was matched), so the maximum commutes with it
-      float mx = -CUDART_INF_F;
-      if (diagonal) {
-        mx = row_max32<true>(va, mx, c0, row);
-        mx = row_max32<true>(vb, mx, c0 + 32, row);
-      } else {
-        mx = row_max32<false>(va, mx, 0, 0);
-        mx = row_max32<false>(vb, mx, 0, 0);
-      }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      // a row with every key of this group masked so far keeps m = -inf: use 0 as the reference point
-      const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;
-      const float alpha = ex2(m_run - m_use);       // 0 while m_run = -inf
-      float sum;
-      if (diagonal) {
-        sum = probabilities32<true>(va, p.scale_log2, m_use, c0, row);
-        sum += probabilities32<true>(vb, p.scale_log2, m_use, c0 + 32, row);
-      } else {
-        sum = probabilities32<false>(va, p.scale_log2, m_use, 0, 0);
-        sum += probabilities32<false>(vb, p.scale_log2, m_use, 0, 0);
-      }
-      if (BF16) {
-        // P rounded to bf16, two keys per 32-bit column: the group's 64 keys take the first 32 columns of
-        // its own 64-column share of the S buffer
-        float packed[32];
+        for (int c = 0; c < kHeadDim; c += 32) {
+          float v[32];
+          tmem_ld32(o_addr + c, v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          __nv_bfloat162 lo = __floats2bfloat162_rn(va[2 * i], va[2 * i + 1]);
-          __nv_bfloat162 hi = __floats2bfloat162_rn(vb[2 * i], vb[2 * i + 1]);
-          packed[i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&lo));
-          packed[16 + i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&hi));
+          for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, v[i]);
         }
-        tmem_st32(s_addr, packed);
-      } else {
-        tmem_st32(s_addr, va);
-        tmem_st32(s_addr + 32, vb);
-      }
-      tmem_st_wait();
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(pfull0 + 8 * (group * 2 + s));
-      ATTN_STAMP(1, j);
-      // fold the PREVIOUS tile's O_part while the tensor pipe works on this one
-      if (j > 0) {
-        fold(j - 1, alpha_prev);
+      };
+      for (int j = 0; j < n_kv; ++j) {
+        const int t = t0 + j;
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        bool got = mbar_wait(sfull0 + 8 * s, ph, abort_ptr);
+        if (!got) give_up(0x31);
+        ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
         if (!ok) break;
+        ATTN_STAMP(0, j);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
+        const bool diagonal = j == it.qt;
+        float va[32], vb[32];
+        tmem_ld32(s_addr, va);
+        tmem_ld32(s_addr + 32, vb);
+        // the scale is positive (checked when the chain was matched), so the maximum commutes with it
+        float mx = -CUDART_INF_F;
+        if (diagonal) {
+          mx = row_max32<true>(va, mx, c0, row);
+          mx = row_max32<true>(vb, mx, c0 + 32, row);
+        } else {
+          mx = row_max32<false>(va, mx, 0, 0);
+          mx = row_max32<false>(vb, mx, 0, 0);
+        }
+        const float m_new = fmaxf(m_run, mx * p.scale_log2);
+        // a row with every key of this group masked so far keeps m = -inf: use 0 as the reference point
+        const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;
+        const float alpha = ex2(m_run - m_use);       // 0 while m_run = -inf
+        float sum;
+        if (diagonal) {
+          sum = probabilities32<true>(va, p.scale_log2, m_use, c0, row);
+          sum += probabilities32<true>(vb, p.scale_log2, m_use, c0 + 32, row);
+        } else {
+          sum = probabilities32<false>(va, p.scale_log2, m_use, 0, 0);
+          sum += probabilities32<false>(vb, p.scale_log2, m_use, 0, 0);
+        }
+        if (BF16) {
+          // P rounded to bf16, two keys per 32-bit column: the group's 64 keys take the first 32 columns of
+          // its own 64-column share of the S buffer
+          float packed[32];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(va[2 * i], va[2 * i + 1]);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(vb[2 * i], vb[2 * i + 1]);
+            packed[i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&lo));
+            packed[16 + i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&hi));
+          }
+          tmem_st32(s_addr, packed);
+        } else {
+          tmem_st32(s_addr, va);
+          tmem_st32(s_addr + 32, vb);
+        }
+        tmem_st_wait();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(pfull0 + 8 * (group * 2 + s));
+        ATTN_STAMP(1, j);
+        // fold the PREVIOUS tile's O_part while the tensor pipe works on this one
+        if (j > 0) {
+          fold(t - 1, alpha_prev);
+          if (!ok) break;
+        }
+        ATTN_STAMP(3, j);
+        alpha_prev = alpha;
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
       }
-      ATTN_STAMP(3, j);
-      alpha_prev = alpha;
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
-    }
-    if (ok) fold(n_kv - 1, alpha_prev);
-    // ---- merge the two groups' states; group g finishes head dims g*32 .. g*32+31 ----
-    // Every MMA has completed (the last O_part arrived after all of them), so the K ring is free.
-    float* xbuf = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);   // [2][128][kXStride], its own 36 KB
-    float* mine = xbuf + (size_t)(group * kRows + row) * kXStride;          // what this thread gives away
-    const float* theirs = xbuf + (size_t)((group ^ 1) * kRows + row) * kXStride;
-    if (ok) {
-      if (group == 0) {
+      if (ok) fold(t0 + n_kv - 1, alpha_prev);
+      t0 += n_kv;
+      // ---- merge the two groups' states; group g finishes head dims g*32 .. g*32+31 ----
+      // The rows this thread is about to overwrite hold what the other group's warp staged for the previous
+      // item: every warp has stored that (first barrier).  Then the states are exchanged (second barrier),
+      // and the merged row goes where the other group's state was read: nobody else looks there.
+      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight softmax warps only
+      if (ok) {
+        if (group == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mine[i] = o[32 + i];
-      } else {
+          for (int q = 0; q < 8; ++q) reinterpret_cast<float4*>(mine)[q] = make_float4(o[32 + 4 * q], o[33 + 4 * q], o[34 + 4 * q], o[35 + 4 * q]);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mine[i] = o[i];
+          for (int q = 0; q < 8; ++q) reinterpret_cast<float4*>(mine)[q] = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+        mine[32] = m_run;
+        mine[33] = l_run;
       }
-      mine[32] = m_run;
-      mine[33] = l_run;
-    }
-    asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight softmax warps only
-    if (ok && !*abort_ptr) {
-      const float m_other = theirs[32], l_other = theirs[33];
-      const float m_all = fmaxf(m_run, m_other);       // finite: key 0 is visible to every row
-      const float w_mine = exp2f(m_run - m_all), w_other = exp2f(m_other - m_all);
-      const float inv = 1.0f / (l_run * w_mine + l_other * w_other);
-      const float a = w_mine * inv, b = w_other * inv;
-      float r[32];
-      if (group == 0) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      // a warp that gave up raised the flag before it arrived here: all eight leave the item loop together
+      if (*abort_ptr) ok = false;
+      if (ok) {
+        const float m_other = theirs[32], l_other = theirs[33];
+        const float m_all = fmaxf(m_run, m_other);       // finite: key 0 is visible to every row
+        const float w_mine = exp2f(m_run - m_all), w_other = exp2f(m_other - m_all);
+        const float inv = 1.0f / (l_run * w_mine + l_other * w_other);
+        const float a = w_mine * inv, b = w_other * inv;
+        if (group == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = o[i] * a + theirs[i] * b;
-      } else {
+          for (int q = 0; q < 8; ++q) {
+            float4 x = reinterpret_cast<float4*>(theirs)[q];
+            x.x = o[4 * q] * a + x.x * b;
+            x.y = o[4 * q + 1] * a + x.y * b;
+            x.z = o[4 * q + 2] * a + x.z * b;
+            x.w = o[4 * q + 3] * a + x.w * b;
+            reinterpret_cast<float4*>(theirs)[q] = x;
+          }
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = o[32 + i] * a + theirs[i] * b;
-      }
-      // A lane holds 32 dims of ONE row: stored from here, a warp instruction would touch 32 lines of 16
-      // bytes each.  The rows go through shared memory instead (the K ring is idle: 128 bytes per row,
-      // the 16-byte slot XORed with the row against bank conflicts) and every store instruction of a
-      // warp then writes four whole 128-byte rows (eight 64-byte rows of the bf16 copy).  Each warp
-      // stores the 32 rows it staged itself, so a warp-level barrier is all it takes.
-      uint8_t* stage = smem_raw + (k_smem - raw) + (size_t)(group * kRows + quad * 32) * 128;
+          for (int q = 0; q < 8; ++q) {
+            float4 x = reinterpret_cast<float4*>(theirs)[q];
+            x.x = o[32 + 4 * q] * a + x.x * b;
+            x.y = o[33 + 4 * q] * a + x.y * b;
+            x.z = o[34 + 4 * q] * a + x.z * b;
+            x.w = o[35 + 4 * q] * a + x.w * b;
+            reinterpret_cast<float4*>(theirs)[q] = x;
+          }
+        }
+        // A lane holds 32 dims of ONE row: stored from here, a warp instruction would touch 32 lines of 16
+        // bytes each.  Read back from shared memory, every store instruction of a warp writes four whole
+        // 128-byte rows (eight 64-byte rows of the bf16 copy).  Each warp stores the 32 rows it merged
+        // itself, so a warp-level barrier is all it takes.
+        __syncwarp();
+        const int64_t first_row = it.row0 + it.q0 + quad * 32;
+        float* dst = p.out + first_row * p.out_row_stride + it.h * kHeadDim + group * 32;
+        __nv_bfloat16* dst16 = p.out16 != nullptr ? p.out16 + first_row * p.out16_row_stride + it.h * kHeadDim + group * 32 : nullptr;
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        *reinterpret_cast<float4*>(stage + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-      __syncwarp();
-      const int64_t first_row = row0 + q0 + quad * 32;
-      float* dst = p.out + first_row * p.out_row_stride + h * kHeadDim + group * 32;
-      __nv_bfloat16* dst16 = p.out16 != nullptr ? p.out16 + first_row * p.out16_row_stride + h * kHeadDim + group * 32 : nullptr;
+        for (int i8 = 0; i8 < 8; ++i8) {
+          const int rr = i8 * 4 + (lane >> 3), q = lane & 7;
+          const float4 t4 = reinterpret_cast<const float4*>(warp_rows + rr * kXStride)[q];
+          *reinterpret_cast<float4*>(dst + (int64_t)rr * p.out_row_stride + 4 * q) = t4;
+        }
+        if (dst16 != nullptr) {
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int rr = it * 4 + (lane >> 3), q = lane & 7;
-        const float4 t = *reinterpret_cast<const float4*>(stage + rr * 128 + ((q ^ (rr & 7)) << 4));
-        *reinterpret_cast<float4*>(dst + (int64_t)rr * p.out_row_stride + 4 * q) = t;
-      }
-      if (dst16 != nullptr) {
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int rr = it * 8 + (lane >> 2), c = lane & 3;       // 8 dims = 16 bytes of bf16 per lane
-          const float4 lo = *reinterpret_cast<const float4*>(stage + rr * 128 + (((2 * c) ^ (rr & 7)) << 4));
-          const float4 hi = *reinterpret_cast<const float4*>(stage + rr * 128 + (((2 * c + 1) ^ (rr & 7)) << 4));
-          __nv_bfloat162 w0 = __floats2bfloat162_rn(lo.x, lo.y), w1 = __floats2bfloat162_rn(lo.z, lo.w);
-          __nv_bfloat162 w2 = __floats2bfloat162_rn(hi.x, hi.y), w3 = __floats2bfloat162_rn(hi.z, hi.w);
-          uint4 packed;
-          packed.x = *reinterpret_cast<uint32_t*>(&w0);
-          packed.y = *reinterpret_cast<uint32_t*>(&w1);
-          packed.z = *reinterpret_cast<uint32_t*>(&w2);
-          packed.w = *reinterpret_cast<uint32_t*>(&w3);
-          *reinterpret_cast<uint4*>(dst16 + (int64_t)rr * p.out16_row_stride + 8 * c) = packed;
+          for (int i4 = 0; i4 < 4; ++i4) {
+            const int rr = i4 * 8 + (lane >> 2), c = lane & 3;       // 8 dims = 16 bytes of bf16 per lane
+            const float4 lo = reinterpret_cast<const float4*>(warp_rows + rr * kXStride)[2 * c];
+            const float4 hi = reinterpret_cast<const float4*>(warp_rows + rr * kXStride)[2 * c + 1];
+            __nv_bfloat162 w0 = __floats2bfloat162_rn(lo.x, lo.y), w1 = __floats2bfloat162_rn(lo.z, lo.w);
+            __nv_bfloat162 w2 = __floats2bfloat162_rn(hi.x, hi.y), w3 = __floats2bfloat162_rn(hi.z, hi.w);
+            uint4 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&w0);
+            packed.y = *reinterpret_cast<uint32_t*>(&w1);
+            packed.z = *reinterpret_cast<uint32_t*>(&w2);
+            packed.w = *reinterpret_cast<uint32_t*>(&w3);
+            *reinterpret_cast<uint4*>(dst16 + (int64_t)rr * p.out16_row_stride + 8 * c) = packed;
+          }
         }
       }
     }
@@ -445,8 +522,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     unsigned long long g;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
     printf("ATTN block0 globaltimer start %lld end %lld (ns) dur %lld | exit cycles %lld n_kv %d\n", marks[0], (long long)g,
-           (long long)g - marks[0], clock64() - marks[1], n_kv);
-    for (int j = 0; j < n_kv && j < 16; ++j)
+           (long long)g - marks[0], clock64() - marks[1], item_of(blockIdx.x).n_kv);
+    for (int j = 0; j < item_of(blockIdx.x).n_kv && j < 16; ++j)
       printf("kv %2d  s_ready %7lld p_stored %7lld folded %7lld\n", j, trace[0][j] - marks[1], trace[1][j] - marks[1],
              trace[3][j] - marks[1]);
   }
@@ -626,7 +703,8 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   p.idesc_pv = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
   p.kernel_index = (int)c.first;
   p.status = plan.d_status;
-  st->grid = dim3((unsigned)(B * H * p.q_tiles), 1, 1);
+  const int64_t items = B * H * p.q_tiles;
+  st->grid = dim3((unsigned)(items < plan.sm_count ? items : plan.sm_count), 1, 1);     // persistent: at most one CTA per SM
 
   for (PlanKernel* k : c.matmuls) destroy_matmul(*k);
   PlanKernel& holder = plan.kernels[c.first];
