@@ -331,6 +331,9 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             for (int k = 0; k < 4; ++k) {
               const uint64_t adesc = ((uint64_t)a_hi << 32) | (a_lo_fixed | ((a16 + (uint32_t)(j * (kPairATileBytes >> 4) + 2 * k)) & 0x3FFFu));
               const uint64_t bdesc = ((uint64_t)b_hi << 32) | (b_lo_fixed | ((b16 + (uint32_t)j * b_slab16 + (uint32_t)k * b_step16) & 0x3FFFu));
+#ifdef KB200_TRACE
+              if (!(p.debug & 32))
+#endif
               umma_pair<BF16>(tmem_d, adesc, bdesc, idesc, accumulate);
               accumulate = 1;
 #ifdef KB200_TRACE

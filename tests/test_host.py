@@ -18,9 +18,11 @@ from kiln_b200.codegen import launches_of, program_from_plan
 from kiln_b200.spec import PlanSpec
 
 ROOT = Path(__file__).resolve().parent.parent
-REFERENCE = Path(os.environ.get("KILN_REFERENCE", "/root/reference"))
+# the reference as installed beside this package (baseline/install_reference.py), or a checkout named by KILN_REFERENCE
+REFERENCE = Path(os.environ.get("KILN_REFERENCE", ROOT / "baseline" / "_ref"))
+REFERENCE_TESTS = REFERENCE / "tests" if (REFERENCE / "tests" / "models").is_dir() else REFERENCE / "kiln_tests"
 needs_reference = pytest.mark.skipif(not (REFERENCE / "kiln" / "api.py").exists(),
-                                     reason="reference checkout not present")
+                                     reason="the reference is neither installed under baseline/_ref nor named by KILN_REFERENCE")
 
 
 @pytest.fixture(scope="session")
@@ -117,7 +119,7 @@ def test_generate_on_a_live_reference_graph_reproduces_the_golden_plan():
     """kiln.compile's own frontend and passes, then this package's generate(): bit-identical plan."""
     code = f"""
 import sys, json
-sys.path[:0] = [{str(ROOT / 'kiln-compiler_b200')!r}, {str(REFERENCE)!r}, {str(REFERENCE / 'tests')!r}]
+sys.path[:0] = [{str(ROOT / 'kiln-compiler_b200')!r}, {str(REFERENCE)!r}, {str(REFERENCE_TESTS)!r}]
 import torch, kiln_b200
 kiln = kiln_b200.install()
 from kiln.api import Options, build_passes
