@@ -565,6 +565,10 @@ static void fold_operand_copies(Plan& plan) {
 // matmul's (row, column); nothing else reads the matmul's output before it is rewritten; and the
 // output does not lie over anything the matmul still reads (variants (a) and (b) below).  The plan
 // (kernel list, offsets) is untouched: the elementwise kernel stays in it and launches nothing.
+// The same for the short chain in front of a register-resident row kernel (LayerNorm(x + matmul),
+// the residual add before the second LayerNorm of a block): the matmul then writes the chain's value
+// -- into the row kernel's second output where it has one, else into its own buffer -- and the row
+// kernel reads it from there and keeps its reductions only.
 static void absorb_elementwise(Plan& plan) {
   // from the last matmul to the first: what a later matmul no longer writes (its own output, once it
   // has taken over an elementwise kernel's) is known when an earlier one looks at its readers
@@ -572,10 +576,13 @@ static void absorb_elementwise(Plan& plan) {
     PlanKernel& m = plan.kernels[j];
     PlanKernel& e = plan.kernels[j + 1];
     if (m.impl != IMPL_MM_TC || !m.has_chain || m.chain.first_slot != -1 || m.batch != 1) continue;
-    if (e.desc.kclass != KB200_K_ELEMENTWISE || e.impl == IMPL_FUSED_AWAY || !e.has_chain || e.chain.first_slot < 0) continue;
-    if (numel_of(e.desc) != m.M * m.N || m.chain.n + e.chain.n > kMaxChain) continue;
+    const bool row = e.desc.kclass == KB200_K_ROW && (e.impl == IMPL_ROW_LAYERNORM || e.impl == IMPL_ROW_SOFTMAX) && e.row_pre.n >= 1;
+    if (!row && (e.desc.kclass != KB200_K_ELEMENTWISE || e.impl == IMPL_FUSED_AWAY || !e.has_chain || e.chain.first_slot < 0)) continue;
+    const Chain e_chain = row ? e.row_pre : e.chain;
+    const int e_out_slot = row ? e.pre_out_slot : e.chain.out_slot;      // a row kernel need not store the chain's value
+    if (numel_of(e.desc) != m.M * m.N || m.chain.n + e_chain.n > kMaxChain) continue;
     if (m.desc.operands[m.chain.out_slot].base_kind != KB200_BASE_ARENA) continue;   // a plan output must be written
-    {
+    if (!row) {
       std::vector<int> reads, writes;
       reads_and_writes(e, &reads, &writes);
       if (writes.size() != 1) continue;
@@ -621,7 +628,8 @@ static void absorb_elementwise(Plan& plan) {
     };
     // where the matmul's value enters the elementwise chain: as its first value, or as the other
     // argument of its first step
-    Chain tail = e.chain;
+    Chain tail = e_chain;
+    const int acc_slot = is_matmul_output(tail.first_slot) ? tail.first_slot : (tail.n >= 1 ? tail.steps[0].slot : -1);
     if (!is_matmul_output(tail.first_slot)) {
       if (tail.n < 1 || tail.steps[0].slot < 0 || !is_matmul_output(tail.steps[0].slot)) continue;
       int swapped;
@@ -680,7 +688,7 @@ static void absorb_elementwise(Plan& plan) {
       }
       merged.chain.steps[merged.chain.n++] = step;
     }
-    if (!ok || !linear(e.ops[e.chain.out_slot], &s_m, &s_n)) continue;
+    if (!ok || (e_out_slot >= 0 && !linear(e.ops[e_out_slot], &s_m, &s_n))) continue;
     // While the matmul runs its operands are still being read: its output may coincide with a side
     // operand element for element (an add in place), and must not touch anything else the kernel reads.
     auto output_is_safe = [&](const PlanKernel& cand) {
@@ -695,10 +703,28 @@ static void absorb_elementwise(Plan& plan) {
       }
       return true;
     };
+    if (row) {
+      // the chain's value goes to the row kernel's second output, or stays in the matmul's own buffer;
+      // the row kernel reads it there and runs its reductions only
+      PlanKernel cand = merged;
+      if (e_out_slot >= 0) {
+        DevOperand out{};
+        out.ptr = e.ops[e_out_slot].ptr;
+        out.stride[1] = s_m;
+        out.stride[2] = s_n;
+        cand.ops[cand.chain.out_slot] = out;
+      }
+      if (acc_slot < 0 || !output_is_safe(cand) || !tc_eligible(cand)) continue;
+      m = cand;
+      e.x_slot = e_out_slot >= 0 ? e_out_slot : acc_slot;
+      e.row_pre.n = 0;
+      e.pre_out_slot = -1;
+      continue;
+    }
     // (a) the matmul writes the elementwise kernel's output where the plan put it
     PlanKernel direct = merged;
     DevOperand out{};
-    out.ptr = e.ops[e.chain.out_slot].ptr;
+    out.ptr = e.ops[e_out_slot].ptr;
     out.stride[1] = s_m;
     out.stride[2] = s_n;
     direct.ops[direct.chain.out_slot] = out;
@@ -713,10 +739,10 @@ static void absorb_elementwise(Plan& plan) {
     // the value stays in the matmul's own output buffer instead, and the kernels that read the
     // elementwise kernel's output read it there.  Needs the same layout in both buffers, every such
     // reader inside that output, and the matmul's buffer untouched for as long as the value is live.
-    const DevOperand eo = e.ops[e.chain.out_slot];
-    if (e.desc.operands[e.chain.out_slot].base_kind != KB200_BASE_ARENA || s_n != 1 || s_m != m.N || (mo.ptr - eo.ptr) % 32 != 0) continue;
+    const DevOperand eo = e.ops[e_out_slot];
+    if (e.desc.operands[e_out_slot].base_kind != KB200_BASE_ARENA || s_n != 1 || s_m != m.N || (mo.ptr - eo.ptr) % 32 != 0) continue;
     if (!output_is_safe(merged) || !tc_eligible(merged)) continue;
-    const Span eo_span = span_of(e, e.chain.out_slot);
+    const Span eo_span = span_of(e, e_out_slot);
     std::vector<std::pair<size_t, int>> redirect;
     bool dead = false;
     for (size_t i = j + 2; i < plan.kernels.size() && ok && !dead; ++i) {
