@@ -791,7 +791,9 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
   p.out16 = out16;
   p.store32 = store32 ? 1 : 0;
   p.slot_bytes = slot_bytes_wanted;
-  p.slots = p.res_step < 0 ? 1 : (out16 ? 2 : 3);   // the third slot lets a residual fly one block ahead
+  // the third slot lets a residual fly one block ahead; with a long K loop the ring has more use for the
+  // memory (an epilogue per 48 steps, and operands that stream from DRAM want depth: 4 -> 5 stages)
+  p.slots = p.res_step < 0 ? 1 : ((out16 || p.num_kb >= 24) ? 2 : 3);
   const int stage_bytes = kps * (kPairATileBytes + p.half_bn * 128);
   // a third slot only where it does not cost the ring its third stage
   if (p.slots == 3 && 3 * stage_bytes + kPairEpiWarps * 3 * p.slot_bytes + 1024 > kPairSmemCeiling) p.slots = 2;
