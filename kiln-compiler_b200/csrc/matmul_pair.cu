@@ -47,11 +47,12 @@ namespace {
 
 using namespace tc;
 
-constexpr int kPairThreads = 384;
-constexpr int kPairEpiWarps = 8;
-constexpr int kPairFirstEpiWarp = 4;
+constexpr int kPairThreads = 512;
+constexpr int kPairEpiWarps = 12;
+constexpr int kPairFirstEpiWarp = 2;
+constexpr int kPairWarpsPerQuad = kPairEpiWarps / 4;
+constexpr int kPairBlocksPerWarp = (8 + kPairWarpsPerQuad - 1) / kPairWarpsPerQuad;   // 32-column blocks of a 256-column tile
 constexpr int kPairMaxStages = 8;
-constexpr int kPairMaxSlots = 4;
 constexpr int kPairATileBytes = 128 * 128;        // 128 rows x one 128-byte K slab
 #ifdef KB200_TRACE
 constexpr int kPairSmemCeiling = 200 * 1024;      // the trace arrays take static shared memory
@@ -62,7 +63,7 @@ constexpr int kPairSmemCeiling = 225 * 1024;      // opt-in ceiling, the same fo
 #endif
 // barrier indices
 constexpr int kBarFull = 0, kBarEmpty = kPairMaxStages, kBarTFull = 2 * kPairMaxStages, kBarTEmpty = kBarTFull + 2,
-              kBarRes = kBarTEmpty + 2, kBarCount = kBarRes + kPairEpiWarps * kPairMaxSlots;
+              kBarRes = kBarTEmpty + 2, kBarCount = kBarRes + kPairEpiWarps;
 
 enum : int { SIDE_NONE = 0, SIDE_IMM = 1, SIDE_COL = 2, SIDE_RES = 3 };
 
@@ -203,8 +204,8 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   cluster_arrive();
   if (lane == 0 && warp < 2)
     asm volatile("" ::"r"(p.bn), "r"(p.idesc), "r"(p.num_tiles), "l"(p.magic_tn), "l"(p.magic_tpb), "l"(p.status) : "memory");
-  if (warp == 3 && lane < kMaxChain) chain_steps[lane] = p.steps[lane];
-  if (warp == 2) {
+  if (warp == 2 && lane < kMaxChain) chain_steps[lane] = p.steps[lane];
+  if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                  "r"((uint32_t)p.tmem_cols)
                  : "memory");
@@ -358,65 +359,57 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (ok) umma_pair_commit(tfull0 + 8 * acc);
       }
     }
-  } else if (warp >= kPairFirstEpiWarp) {
-    // ---------------- epilogue (warps 4..11) ----------------
-    // Two warps per TMEM lane quadrant (a warp may only touch lanes 32 * (warp % 4) ..+31); the pair
-    // takes alternate 32-column blocks of the tile.
-    const int e = warp - kPairFirstEpiWarp, quad = warp & 3, half = e >> 2;
-    const int nblk = p.bn >> 6;
-    const int slots = p.slots, slot_bytes = p.slot_bytes;
-    const uint32_t slot0 = epi_base + (uint32_t)(e * slots * slot_bytes);
+  } else if (warp >= kPairFirstEpiWarp && warp < kPairFirstEpiWarp + kPairEpiWarps) {
+    // ---------------- epilogue (warps 2..17) ----------------
+    // Four warps per TMEM lane quadrant (a warp may only touch lanes 32 * (warp % 4) ..+31); warp g of a
+    // quadrant takes the 32-column blocks g, g + 4 of the tile.  Sixteen warps, because the epilogue is
+    // bound by instruction issue and by the latencies inside a pass (tensor-memory load, the wait for
+    // the slot's last store, the proxy fence): with two warps per scheduler the schedulers issued in
+    // 46 % of the cycles, a probe of independent multiply-adds in 90 %.
+    const int e = warp - kPairFirstEpiWarp, quad = warp & 3, group = e >> 2;
+    const int slot_bytes = p.slot_bytes;
+    const uint32_t slot0 = epi_base + (uint32_t)(e * slot_bytes);
     uint8_t* const slot0_ptr = smem_raw + (slot0 - raw);
-    const uint32_t res0 = smem_u32(&bars[kBarRes + e * kPairMaxSlots]);
+    const uint32_t res_bar = smem_u32(&bars[kBarRes + e]);
     const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
     const bool has_res = p.res_step >= 0, with16 = p.out16 != nullptr, with32 = p.store32 != 0;
-    const int allowed = has_res ? slots - 2 : slots - 1;   // store groups that may be in flight when a slot is reused
-    // The first per-column operand of the chain (a bias) is fetched for the whole tile before its
-    // accumulator is ready: lane l holds column l of each of this warp's blocks, and the chain takes
-    // value q from lane q by shuffle (one coalesced 128-byte load per block instead of eight
-    // broadcast loads whose L2 latency sat in front of every block's arithmetic).
+    // where the block's per-column operand passes through shared memory (-1: broadcast by shuffles)
+    const int scratch_off = !has_res ? 0 : (with16 ? 4096 : -1);
     const int n_steps = p.n_steps;
     int col_step = -1;
     for (int s = 0; s < n_steps && col_step < 0; ++s)
       if (chain_steps[s].kind == SIDE_COL) col_step = s;
-    float col_pre[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t res_phase = 0;        // one parity bit per slot
-    int slot = 0;                  // slot of the next block this warp stages
-    bool res_ready = false;        // the residual of the next block has been requested into `slot`
+    float col_pre[kPairBlocksPerWarp];
+#pragma unroll
+    for (int j = 0; j < kPairBlocksPerWarp; ++j) col_pre[j] = 0.0f;
+    uint32_t res_phase = 0;
     bool ok = true;
     int i = 0;
     bool dry = true;               // the rehearsal pass described at the tile loop
-    auto request_residual = [&](int into, int n, int m_first, int batch) {
-      if (lane == 0) {
-        const uint32_t bar = res0 + 8 * into;
-        mbar_expect_tx(bar, 4096);
-        tma_load_3d(slot0 + (uint32_t)(into * slot_bytes), &tma_res, bar, n, m_first, p.res_batched ? batch : 0);
-      }
-    };
     // The fused chain on one 32 x 32 block held a lane per row (v[q] = column n + q of this lane's row).
-    auto run_chain = [&](float (&v)[32], int j, int n, int batch, const uint8_t* sf, int res_slot, const float4* col_smem = nullptr) {
+    auto run_chain = [&](float (&v)[32], float mine, int n, int batch) {
       for (int s = 0; s < n_steps; ++s) {
         const PairStep st = chain_steps[s];
         float side[32];
         if (st.kind == SIDE_RES) {
           if (!dry) {
-            bool landed = mbar_wait(res0 + 8 * res_slot, (res_phase >> res_slot) & 1u, abort_ptr);
+            bool landed = mbar_wait(res_bar, res_phase, abort_ptr);
             if (!landed && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 5); *abort_ptr = 1; }
-            res_phase ^= 1u << res_slot;
+            res_phase ^= 1u;
           }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            const float4 t = *reinterpret_cast<const float4*>(sf + lane * 128 + ((q ^ (lane & 7)) << 4));
+            const float4 t = *reinterpret_cast<const float4*>(slot0_ptr + lane * 128 + ((q ^ (lane & 7)) << 4));
             side[4 * q] = t.x; side[4 * q + 1] = t.y; side[4 * q + 2] = t.z; side[4 * q + 3] = t.w;
           }
-        } else if (s == col_step && col_smem != nullptr) {
+        } else if (s == col_step && scratch_off >= 0) {
+          const float4* col_smem = reinterpret_cast<const float4*>(slot0_ptr + scratch_off);
 #pragma unroll
           for (int q = 0; q < 8; ++q) {        // every lane reads the same 16 bytes: a broadcast
             const float4 t = col_smem[q];
             side[4 * q] = t.x; side[4 * q + 1] = t.y; side[4 * q + 2] = t.z; side[4 * q + 3] = t.w;
           }
         } else if (s == col_step) {
-          const float mine = j == 0 ? col_pre[0] : j == 1 ? col_pre[1] : j == 2 ? col_pre[2] : col_pre[3];
 #pragma unroll
           for (int q = 0; q < 32; ++q) side[q] = __shfl_sync(0xffffffffu, mine, q);
         } else if (st.kind == SIDE_COL) {
@@ -434,10 +427,10 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
     };
     // The first pass over the loop body is a rehearsal: while the first tile is still being multiplied
-    // the warp runs one strip (or block) of the same instructions on whatever tensor memory holds, waits
-    // for nothing, requests nothing and stores nothing.  The kernel's code is cold at every launch, and
-    // the instruction-cache misses of the first real epilogue (~10 000 cycles against ~4 000 warm) would
-    // otherwise hold back the accumulator the main loop needs two tiles later.
+    // the warp runs one block of the same instructions on whatever tensor memory holds, waits for
+    // nothing, requests nothing and stores nothing.  The kernel's code is cold at every launch, and the
+    // instruction-cache misses of the first real epilogue would otherwise hold back the accumulator the
+    // main loop needs two tiles later.
     for (int tile = pair; tile < p.num_tiles && ok;) {
       const int batch = pair_div(tile, p.magic_tpb);
       const int rem = tile - batch * p.tiles_per_batch;
@@ -448,25 +441,28 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int m_first = tm_i * 256 + (int)rank * 128 + quad * 32;
       const int n0 = tn_i * p.bn;
       const bool rows_ok = m_first < p.M;
+      // the first per-column operand of the chain (a bias) is fetched for this warp's blocks before the
+      // accumulator is ready: lane l holds column l of each block, one coalesced 128-byte load per block
       if (col_step >= 0 && rows_ok) {
-        const float* src = chain_steps[col_step].ptr + (int64_t)batch * chain_steps[col_step].batch_stride + n0;
+        const float* src = chain_steps[col_step].ptr + (int64_t)batch * chain_steps[col_step].batch_stride + n0 + lane;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          // block j of this warp: alternate 32-column blocks with a matrix operand, else the halves of
-          // alternate 64-column strips
-          const int c = has_res ? half * 32 + 64 * j + lane : half * 64 + 128 * (j >> 1) + 32 * (j & 1) + lane;
-          if (j < nblk) col_pre[j] = n0 + c < p.N ? __ldg(src + c) : 0.0f;
+        for (int j = 0; j < kPairBlocksPerWarp; ++j) {
+          const int c = 32 * (group + kPairWarpsPerQuad * j);
+          col_pre[j] = (c < p.bn && n0 + c + lane < p.N) ? __ldg(src + c) : 0.0f;
         }
       }
-      // the first block's residual is requested before the accumulator is ready
-      if (has_res && !dry && !res_ready && rows_ok && n0 + half * 32 < p.N) {
-        if (lane == 0) store_wait_read(allowed);
-        __syncwarp();
-        request_residual(slot, n0 + half * 32, m_first, batch);
+      // the first block's matrix operand is requested before the accumulator is ready
+      bool res_ready = false;
+      if (has_res && !dry && rows_ok && 32 * group < p.bn && n0 + 32 * group < p.N) {
+        if (lane == 0) {
+          store_wait_read(0);
+          mbar_expect_tx(res_bar, 4096);
+          tma_load_3d(slot0, &tma_res, res_bar, n0 + 32 * group, m_first, p.res_batched ? batch : 0);
+        }
         res_ready = true;
       }
       if (!dry) {
-        bool got = mbar_wait_cluster(tfull0 + 8 * acc, aph, abort_ptr);
+        bool got = mbar_wait_cluster_relaxed(tfull0 + 8 * acc, aph, abort_ptr);
         if (!got && lane == 0 && !*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | 3); *abort_ptr = 1; }
         ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0 && !*abort_ptr;
         if (!ok) break;
@@ -475,126 +471,58 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #ifdef KB200_TRACE
       if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-      // Without a matrix operand a pass takes a strip of 64 columns (the warps of a quadrant take
-      // alternate strips): the fixed latencies of a pass -- tensor-memory load, the wait for the
-      // staging area's last stores, the proxy fence, the store issue -- are paid once per strip, and
-      // the strip's bf16 mirror is one box of 128-byte rows.  Staging area of a warp: two float32
-      // blocks (unless only the mirror is stored), then the bf16 box.
-      for (int j = 0; !has_res && j < nblk; j += 2) {
-        const int c = half * 64 + 64 * j;
+#pragma unroll 1
+      for (int j = 0; j < kPairBlocksPerWarp; ++j) {
+        const int c = 32 * (group + kPairWarpsPerQuad * j);
         const int n = n0 + c;
-        if (!rows_ok || n >= p.N) break;             // uniform across the warp
-        const bool two = n + 32 < p.N;
-        const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c);
-        float v[32], w[32];
+        if (c >= p.bn || !rows_ok || n >= p.N) break;          // uniform across the warp
+        float mine = col_pre[0];
+#pragma unroll
+        for (int q = 1; q < kPairBlocksPerWarp; ++q)
+          if (j == q) mine = col_pre[q];
+        // the slot's last bulk stores have finished reading it
+        if (lane == 0) store_wait_read(0);
+        __syncwarp();
+        // a full-matrix operand of the chain (residual, mask) is brought INTO the slot by a bulk tensor
+        // load, under the tensor-memory load below
+        if (has_res && !dry && !(j == 0 && res_ready) && lane == 0) {
+          mbar_expect_tx(res_bar, 4096);
+          tma_load_3d(slot0, &tma_res, res_bar, n, m_first, p.res_batched ? batch : 0);
+        }
+        if (col_step >= 0 && scratch_off >= 0) reinterpret_cast<float*>(slot0_ptr + scratch_off)[lane] = mine;
+        float v[32];
 #ifdef KB200_TRACE
         if (p.debug & 4) {
 #pragma unroll
-          for (int q = 0; q < 32; ++q) v[q] = w[q] = 1.0f;
+          for (int q = 0; q < 32; ++q) v[q] = 1.0f;
         } else
 #endif
-        if (two) {
-          tmem_ld32x2(t_addr, t_addr + 32, v, w);
-        } else {
-          tmem_ld32(t_addr, v);
-#pragma unroll
-          for (int q = 0; q < 32; ++q) w[q] = 0.0f;
-        }
-#ifdef KB200_TRACE
-        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
-#endif
-        // the staging area's last bulk stores had the load above to finish reading it
-        if (lane == 0) store_wait_read(0);
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
         __syncwarp();
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-        // the strip's per-column operand goes through the (still free) staging area: written once by
-        // the lanes that fetched it, read back as broadcasts
-        float* const col_smem = reinterpret_cast<float*>(slot0_ptr);
-        if (col_step >= 0) {
-          col_smem[lane] = j == 0 ? col_pre[0] : col_pre[2];
-          col_smem[32 + lane] = j == 0 ? col_pre[1] : col_pre[3];
-          __syncwarp();
-        }
-        run_chain(v, j, n, batch, slot0_ptr, 0, reinterpret_cast<const float4*>(col_smem));
-        if (two) run_chain(w, j + 1, n + 32, batch, slot0_ptr, 0, reinterpret_cast<const float4*>(col_smem + 32));
+        run_chain(v, mine, n, batch);
         __syncwarp();
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
-        uint8_t* const sh = slot0_ptr + (with32 ? 8192 : 0);
-#ifdef KB200_TRACE
-        if (!(p.debug & 2)) {
-#endif
-        if (with32) {
-          stage_rows(slot0_ptr, nullptr, v, lane, false);
-          if (two) stage_rows(slot0_ptr + 4096, nullptr, w, lane, false);
-        }
-        if (with16) stage_rows_bf16x64(sh, v, w, lane);
+        stage_rows(slot0_ptr, slot0_ptr + (with32 || has_res ? 4096 : 0), v, lane, with16, with32);
         fence_async_smem();
-#ifdef KB200_TRACE
-        } else if (v[0] + w[1] == 12345.0f) slot0_ptr[lane] = 1;
-#endif
         __syncwarp();
 #ifdef KB200_TRACE
         if (lane == 0 && !dry && !(p.debug & 1)) {
 #else
         if (lane == 0 && !dry) {
 #endif
-          if (with32) {
-            tma_store_3d(&tma_out, slot0, n, m_first, batch);
-            if (two) tma_store_3d(&tma_out, slot0 + 4096, n + 32, m_first, batch);
-          }
-          if (with16) tma_store_3d(&tma_out16, slot0 + (with32 ? 8192u : 0u), n, m_first, batch);
+          if (with32) tma_store_3d(&tma_out, slot0, n, m_first, batch);
+          if (with16) tma_store_3d(&tma_out16, slot0 + (with32 || has_res ? 4096u : 0u), n, m_first, batch);
           tma_store_commit();
         }
 #ifdef KB200_TRACE
         if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
 #endif
         if (dry) break;
-      }
-      for (int j = 0; has_res && j < nblk; ++j) {
-        const int c = half * 32 + 64 * j;
-        const int n = n0 + c;
-        if (!rows_ok || n >= p.N) continue;          // uniform across the warp
-        float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.bn + c), v);
-#ifdef KB200_TRACE
-        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
-#endif
-        // the bulk stores that last used this slot and the next one have read them
-        if (lane == 0) store_wait_read(allowed);
-        __syncwarp();
-#ifdef KB200_TRACE
-        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
-#endif
-        if (!dry && !res_ready) request_residual(slot, n, m_first, batch);
-        res_ready = false;
-        const int next_slot = slot + 1 == slots ? 0 : slot + 1;
-        if (!dry && j + 1 < nblk && n + 64 < p.N) {       // the next block's residual flies under this block's arithmetic
-          request_residual(next_slot, n + 64, m_first, batch);
-          res_ready = true;
-        }
-        uint8_t* const sf = slot0_ptr + slot * slot_bytes;
-        run_chain(v, j, n, batch, sf, slot);
-#ifdef KB200_TRACE
-        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
-#endif
-        stage_rows(sf, sf + 4096, v, lane, with16, with32);
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0 && !dry) {
-          const uint32_t src = slot0 + (uint32_t)(slot * slot_bytes);
-          if (with32) tma_store_3d(&tma_out, src, n, m_first, batch);
-          if (with16) tma_store_3d(&tma_out16, src + 4096, n, m_first, batch);
-          tma_store_commit();
-        }
-#ifdef KB200_TRACE
-        if (warp == 4 && lane == 0) { PAIR_STAMP(4, te); ++te; }
-#endif
-        if (dry) break;
-        slot = next_slot;
       }
       if (dry) {
         dry = false;
@@ -634,7 +562,7 @@ mm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // neither CTA leaves (or frees TMEM the other's MMAs write) before both are done
   cluster_arrive();
   cluster_wait();
-  if (warp == 2) {
+  if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
   }
@@ -746,15 +674,13 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
     }
   }
   while (bn > 128 && bn / 2 >= k.N) bn /= 2;
-  // Staging per epilogue warp.  With a matrix operand: rotating slots of one float32 block and its
-  // bf16 copy.  Without: one area for a 64-column strip, two float32 blocks (unless only the mirror is
-  // stored) and the strip's bf16 box.
+  // Staging per epilogue warp: one slot for a 32 x 32 block, float32 (also where a matrix operand of
+  // the chain lands; left out when only the mirror is stored) and its bf16 copy.
   const bool store32 = !(k.mirror_only && out16 != nullptr);
-  const int slot_bytes_wanted = p.res_step >= 0 ? (out16 ? 4096 + 2048 : 4096) : (store32 ? 8192 : 0) + (out16 ? 4096 : 0);
-  const int min_slots = p.res_step >= 0 ? 2 : 1;
+  const int slot_bytes_wanted = ((store32 || p.res_step >= 0) ? 4096 : 0) + (out16 ? 2048 : 0);
   // two slabs per step where the ring still has three stages beside the staging slots
   if (kps == 0)
-    kps = bn <= 128 && slabs >= 4 && 3 * 2 * (kPairATileBytes + bn / 2 * 128) + kPairEpiWarps * min_slots * slot_bytes_wanted + 1024 <= kPairSmemCeiling ? 2 : 1;
+    kps = bn <= 128 && slabs >= 4 && 3 * 2 * (kPairATileBytes + bn / 2 * 128) + kPairEpiWarps * slot_bytes_wanted + 1024 <= kPairSmemCeiling ? 2 : 1;
   p.bn = bn;
   p.half_bn = bn / 2;
   p.slab_k = slab_k;
@@ -791,13 +717,9 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
   p.out16 = out16;
   p.store32 = store32 ? 1 : 0;
   p.slot_bytes = slot_bytes_wanted;
-  // the third slot lets a residual fly one block ahead; with a long K loop the ring has more use for the
-  // memory (an epilogue per 48 steps, and operands that stream from DRAM want depth: 4 -> 5 stages)
-  p.slots = p.res_step < 0 ? 1 : ((out16 || p.num_kb >= 24) ? 2 : 3);
+  p.slots = 1;
   const int stage_bytes = kps * (kPairATileBytes + p.half_bn * 128);
-  // a third slot only where it does not cost the ring its third stage
-  if (p.slots == 3 && 3 * stage_bytes + kPairEpiWarps * 3 * p.slot_bytes + 1024 > kPairSmemCeiling) p.slots = 2;
-  const int epi_bytes = kPairEpiWarps * p.slots * p.slot_bytes;
+  const int epi_bytes = kPairEpiWarps * p.slot_bytes;
   int stages = d.cfg[3] > 0 ? d.cfg[3] : kPairMaxStages;
   if (stages > kPairMaxStages) stages = kPairMaxStages;
   while (stages > 2 && (size_t)stages * stage_bytes + epi_bytes + 1024 > (size_t)kPairSmemCeiling) --stages;
@@ -823,7 +745,7 @@ int pair_bind(Plan& plan, PlanKernel& k, int kernel_index, const PairOperands& o
   if (ok) ok = encode_map_store(&st->map_out, false, O.ptr, k.N, k.M, k.batch, O.stride[1], O.stride[0]);
   st->map_out16 = st->map_out;
   st->map_res = st->map_out;
-  if (ok && out16) ok = encode_map_store(&st->map_out16, true, out16, k.N, k.M, k.batch, O.stride[1], O.stride[0], p.res_step < 0);
+  if (ok && out16) ok = encode_map_store(&st->map_out16, true, out16, k.N, k.M, k.batch, O.stride[1], O.stride[0]);
   if (ok && res) ok = encode_map_store(&st->map_res, false, res->ptr, k.N, k.M, p.res_batched ? k.batch : 1, res->stride[1], res->stride[0]);
   if (!ok) { delete st; return KB200_OK; }
   st->kernel = ops.bf16 ? (kps == 2 ? mm_pair_kernel<true, 2> : mm_pair_kernel<true, 1>)

@@ -205,6 +205,17 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   }
   return false;
 }
+// The same for a wait that is expected to last (an epilogue warp waiting for its tile): the thread
+// sleeps between polls, so that sixteen waiting warps leave the issue slots and the barrier's
+// shared-memory bank to the threads that feed the tensor cores.
+__device__ __forceinline__ bool mbar_wait_cluster_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    __nanosleep(100);
+    if ((i & 63) == 63 && *abort_flag) return false;
+  }
+  return false;
+}
 // Shared-memory address of the same location in the CTA with rank `rank` of this cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
