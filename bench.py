@@ -82,9 +82,10 @@ class ClockSampler:
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
-        self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.index, self.rows, self.stamps, self.proc, self.thread = index, [], [], None, None
         self.stop = threading.Event()
         self.nvml = None
+        self.t_begin = 0.0
 
     def _nvml_handle(self):
         import pynvml
@@ -110,6 +111,7 @@ class ClockSampler:
                 sm = n.nvmlDeviceGetClockInfo(handle, n.NVML_CLOCK_SM)
                 mask = reasons_fn(handle)
                 self.rows.append([str(sm), str(mx)] + ["Active" if mask & bits[k] else "Not Active" for k in self.NAMES])
+                self.stamps.append(time.perf_counter())
             except Exception:   # noqa: BLE001
                 break
             time.sleep(0.002)
@@ -119,6 +121,12 @@ class ClockSampler:
             handle = self._nvml_handle()
             self.thread = threading.Thread(target=self._poll_nvml, args=(handle,), daemon=True)
             self.thread.start()
+            # the first NVML queries of a process take tens of milliseconds, longer than a short timed
+            # region: wait until the poller delivers, then count only what it samples from here on
+            deadline = time.perf_counter() + 2.0
+            while not self.rows and time.perf_counter() < deadline:
+                time.sleep(0.001)
+            self.t_begin = time.perf_counter()
             return self
         except Exception:   # noqa: BLE001  (no NVML bindings: fall back to the command-line tool)
             self.nvml = None
@@ -135,6 +143,7 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
+            self.stamps.append(time.perf_counter())
 
     def __exit__(self, *exc):
         self.stop.set()
@@ -149,7 +158,8 @@ class ClockSampler:
 
     def summary(self):
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        inside = [r for r, t in zip(self.rows, self.stamps) if t >= self.t_begin]
+        for r in inside or self.rows:       # (a region shorter than one poll: what was sampled around it)
             if len(r) < 6:
                 continue
             try:
@@ -751,6 +761,7 @@ def gpu_arm(args, dist, rank, world, local):
     for _ in range(args.warmup):
         resident.run()
     with ClockSampler(local) as clocks:
+        resident.run()          # (untimed: the sampler's start-up left the GPU idle for a moment)
         ms = time_region(dist, resident.run, args.steps)
     resident.status()
     # end to end: the same step with pinned host tensors as sources and sinks (201 MB each way per step)
