@@ -256,6 +256,39 @@ def test_a_matmul_whose_own_value_is_needed_keeps_its_output(kiln, variant):
     assert names[gelu] != "fused_away", names
 
 
+class ProjectAddNorm(torch.nn.Module):
+    """LayerNorm(x + Linear(a)) on a [batch, tokens, d] input: the reference plans the add in front of the
+    LayerNorm's reductions; here it runs in the matmul's epilogue and the row kernel reads the sum."""
+
+    def __init__(self, keep_sum):
+        super().__init__()
+        torch.manual_seed(23)
+        self.proj, self.ln = torch.nn.Linear(512, 256), torch.nn.LayerNorm(256)
+        self.keep_sum = keep_sum
+
+    def forward(self, x, a):
+        s = x + self.proj(a)
+        y = self.ln(s)
+        return (y, s) if self.keep_sum else y
+
+
+@pytest.mark.parametrize("keep_sum", [False, True], ids=["value only", "value and sum"])
+@pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
+def test_the_add_in_front_of_a_layernorm_runs_in_the_matmul_before_it(kiln, precision, keep_sum, monkeypatch):
+    if precision == "bf16":
+        monkeypatch.setenv("KILN_GPU_PRECISION", "bf16")
+    tol = {"fp32": 1e-4, "tf32": 1e-2, "bf16": 5e-2}[precision]
+    gen = torch.Generator().manual_seed(7)
+    x, a = torch.randn(3, 128, 256, generator=gen), torch.randn(3, 128, 512, generator=gen)
+    model = ProjectAddNorm(keep_sum).eval()
+    fused = compile_and_compare(kiln, model, x, a, allow_tf32=precision != "fp32", rtol=tol, atol=tol)
+    assert "mm_tcgen05" in fused._exe.impls and "row_layernorm" in fused._exe.impls, fused._exe.impls
+    monkeypatch.setenv("KILN_GPU_ABSORB_ELEMENTWISE", "0")
+    plain = compile_and_compare(kiln, model, x, a, allow_tf32=precision != "fp32", rtol=tol, atol=tol)
+    for got, want in zip(outputs(fused(x, a)), outputs(plain(x, a))):
+        torch.testing.assert_close(got.cpu(), want.cpu(), rtol=tol, atol=tol)
+
+
 def test_wrong_shape_is_a_value_error(kiln):
     compiled = kiln.compile(torch.nn.Linear(8, 4).eval(), (torch.randn(3, 8),), device="cuda")
     with pytest.raises(ValueError):
