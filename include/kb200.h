@@ -231,6 +231,13 @@ int kb200_plan_launch_count(const kb200_plan* plan);
  * "row_layernorm_warp", "mm_tcgen05_tf32", ...).  Never NULL for a valid i. */
 const char* kb200_kernel_impl(const kb200_plan* plan, int i);
 
+/* Number of fused scalar steps kernel `i` applies per element as bound: the epilogue chain of a
+ * matmul (including the steps of an elementwise or row kernel it took over, see
+ * KB200_OPT_ABSORB_ELEMENTWISE), the chain of an elementwise kernel, the chain in front of a
+ * register-resident row kernel's reductions; 0 for a kernel that launches nothing and for the
+ * general tape kernels; -1 for a bad index or an unbound plan.  Introspection only. */
+int kb200_kernel_chain_length(const kb200_plan* plan, int i);
+
 /* Reads back the plan's device status word after the caller synchronised:
  * 0 = ok, otherwise KB200_ERR_DEVICE_WAIT with the kernel index in
  * kb200_last_error().  Device-side waits are bounded; when one runs out the

@@ -1102,6 +1102,19 @@ KB200_EXPORT const char* kb200_kernel_impl(const kb200_plan* p, int i) {
   return impl_name(plan.kernels[i].impl);
 }
 
+KB200_EXPORT int kb200_kernel_chain_length(const kb200_plan* p, int i) {
+  if (p == nullptr) return -1;
+  const Plan& plan = *reinterpret_cast<const Plan*>(p);
+  if (i < 0 || i >= (int)plan.kernels.size() || !plan.bound) return -1;
+  const PlanKernel& k = plan.kernels[i];
+  switch (k.impl) {
+    case IMPL_MM_TC: case IMPL_MM_GEMV: case IMPL_MM_SIMT: case IMPL_EW_CHAIN_VEC4: case IMPL_EW_TRANSPOSE:
+      return k.has_chain ? k.chain.n : 0;
+    case IMPL_ROW_LAYERNORM: case IMPL_ROW_SOFTMAX: return k.row_pre.n;
+    default: return 0;
+  }
+}
+
 KB200_EXPORT int kb200_plan_status(kb200_plan* p) {
   if (p == nullptr) return fail(KB200_ERR_ARGUMENT, "kb200_plan_status: plan is null");
   Plan& plan = *reinterpret_cast<Plan*>(p);

@@ -70,6 +70,7 @@ EXPORTS = {
     "kb200_kernel_launch": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "kb200_plan_launch_count": (C.c_int, [C.c_void_p]),
     "kb200_kernel_impl": (C.c_char_p, [C.c_void_p, C.c_int]),
+    "kb200_kernel_chain_length": (C.c_int, [C.c_void_p, C.c_int]),
     "kb200_plan_status": (C.c_int, [C.c_void_p]),
     "kb200_plan_selftest_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "kb200_plan_destroy": (None, [C.c_void_p]),

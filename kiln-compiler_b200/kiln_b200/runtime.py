@@ -208,6 +208,8 @@ class GPUExecutable:
         self.launch_names = [l.name for l in program.launches]
         self.kernel_names = list(dict.fromkeys(l.kernel for l in program.launches))
         self.impls = [self._lib.kb200_kernel_impl(self._plan, i).decode() for i in range(len(program.launches))]
+        # fused scalar steps per element of every launch as bound (a matmul that took over the kernel behind it shows more)
+        self.chain_lengths = [self._lib.kb200_kernel_chain_length(self._plan, i) for i in range(len(program.launches))]
         self.device_launches = self._lib.kb200_plan_launch_count(self._plan)
         self.graph = None
         self.use_cuda_graphs = bool(cuda_graphs)

@@ -283,8 +283,12 @@ def test_the_add_in_front_of_a_layernorm_runs_in_the_matmul_before_it(kiln, prec
     model = ProjectAddNorm(keep_sum).eval()
     fused = compile_and_compare(kiln, model, x, a, allow_tf32=precision != "fp32", rtol=tol, atol=tol)
     assert "mm_tcgen05" in fused._exe.impls and "row_layernorm" in fused._exe.impls, fused._exe.impls
+    steps = dict(zip(fused._exe.impls, fused._exe.chain_lengths))
+    assert steps["mm_tcgen05"] == 2 and steps["row_layernorm"] == 0, steps        # bias and the add; no chain left in front of the row
     monkeypatch.setenv("KILN_GPU_ABSORB_ELEMENTWISE", "0")
     plain = compile_and_compare(kiln, model, x, a, allow_tf32=precision != "fp32", rtol=tol, atol=tol)
+    steps = dict(zip(plain._exe.impls, plain._exe.chain_lengths))
+    assert steps["mm_tcgen05"] == 1 and steps["row_layernorm"] == 1, steps
     for got, want in zip(outputs(fused(x, a)), outputs(plain(x, a))):
         torch.testing.assert_close(got.cpu(), want.cpu(), rtol=tol, atol=tol)
 
