@@ -101,21 +101,30 @@ __device__ __forceinline__ float ex2(float x) {
 // block's first key relative to the query tile's first row (only used on the diagonal tile).
 template <bool DIAGONAL>
 __device__ __forceinline__ float probabilities32(float (&v)[32], float scale_log2, float m_use, int first_col, int row) {
-  float sum = 0.0f;
+  const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-m_use, -m_use);
+  float2 sum2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float pr = ex2(fmaf(v[i], scale_log2, -m_use));
-    if (DIAGONAL && first_col + i > row) pr = 0.0f;
-    v[i] = pr;
-    sum += pr;
+  for (int i = 0; i < 32; i += 2) {
+    const float2 t = ffma2(make_float2(v[i], v[i + 1]), scale2, shift2);     // two exponents per instruction
+    float2 pr = make_float2(ex2(t.x), ex2(t.y));
+    if (DIAGONAL && first_col + i > row) pr.x = 0.0f;
+    if (DIAGONAL && first_col + i + 1 > row) pr.y = 0.0f;
+    v[i] = pr.x;
+    v[i + 1] = pr.y;
+    sum2 = fadd2(sum2, pr);
   }
-  return sum;
+  return sum2.x + sum2.y;
 }
 template <bool DIAGONAL>
 __device__ __forceinline__ float row_max32(const float (&v)[32], float m, int first_col, int row) {
+  if (DIAGONAL) {
 #pragma unroll
-  for (int i = 0; i < 32; ++i)
-    if (!DIAGONAL || first_col + i <= row) m = fmaxf(m, v[i]);
+    for (int i = 0; i < 32; ++i)
+      if (first_col + i <= row) m = fmaxf(m, v[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) m = fmax3(m, v[i], v[i + 1]);
+  }
   return m;
 }
 
@@ -133,7 +142,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
 #ifdef KB200_TRACE
   __shared__ long long trace[4][16];
+  __shared__ long long mma_trace[64];
   __shared__ long long marks[4];
+  int tm = 0;
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned long long g;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
@@ -141,8 +152,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     marks[1] = clock64();
   }
 #define ATTN_STAMP(role, idx) do { if (blockIdx.x == 0 && threadIdx.x == 64 && (idx) < 16) trace[role][idx] = clock64(); } while (0)
+#define ATTN_MMA_STAMP(idx) do { if (blockIdx.x == 0 && (idx) < 64) mma_trace[idx] = clock64(); } while (0)
 #else
 #define ATTN_STAMP(role, idx) do { } while (0)
+#define ATTN_MMA_STAMP(idx) do { } while (0)
 #endif
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t q_smem = (raw + 1023u) & ~1023u;
@@ -303,25 +316,29 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (ok && n_kv == 1) umma_commit(q_empty);
       };
       int t = 0;
-      bool started = false;                          // the current item's first scores were issued under the previous item
       for (int ii = 0; ok; ++ii) {
         const int w = nth_item(ii);
         if (w < 0) break;
-        const int w_next = nth_item(ii + 1);
         const int n_kv = item_of(w).n_kv;
-        if (!started) first_qk(ii, t, n_kv);
-        started = false;
+        // (The next item's first scores are NOT issued ahead of this item's last P V: the softmax warps
+        // wait for that P V to finish the item, and have the merge and the stores to do before they
+        // need the next scores.)
+        first_qk(ii, t, n_kv);
         for (int j = 0; j < n_kv && ok; ++j) {
+#ifdef KB200_TRACE
+          ATTN_MMA_STAMP(tm); ++tm;
+#endif
           if (j + 1 < n_kv) {
             issue_qk(t + j + 1);                     // the next scores are computed while the softmax warps work on tile j
             if (ok && j + 2 == n_kv) umma_commit(q_empty);
-          } else if (w_next >= 0 && mbar_try_wait(q_full, (ii + 1) & 1) &&
-                     mbar_try_wait(k_full + 8 * ((t + n_kv) & 1), ((t + n_kv) >> 1) & 1)) {
-            // last tile, and the next item's Q and first keys are already here: its first scores go ahead of this P V
-            first_qk(ii + 1, t + n_kv, item_of(w_next).n_kv);
-            started = true;
           }
+#ifdef KB200_TRACE
+          ATTN_MMA_STAMP(tm); ++tm;
+#endif
           if (ok) issue_pv(t + j);
+#ifdef KB200_TRACE
+          ATTN_MMA_STAMP(tm); ++tm;
+#endif
         }
         t += n_kv;
       }
@@ -350,20 +367,27 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
       float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
-      // running output <- running output * alpha + O_part of tile t
-      auto fold = [&](int t, float alpha) {
+      // running output <- running output * alpha + O_part of tile t, in two halves: the request (wait for
+      // the P V of tile t, then both tensor-memory loads in flight) and, after other work, the arithmetic
+      uint32_t oa[32], ob[32];
+      auto fold_request = [&](int t) {
         bool got = mbar_wait(ofull0 + 8 * (group * 2 + (t & 1)), (t >> 1) & 1, abort_ptr);
         if (!got) give_up(0x32);
         ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
         if (!ok) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t o_addr = tmem_o0 + lane_addr + (uint32_t)(group * 2 + (t & 1)) * 64;
+        tmem_ld32x2_issue(o_addr, o_addr + 32, oa, ob);
+      };
+      auto fold_apply = [&](float alpha) {
+        tmem_ld_wait64(oa, ob);
+        const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-        for (int c = 0; c < kHeadDim; c += 32) {
-          float v[32];
-          tmem_ld32(o_addr + c, v);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, v[i]);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 lo = ffma2(make_float2(o[i], o[i + 1]), alpha2, make_float2(__uint_as_float(oa[i]), __uint_as_float(oa[i + 1])));
+          const float2 hi = ffma2(make_float2(o[32 + i], o[33 + i]), alpha2, make_float2(__uint_as_float(ob[i]), __uint_as_float(ob[i + 1])));
+          o[i] = lo.x; o[i + 1] = lo.y;
+          o[32 + i] = hi.x; o[33 + i] = hi.y;
         }
       };
       for (int j = 0; j < n_kv; ++j) {
@@ -378,9 +402,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
         const bool diagonal = j == it.qt;
+        // The two groups of a scheduler start a tile at the same moment, and their exponentials would
+        // queue on the one special-function unit: group 1 folds the previous tile's O_part first, group 0
+        // afterwards, so the exponential phases only half overlap.
+        if (group == 1 && j > 0) {
+          fold_request(t - 1);
+          if (!ok) break;
+          fold_apply(alpha_prev);
+        }
         float va[32], vb[32];
-        tmem_ld32(s_addr, va);
-        tmem_ld32(s_addr + 32, vb);
+        tmem_ld32x2(s_addr, s_addr + 32, va, vb);       // both halves in flight, one wait
         // the scale is positive (checked when the chain was matched), so the maximum commutes with it
         float mx = -CUDART_INF_F;
         if (diagonal) {
@@ -423,17 +454,22 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_arrive(pfull0 + 8 * (group * 2 + s));
         ATTN_STAMP(1, j);
         // fold the PREVIOUS tile's O_part while the tensor pipe works on this one
-        if (j > 0) {
-          fold(t - 1, alpha_prev);
+        if (group == 0 && j > 0) {
+          fold_request(t - 1);
           if (!ok) break;
+          fold_apply(alpha_prev);
         }
         ATTN_STAMP(3, j);
         alpha_prev = alpha;
         l_run = l_run * alpha + sum;
         m_run = m_new;
       }
-      if (ok) fold(t0 + n_kv - 1, alpha_prev);
+      if (ok) {
+        fold_request(t0 + n_kv - 1);
+        if (ok) fold_apply(alpha_prev);
+      }
       t0 += n_kv;
+      ATTN_STAMP(2, 3 * ii);
       // ---- merge the two groups' states; group g finishes head dims g*32 .. g*32+31 ----
       // The rows this thread is about to overwrite hold what the other group's warp staged for the previous
       // item: every warp has stored that (first barrier).  Then the states are exchanged (second barrier),
@@ -453,6 +489,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       asm volatile("bar.sync 1, 256;" ::: "memory");
       // a warp that gave up raised the flag before it arrived here: all eight leave the item loop together
       if (*abort_ptr) ok = false;
+      ATTN_STAMP(2, 3 * ii + 1);
       if (ok) {
         const float m_other = theirs[32], l_other = theirs[33];
         const float m_all = fmaxf(m_run, m_other);       // finite: key 0 is visible to every row
@@ -511,6 +548,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
         }
       }
+      ATTN_STAMP(2, 3 * ii + 2);
     }
   }
 
@@ -523,6 +561,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
     printf("ATTN block0 globaltimer start %lld end %lld (ns) dur %lld | exit cycles %lld n_kv %d\n", marks[0], (long long)g,
            (long long)g - marks[0], clock64() - marks[1], item_of(blockIdx.x).n_kv);
+    printf("softmax thread per item (tiles done, states exchanged, rows stored):");
+    for (int j = 0; j < 15; ++j) printf(" %lld", trace[2][j] - marks[1]);
+    printf("\n");
+    printf("MMA thread (per tile: loop top, after Q K^T of the next tile, after P V):");
+    for (int j = 0; j < 48; ++j) printf(" %lld", mma_trace[j] - marks[1]);
+    printf("\n");
     for (int j = 0; j < item_of(blockIdx.x).n_kv && j < 16; ++j)
       printf("kv %2d  s_ready %7lld p_stored %7lld folded %7lld\n", j, trace[0][j] - marks[1], trace[1][j] - marks[1],
              trace[3][j] - marks[1]);

@@ -13,6 +13,36 @@ constexpr uint32_t kWaitLimit = 1u << 20;   // polls of an mbarrier before a wai
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Two float32 operations per instruction (sm_100 packed forms) and the three-input maximum: the
+// softmax warps and the matmul epilogues are bound by instruction issue, not by the FP32 pipes.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
@@ -135,6 +165,24 @@ __device__ __forceinline__ void tmem_ld32x2(uint32_t taddr_a, uint32_t taddr_b, 
       : "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) { va[i] = __uint_as_float(ra[i]); vb[i] = __uint_as_float(rb[i]); }
+}
+
+// The same two loads without the wait, and the wait as a statement of its own that names the
+// registers as in-out operands (nothing that reads them may be scheduled above it): other work --
+// a tensor-memory store, a barrier arrival -- goes between the two.
+__device__ __forceinline__ void tmem_ld32x2_issue(uint32_t taddr_a, uint32_t taddr_b, uint32_t (&ra)[32], uint32_t (&rb)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];"
+      : "=r"(ra[0]), "=r"(ra[1]), "=r"(ra[2]), "=r"(ra[3]), "=r"(ra[4]), "=r"(ra[5]), "=r"(ra[6]), "=r"(ra[7]), "=r"(ra[8]), "=r"(ra[9]), "=r"(ra[10]), "=r"(ra[11]), "=r"(ra[12]), "=r"(ra[13]), "=r"(ra[14]), "=r"(ra[15]), "=r"(ra[16]), "=r"(ra[17]), "=r"(ra[18]), "=r"(ra[19]), "=r"(ra[20]), "=r"(ra[21]), "=r"(ra[22]), "=r"(ra[23]), "=r"(ra[24]), "=r"(ra[25]), "=r"(ra[26]), "=r"(ra[27]), "=r"(ra[28]), "=r"(ra[29]), "=r"(ra[30]), "=r"(ra[31]), "=r"(rb[0]), "=r"(rb[1]), "=r"(rb[2]), "=r"(rb[3]), "=r"(rb[4]), "=r"(rb[5]), "=r"(rb[6]), "=r"(rb[7]), "=r"(rb[8]), "=r"(rb[9]), "=r"(rb[10]), "=r"(rb[11]), "=r"(rb[12]), "=r"(rb[13]), "=r"(rb[14]), "=r"(rb[15]), "=r"(rb[16]), "=r"(rb[17]), "=r"(rb[18]), "=r"(rb[19]), "=r"(rb[20]), "=r"(rb[21]), "=r"(rb[22]), "=r"(rb[23]), "=r"(rb[24]), "=r"(rb[25]), "=r"(rb[26]), "=r"(rb[27]), "=r"(rb[28]), "=r"(rb[29]), "=r"(rb[30]), "=r"(rb[31])
+      : "r"(taddr_a), "r"(taddr_b)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait64(uint32_t (&ra)[32], uint32_t (&rb)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(ra[0]), "+r"(ra[1]), "+r"(ra[2]), "+r"(ra[3]), "+r"(ra[4]), "+r"(ra[5]), "+r"(ra[6]), "+r"(ra[7]), "+r"(ra[8]), "+r"(ra[9]), "+r"(ra[10]), "+r"(ra[11]), "+r"(ra[12]), "+r"(ra[13]), "+r"(ra[14]), "+r"(ra[15]), "+r"(ra[16]), "+r"(ra[17]), "+r"(ra[18]), "+r"(ra[19]), "+r"(ra[20]), "+r"(ra[21]), "+r"(ra[22]), "+r"(ra[23]), "+r"(ra[24]), "+r"(ra[25]), "+r"(ra[26]), "+r"(ra[27]), "+r"(ra[28]), "+r"(ra[29]), "+r"(ra[30]), "+r"(ra[31]), "+r"(rb[0]), "+r"(rb[1]), "+r"(rb[2]), "+r"(rb[3]), "+r"(rb[4]), "+r"(rb[5]), "+r"(rb[6]), "+r"(rb[7]), "+r"(rb[8]), "+r"(rb[9]), "+r"(rb[10]), "+r"(rb[11]), "+r"(rb[12]), "+r"(rb[13]), "+r"(rb[14]), "+r"(rb[15]), "+r"(rb[16]), "+r"(rb[17]), "+r"(rb[18]), "+r"(rb[19]), "+r"(rb[20]), "+r"(rb[21]), "+r"(rb[22]), "+r"(rb[23]), "+r"(rb[24]), "+r"(rb[25]), "+r"(rb[26]), "+r"(rb[27]), "+r"(rb[28]), "+r"(rb[29]), "+r"(rb[30]), "+r"(rb[31])
+               :
+               : "memory");
 }
 
 // tcgen05.mma with the A operand read from tensor memory (M x K, one 32-bit element per column)
