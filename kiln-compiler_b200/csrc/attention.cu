@@ -33,6 +33,7 @@
 #include "device_math.cuh"
 #include "kb200_internal.h"
 #include "tc_common.cuh"
+#include "tc_epilogue.cuh"
 
 namespace kb200 {
 
@@ -44,9 +45,10 @@ constexpr int kRows = 128;                   // queries per CTA and keys per til
 constexpr int kHeadDim = 64;
 constexpr int kSlab = kRows * 128;           // one [128 rows x 128 bytes] swizzled slab
 constexpr int kAttnThreads = 64 + 256;
-constexpr int kXStride = 36;                 // floats per row of the merge buffers: 32 dims, max, sum; 144 bytes, so 128-bit accesses of eight rows spread over the banks
+constexpr int kExchangeBytes = 2 * (2 * 2 * kRows * 4);   // the pairs' maxima (two tile parities) and row sums (two item parities)
+constexpr int kStageBytes = 4096 + 2048;      // a warp's output rows: 32 x 32 float32 and their bf16 copy
 // Q + 2 x K + 2 x V tiles (two 16 KB slabs each in float32, one in bf16), the two merge buffers, alignment slack
-constexpr int attn_smem(bool bf16) { return 5 * (bf16 ? 1 : 2) * kSlab + 2 * kRows * kXStride * 4 + 1024; }
+constexpr int attn_smem(bool bf16) { return 5 * (bf16 ? 1 : 2) * kSlab + kExchangeBytes + 8 * kStageBytes + 1024; }
 
 struct AttnParams {
   int T, H, q_tiles;
@@ -63,6 +65,7 @@ struct AttnParams {
 
 struct AttnState {
   CUtensorMap map_q, map_k, map_v;
+  CUtensorMap map_out, map_out16;   // bulk-store maps of the merged heads [B * T, H * 64] and of their bf16 copy
   // BF16 mode: Q, K and V are read from the bf16 mirror of the QKV projection's output (set after the
   // mirror is allocated); the kernel then runs its matmuls with bf16 operands and P rounded to bf16.
   bool bf16 = false;
@@ -131,7 +134,8 @@ __device__ __forceinline__ float row_max32(const float (&v)[32], float m, int fi
 template <bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_out,
+                 const __grid_constant__ CUtensorMap map_out16, const __grid_constant__ AttnParams p) {
   // a [128 rows x 64 dims] operand tile is two 128-byte-wide slabs in float32, one in bf16
   constexpr int kTileSlabs = BF16 ? 1 : 2;
   constexpr int kTileBytes = kTileSlabs * kSlab;
@@ -194,6 +198,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
+    prefetch_tensormap(&map_out);
+    if (p.out16 != nullptr) prefetch_tensormap(&map_out16);
   }
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -224,7 +230,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   pdl_wait();
   pdl_launch_dependents();
   const uint32_t tmem_base = tmem_base_slot;
-  // columns: S0 0..127 | S1 128..255 | O_part[group][buffer] 256 + (group * 2 + buffer) * 64
+  // columns: S0 0..127 | S1 128..255 | O_part[buffer] 256 + buffer * 64
   const uint32_t tmem_o0 = tmem_base + 256;
   volatile int* abort_ptr = &abort_flag;
   auto give_up = [&](int site) {
@@ -279,34 +285,35 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         umma_commit(sfull0 + 8 * s);
         umma_commit(k_empty + 8 * s);
       };
-      // P V of tile t: each group's 64 keys into that group's O_part buffer (t & 1).  In-order execution
-      // of the tensor pipe keeps S[s] intact until these reads of P are done (the next Q K^T into S[s]
-      // is issued later), and the buffer (t & 1) was folded by the softmax threads before they
-      // published P of tile t.
+      // P V of tile t: the 128 keys of both threads of a row pair into the O_part buffer (t & 1), as two
+      // runs of MMAs (a group's P occupies the first columns of its 64-column share of S).  In-order
+      // execution of the tensor pipe keeps S[s] intact until these reads of P are done (the next Q K^T
+      // into S[s] is issued later), and the buffer (t & 1) was folded by the softmax threads before
+      // they published P of tile t.
       auto issue_pv = [&](int t) {
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
         if (!mbar_wait(v_full + 8 * s, ph, abort_ptr)) { give_up(0x23); ok = false; return; }
         const uint32_t vb = v_smem + s * kTileBytes;
+        const uint32_t o_addr = tmem_o0 + (uint32_t)s * 64;
         for (int g = 0; g < 2; ++g) {
           if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t o_addr = tmem_o0 + (uint32_t)(g * 2 + s) * 64;
           if (BF16) {
             // P: two bf16 per TMEM column, 16 keys = 8 columns per instruction; V: [keys x 64 dims] bf16,
             // one 128-byte swizzled row per key, 16 rows per instruction
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
-                      make_desc(vb + (uint32_t)(g * 4 + kk) * 2048, kSlab, 1024, 2), p.idesc_pv, kk != 0 ? 1u : 0u, true);
+                      make_desc(vb + (uint32_t)(g * 4 + kk) * 2048, kSlab, 1024, 2), p.idesc_pv, (g | kk) != 0 ? 1u : 0u, true);
           } else {
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)
               umma_ts(o_addr, tmem_base + (uint32_t)s * 128 + (uint32_t)(g * 64 + kk * 8),
-                      make_desc(vb + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1), p.idesc_pv, kk != 0 ? 1u : 0u, false);
+                      make_desc(vb + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1), p.idesc_pv, (g | kk) != 0 ? 1u : 0u, false);
           }
-          umma_commit(ofull0 + 8 * (g * 2 + s));
         }
+        umma_commit(ofull0 + 8 * s);
         umma_commit(v_empty + 8 * s);
       };
       // An item's first scores: its Q must have landed; once its last scores are issued, the Q tile is handed back.
@@ -345,17 +352,34 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
   } else {
     // ---------------- softmax / output (warps 2..9) ----------------
+    // Two threads share a query row (TMEM lane): thread g of the pair takes keys g*64 .. g*64+63 of every
+    // tile.  They keep ONE online-softmax state per row: each tile they exchange the maxima of their
+    // halves through shared memory (a 64-thread barrier per lane quadrant), so both use the same
+    // reference point, their probabilities go into one P V of 128 keys and one O_part, and thread g
+    // folds, normalises and stores head dims g*32 .. g*32+31.  Per item only the two partial row sums
+    // cross between them.
     const int quad = warp & 3;
-    const int group = (warp - 2) >> 2;             // which 64 keys of every tile
+    const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;              // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int c0 = group * 64;
-    // Merge buffers [2][128][kXStride] behind the rings: a thread leaves the half of its state the other
-    // group finishes in its own row, and later puts its merged result where it read the other group's.
-    float* const xbuf = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
-    float* const mine = xbuf + (size_t)(group * kRows + row) * kXStride;
-    float* const theirs = xbuf + (size_t)((group ^ 1) * kRows + row) * kXStride;
-    const float* const warp_rows = xbuf + (size_t)((group ^ 1) * kRows + quad * 32) * kXStride;   // the 32 rows this warp stores
+    // behind the rings: [2 tile parities][2 groups][128 rows] maxima, [2 item parities][2][128] row sums,
+    // then a staging slot per warp for the output rows (32 x 32 float32 + their bf16 copy)
+    float* const xmax = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
+    float* const xsum = xmax + 4 * kRows;
+    uint8_t* const stage = reinterpret_cast<uint8_t*>(xmax) + kExchangeBytes + (size_t)((warp - 2) * kStageBytes);
+    const int pair_barrier = 2 + quad;              // hardware barriers 2..5, 64 threads each
+    // The pair's barrier also carries the abort flag (an OR over what the 64 threads read before they
+    // arrived), so that both threads of a row take the same decision and neither waits for the other.
+    auto pair_sync_aborted = [&]() {
+      uint32_t any;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %2, 0;\n\tbar.red.or.pred q, %1, 64, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(any)
+          : "r"(pair_barrier), "r"((uint32_t)*abort_ptr)
+          : "memory");
+      return any != 0;
+    };
     bool ok = true;
     int t0 = 0;                                      // tiles of the items before this one
     for (int ii = 0; ok; ++ii) {
@@ -363,53 +387,36 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (w < 0) break;
       const Item it = item_of(w);
       const int n_kv = it.n_kv;
-      float o[kHeadDim];
+      float o[32];
 #pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
+      for (int i = 0; i < 32; ++i) o[i] = 0.0f;
       float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
-      // running output <- running output * alpha + O_part of tile t, in two halves: the request (wait for
-      // the P V of tile t, then both tensor-memory loads in flight) and, after other work, the arithmetic
-      uint32_t oa[32], ob[32];
-      auto fold_request = [&](int t) {
-        bool got = mbar_wait(ofull0 + 8 * (group * 2 + (t & 1)), (t >> 1) & 1, abort_ptr);
+      // running output <- running output * alpha + this thread's 32 dims of the O_part of tile t
+      auto fold = [&](int t, float alpha) {
+        bool got = mbar_wait(ofull0 + 8 * (t & 1), (t >> 1) & 1, abort_ptr);
         if (!got) give_up(0x32);
-        ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
-        if (!ok) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t o_addr = tmem_o0 + lane_addr + (uint32_t)(group * 2 + (t & 1)) * 64;
-        tmem_ld32x2_issue(o_addr, o_addr + 32, oa, ob);
-      };
-      auto fold_apply = [&](float alpha) {
-        tmem_ld_wait64(oa, ob);
+        float v[32];
+        tmem_ld32(tmem_o0 + lane_addr + (uint32_t)((t & 1) * 64 + group * 32), v);
         const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float2 lo = ffma2(make_float2(o[i], o[i + 1]), alpha2, make_float2(__uint_as_float(oa[i]), __uint_as_float(oa[i + 1])));
-          const float2 hi = ffma2(make_float2(o[32 + i], o[33 + i]), alpha2, make_float2(__uint_as_float(ob[i]), __uint_as_float(ob[i + 1])));
-          o[i] = lo.x; o[i + 1] = lo.y;
-          o[32 + i] = hi.x; o[33 + i] = hi.y;
+          const float2 r2 = ffma2(make_float2(o[i], o[i + 1]), alpha2, make_float2(v[i], v[i + 1]));
+          o[i] = r2.x;
+          o[i + 1] = r2.y;
         }
       };
+      // Every thread of a pair passes the same barriers: a wait that ran out raises the CTA's flag and the
+      // thread carries on to the next barrier, after which both see the flag and leave together.
       for (int j = 0; j < n_kv; ++j) {
         const int t = t0 + j;
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
-        bool got = mbar_wait(sfull0 + 8 * s, ph, abort_ptr);
-        if (!got) give_up(0x31);
-        ok = __all_sync(0xffffffffu, got) && !*abort_ptr;
-        if (!ok) break;
+        if (!mbar_wait(sfull0 + 8 * s, ph, abort_ptr)) give_up(0x31);
         ATTN_STAMP(0, j);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
         const bool diagonal = j == it.qt;
-        // The two groups of a scheduler start a tile at the same moment, and their exponentials would
-        // queue on the one special-function unit: group 1 folds the previous tile's O_part first, group 0
-        // afterwards, so the exponential phases only half overlap.
-        if (group == 1 && j > 0) {
-          fold_request(t - 1);
-          if (!ok) break;
-          fold_apply(alpha_prev);
-        }
         float va[32], vb[32];
         tmem_ld32x2(s_addr, s_addr + 32, va, vb);       // both halves in flight, one wait
         // the scale is positive (checked when the chain was matched), so the maximum commutes with it
@@ -421,20 +428,22 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           mx = row_max32<false>(va, mx, 0, 0);
           mx = row_max32<false>(vb, mx, 0, 0);
         }
+        xmax[(s * 2 + group) * kRows + row] = mx;
+        if (pair_sync_aborted()) { ok = false; break; }
+        mx = fmaxf(mx, xmax[(s * 2 + (group ^ 1)) * kRows + row]);
+        // key 0 is visible to every row, so the maximum over a whole tile is finite
         const float m_new = fmaxf(m_run, mx * p.scale_log2);
-        // a row with every key of this group masked so far keeps m = -inf: use 0 as the reference point
-        const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;
-        const float alpha = ex2(m_run - m_use);       // 0 while m_run = -inf
+        const float alpha = ex2(m_run - m_new);       // 0 while m_run = -inf
         float sum;
         if (diagonal) {
-          sum = probabilities32<true>(va, p.scale_log2, m_use, c0, row);
-          sum += probabilities32<true>(vb, p.scale_log2, m_use, c0 + 32, row);
+          sum = probabilities32<true>(va, p.scale_log2, m_new, c0, row);
+          sum += probabilities32<true>(vb, p.scale_log2, m_new, c0 + 32, row);
         } else {
-          sum = probabilities32<false>(va, p.scale_log2, m_use, 0, 0);
-          sum += probabilities32<false>(vb, p.scale_log2, m_use, 0, 0);
+          sum = probabilities32<false>(va, p.scale_log2, m_new, 0, 0);
+          sum += probabilities32<false>(vb, p.scale_log2, m_new, 0, 0);
         }
         if (BF16) {
-          // P rounded to bf16, two keys per 32-bit column: the group's 64 keys take the first 32 columns of
+          // P rounded to bf16, two keys per 32-bit column: the thread's 64 keys take the first 32 columns of
           // its own 64-column share of the S buffer
           float packed[32];
 #pragma unroll
@@ -454,102 +463,40 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_arrive(pfull0 + 8 * (group * 2 + s));
         ATTN_STAMP(1, j);
         // fold the PREVIOUS tile's O_part while the tensor pipe works on this one
-        if (group == 0 && j > 0) {
-          fold_request(t - 1);
-          if (!ok) break;
-          fold_apply(alpha_prev);
-        }
+        if (j > 0) fold(t - 1, alpha_prev);
         ATTN_STAMP(3, j);
         alpha_prev = alpha;
         l_run = l_run * alpha + sum;
         m_run = m_new;
       }
-      if (ok) {
-        fold_request(t0 + n_kv - 1);
-        if (ok) fold_apply(alpha_prev);
-      }
+      if (ok) fold(t0 + n_kv - 1, alpha_prev);
       t0 += n_kv;
       ATTN_STAMP(2, 3 * ii);
-      // ---- merge the two groups' states; group g finishes head dims g*32 .. g*32+31 ----
-      // The rows this thread is about to overwrite hold what the other group's warp staged for the previous
-      // item: every warp has stored that (first barrier).  Then the states are exchanged (second barrier),
-      // and the merged row goes where the other group's state was read: nobody else looks there.
-      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight softmax warps only
-      if (ok) {
-        if (group == 0) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) reinterpret_cast<float4*>(mine)[q] = make_float4(o[32 + 4 * q], o[33 + 4 * q], o[34 + 4 * q], o[35 + 4 * q]);
-        } else {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) reinterpret_cast<float4*>(mine)[q] = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-        }
-        mine[32] = m_run;
-        mine[33] = l_run;
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      // a warp that gave up raised the flag before it arrived here: all eight leave the item loop together
-      if (*abort_ptr) ok = false;
+      // ---- the row sum is the two threads' partial sums; thread g normalises and stores dims g*32 .. g*32+31 ----
+      xsum[((ii & 1) * 2 + group) * kRows + row] = l_run;
+      if (pair_sync_aborted()) ok = false;
       ATTN_STAMP(2, 3 * ii + 1);
       if (ok) {
-        const float m_other = theirs[32], l_other = theirs[33];
-        const float m_all = fmaxf(m_run, m_other);       // finite: key 0 is visible to every row
-        const float w_mine = exp2f(m_run - m_all), w_other = exp2f(m_other - m_all);
-        const float inv = 1.0f / (l_run * w_mine + l_other * w_other);
-        const float a = w_mine * inv, b = w_other * inv;
-        if (group == 0) {
+        const float inv = __fdividef(1.0f, l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row]);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 x = reinterpret_cast<float4*>(theirs)[q];
-            x.x = o[4 * q] * a + x.x * b;
-            x.y = o[4 * q + 1] * a + x.y * b;
-            x.z = o[4 * q + 2] * a + x.z * b;
-            x.w = o[4 * q + 3] * a + x.w * b;
-            reinterpret_cast<float4*>(theirs)[q] = x;
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 x = reinterpret_cast<float4*>(theirs)[q];
-            x.x = o[32 + 4 * q] * a + x.x * b;
-            x.y = o[33 + 4 * q] * a + x.y * b;
-            x.z = o[34 + 4 * q] * a + x.z * b;
-            x.w = o[35 + 4 * q] * a + x.w * b;
-            reinterpret_cast<float4*>(theirs)[q] = x;
-          }
-        }
-        // A lane holds 32 dims of ONE row: stored from here, a warp instruction would touch 32 lines of 16
-        // bytes each.  Read back from shared memory, every store instruction of a warp writes four whole
-        // 128-byte rows (eight 64-byte rows of the bf16 copy).  Each warp stores the 32 rows it merged
-        // itself, so a warp-level barrier is all it takes.
+        for (int i = 0; i < 32; ++i) o[i] *= inv;
+        // A lane holds 32 dims of ONE row: the rows go through the warp's staging slot (128-byte rows, the
+        // 16-byte unit XORed with the row against bank conflicts) and leave as bulk tensor stores.
+        if (lane == 0) tma_store_wait_read();          // the slot's last stores have read it
         __syncwarp();
-        const int64_t first_row = it.row0 + it.q0 + quad * 32;
-        float* dst = p.out + first_row * p.out_row_stride + it.h * kHeadDim + group * 32;
-        __nv_bfloat16* dst16 = p.out16 != nullptr ? p.out16 + first_row * p.out16_row_stride + it.h * kHeadDim + group * 32 : nullptr;
-#pragma unroll
-        for (int i8 = 0; i8 < 8; ++i8) {
-          const int rr = i8 * 4 + (lane >> 3), q = lane & 7;
-          const float4 t4 = reinterpret_cast<const float4*>(warp_rows + rr * kXStride)[q];
-          *reinterpret_cast<float4*>(dst + (int64_t)rr * p.out_row_stride + 4 * q) = t4;
-        }
-        if (dst16 != nullptr) {
-#pragma unroll
-          for (int i4 = 0; i4 < 4; ++i4) {
-            const int rr = i4 * 8 + (lane >> 2), c = lane & 3;       // 8 dims = 16 bytes of bf16 per lane
-            const float4 lo = reinterpret_cast<const float4*>(warp_rows + rr * kXStride)[2 * c];
-            const float4 hi = reinterpret_cast<const float4*>(warp_rows + rr * kXStride)[2 * c + 1];
-            __nv_bfloat162 w0 = __floats2bfloat162_rn(lo.x, lo.y), w1 = __floats2bfloat162_rn(lo.z, lo.w);
-            __nv_bfloat162 w2 = __floats2bfloat162_rn(hi.x, hi.y), w3 = __floats2bfloat162_rn(hi.z, hi.w);
-            uint4 packed;
-            packed.x = *reinterpret_cast<uint32_t*>(&w0);
-            packed.y = *reinterpret_cast<uint32_t*>(&w1);
-            packed.z = *reinterpret_cast<uint32_t*>(&w2);
-            packed.w = *reinterpret_cast<uint32_t*>(&w3);
-            *reinterpret_cast<uint4*>(dst16 + (int64_t)rr * p.out16_row_stride + 8 * c) = packed;
-          }
+        stage_rows(stage, stage + 4096, o, lane, p.out16 != nullptr, true);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int col = it.h * kHeadDim + group * 32, first_row = it.row0 + it.q0 + quad * 32;
+          tma_store_3d(&map_out, smem_u32(stage), col, first_row, 0);
+          if (p.out16 != nullptr) tma_store_3d(&map_out16, smem_u32(stage + 4096), col, first_row, 0);
+          tma_store_commit();
         }
       }
       ATTN_STAMP(2, 3 * ii + 2);
     }
+    if (lane == 0) tma_store_wait_read();              // shared memory must outlive the stores that read it
   }
 
   // ---------------- common exit ----------------
@@ -747,6 +694,13 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   p.idesc_pv = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
   p.kernel_index = (int)c.first;
   p.status = plan.d_status;
+  // the output rows leave by bulk tensor stores: [B * T, H * 64], boxes of 32 rows x 32 dims
+  if (!aligned16(p.out) || !encode_map_store(&st->map_out, false, p.out, H * hd, B * T, 1, p.out_row_stride, 0)) {
+    if (st->staged_out) cudaFree(st->staged_out);
+    delete st;
+    return false;
+  }
+  st->map_out16 = st->map_out;
   const int64_t items = B * H * p.q_tiles;
   st->grid = dim3((unsigned)(items < plan.sm_count ? items : plan.sm_count), 1, 1);     // persistent: at most one CTA per SM
 
@@ -965,10 +919,10 @@ int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   const AttnState* st = static_cast<const AttnState*>(k.attn);
   if (st->bf16)
     KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q, st->map_k,
-                             st->map_v, st->params));
+                             st->map_v, st->map_out, st->map_out16, st->params));
   else
     KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
-                             st->map_k, st->map_v, st->params));
+                             st->map_k, st->map_v, st->map_out, st->map_out16, st->params));
   if (st->staged_out && st->final_out) {
     const int64_t n4 = st->out_elems / 4;
     const int64_t blocks = (n4 + 255) / 256;
@@ -1070,7 +1024,14 @@ void attention_elide_copy(Plan& plan, size_t first) {
 bool attention_reads_mirror(const PlanKernel& k) { return k.attn && static_cast<const AttnState*>(k.attn)->bf16; }
 
 void attention_set_shadow(PlanKernel& k, void* shadow_out) {
-  if (k.attn) static_cast<AttnState*>(k.attn)->params.out16 = static_cast<__nv_bfloat16*>(shadow_out);
+  AttnState* st = static_cast<AttnState*>(k.attn);
+  if (!st) return;
+  // the bf16 copy of the merged heads needs a store map of its own; without one it is not written
+  // (its reader was told to expect it: assign_shadows asks attention_can_shadow first)
+  __nv_bfloat16* out16 = static_cast<__nv_bfloat16*>(shadow_out);
+  if (out16 != nullptr && encode_map_store(&st->map_out16, true, out16, (int64_t)st->params.H * kHeadDim,
+                                            (int64_t)st->params.B * st->params.T, 1, st->params.out16_row_stride, 0))
+    st->params.out16 = out16;
 }
 
 const DevOperand* attention_output(const Plan& plan, size_t first, int64_t* elems) {
