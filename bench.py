@@ -391,13 +391,13 @@ def kernel_flops(kernel):
 # profiles/gpt2_block_b8_t1024_bf16_launches_and_top_kernels.md ("bf16:b8:" keys; outputs that the next
 # kernel reads stay in the 126 MB L2 and are not written back inside the launch).
 NCU_DRAM_BYTES = {
-    "bf16:b8:k0_row": 25245184,
-    "bf16:b8:k1_matmul": 16422656,
-    "bf16:b8:k2_ew0": 41128960,
-    "bf16:b8:k9_matmul": 13855488,
-    "bf16:b8:k10_row": 52687104,
-    "bf16:b8:k11_matmul": 18513408,
-    "bf16:b8:k13_matmul": 85074432,
+    "bf16:b8:k0_row": 25245440,
+    "bf16:b8:k1_matmul": 17290496,
+    "bf16:b8:k2_ew0": 41667840,
+    "bf16:b8:k9_matmul": 39930112,
+    "bf16:b8:k10_row": 25245952,
+    "bf16:b8:k11_matmul": 21331968,
+    "bf16:b8:k13_matmul": 85108992,
 }
 
 
