@@ -17,13 +17,14 @@
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through 2-deep rings.
 //   warp 1      MMA issuer: S = Q K^T (operands in shared memory, TF32) into one of two S buffers in
 //               TMEM; O_part = P V with P read from TMEM (written there by the softmax warps).
-//   warps 2..9  softmax, as two groups of 128 threads.  Group g owns keys g*64 .. g*64+63 of every
-//               tile and keeps its OWN online-softmax state (running max, sum and output) for them,
-//               one query row per thread: scale, causal mask on the diagonal tile, P stored back
-//               over S in TMEM, then P V of its 64 keys accumulates into its own O_part buffer.  The
-//               two partial results are merged once, at the end, through shared memory.  O_part is
-//               double-buffered and folded into the running output one tile late, so the P V of
-//               tile j runs under the softmax of tile j+1.
+//   warps 2..9  softmax.  Two threads share a query row (TMEM lane); thread g takes keys g*64 ..
+//               g*64+63 of every tile.  One online-softmax state per row: each tile the two exchange
+//               the maxima of their halves through shared memory (a 64-thread barrier per lane
+//               quadrant), scale, mask the diagonal tile, store P back over S in TMEM; one P V of
+//               128 keys accumulates into one O_part (double buffered, folded into the running
+//               output one tile late, so the P V of tile j runs under the softmax of tile j+1);
+//               thread g folds, normalises and stores head dims g*32 .. g*32+31 through a staging
+//               slot per warp and bulk tensor stores.
 // Causal tiles above the diagonal are skipped.  Every mbarrier wait is bounded (see matmul_tc.cu).
 #include <cuda.h>
 #include <cuda_bf16.h>

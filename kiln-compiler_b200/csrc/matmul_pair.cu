@@ -9,22 +9,24 @@
 // ~62 cycles an instruction occupies the pipe whatever its width.
 //
 // A cluster is two CTAs (ranks 0 = leader, 1 = peer), one per SM, persistent over a static list
-// of tiles.  Per CTA, 384 threads:
+// of tiles.  Per CTA, 512 threads:
 //   warp 0      TMA producer (one lane): its CTA's 128 rows of A and its half of the B columns per
 //               pipeline stage, plain (non-multicast) bulk tensor loads with .cta_group::2 so that
 //               both CTAs' bytes complete on the LEADER's `full` barrier.
-//   warp 1      MMA issuer, leader only: tcgen05.mma.cta_group::2 (M = 256, N = BN) reads both
+//   warp 1      TMEM allocation (both CTAs execute the .cta_group::2 alloc / dealloc); then, leader
+//               only, the MMA issuer (one lane): tcgen05.mma.cta_group::2 (M = 256, N = BN) reads both
 //               CTAs' stages and writes each CTA's 128 accumulator rows into that CTA's TMEM; one
-//               tcgen05.commit per CTA hands the stage back (`empty`) or the accumulator on (`tfull`).
-//   warp 2      TMEM allocation (both CTAs execute the .cta_group::2 alloc / dealloc).
-//   warps 4-11  epilogue of the CTA's own 128 rows: tcgen05.ld 32 columns, the fused chain with a
-//               lane per accumulator row, the block staged in shared memory (two to three rotating
-//               slots per warp) and written by bulk tensor stores, float32 and the optional bf16
-//               mirror.  A full-matrix operand of the chain (residual, mask) is brought into the
-//               slot by a bulk tensor LOAD one block ahead, so no warp ever gathers rows from
+//               multicast tcgen05.commit hands the stage back to both CTAs (`empty`) or the
+//               accumulator on (`tfull`).
+//   warps 2-13  epilogue of the CTA's own 128 rows, three warps per TMEM lane quadrant: tcgen05.ld
+//               of a 32-column block, the fused chain with a lane per accumulator row, the block
+//               staged in the warp's shared-memory slot and written by bulk tensor stores, float32
+//               and / or the bf16 mirror.  A full-matrix operand of the chain (residual, mask) is
+//               brought into the slot by a bulk tensor LOAD, so no warp ever gathers rows from
 //               global memory.  Accumulators are double buffered in TMEM: the epilogue of tile i
 //               runs under the main loop of tile i + 1; both CTAs' warps release the buffer on the
-//               leader's `tempty` barrier.
+//               leader's `tempty` barrier.  (Warps 14 and 15 are idle: 512 threads are what leaves
+//               the compiler 128 registers per thread.)
 // Every mbarrier wait is bounded: on expiry the thread records (kernel, site) in the plan's status
 // word, raises its CTA's abort flag, all roles fall through to the exit, which passes the cluster
 // barrier (every path reaches it), frees TMEM and returns.  The other CTA's waits run out by themselves.
