@@ -753,12 +753,14 @@ mm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #ifdef KB200_TRACE
     if (blockIdx.x <= 1 && threadIdx.x == 0) marks[3] = clock64();
 #endif
-    if (warp == kIssuerBWarp && lane < p.splits && lane != (int)rank && !abort_flag) {
-      // my partial of band `lane` -> slot `rank` of CTA `lane`'s receive area
-      const uint32_t dst = map_to_cta(recv0 + rank * band_bytes, (uint32_t)lane);
-      const uint32_t bar = map_to_cta(received, (uint32_t)lane);
+    if (lane == 0 && warp < p.splits && warp != (int)rank && !abort_flag) {
+      // my partial of band `warp` -> slot `rank` of CTA `warp`'s receive area.  One copy per WARP: issued
+      // by the lanes of one warp the seven copies went out one after the other, ~680 cycles each
+      // (4760 cycles between the barrier above and the last issue in the cycle stamps).
+      const uint32_t dst = map_to_cta(recv0 + rank * band_bytes, (uint32_t)warp);
+      const uint32_t bar = map_to_cta(received, (uint32_t)warp);
       asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(dst), "r"(tiles + (uint32_t)lane * band_bytes), "r"(band_bytes), "r"(bar)
+                   ::"r"(dst), "r"(tiles + (uint32_t)warp * band_bytes), "r"(band_bytes), "r"(bar)
                    : "memory");
     }
 #ifdef KB200_TRACE
