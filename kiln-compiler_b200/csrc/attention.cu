@@ -64,6 +64,22 @@ struct AttnParams {
   int* status;
 };
 
+constexpr int kFTile = 64;                 // queries per CTA and keys per tile
+constexpr int kFPitch = 68;                // floats per shared-memory row of Q, K and P (16-byte aligned, rows 4 banks apart)
+constexpr int kFThreads = 256;
+constexpr int kFSmemBytes = (3 * kFTile * kFPitch + kFTile * kHeadDim) * 4;
+
+struct AttnF32Params {
+  const float* q;
+  const float* k;
+  const float* v;
+  int64_t row_stride;        // floats between consecutive tokens of the Q / K / V views
+  float* out;                // [B * T, H * 64] merged heads
+  int64_t out_row_stride;
+  int T, H, B, q_tiles;      // q_tiles = T / 64
+  float scale_log2;
+};
+
 struct AttnState {
   CUtensorMap map_q, map_k, map_v;
   CUtensorMap map_out, map_out16;   // bulk-store maps of the merged heads [B * T, H * 64] and of their bf16 copy
@@ -85,6 +101,8 @@ struct AttnState {
   int64_t out_elems = 0;
   int chain = 5;                   // plan kernels this launch stands for: 5 (one sequence) or 7 (a batch of sequences)
   bool wants_bf16 = false;         // the chain's matmuls are in BF16 mode
+  bool exact = false;              // FP32 mode: the CUDA-core kernel (float32 products) runs instead of the tensor-core one
+  AttnF32Params f32;
 };
 
 __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
@@ -130,6 +148,162 @@ __device__ __forceinline__ float row_max32(const float (&v)[32], float m, int fi
     for (int i = 0; i < 32; i += 2) m = fmax3(m, v[i], v[i + 1]);
   }
   return m;
+}
+
+// ---------------------------------------------------------------------------------------------
+// FP32 mode: the same fusion on the CUDA cores.
+//
+// In FP32 mode (the reference's allow_tf32=False, kiln/gpu/codegen.py:515) the products must be
+// float32 products, which the tensor cores only give through three TF32 MMAs on split operands; with
+// Q, K, V and P all split that does not fit one CTA's shared and tensor memory next to the softmax.
+// This kernel keeps the arithmetic on the FMA pipes instead: one CTA per (sequence, head, 64 queries),
+// key tiles of 64, 256 threads as 16 x 16, each with a 4 x 4 block of the scores (rows ty + 16 i,
+// keys tx + 16 j: every quarter-warp load of K then covers all 32 banks) and a 4 x 4 block of the
+// output (rows ty + 16 i, dims 4 tx ..).  A row's 64 scores live in the 16 lanes of one half-warp:
+// maxima and sums go through shuffles, and the probabilities a half-warp writes to shared memory are
+// read back by that half-warp only.  Online softmax in base 2 with Q pre-multiplied by scale * log2(e);
+// causal tiles above the diagonal are skipped; the next K / V tile is fetched into registers while
+// the current one is worked on.  The scores never leave the SM.
+__global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __grid_constant__ AttnF32Params p) {
+  extern __shared__ __align__(16) float fsm[];
+  float* const Qs = fsm;                               // [64 queries][68]
+  float* const Ks = Qs + kFTile * kFPitch;             // [64 keys][68]
+  float* const Ps = Ks + kFTile * kFPitch;             // [64 queries][68] probabilities of the current tile
+  float* const Vs = Ps + kFTile * kFPitch;             // [64 keys][64]
+  pdl_wait();                 // Q, K and V are the previous kernel's output
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  // work item: heaviest (longest causal prefix) query tiles first
+  const int w = blockIdx.x;
+  const int h = w % p.H;
+  const int seq = (w / p.H) % p.B;
+  const int qt = p.q_tiles - 1 - w / (p.H * p.B);
+  const int64_t row0 = (int64_t)seq * p.T;
+  const int64_t rs = p.row_stride;
+  const float* const qg = p.q + (row0 + (int64_t)qt * kFTile) * rs + h * kHeadDim;
+  const float* const kg = p.k + row0 * rs + h * kHeadDim;
+  const float* const vg = p.v + row0 * rs + h * kHeadDim;
+  // a 64 x 64 tile is 1024 float4: thread t moves float4 t, t + 256, ... (row = index / 16)
+  const int ld_r = tid >> 4, ld_c = (tid & 15) * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 v = __ldg(reinterpret_cast<const float4*>(qg + (int64_t)(ld_r + 16 * i) * rs + ld_c));
+    v.x *= p.scale_log2; v.y *= p.scale_log2; v.z *= p.scale_log2; v.w *= p.scale_log2;
+    *reinterpret_cast<float4*>(Qs + (ld_r + 16 * i) * kFPitch + ld_c) = v;
+  }
+  float4 kr[4], vr[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    kr[i] = __ldg(reinterpret_cast<const float4*>(kg + (int64_t)(ld_r + 16 * i) * rs + ld_c));
+    vr[i] = __ldg(reinterpret_cast<const float4*>(vg + (int64_t)(ld_r + 16 * i) * rs + ld_c));
+  }
+  float o[4][4];
+  float m_run[4], l_run[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m_run[i] = -CUDART_INF_F;
+    l_run[i] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+  }
+  for (int j = 0; j <= qt; ++j) {
+    __syncthreads();          // every thread is done with the previous K and V tile
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      *reinterpret_cast<float4*>(Ks + (ld_r + 16 * i) * kFPitch + ld_c) = kr[i];
+      *reinterpret_cast<float4*>(Vs + (ld_r + 16 * i) * kHeadDim + ld_c) = vr[i];
+    }
+    __syncthreads();
+    if (j < qt) {
+      const int64_t next = (int64_t)(j + 1) * kFTile;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        kr[i] = __ldg(reinterpret_cast<const float4*>(kg + (next + ld_r + 16 * i) * rs + ld_c));
+        vr[i] = __ldg(reinterpret_cast<const float4*>(vg + (next + ld_r + 16 * i) * rs + ld_c));
+      }
+    }
+    // ---- scores: s[i][jj] = q[ty + 16 i] . k[tx + 16 jj] ----
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) s[i][jj] = 0.0f;
+#pragma unroll 4
+    for (int kk = 0; kk < kHeadDim; kk += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * kFPitch + kk);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) b[jj] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * jj) * kFPitch + kk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          s[i][jj] = fmaf(a[i].x, b[jj].x, s[i][jj]);
+          s[i][jj] = fmaf(a[i].y, b[jj].y, s[i][jj]);
+          s[i][jj] = fmaf(a[i].z, b[jj].z, s[i][jj]);
+          s[i][jj] = fmaf(a[i].w, b[jj].w, s[i][jj]);
+        }
+    }
+    if (j == qt) {            // the diagonal tile: keys after the query are masked
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          if (tx + 16 * jj > ty + 16 * i) s[i][jj] = -CUDART_INF_F;
+    }
+    // ---- online softmax, one row per half-warp lane group ----
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float mx = fmaxf(fmaxf(s[i][0], s[i][1]), fmaxf(s[i][2], s[i][3]));
+#pragma unroll
+      for (int d = 8; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+      const float m_new = fmaxf(m_run[i], mx);       // finite: key 0 of the first tile is never masked
+      const float alpha = exp2f(m_run[i] - m_new);
+      m_run[i] = m_new;
+      float sum = 0.0f;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const float pr = exp2f(s[i][jj] - m_new);
+        sum += pr;
+        Ps[(ty + 16 * i) * kFPitch + tx + 16 * jj] = pr;
+      }
+#pragma unroll
+      for (int d = 8; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+      l_run[i] = fmaf(l_run[i], alpha, sum);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) o[i][jj] *= alpha;
+    }
+    __syncwarp();             // a row's probabilities are written and read by the same half-warp
+    // ---- o[i][d] += sum over keys of P[ty + 16 i][key] * V[key][4 tx + d] ----
+#pragma unroll 4
+    for (int key = 0; key < kFTile; key += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * kFPitch + key);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4*>(Vs + (key + q) * kHeadDim + 4 * tx);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o[i][0] = fmaf(a[i].x, b[0].x, o[i][0]); o[i][1] = fmaf(a[i].x, b[0].y, o[i][1]);
+        o[i][2] = fmaf(a[i].x, b[0].z, o[i][2]); o[i][3] = fmaf(a[i].x, b[0].w, o[i][3]);
+        o[i][0] = fmaf(a[i].y, b[1].x, o[i][0]); o[i][1] = fmaf(a[i].y, b[1].y, o[i][1]);
+        o[i][2] = fmaf(a[i].y, b[1].z, o[i][2]); o[i][3] = fmaf(a[i].y, b[1].w, o[i][3]);
+        o[i][0] = fmaf(a[i].z, b[2].x, o[i][0]); o[i][1] = fmaf(a[i].z, b[2].y, o[i][1]);
+        o[i][2] = fmaf(a[i].z, b[2].z, o[i][2]); o[i][3] = fmaf(a[i].z, b[2].w, o[i][3]);
+        o[i][0] = fmaf(a[i].w, b[3].x, o[i][0]); o[i][1] = fmaf(a[i].w, b[3].y, o[i][1]);
+        o[i][2] = fmaf(a[i].w, b[3].z, o[i][2]); o[i][3] = fmaf(a[i].w, b[3].w, o[i][3]);
+      }
+    }
+    __syncwarp();             // before the next tile's probabilities overwrite these
+  }
+  float* const og = p.out + (row0 + (int64_t)qt * kFTile) * p.out_row_stride + h * kHeadDim + 4 * tx;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float inv = 1.0f / l_run[i];
+    *reinterpret_cast<float4*>(og + (int64_t)(ty + 16 * i) * p.out_row_stride) =
+        make_float4(o[i][0] * inv, o[i][1] * inv, o[i][2] * inv, o[i][3] * inv);
+  }
 }
 
 template <bool BF16>
@@ -601,6 +775,7 @@ struct AttnChain {
   std::vector<Range> sources;         // what the fused kernel reads (Q, K, V views)
   std::vector<PlanKernel*> matmuls;   // tensor-core state to drop
   bool bf16 = false;
+  bool exact = false;                 // the chain's matmuls are in FP32 mode
 };
 
 // Shared tail of the two matchers: the intermediates must be dead afterwards, the mask causal; then
@@ -650,13 +825,15 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
 
   // Q, K, V as [head, row, 64] views with rows b * T + t: a batch of sequences is more rows of the same map
   AttnState* st = new AttnState();
-  if (!encode_map(&st->map_q, false, c.q, hd, B * T, H, rs, hd, 32, kRows, false) ||
-      !encode_map(&st->map_k, false, c.k, hd, B * T, H, rs, hd, 32, kRows, false) ||
-      !encode_map(&st->map_v, false, c.v, hd, B * T, H, rs, hd, 32, kRows, true)) {
+  st->exact = c.exact;
+  if (!c.exact && (!encode_map(&st->map_q, false, c.q, hd, B * T, H, rs, hd, 32, kRows, false) ||
+                   !encode_map(&st->map_k, false, c.k, hd, B * T, H, rs, hd, 32, kRows, false) ||
+                   !encode_map(&st->map_v, false, c.v, hd, B * T, H, rs, hd, 32, kRows, true))) {
     delete st;
     return false;
   }
   if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
+      cudaFuncSetAttribute(attention_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmemBytes) != cudaSuccess ||
       cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess) {
     cudaGetLastError();
     delete st;
@@ -704,6 +881,17 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   st->map_out16 = st->map_out;
   const int64_t items = B * H * p.q_tiles;
   st->grid = dim3((unsigned)(items < plan.sm_count ? items : plan.sm_count), 1, 1);     // persistent: at most one CTA per SM
+  if (c.exact) {
+    AttnF32Params& f = st->f32;
+    f.q = c.q; f.k = c.k; f.v = c.v;
+    f.row_stride = rs;
+    f.out = p.out;
+    f.out_row_stride = p.out_row_stride;
+    f.T = (int)T; f.H = (int)H; f.B = (int)B;
+    f.q_tiles = (int)(T / kFTile);
+    f.scale_log2 = p.scale_log2;
+    st->grid = dim3((unsigned)(B * H * f.q_tiles), 1, 1);                                // one CTA per (sequence, head, 64 queries)
+  }
 
   for (PlanKernel* k : c.matmuls) destroy_matmul(*k);
   PlanKernel& holder = plan.kernels[c.first];
@@ -726,7 +914,7 @@ bool try_fuse_single(Plan& plan, size_t i) {
   PlanKernel& k5 = plan.kernels[i + 3];
   PlanKernel& k6 = plan.kernels[i + 4];
   // --- k3: scores = Q K^T * scale + mask ---
-  if (k3.desc.kclass != KB200_K_MATMUL || k3.desc.precision == KB200_PREC_FP32 || !k3.has_chain) return false;
+  if (k3.desc.kclass != KB200_K_MATMUL || !k3.has_chain) return false;
   const int64_t H = k3.batch, T = k3.M, hd = k3.K;
   if (hd != kHeadDim || k3.N != T || T % kRows != 0 || T < kRows || H < 1 || H > 65535) return false;
   const DevOperand& Q = k3.ops[k3.desc.a_slot];
@@ -754,7 +942,8 @@ bool try_fuse_single(Plan& plan, size_t i) {
   const DevOperand& P = k4.ops[k4.out_slot];
   if (P.stride[0] != T || P.stride[1] != 1) return false;
   // --- k5: O = P V ---
-  if (k5.desc.kclass != KB200_K_MATMUL || k5.desc.precision == KB200_PREC_FP32 || !k5.has_chain || k5.chain.n != 0) return false;
+  if (k5.desc.kclass != KB200_K_MATMUL || !k5.has_chain || k5.chain.n != 0) return false;
+  if ((k5.desc.precision == KB200_PREC_FP32) != (k3.desc.precision == KB200_PREC_FP32)) return false;
   if (k5.batch != H || k5.M != T || k5.N != hd || k5.K != T) return false;
   const DevOperand& Pa = k5.ops[k5.desc.a_slot];
   const DevOperand& V = k5.ops[k5.desc.b_slot];
@@ -792,6 +981,7 @@ bool try_fuse_single(Plan& plan, size_t i) {
   c.sources = {operand_range(k3, k3.desc.a_slot), operand_range(k5, k5.desc.b_slot), operand_range(k2, k2.chain.first_slot)};
   c.matmuls = {&k3, &k5};
   c.bf16 = k3.desc.precision == KB200_PREC_BF16;
+  c.exact = k3.desc.precision == KB200_PREC_FP32;
   return finish_fusion(plan, c);
 }
 
@@ -818,7 +1008,7 @@ bool try_fuse_batched(Plan& plan, size_t i) {
   PlanKernel& merge = plan.kernels[i + 6];
   const int64_t hd = kHeadDim;
   // --- scores ---
-  if (mm1.desc.kclass != KB200_K_MATMUL || mm1.desc.precision == KB200_PREC_FP32 || !mm1.has_chain || mm1.chain.n != 0) return false;
+  if (mm1.desc.kclass != KB200_K_MATMUL || !mm1.has_chain || mm1.chain.n != 0) return false;
   const int64_t BH = mm1.batch, T = mm1.M;
   if (mm1.K != hd || mm1.N != T || T % kRows != 0 || T < kRows) return false;
   const DevOperand& Qc = mm1.ops[mm1.desc.a_slot];
@@ -865,7 +1055,8 @@ bool try_fuse_batched(Plan& plan, size_t i) {
   if (Vsrc.stride[0] != T * rs || Vsrc.stride[1] != hd || Vsrc.stride[2] != rs || Vsrc.stride[3] != 1) return false;
   if (Vdst.stride[0] != H * T * hd || Vdst.stride[1] != T * hd || Vdst.stride[2] != hd || Vdst.stride[3] != 1) return false;
   // --- O = P V ---
-  if (mm2.desc.kclass != KB200_K_MATMUL || mm2.desc.precision == KB200_PREC_FP32 || !mm2.has_chain || mm2.chain.n != 0) return false;
+  if (mm2.desc.kclass != KB200_K_MATMUL || !mm2.has_chain || mm2.chain.n != 0) return false;
+  if ((mm2.desc.precision == KB200_PREC_FP32) != (mm1.desc.precision == KB200_PREC_FP32)) return false;
   if (mm2.batch != BH || mm2.M != T || mm2.N != hd || mm2.K != T) return false;
   const DevOperand& Pa = mm2.ops[mm2.desc.a_slot];
   const DevOperand& Vc = mm2.ops[mm2.desc.b_slot];
@@ -899,6 +1090,7 @@ bool try_fuse_batched(Plan& plan, size_t i) {
   c.sources = {out_range(cq, cq.chain.first_slot), out_range(ck, ck.chain.first_slot), out_range(cv, cv.chain.first_slot)};
   c.matmuls = {&mm1, &mm2};
   c.bf16 = mm1.desc.precision == KB200_PREC_BF16;
+  c.exact = mm1.desc.precision == KB200_PREC_FP32;
   return finish_fusion(plan, c);
 }
 
@@ -918,7 +1110,9 @@ bool attention_wants_bf16(const PlanKernel& k) { return k.attn && static_cast<co
 
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   const AttnState* st = static_cast<const AttnState*>(k.attn);
-  if (st->bf16)
+  if (st->exact)
+    KB200_CUDA(launch_kernel(plan.pdl, attention_fp32_kernel, st->grid, dim3(kFThreads), kFSmemBytes, s, st->f32));
+  else if (st->bf16)
     KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q, st->map_k,
                              st->map_v, st->map_out, st->map_out16, st->params));
   else
@@ -954,7 +1148,7 @@ bool attention_use_mirror(PlanKernel& k, const float* arena_base, const void* mi
   if (!st) return false;
   // When the planner put the output over the QKV buffer, the output's mirror lies over the operands'
   // mirror as well: CTAs would overwrite bf16 operands others still read.  Keep the float32 operands then.
-  if (st->staged_out != nullptr) return false;
+  if (st->staged_out != nullptr || st->exact) return false;
   const __nv_bfloat16* m = static_cast<const __nv_bfloat16*>(mirror_base);
   const __nv_bfloat16* q = m + (st->q_ptr - arena_base);
   const __nv_bfloat16* kk = m + (st->k_ptr - arena_base);
@@ -1026,7 +1220,7 @@ bool attention_reads_mirror(const PlanKernel& k) { return k.attn && static_cast<
 
 void attention_set_shadow(PlanKernel& k, void* shadow_out) {
   AttnState* st = static_cast<AttnState*>(k.attn);
-  if (!st) return;
+  if (!st || st->exact) return;
   // the bf16 copy of the merged heads needs a store map of its own; without one it is not written
   // (its reader was told to expect it: assign_shadows asks attention_can_shadow first)
   __nv_bfloat16* out16 = static_cast<__nv_bfloat16*>(shadow_out);

@@ -93,10 +93,11 @@ def test_every_kernel_of_the_block_matches_the_oracle_step_by_step(precision, mo
     assert not bad, (bad, errors)
 
 
-@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
 @pytest.mark.parametrize("tokens", [128, 512, 1024])
 def test_fused_attention_equals_the_five_planned_kernels(tokens, precision, monkeypatch):
-    """The fused attention kernel against the unfused plan on the same inputs, and both against float64."""
+    """The fused attention kernel (tensor cores in TF32 / BF16 mode, float32 FMAs in FP32 mode) against
+    the unfused plan on the same inputs, and both against float64."""
     from gpu_helpers import run_case
 
     case = f"gpt2_block_t{tokens}"
@@ -112,11 +113,15 @@ def test_fused_attention_equals_the_five_planned_kernels(tokens, precision, monk
     assert scale_relative_error(fused[0], plain[0]) <= REL_TOL[precision]
 
 
-def test_fp32_never_fuses_attention():
+def test_fp32_mode_fuses_attention_too(monkeypatch):
+    """FP32 mode (the reference's allow_tf32=False) takes the CUDA-core fused kernel: the scores are never written."""
     from gpu_helpers import build_executable
 
     exe = build_executable("gpt2_block_t128", "fp32")
-    assert "attention_fused" not in exe.impls and exe.device_launches == 10      # 11 planned, the K^T copy is folded
+    assert "attention_fused" in exe.impls and exe.impls.count("fused_away") >= 4
+    monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")
+    plain = build_executable("gpt2_block_t128", "fp32")
+    assert "attention_fused" not in plain.impls and plain.device_launches > exe.device_launches
 
 
 def test_replay_with_new_inputs():
@@ -286,6 +291,7 @@ def test_bulk_tensor_stores_equal_plain_stores(case, precision, monkeypatch):
 def test_hot_path_kernels_are_the_specialised_ones(monkeypatch):
     from gpu_helpers import build_executable
 
+    monkeypatch.setenv("KILN_GPU_FUSE_ATTENTION", "0")   # the five planned attention kernels, each on its own
     exe = build_executable("gpt2_block_t128")
     by_name = dict(zip(exe.launch_names, exe.impls))
     assert by_name["k0_row"] == "row_layernorm" and by_name["k8_row"] == "row_layernorm"
