@@ -78,7 +78,14 @@ struct AttnF32Params {
   int64_t out_row_stride;
   int T, H, B, q_tiles;      // q_tiles = T / 64
   float scale_log2;
+  // Query tiles from `split_from` on (the long causal prefixes) are worked on by two CTAs, one per half
+  // of the key tiles; each leaves its unnormalised output and softmax state in `partial`, and the one
+  // that finishes second (a counter per tile in `arrivals`) merges the two and writes the rows.
+  int split_from;
+  float* partial;            // [split item][2 halves][64 x 64 output | 64 maxima | 64 sums]
+  int* arrivals;             // [split item], zero between launches
 };
+constexpr int kFPartialFloats = kFTile * kHeadDim + 2 * kFTile;
 
 struct AttnState {
   CUtensorMap map_q, map_k, map_v;
@@ -103,6 +110,7 @@ struct AttnState {
   bool wants_bf16 = false;         // the chain's matmuls are in BF16 mode
   bool exact = false;              // FP32 mode: the CUDA-core kernel (float32 products) runs instead of the tensor-core one
   AttnF32Params f32;
+  void* f32_scratch = nullptr;     // the split tiles' partial results and arrival counters
 };
 
 __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
@@ -173,11 +181,17 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
   pdl_wait();                 // Q, K and V are the previous kernel's output
   pdl_launch_dependents();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  // work item: heaviest (longest causal prefix) query tiles first
+  // work item: the halves of the split query tiles first (longest causal prefixes first), then the rest
   const int w = blockIdx.x;
   const int h = w % p.H;
   const int seq = (w / p.H) % p.B;
-  const int qt = p.q_tiles - 1 - w / (p.H * p.B);
+  const int v = w / (p.H * p.B);
+  const int n_split = p.q_tiles - p.split_from;
+  const bool split = v < 2 * n_split;
+  const int qt = split ? p.q_tiles - 1 - (v >> 1) : p.split_from - 1 - (v - 2 * n_split);
+  const int half = split ? (v & 1) : 0;
+  const int j_begin = split && half ? (qt + 1) >> 1 : 0;            // key tiles [j_begin, j_end)
+  const int j_end = split && !half ? (qt + 1) >> 1 : qt + 1;
   const int64_t row0 = (int64_t)seq * p.T;
   const int64_t rs = p.row_stride;
   const float* const qg = p.q + (row0 + (int64_t)qt * kFTile) * rs + h * kHeadDim;
@@ -194,8 +208,8 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
   float4 kr[4], vr[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    kr[i] = __ldg(reinterpret_cast<const float4*>(kg + (int64_t)(ld_r + 16 * i) * rs + ld_c));
-    vr[i] = __ldg(reinterpret_cast<const float4*>(vg + (int64_t)(ld_r + 16 * i) * rs + ld_c));
+    kr[i] = __ldg(reinterpret_cast<const float4*>(kg + ((int64_t)j_begin * kFTile + ld_r + 16 * i) * rs + ld_c));
+    vr[i] = __ldg(reinterpret_cast<const float4*>(vg + ((int64_t)j_begin * kFTile + ld_r + 16 * i) * rs + ld_c));
   }
   float o[4][4];
   float m_run[4], l_run[4];
@@ -206,7 +220,7 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
   }
-  for (int j = 0; j <= qt; ++j) {
+  for (int j = j_begin; j < j_end; ++j) {
     __syncthreads();          // every thread is done with the previous K and V tile
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -214,7 +228,7 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
       *reinterpret_cast<float4*>(Vs + (ld_r + 16 * i) * kHeadDim + ld_c) = vr[i];
     }
     __syncthreads();
-    if (j < qt) {
+    if (j + 1 < j_end) {
       const int64_t next = (int64_t)(j + 1) * kFTile;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -296,6 +310,45 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
       }
     }
     __syncwarp();             // before the next tile's probabilities overwrite these
+  }
+  if (split) {
+    // Leave this half's state in the workspace; the CTA that arrives second merges.  No CTA waits
+    // for another: whoever is first just leaves.
+    const int item = (seq * p.H + h) * n_split + (qt - p.split_from);
+    float* const mine = p.partial + ((size_t)item * 2 + half) * kFPartialFloats;
+    const float* const other = p.partial + ((size_t)item * 2 + (half ^ 1)) * kFPartialFloats;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __stcg(reinterpret_cast<float4*>(mine + (ty + 16 * i) * kHeadDim + 4 * tx), make_float4(o[i][0], o[i][1], o[i][2], o[i][3]));
+      if (tx == 0) {
+        __stcg(mine + kFTile * kHeadDim + ty + 16 * i, m_run[i]);
+        __stcg(mine + kFTile * kHeadDim + kFTile + ty + 16 * i, l_run[i]);
+      }
+    }
+    __threadfence();
+    __shared__ int second;
+    __syncthreads();
+    if (tid == 0) {
+      second = atomicAdd(p.arrivals + item, 1);
+      __threadfence();
+    }
+    __syncthreads();
+    if (!second) return;
+    if (tid == 0) p.arrivals[item] = 0;            // for the next launch
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float m2 = __ldcg(other + kFTile * kHeadDim + ty + 16 * i);
+      const float l2 = __ldcg(other + kFTile * kHeadDim + kFTile + ty + 16 * i);
+      const float4 o2 = __ldcg(reinterpret_cast<const float4*>(other + (ty + 16 * i) * kHeadDim + 4 * tx));
+      const float m = fmaxf(m_run[i], m2);
+      const float a1 = exp2f(m_run[i] - m), a2 = exp2f(m2 - m);
+      // symmetric in the two halves: the same bits whichever CTA merges
+      l_run[i] = l_run[i] * a1 + l2 * a2;
+      o[i][0] = o[i][0] * a1 + o2.x * a2;
+      o[i][1] = o[i][1] * a1 + o2.y * a2;
+      o[i][2] = o[i][2] * a1 + o2.z * a2;
+      o[i][3] = o[i][3] * a1 + o2.w * a2;
+    }
   }
   float* const og = p.out + (row0 + (int64_t)qt * kFTile) * p.out_row_stride + h * kHeadDim + 4 * tx;
 #pragma unroll
@@ -890,7 +943,25 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
     f.T = (int)T; f.H = (int)H; f.B = (int)B;
     f.q_tiles = (int)(T / kFTile);
     f.scale_log2 = p.scale_log2;
-    st->grid = dim3((unsigned)(B * H * f.q_tiles), 1, 1);                                // one CTA per (sequence, head, 64 queries)
+    // the upper half of the query tiles (the longest causal prefixes) is shared by two CTAs each
+    f.split_from = f.q_tiles >= 2 ? f.q_tiles / 2 : f.q_tiles;
+    const int64_t n_split = f.q_tiles - f.split_from, split_items = B * H * n_split;
+    f.partial = nullptr;
+    f.arrivals = nullptr;
+    if (split_items > 0) {
+      const size_t partial_bytes = (size_t)split_items * 2 * kFPartialFloats * sizeof(float);
+      if (cudaMalloc(&st->f32_scratch, partial_bytes + (size_t)split_items * sizeof(int)) != cudaSuccess ||
+          cudaMemset(static_cast<uint8_t*>(st->f32_scratch) + partial_bytes, 0, (size_t)split_items * sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        if (st->f32_scratch) cudaFree(st->f32_scratch);
+        if (st->staged_out) cudaFree(st->staged_out);
+        delete st;
+        return false;
+      }
+      f.partial = static_cast<float*>(st->f32_scratch);
+      f.arrivals = reinterpret_cast<int*>(static_cast<uint8_t*>(st->f32_scratch) + partial_bytes);
+    }
+    st->grid = dim3((unsigned)(B * H * (f.q_tiles + n_split)), 1, 1);    // a CTA per (sequence, head, 64 queries[, half of the keys])
   }
 
   for (PlanKernel* k : c.matmuls) destroy_matmul(*k);
@@ -1239,6 +1310,7 @@ void attention_destroy(PlanKernel& k) {
   if (k.attn) {
     AttnState* st = static_cast<AttnState*>(k.attn);
     if (st->staged_out) cudaFree(st->staged_out);
+    if (st->f32_scratch) cudaFree(st->f32_scratch);
     delete st;
   }
   k.attn = nullptr;
