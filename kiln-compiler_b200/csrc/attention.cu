@@ -66,8 +66,9 @@ struct AttnParams {
 
 constexpr int kFTile = 64;                 // queries per CTA and keys per tile
 constexpr int kFPitch = 68;                // floats per shared-memory row of Q, K and P (16-byte aligned, rows 4 banks apart)
-constexpr int kFThreads = 256;
-constexpr int kFSmemBytes = (3 * kFTile * kFPitch + kFTile * kHeadDim) * 4;
+constexpr int kFThreads = 128;
+constexpr int kFRows = 8;                  // query rows per thread (64 rows over 8 thread rows)
+constexpr int kFSmemBytes = (4 * kFTile * kFPitch + 2 * kFTile * kHeadDim) * 4;   // Q, P, two K tiles | two V tiles
 
 struct AttnF32Params {
   const float* q;
@@ -164,20 +165,27 @@ __device__ __forceinline__ float row_max32(const float (&v)[32], float m, int fi
 // In FP32 mode (the reference's allow_tf32=False, kiln/gpu/codegen.py:515) the products must be
 // float32 products, which the tensor cores only give through three TF32 MMAs on split operands; with
 // Q, K, V and P all split that does not fit one CTA's shared and tensor memory next to the softmax.
-// This kernel keeps the arithmetic on the FMA pipes instead: one CTA per (sequence, head, 64 queries),
-// key tiles of 64, 256 threads as 16 x 16, each with a 4 x 4 block of the scores (rows ty + 16 i,
-// keys tx + 16 j: every quarter-warp load of K then covers all 32 banks) and a 4 x 4 block of the
-// output (rows ty + 16 i, dims 4 tx ..).  A row's 64 scores live in the 16 lanes of one half-warp:
-// maxima and sums go through shuffles, and the probabilities a half-warp writes to shared memory are
-// read back by that half-warp only.  Online softmax in base 2 with Q pre-multiplied by scale * log2(e);
-// causal tiles above the diagonal are skipped; the next K / V tile is fetched into registers while
-// the current one is worked on.  The scores never leave the SM.
+// This kernel keeps the arithmetic on the FMA pipes instead: one CTA per (sequence, head, 64 queries
+// [, half of the keys]), key tiles of 64, 128 threads as 8 x 16, each with an 8 x 4 block of the
+// scores (rows ty + 8 i, keys tx + 16 j: every quarter-warp load of K then covers all 32 banks) and
+// an 8 x 4 block of the output (rows ty + 8 i, dims 4 tx ..).  What bounds such a kernel is the
+// shared-memory-to-register path (128 bytes per clock and SM, whatever is broadcast): a 4 x 4 block
+// per thread loads half a float per multiply-add and stopped at 53 % of the FMA pipe; 8 x 4 loads
+// 0.375.  A row's 64 scores live in the 16 lanes of one half-warp: maxima and sums go through
+// shuffles, and the probabilities a half-warp writes to shared memory are read back by that
+// half-warp only.  Online softmax in base 2 with Q pre-multiplied by scale * log2(e); causal tiles
+// above the diagonal are skipped; K / V tiles arrive through a two-deep cp.async ring.  The scores
+// never leave the SM.
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+
 __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __grid_constant__ AttnF32Params p) {
   extern __shared__ __align__(16) float fsm[];
   float* const Qs = fsm;                               // [64 queries][68]
-  float* const Ks = Qs + kFTile * kFPitch;             // [64 keys][68]
-  float* const Ps = Ks + kFTile * kFPitch;             // [64 queries][68] probabilities of the current tile
-  float* const Vs = Ps + kFTile * kFPitch;             // [64 keys][64]
+  float* const Ps = Qs + kFTile * kFPitch;             // [64 queries][68] probabilities of the current tile
+  float* const Ks = Ps + kFTile * kFPitch;             // 2 x [64 keys][68]
+  float* const Vs = Ks + 2 * kFTile * kFPitch;         // 2 x [64 keys][64]
   pdl_wait();                 // Q, K and V are the previous kernel's output
   pdl_launch_dependents();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -197,82 +205,78 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
   const float* const qg = p.q + (row0 + (int64_t)qt * kFTile) * rs + h * kHeadDim;
   const float* const kg = p.k + row0 * rs + h * kHeadDim;
   const float* const vg = p.v + row0 * rs + h * kHeadDim;
-  // a 64 x 64 tile is 1024 float4: thread t moves float4 t, t + 256, ... (row = index / 16)
+  // a 64 x 64 tile is 1024 float4: thread t moves float4 t, t + 128, ... (row = index / 16)
   const int ld_r = tid >> 4, ld_c = (tid & 15) * 4;
+  auto fetch = [&](int j) {
+    float* const kd = Ks + (j & 1) * kFTile * kFPitch;
+    float* const vd = Vs + (j & 1) * kFTile * kHeadDim;
+    const int64_t first = (int64_t)j * kFTile;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float4 v = __ldg(reinterpret_cast<const float4*>(qg + (int64_t)(ld_r + 16 * i) * rs + ld_c));
-    v.x *= p.scale_log2; v.y *= p.scale_log2; v.z *= p.scale_log2; v.w *= p.scale_log2;
-    *reinterpret_cast<float4*>(Qs + (ld_r + 16 * i) * kFPitch + ld_c) = v;
+    for (int i = 0; i < kFRows; ++i) {
+      cp_async16(kd + (ld_r + 8 * i) * kFPitch + ld_c, kg + (first + ld_r + 8 * i) * rs + ld_c);
+      cp_async16(vd + (ld_r + 8 * i) * kHeadDim + ld_c, vg + (first + ld_r + 8 * i) * rs + ld_c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(j_begin);
+#pragma unroll
+  for (int i = 0; i < kFRows; ++i) {
+    float4 q4 = __ldg(reinterpret_cast<const float4*>(qg + (int64_t)(ld_r + 8 * i) * rs + ld_c));
+    q4.x *= p.scale_log2; q4.y *= p.scale_log2; q4.z *= p.scale_log2; q4.w *= p.scale_log2;
+    *reinterpret_cast<float4*>(Qs + (ld_r + 8 * i) * kFPitch + ld_c) = q4;
   }
-  float4 kr[4], vr[4];
+  float o[kFRows][4];
+  float m_run[kFRows], l_run[kFRows];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    kr[i] = __ldg(reinterpret_cast<const float4*>(kg + ((int64_t)j_begin * kFTile + ld_r + 16 * i) * rs + ld_c));
-    vr[i] = __ldg(reinterpret_cast<const float4*>(vg + ((int64_t)j_begin * kFTile + ld_r + 16 * i) * rs + ld_c));
-  }
-  float o[4][4];
-  float m_run[4], l_run[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < kFRows; ++i) {
     m_run[i] = -CUDART_INF_F;
     l_run[i] = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+    for (int jj = 0; jj < 4; ++jj) o[i][jj] = 0.0f;
   }
   for (int j = j_begin; j < j_end; ++j) {
-    __syncthreads();          // every thread is done with the previous K and V tile
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();          // tile j has landed for everyone (Q too), and everyone is done with tile j - 1
+    if (j + 1 < j_end) fetch(j + 1);
+    const float* const Kt = Ks + (j & 1) * kFTile * kFPitch;
+    const float* const Vt = Vs + (j & 1) * kFTile * kHeadDim;
+    // ---- scores: s[i][jj] = q[ty + 8 i] . k[tx + 16 jj] ----
+    float s[kFRows][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      *reinterpret_cast<float4*>(Ks + (ld_r + 16 * i) * kFPitch + ld_c) = kr[i];
-      *reinterpret_cast<float4*>(Vs + (ld_r + 16 * i) * kHeadDim + ld_c) = vr[i];
-    }
-    __syncthreads();
-    if (j + 1 < j_end) {
-      const int64_t next = (int64_t)(j + 1) * kFTile;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        kr[i] = __ldg(reinterpret_cast<const float4*>(kg + (next + ld_r + 16 * i) * rs + ld_c));
-        vr[i] = __ldg(reinterpret_cast<const float4*>(vg + (next + ld_r + 16 * i) * rs + ld_c));
-      }
-    }
-    // ---- scores: s[i][jj] = q[ty + 16 i] . k[tx + 16 jj] ----
-    float s[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < kFRows; ++i)
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) s[i][jj] = 0.0f;
-#pragma unroll 4
+#pragma unroll 2
     for (int kk = 0; kk < kHeadDim; kk += 4) {
-      float4 a[4], b[4];
+      float4 b[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * kFPitch + kk);
+      for (int jj = 0; jj < 4; ++jj) b[jj] = *reinterpret_cast<const float4*>(Kt + (tx + 16 * jj) * kFPitch + kk);
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) b[jj] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * jj) * kFPitch + kk);
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < kFRows; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(Qs + (ty + 8 * i) * kFPitch + kk);
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          s[i][jj] = fmaf(a[i].x, b[jj].x, s[i][jj]);
-          s[i][jj] = fmaf(a[i].y, b[jj].y, s[i][jj]);
-          s[i][jj] = fmaf(a[i].z, b[jj].z, s[i][jj]);
-          s[i][jj] = fmaf(a[i].w, b[jj].w, s[i][jj]);
+          s[i][jj] = fmaf(a.x, b[jj].x, s[i][jj]);
+          s[i][jj] = fmaf(a.y, b[jj].y, s[i][jj]);
+          s[i][jj] = fmaf(a.z, b[jj].z, s[i][jj]);
+          s[i][jj] = fmaf(a.w, b[jj].w, s[i][jj]);
         }
+      }
     }
     if (j == qt) {            // the diagonal tile: keys after the query are masked
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < kFRows; ++i)
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj)
-          if (tx + 16 * jj > ty + 16 * i) s[i][jj] = -CUDART_INF_F;
+          if (tx + 16 * jj > ty + 8 * i) s[i][jj] = -CUDART_INF_F;
     }
-    // ---- online softmax, one row per half-warp lane group ----
+    // ---- online softmax, one row per half-warp ----
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < kFRows; ++i) {
       float mx = fmaxf(fmaxf(s[i][0], s[i][1]), fmaxf(s[i][2], s[i][3]));
 #pragma unroll
       for (int d = 8; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-      const float m_new = fmaxf(m_run[i], mx);       // finite: key 0 of the first tile is never masked
+      const float m_new = fmaxf(m_run[i], mx);       // finite: the first key of a tile is never masked
       const float alpha = exp2f(m_run[i] - m_new);
       m_run[i] = m_new;
       float sum = 0.0f;
@@ -280,7 +284,7 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
       for (int jj = 0; jj < 4; ++jj) {
         const float pr = exp2f(s[i][jj] - m_new);
         sum += pr;
-        Ps[(ty + 16 * i) * kFPitch + tx + 16 * jj] = pr;
+        Ps[(ty + 8 * i) * kFPitch + tx + 16 * jj] = pr;
       }
 #pragma unroll
       for (int d = 8; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
@@ -289,24 +293,23 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
       for (int jj = 0; jj < 4; ++jj) o[i][jj] *= alpha;
     }
     __syncwarp();             // a row's probabilities are written and read by the same half-warp
-    // ---- o[i][d] += sum over keys of P[ty + 16 i][key] * V[key][4 tx + d] ----
-#pragma unroll 4
+    // ---- o[i][d] += sum over keys of P[ty + 8 i][key] * V[key][4 tx + d] ----
+#pragma unroll 2
     for (int key = 0; key < kFTile; key += 4) {
-      float4 a[4], b[4];
+      float4 b[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * kFPitch + key);
+      for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4*>(Vt + (key + q) * kHeadDim + 4 * tx);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4*>(Vs + (key + q) * kHeadDim + 4 * tx);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        o[i][0] = fmaf(a[i].x, b[0].x, o[i][0]); o[i][1] = fmaf(a[i].x, b[0].y, o[i][1]);
-        o[i][2] = fmaf(a[i].x, b[0].z, o[i][2]); o[i][3] = fmaf(a[i].x, b[0].w, o[i][3]);
-        o[i][0] = fmaf(a[i].y, b[1].x, o[i][0]); o[i][1] = fmaf(a[i].y, b[1].y, o[i][1]);
-        o[i][2] = fmaf(a[i].y, b[1].z, o[i][2]); o[i][3] = fmaf(a[i].y, b[1].w, o[i][3]);
-        o[i][0] = fmaf(a[i].z, b[2].x, o[i][0]); o[i][1] = fmaf(a[i].z, b[2].y, o[i][1]);
-        o[i][2] = fmaf(a[i].z, b[2].z, o[i][2]); o[i][3] = fmaf(a[i].z, b[2].w, o[i][3]);
-        o[i][0] = fmaf(a[i].w, b[3].x, o[i][0]); o[i][1] = fmaf(a[i].w, b[3].y, o[i][1]);
-        o[i][2] = fmaf(a[i].w, b[3].z, o[i][2]); o[i][3] = fmaf(a[i].w, b[3].w, o[i][3]);
+      for (int i = 0; i < kFRows; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(Ps + (ty + 8 * i) * kFPitch + key);
+        o[i][0] = fmaf(a.x, b[0].x, o[i][0]); o[i][1] = fmaf(a.x, b[0].y, o[i][1]);
+        o[i][2] = fmaf(a.x, b[0].z, o[i][2]); o[i][3] = fmaf(a.x, b[0].w, o[i][3]);
+        o[i][0] = fmaf(a.y, b[1].x, o[i][0]); o[i][1] = fmaf(a.y, b[1].y, o[i][1]);
+        o[i][2] = fmaf(a.y, b[1].z, o[i][2]); o[i][3] = fmaf(a.y, b[1].w, o[i][3]);
+        o[i][0] = fmaf(a.z, b[2].x, o[i][0]); o[i][1] = fmaf(a.z, b[2].y, o[i][1]);
+        o[i][2] = fmaf(a.z, b[2].z, o[i][2]); o[i][3] = fmaf(a.z, b[2].w, o[i][3]);
+        o[i][0] = fmaf(a.w, b[3].x, o[i][0]); o[i][1] = fmaf(a.w, b[3].y, o[i][1]);
+        o[i][2] = fmaf(a.w, b[3].z, o[i][2]); o[i][3] = fmaf(a.w, b[3].w, o[i][3]);
       }
     }
     __syncwarp();             // before the next tile's probabilities overwrite these
@@ -318,11 +321,11 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
     float* const mine = p.partial + ((size_t)item * 2 + half) * kFPartialFloats;
     const float* const other = p.partial + ((size_t)item * 2 + (half ^ 1)) * kFPartialFloats;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __stcg(reinterpret_cast<float4*>(mine + (ty + 16 * i) * kHeadDim + 4 * tx), make_float4(o[i][0], o[i][1], o[i][2], o[i][3]));
+    for (int i = 0; i < kFRows; ++i) {
+      __stcg(reinterpret_cast<float4*>(mine + (ty + 8 * i) * kHeadDim + 4 * tx), make_float4(o[i][0], o[i][1], o[i][2], o[i][3]));
       if (tx == 0) {
-        __stcg(mine + kFTile * kHeadDim + ty + 16 * i, m_run[i]);
-        __stcg(mine + kFTile * kHeadDim + kFTile + ty + 16 * i, l_run[i]);
+        __stcg(mine + kFTile * kHeadDim + ty + 8 * i, m_run[i]);
+        __stcg(mine + kFTile * kHeadDim + kFTile + ty + 8 * i, l_run[i]);
       }
     }
     __threadfence();
@@ -336,10 +339,10 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
     if (!second) return;
     if (tid == 0) p.arrivals[item] = 0;            // for the next launch
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float m2 = __ldcg(other + kFTile * kHeadDim + ty + 16 * i);
-      const float l2 = __ldcg(other + kFTile * kHeadDim + kFTile + ty + 16 * i);
-      const float4 o2 = __ldcg(reinterpret_cast<const float4*>(other + (ty + 16 * i) * kHeadDim + 4 * tx));
+    for (int i = 0; i < kFRows; ++i) {
+      const float m2 = __ldcg(other + kFTile * kHeadDim + ty + 8 * i);
+      const float l2 = __ldcg(other + kFTile * kHeadDim + kFTile + ty + 8 * i);
+      const float4 o2 = __ldcg(reinterpret_cast<const float4*>(other + (ty + 8 * i) * kHeadDim + 4 * tx));
       const float m = fmaxf(m_run[i], m2);
       const float a1 = exp2f(m_run[i] - m), a2 = exp2f(m2 - m);
       // symmetric in the two halves: the same bits whichever CTA merges
@@ -352,9 +355,9 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
   }
   float* const og = p.out + (row0 + (int64_t)qt * kFTile) * p.out_row_stride + h * kHeadDim + 4 * tx;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < kFRows; ++i) {
     const float inv = 1.0f / l_run[i];
-    *reinterpret_cast<float4*>(og + (int64_t)(ty + 16 * i) * p.out_row_stride) =
+    *reinterpret_cast<float4*>(og + (int64_t)(ty + 8 * i) * p.out_row_stride) =
         make_float4(o[i][0] * inv, o[i][1] * inv, o[i][2] * inv, o[i][3] * inv);
   }
 }
