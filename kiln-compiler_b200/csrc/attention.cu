@@ -225,14 +225,13 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
     q4.x *= p.scale_log2; q4.y *= p.scale_log2; q4.z *= p.scale_log2; q4.w *= p.scale_log2;
     *reinterpret_cast<float4*>(Qs + (ld_r + 8 * i) * kFPitch + ld_c) = q4;
   }
-  float o[kFRows][4];
+  float2 o2[kFRows][2];        // dims (4 tx, 4 tx + 1) and (4 tx + 2, 4 tx + 3)
   float m_run[kFRows], l_run[kFRows];
 #pragma unroll
   for (int i = 0; i < kFRows; ++i) {
     m_run[i] = -CUDART_INF_F;
     l_run[i] = 0.0f;
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) o[i][jj] = 0.0f;
+    o2[i][0] = o2[i][1] = make_float2(0.0f, 0.0f);
   }
   for (int j = j_begin; j < j_end; ++j) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -241,11 +240,14 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
     const float* const Kt = Ks + (j & 1) * kFTile * kFPitch;
     const float* const Vt = Vs + (j & 1) * kFTile * kHeadDim;
     // ---- scores: s[i][jj] = q[ty + 8 i] . k[tx + 16 jj] ----
-    float s[kFRows][4];
+    // Packed multiply-adds (two per instruction): the even and the odd head dims of a product are
+    // summed apart -- both operand pairs are then halves of the 128-bit loads as they stand -- and
+    // added at the end.
+    float2 s2[kFRows][4];
 #pragma unroll
     for (int i = 0; i < kFRows; ++i)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) s[i][jj] = 0.0f;
+      for (int jj = 0; jj < 4; ++jj) s2[i][jj] = make_float2(0.0f, 0.0f);
 #pragma unroll 2
     for (int kk = 0; kk < kHeadDim; kk += 4) {
       float4 b[4];
@@ -256,13 +258,16 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
         const float4 a = *reinterpret_cast<const float4*>(Qs + (ty + 8 * i) * kFPitch + kk);
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          s[i][jj] = fmaf(a.x, b[jj].x, s[i][jj]);
-          s[i][jj] = fmaf(a.y, b[jj].y, s[i][jj]);
-          s[i][jj] = fmaf(a.z, b[jj].z, s[i][jj]);
-          s[i][jj] = fmaf(a.w, b[jj].w, s[i][jj]);
+          s2[i][jj] = ffma2(make_float2(a.x, a.y), make_float2(b[jj].x, b[jj].y), s2[i][jj]);
+          s2[i][jj] = ffma2(make_float2(a.z, a.w), make_float2(b[jj].z, b[jj].w), s2[i][jj]);
         }
       }
     }
+    float s[kFRows][4];
+#pragma unroll
+    for (int i = 0; i < kFRows; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) s[i][jj] = s2[i][jj].x + s2[i][jj].y;
     if (j == qt) {            // the diagonal tile: keys after the query are masked
 #pragma unroll
       for (int i = 0; i < kFRows; ++i)
@@ -289,8 +294,8 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
 #pragma unroll
       for (int d = 8; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
       l_run[i] = fmaf(l_run[i], alpha, sum);
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) o[i][jj] *= alpha;
+      o2[i][0] = fmul2(o2[i][0], make_float2(alpha, alpha));
+      o2[i][1] = fmul2(o2[i][1], make_float2(alpha, alpha));
     }
     __syncwarp();             // a row's probabilities are written and read by the same half-warp
     // ---- o[i][d] += sum over keys of P[ty + 8 i][key] * V[key][4 tx + d] ----
@@ -302,17 +307,23 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
 #pragma unroll
       for (int i = 0; i < kFRows; ++i) {
         const float4 a = *reinterpret_cast<const float4*>(Ps + (ty + 8 * i) * kFPitch + key);
-        o[i][0] = fmaf(a.x, b[0].x, o[i][0]); o[i][1] = fmaf(a.x, b[0].y, o[i][1]);
-        o[i][2] = fmaf(a.x, b[0].z, o[i][2]); o[i][3] = fmaf(a.x, b[0].w, o[i][3]);
-        o[i][0] = fmaf(a.y, b[1].x, o[i][0]); o[i][1] = fmaf(a.y, b[1].y, o[i][1]);
-        o[i][2] = fmaf(a.y, b[1].z, o[i][2]); o[i][3] = fmaf(a.y, b[1].w, o[i][3]);
-        o[i][0] = fmaf(a.z, b[2].x, o[i][0]); o[i][1] = fmaf(a.z, b[2].y, o[i][1]);
-        o[i][2] = fmaf(a.z, b[2].z, o[i][2]); o[i][3] = fmaf(a.z, b[2].w, o[i][3]);
-        o[i][0] = fmaf(a.w, b[3].x, o[i][0]); o[i][1] = fmaf(a.w, b[3].y, o[i][1]);
-        o[i][2] = fmaf(a.w, b[3].z, o[i][2]); o[i][3] = fmaf(a.w, b[3].w, o[i][3]);
+        // dims (0, 1) and (2, 3) as pairs; a probability is duplicated into both halves of its operand
+        o2[i][0] = ffma2(make_float2(a.x, a.x), make_float2(b[0].x, b[0].y), o2[i][0]);
+        o2[i][1] = ffma2(make_float2(a.x, a.x), make_float2(b[0].z, b[0].w), o2[i][1]);
+        o2[i][0] = ffma2(make_float2(a.y, a.y), make_float2(b[1].x, b[1].y), o2[i][0]);
+        o2[i][1] = ffma2(make_float2(a.y, a.y), make_float2(b[1].z, b[1].w), o2[i][1]);
+        o2[i][0] = ffma2(make_float2(a.z, a.z), make_float2(b[2].x, b[2].y), o2[i][0]);
+        o2[i][1] = ffma2(make_float2(a.z, a.z), make_float2(b[2].z, b[2].w), o2[i][1]);
+        o2[i][0] = ffma2(make_float2(a.w, a.w), make_float2(b[3].x, b[3].y), o2[i][0]);
+        o2[i][1] = ffma2(make_float2(a.w, a.w), make_float2(b[3].z, b[3].w), o2[i][1]);
       }
     }
     __syncwarp();             // before the next tile's probabilities overwrite these
+  }
+  float o[kFRows][4];
+#pragma unroll
+  for (int i = 0; i < kFRows; ++i) {
+    o[i][0] = o2[i][0].x; o[i][1] = o2[i][0].y; o[i][2] = o2[i][1].x; o[i][3] = o2[i][1].y;
   }
   if (split) {
     // Leave this half's state in the workspace; the CTA that arrives second merges.  No CTA waits
