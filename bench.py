@@ -603,6 +603,8 @@ def extras(precision):
     if precision not in ("fp32", "tf32"):
         out["block_t128"] = block_numbers("gpt2_block_t128", precision)
     out["block_t2048"] = block_numbers("gpt2_block_t2048", precision)
+    if precision != "fp32":
+        out["block_t2048_fp32"] = block_numbers("gpt2_block_t2048", "fp32")    # FP32 mode's attention runs on the FMA pipes
     return out
 
 
@@ -685,6 +687,7 @@ def reference_triton_arm(args):
     section("block_t128_fp32", block(128, 0, False))
     section("block_t128", block(128, 0, True))
     section("block_t2048", block(2048, SEED, True))
+    section("block_t2048_fp32", block(2048, SEED, False))
     section("block_t1024", block(1024, SEED, True))
     for m, n, k in W.LINEAR_SHAPES:
         section(f"linear_tf32_{m}x{n}x{k}", kernel_case(f"linear_{m}x{n}x{k}", True, args.autotune, flops=2 * m * n * k))
