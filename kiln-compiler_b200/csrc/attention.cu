@@ -29,6 +29,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <vector>
 
 #include "device_math.cuh"
@@ -50,6 +52,8 @@ constexpr int kExchangeBytes = 2 * (2 * 2 * kRows * 4);   // the pairs' maxima (
 constexpr int kStageBytes = 4096 + 2048;      // a warp's output rows: 32 x 32 float32 and their bf16 copy
 // Q + 2 x K + 2 x V tiles (two 16 KB slabs each in float32, one in bf16), the two merge buffers, alignment slack
 constexpr int attn_smem(bool bf16) { return 5 * (bf16 ? 1 : 2) * kSlab + kExchangeBytes + 8 * kStageBytes + 1024; }
+// FP32 mode on the tensor cores: Q, K, V once each with their tails (4 slabs per operand), the exchange area, slack
+constexpr int kExactSmemBytes = 3 * 4 * kSlab + kExchangeBytes + 1024;
 
 struct AttnParams {
   int T, H, q_tiles;
@@ -109,10 +113,31 @@ struct AttnState {
   int64_t out_elems = 0;
   int chain = 5;                   // plan kernels this launch stands for: 5 (one sequence) or 7 (a batch of sequences)
   bool wants_bf16 = false;         // the chain's matmuls are in BF16 mode
-  bool exact = false;              // FP32 mode: the CUDA-core kernel (float32 products) runs instead of the tensor-core one
+  bool exact = false;              // FP32 mode: float32 products, on the tensor cores (three TF32 MMAs each) or on the FMA pipes
+  bool exact_tc = false;           // ... on the tensor cores (enough work items to fill the GPU), else the CUDA-core kernel
   AttnF32Params f32;
-  void* f32_scratch = nullptr;     // the split tiles' partial results and arrival counters
+  void* f32_scratch = nullptr;     // CUDA-core kernel: the split tiles' partial results and arrival counters
+  CUtensorMap map_qt, map_kt, map_vt;   // tensor-core FP32 kernel: Q, K, V views of the tails buffer
+  float* tails = nullptr;          // tails (x minus its 19 leading bits) of the span of the QKV buffer the views cover
+  const float* span_lo = nullptr;
+  int64_t span_n4 = 0;
 };
+
+// tails[i] = src[i] minus its 19 leading bits (what a TF32 operand keeps): the second terms of the
+// split products of the FP32-mode tensor-core attention.
+__global__ void __launch_bounds__(256) tails_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
+  pdl_wait();                 // the producer of Q, K and V has completed
+  pdl_launch_dependents();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = src[i];
+    float4 t;
+    t.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+    t.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+    t.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+    t.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+    dst[i] = t;
+  }
+}
 
 __global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
   pdl_wait();                 // the producer of this kernel's inputs has completed
@@ -775,6 +800,403 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// FP32 mode on the tensor cores: the kernel above with float32 products from three TF32 MMAs each
+// (x = head + tail, head the 19 leading bits the tensor core reads anyway: x y ~ head head + head tail
+// + tail head).  The tails of Q, K and V come from a copy of the QKV buffer that a small kernel
+// fills in front of this one (`tails_kernel`), through tensor maps of their own into the second
+// half of every operand buffer; the softmax threads write the probabilities' tails into tensor
+// memory next to the probabilities.  Differences in structure, all for space: K and V have one
+// buffer each instead of a ring of two (heads + tails of Q, K, V fill 192 KB; the next tile's loads
+// run under the softmax, which is the long pole), the tails of P have one buffer (a thread folds the
+// previous tile's O_part -- whose completion says its P V has read them -- before it writes the
+// next), and the output rows leave by ordinary stores (no staging slots).
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_qt,
+                       const __grid_constant__ CUtensorMap map_kt, const __grid_constant__ CUtensorMap map_vt,
+                       const __grid_constant__ AttnParams p) {
+  // a [128 rows x 64 dims] float32 operand tile is two 128-byte-wide slabs; an operand buffer holds the tile and its tails
+  constexpr int kTileSlabs = 2;
+  constexpr int kTileBytes = kTileSlabs * kSlab;
+  constexpr int kOpBytes = 2 * kTileBytes;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[20];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+#ifdef KB200_TRACE
+  __shared__ long long trace[4][16];
+  __shared__ long long mma_trace[64];
+  __shared__ long long marks[4];
+  int tm = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    marks[0] = (long long)g;
+    marks[1] = clock64();
+  }
+#endif
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t q_smem = (raw + 1023u) & ~1023u;
+  const uint32_t k_smem = q_smem + kOpBytes;        // one buffer each: tile, then its tails
+  const uint32_t v_smem = k_smem + kOpBytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
+  //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer] | 19 q_empty
+  const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
+  const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
+  const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull0 = smem_u32(&bars[15]);
+  const uint32_t q_empty = smem_u32(&bars[19]);
+
+  // work item w -> (head, sequence, query tile): heaviest (longest causal prefix) tiles first, of every sequence
+  const int n_items = p.B * p.H * p.q_tiles;
+  // This CTA's r-th item (-1: none).  Rounds alternate direction over the CTAs, so that the CTA with the
+  // heaviest item of one round takes the lightest of the next (24 key tiles at most per CTA instead of
+  // 27 for 8 x 12 x 8 items on 148 CTAs).
+  auto nth_item = [&](int r) {
+    const int w = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return w < n_items ? w : -1;
+  };
+  struct Item { int h, q0, n_kv, row0, qt; };
+  auto item_of = [&](int w) {
+    Item it;
+    it.h = w % p.H;
+    const int seq = (w / p.H) % p.B;
+    it.qt = p.q_tiles - 1 - w / (p.H * p.B);
+    it.q0 = it.qt * kRows;
+    it.n_kv = it.qt + 1;                               // causal: key tiles 0..qt
+    it.row0 = seq * p.T;                               // this sequence's first row in Q, K, V and the output
+    return it;
+  };
+
+  if (threadIdx.x == 32) {
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    prefetch_tensormap(&map_qt);
+    prefetch_tensormap(&map_kt);
+    prefetch_tensormap(&map_vt);
+  }
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + 8 * s, 1);
+      mbar_init(k_empty + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1);
+      mbar_init(v_empty + 8 * s, 1);
+      mbar_init(sfull0 + 8 * s, 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(pfull0 + 8 * i, 128);
+      mbar_init(ofull0 + 8 * i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // Everything above overlapped the previous kernel's tail; Q, K and V are its output.
+  pdl_wait();
+  pdl_launch_dependents();
+  const uint32_t tmem_base = tmem_base_slot;
+  // columns: S0 0..127 | S1 128..255 | O_part[buffer] 256 + buffer * 64 | tails of P 384..511
+  const uint32_t tmem_o0 = tmem_base + 256;
+  const uint32_t tmem_pt = tmem_base + 384;
+  volatile int* abort_ptr = &abort_flag;
+  auto give_up = [&](int site) {
+    if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | site); *abort_ptr = 1; }
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int t = 0;                                     // key tiles loaded so far, over all items
+      bool ok = true;
+      for (int ii = 0; ok; ++ii) {
+        const int w = nth_item(ii);
+        if (w < 0) break;
+        const Item it = item_of(w);
+        // the Q tile is free once every Q K^T of the previous item has been executed
+        if (!mbar_wait(q_empty, (ii & 1) ^ 1, abort_ptr)) { give_up(0x13); break; }
+        // an operand buffer: the tile's two slabs, then the two slabs of its tails
+        auto load4 = [&](uint32_t dst, const CUtensorMap* heads, const CUtensorMap* tails, uint32_t bar, int first_row) {
+          mbar_expect_tx(bar, kOpBytes);
+          tma_load_3d(dst, heads, bar, 0, first_row, it.h);
+          tma_load_3d(dst + kSlab, heads, bar, 32, first_row, it.h);
+          tma_load_3d(dst + kTileBytes, tails, bar, 0, first_row, it.h);
+          tma_load_3d(dst + kTileBytes + kSlab, tails, bar, 32, first_row, it.h);
+        };
+        load4(q_smem, &map_q, &map_qt, q_full, it.row0 + it.q0);
+        for (int j = 0; j < it.n_kv; ++j, ++t) {
+          const uint32_t ph = t & 1;                   // one buffer: the phase alternates with every tile
+          if (!mbar_wait(k_empty, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
+          load4(k_smem, &map_k, &map_kt, k_full, it.row0 + j * kRows);
+          if (!mbar_wait(v_empty, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
+          load4(v_smem, &map_v, &map_vt, v_full, it.row0 + j * kRows);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      // Tiles are numbered over all items (t): ring slot, S buffer and O_part buffer are t & 1, phases (t >> 1) & 1.
+      auto issue_qk = [&](int t) {
+        const int s = t & 1;
+        if (!mbar_wait(k_full, t & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t kb = k_smem;
+        // 32 bytes of the head dimension per instruction (8 float32); heads x heads, heads x tails, tails x heads
+#pragma unroll
+        for (int pass = 0; pass < 3; ++pass) {
+          const uint32_t qa = q_smem + (pass == 2 ? kTileBytes : 0), ka = kb + (pass == 1 ? kTileBytes : 0);
+#pragma unroll
+          for (int kd = 0; kd < kTileSlabs * 4; ++kd) {
+            const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
+            umma(tmem_base + (uint32_t)s * 128, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024), p.idesc_qk,
+                 (pass | kd) != 0 ? 1u : 0u, false);
+          }
+        }
+        umma_commit(sfull0 + 8 * s);
+        umma_commit(k_empty);
+      };
+      // P V of tile t: the 128 keys of both threads of a row pair into the O_part buffer (t & 1), as two
+      // runs of MMAs (a group's P occupies the first columns of its 64-column share of S).  In-order
+      // execution of the tensor pipe keeps S[s] intact until these reads of P are done (the next Q K^T
+      // into S[s] is issued later), and the buffer (t & 1) was folded by the softmax threads before
+      // they published P of tile t.
+      auto issue_pv = [&](int t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(v_full, t & 1, abort_ptr)) { give_up(0x23); ok = false; return; }
+        const uint32_t vb = v_smem;
+        const uint32_t o_addr = tmem_o0 + (uint32_t)s * 64;
+        for (int g = 0; g < 2; ++g) {
+          if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // P x V, P x tails of V, tails of P x V
+#pragma unroll
+          for (int pass = 0; pass < 3; ++pass) {
+            const uint32_t pa = pass == 2 ? tmem_pt : tmem_base + (uint32_t)s * 128;
+            const uint32_t va = vb + (pass == 1 ? kTileBytes : 0);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ts(o_addr, pa + (uint32_t)(g * 64 + kk * 8), make_desc(va + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1),
+                      p.idesc_pv, (g | kk | pass) != 0 ? 1u : 0u, false);
+          }
+        }
+        umma_commit(ofull0 + 8 * s);
+        umma_commit(v_empty);
+      };
+      // An item's first scores: its Q must have landed; once its last scores are issued, the Q tile is handed back.
+      auto first_qk = [&](int ii, int t, int n_kv) {
+        if (!mbar_wait(q_full, ii & 1, abort_ptr)) { give_up(0x21); ok = false; return; }
+        issue_qk(t);
+        if (ok && n_kv == 1) umma_commit(q_empty);
+      };
+      int t = 0;
+      for (int ii = 0; ok; ++ii) {
+        const int w = nth_item(ii);
+        if (w < 0) break;
+        const int n_kv = item_of(w).n_kv;
+        // (The next item's first scores are NOT issued ahead of this item's last P V: the softmax warps
+        // wait for that P V to finish the item, and have the merge and the stores to do before they
+        // need the next scores.)
+        first_qk(ii, t, n_kv);
+        for (int j = 0; j < n_kv && ok; ++j) {
+#ifdef KB200_TRACE
+          ATTN_MMA_STAMP(tm); ++tm;
+#endif
+          if (j + 1 < n_kv) {
+            issue_qk(t + j + 1);                     // the next scores are computed while the softmax warps work on tile j
+            if (ok && j + 2 == n_kv) umma_commit(q_empty);
+          }
+#ifdef KB200_TRACE
+          ATTN_MMA_STAMP(tm); ++tm;
+#endif
+          if (ok) issue_pv(t + j);
+#ifdef KB200_TRACE
+          ATTN_MMA_STAMP(tm); ++tm;
+#endif
+        }
+        t += n_kv;
+      }
+    }
+  } else {
+    // ---------------- softmax / output (warps 2..9) ----------------
+    // Two threads share a query row (TMEM lane): thread g of the pair takes keys g*64 .. g*64+63 of every
+    // tile.  They keep ONE online-softmax state per row: each tile they exchange the maxima of their
+    // halves through shared memory (a 64-thread barrier per lane quadrant), so both use the same
+    // reference point, their probabilities go into one P V of 128 keys and one O_part, and thread g
+    // folds, normalises and stores head dims g*32 .. g*32+31.  Per item only the two partial row sums
+    // cross between them.
+    const int quad = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;              // row of the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const int c0 = group * 64;
+    // behind the rings: [2 tile parities][2 groups][128 rows] maxima, [2 item parities][2][128] row sums,
+    // then a staging slot per warp for the output rows (32 x 32 float32 + their bf16 copy)
+    float* const xmax = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
+    float* const xsum = xmax + 4 * kRows;
+    const int pair_barrier = 2 + quad;              // hardware barriers 2..5, 64 threads each
+    // The pair's barrier also carries the abort flag (an OR over what the 64 threads read before they
+    // arrived), so that both threads of a row take the same decision and neither waits for the other.
+    auto pair_sync_aborted = [&]() {
+      uint32_t any;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %2, 0;\n\tbar.red.or.pred q, %1, 64, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(any)
+          : "r"(pair_barrier), "r"((uint32_t)*abort_ptr)
+          : "memory");
+      return any != 0;
+    };
+    bool ok = true;
+    int t0 = 0;                                      // tiles of the items before this one
+    for (int ii = 0; ok; ++ii) {
+      const int w = nth_item(ii);
+      if (w < 0) break;
+      const Item it = item_of(w);
+      const int n_kv = it.n_kv;
+      float o[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+      float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
+      // running output <- running output * alpha + this thread's 32 dims of the O_part of tile t
+      auto fold = [&](int t, float alpha) {
+        bool got = mbar_wait(ofull0 + 8 * (t & 1), (t >> 1) & 1, abort_ptr);
+        if (!got) give_up(0x32);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float v[32];
+        tmem_ld32(tmem_o0 + lane_addr + (uint32_t)((t & 1) * 64 + group * 32), v);
+        const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 r2 = ffma2(make_float2(o[i], o[i + 1]), alpha2, make_float2(v[i], v[i + 1]));
+          o[i] = r2.x;
+          o[i + 1] = r2.y;
+        }
+      };
+      // Every thread of a pair passes the same barriers: a wait that ran out raises the CTA's flag and the
+      // thread carries on to the next barrier, after which both see the flag and leave together.
+      for (int j = 0; j < n_kv; ++j) {
+        const int t = t0 + j;
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(sfull0 + 8 * s, ph, abort_ptr)) give_up(0x31);
+        ATTN_STAMP(0, j);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
+        const bool diagonal = j == it.qt;
+        float va[32], vb[32];
+        tmem_ld32x2(s_addr, s_addr + 32, va, vb);       // both halves in flight, one wait
+        // the scale is positive (checked when the chain was matched), so the maximum commutes with it
+        float mx = -CUDART_INF_F;
+        if (diagonal) {
+          mx = row_max32<true>(va, mx, c0, row);
+          mx = row_max32<true>(vb, mx, c0 + 32, row);
+        } else {
+          mx = row_max32<false>(va, mx, 0, 0);
+          mx = row_max32<false>(vb, mx, 0, 0);
+        }
+        xmax[(s * 2 + group) * kRows + row] = mx;
+        if (pair_sync_aborted()) { ok = false; break; }
+        mx = fmaxf(mx, xmax[(s * 2 + (group ^ 1)) * kRows + row]);
+        // key 0 is visible to every row, so the maximum over a whole tile is finite
+        const float m_new = fmaxf(m_run, mx * p.scale_log2);
+        const float alpha = ex2(m_run - m_new);       // 0 while m_run = -inf
+        float sum;
+        if (diagonal) {
+          sum = probabilities32<true>(va, p.scale_log2, m_new, c0, row);
+          sum += probabilities32<true>(vb, p.scale_log2, m_new, c0 + 32, row);
+        } else {
+          sum = probabilities32<false>(va, p.scale_log2, m_new, 0, 0);
+          sum += probabilities32<false>(vb, p.scale_log2, m_new, 0, 0);
+        }
+        // Fold the PREVIOUS tile's O_part first: that it is complete also says that its P V has read the
+        // tails of P, whose single buffer is written next.
+        if (j > 0) fold(t - 1, alpha_prev);
+        ATTN_STAMP(3, j);
+        {
+          const uint32_t pt_addr = tmem_pt + lane_addr + (uint32_t)c0;
+          float ta[32];
+          tmem_st32(s_addr, va);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ta[i] = va[i] - __uint_as_float(__float_as_uint(va[i]) & 0xFFFFE000u);
+          tmem_st32(pt_addr, ta);
+          tmem_st32(s_addr + 32, vb);
+          float tb[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tb[i] = vb[i] - __uint_as_float(__float_as_uint(vb[i]) & 0xFFFFE000u);
+          tmem_st32(pt_addr + 32, tb);
+        }
+        tmem_st_wait();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(pfull0 + 8 * (group * 2 + s));
+        ATTN_STAMP(1, j);
+        alpha_prev = alpha;
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
+      }
+      if (ok) fold(t0 + n_kv - 1, alpha_prev);
+      t0 += n_kv;
+      ATTN_STAMP(2, 3 * ii);
+      // ---- the row sum is the two threads' partial sums; thread g normalises and stores dims g*32 .. g*32+31 ----
+      xsum[((ii & 1) * 2 + group) * kRows + row] = l_run;
+      if (pair_sync_aborted()) ok = false;
+      ATTN_STAMP(2, 3 * ii + 1);
+      if (ok) {
+        const float inv = 1.0f / (l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= inv;
+        // a lane holds 32 dims of ONE row: 128 contiguous bytes
+        float* const dst = p.out + (int64_t)(it.row0 + it.q0 + row) * p.out_row_stride + it.h * kHeadDim + group * 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+      }
+      ATTN_STAMP(2, 3 * ii + 2);
+    }
+  }
+
+  // ---------------- common exit ----------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+#ifdef KB200_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    printf("ATTN block0 globaltimer start %lld end %lld (ns) dur %lld | exit cycles %lld n_kv %d\n", marks[0], (long long)g,
+           (long long)g - marks[0], clock64() - marks[1], item_of(blockIdx.x).n_kv);
+    printf("softmax thread per item (tiles done, states exchanged, rows stored):");
+    for (int j = 0; j < 15; ++j) printf(" %lld", trace[2][j] - marks[1]);
+    printf("\n");
+    printf("MMA thread (per tile: loop top, after Q K^T of the next tile, after P V):");
+    for (int j = 0; j < 48; ++j) printf(" %lld", mma_trace[j] - marks[1]);
+    printf("\n");
+    for (int j = 0; j < item_of(blockIdx.x).n_kv && j < 16; ++j)
+      printf("kv %2d  s_ready %7lld p_stored %7lld folded %7lld\n", j, trace[0][j] - marks[1], trace[1][j] - marks[1],
+             trace[3][j] - marks[1]);
+  }
+#endif
+  if (abort_flag && threadIdx.x == 0) {
+    for (uint32_t i = 0; i < 4096u; ++i)
+      if ((mbar_try_wait(k_full, 0) || mbar_try_wait(k_full, 1)) && (mbar_try_wait(v_full, 0) || mbar_try_wait(v_full, 1))) break;
+  }
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 struct Range {
   const float* lo;
   const float* hi;
@@ -893,11 +1315,43 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   // Q, K, V as [head, row, 64] views with rows b * T + t: a batch of sequences is more rows of the same map
   AttnState* st = new AttnState();
   st->exact = c.exact;
-  if (!c.exact && (!encode_map(&st->map_q, false, c.q, hd, B * T, H, rs, hd, 32, kRows, false) ||
-                   !encode_map(&st->map_k, false, c.k, hd, B * T, H, rs, hd, 32, kRows, false) ||
-                   !encode_map(&st->map_v, false, c.v, hd, B * T, H, rs, hd, 32, kRows, true))) {
+  // FP32 mode: the tensor-core kernel when its work items (128 queries each) fill at least half the
+  // SMs, the CUDA-core kernel (64 queries per CTA, long prefixes split) for the short sequences below
+  // that; KILN_GPU_FP32_ATTENTION=fma / tensor forces one of them.
+  if (c.exact) {
+    st->exact_tc = B * H * (T / kRows) * 2 >= plan.sm_count;
+    if (const char* e = getenv("KILN_GPU_FP32_ATTENTION")) {
+      if (!strcmp(e, "fma")) st->exact_tc = false;
+      if (!strcmp(e, "tensor")) st->exact_tc = true;
+    }
+  }
+  if ((!c.exact || st->exact_tc) && (!encode_map(&st->map_q, false, c.q, hd, B * T, H, rs, hd, 32, kRows, false) ||
+                                     !encode_map(&st->map_k, false, c.k, hd, B * T, H, rs, hd, 32, kRows, false) ||
+                                     !encode_map(&st->map_v, false, c.v, hd, B * T, H, rs, hd, 32, kRows, true))) {
     delete st;
     return false;
+  }
+  if (st->exact_tc) {
+    // the tails of everything the three views cover, in a buffer of the same shape
+    const float* lo = c.q < c.k ? c.q : c.k;
+    if (c.v < lo) lo = c.v;
+    const float* last = c.q > c.k ? c.q : c.k;
+    if (c.v > last) last = c.v;
+    const int64_t span = (last - lo) + (B * T - 1) * rs + H * hd;
+    st->span_lo = lo;
+    st->span_n4 = span / 4;
+    const bool ok = span % 4 == 0 && cudaMalloc(&st->tails, (size_t)span * sizeof(float)) == cudaSuccess &&
+                    encode_map(&st->map_qt, false, st->tails + (c.q - lo), hd, B * T, H, rs, hd, 32, kRows, false) &&
+                    encode_map(&st->map_kt, false, st->tails + (c.k - lo), hd, B * T, H, rs, hd, 32, kRows, false) &&
+                    encode_map(&st->map_vt, false, st->tails + (c.v - lo), hd, B * T, H, rs, hd, 32, kRows, true) &&
+                    cudaFuncSetAttribute(attention_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExactSmemBytes) ==
+                        cudaSuccess;
+    if (!ok) {
+      cudaGetLastError();
+      if (st->tails) cudaFree(st->tails);
+      delete st;
+      return false;
+    }
   }
   if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
       cudaFuncSetAttribute(attention_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmemBytes) != cudaSuccess ||
@@ -928,6 +1382,7 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
     st->out_elems = B * T * H * hd;
     if (cudaMalloc(&st->staged_out, (size_t)st->out_elems * sizeof(float)) != cudaSuccess) {
       cudaGetLastError();
+      if (st->tails) cudaFree(st->tails);
       delete st;
       return false;
     }
@@ -942,13 +1397,14 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   // the output rows leave by bulk tensor stores: [B * T, H * 64], boxes of 32 rows x 32 dims
   if (!aligned16(p.out) || !encode_map_store(&st->map_out, false, p.out, H * hd, B * T, 1, p.out_row_stride, 0)) {
     if (st->staged_out) cudaFree(st->staged_out);
+    if (st->tails) cudaFree(st->tails);
     delete st;
     return false;
   }
   st->map_out16 = st->map_out;
   const int64_t items = B * H * p.q_tiles;
   st->grid = dim3((unsigned)(items < plan.sm_count ? items : plan.sm_count), 1, 1);     // persistent: at most one CTA per SM
-  if (c.exact) {
+  if (c.exact && !st->exact_tc) {
     AttnF32Params& f = st->f32;
     f.q = c.q; f.k = c.k; f.v = c.v;
     f.row_stride = rs;
@@ -982,7 +1438,7 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   PlanKernel& holder = plan.kernels[c.first];
   holder.attn = st;
   holder.impl = IMPL_ATTN_FUSED;
-  holder.launches = aliased ? 2 : 1;
+  holder.launches = (aliased ? 2 : 1) + (st->exact_tc ? 1 : 0);
   for (int j = 1; j < c.count; ++j) {
     plan.kernels[c.first + j].impl = IMPL_FUSED_AWAY;
     plan.kernels[c.first + j].launches = 0;
@@ -1195,7 +1651,13 @@ bool attention_wants_bf16(const PlanKernel& k) { return k.attn && static_cast<co
 
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
   const AttnState* st = static_cast<const AttnState*>(k.attn);
-  if (st->exact)
+  if (st->exact_tc) {
+    const int64_t blocks = (st->span_n4 + 255) / 256;
+    KB200_CUDA(launch_kernel(plan.pdl, tails_kernel, dim3((unsigned)(blocks < 1184 ? blocks : 1184)), dim3(256), 0, s,
+                             reinterpret_cast<const float4*>(st->span_lo), reinterpret_cast<float4*>(st->tails), st->span_n4));
+    KB200_CUDA(launch_kernel(plan.pdl, attention_exact_kernel, st->grid, dim3(kAttnThreads), kExactSmemBytes, s, st->map_q, st->map_k,
+                             st->map_v, st->map_qt, st->map_kt, st->map_vt, st->params));
+  } else if (st->exact)
     KB200_CUDA(launch_kernel(plan.pdl, attention_fp32_kernel, st->grid, dim3(kFThreads), kFSmemBytes, s, st->f32));
   else if (st->bf16)
     KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q, st->map_k,
@@ -1298,7 +1760,7 @@ void attention_elide_copy(Plan& plan, size_t first) {
   }
   for (auto& [k, slot] : redirect) k->ops[slot].ptr = st->staged_out;
   st->final_out = nullptr;
-  holder.launches = 1;
+  holder.launches = 1 + (st->exact_tc ? 1 : 0);
 }
 
 bool attention_reads_mirror(const PlanKernel& k) { return k.attn && static_cast<const AttnState*>(k.attn)->bf16; }
@@ -1325,6 +1787,7 @@ void attention_destroy(PlanKernel& k) {
     AttnState* st = static_cast<AttnState*>(k.attn);
     if (st->staged_out) cudaFree(st->staged_out);
     if (st->f32_scratch) cudaFree(st->f32_scratch);
+    if (st->tails) cudaFree(st->tails);
     delete st;
   }
   k.attn = nullptr;
