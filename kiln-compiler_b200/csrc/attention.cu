@@ -5,10 +5,13 @@
 // with the scale + mask epilogue that writes [H, T, T] scores, a softmax row kernel over them, a
 // batched matmul with V, and a copy that merges the heads.  The reference lists "no fused attention"
 // as a limitation (README.md:185): the scores cross HBM twice.  When the plan contains exactly that
-// chain, the mask is the causal one, and a reduced-precision matmul mode is selected, this kernel
-// replaces the five launches: it reads Q, K and V as strided views of the QKV projection's output
-// and writes the merged-heads buffer, the only value of the chain that is live afterwards.  The
-// plan itself (kernel list, arena offsets) is untouched; the score buffers are simply never written.
+// chain and the mask is the causal one, a fused kernel replaces the five launches: it reads Q, K and
+// V as strided views of the QKV projection's output and writes the merged-heads buffer, the only
+// value of the chain that is live afterwards.  The plan itself (kernel list, arena offsets) is
+// untouched; the score buffers are simply never written.  Three kernels: `attention_kernel` for the
+// TF32 and BF16 matmul modes (described next), `attention_exact_kernel` for FP32 mode (the same
+// structure with three TF32 MMAs per product) and `attention_fp32_kernel` for short sequences in
+// FP32 mode (CUDA cores).
 //
 // Persistent CTAs (one per SM) walk the (sequence, head, 128-query tile) work items, heaviest first, in
 // steps of the grid size: barrier set-up, the TMEM allocation and the latency of an item's first
@@ -1265,6 +1268,7 @@ struct AttnChain {
   std::vector<PlanKernel*> matmuls;   // tensor-core state to drop
   bool bf16 = false;
   bool exact = false;                 // the chain's matmuls are in FP32 mode
+  bool ieee = false;                  // ... and were asked to behave like FMA matmuls on non-finite operands (config bit 1024)
 };
 
 // Shared tail of the two matchers: the intermediates must be dead afterwards, the mask causal; then
@@ -1315,11 +1319,13 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   // Q, K, V as [head, row, 64] views with rows b * T + t: a batch of sequences is more rows of the same map
   AttnState* st = new AttnState();
   st->exact = c.exact;
-  // FP32 mode: the tensor-core kernel when its work items (128 queries each) fill at least half the
-  // SMs, the CUDA-core kernel (64 queries per CTA, long prefixes split) for the short sequences below
-  // that; KILN_GPU_FP32_ATTENTION=fma / tensor forces one of them.
+  // FP32 mode: the tensor-core kernel when its work items (128 queries each) fill at least a quarter
+  // of the SMs, the CUDA-core kernel (64 queries per CTA, long prefixes split) for the short sequences
+  // below that (one 128-token sequence: 8.6 against 10.4 us; 512 tokens: 22.4 against 20.9);
+  // KILN_GPU_FP32_ATTENTION=fma / tensor forces one of them.
   if (c.exact) {
-    st->exact_tc = B * H * (T / kRows) * 2 >= plan.sm_count;
+    // (split operands turn an infinite element into a NaN tail: a plan that asked for IEEE behaviour keeps the FMA kernel)
+    st->exact_tc = !c.ieee && B * H * (T / kRows) * 4 >= plan.sm_count;
     if (const char* e = getenv("KILN_GPU_FP32_ATTENTION")) {
       if (!strcmp(e, "fma")) st->exact_tc = false;
       if (!strcmp(e, "tensor")) st->exact_tc = true;
@@ -1523,6 +1529,7 @@ bool try_fuse_single(Plan& plan, size_t i) {
   c.matmuls = {&k3, &k5};
   c.bf16 = k3.desc.precision == KB200_PREC_BF16;
   c.exact = k3.desc.precision == KB200_PREC_FP32;
+  c.ieee = (k3.desc.cfg[6] & 1024) != 0;
   return finish_fusion(plan, c);
 }
 
@@ -1632,6 +1639,7 @@ bool try_fuse_batched(Plan& plan, size_t i) {
   c.matmuls = {&mm1, &mm2};
   c.bf16 = mm1.desc.precision == KB200_PREC_BF16;
   c.exact = mm1.desc.precision == KB200_PREC_FP32;
+  c.ieee = (mm1.desc.cfg[6] & 1024) != 0;
   return finish_fusion(plan, c);
 }
 

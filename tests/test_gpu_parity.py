@@ -113,6 +113,25 @@ def test_fused_attention_equals_the_five_planned_kernels(tokens, precision, monk
     assert scale_relative_error(fused[0], plain[0]) <= REL_TOL[precision]
 
 
+@pytest.mark.parametrize("kernel", ["fma", "tensor"])
+@pytest.mark.parametrize("tokens", [128, 1024])
+def test_both_fp32_attention_kernels_match_float64(tokens, kernel, monkeypatch):
+    """FP32 mode picks the CUDA-core kernel for short sequences and the tensor-core kernel (three TF32
+    MMAs per product) for long ones; each is forced here at both lengths."""
+    from gpu_helpers import run_case
+
+    monkeypatch.setenv("KILN_GPU_FP32_ATTENTION", kernel)
+    case = f"gpt2_block_t{tokens}"
+    exe, got, (plan, inputs, consts, _) = run_case(case, "fp32")
+    assert "attention_fused" in exe.impls
+    # the tensor-core kernel has a launch in front that writes the operands' tails
+    monkeypatch.setenv("KILN_GPU_FP32_ATTENTION", "fma" if kernel == "tensor" else "tensor")
+    other, _, _ = run_case(case, "fp32")
+    assert abs(exe.device_launches - other.device_launches) == 1
+    (exact,) = run_plan(plan, inputs, consts, dtype=np.float64)
+    assert scale_relative_error(got[0], exact) <= REL_TOL["fp32"]
+
+
 def test_fp32_mode_fuses_attention_too(monkeypatch):
     """FP32 mode (the reference's allow_tf32=False) takes the CUDA-core fused kernel: the scores are never written."""
     from gpu_helpers import build_executable
