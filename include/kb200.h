@@ -16,7 +16,8 @@
  * plan's status word, and kb200_plan_bind allocates the library-owned scratch
  * (in BF16 mode a bf16 mirror of the arena and packed bf16 copies of constant
  * matmul operands; a staging buffer for a fused attention whose output aliases
- * its inputs), converts the constants (cudaDeviceSynchronize) and reads the
+ * its inputs; in FP32 mode the fused attention's scratch: the operands' tails or
+ * the split tiles' partial results), converts the constants (cudaDeviceSynchronize) and reads the
  * attention mask back once (a blocking copy).  kb200_plan_launch and
  * kb200_kernel_launch neither allocate nor synchronise and are therefore
  * capturable into a CUDA graph; kb200_plan_status is a blocking 4-byte copy.
@@ -182,9 +183,11 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
 /* Plan options, set between kb200_plan_create and kb200_plan_bind.
  * KB200_OPT_FUSE_ATTENTION (default 1): when the plan contains the reference's five-kernel
  * attention chain (K^T copy, QK^T * scale + causal mask, softmax, PV, head merge; see
- * tests/models/transformer.py:16-25 of the reference) and the matmul precision is not FP32, run
- * it as one fused kernel.  The kernel list and arena offsets stay the reference's; the score
- * buffers are then never written.  0 keeps one launch per planned kernel.
+ * tests/models/transformer.py:16-25 of the reference), or the seven-kernel chain of a batch of
+ * sequences, run it as one fused kernel (in FP32 precision: with float32 products, behind a small
+ * launch that prepares the operands' tails when the tensor cores are used).  The kernel list and
+ * arena offsets stay the reference's; the score buffers are then never written.  0 keeps one launch
+ * per planned kernel.
  * KB200_OPT_DEPENDENT_LAUNCH (default 1): kernels are enqueued with programmatic stream
  * serialization, so that a kernel's start-up overlaps the tail of the one before it (each kernel
  * waits for its predecessor before it touches global memory).  0 = plain stream order.

@@ -164,6 +164,10 @@ class GPUExecutable:
         library_bytes = 0
         if program.precision == "bf16":
             library_bytes = arena_bytes // 2 + 256 + const_bytes // 2 + (io_bytes + arena_bytes) // 2
+        elif program.precision == "fp32":
+            # the fused attention's scratch: the tails of Q, K and V (a copy of part of the arena) or the
+            # split tiles' partial results (smaller than the merged heads)
+            library_bytes = arena_bytes
         check_memory(self.device, arena_bytes + const_bytes + io_bytes + out_bytes + library_bytes,
                      f"the arena ({arena_bytes / 2**20:.1f} MiB), weights ({const_bytes / 2**20:.1f} MiB) "
                      f"and outputs")
