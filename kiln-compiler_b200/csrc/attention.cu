@@ -32,8 +32,10 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <utility>
 #include <vector>
 
 #include "device_math.cuh"
@@ -69,7 +71,12 @@ struct AttnParams {
   uint32_t idesc_qk, idesc_pv;
   int kernel_index;
   int* status;
+  int split_from;            // query tiles from this one on are shared by two CTAs (q_tiles: none)
+  float* partial;            // [split tile][2 halves][128 x 64 unnormalised output | 128 maxima | 128 sums]
+  int* arrivals;             // [split tile][4 lane quadrants], zero between launches
+  const unsigned short* order;   // with split tiles: (query tile << 1 | half) of the q_tiles + split tiles entries, heaviest first
 };
+constexpr int kPartialFloats = kRows * kHeadDim + 2 * kRows;
 
 constexpr int kFTile = 64;                 // queries per CTA and keys per tile
 constexpr int kFPitch = 68;                // floats per shared-memory row of Q, K and P (16-byte aligned, rows 4 banks apart)
@@ -120,6 +127,7 @@ struct AttnState {
   bool exact_tc = false;           // ... on the tensor cores (enough work items to fill the GPU), else the CUDA-core kernel
   AttnF32Params f32;
   void* f32_scratch = nullptr;     // CUDA-core kernel: the split tiles' partial results and arrival counters
+  void* split_scratch = nullptr;   // tensor-core kernels: the same for their split tiles
   CUtensorMap map_qt, map_kt, map_vt;   // tensor-core FP32 kernel: Q, K, V views of the tails buffer
   float* tails = nullptr;          // tails (x minus its 19 leading bits) of the span of the QKV buffer the views cover
   const float* span_lo = nullptr;
@@ -413,6 +421,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __shared__ __align__(8) uint64_t bars[20];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int arrived[4];                  // split items: was this lane quadrant's half the second to arrive?
 
 #ifdef KB200_TRACE
   __shared__ long long trace[4][16];
@@ -444,7 +453,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t q_empty = smem_u32(&bars[19]);
 
   // work item w -> (head, sequence, query tile): heaviest (longest causal prefix) tiles first, of every sequence
-  const int n_items = p.B * p.H * p.q_tiles;
+  // Query tiles from p.split_from on (the longest causal prefixes; none when split_from = q_tiles) are
+  // TWO items, one per half of their key tiles: each leaves its unnormalised rows and softmax state in
+  // a workspace, and the one that arrives second (a counter per tile and lane quadrant) merges them.
+  const int n_split = p.q_tiles - p.split_from;
+  const int n_items = p.B * p.H * (p.q_tiles + n_split);
   // This CTA's r-th item (-1: none).  Rounds alternate direction over the CTAs, so that the CTA with the
   // heaviest item of one round takes the lightest of the next (24 key tiles at most per CTA instead of
   // 27 for 8 x 12 x 8 items on 148 CTAs).
@@ -452,14 +465,26 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int w = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
     return w < n_items ? w : -1;
   };
-  struct Item { int h, q0, n_kv, row0, qt; };
+  struct Item { int h, q0, n_kv, row0, qt, j0, half, slot; bool split; };
   auto item_of = [&](int w) {
     Item it;
     it.h = w % p.H;
     const int seq = (w / p.H) % p.B;
-    it.qt = p.q_tiles - 1 - w / (p.H * p.B);
+    const int v = w / (p.H * p.B);
+    if (n_split == 0) {                                // heaviest (longest causal prefix) first
+      it.qt = p.q_tiles - 1 - v;
+      it.half = 0;
+    } else {                                           // whole tiles and halves in descending order of their key tiles (host table)
+      const unsigned e = __ldg(p.order + v);
+      it.qt = (int)(e >> 1);
+      it.half = (int)(e & 1);
+    }
+    it.split = it.qt >= p.split_from;
     it.q0 = it.qt * kRows;
-    it.n_kv = it.qt + 1;                               // causal: key tiles 0..qt
+    const int n = it.qt + 1;                           // causal: key tiles 0..qt
+    it.j0 = it.split && it.half ? n >> 1 : 0;          // this item's key tiles: j0 .. j0 + n_kv - 1
+    it.n_kv = (it.split && !it.half ? n >> 1 : n) - it.j0;
+    it.slot = it.split ? (seq * p.H + it.h) * n_split + (it.qt - p.split_from) : 0;
     it.row0 = seq * p.T;                               // this sequence's first row in Q, K, V and the output
     return it;
   };
@@ -526,12 +551,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           const uint32_t ph = (t >> 1) & 1;
           if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
           mbar_expect_tx(k_full + 8 * s, kTileBytes);
-          tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, it.row0 + j * kRows, it.h);
-          if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, it.row0 + j * kRows, it.h);
+          tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, it.row0 + (it.j0 + j) * kRows, it.h);
+          if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, it.row0 + (it.j0 + j) * kRows, it.h);
           if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
           mbar_expect_tx(v_full + 8 * s, kTileBytes);
-          tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, it.row0 + j * kRows, it.h);
-          if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, it.row0 + j * kRows, it.h);
+          tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, it.row0 + (it.j0 + j) * kRows, it.h);
+          if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, it.row0 + (it.j0 + j) * kRows, it.h);
         }
       }
     }
@@ -686,7 +711,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         ATTN_STAMP(0, j);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
-        const bool diagonal = j == it.qt;
+        const bool diagonal = it.j0 + j == it.qt;
         float va[32], vb[32];
         tmem_ld32x2(s_addr, s_addr + 32, va, vb);       // both halves in flight, one wait
         // the scale is positive (checked when the chain was matched), so the maximum commutes with it
@@ -746,8 +771,52 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       xsum[((ii & 1) * 2 + group) * kRows + row] = l_run;
       if (pair_sync_aborted()) ok = false;
       ATTN_STAMP(2, 3 * ii + 1);
-      if (ok) {
-        const float inv = __fdividef(1.0f, l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row]);
+      // ---- a split item: leave this half's rows and state in the workspace; whoever arrives second merges.
+      // Nobody waits for the other half.  The arrival is counted per lane quadrant (its 64 threads have a
+      // barrier of their own, the one that also carries the abort flag), so no CTA-wide barrier is needed.
+      bool writes = ok;
+      float l_tot = ok ? l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row] : 1.0f;
+      if (ok && it.split) {
+        float* const mine = p.partial + ((size_t)it.slot * 2 + it.half) * kPartialFloats;
+        const float* const other = p.partial + ((size_t)it.slot * 2 + (it.half ^ 1)) * kPartialFloats;
+        float4* const mine4 = reinterpret_cast<float4*>(mine + row * kHeadDim + group * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) __stcg(mine4 + i, make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
+        if (group == 0) {
+          __stcg(mine + kRows * kHeadDim + row, m_run);
+          __stcg(mine + kRows * kHeadDim + kRows + row, l_tot);
+        }
+        __threadfence();
+        if (pair_sync_aborted()) ok = false;          // the quadrant's 64 threads have written and fenced
+        if (ok) {
+          if (lane == 0 && group == 0) {
+            arrived[quad] = atomicAdd(p.arrivals + it.slot * 4 + quad, 1);
+            __threadfence();
+          }
+          if (pair_sync_aborted()) ok = false;
+        }
+        if (ok) {
+          writes = arrived[quad] != 0;
+          if (writes) {
+            if (lane == 0 && group == 0) p.arrivals[it.slot * 4 + quad] = 0;      // for the next launch
+            const float m2 = __ldcg(other + kRows * kHeadDim + row), l2 = __ldcg(other + kRows * kHeadDim + kRows + row);
+            const float m = fmaxf(m_run, m2);
+            const float a1 = ex2(m_run - m), a2 = ex2(m2 - m);
+            l_tot = l_tot * a1 + l2 * a2;             // symmetric in the halves: the same bits whoever merges
+            const float4* const other4 = reinterpret_cast<const float4*>(other + row * kHeadDim + group * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 o2 = __ldcg(other4 + i);
+              o[4 * i] = o[4 * i] * a1 + o2.x * a2;
+              o[4 * i + 1] = o[4 * i + 1] * a1 + o2.y * a2;
+              o[4 * i + 2] = o[4 * i + 2] * a1 + o2.z * a2;
+              o[4 * i + 3] = o[4 * i + 3] * a1 + o2.w * a2;
+            }
+          }
+        }
+      }
+      if (ok && writes) {
+        const float inv = __fdividef(1.0f, l_tot);
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] *= inv;
         // A lane holds 32 dims of ONE row: the rows go through the warp's staging slot (128-byte rows, the
@@ -827,6 +896,7 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ __align__(8) uint64_t bars[20];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int arrived[4];                  // split items: was this lane quadrant's half the second to arrive?
 
 #ifdef KB200_TRACE
   __shared__ long long trace[4][16];
@@ -853,7 +923,11 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t q_empty = smem_u32(&bars[19]);
 
   // work item w -> (head, sequence, query tile): heaviest (longest causal prefix) tiles first, of every sequence
-  const int n_items = p.B * p.H * p.q_tiles;
+  // Query tiles from p.split_from on (the longest causal prefixes; none when split_from = q_tiles) are
+  // TWO items, one per half of their key tiles: each leaves its unnormalised rows and softmax state in
+  // a workspace, and the one that arrives second (a counter per tile and lane quadrant) merges them.
+  const int n_split = p.q_tiles - p.split_from;
+  const int n_items = p.B * p.H * (p.q_tiles + n_split);
   // This CTA's r-th item (-1: none).  Rounds alternate direction over the CTAs, so that the CTA with the
   // heaviest item of one round takes the lightest of the next (24 key tiles at most per CTA instead of
   // 27 for 8 x 12 x 8 items on 148 CTAs).
@@ -861,14 +935,26 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int w = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
     return w < n_items ? w : -1;
   };
-  struct Item { int h, q0, n_kv, row0, qt; };
+  struct Item { int h, q0, n_kv, row0, qt, j0, half, slot; bool split; };
   auto item_of = [&](int w) {
     Item it;
     it.h = w % p.H;
     const int seq = (w / p.H) % p.B;
-    it.qt = p.q_tiles - 1 - w / (p.H * p.B);
+    const int v = w / (p.H * p.B);
+    if (n_split == 0) {                                // heaviest (longest causal prefix) first
+      it.qt = p.q_tiles - 1 - v;
+      it.half = 0;
+    } else {                                           // whole tiles and halves in descending order of their key tiles (host table)
+      const unsigned e = __ldg(p.order + v);
+      it.qt = (int)(e >> 1);
+      it.half = (int)(e & 1);
+    }
+    it.split = it.qt >= p.split_from;
     it.q0 = it.qt * kRows;
-    it.n_kv = it.qt + 1;                               // causal: key tiles 0..qt
+    const int n = it.qt + 1;                           // causal: key tiles 0..qt
+    it.j0 = it.split && it.half ? n >> 1 : 0;          // this item's key tiles: j0 .. j0 + n_kv - 1
+    it.n_kv = (it.split && !it.half ? n >> 1 : n) - it.j0;
+    it.slot = it.split ? (seq * p.H + it.h) * n_split + (it.qt - p.split_from) : 0;
     it.row0 = seq * p.T;                               // this sequence's first row in Q, K, V and the output
     return it;
   };
@@ -941,9 +1027,9 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int j = 0; j < it.n_kv; ++j, ++t) {
           const uint32_t ph = t & 1;                   // one buffer: the phase alternates with every tile
           if (!mbar_wait(k_empty, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
-          load4(k_smem, &map_k, &map_kt, k_full, it.row0 + j * kRows);
+          load4(k_smem, &map_k, &map_kt, k_full, it.row0 + (it.j0 + j) * kRows);
           if (!mbar_wait(v_empty, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
-          load4(v_smem, &map_v, &map_vt, v_full, it.row0 + j * kRows);
+          load4(v_smem, &map_v, &map_vt, v_full, it.row0 + (it.j0 + j) * kRows);
         }
       }
     }
@@ -1098,7 +1184,7 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ATTN_STAMP(0, j);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
-        const bool diagonal = j == it.qt;
+        const bool diagonal = it.j0 + j == it.qt;
         float va[32], vb[32];
         tmem_ld32x2(s_addr, s_addr + 32, va, vb);       // both halves in flight, one wait
         // the scale is positive (checked when the chain was matched), so the maximum commutes with it
@@ -1156,8 +1242,52 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       xsum[((ii & 1) * 2 + group) * kRows + row] = l_run;
       if (pair_sync_aborted()) ok = false;
       ATTN_STAMP(2, 3 * ii + 1);
-      if (ok) {
-        const float inv = 1.0f / (l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row]);
+      // ---- a split item: leave this half's rows and state in the workspace; whoever arrives second merges.
+      // Nobody waits for the other half.  The arrival is counted per lane quadrant (its 64 threads have a
+      // barrier of their own, the one that also carries the abort flag), so no CTA-wide barrier is needed.
+      bool writes = ok;
+      float l_tot = ok ? l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row] : 1.0f;
+      if (ok && it.split) {
+        float* const mine = p.partial + ((size_t)it.slot * 2 + it.half) * kPartialFloats;
+        const float* const other = p.partial + ((size_t)it.slot * 2 + (it.half ^ 1)) * kPartialFloats;
+        float4* const mine4 = reinterpret_cast<float4*>(mine + row * kHeadDim + group * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) __stcg(mine4 + i, make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
+        if (group == 0) {
+          __stcg(mine + kRows * kHeadDim + row, m_run);
+          __stcg(mine + kRows * kHeadDim + kRows + row, l_tot);
+        }
+        __threadfence();
+        if (pair_sync_aborted()) ok = false;          // the quadrant's 64 threads have written and fenced
+        if (ok) {
+          if (lane == 0 && group == 0) {
+            arrived[quad] = atomicAdd(p.arrivals + it.slot * 4 + quad, 1);
+            __threadfence();
+          }
+          if (pair_sync_aborted()) ok = false;
+        }
+        if (ok) {
+          writes = arrived[quad] != 0;
+          if (writes) {
+            if (lane == 0 && group == 0) p.arrivals[it.slot * 4 + quad] = 0;      // for the next launch
+            const float m2 = __ldcg(other + kRows * kHeadDim + row), l2 = __ldcg(other + kRows * kHeadDim + kRows + row);
+            const float m = fmaxf(m_run, m2);
+            const float a1 = ex2(m_run - m), a2 = ex2(m2 - m);
+            l_tot = l_tot * a1 + l2 * a2;             // symmetric in the halves: the same bits whoever merges
+            const float4* const other4 = reinterpret_cast<const float4*>(other + row * kHeadDim + group * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 o2 = __ldcg(other4 + i);
+              o[4 * i] = o[4 * i] * a1 + o2.x * a2;
+              o[4 * i + 1] = o[4 * i + 1] * a1 + o2.y * a2;
+              o[4 * i + 2] = o[4 * i + 2] * a1 + o2.z * a2;
+              o[4 * i + 3] = o[4 * i + 3] * a1 + o2.w * a2;
+            }
+          }
+        }
+      }
+      if (ok && writes) {
+        const float inv = 1.0f / l_tot;
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] *= inv;
         // a lane holds 32 dims of ONE row: 128 contiguous bytes
@@ -1408,7 +1538,56 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
     return false;
   }
   st->map_out16 = st->map_out;
-  const int64_t items = B * H * p.q_tiles;
+  // When the items do not fill the persistent CTAs, the launch takes as long as its longest item: the
+  // upper half of the query tiles is then shared by two CTAs each (one sequence of 1024 tokens: 96
+  // items of 1..8 key tiles become 144 of at most 4).  A split item costs about three BF16 key tiles
+  // (partial rows out, fence, counter, the other half's rows in), so it pays only for long items in an
+  // underfilled launch -- measured, one sequence: BF16 1024 tokens 14.4 -> 13.4 us but 512 tokens 9.6
+  // -> 10.8 and 2048 tokens (192 items, two rounds) 24.4 -> 29.4; FP32 mode, whose tiles take three
+  // times the MMAs, 1024 tokens 37.0 -> 28.1 and 2048 tokens 67.8 -> 65.4.
+  p.split_from = p.q_tiles;
+  p.partial = nullptr;
+  p.arrivals = nullptr;
+  p.order = nullptr;
+  const char* split_env = getenv("KILN_GPU_ATTENTION_SPLIT");      // 0: never share a query tile between CTAs
+  if (!(c.exact && !st->exact_tc) && p.q_tiles >= 8 && B * H * p.q_tiles <= (c.exact ? 2 : 1) * (int64_t)plan.sm_count &&
+      !(split_env && !strcmp(split_env, "0"))) {
+    p.split_from = p.q_tiles / 2;
+    const int64_t split_tiles = B * H * (p.q_tiles - p.split_from);
+    const size_t partial_bytes = (size_t)split_tiles * 2 * kPartialFloats * sizeof(float);
+    const size_t counter_bytes = (size_t)split_tiles * 4 * sizeof(int);
+    // whole tiles and halves by descending number of key tiles, so that the alternating rounds of the
+    // persistent CTAs pair a long item with a short one
+    std::vector<std::pair<int, unsigned short>> entries;
+    for (int qt = 0; qt < p.q_tiles; ++qt) {
+      const int n = qt + 1;
+      if (qt >= p.split_from) {
+        entries.push_back({n >> 1, (unsigned short)(qt << 1)});
+        entries.push_back({n - (n >> 1), (unsigned short)(qt << 1 | 1)});
+      } else {
+        entries.push_back({n, (unsigned short)(qt << 1)});
+      }
+    }
+    std::stable_sort(entries.begin(), entries.end(), [](const auto& a, const auto& b) { return a.first > b.first; });
+    std::vector<unsigned short> order;
+    for (const auto& e : entries) order.push_back(e.second);
+    const size_t order_bytes = (order.size() * sizeof(unsigned short) + 15) & ~size_t(15);
+    if (cudaMalloc(&st->split_scratch, partial_bytes + counter_bytes + order_bytes) != cudaSuccess ||
+        cudaMemset(static_cast<uint8_t*>(st->split_scratch) + partial_bytes, 0, counter_bytes) != cudaSuccess ||
+        cudaMemcpy(static_cast<uint8_t*>(st->split_scratch) + partial_bytes + counter_bytes, order.data(),
+                   order.size() * sizeof(unsigned short), cudaMemcpyHostToDevice) != cudaSuccess) {
+      cudaGetLastError();
+      if (st->split_scratch) cudaFree(st->split_scratch);
+      if (st->staged_out) cudaFree(st->staged_out);
+      if (st->tails) cudaFree(st->tails);
+      delete st;
+      return false;
+    }
+    p.partial = static_cast<float*>(st->split_scratch);
+    p.arrivals = reinterpret_cast<int*>(static_cast<uint8_t*>(st->split_scratch) + partial_bytes);
+    p.order = reinterpret_cast<const unsigned short*>(static_cast<uint8_t*>(st->split_scratch) + partial_bytes + counter_bytes);
+  }
+  const int64_t items = B * H * (p.q_tiles + (p.q_tiles - p.split_from));
   st->grid = dim3((unsigned)(items < plan.sm_count ? items : plan.sm_count), 1, 1);     // persistent: at most one CTA per SM
   if (c.exact && !st->exact_tc) {
     AttnF32Params& f = st->f32;
@@ -1796,6 +1975,7 @@ void attention_destroy(PlanKernel& k) {
     if (st->staged_out) cudaFree(st->staged_out);
     if (st->f32_scratch) cudaFree(st->f32_scratch);
     if (st->tails) cudaFree(st->tails);
+    if (st->split_scratch) cudaFree(st->split_scratch);
     delete st;
   }
   k.attn = nullptr;
