@@ -132,6 +132,27 @@ def test_both_fp32_attention_kernels_match_float64(tokens, kernel, monkeypatch):
     assert scale_relative_error(got[0], exact) <= REL_TOL["fp32"]
 
 
+@pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16"])
+def test_query_tiles_shared_by_two_ctas_merge_to_the_same_rows(precision, monkeypatch):
+    """One 1024-token sequence leaves SMs idle, so the long query tiles are worked on by two CTAs each
+    and merged by the one that finishes second; replays must keep working (the arrival counters are
+    reset by the merging CTA) and the rows must match the unsplit kernel's and float64."""
+    from gpu_helpers import run_case
+
+    case = "gpt2_block_t1024"
+    split_exe, split, (plan, inputs, consts, _) = run_case(case, precision)
+    x = torch.from_numpy(inputs[0])
+    again = [split_exe(x)[0].cpu().numpy() for _ in range(3)]
+    for other in again:
+        assert scale_relative_error(other, split[0]) <= 1e-6      # the merge is symmetric: no dependence on arrival order beyond rounding
+    monkeypatch.setenv("KILN_GPU_ATTENTION_SPLIT", "0")
+    _, whole, _ = run_case(case, precision)
+    (exact,) = run_plan(plan, inputs, consts, dtype=np.float64)
+    assert scale_relative_error(split[0], exact) <= REL_TOL[precision]
+    assert scale_relative_error(whole[0], exact) <= REL_TOL[precision]
+    assert scale_relative_error(split[0], whole[0]) <= REL_TOL[precision]
+
+
 def test_fp32_mode_fuses_attention_too(monkeypatch):
     """FP32 mode (the reference's allow_tf32=False) takes the CUDA-core fused kernel: the scores are never written."""
     from gpu_helpers import build_executable
