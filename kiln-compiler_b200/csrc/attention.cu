@@ -728,7 +728,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         xmax[(s * 2 + group) * kRows + row] = mx;
         if (pair_sync_aborted()) { ok = false; break; }
         mx = fmaxf(mx, xmax[(s * 2 + (group ^ 1)) * kRows + row]);
-        // key 0 is visible to every row, so the maximum over a whole tile is finite
+        // the first key of every tile at or below the diagonal is visible to every row, so the maximum is finite
         const float m_new = fmaxf(m_run, mx * p.scale_log2);
         const float alpha = ex2(m_run - m_new);       // 0 while m_run = -inf
         float sum;
@@ -918,7 +918,7 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t k_smem = q_smem + kOpBytes;        // one buffer each: tile, then its tails
   const uint32_t v_smem = k_smem + kOpBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
+  // bars (same numbering as the TF32 kernel; of the K / V pairs only the first is used): 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
   //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer] | 19 q_empty
   const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
   const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
@@ -1042,7 +1042,8 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       bool ok = true;
-      // Tiles are numbered over all items (t): ring slot, S buffer and O_part buffer are t & 1, phases (t >> 1) & 1.
+      // Tiles are numbered over all items (t): S buffer and O_part buffer are t & 1, their phases (t >> 1) & 1;
+      // the single K and V buffers change phase with every tile.
       auto issue_qk = [&](int t) {
         const int s = t & 1;
         if (!mbar_wait(k_full, t & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
@@ -1137,8 +1138,7 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int row = quad * 32 + lane;              // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int c0 = group * 64;
-    // behind the rings: [2 tile parities][2 groups][128 rows] maxima, [2 item parities][2][128] row sums,
-    // then a staging slot per warp for the output rows (32 x 32 float32 + their bf16 copy)
+    // behind the operand buffers: [2 tile parities][2 groups][128 rows] maxima, [2 item parities][2][128] row sums
     float* const xmax = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
     float* const xsum = xmax + 4 * kRows;
     const int pair_barrier = 2 + quad;              // hardware barriers 2..5, 64 threads each
@@ -1204,7 +1204,7 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         xmax[(s * 2 + group) * kRows + row] = mx;
         if (pair_sync_aborted()) { ok = false; break; }
         mx = fmaxf(mx, xmax[(s * 2 + (group ^ 1)) * kRows + row]);
-        // key 0 is visible to every row, so the maximum over a whole tile is finite
+        // the first key of every tile at or below the diagonal is visible to every row, so the maximum is finite
         const float m_new = fmaxf(m_run, mx * p.scale_log2);
         const float alpha = ex2(m_run - m_new);       // 0 while m_run = -inf
         float sum;
