@@ -207,14 +207,23 @@ int kb200_plan_bind(kb200_plan* plan, void* arena, uint64_t arena_bytes,
  * KB200_OPT_MIRROR_ONLY (default 1, BF16 mode): a LayerNorm or matmul whose output is read only by
  * kernels that take its bf16 mirror (tensor-core matmul operands, the fused attention) does not store
  * the float32 values: that arena region then holds stale data, which no planned kernel reads.  0 stores
- * both, for a caller that inspects intermediate buffers. */
+ * both, for a caller that inspects intermediate buffers.
+ * KB200_OPT_FP32_ATTENTION (default 0, FP32 precision): which kernel runs the fused attention.
+ * 0 = by size (the tensor-core kernel, three TF32 products per float32 product, when its work items
+ * fill a quarter of the SMs and no matmul of the chain asked for IEEE behaviour on non-finite
+ * operands; else the CUDA-core kernel), 1 = always the CUDA-core kernel, 2 = always the tensor cores.
+ * KB200_OPT_ATTENTION_SPLIT (default 1): in a launch that leaves SMs idle (one long sequence,
+ * KB200_OPT_CONCURRENCY 1) the fused attention shares its long query tiles between two CTAs, which
+ * merge their halves through a workspace.  0 keeps every query tile on one CTA. */
 typedef enum kb200_option {
   KB200_OPT_FUSE_ATTENTION = 1,
   KB200_OPT_DEPENDENT_LAUNCH = 2,
   KB200_OPT_FOLD_OPERAND_COPIES = 3,
   KB200_OPT_CONCURRENCY = 4,
   KB200_OPT_ABSORB_ELEMENTWISE = 5,
-  KB200_OPT_MIRROR_ONLY = 6
+  KB200_OPT_MIRROR_ONLY = 6,
+  KB200_OPT_FP32_ATTENTION = 7,
+  KB200_OPT_ATTENTION_SPLIT = 8
 } kb200_option;
 int kb200_plan_set_option(kb200_plan* plan, int option, int value);
 

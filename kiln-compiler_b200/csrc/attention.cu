@@ -33,8 +33,6 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
-#include <cstdlib>
-#include <cstring>
 #include <utility>
 #include <vector>
 
@@ -392,12 +390,13 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
       const float4 o2 = __ldcg(reinterpret_cast<const float4*>(other + (ty + 8 * i) * kHeadDim + 4 * tx));
       const float m = fmaxf(m_run[i], m2);
       const float a1 = exp2f(m_run[i] - m), a2 = exp2f(m2 - m);
-      // symmetric in the two halves: the same bits whichever CTA merges
-      l_run[i] = l_run[i] * a1 + l2 * a2;
-      o[i][0] = o[i][0] * a1 + o2.x * a2;
-      o[i][1] = o[i][1] * a1 + o2.y * a2;
-      o[i][2] = o[i][2] * a1 + o2.z * a2;
-      o[i][3] = o[i][3] * a1 + o2.w * a2;
+      // products rounded one by one and then added (no fused multiply-add): symmetric in the two
+      // halves, so the bits do not depend on which CTA merges
+      l_run[i] = __fadd_rn(__fmul_rn(l_run[i], a1), __fmul_rn(l2, a2));
+      o[i][0] = __fadd_rn(__fmul_rn(o[i][0], a1), __fmul_rn(o2.x, a2));
+      o[i][1] = __fadd_rn(__fmul_rn(o[i][1], a1), __fmul_rn(o2.y, a2));
+      o[i][2] = __fadd_rn(__fmul_rn(o[i][2], a1), __fmul_rn(o2.z, a2));
+      o[i][3] = __fadd_rn(__fmul_rn(o[i][3], a1), __fmul_rn(o2.w, a2));
     }
   }
   float* const og = p.out + (row0 + (int64_t)qt * kFTile) * p.out_row_stride + h * kHeadDim + 4 * tx;
@@ -804,15 +803,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float m2 = __ldcg(other + kRows * kHeadDim + row), l2 = __ldcg(other + kRows * kHeadDim + kRows + row);
             const float m = fmaxf(m_run, m2);
             const float a1 = ex2(m_run - m), a2 = ex2(m2 - m);
-            l_tot = l_tot * a1 + l2 * a2;             // symmetric in the halves: the same bits whoever merges
+            // Products rounded one by one and then added (no fused multiply-add): symmetric in the two
+            // halves, so the bits do not depend on which of them merges.
+            l_tot = __fadd_rn(__fmul_rn(l_tot, a1), __fmul_rn(l2, a2));
             const float4* const other4 = reinterpret_cast<const float4*>(other + row * kHeadDim + group * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float4 o2 = __ldcg(other4 + i);
-              o[4 * i] = o[4 * i] * a1 + o2.x * a2;
-              o[4 * i + 1] = o[4 * i + 1] * a1 + o2.y * a2;
-              o[4 * i + 2] = o[4 * i + 2] * a1 + o2.z * a2;
-              o[4 * i + 3] = o[4 * i + 3] * a1 + o2.w * a2;
+              o[4 * i] = __fadd_rn(__fmul_rn(o[4 * i], a1), __fmul_rn(o2.x, a2));
+              o[4 * i + 1] = __fadd_rn(__fmul_rn(o[4 * i + 1], a1), __fmul_rn(o2.y, a2));
+              o[4 * i + 2] = __fadd_rn(__fmul_rn(o[4 * i + 2], a1), __fmul_rn(o2.z, a2));
+              o[4 * i + 3] = __fadd_rn(__fmul_rn(o[4 * i + 3], a1), __fmul_rn(o2.w, a2));
             }
           }
         }
@@ -1278,15 +1279,17 @@ attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float m2 = __ldcg(other + kRows * kHeadDim + row), l2 = __ldcg(other + kRows * kHeadDim + kRows + row);
             const float m = fmaxf(m_run, m2);
             const float a1 = ex2(m_run - m), a2 = ex2(m2 - m);
-            l_tot = l_tot * a1 + l2 * a2;             // symmetric in the halves: the same bits whoever merges
+            // Products rounded one by one and then added (no fused multiply-add): symmetric in the two
+            // halves, so the bits do not depend on which of them merges.
+            l_tot = __fadd_rn(__fmul_rn(l_tot, a1), __fmul_rn(l2, a2));
             const float4* const other4 = reinterpret_cast<const float4*>(other + row * kHeadDim + group * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float4 o2 = __ldcg(other4 + i);
-              o[4 * i] = o[4 * i] * a1 + o2.x * a2;
-              o[4 * i + 1] = o[4 * i + 1] * a1 + o2.y * a2;
-              o[4 * i + 2] = o[4 * i + 2] * a1 + o2.z * a2;
-              o[4 * i + 3] = o[4 * i + 3] * a1 + o2.w * a2;
+              o[4 * i] = __fadd_rn(__fmul_rn(o[4 * i], a1), __fmul_rn(o2.x, a2));
+              o[4 * i + 1] = __fadd_rn(__fmul_rn(o[4 * i + 1], a1), __fmul_rn(o2.y, a2));
+              o[4 * i + 2] = __fadd_rn(__fmul_rn(o[4 * i + 2], a1), __fmul_rn(o2.z, a2));
+              o[4 * i + 3] = __fadd_rn(__fmul_rn(o[4 * i + 3], a1), __fmul_rn(o2.w, a2));
             }
           }
         }
@@ -1457,14 +1460,12 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   // FP32 mode: the tensor-core kernel when its work items (128 queries each) fill at least a quarter
   // of the SMs, the CUDA-core kernel (64 queries per CTA, long prefixes split) for the short sequences
   // below that (one 128-token sequence: 8.6 against 10.4 us; 512 tokens: 22.4 against 20.9);
-  // KILN_GPU_FP32_ATTENTION=fma / tensor forces one of them.
+  // the plan option KB200_OPT_FP32_ATTENTION forces one of them.
   if (c.exact) {
     // (split operands turn an infinite element into a NaN tail: a plan that asked for IEEE behaviour keeps the FMA kernel)
     st->exact_tc = !c.ieee && B * H * (T / kRows) * 4 >= plan.sm_count;
-    if (const char* e = getenv("KILN_GPU_FP32_ATTENTION")) {
-      if (!strcmp(e, "fma")) st->exact_tc = false;
-      if (!strcmp(e, "tensor")) st->exact_tc = true;
-    }
+    if (plan.fp32_attention == 1) st->exact_tc = false;
+    if (plan.fp32_attention == 2) st->exact_tc = true;
   }
   if ((!c.exact || st->exact_tc) && (!encode_map(&st->map_q, false, c.q, hd, B * T, H, rs, hd, 32, kRows, false) ||
                                      !encode_map(&st->map_k, false, c.k, hd, B * T, H, rs, hd, 32, kRows, false) ||
@@ -1558,10 +1559,9 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
   p.partial = nullptr;
   p.arrivals = nullptr;
   p.order = nullptr;
-  const char* split_env = getenv("KILN_GPU_ATTENTION_SPLIT");      // 0: never share a query tile between CTAs
   if (!(c.exact && !st->exact_tc) && p.q_tiles >= 8 && B * H * p.q_tiles <= (c.exact ? 2 : 1) * (int64_t)plan.sm_count &&
       plan.concurrency == 1 &&                       // other plans in flight fill the SMs this one leaves idle
-      !(split_env && !strcmp(split_env, "0"))) {
+      plan.attention_split) {
     p.split_from = p.q_tiles / 2;
     const int64_t split_tiles = B * H * (p.q_tiles - p.split_from);
     const size_t partial_bytes = (size_t)split_tiles * 2 * kPartialFloats * sizeof(float);
@@ -1991,6 +1991,13 @@ const DevOperand* attention_output(const Plan& plan, size_t first, int64_t* elem
   const AttnState* st = static_cast<const AttnState*>(plan.kernels[first].attn);
   *elems = st->y_elems;
   return st->y;
+}
+
+void attention_reset_arrivals(PlanKernel& k) {
+  AttnState* st = static_cast<AttnState*>(k.attn);
+  if (!st || !st->params.arrivals) return;
+  const int64_t split_tiles = (int64_t)st->params.B * st->params.H * (st->params.q_tiles - st->params.split_from);
+  cudaMemset(st->params.arrivals, 0, (size_t)split_tiles * 4 * sizeof(int));
 }
 
 void attention_destroy(PlanKernel& k) {

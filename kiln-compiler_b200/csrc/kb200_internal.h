@@ -111,6 +111,8 @@ struct Plan {
   std::vector<PlanKernel> kernels;
   int* d_status = nullptr;       // device status word for bounded waits
   bool fuse_attention = true;    // replace the five-kernel attention chain by the fused kernel when it matches
+  int fp32_attention = 0;        // FP32 precision: 0 = pick the fused attention kernel by size, 1 = CUDA cores, 2 = tensor cores
+  bool attention_split = true;   // share long query tiles between two CTAs when a launch would leave SMs idle
   bool fold_copies = true;       // a matmul reads a K-contiguous B at its source; the plan's transposing copy is not launched
   bool pdl = true;               // programmatic dependent launch: a kernel's start-up overlaps its predecessor's tail
   bool absorb_elementwise = true; // a tensor-core matmul also runs the elementwise kernel that only continues it
@@ -155,6 +157,7 @@ bool attention_reads_mirror(const PlanKernel& k);
 bool tc_eligible(const PlanKernel& k);
 int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s);
 void attention_destroy(PlanKernel& k);
+void attention_reset_arrivals(PlanKernel& k);    // after a reported wait error: clear the split tiles' arrival counters
 
 // Every kernel of the library is launched through this: with programmatic stream serialization the
 // next kernel in the stream may start (barrier set-up, TMEM allocation, descriptor prefetch) while

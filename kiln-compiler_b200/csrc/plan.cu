@@ -1063,6 +1063,8 @@ KB200_EXPORT int kb200_plan_set_option(kb200_plan* p, int option, int value) {
     case KB200_OPT_CONCURRENCY: plan.concurrency = value < 1 ? 1 : value; return KB200_OK;
     case KB200_OPT_ABSORB_ELEMENTWISE: plan.absorb_elementwise = value != 0; return KB200_OK;
     case KB200_OPT_MIRROR_ONLY: plan.mirror_only = value != 0; return KB200_OK;
+    case KB200_OPT_FP32_ATTENTION: plan.fp32_attention = value < 0 || value > 2 ? 0 : value; return KB200_OK;
+    case KB200_OPT_ATTENTION_SPLIT: plan.attention_split = value != 0; return KB200_OK;
     default: return fail(KB200_ERR_ARGUMENT, "kb200_plan_set_option: unknown option %d", option);
   }
 }
@@ -1122,6 +1124,8 @@ KB200_EXPORT int kb200_plan_status(kb200_plan* p) {
   KB200_CUDA(cudaMemcpy(&word, plan.d_status, sizeof(int), cudaMemcpyDeviceToHost));
   if (word != 0) {
     cudaMemset(plan.d_status, 0, sizeof(int));
+    // a fused attention that gave up may have counted one half of a shared query tile and not the other
+    for (PlanKernel& k : plan.kernels) attention_reset_arrivals(k);
     return fail(KB200_ERR_DEVICE_WAIT, "a bounded device-side wait ran out (code 0x%x: kernel %d, site %d)", word,
                 (word >> 8) & 0xffff, word & 0xff);
   }

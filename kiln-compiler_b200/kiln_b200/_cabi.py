@@ -28,6 +28,8 @@ OPT_FOLD_OPERAND_COPIES = 3
 OPT_CONCURRENCY = 4
 OPT_ABSORB_ELEMENTWISE = 5
 OPT_MIRROR_ONLY = 6
+OPT_FP32_ATTENTION = 7
+OPT_ATTENTION_SPLIT = 8
 BASE_KINDS = {"arena": 0, "const": 1, "input": 2, "output": 3}
 PRECISIONS = {"fp32": 0, "tf32": 1, "bf16": 2}
 OPCODES = {

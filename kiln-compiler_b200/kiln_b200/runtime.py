@@ -206,6 +206,12 @@ class GPUExecutable:
         _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_ABSORB_ELEMENTWISE, int(absorb)), self._lib)
         mirror_only = os.environ.get("KILN_GPU_MIRROR_ONLY", "1") not in ("0", "false", "False", "")
         _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_MIRROR_ONLY, int(mirror_only)), self._lib)
+        # FP32 mode's fused attention: KILN_GPU_FP32_ATTENTION=fma / tensor forces the CUDA-core or the
+        # tensor-core kernel (default: by size); KILN_GPU_ATTENTION_SPLIT=0 keeps every query tile on one CTA.
+        fp32_attention = {"fma": 1, "tensor": 2}.get(os.environ.get("KILN_GPU_FP32_ATTENTION", "").lower(), 0)
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_FP32_ATTENTION, fp32_attention), self._lib)
+        split = os.environ.get("KILN_GPU_ATTENTION_SPLIT", "1") not in ("0", "false", "False", "")
+        _cabi.check(self._lib.kb200_plan_set_option(self._plan, _cabi.OPT_ATTENTION_SPLIT, int(split)), self._lib)
         self._bind()
         # launch_names: one per device launch of the plan (k3_matmul, k2_ew0 ...); kernel_names: the Kiln
         # kernels they come from, which is what CompiledModule.profile keys on (kiln/api.py:204-211)

@@ -144,7 +144,7 @@ def test_query_tiles_shared_by_two_ctas_merge_to_the_same_rows(precision, monkey
     x = torch.from_numpy(inputs[0])
     again = [split_exe(x)[0].cpu().numpy() for _ in range(3)]
     for other in again:
-        assert scale_relative_error(other, split[0]) <= 1e-6      # the merge is symmetric: no dependence on arrival order beyond rounding
+        assert np.array_equal(other, split[0])      # the merge is symmetric in the halves: the same bits whichever CTA arrives second
     monkeypatch.setenv("KILN_GPU_ATTENTION_SPLIT", "0")
     _, whole, _ = run_case(case, precision)
     (exact,) = run_plan(plan, inputs, consts, dtype=np.float64)
