@@ -49,6 +49,15 @@ def test_struct_layout_matches_the_header():
     assert ctypes.sizeof(_cabi.KernelDesc) == expected
 
 
+def test_option_numbers_match_the_header():
+    """The plan options the runtime sets (attention fusion ... shared attention query tiles) carry the header's numbers."""
+    header = (ROOT / "include" / "kb200.h").read_text()
+    declared = {name: int(value) for name, value in re.findall(r"\bKB200_(OPT_[A-Z0-9_]+)\s*=\s*(\d+)", header)}
+    assert declared and sorted(declared.values()) == list(range(1, len(declared) + 1))
+    ours = {name: getattr(_cabi, name) for name in dir(_cabi) if name.startswith("OPT_")}
+    assert ours == declared
+
+
 def test_plan_create_rejects_bad_arguments_without_a_gpu(lib):
     out = ctypes.c_void_p()
     assert lib.kb200_plan_create(None, 1, 0, ctypes.byref(out)) == -1
