@@ -8,10 +8,10 @@
 // chain and the mask is the causal one, a fused kernel replaces the five launches: it reads Q, K and
 // V as strided views of the QKV projection's output and writes the merged-heads buffer, the only
 // value of the chain that is live afterwards.  The plan itself (kernel list, arena offsets) is
-// untouched; the score buffers are simply never written.  Three kernels: `attention_kernel` for the
-// TF32 and BF16 matmul modes (described next), `attention_exact_kernel` for FP32 mode (the same
-// structure with three TF32 MMAs per product) and `attention_fp32_kernel` for short sequences in
-// FP32 mode (CUDA cores).
+// untouched; the score buffers are simply never written.  Two kernels: `attention_kernel` on the tensor
+// cores -- for the TF32 and BF16 matmul modes (described next) and, with its EXACT parameter, for FP32
+// mode (the same structure with three TF32 MMAs per product) -- and `attention_fp32_kernel` for short
+// sequences in FP32 mode (CUDA cores).
 //
 // Persistent CTAs (one per SM) walk the (sequence, head, 128-query tile) work items, heaviest first, in
 // steps of the grid size: barrier set-up, the TMEM allocation and the latency of an item's first
@@ -408,14 +408,29 @@ __global__ void __launch_bounds__(kFThreads, 2) attention_fp32_kernel(const __gr
   }
 }
 
-template <bool BF16, bool SPLIT>
+// EXACT (FP32 mode on the tensor cores, never with BF16): float32 products from three TF32 MMAs each
+// (x = head + tail, head the 19 leading bits the tensor core reads anyway: x y ~ head head + head tail
+// + tail head).  The tails of Q, K and V come from a copy of the QKV buffer that a small kernel
+// fills in front of this one (`tails_kernel`), through tensor maps of their own into the second
+// half of every operand buffer; the softmax threads write the probabilities' tails into tensor
+// memory next to the probabilities.  Differences in structure, all for space: K and V have one
+// buffer each instead of a ring of two (heads + tails of Q, K, V fill 192 KB; the next tile's loads
+// run under the softmax, which is the long pole), the tails of P have one buffer (a thread folds the
+// previous tile's O_part -- whose completion says its P V has read them -- before it writes the
+// next), and the output rows leave by ordinary stores (no staging slots).
+template <bool BF16, bool SPLIT, bool EXACT>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_out,
-                 const __grid_constant__ CUtensorMap map_out16, const __grid_constant__ AttnParams p) {
-  // a [128 rows x 64 dims] operand tile is two 128-byte-wide slabs in float32, one in bf16
+                 const __grid_constant__ CUtensorMap map_out16, const __grid_constant__ CUtensorMap map_qt,
+                 const __grid_constant__ CUtensorMap map_kt, const __grid_constant__ CUtensorMap map_vt,
+                 const __grid_constant__ AttnParams p) {
+  static_assert(!(BF16 && EXACT), "the FP32 mode has float32 operands");
+  // a [128 rows x 64 dims] operand tile is two 128-byte-wide slabs in float32, one in bf16;
+  // EXACT: an operand buffer holds the tile and, behind it, its tails
   constexpr int kTileSlabs = BF16 ? 1 : 2;
   constexpr int kTileBytes = kTileSlabs * kSlab;
+  constexpr int kOpBytes = 2 * kTileBytes;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[20];
   __shared__ uint32_t tmem_base_slot;
@@ -441,10 +456,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #endif
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t q_smem = (raw + 1023u) & ~1023u;
-  const uint32_t k_smem = q_smem + kTileBytes;      // ring of 2 tiles
+  const uint32_t k_smem = q_smem + (EXACT ? kOpBytes : kTileBytes);   // ring of 2 tiles | EXACT: one buffer (tile, then its tails)
   const uint32_t v_smem = k_smem + 2 * kTileBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
+  // bars (EXACT uses only the first of each K / V pair): 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
   //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer] | 19 q_empty
   const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
   const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
@@ -494,8 +509,14 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
-    prefetch_tensormap(&map_out);
-    if (p.out16 != nullptr) prefetch_tensormap(&map_out16);
+    if constexpr (EXACT) {
+      prefetch_tensormap(&map_qt);
+      prefetch_tensormap(&map_kt);
+      prefetch_tensormap(&map_vt);
+    } else {
+      prefetch_tensormap(&map_out);
+      if (p.out16 != nullptr) prefetch_tensormap(&map_out16);
+    }
   }
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -526,8 +547,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   pdl_wait();
   pdl_launch_dependents();
   const uint32_t tmem_base = tmem_base_slot;
-  // columns: S0 0..127 | S1 128..255 | O_part[buffer] 256 + buffer * 64
+  // columns: S0 0..127 | S1 128..255 | O_part[buffer] 256 + buffer * 64 | EXACT: tails of P 384..511
   const uint32_t tmem_o0 = tmem_base + 256;
+  [[maybe_unused]] const uint32_t tmem_pt = tmem_base + 384;
   volatile int* abort_ptr = &abort_flag;
   auto give_up = [&](int site) {
     if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | site); *abort_ptr = 1; }
@@ -544,20 +566,40 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const Item it = item_of(w);
         // the Q tile is free once every Q K^T of the previous item has been executed
         if (!mbar_wait(q_empty, (ii & 1) ^ 1, abort_ptr)) { give_up(0x13); break; }
-        mbar_expect_tx(q_full, kTileBytes);
-        tma_load_3d(q_smem, &map_q, q_full, 0, it.row0 + it.q0, it.h);
-        if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, it.row0 + it.q0, it.h);
+        // EXACT, an operand buffer: the tile's two slabs, then the two slabs of its tails
+        [[maybe_unused]] auto load4 = [&](uint32_t dst, const CUtensorMap* heads, const CUtensorMap* tails, uint32_t bar, int first_row) {
+          mbar_expect_tx(bar, kOpBytes);
+          tma_load_3d(dst, heads, bar, 0, first_row, it.h);
+          tma_load_3d(dst + kSlab, heads, bar, 32, first_row, it.h);
+          tma_load_3d(dst + kTileBytes, tails, bar, 0, first_row, it.h);
+          tma_load_3d(dst + kTileBytes + kSlab, tails, bar, 32, first_row, it.h);
+        };
+        if constexpr (EXACT) {
+          load4(q_smem, &map_q, &map_qt, q_full, it.row0 + it.q0);
+        } else {
+          mbar_expect_tx(q_full, kTileBytes);
+          tma_load_3d(q_smem, &map_q, q_full, 0, it.row0 + it.q0, it.h);
+          if (!BF16) tma_load_3d(q_smem + kSlab, &map_q, q_full, 32, it.row0 + it.q0, it.h);
+        }
         for (int j = 0; j < it.n_kv; ++j, ++t) {
-          const int s = t & 1;
-          const uint32_t ph = (t >> 1) & 1;
-          if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
-          mbar_expect_tx(k_full + 8 * s, kTileBytes);
-          tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, it.row0 + (it.j0 + j) * kRows, it.h);
-          if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, it.row0 + (it.j0 + j) * kRows, it.h);
-          if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
-          mbar_expect_tx(v_full + 8 * s, kTileBytes);
-          tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, it.row0 + (it.j0 + j) * kRows, it.h);
-          if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, it.row0 + (it.j0 + j) * kRows, it.h);
+          if constexpr (EXACT) {
+            const uint32_t ph = t & 1;                   // one buffer: the phase alternates with every tile
+            if (!mbar_wait(k_empty, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
+            load4(k_smem, &map_k, &map_kt, k_full, it.row0 + (it.j0 + j) * kRows);
+            if (!mbar_wait(v_empty, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
+            load4(v_smem, &map_v, &map_vt, v_full, it.row0 + (it.j0 + j) * kRows);
+          } else {
+            const int s = t & 1;
+            const uint32_t ph = (t >> 1) & 1;
+            if (!mbar_wait(k_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
+            mbar_expect_tx(k_full + 8 * s, kTileBytes);
+            tma_load_3d(k_smem + s * kTileBytes, &map_k, k_full + 8 * s, 0, it.row0 + (it.j0 + j) * kRows, it.h);
+            if (!BF16) tma_load_3d(k_smem + s * kTileBytes + kSlab, &map_k, k_full + 8 * s, 32, it.row0 + (it.j0 + j) * kRows, it.h);
+            if (!mbar_wait(v_empty + 8 * s, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
+            mbar_expect_tx(v_full + 8 * s, kTileBytes);
+            tma_load_3d(v_smem + s * kTileBytes, &map_v, v_full + 8 * s, 0, it.row0 + (it.j0 + j) * kRows, it.h);
+            if (!BF16) tma_load_3d(v_smem + s * kTileBytes + kSlab, &map_v, v_full + 8 * s, 32, it.row0 + (it.j0 + j) * kRows, it.h);
+          }
         }
       }
     }
@@ -565,21 +607,36 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       bool ok = true;
-      // Tiles are numbered over all items (t): ring slot, S buffer and O_part buffer are t & 1, phases (t >> 1) & 1.
+      // Tiles are numbered over all items (t): ring slot, S buffer and O_part buffer are t & 1, phases (t >> 1) & 1
+      // (EXACT: the single K and V buffers change phase with every tile).
       auto issue_qk = [&](int t) {
         const int s = t & 1;
-        if (!mbar_wait(k_full + 8 * s, (t >> 1) & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
+        if (!mbar_wait(EXACT ? k_full : k_full + 8 * s, EXACT ? (t & 1) : ((t >> 1) & 1), abort_ptr)) { give_up(0x22); ok = false; return; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kb = k_smem + s * kTileBytes;
+        const uint32_t kb = EXACT ? k_smem : k_smem + s * kTileBytes;
         // 32 bytes of the head dimension per instruction: 8 float32 (TF32) or 16 bf16
+        if constexpr (EXACT) {
+          // heads x heads, heads x tails, tails x heads
 #pragma unroll
-        for (int kd = 0; kd < kTileSlabs * 4; ++kd) {
-          const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
-          umma(tmem_base + (uint32_t)s * 128, make_desc(q_smem + off, 16, 1024), make_desc(kb + off, 16, 1024), p.idesc_qk,
-               kd != 0 ? 1u : 0u, BF16);
+          for (int pass = 0; pass < 3; ++pass) {
+            const uint32_t qa = q_smem + (pass == 2 ? kTileBytes : 0), ka = kb + (pass == 1 ? kTileBytes : 0);
+#pragma unroll
+            for (int kd = 0; kd < kTileSlabs * 4; ++kd) {
+              const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
+              umma(tmem_base + (uint32_t)s * 128, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024), p.idesc_qk,
+                   (pass | kd) != 0 ? 1u : 0u, false);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int kd = 0; kd < kTileSlabs * 4; ++kd) {
+            const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
+            umma(tmem_base + (uint32_t)s * 128, make_desc(q_smem + off, 16, 1024), make_desc(kb + off, 16, 1024), p.idesc_qk,
+                 kd != 0 ? 1u : 0u, BF16);
+          }
         }
         umma_commit(sfull0 + 8 * s);
-        umma_commit(k_empty + 8 * s);
+        umma_commit(EXACT ? k_empty : k_empty + 8 * s);
       };
       // P V of tile t: the 128 keys of both threads of a row pair into the O_part buffer (t & 1), as two
       // runs of MMAs (a group's P occupies the first columns of its 64-column share of S).  In-order
@@ -589,13 +646,24 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       auto issue_pv = [&](int t) {
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(v_full + 8 * s, ph, abort_ptr)) { give_up(0x23); ok = false; return; }
-        const uint32_t vb = v_smem + s * kTileBytes;
+        if (!mbar_wait(EXACT ? v_full : v_full + 8 * s, EXACT ? (uint32_t)(t & 1) : ph, abort_ptr)) { give_up(0x23); ok = false; return; }
+        const uint32_t vb = EXACT ? v_smem : v_smem + s * kTileBytes;
         const uint32_t o_addr = tmem_o0 + (uint32_t)s * 64;
         for (int g = 0; g < 2; ++g) {
           if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (BF16) {
+          if constexpr (EXACT) {
+            // P x V, P x tails of V, tails of P x V
+#pragma unroll
+            for (int pass = 0; pass < 3; ++pass) {
+              const uint32_t pa = pass == 2 ? tmem_pt : tmem_base + (uint32_t)s * 128;
+              const uint32_t va = vb + (pass == 1 ? kTileBytes : 0);
+#pragma unroll
+              for (int kk = 0; kk < 8; ++kk)
+                umma_ts(o_addr, pa + (uint32_t)(g * 64 + kk * 8), make_desc(va + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1),
+                        p.idesc_pv, (g | kk | pass) != 0 ? 1u : 0u, false);
+            }
+          } else if (BF16) {
             // P: two bf16 per TMEM column, 16 keys = 8 columns per instruction; V: [keys x 64 dims] bf16,
             // one 128-byte swizzled row per key, 16 rows per instruction
 #pragma unroll
@@ -610,7 +678,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
         }
         umma_commit(ofull0 + 8 * s);
-        umma_commit(v_empty + 8 * s);
+        umma_commit(EXACT ? v_empty : v_empty + 8 * s);
       };
       // An item's first scores: its Q must have landed; once its last scores are issued, the Q tile is handed back.
       auto first_qk = [&](int ii, int t, int n_kv) {
@@ -663,7 +731,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // then a staging slot per warp for the output rows (32 x 32 float32 + their bf16 copy)
     float* const xmax = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
     float* const xsum = xmax + 4 * kRows;
-    uint8_t* const stage = reinterpret_cast<uint8_t*>(xmax) + kExchangeBytes + (size_t)((warp - 2) * kStageBytes);
+    [[maybe_unused]] uint8_t* const stage = reinterpret_cast<uint8_t*>(xmax) + kExchangeBytes + (size_t)((warp - 2) * kStageBytes);   // (not EXACT)
     const int pair_barrier = 2 + quad;              // hardware barriers 2..5, 64 threads each
     // The pair's barrier also carries the abort flag (an OR over what the 64 threads read before they
     // arrived), so that both threads of a row take the same decision and neither waits for the other.
@@ -738,7 +806,23 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           sum = probabilities32<false>(va, p.scale_log2, m_new, 0, 0);
           sum += probabilities32<false>(vb, p.scale_log2, m_new, 0, 0);
         }
-        if (BF16) {
+        if constexpr (EXACT) {
+          // Fold the PREVIOUS tile's O_part first: that it is complete also says that its P V has read the
+          // tails of P, whose single buffer is written next.
+          if (j > 0) fold(t - 1, alpha_prev);
+          ATTN_STAMP(3, j);
+          const uint32_t pt_addr = tmem_pt + lane_addr + (uint32_t)c0;
+          float ta[32];
+          tmem_st32(s_addr, va);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ta[i] = va[i] - __uint_as_float(__float_as_uint(va[i]) & 0xFFFFE000u);
+          tmem_st32(pt_addr, ta);
+          tmem_st32(s_addr + 32, vb);
+          float tb[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tb[i] = vb[i] - __uint_as_float(__float_as_uint(vb[i]) & 0xFFFFE000u);
+          tmem_st32(pt_addr + 32, tb);
+        } else if (BF16) {
           // P rounded to bf16, two keys per 32-bit column: the thread's 64 keys take the first 32 columns of
           // its own 64-column share of the S buffer
           float packed[32];
@@ -759,8 +843,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_arrive(pfull0 + 8 * (group * 2 + s));
         ATTN_STAMP(1, j);
         // fold the PREVIOUS tile's O_part while the tensor pipe works on this one
-        if (j > 0) fold(t - 1, alpha_prev);
-        ATTN_STAMP(3, j);
+        if constexpr (!EXACT) {
+          if (j > 0) fold(t - 1, alpha_prev);
+          ATTN_STAMP(3, j);
+        }
         alpha_prev = alpha;
         l_run = l_run * alpha + sum;
         m_run = m_new;
@@ -819,26 +905,33 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
       }
       if (ok && writes) {
-        const float inv = __fdividef(1.0f, l_tot);
+        const float inv = EXACT ? 1.0f / l_tot : __fdividef(1.0f, l_tot);
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] *= inv;
-        // A lane holds 32 dims of ONE row: the rows go through the warp's staging slot (128-byte rows, the
-        // 16-byte unit XORed with the row against bank conflicts) and leave as bulk tensor stores.
-        if (lane == 0) tma_store_wait_read();          // the slot's last stores have read it
-        __syncwarp();
-        stage_rows(stage, stage + 4096, o, lane, p.out16 != nullptr, true);
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int col = it.h * kHeadDim + group * 32, first_row = it.row0 + it.q0 + quad * 32;
-          tma_store_3d(&map_out, smem_u32(stage), col, first_row, 0);
-          if (p.out16 != nullptr) tma_store_3d(&map_out16, smem_u32(stage + 4096), col, first_row, 0);
-          tma_store_commit();
+        if constexpr (EXACT) {
+          // a lane holds 32 dims of ONE row: 128 contiguous bytes
+          float* const dst = p.out + (int64_t)(it.row0 + it.q0 + row) * p.out_row_stride + it.h * kHeadDim + group * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        } else {
+          // A lane holds 32 dims of ONE row: the rows go through the warp's staging slot (128-byte rows, the
+          // 16-byte unit XORed with the row against bank conflicts) and leave as bulk tensor stores.
+          if (lane == 0) tma_store_wait_read();          // the slot's last stores have read it
+          __syncwarp();
+          stage_rows(stage, stage + 4096, o, lane, p.out16 != nullptr, true);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int col = it.h * kHeadDim + group * 32, first_row = it.row0 + it.q0 + quad * 32;
+            tma_store_3d(&map_out, smem_u32(stage), col, first_row, 0);
+            if (p.out16 != nullptr) tma_store_3d(&map_out16, smem_u32(stage + 4096), col, first_row, 0);
+            tma_store_commit();
+          }
         }
       }
       ATTN_STAMP(2, 3 * ii + 2);
     }
-    if (lane == 0) tma_store_wait_read();              // shared memory must outlive the stores that read it
+    if (!EXACT && lane == 0) tma_store_wait_read();    // shared memory must outlive the stores that read it
   }
 
   // ---------------- common exit ----------------
@@ -862,474 +955,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
 #endif
   if (abort_flag && threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s)
+    for (int s = 0; s < (EXACT ? 1 : 2); ++s)
       for (uint32_t i = 0; i < 4096u; ++i)
         if ((mbar_try_wait(k_full + 8 * s, 0) || mbar_try_wait(k_full + 8 * s, 1)) &&
             (mbar_try_wait(v_full + 8 * s, 0) || mbar_try_wait(v_full + 8 * s, 1)))
           break;
-  }
-  __syncthreads();
-  if (warp == 2) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// FP32 mode on the tensor cores: the kernel above with float32 products from three TF32 MMAs each
-// (x = head + tail, head the 19 leading bits the tensor core reads anyway: x y ~ head head + head tail
-// + tail head).  The tails of Q, K and V come from a copy of the QKV buffer that a small kernel
-// fills in front of this one (`tails_kernel`), through tensor maps of their own into the second
-// half of every operand buffer; the softmax threads write the probabilities' tails into tensor
-// memory next to the probabilities.  Differences in structure, all for space: K and V have one
-// buffer each instead of a ring of two (heads + tails of Q, K, V fill 192 KB; the next tile's loads
-// run under the softmax, which is the long pole), the tails of P have one buffer (a thread folds the
-// previous tile's O_part -- whose completion says its P V has read them -- before it writes the
-// next), and the output rows leave by ordinary stores (no staging slots).
-template <bool SPLIT>
-__global__ void __launch_bounds__(kAttnThreads, 1)
-attention_exact_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_qt,
-                       const __grid_constant__ CUtensorMap map_kt, const __grid_constant__ CUtensorMap map_vt,
-                       const __grid_constant__ AttnParams p) {
-  // a [128 rows x 64 dims] float32 operand tile is two 128-byte-wide slabs; an operand buffer holds the tile and its tails
-  constexpr int kTileSlabs = 2;
-  constexpr int kTileBytes = kTileSlabs * kSlab;
-  constexpr int kOpBytes = 2 * kTileBytes;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[20];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ int abort_flag;
-  __shared__ int arrived[4];                  // split items: was this lane quadrant's half the second to arrive?
-
-#ifdef KB200_TRACE
-  __shared__ long long trace[4][16];
-  __shared__ long long mma_trace[64];
-  __shared__ long long marks[4];
-  int tm = 0;
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    unsigned long long g;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
-    marks[0] = (long long)g;
-    marks[1] = clock64();
-  }
-#endif
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t q_smem = (raw + 1023u) & ~1023u;
-  const uint32_t k_smem = q_smem + kOpBytes;        // one buffer each: tile, then its tails
-  const uint32_t v_smem = k_smem + kOpBytes;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // bars (same numbering as the TF32 kernel; of the K / V pairs only the first is used): 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full |
-  //       11..14 p_full[group][s buffer] | 15..18 o_full[group][o buffer] | 19 q_empty
-  const uint32_t q_full = smem_u32(&bars[0]), k_full = smem_u32(&bars[1]), k_empty = smem_u32(&bars[3]);
-  const uint32_t v_full = smem_u32(&bars[5]), v_empty = smem_u32(&bars[7]);
-  const uint32_t sfull0 = smem_u32(&bars[9]), pfull0 = smem_u32(&bars[11]), ofull0 = smem_u32(&bars[15]);
-  const uint32_t q_empty = smem_u32(&bars[19]);
-
-  // work item w -> (head, sequence, query tile): heaviest (longest causal prefix) tiles first, of every sequence
-  // Query tiles from p.split_from on (the longest causal prefixes; none when split_from = q_tiles) are
-  // TWO items, one per half of their key tiles: each leaves its unnormalised rows and softmax state in
-  // a workspace, and the one that arrives second (a counter per tile and lane quadrant) merges them.
-  // (SPLIT is a template parameter so that the kernel without split tiles keeps its code: with the
-  // choice made at run time the eight-sequence attention took 44.4 instead of 43.4 us.)
-  const int n_split = SPLIT ? p.q_tiles - p.split_from : 0;
-  const int n_items = p.B * p.H * (p.q_tiles + n_split);
-  // This CTA's r-th item (-1: none).  Rounds alternate direction over the CTAs, so that the CTA with the
-  // heaviest item of one round takes the lightest of the next (24 key tiles at most per CTA instead of
-  // 27 for 8 x 12 x 8 items on 148 CTAs).
-  auto nth_item = [&](int r) {
-    const int w = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
-    return w < n_items ? w : -1;
-  };
-  struct Item { int h, q0, n_kv, row0, qt, j0, half, slot; bool split; };
-  auto item_of = [&](int w) {
-    Item it;
-    it.h = w % p.H;
-    const int seq = (w / p.H) % p.B;
-    const int v = w / (p.H * p.B);
-    if (!SPLIT) {                                      // heaviest (longest causal prefix) first
-      it.qt = p.q_tiles - 1 - v;
-      it.half = 0;
-    } else {                                           // whole tiles and halves in descending order of their key tiles (host table)
-      const unsigned e = __ldg(p.order + v);
-      it.qt = (int)(e >> 1);
-      it.half = (int)(e & 1);
-    }
-    it.split = SPLIT && it.qt >= p.split_from;
-    it.q0 = it.qt * kRows;
-    const int n = it.qt + 1;                           // causal: key tiles 0..qt
-    it.j0 = it.split && it.half ? n >> 1 : 0;          // this item's key tiles: j0 .. j0 + n_kv - 1
-    it.n_kv = (it.split && !it.half ? n >> 1 : n) - it.j0;
-    it.slot = it.split ? (seq * p.H + it.h) * n_split + (it.qt - p.split_from) : 0;
-    it.row0 = seq * p.T;                               // this sequence's first row in Q, K, V and the output
-    return it;
-  };
-
-  if (threadIdx.x == 32) {
-    prefetch_tensormap(&map_q);
-    prefetch_tensormap(&map_k);
-    prefetch_tensormap(&map_v);
-    prefetch_tensormap(&map_qt);
-    prefetch_tensormap(&map_kt);
-    prefetch_tensormap(&map_vt);
-  }
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(k_full + 8 * s, 1);
-      mbar_init(k_empty + 8 * s, 1);
-      mbar_init(v_full + 8 * s, 1);
-      mbar_init(v_empty + 8 * s, 1);
-      mbar_init(sfull0 + 8 * s, 1);
-    }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(pfull0 + 8 * i, 128);
-      mbar_init(ofull0 + 8 * i, 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  // Everything above overlapped the previous kernel's tail; Q, K and V are its output.
-  pdl_wait();
-  pdl_launch_dependents();
-  const uint32_t tmem_base = tmem_base_slot;
-  // columns: S0 0..127 | S1 128..255 | O_part[buffer] 256 + buffer * 64 | tails of P 384..511
-  const uint32_t tmem_o0 = tmem_base + 256;
-  const uint32_t tmem_pt = tmem_base + 384;
-  volatile int* abort_ptr = &abort_flag;
-  auto give_up = [&](int site) {
-    if (!*abort_ptr) { atomicCAS(p.status, 0, (p.kernel_index << 8) | site); *abort_ptr = 1; }
-  };
-
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int t = 0;                                     // key tiles loaded so far, over all items
-      bool ok = true;
-      for (int ii = 0; ok; ++ii) {
-        const int w = nth_item(ii);
-        if (w < 0) break;
-        const Item it = item_of(w);
-        // the Q tile is free once every Q K^T of the previous item has been executed
-        if (!mbar_wait(q_empty, (ii & 1) ^ 1, abort_ptr)) { give_up(0x13); break; }
-        // an operand buffer: the tile's two slabs, then the two slabs of its tails
-        auto load4 = [&](uint32_t dst, const CUtensorMap* heads, const CUtensorMap* tails, uint32_t bar, int first_row) {
-          mbar_expect_tx(bar, kOpBytes);
-          tma_load_3d(dst, heads, bar, 0, first_row, it.h);
-          tma_load_3d(dst + kSlab, heads, bar, 32, first_row, it.h);
-          tma_load_3d(dst + kTileBytes, tails, bar, 0, first_row, it.h);
-          tma_load_3d(dst + kTileBytes + kSlab, tails, bar, 32, first_row, it.h);
-        };
-        load4(q_smem, &map_q, &map_qt, q_full, it.row0 + it.q0);
-        for (int j = 0; j < it.n_kv; ++j, ++t) {
-          const uint32_t ph = t & 1;                   // one buffer: the phase alternates with every tile
-          if (!mbar_wait(k_empty, ph ^ 1, abort_ptr)) { give_up(0x11); ok = false; break; }
-          load4(k_smem, &map_k, &map_kt, k_full, it.row0 + (it.j0 + j) * kRows);
-          if (!mbar_wait(v_empty, ph ^ 1, abort_ptr)) { give_up(0x12); ok = false; break; }
-          load4(v_smem, &map_v, &map_vt, v_full, it.row0 + (it.j0 + j) * kRows);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      bool ok = true;
-      // Tiles are numbered over all items (t): S buffer and O_part buffer are t & 1, their phases (t >> 1) & 1;
-      // the single K and V buffers change phase with every tile.
-      auto issue_qk = [&](int t) {
-        const int s = t & 1;
-        if (!mbar_wait(k_full, t & 1, abort_ptr)) { give_up(0x22); ok = false; return; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kb = k_smem;
-        // 32 bytes of the head dimension per instruction (8 float32); heads x heads, heads x tails, tails x heads
-#pragma unroll
-        for (int pass = 0; pass < 3; ++pass) {
-          const uint32_t qa = q_smem + (pass == 2 ? kTileBytes : 0), ka = kb + (pass == 1 ? kTileBytes : 0);
-#pragma unroll
-          for (int kd = 0; kd < kTileSlabs * 4; ++kd) {
-            const uint32_t off = (uint32_t)(kd >> 2) * kSlab + (uint32_t)(kd & 3) * 32;
-            umma(tmem_base + (uint32_t)s * 128, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024), p.idesc_qk,
-                 (pass | kd) != 0 ? 1u : 0u, false);
-          }
-        }
-        umma_commit(sfull0 + 8 * s);
-        umma_commit(k_empty);
-      };
-      // P V of tile t: the 128 keys of both threads of a row pair into the O_part buffer (t & 1), as two
-      // runs of MMAs (a group's P occupies the first columns of its 64-column share of S).  In-order
-      // execution of the tensor pipe keeps S[s] intact until these reads of P are done (the next Q K^T
-      // into S[s] is issued later), and the buffer (t & 1) was folded by the softmax threads before
-      // they published P of tile t.
-      auto issue_pv = [&](int t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(v_full, t & 1, abort_ptr)) { give_up(0x23); ok = false; return; }
-        const uint32_t vb = v_smem;
-        const uint32_t o_addr = tmem_o0 + (uint32_t)s * 64;
-        for (int g = 0; g < 2; ++g) {
-          if (!mbar_wait(pfull0 + 8 * (g * 2 + s), ph, abort_ptr)) { give_up(0x24); ok = false; return; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          // P x V, P x tails of V, tails of P x V
-#pragma unroll
-          for (int pass = 0; pass < 3; ++pass) {
-            const uint32_t pa = pass == 2 ? tmem_pt : tmem_base + (uint32_t)s * 128;
-            const uint32_t va = vb + (pass == 1 ? kTileBytes : 0);
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              umma_ts(o_addr, pa + (uint32_t)(g * 64 + kk * 8), make_desc(va + (uint32_t)(g * 8 + kk) * 1024, kSlab, 512, 1),
-                      p.idesc_pv, (g | kk | pass) != 0 ? 1u : 0u, false);
-          }
-        }
-        umma_commit(ofull0 + 8 * s);
-        umma_commit(v_empty);
-      };
-      // An item's first scores: its Q must have landed; once its last scores are issued, the Q tile is handed back.
-      auto first_qk = [&](int ii, int t, int n_kv) {
-        if (!mbar_wait(q_full, ii & 1, abort_ptr)) { give_up(0x21); ok = false; return; }
-        issue_qk(t);
-        if (ok && n_kv == 1) umma_commit(q_empty);
-      };
-      int t = 0;
-      for (int ii = 0; ok; ++ii) {
-        const int w = nth_item(ii);
-        if (w < 0) break;
-        const int n_kv = item_of(w).n_kv;
-        // (The next item's first scores are NOT issued ahead of this item's last P V: the softmax warps
-        // wait for that P V to finish the item, and have the merge and the stores to do before they
-        // need the next scores.)
-        first_qk(ii, t, n_kv);
-        for (int j = 0; j < n_kv && ok; ++j) {
-#ifdef KB200_TRACE
-          ATTN_MMA_STAMP(tm); ++tm;
-#endif
-          if (j + 1 < n_kv) {
-            issue_qk(t + j + 1);                     // the next scores are computed while the softmax warps work on tile j
-            if (ok && j + 2 == n_kv) umma_commit(q_empty);
-          }
-#ifdef KB200_TRACE
-          ATTN_MMA_STAMP(tm); ++tm;
-#endif
-          if (ok) issue_pv(t + j);
-#ifdef KB200_TRACE
-          ATTN_MMA_STAMP(tm); ++tm;
-#endif
-        }
-        t += n_kv;
-      }
-    }
-  } else {
-    // ---------------- softmax / output (warps 2..9) ----------------
-    // Two threads share a query row (TMEM lane): thread g of the pair takes keys g*64 .. g*64+63 of every
-    // tile.  They keep ONE online-softmax state per row: each tile they exchange the maxima of their
-    // halves through shared memory (a 64-thread barrier per lane quadrant), so both use the same
-    // reference point, their probabilities go into one P V of 128 keys and one O_part, and thread g
-    // folds, normalises and stores head dims g*32 .. g*32+31.  Per item only the two partial row sums
-    // cross between them.
-    const int quad = warp & 3;
-    const int group = (warp - 2) >> 2;
-    const int row = quad * 32 + lane;              // row of the tile = TMEM lane
-    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const int c0 = group * 64;
-    // behind the operand buffers: [2 tile parities][2 groups][128 rows] maxima, [2 item parities][2][128] row sums
-    float* const xmax = reinterpret_cast<float*>(smem_raw + (v_smem - raw) + 2 * kTileBytes);
-    float* const xsum = xmax + 4 * kRows;
-    const int pair_barrier = 2 + quad;              // hardware barriers 2..5, 64 threads each
-    // The pair's barrier also carries the abort flag (an OR over what the 64 threads read before they
-    // arrived), so that both threads of a row take the same decision and neither waits for the other.
-    auto pair_sync_aborted = [&]() {
-      uint32_t any;
-      asm volatile(
-          "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %2, 0;\n\tbar.red.or.pred q, %1, 64, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-          : "=r"(any)
-          : "r"(pair_barrier), "r"((uint32_t)*abort_ptr)
-          : "memory");
-      return any != 0;
-    };
-    bool ok = true;
-    int t0 = 0;                                      // tiles of the items before this one
-    for (int ii = 0; ok; ++ii) {
-      const int w = nth_item(ii);
-      if (w < 0) break;
-      const Item it = item_of(w);
-      const int n_kv = it.n_kv;
-      float o[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[i] = 0.0f;
-      float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 0.0f;
-      // running output <- running output * alpha + this thread's 32 dims of the O_part of tile t
-      auto fold = [&](int t, float alpha) {
-        bool got = mbar_wait(ofull0 + 8 * (t & 1), (t >> 1) & 1, abort_ptr);
-        if (!got) give_up(0x32);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float v[32];
-        tmem_ld32(tmem_o0 + lane_addr + (uint32_t)((t & 1) * 64 + group * 32), v);
-        const float2 alpha2 = make_float2(alpha, alpha);
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 r2 = ffma2(make_float2(o[i], o[i + 1]), alpha2, make_float2(v[i], v[i + 1]));
-          o[i] = r2.x;
-          o[i + 1] = r2.y;
-        }
-      };
-      // Every thread of a pair passes the same barriers: a wait that ran out raises the CTA's flag and the
-      // thread carries on to the next barrier, after which both see the flag and leave together.
-      for (int j = 0; j < n_kv; ++j) {
-        const int t = t0 + j;
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(sfull0 + 8 * s, ph, abort_ptr)) give_up(0x31);
-        ATTN_STAMP(0, j);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128 + c0);
-        const bool diagonal = it.j0 + j == it.qt;
-        float va[32], vb[32];
-        tmem_ld32x2(s_addr, s_addr + 32, va, vb);       // both halves in flight, one wait
-        // the scale is positive (checked when the chain was matched), so the maximum commutes with it
-        float mx = -CUDART_INF_F;
-        if (diagonal) {
-          mx = row_max32<true>(va, mx, c0, row);
-          mx = row_max32<true>(vb, mx, c0 + 32, row);
-        } else {
-          mx = row_max32<false>(va, mx, 0, 0);
-          mx = row_max32<false>(vb, mx, 0, 0);
-        }
-        xmax[(s * 2 + group) * kRows + row] = mx;
-        if (pair_sync_aborted()) { ok = false; break; }
-        mx = fmaxf(mx, xmax[(s * 2 + (group ^ 1)) * kRows + row]);
-        // the first key of every tile at or below the diagonal is visible to every row, so the maximum is finite
-        const float m_new = fmaxf(m_run, mx * p.scale_log2);
-        const float alpha = ex2(m_run - m_new);       // 0 while m_run = -inf
-        float sum;
-        if (diagonal) {
-          sum = probabilities32<true>(va, p.scale_log2, m_new, c0, row);
-          sum += probabilities32<true>(vb, p.scale_log2, m_new, c0 + 32, row);
-        } else {
-          sum = probabilities32<false>(va, p.scale_log2, m_new, 0, 0);
-          sum += probabilities32<false>(vb, p.scale_log2, m_new, 0, 0);
-        }
-        // Fold the PREVIOUS tile's O_part first: that it is complete also says that its P V has read the
-        // tails of P, whose single buffer is written next.
-        if (j > 0) fold(t - 1, alpha_prev);
-        ATTN_STAMP(3, j);
-        {
-          const uint32_t pt_addr = tmem_pt + lane_addr + (uint32_t)c0;
-          float ta[32];
-          tmem_st32(s_addr, va);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ta[i] = va[i] - __uint_as_float(__float_as_uint(va[i]) & 0xFFFFE000u);
-          tmem_st32(pt_addr, ta);
-          tmem_st32(s_addr + 32, vb);
-          float tb[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) tb[i] = vb[i] - __uint_as_float(__float_as_uint(vb[i]) & 0xFFFFE000u);
-          tmem_st32(pt_addr + 32, tb);
-        }
-        tmem_st_wait();
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(pfull0 + 8 * (group * 2 + s));
-        ATTN_STAMP(1, j);
-        alpha_prev = alpha;
-        l_run = l_run * alpha + sum;
-        m_run = m_new;
-      }
-      if (ok) fold(t0 + n_kv - 1, alpha_prev);
-      t0 += n_kv;
-      ATTN_STAMP(2, 3 * ii);
-      // ---- the row sum is the two threads' partial sums; thread g normalises and stores dims g*32 .. g*32+31 ----
-      xsum[((ii & 1) * 2 + group) * kRows + row] = l_run;
-      if (pair_sync_aborted()) ok = false;
-      ATTN_STAMP(2, 3 * ii + 1);
-      // ---- a split item: leave this half's rows and state in the workspace; whoever arrives second merges.
-      // Nobody waits for the other half.  The arrival is counted per lane quadrant (its 64 threads have a
-      // barrier of their own, the one that also carries the abort flag), so no CTA-wide barrier is needed.
-      bool writes = ok;
-      float l_tot = ok ? l_run + xsum[((ii & 1) * 2 + (group ^ 1)) * kRows + row] : 1.0f;
-      if (SPLIT && ok && it.split) {
-        float* const mine = p.partial + ((size_t)it.slot * 2 + it.half) * kPartialFloats;
-        const float* const other = p.partial + ((size_t)it.slot * 2 + (it.half ^ 1)) * kPartialFloats;
-        float4* const mine4 = reinterpret_cast<float4*>(mine + row * kHeadDim + group * 32);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) __stcg(mine4 + i, make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
-        if (group == 0) {
-          __stcg(mine + kRows * kHeadDim + row, m_run);
-          __stcg(mine + kRows * kHeadDim + kRows + row, l_tot);
-        }
-        __threadfence();
-        if (pair_sync_aborted()) ok = false;          // the quadrant's 64 threads have written and fenced
-        if (ok) {
-          if (lane == 0 && group == 0) {
-            arrived[quad] = atomicAdd(p.arrivals + it.slot * 4 + quad, 1);
-            __threadfence();
-          }
-          if (pair_sync_aborted()) ok = false;
-        }
-        if (ok) {
-          writes = arrived[quad] != 0;
-          if (writes) {
-            if (lane == 0 && group == 0) p.arrivals[it.slot * 4 + quad] = 0;      // for the next launch
-            const float m2 = __ldcg(other + kRows * kHeadDim + row), l2 = __ldcg(other + kRows * kHeadDim + kRows + row);
-            const float m = fmaxf(m_run, m2);
-            const float a1 = ex2(m_run - m), a2 = ex2(m2 - m);
-            // Products rounded one by one and then added (no fused multiply-add): symmetric in the two
-            // halves, so the bits do not depend on which of them merges.
-            l_tot = __fadd_rn(__fmul_rn(l_tot, a1), __fmul_rn(l2, a2));
-            const float4* const other4 = reinterpret_cast<const float4*>(other + row * kHeadDim + group * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 o2 = __ldcg(other4 + i);
-              o[4 * i] = __fadd_rn(__fmul_rn(o[4 * i], a1), __fmul_rn(o2.x, a2));
-              o[4 * i + 1] = __fadd_rn(__fmul_rn(o[4 * i + 1], a1), __fmul_rn(o2.y, a2));
-              o[4 * i + 2] = __fadd_rn(__fmul_rn(o[4 * i + 2], a1), __fmul_rn(o2.z, a2));
-              o[4 * i + 3] = __fadd_rn(__fmul_rn(o[4 * i + 3], a1), __fmul_rn(o2.w, a2));
-            }
-          }
-        }
-      }
-      if (ok && writes) {
-        const float inv = 1.0f / l_tot;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] *= inv;
-        // a lane holds 32 dims of ONE row: 128 contiguous bytes
-        float* const dst = p.out + (int64_t)(it.row0 + it.q0 + row) * p.out_row_stride + it.h * kHeadDim + group * 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
-      }
-      ATTN_STAMP(2, 3 * ii + 2);
-    }
-  }
-
-  // ---------------- common exit ----------------
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-#ifdef KB200_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    unsigned long long g;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
-    printf("ATTN block0 globaltimer start %lld end %lld (ns) dur %lld | exit cycles %lld n_kv %d\n", marks[0], (long long)g,
-           (long long)g - marks[0], clock64() - marks[1], item_of(blockIdx.x).n_kv);
-    printf("softmax thread per item (tiles done, states exchanged, rows stored):");
-    for (int j = 0; j < 15; ++j) printf(" %lld", trace[2][j] - marks[1]);
-    printf("\n");
-    printf("MMA thread (per tile: loop top, after Q K^T of the next tile, after P V):");
-    for (int j = 0; j < 48; ++j) printf(" %lld", mma_trace[j] - marks[1]);
-    printf("\n");
-    for (int j = 0; j < item_of(blockIdx.x).n_kv && j < 16; ++j)
-      printf("kv %2d  s_ready %7lld p_stored %7lld folded %7lld\n", j, trace[0][j] - marks[1], trace[1][j] - marks[1],
-             trace[3][j] - marks[1]);
-  }
-#endif
-  if (abort_flag && threadIdx.x == 0) {
-    for (uint32_t i = 0; i < 4096u; ++i)
-      if ((mbar_try_wait(k_full, 0) || mbar_try_wait(k_full, 1)) && (mbar_try_wait(v_full, 0) || mbar_try_wait(v_full, 1))) break;
   }
   __syncthreads();
   if (warp == 2) {
@@ -1486,10 +1116,10 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
                     encode_map(&st->map_qt, false, st->tails + (c.q - lo), hd, B * T, H, rs, hd, 32, kRows, false) &&
                     encode_map(&st->map_kt, false, st->tails + (c.k - lo), hd, B * T, H, rs, hd, 32, kRows, false) &&
                     encode_map(&st->map_vt, false, st->tails + (c.v - lo), hd, B * T, H, rs, hd, 32, kRows, true) &&
-                    cudaFuncSetAttribute(attention_exact_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExactSmemBytes) ==
-                        cudaSuccess &&
-                    cudaFuncSetAttribute(attention_exact_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExactSmemBytes) ==
-                        cudaSuccess;
+                    cudaFuncSetAttribute(attention_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kExactSmemBytes) == cudaSuccess &&
+                    cudaFuncSetAttribute(attention_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kExactSmemBytes) == cudaSuccess;
     if (!ok) {
       cudaGetLastError();
       if (st->tails) cudaFree(st->tails);
@@ -1497,11 +1127,11 @@ bool finish_fusion(Plan& plan, const AttnChain& c) {
       return false;
     }
   }
-  if (cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
-      cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
+  if (cudaFuncSetAttribute(attention_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
+      cudaFuncSetAttribute(attention_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(false)) != cudaSuccess ||
       cudaFuncSetAttribute(attention_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmemBytes) != cudaSuccess ||
-      cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess ||
-      cudaFuncSetAttribute(attention_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess) {
+      cudaFuncSetAttribute(attention_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess ||
+      cudaFuncSetAttribute(attention_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem(true)) != cudaSuccess) {
     cudaGetLastError();
     delete st;
     return false;
@@ -1853,28 +1483,30 @@ int attention_launch(const Plan& plan, const PlanKernel& k, cudaStream_t s) {
     const int64_t blocks = (st->span_n4 + 255) / 256;
     KB200_CUDA(launch_kernel(plan.pdl, tails_kernel, dim3((unsigned)(blocks < 1184 ? blocks : 1184)), dim3(256), 0, s,
                              reinterpret_cast<const float4*>(st->span_lo), reinterpret_cast<float4*>(st->tails), st->span_n4));
+    // (the store maps are not used by this instantiation)
     if (split)
-      KB200_CUDA(launch_kernel(plan.pdl, attention_exact_kernel<true>, st->grid, dim3(kAttnThreads), kExactSmemBytes, s, st->map_q,
-                               st->map_k, st->map_v, st->map_qt, st->map_kt, st->map_vt, st->params));
+      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false, true, true>, st->grid, dim3(kAttnThreads), kExactSmemBytes, s, st->map_q,
+                               st->map_k, st->map_v, st->map_out, st->map_out16, st->map_qt, st->map_kt, st->map_vt, st->params));
     else
-      KB200_CUDA(launch_kernel(plan.pdl, attention_exact_kernel<false>, st->grid, dim3(kAttnThreads), kExactSmemBytes, s, st->map_q,
-                               st->map_k, st->map_v, st->map_qt, st->map_kt, st->map_vt, st->params));
+      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false, false, true>, st->grid, dim3(kAttnThreads), kExactSmemBytes, s, st->map_q,
+                               st->map_k, st->map_v, st->map_out, st->map_out16, st->map_qt, st->map_kt, st->map_vt, st->params));
   } else if (st->exact) {
     KB200_CUDA(launch_kernel(plan.pdl, attention_fp32_kernel, st->grid, dim3(kFThreads), kFSmemBytes, s, st->f32));
   } else if (st->bf16) {
+    // (the maps of the tails are not used by these instantiations: any valid map will do)
     if (split)
-      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true, true>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q,
-                               st->map_k, st->map_v, st->map_out, st->map_out16, st->params));
+      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true, true, false>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q,
+                               st->map_k, st->map_v, st->map_out, st->map_out16, st->map_q, st->map_k, st->map_v, st->params));
     else
-      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true, false>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q,
-                               st->map_k, st->map_v, st->map_out, st->map_out16, st->params));
+      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<true, false, false>, st->grid, dim3(kAttnThreads), attn_smem(true), s, st->map_q,
+                               st->map_k, st->map_v, st->map_out, st->map_out16, st->map_q, st->map_k, st->map_v, st->params));
   } else {
     if (split)
-      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false, true>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
-                               st->map_k, st->map_v, st->map_out, st->map_out16, st->params));
+      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false, true, false>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
+                               st->map_k, st->map_v, st->map_out, st->map_out16, st->map_q, st->map_k, st->map_v, st->params));
     else
-      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false, false>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
-                               st->map_k, st->map_v, st->map_out, st->map_out16, st->params));
+      KB200_CUDA(launch_kernel(plan.pdl, attention_kernel<false, false, false>, st->grid, dim3(kAttnThreads), attn_smem(false), s, st->map_q,
+                               st->map_k, st->map_v, st->map_out, st->map_out16, st->map_q, st->map_k, st->map_v, st->params));
   }
   if (st->staged_out && st->final_out) {
     const int64_t n4 = st->out_elems / 4;
