@@ -25,13 +25,14 @@ Timed regions, each K steps bracketed by barrier + synchronize, CUDA events, max
           host-to-device copy and every result's device-to-host copy inside the timed region;
           e2e.copy_only_ms is the same step with the kernels left out (the host link alone);
   extras.strong_scaling   64 sequences in total, 64 / N per GPU (BASELINE config 4's sharding).
-A step touches 64 x 3 MiB of inputs plus six 10-17 MiB arenas, more than the 126 MB L2, so no
+A step touches 64 x 3 MiB of inputs plus eight arenas of tens of MiB, more than the 126 MB L2, so no
 explicit flush is needed between iterations; the weights stay L2-resident, as in serving.
 
 ``extras`` (rank 0 of a one-GPU run) measures every other BASELINE configuration at its stated
 precision whatever --precision says: the 128-token block in FP32, the 2048-token MLP in TF32,
 the six Linear shapes in TF32 and BF16, the fused memory-bound ops in FP32, the 2048-token
-block; and, in a process of its own, the reference's Triton backend on the same shapes.
+block (in the run's precision and in FP32); and, in a process of its own, the reference's Triton
+backend on the same shapes.
 
 --impl reference times the CPU implementation of the same block (eager PyTorch float32 on the
 host cores, the stand-in for the reference's MLIR CPU backend, see oracle/torch_block.py) on a
